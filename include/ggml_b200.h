@@ -1,0 +1,151 @@
+/* ggml_b200.h — C ABI of libggml-b200.so, a CUDA (sm_100a) implementation of
+ * the ggml quantized mat-mul / flash-attention hot path.
+ *
+ * Two faces:
+ *   1. op-level entry points (this file): plain pointers and sizes, what an
+ *      FFI crate binds when it wants one op at a time;
+ *   2. the ggml backend plug-in vtables (ggml_b200_backend.h): what the ggml
+ *      crate's registry loads with dlopen and drives through graph_compute.
+ *
+ * Every entry point returns a ggml status code and never aborts:
+ * crates/ggml/src/backend.rs:54-62 (GgmlStatus).
+ */
+#ifndef GGML_B200_H
+#define GGML_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* enum ggml_status — crates/ggml/src/backend.rs:54-62, sysffi.rs:360-364 */
+enum b200_status {
+    B200_STATUS_SUCCESS = 0,
+    B200_STATUS_ALLOC_FAILED = 1,
+    B200_STATUS_OUT_OF_MEMORY = 2,
+    B200_STATUS_BACKEND_ERROR = 3,
+    B200_STATUS_ABORTED = 4,
+    /* argument errors are reported as BACKEND_ERROR + b200_last_error() text */
+};
+
+/* enum ggml_type (GGUF wire ids) — crates/ggml/src/types.rs:15-53 */
+enum b200_type {
+    B200_TYPE_F32 = 0,
+    B200_TYPE_F16 = 1,
+    B200_TYPE_Q4_0 = 2,
+    B200_TYPE_Q8_0 = 8,
+    B200_TYPE_Q4_K = 12,
+    B200_TYPE_Q6_K = 14,
+    B200_TYPE_Q8_K = 15,
+    B200_TYPE_I32 = 26,
+    B200_TYPE_I64 = 27,
+    B200_TYPE_MXFP4 = 39,
+};
+
+/* Activation quantizers of the CPU path (which Q8 blocks an op builds):
+ *   A1 quantize_row_q8_0       crates/ggml/src/quants.rs:331-362
+ *   A2 quantize_row_q8_K       crates/ggml/src/quants.rs:615-654
+ *   A3 quantize_mat_q8_K_4x8   crates/ggml/src/repack.rs:1561-1606 (values) */
+enum b200_act_quant { B200_ACT_Q8_0 = 1, B200_ACT_Q8_K = 2, B200_ACT_Q8_K_4X8 = 3 };
+
+/* Which CPU route's arithmetic a mat-mul reproduces (crates/ggml/src/compute.rs:1420-1841).
+ * AUTO picks what the reference picks for (type, N, M). */
+enum b200_route { B200_ROUTE_AUTO = 0, B200_ROUTE_ROWDOT = 1, B200_ROUTE_REPACK = 2, B200_ROUTE_TILED = 3 };
+
+/* ---- library / device ---------------------------------------------------- */
+const char *b200_last_error(void);             /* thread-local text of the last failure */
+int b200_device_count(void);                   /* 0 when no CUDA device is usable */
+int b200_set_device(int device);
+int b200_device_info(int device, char *name, size_t name_len, size_t *free_bytes, size_t *total_bytes,
+                     int *sm_count, int *cc_major, int *cc_minor);
+int b200_synchronize(void *stream);
+
+/* ---- device memory (cudaMalloc-backed; buffers of the backend use the same) */
+int b200_malloc(void **dev_ptr, size_t bytes);
+int b200_free(void *dev_ptr);
+int b200_memcpy_h2d(void *dev_dst, const void *host_src, size_t bytes, void *stream);
+int b200_memcpy_d2h(void *host_dst, const void *dev_src, size_t bytes, void *stream);
+int b200_memset(void *dev_dst, int value, size_t bytes, void *stream);
+int b200_host_alloc_pinned(void **host_ptr, size_t bytes);
+int b200_host_free_pinned(void *host_ptr);
+
+/* ---- weights: device tile layout ------------------------------------------
+ * Quantized tensors live on the device in a 32-row interleaved tile layout
+ * (same bytes, re-ordered so that a warp reads 512 contiguous bytes per load).
+ * This replaces the CPU path's load-time CPU_REPACK interleave
+ * (crates/ggml/src/repack.rs:165,1435,3260; cache crates/ggml/src/compute.rs:698-775).
+ * n_rows = ne01 * ne02 * ne03 (experts are stacked rows), k = ne00. */
+size_t b200_weight_nbytes(int type, int64_t n_rows, int64_t k);   /* 0 = unsupported shape */
+/* host ggml blocks (row-major, ggml row size) -> device tile layout */
+int b200_weight_upload(int type, int64_t n_rows, int64_t k, const void *host_blocks, void *dev_tiles,
+                       void *stream);
+/* device tile layout -> host ggml blocks (round trip of the above) */
+int b200_weight_download(int type, int64_t n_rows, int64_t k, const void *dev_tiles, void *host_blocks,
+                         void *stream);
+/* dequantize_row(ty, ..) of every row: crates/ggml/src/quants.rs:1098 */
+int b200_dequantize(int type, int64_t n_rows, int64_t k, const void *dev_tiles, float *dev_out, void *stream);
+
+/* ---- activations ------------------------------------------------------------
+ * Runs the device quantizer on dev_x [m][k] f32 and returns the blocks in the
+ * CPU path's own byte layout (block_q8_0 / block_q8_K rows; block_q8_Kx4 tiles
+ * for A3, m % 4 == 0), for bit-exact comparison. */
+int b200_quantize_activations(int kind, int64_t m, int64_t k, const float *dev_x, void *host_blocks,
+                              void *stream);
+
+/* Device-side form of the same quantizers for callers that own the scratch:
+ * dev_act must hold b200_act_scratch_nbytes(m, k) bytes (256-byte aligned). One
+ * quantized activation can feed several mat-muls (wq/wk/wv read the same row). */
+size_t b200_act_scratch_nbytes(int64_t m, int64_t k);
+int b200_quantize_activations_device(int kind, int64_t m, int64_t k, const float *dev_x, int64_t ldx,
+                                     void *dev_act, void *stream);
+
+/* ---- events (timing on the launching stream; ggml's event_record / event_synchronize,
+ * crates/ggml/src/backend.rs:652-669) */
+int b200_event_create(void **event);
+int b200_event_destroy(void *event);
+int b200_event_record(void *event, void *stream);
+int b200_event_synchronize(void *event);
+int b200_event_elapsed_ms(void *start, void *stop, float *ms);
+
+/* ---- MUL_MAT — crates/ggml/src/compute.rs:1420 (forward_mul_mat), ops.rs:1329
+ * dst[m][n] = sum_k W[n][k] * X[m][k]; W in device tile layout, X/dst f32 on
+ * the device (row strides in elements).  route: enum b200_route. */
+int b200_mul_mat(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, const float *dev_x,
+                 int64_t ldx, float *dev_dst, int64_t lddst, int route, void *stream);
+/* the mat-mul proper on activations already quantized by
+ * b200_quantize_activations_device (act_kind must be the kind the route reads) */
+int b200_mul_mat_q8(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, const void *dev_act,
+                    int act_kind, float *dev_dst, int64_t lddst, int route, void *stream);
+/* same op with host activations / results: copies X in, runs, copies dst out */
+int b200_mul_mat_host(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, const float *host_x,
+                      float *host_dst, int route, void *stream);
+
+/* ---- MUL_MAT_ID — crates/ggml/src/compute.rs:1917 (forward_mul_mat_id), ops.rs:1421
+ * as: [n_expert][n][k] tiles (stacked rows); b: [n_tok][ne11][k] f32;
+ * ids: [n_tok][n_ids] i32; dst: [n_tok][n_ids][n] f32.  All device pointers. */
+int b200_mul_mat_id(int type, int64_t n, int64_t k, int64_t n_expert, int64_t ne11, int64_t n_tok,
+                    int64_t n_ids, const void *dev_as, const float *dev_b, const int32_t *dev_ids,
+                    float *dev_dst, int route, void *stream);
+
+/* ---- FLASH_ATTN_EXT — crates/ggml/src/compute.rs:4563, flash_attn.rs:907,920, ops.rs:2430
+ * q f32 [T][H][DK] by byte strides, k/v f16 by byte strides (KV-cache views,
+ * crates/llama/src/kv_cache.rs:2528-2579), mask f16 [T][n_kv] or NULL,
+ * dst f32 [T][H][DV] contiguous. */
+struct b200_flash_attn_args {
+    int64_t dk, dv, n_tok, n_head, n_head_kv, n_kv;
+    const float *q;      int64_t q_nb1, q_nb2;     /* bytes per token, per head */
+    const void *k;       int64_t k_nb1, k_nb2;     /* bytes per position, per kv head */
+    const void *v;       int64_t v_nb1, v_nb2;
+    const void *mask;    int64_t mask_nb1;         /* bytes per token row */
+    const float *sinks;                            /* [n_head] or NULL */
+    float scale, max_bias, logit_softcap;
+    float *dst;
+};
+int b200_flash_attn_ext(const struct b200_flash_attn_args *args, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GGML_B200_H */

@@ -1,0 +1,225 @@
+"""ctypes binding of libggml-b200.so (the C ABI in include/ggml_b200.h).
+
+This package holds no compute of its own: every call goes straight into the
+CUDA library, and importing it fails loudly when the library has not been
+built.  The directory name contains a dot, so load it by path:
+
+    import importlib.util, sys
+    spec = importlib.util.spec_from_file_location("llama_rust_b200", "<repo>/llama.rust_b200/__init__.py")
+    mod = importlib.util.module_from_spec(spec); sys.modules["llama_rust_b200"] = mod
+    spec.loader.exec_module(mod)
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libggml-b200.so")
+
+F32, F16, Q4_0, Q8_0, Q4_K, Q6_K, Q8_K, MXFP4 = 0, 1, 2, 8, 12, 14, 15, 39
+ACT_Q8_0, ACT_Q8_K, ACT_Q8_K_4X8 = 1, 2, 3
+ROUTE_AUTO, ROUTE_ROWDOT, ROUTE_REPACK, ROUTE_TILED = 0, 1, 2, 3
+STATUS_SUCCESS = 0
+
+# bytes per 256 elements of one row, in ggml block order
+GROUP_BYTES = {Q4_K: 144, Q6_K: 210, Q8_0: 8 * 34, Q4_0: 8 * 18, MXFP4: 8 * 17}
+
+
+class B200Error(RuntimeError):
+    pass
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise B200Error(f"{LIB_PATH} is missing: build it with `python llama.rust_b200/build.py`")
+    L = C.CDLL(LIB_PATH)
+    vp, i64, i32, sz = C.c_void_p, C.c_int64, C.c_int, C.c_size_t
+    L.b200_last_error.restype = C.c_char_p
+    L.b200_device_count.restype = i32
+    L.b200_set_device.argtypes = [i32]
+    L.b200_device_info.argtypes = [i32, C.c_char_p, sz, C.POINTER(sz), C.POINTER(sz), C.POINTER(i32),
+                                   C.POINTER(i32), C.POINTER(i32)]
+    L.b200_synchronize.argtypes = [vp]
+    L.b200_malloc.argtypes = [C.POINTER(vp), sz]
+    L.b200_free.argtypes = [vp]
+    L.b200_memcpy_h2d.argtypes = [vp, vp, sz, vp]
+    L.b200_memcpy_d2h.argtypes = [vp, vp, sz, vp]
+    L.b200_memset.argtypes = [vp, i32, sz, vp]
+    L.b200_host_alloc_pinned.argtypes = [C.POINTER(vp), sz]
+    L.b200_host_free_pinned.argtypes = [vp]
+    L.b200_weight_nbytes.restype = sz
+    L.b200_weight_nbytes.argtypes = [i32, i64, i64]
+    L.b200_weight_upload.argtypes = [i32, i64, i64, vp, vp, vp]
+    L.b200_weight_download.argtypes = [i32, i64, i64, vp, vp, vp]
+    L.b200_dequantize.argtypes = [i32, i64, i64, vp, vp, vp]
+    L.b200_quantize_activations.argtypes = [i32, i64, i64, vp, vp, vp]
+    L.b200_act_scratch_nbytes.restype = sz
+    L.b200_act_scratch_nbytes.argtypes = [i64, i64]
+    L.b200_quantize_activations_device.argtypes = [i32, i64, i64, vp, i64, vp, vp]
+    L.b200_mul_mat_q8.argtypes = [i32, i64, i64, i64, vp, vp, i32, vp, i64, i32, vp]
+    L.b200_event_create.argtypes = [C.POINTER(vp)]
+    L.b200_event_destroy.argtypes = [vp]
+    L.b200_event_record.argtypes = [vp, vp]
+    L.b200_event_synchronize.argtypes = [vp]
+    L.b200_event_elapsed_ms.argtypes = [vp, vp, C.POINTER(C.c_float)]
+    L.b200_mul_mat.argtypes = [i32, i64, i64, i64, vp, vp, i64, vp, i64, i32, vp]
+    L.b200_mul_mat_host.argtypes = [i32, i64, i64, i64, vp, vp, vp, i32, vp]
+    L.b200_mul_mat_id.argtypes = [i32, i64, i64, i64, i64, i64, i64, vp, vp, vp, vp, i32, vp]
+    L.b200_flash_attn_ext.argtypes = [vp, vp]
+    return L
+
+
+lib = _load()
+
+
+def check(rc, what=""):
+    if rc != STATUS_SUCCESS:
+        raise B200Error(f"{what}: status {rc}: {lib.b200_last_error().decode()}")
+
+
+def device_count():
+    return lib.b200_device_count()
+
+
+def set_device(i):
+    check(lib.b200_set_device(i), "set_device")
+
+
+def synchronize(stream=None):
+    check(lib.b200_synchronize(stream), "synchronize")
+
+
+class DeviceBuffer:
+    """A cudaMalloc allocation owned by Python."""
+
+    def __init__(self, nbytes):
+        self.nbytes = int(nbytes)
+        p = C.c_void_p()
+        check(lib.b200_malloc(C.byref(p), max(self.nbytes, 1)), "malloc")
+        self.ptr = p.value
+
+    def upload(self, arr, offset=0, stream=None):
+        arr = np.ascontiguousarray(arr)
+        assert offset + arr.nbytes <= self.nbytes
+        check(lib.b200_memcpy_h2d(self.ptr + offset, arr.ctypes.data, arr.nbytes, stream), "h2d")
+        synchronize(stream)
+        return self
+
+    def download(self, dtype, count, offset=0, stream=None):
+        out = np.empty(count, dtype=dtype)
+        assert offset + out.nbytes <= self.nbytes
+        check(lib.b200_memcpy_d2h(out.ctypes.data, self.ptr + offset, out.nbytes, stream), "d2h")
+        return out
+
+    def free(self):
+        if self.ptr:
+            lib.b200_free(self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def device_array(arr):
+    arr = np.ascontiguousarray(arr)
+    return DeviceBuffer(arr.nbytes).upload(arr)
+
+
+class Weight:
+    """A quantized [n_rows, k] tensor resident on the device in tile layout."""
+
+    def __init__(self, ty, blocks, k):
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        self.ty, self.k = ty, int(k)
+        self.row_bytes = self.k // 256 * GROUP_BYTES[ty]
+        self.n_rows = blocks.size // self.row_bytes
+        assert blocks.size == self.n_rows * self.row_bytes
+        nbytes = lib.b200_weight_nbytes(ty, self.n_rows, self.k)
+        if nbytes == 0 and self.n_rows:
+            raise B200Error(f"unsupported weight shape type={ty} rows={self.n_rows} k={k}")
+        self.buf = DeviceBuffer(nbytes)
+        check(lib.b200_weight_upload(ty, self.n_rows, self.k, blocks.ctypes.data, self.buf.ptr, None), "weight_upload")
+
+    @property
+    def ptr(self):
+        return self.buf.ptr
+
+    def download(self):
+        out = np.empty((self.n_rows, self.row_bytes), dtype=np.uint8)
+        check(lib.b200_weight_download(self.ty, self.n_rows, self.k, self.buf.ptr, out.ctypes.data, None),
+              "weight_download")
+        return out
+
+    def dequantize(self):
+        out = DeviceBuffer(self.n_rows * self.k * 4)
+        check(lib.b200_dequantize(self.ty, self.n_rows, self.k, self.buf.ptr, out.ptr, None), "dequantize")
+        return out.download(np.float32, self.n_rows * self.k).reshape(self.n_rows, self.k)
+
+
+def quantize_activations(kind, x):
+    """x f32 [m, k] -> the CPU path's block bytes (uint8, flat)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    m, k = x.shape
+    dx = device_array(x)
+    if kind == ACT_Q8_0:
+        nbytes = m * (k // 32) * 34
+    elif kind == ACT_Q8_K:
+        nbytes = m * (k // 256) * 292
+    else:
+        nbytes = (m // 4) * (k // 256) * 1168
+    out = np.zeros(nbytes, dtype=np.uint8)
+    check(lib.b200_quantize_activations(kind, m, k, dx.ptr, out.ctypes.data, None), "quantize_activations")
+    return out
+
+
+def mul_mat(w, x, route=ROUTE_AUTO):
+    """w: Weight [n, k]; x: f32 [m, k] host -> f32 [m, n] through the host-buffer entry point."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    m, k = x.shape
+    assert k == w.k
+    out = np.empty((m, w.n_rows), dtype=np.float32)
+    check(lib.b200_mul_mat_host(w.ty, w.n_rows, k, m, w.ptr, x.ctypes.data, out.ctypes.data, route, None), "mul_mat_host")
+    return out
+
+
+def mul_mat_device(w, dx, m, ddst, route=ROUTE_AUTO, stream=None):
+    """Device-resident activations and result (DeviceBuffer or raw pointers)."""
+    xp = dx.ptr if isinstance(dx, DeviceBuffer) else dx
+    dp = ddst.ptr if isinstance(ddst, DeviceBuffer) else ddst
+    check(lib.b200_mul_mat(w.ty, w.n_rows, w.k, m, w.ptr, xp, w.k, dp, w.n_rows, route, stream), "mul_mat")
+
+
+class Event:
+    """A CUDA event on the library's launching stream."""
+
+    def __init__(self):
+        p = C.c_void_p()
+        check(lib.b200_event_create(C.byref(p)), "event_create")
+        self.ptr = p.value
+
+    def record(self, stream=None):
+        check(lib.b200_event_record(self.ptr, stream), "event_record")
+
+    def synchronize(self):
+        check(lib.b200_event_synchronize(self.ptr), "event_synchronize")
+
+    def elapsed_ms(self, stop):
+        ms = C.c_float()
+        check(lib.b200_event_elapsed_ms(self.ptr, stop.ptr, C.byref(ms)), "event_elapsed")
+        return ms.value
+
+    def __del__(self):
+        try:
+            if self.ptr:
+                lib.b200_event_destroy(self.ptr)
+                self.ptr = None
+        except Exception:
+            pass
+
+
+def act_kind_for(ty):
+    return ACT_Q8_K if ty in (Q4_K, Q6_K) else ACT_Q8_0

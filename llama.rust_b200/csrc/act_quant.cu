@@ -1,0 +1,132 @@
+// On-the-fly Q8 quantization of f32 activation rows, bit-exact with the CPU
+// path's three value rules:
+//   A1 quantize_row_q8_0      crates/ggml/src/quants.rs:331-362
+//   A2 quantize_row_q8_K      crates/ggml/src/quants.rs:615-654
+//   A3 quantize_mat_q8_K_4x8  crates/ggml/src/repack.rs:1561-1606 (values; the
+//      4-row interleaved storage is a CPU detail, the device keeps plain rows)
+// Every float op is an explicit round-to-nearest intrinsic: no FMA contraction.
+#include "common.cuh"
+
+namespace b200 {
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+size_t act_scratch_bytes(int64_t m, int64_t k) {
+    size_t b = 0;
+    b += align_up((size_t)m * k, 256);            // qs
+    b += align_up((size_t)m * (k / 256) * 4, 256);  // d
+    b += align_up((size_t)m * (k / 16) * 2, 256);   // bsums
+    b += align_up((size_t)m * (k / 32) * 2, 256);   // dh
+    return b;
+}
+
+ActBuf act_carve(void *scratch, int64_t m, int64_t k) {
+    uint8_t *p = (uint8_t *)scratch;
+    ActBuf a;
+    a.k = k;
+    a.qs = (int8_t *)p;
+    p += align_up((size_t)m * k, 256);
+    a.d = (float *)p;
+    p += align_up((size_t)m * (k / 256) * 4, 256);
+    a.bsums = (int16_t *)p;
+    p += align_up((size_t)m * (k / 16) * 2, 256);
+    a.dh = (uint16_t *)p;
+    return a;
+}
+
+// A2 / A3: one CTA of 256 threads per (256-element block, row).
+template <bool A3>
+__global__ void __launch_bounds__(256) quantize_q8_K_kernel(const float *__restrict__ x, int64_t ldx, ActBuf out) {
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int64_t blk = blockIdx.x, row = blockIdx.y;
+    const int64_t nb = out.k / 256;
+    const float v = x[row * ldx + blk * 256 + t];
+    __shared__ float s_a[8];
+    __shared__ int s_i[8];
+    __shared__ float s_x[256];
+    s_x[t] = v;
+    // largest |v|, first index on ties (the CPU scans with a strict '>')
+    float a = fabsf(v);
+    int idx = t;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float a2 = __shfl_xor_sync(0xffffffffu, a, o);
+        int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (a2 > a || (a2 == a && i2 < idx)) { a = a2; idx = i2; }
+    }
+    if (lane == 0) { s_a[warp] = a; s_i[warp] = idx; }
+    __syncthreads();
+    a = s_a[0];
+    idx = s_i[0];
+#pragma unroll
+    for (int w = 1; w < 8; w++) {
+        float a2 = s_a[w];
+        if (a2 > a) { a = a2; idx = s_i[w]; }  // later warps have larger indices: strict '>' keeps the first
+    }
+    const float amax = a;
+    const float maxv = s_x[idx];
+    int q = 0;
+    float d = 0.0f;
+    if (amax != 0.0f) {
+        if (A3) {
+            const float iscale = __fdiv_rn(127.0f, amax);
+            q = __float2int_rn(__fmul_rn(iscale, v));  // round to nearest even
+            q = max(-128, min(127, q));
+            d = __fdiv_rn(1.0f, iscale);
+        } else {
+            const float iscale = __fdiv_rn(-127.0f, maxv);
+            // nearest_int(): crates/ggml/src/quants.rs:13-18
+            const float val = __fadd_rn(__fmul_rn(iscale, v), 12582912.0f);
+            q = (__float_as_int(val) & 0x007fffff) - 0x00400000;
+            q = min(127, q);
+            d = __fdiv_rn(1.0f, iscale);
+        }
+    }
+    out.qs[row * out.k + blk * 256 + t] = (int8_t)q;
+    int s = q;
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((t & 15) == 0) out.bsums[row * (out.k / 16) + blk * 16 + (t >> 4)] = (int16_t)s;
+    if (t == 0) out.d[row * nb + blk] = d;
+}
+
+// A1: one warp per 32-element block, 8 blocks per CTA.
+__global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float *__restrict__ x, int64_t ldx, ActBuf out) {
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int64_t row = blockIdx.y;
+    const int64_t blk = (int64_t)blockIdx.x * 8 + warp;
+    if (blk >= out.k / 32) return;
+    const float v = x[row * ldx + blk * 32 + lane];
+    float amax = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float id = amax != 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    const float r = rintf(__fmul_rn(v, id));
+    int q;
+    if (isnan(r) || fabsf(r) >= 2147483648.0f) q = -128;  // the AVX2 cvt/packs saturation
+    else q = max(-128, min(127, (int)r));
+    out.qs[row * out.k + blk * 32 + lane] = (int8_t)q;
+    if (lane == 0) out.dh[row * (out.k / 32) + blk] = __half_as_ushort(__float2half_rn(d));
+}
+
+int launch_quantize_acts(int kind, int64_t m, int64_t k, const float *x, int64_t ldx, ActBuf out, cudaStream_t s) {
+    B200_REQUIRE(m >= 0 && m <= 65535, "quantize: %lld activation rows exceed one launch (max 65535)", (long long)m);
+    if (m == 0) return B200_STATUS_SUCCESS;
+    if (kind == B200_ACT_Q8_0) {
+        B200_REQUIRE(k > 0 && k % 32 == 0, "quantize q8_0: k = %lld must be a positive multiple of 32", (long long)k);
+        dim3 grid((unsigned)((k / 32 + 7) / 8), (unsigned)m);
+        quantize_q8_0_kernel<<<grid, 256, 0, s>>>(x, ldx, out);
+    } else if (kind == B200_ACT_Q8_K || kind == B200_ACT_Q8_K_4X8) {
+        B200_REQUIRE(k > 0 && k % 256 == 0, "quantize q8_K: k = %lld must be a positive multiple of 256", (long long)k);
+        dim3 grid((unsigned)(k / 256), (unsigned)m);
+        if (kind == B200_ACT_Q8_K) quantize_q8_K_kernel<false><<<grid, 256, 0, s>>>(x, ldx, out);
+        else quantize_q8_K_kernel<true><<<grid, 256, 0, s>>>(x, ldx, out);
+    } else {
+        B200_REQUIRE(false, "quantize: unknown activation kind %d", kind);
+    }
+    B200_CUDA(cudaGetLastError());
+    return B200_STATUS_SUCCESS;
+}
+
+}  // namespace b200

@@ -1,0 +1,414 @@
+// Op-level C entry points of libggml-b200 (declared in include/ggml_b200.h).
+// Argument checking, scratch management and route selection live here; the
+// kernels are in the other translation units.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+
+namespace b200 {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char *what, const char *file, int line) {
+    set_error("CUDA error %d (%s) at %s:%d: %s", (int)e, cudaGetErrorString(e), file, line, what);
+    if (e == cudaErrorMemoryAllocation) return B200_STATUS_ALLOC_FAILED;
+    return B200_STATUS_BACKEND_ERROR;
+}
+
+// ---- scratch: one growing allocation per device ------------------------------
+struct Scratch {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+};
+static std::mutex g_scratch_mu;
+static Scratch g_scratch[64];
+
+int scratch_get(size_t bytes, void **ptr) {
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    B200_REQUIRE(dev >= 0 && dev < 64, "scratch: device index %d out of range", dev);
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    Scratch &s = g_scratch[dev];
+    if (s.bytes < bytes) {
+        if (s.ptr) {
+            // work queued on any stream may still read the old block
+            B200_CUDA(cudaDeviceSynchronize());
+            B200_CUDA(cudaFree(s.ptr));
+            s.ptr = nullptr;
+            s.bytes = 0;
+        }
+        size_t want = bytes + bytes / 4;
+        if (want < (size_t)8 << 20) want = (size_t)8 << 20;
+        B200_CUDA(cudaMalloc(&s.ptr, want));
+        s.bytes = want;
+    }
+    *ptr = s.ptr;
+    return B200_STATUS_SUCCESS;
+}
+
+// What the reference picks for (type, n, m): crates/ggml/src/compute.rs:1420-1841.
+static int pick_route(int type, int64_t n, int64_t m) {
+    switch (type) {
+        case B200_TYPE_Q4_K:
+            if (n % 8 == 0) return B200_ROUTE_REPACK;
+            return m >= 8 ? B200_ROUTE_TILED : B200_ROUTE_ROWDOT;
+        case B200_TYPE_Q6_K: return m >= 8 ? B200_ROUTE_TILED : B200_ROUTE_ROWDOT;
+        case B200_TYPE_Q8_0: return B200_ROUTE_ROWDOT;
+        case B200_TYPE_Q4_0:
+        case B200_TYPE_MXFP4: return n % 8 == 0 ? B200_ROUTE_REPACK : B200_ROUTE_ROWDOT;
+        default: return -1;
+    }
+}
+
+static size_t ggml_row_bytes(int type, int64_t k) { return (size_t)(k / GROUP_K) * group_src_bytes(type); }
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+const char *b200_last_error(void) { return g_err; }
+
+int b200_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+int b200_set_device(int device) {
+    B200_CUDA(cudaSetDevice(device));
+    return B200_STATUS_SUCCESS;
+}
+
+int b200_device_info(int device, char *name, size_t name_len, size_t *free_bytes, size_t *total_bytes, int *sm_count,
+                     int *cc_major, int *cc_minor) {
+    cudaDeviceProp p;
+    B200_CUDA(cudaGetDeviceProperties(&p, device));
+    if (name && name_len) snprintf(name, name_len, "%s", p.name);
+    if (sm_count) *sm_count = p.multiProcessorCount;
+    if (cc_major) *cc_major = p.major;
+    if (cc_minor) *cc_minor = p.minor;
+    if (free_bytes || total_bytes) {
+        int cur = 0;
+        B200_CUDA(cudaGetDevice(&cur));
+        B200_CUDA(cudaSetDevice(device));
+        size_t f = 0, t = 0;
+        cudaError_t e = cudaMemGetInfo(&f, &t);
+        cudaSetDevice(cur);
+        B200_CUDA(e);
+        if (free_bytes) *free_bytes = f;
+        if (total_bytes) *total_bytes = t;
+    }
+    return B200_STATUS_SUCCESS;
+}
+
+int b200_synchronize(void *stream) {
+    B200_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return B200_STATUS_SUCCESS;
+}
+
+int b200_malloc(void **dev_ptr, size_t bytes) {
+    B200_REQUIRE(dev_ptr != nullptr, "malloc: null out pointer");
+    *dev_ptr = nullptr;
+    if (bytes == 0) return B200_STATUS_SUCCESS;
+    B200_CUDA(cudaMalloc(dev_ptr, bytes));
+    return B200_STATUS_SUCCESS;
+}
+
+int b200_free(void *dev_ptr) {
+    if (dev_ptr) B200_CUDA(cudaFree(dev_ptr));
+    return B200_STATUS_SUCCESS;
+}
+
+int b200_memcpy_h2d(void *dst, const void *src, size_t bytes, void *stream) {
+    if (bytes == 0) return B200_STATUS_SUCCESS;
+    B200_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    return B200_STATUS_SUCCESS;
+}
+
+int b200_memcpy_d2h(void *dst, const void *src, size_t bytes, void *stream) {
+    if (bytes == 0) return B200_STATUS_SUCCESS;
+    B200_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    B200_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return B200_STATUS_SUCCESS;
+}
+
+int b200_memset(void *dst, int value, size_t bytes, void *stream) {
+    if (bytes == 0) return B200_STATUS_SUCCESS;
+    B200_CUDA(cudaMemsetAsync(dst, value, bytes, (cudaStream_t)stream));
+    return B200_STATUS_SUCCESS;
+}
+
+int b200_host_alloc_pinned(void **host_ptr, size_t bytes) {
+    B200_REQUIRE(host_ptr != nullptr, "host_alloc_pinned: null out pointer");
+    B200_CUDA(cudaMallocHost(host_ptr, bytes));
+    return B200_STATUS_SUCCESS;
+}
+
+int b200_host_free_pinned(void *host_ptr) {
+    if (host_ptr) B200_CUDA(cudaFreeHost(host_ptr));
+    return B200_STATUS_SUCCESS;
+}
+
+size_t b200_weight_nbytes(int type, int64_t n_rows, int64_t k) {
+    if (!is_quant_type(type) || n_rows < 0 || k <= 0 || k % GROUP_K != 0) return 0;
+    const int64_t tiles = (n_rows + TILE_ROWS - 1) / TILE_ROWS;
+    return (size_t)tiles * (size_t)(k / GROUP_K) * (size_t)chunk_bytes(type);
+}
+
+// Uploads in pieces of whole row tiles so that the staging copy stays small.
+int b200_weight_upload(int type, int64_t n_rows, int64_t k, const void *host_blocks, void *dev_tiles, void *stream) {
+    B200_REQUIRE(is_quant_type(type), "weight_upload: type %d is not a supported quantized type", type);
+    B200_REQUIRE(k > 0 && k % GROUP_K == 0, "weight_upload: k = %lld must be a positive multiple of 256", (long long)k);
+    B200_REQUIRE(n_rows >= 0, "weight_upload: negative row count");
+    if (n_rows == 0) return B200_STATUS_SUCCESS;
+    B200_REQUIRE(host_blocks && dev_tiles, "weight_upload: null pointer");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t rb = ggml_row_bytes(type, k);
+    const int64_t groups = k / GROUP_K;
+    int64_t rows_per_piece = ((int64_t)(64 << 20) / (int64_t)rb) / TILE_ROWS * TILE_ROWS;
+    if (rows_per_piece < TILE_ROWS) rows_per_piece = TILE_ROWS;
+    void *stage = nullptr;
+    B200_CUDA(cudaMalloc(&stage, (size_t)std::min<int64_t>(rows_per_piece, n_rows) * rb));
+    int rc = B200_STATUS_SUCCESS;
+    for (int64_t r0 = 0; r0 < n_rows && rc == B200_STATUS_SUCCESS; r0 += rows_per_piece) {
+        const int64_t nr = std::min<int64_t>(rows_per_piece, n_rows - r0);
+        cudaError_t e = cudaMemcpyAsync(stage, (const uint8_t *)host_blocks + (size_t)r0 * rb, (size_t)nr * rb,
+                                        cudaMemcpyHostToDevice, s);
+        if (e != cudaSuccess) { rc = cuda_fail(e, "cudaMemcpyAsync(stage)", __FILE__, __LINE__); break; }
+        uint8_t *dst = (uint8_t *)dev_tiles + (size_t)(r0 / TILE_ROWS) * groups * chunk_bytes(type);
+        rc = launch_repack(type, nr, k, (const uint8_t *)stage, dst, false, s);
+        if (rc == B200_STATUS_SUCCESS) {
+            e = cudaStreamSynchronize(s);
+            if (e != cudaSuccess) rc = cuda_fail(e, "cudaStreamSynchronize", __FILE__, __LINE__);
+        }
+    }
+    cudaFree(stage);
+    return rc;
+}
+
+int b200_weight_download(int type, int64_t n_rows, int64_t k, const void *dev_tiles, void *host_blocks, void *stream) {
+    B200_REQUIRE(is_quant_type(type), "weight_download: type %d is not a supported quantized type", type);
+    B200_REQUIRE(k > 0 && k % GROUP_K == 0, "weight_download: k = %lld must be a positive multiple of 256", (long long)k);
+    if (n_rows <= 0) return B200_STATUS_SUCCESS;
+    B200_REQUIRE(host_blocks && dev_tiles, "weight_download: null pointer");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t rb = ggml_row_bytes(type, k);
+    const int64_t groups = k / GROUP_K;
+    int64_t rows_per_piece = ((int64_t)(64 << 20) / (int64_t)rb) / TILE_ROWS * TILE_ROWS;
+    if (rows_per_piece < TILE_ROWS) rows_per_piece = TILE_ROWS;
+    void *stage = nullptr;
+    B200_CUDA(cudaMalloc(&stage, (size_t)std::min<int64_t>(rows_per_piece, n_rows) * rb));
+    int rc = B200_STATUS_SUCCESS;
+    for (int64_t r0 = 0; r0 < n_rows && rc == B200_STATUS_SUCCESS; r0 += rows_per_piece) {
+        const int64_t nr = std::min<int64_t>(rows_per_piece, n_rows - r0);
+        const uint8_t *src = (const uint8_t *)dev_tiles + (size_t)(r0 / TILE_ROWS) * groups * chunk_bytes(type);
+        rc = launch_repack(type, nr, k, src, (uint8_t *)stage, true, s);
+        if (rc != B200_STATUS_SUCCESS) break;
+        cudaError_t e = cudaMemcpyAsync((uint8_t *)host_blocks + (size_t)r0 * rb, stage, (size_t)nr * rb,
+                                        cudaMemcpyDeviceToHost, s);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+        if (e != cudaSuccess) rc = cuda_fail(e, "download copy", __FILE__, __LINE__);
+    }
+    cudaFree(stage);
+    return rc;
+}
+
+int b200_dequantize(int type, int64_t n_rows, int64_t k, const void *dev_tiles, float *dev_out, void *stream) {
+    return launch_dequantize(type, n_rows, k, (const uint8_t *)dev_tiles, dev_out, (cudaStream_t)stream);
+}
+
+int b200_quantize_activations(int kind, int64_t m, int64_t k, const float *dev_x, void *host_blocks, void *stream) {
+    B200_REQUIRE(m >= 0 && k > 0, "quantize_activations: bad shape m=%lld k=%lld", (long long)m, (long long)k);
+    B200_REQUIRE(kind != B200_ACT_Q8_K_4X8 || m % 4 == 0, "quantize_activations: the 4x8 form needs m %% 4 == 0");
+    if (m == 0) return B200_STATUS_SUCCESS;
+    cudaStream_t s = (cudaStream_t)stream;
+    void *scratch = nullptr;
+    int rc = scratch_get(act_scratch_bytes(m, k), &scratch);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    ActBuf a = act_carve(scratch, m, k);
+    rc = launch_quantize_acts(kind, m, k, dev_x, k, a, s);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    std::vector<int8_t> qs((size_t)m * k);
+    B200_CUDA(cudaMemcpyAsync(qs.data(), a.qs, qs.size(), cudaMemcpyDeviceToHost, s));
+    uint8_t *out = (uint8_t *)host_blocks;
+    if (kind == B200_ACT_Q8_0) {
+        const int64_t nb = k / 32;
+        std::vector<uint16_t> dh((size_t)m * nb);
+        B200_CUDA(cudaMemcpyAsync(dh.data(), a.dh, dh.size() * 2, cudaMemcpyDeviceToHost, s));
+        B200_CUDA(cudaStreamSynchronize(s));
+        for (int64_t r = 0; r < m; r++)
+            for (int64_t b = 0; b < nb; b++) {
+                uint8_t *blk = out + (r * nb + b) * 34;
+                memcpy(blk, &dh[r * nb + b], 2);
+                memcpy(blk + 2, &qs[r * k + b * 32], 32);
+            }
+        return B200_STATUS_SUCCESS;
+    }
+    const int64_t nb = k / 256;
+    std::vector<float> d((size_t)m * nb);
+    std::vector<int16_t> bs((size_t)m * (k / 16));
+    B200_CUDA(cudaMemcpyAsync(d.data(), a.d, d.size() * 4, cudaMemcpyDeviceToHost, s));
+    B200_CUDA(cudaMemcpyAsync(bs.data(), a.bsums, bs.size() * 2, cudaMemcpyDeviceToHost, s));
+    B200_CUDA(cudaStreamSynchronize(s));
+    if (kind == B200_ACT_Q8_K) {
+        for (int64_t r = 0; r < m; r++)
+            for (int64_t b = 0; b < nb; b++) {
+                uint8_t *blk = out + (r * nb + b) * 292;
+                memcpy(blk, &d[r * nb + b], 4);
+                memcpy(blk + 4, &qs[r * k + b * 256], 256);
+                memcpy(blk + 260, &bs[r * (k / 16) + b * 16], 32);
+            }
+    } else {  // block_q8_Kx4: crates/ggml/src/repack.rs:1557-1606
+        for (int64_t g = 0; g < m / 4; g++)
+            for (int64_t b = 0; b < nb; b++) {
+                uint8_t *blk = out + (g * nb + b) * 1168;
+                int16_t *obs = (int16_t *)(blk + 1040);
+                for (int r = 0; r < 4; r++) {
+                    const int64_t row = g * 4 + r;
+                    memcpy(blk + 4 * r, &d[row * nb + b], 4);
+                    for (int el = 0; el < 256; el++)
+                        blk[16 + (el / 8) * 32 + r * 8 + el % 8] = (uint8_t)qs[row * k + b * 256 + el];
+                    for (int j = 0; j < 16; j++) obs[16 * (j / 4) + 4 * r + j % 4] = bs[row * (k / 16) + b * 16 + j];
+                }
+            }
+    }
+    return B200_STATUS_SUCCESS;
+}
+
+size_t b200_act_scratch_nbytes(int64_t m, int64_t k) {
+    if (m < 0 || k <= 0 || k % 32 != 0) return 0;
+    return act_scratch_bytes(m, k);
+}
+
+int b200_quantize_activations_device(int kind, int64_t m, int64_t k, const float *dev_x, int64_t ldx, void *dev_act,
+                                     void *stream) {
+    B200_REQUIRE(m >= 0 && k > 0 && ldx >= k, "quantize_activations_device: bad shape");
+    if (m == 0) return B200_STATUS_SUCCESS;
+    B200_REQUIRE(dev_x && dev_act, "quantize_activations_device: null pointer");
+    B200_REQUIRE(((uintptr_t)dev_act & 255) == 0, "quantize_activations_device: scratch must be 256-byte aligned");
+    return launch_quantize_acts(kind, m, k, dev_x, ldx, act_carve(dev_act, m, k), (cudaStream_t)stream);
+}
+
+int b200_event_create(void **event) {
+    B200_REQUIRE(event != nullptr, "event_create: null out pointer");
+    cudaEvent_t e;
+    B200_CUDA(cudaEventCreate(&e));
+    *event = (void *)e;
+    return B200_STATUS_SUCCESS;
+}
+int b200_event_destroy(void *event) {
+    if (event) B200_CUDA(cudaEventDestroy((cudaEvent_t)event));
+    return B200_STATUS_SUCCESS;
+}
+int b200_event_record(void *event, void *stream) {
+    B200_CUDA(cudaEventRecord((cudaEvent_t)event, (cudaStream_t)stream));
+    return B200_STATUS_SUCCESS;
+}
+int b200_event_synchronize(void *event) {
+    B200_CUDA(cudaEventSynchronize((cudaEvent_t)event));
+    return B200_STATUS_SUCCESS;
+}
+int b200_event_elapsed_ms(void *start, void *stop, float *ms) {
+    B200_CUDA(cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)stop));
+    return B200_STATUS_SUCCESS;
+}
+
+static int check_mul_mat_args(int type, int64_t n, int64_t k, int64_t m) {
+    B200_REQUIRE(is_quant_type(type), "mul_mat: weight type %d is not supported", type);
+    B200_REQUIRE(n >= 0 && m >= 0 && k > 0, "mul_mat: bad shape n=%lld k=%lld m=%lld", (long long)n, (long long)k,
+                 (long long)m);
+    B200_REQUIRE(k % GROUP_K == 0, "mul_mat: k = %lld must be a multiple of 256", (long long)k);
+    return B200_STATUS_SUCCESS;
+}
+
+// which activation quantizer a (type, route) reads
+static int act_kind_for(int type, int route, int64_t m) {
+    (void)route;
+    (void)m;
+    return is_k_quant(type) ? B200_ACT_Q8_K : B200_ACT_Q8_0;
+}
+
+int b200_mul_mat_q8(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, const void *dev_act, int act_kind,
+                    float *dev_dst, int64_t lddst, int route, void *stream) {
+    int rc = check_mul_mat_args(type, n, k, m);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
+    B200_REQUIRE(dev_w && dev_act && dev_dst, "mul_mat_q8: null pointer");
+    B200_REQUIRE(lddst >= n, "mul_mat_q8: dst row stride smaller than n");
+    if (route == B200_ROUTE_AUTO) route = pick_route(type, n, m);
+    B200_REQUIRE(act_kind == act_kind_for(type, route, m), "mul_mat_q8: activation kind %d does not fit type %d", act_kind,
+                 type);
+    ActBuf a = act_carve(const_cast<void *>(dev_act), m, k);
+    return launch_gemv(type, route, n, k, m, (const uint8_t *)dev_w, a.view(), dev_dst, lddst, (cudaStream_t)stream);
+}
+
+int b200_mul_mat(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, const float *dev_x, int64_t ldx,
+                 float *dev_dst, int64_t lddst, int route, void *stream) {
+    B200_REQUIRE(is_quant_type(type), "mul_mat: weight type %d is not supported", type);
+    B200_REQUIRE(n >= 0 && m >= 0 && k > 0, "mul_mat: bad shape n=%lld k=%lld m=%lld", (long long)n, (long long)k,
+                 (long long)m);
+    B200_REQUIRE(k % GROUP_K == 0, "mul_mat: k = %lld must be a multiple of 256", (long long)k);
+    if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
+    B200_REQUIRE(dev_w && dev_x && dev_dst, "mul_mat: null pointer");
+    B200_REQUIRE(ldx >= k && lddst >= n, "mul_mat: row strides smaller than the rows");
+    if (route == B200_ROUTE_AUTO) route = pick_route(type, n, m);
+    cudaStream_t s = (cudaStream_t)stream;
+    void *scratch = nullptr;
+    int rc = scratch_get(act_scratch_bytes(m, k), &scratch);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    ActBuf a = act_carve(scratch, m, k);
+    const int kind = is_k_quant(type) ? B200_ACT_Q8_K : B200_ACT_Q8_0;
+    rc = launch_quantize_acts(kind, m, k, dev_x, ldx, a, s);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    return launch_gemv(type, route, n, k, m, (const uint8_t *)dev_w, a.view(), dev_dst, lddst, s);
+}
+
+int b200_mul_mat_host(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, const float *host_x,
+                      float *host_dst, int route, void *stream) {
+    B200_REQUIRE(n >= 0 && m >= 0 && k > 0, "mul_mat_host: bad shape");
+    if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t xb = (size_t)m * k * 4, ob = (size_t)m * n * 4;
+    // the activation scratch sits in front, the f32 staging behind it
+    const size_t act_b = act_scratch_bytes(m, k);
+    void *scratch = nullptr;
+    int rc = scratch_get(act_b + xb + ob + 512, &scratch);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    float *dx = (float *)((uint8_t *)scratch + act_b);
+    float *dout = (float *)((uint8_t *)dx + (xb + 255) / 256 * 256);
+    B200_CUDA(cudaMemcpyAsync(dx, host_x, xb, cudaMemcpyHostToDevice, s));
+    rc = b200_mul_mat(type, n, k, m, dev_w, dx, k, dout, n, route, stream);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    B200_CUDA(cudaMemcpyAsync(host_dst, dout, ob, cudaMemcpyDeviceToHost, s));
+    B200_CUDA(cudaStreamSynchronize(s));
+    return B200_STATUS_SUCCESS;
+}
+
+int b200_mul_mat_id(int, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, const void *, const float *,
+                    const int32_t *, float *, int, void *) {
+    set_error("mul_mat_id: not built yet");
+    return B200_STATUS_BACKEND_ERROR;
+}
+
+int b200_flash_attn_ext(const struct b200_flash_attn_args *, void *) {
+    set_error("flash_attn_ext: not built yet");
+    return B200_STATUS_BACKEND_ERROR;
+}
+
+}  // extern "C"

@@ -1,0 +1,149 @@
+// Shared declarations of libggml-b200: status handling, device helpers, the
+// device-side tile geometry of quantized tensors and the activation buffers.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "ggml_b200.h"
+
+namespace b200 {
+
+// ---- status / error text ---------------------------------------------------
+void set_error(const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what, const char *file, int line);
+
+#define B200_CUDA(call)                                                        \
+    do {                                                                       \
+        cudaError_t e__ = (call);                                              \
+        if (e__ != cudaSuccess) return b200::cuda_fail(e__, #call, __FILE__, __LINE__); \
+    } while (0)
+
+#define B200_REQUIRE(cond, ...)                                                \
+    do {                                                                       \
+        if (!(cond)) {                                                         \
+            b200::set_error(__VA_ARGS__);                                      \
+            return B200_STATUS_BACKEND_ERROR;                                  \
+        }                                                                      \
+    } while (0)
+
+// ---- tile geometry ---------------------------------------------------------
+// A quantized tensor of n_rows x k lives on the device as
+//   [row tile of 32 rows][group of 256 k-elements][region][sub-chunk][row][unit bytes]
+// so that lane r of a warp owns row r of the tile and every warp-wide load is
+// one contiguous 512-byte (16 B per lane) access.  The bytes are those of the
+// ggml blocks, only re-ordered; rows past n_rows in the last tile are zero.
+constexpr int TILE_ROWS = 32;
+constexpr int GROUP_K = 256;
+
+struct TileGeom {
+    int group_src_bytes;   // bytes of one row's 256-element group in ggml order
+    int chunk_bytes;       // bytes of one (tile, group) chunk = 32 * group_src_bytes
+};
+
+__host__ __device__ inline int group_src_bytes(int type) {
+    switch (type) {
+        case B200_TYPE_Q4_K: return 144;
+        case B200_TYPE_Q6_K: return 210;
+        case B200_TYPE_Q8_0: return 8 * 34;
+        case B200_TYPE_Q4_0: return 8 * 18;
+        case B200_TYPE_MXFP4: return 8 * 17;
+        default: return 0;
+    }
+}
+__host__ __device__ inline int chunk_bytes(int type) { return TILE_ROWS * group_src_bytes(type); }
+
+// Map byte p of a (tile, group) chunk to (row in tile, byte offset inside that
+// row's 256-element group in ggml block order).  Regions per type:
+//   Q4_K : [hdr 1x32x16][qs 8x32x16]           hdr = d, dmin, scales[12]
+//   Q6_K : [ql 8x32x16][qh 4x32x16][sc 1x32x16][d 1x32x2]
+//   Q8_0 : [qs 16x32x16][d 1x32x16]            sub s = block s/2, half s%2
+//   Q4_0 : [qs 8x32x16][d 1x32x16]             sub s = block s
+//   MXFP4: [qs 8x32x16][e 1x32x8]
+__host__ __device__ inline void chunk_byte_to_src(int type, int p, int *row, int *src) {
+    switch (type) {
+        case B200_TYPE_Q4_K: {
+            if (p < 512) { *row = p / 16; *src = p % 16; return; }
+            int q = p - 512, sub = q / 512, r = (q % 512) / 16, b = q % 16;
+            *row = r; *src = 16 + 16 * sub + b; return;
+        }
+        case B200_TYPE_Q6_K: {
+            if (p < 4096) { int sub = p / 512, r = (p % 512) / 16, b = p % 16; *row = r; *src = 16 * sub + b; return; }
+            if (p < 6144) { int q = p - 4096, sub = q / 512, r = (q % 512) / 16, b = q % 16; *row = r; *src = 128 + 16 * sub + b; return; }
+            if (p < 6656) { int q = p - 6144; *row = q / 16; *src = 192 + q % 16; return; }
+            { int q = p - 6656; *row = q / 2; *src = 208 + q % 2; return; }
+        }
+        case B200_TYPE_Q8_0: {
+            if (p < 8192) { int sub = p / 512, r = (p % 512) / 16, b = p % 16; *row = r; *src = 34 * (sub / 2) + 2 + 16 * (sub % 2) + b; return; }
+            { int q = p - 8192, r = q / 16, i = q % 16; *row = r; *src = 34 * (i / 2) + (i % 2); return; }
+        }
+        case B200_TYPE_Q4_0: {
+            if (p < 4096) { int sub = p / 512, r = (p % 512) / 16, b = p % 16; *row = r; *src = 18 * sub + 2 + b; return; }
+            { int q = p - 4096, r = q / 16, i = q % 16; *row = r; *src = 18 * (i / 2) + (i % 2); return; }
+        }
+        case B200_TYPE_MXFP4: {
+            if (p < 4096) { int sub = p / 512, r = (p % 512) / 16, b = p % 16; *row = r; *src = 17 * sub + 1 + b; return; }
+            { int q = p - 4096, r = q / 8, i = q % 8; *row = r; *src = 17 * i; return; }
+        }
+        default: *row = 0; *src = 0; return;
+    }
+}
+
+inline bool is_quant_type(int type) { return group_src_bytes(type) != 0; }
+inline bool is_k_quant(int type) { return type == B200_TYPE_Q4_K || type == B200_TYPE_Q6_K; }
+
+// ---- quantized activations on the device -----------------------------------
+// Structure of arrays; one instance holds m rows of k elements.
+//   Q8_K kinds (A2, A3): qs[m][k] i8, d[m][k/256] f32, bsums[m][k/16] i16
+//   Q8_0 (A1)          : qs[m][k] i8, dh[m][k/32] f16 bits (as the CPU stores them)
+struct ActView {
+    const int8_t *qs;
+    const float *d;        // Q8_K scales
+    const int16_t *bsums;  // Q8_K 16-element sums
+    const uint16_t *dh;    // Q8_0 scales (f16 bits)
+    int64_t k;
+};
+struct ActBuf {
+    int8_t *qs;
+    float *d;
+    int16_t *bsums;
+    uint16_t *dh;
+    int64_t k;
+    ActView view() const { return ActView{qs, d, bsums, dh, k}; }
+};
+size_t act_scratch_bytes(int64_t m, int64_t k);
+ActBuf act_carve(void *scratch, int64_t m, int64_t k);
+
+// ---- kernels' host launchers (each returns a b200_status) -------------------
+int launch_quantize_acts(int kind, int64_t m, int64_t k, const float *x, int64_t ldx, ActBuf out, cudaStream_t s);
+int launch_repack(int type, int64_t n_rows, int64_t k, const uint8_t *src_blocks, uint8_t *tiles, bool inverse,
+                  cudaStream_t s);
+int launch_dequantize(int type, int64_t n_rows, int64_t k, const uint8_t *tiles, float *out, cudaStream_t s);
+int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts,
+                float *dst, int64_t lddst, cudaStream_t s);
+
+// scratch owned by the library (one growing allocation per device)
+int scratch_get(size_t bytes, void **ptr);
+
+// ---- device helpers ----------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ float f16_bits_to_f32(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+// 16-byte streaming load: weights are read exactly once, keep them out of L1
+__device__ __forceinline__ uint4 ld_stream16(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float e8m0_half_to_f32(uint32_t e) {
+    // 2^(e-128): crates/ggml/src/quants.rs:682-691
+    uint32_t bits = e < 2 ? (0x00200000u << e) : ((e - 1) << 23);
+    return __uint_as_float(bits);
+}
+#endif
+
+}  // namespace b200

@@ -59,6 +59,7 @@ int orc_block_elems(int type);
 // 0 on success, -1 for an unsupported type or a k that is not a block multiple
 int orc_quantize_row(int type, const float *x, void *y, int64_t k);
 int orc_dequantize_row(int type, const void *x, float *y, int64_t k);
+int orc_quantize_rows(int type, const float *x, void *y, int64_t rows, int64_t k);
 
 // ---- activation quantizers (A1..A4) --------------------------------------
 void orc_quantize_row_q8_0(const float *x, void *y, int64_t k);            // A1
@@ -112,6 +113,8 @@ struct OrcFlashArgs {
 };
 int orc_flash_attn_ext(const OrcFlashArgs *a);
 
+int orc_mul_mat_repacked(int type, int64_t N, int64_t K, int64_t M, const void *Wrep, const float *X,
+                         float *out, int n_threads);
 int orc_num_threads();
 
 }  // extern "C"

@@ -17,6 +17,17 @@ static const int8_t KVALUES_MXFP4[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3,
 
 extern "C" int orc_num_threads() { return omp_get_max_threads(); }
 
+// rows x k f32 -> rows of blocks, rows spread over the host threads
+extern "C" int orc_quantize_rows(int type, const float *x, void *y, int64_t rows, int64_t k) {
+    const size_t rs = orc_row_size(type, k);
+    if (rs == 0) return -1;
+    int bad = 0;
+#pragma omp parallel for schedule(dynamic, 16)
+    for (int64_t r = 0; r < rows; r++)
+        if (orc_quantize_row(type, x + r * k, (uint8_t *)y + r * rs, k) != 0) bad = 1;
+    return bad ? -1 : 0;
+}
+
 // crates/ggml/src/vec_dot.rs:564-572 hsum8 (the AVX2 horizontal-add tree)
 static inline float hsum8(const float *a) {
     float r[4];

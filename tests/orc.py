@@ -41,6 +41,7 @@ def lib():
     L.orc_row_size.argtypes = [i32, i64]
     L.orc_quantize_row.argtypes = [i32, vp, vp, i64]
     L.orc_dequantize_row.argtypes = [i32, vp, vp, i64]
+    L.orc_quantize_rows.argtypes = [i32, vp, vp, i64, i64]
     L.orc_quantize_row_q8_0.argtypes = [vp, vp, i64]
     L.orc_quantize_row_q8_K.argtypes = [vp, vp, i64]
     L.orc_quantize_mat_q8_K_4x8.argtypes = [vp, i64, i64, vp]
@@ -79,9 +80,13 @@ def quantize(ty, x):
     return out.reshape(x.shape[:-1] + (rs,))
 
 
-def quantize_rows_fast(ty, x):
-    """Same as quantize() but one call per row block via OpenMP-free loop in C."""
-    return quantize(ty, x)
+def quantize_rows(ty, x):
+    """x: f32 [rows, k] -> uint8 [rows, row_size], rows spread over the host threads."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, k = x.shape
+    out = np.zeros((rows, row_size(ty, k)), dtype=np.uint8)
+    assert lib().orc_quantize_rows(ty, _p(x), _p(out), rows, k) == 0
+    return out
 
 
 def dequantize(ty, q, k):
