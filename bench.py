@@ -300,13 +300,51 @@ def run_b200(args, rank, world, barrier, reduce_max):
     print(json.dumps(line), flush=True)
 
 
+def run_profile_case(args):
+    """A small case for ncu: `--only NxK --launches R` runs R decode mat-muls of one shape,
+    rotating over enough weight copies to stay out of L2, and prints the event-timed mean."""
+    b = load_pkg()
+    b.set_device(0)
+    n, k = (int(v) for v in args.only.lower().split("x"))
+    wbytes = n * k * 144 // 256
+    copies = max(2, min(32, (300 << 20) // wbytes + 1))
+    W = synth_weights(n, k, seed=7)
+    weights = [b.Weight(Q4_K, W, k) for _ in range(copies)]
+    x = np.random.default_rng(8).standard_normal((1, k)).astype(np.float32)
+    dx, do = b.device_array(x), b.DeviceBuffer(4 * n)
+    act = b.DeviceBuffer(b.lib.b200_act_scratch_nbytes(1, k))
+    b.check(b.lib.b200_quantize_activations_device(b.ACT_Q8_K, 1, k, dx.ptr, k, act.ptr, None), "quantize")
+
+    def launch(i):
+        w = weights[i % copies]
+        b.check(b.lib.b200_mul_mat_q8(Q4_K, n, k, 1, w.ptr, act.ptr, b.ACT_Q8_K, do.ptr, n, 0, None), "mul_mat_q8")
+
+    for i in range(copies):
+        launch(i)
+    b.synchronize()
+    e0, e1 = b.Event(), b.Event()
+    e0.record()
+    for i in range(args.launches):
+        launch(i)
+    e1.record()
+    e1.synchronize()
+    us = e0.elapsed_ms(e1) * 1e3 / args.launches
+    print(json.dumps({"case": args.only, "copies": copies, "launches": args.launches, "us_per_launch": us,
+                      "gbs": algorithmic_bytes(n, k) / us / 1e3}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None, help="profile case: one shape NxK, see --launches")
+    ap.add_argument("--launches", type=int, default=64)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     args = ap.parse_args()
+    if args.only:
+        run_profile_case(args)
+        return
     rank, world, barrier, reduce_max = dist_setup(args.gpus)
     if args.impl == "reference":
         run_reference(args, rank, world)
