@@ -122,6 +122,27 @@ int b200_mul_mat_q8(int type, int64_t n, int64_t k, int64_t m, const void *dev_w
 int b200_mul_mat_host(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, const float *host_x,
                       float *host_dst, int route, void *stream);
 
+/* b200_mul_mat for callers that must not allocate.  It has no counterpart in the
+ * reference (whose CPU path takes its work buffer from the graph planner).
+ * b200_mul_mat keeps the quantized activations in a block it gets from
+ * cudaMalloc and may re-allocate; hosts that fixed their device-memory budget
+ * up front, that route every allocation through their own memory manager, or
+ * that call from a point where the allocator is out of reach use this form
+ * instead: its scratch is a fixed 256 KiB array inside the loaded module
+ * (b200_static_scratch_nbytes), one copy per device for the life of the
+ * process, and the call performs no allocation of any kind.
+ *  - m x k activations whose quantized form exceeds the array are refused with
+ *    B200_STATUS_BACKEND_ERROR and a message; nothing is launched.
+ *  - The first call on a device resolves the array's device address (that
+ *    device must be current); issue it before beginning any stream capture.
+ *  - Every call on a device shares the array, which keeps the previous call's
+ *    contents (none of it has to be zero on entry).  Calls in one stream are
+ *    ordered; calls whose kernels may overlap on the GPU race on the array. */
+size_t b200_static_scratch_nbytes(void);
+int b200_mul_mat_static_scratch(int type, int64_t n, int64_t k, int64_t m, const void *dev_w,
+                                const float *dev_x, int64_t ldx, float *dev_dst, int64_t lddst, int route,
+                                void *stream);
+
 /* ---- MUL_MAT_ID — crates/ggml/src/compute.rs:1917 (forward_mul_mat_id), ops.rs:1421
  * as: [n_expert][n][k] tiles (stacked rows); b: [n_tok][ne11][k] f32;
  * ids: [n_tok][n_ids] i32; dst: [n_tok][n_ids][n] f32.  All device pointers. */

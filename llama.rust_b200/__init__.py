@@ -64,6 +64,8 @@ def _load():
     L.b200_event_synchronize.argtypes = [vp]
     L.b200_event_elapsed_ms.argtypes = [vp, vp, C.POINTER(C.c_float)]
     L.b200_mul_mat.argtypes = [i32, i64, i64, i64, vp, vp, i64, vp, i64, i32, vp]
+    L.b200_static_scratch_nbytes.restype = sz
+    L.b200_mul_mat_static_scratch.argtypes = [i32, i64, i64, i64, vp, vp, i64, vp, i64, i32, vp]
     L.b200_mul_mat_host.argtypes = [i32, i64, i64, i64, vp, vp, vp, i32, vp]
     L.b200_mul_mat_id.argtypes = [i32, i64, i64, i64, i64, i64, i64, vp, vp, vp, vp, i32, vp]
     L.b200_flash_attn_ext.argtypes = [vp, vp]

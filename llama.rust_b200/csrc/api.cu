@@ -58,7 +58,7 @@ int scratch_get(size_t bytes, void **ptr) {
 }
 
 // What the reference picks for (type, n, m): crates/ggml/src/compute.rs:1420-1841.
-static int pick_route(int type, int64_t n, int64_t m) {
+int pick_route(int type, int64_t n, int64_t m) {
     switch (type) {
         case B200_TYPE_Q4_K:
             if (n % 8 == 0) return B200_ROUTE_REPACK;
@@ -69,6 +69,13 @@ static int pick_route(int type, int64_t n, int64_t m) {
         case B200_TYPE_MXFP4: return n % 8 == 0 ? B200_ROUTE_REPACK : B200_ROUTE_ROWDOT;
         default: return -1;
     }
+}
+
+// which activation quantizer a (type, route) reads
+int act_kind_for(int type, int route, int64_t m) {
+    (void)route;
+    (void)m;
+    return is_k_quant(type) ? B200_ACT_Q8_K : B200_ACT_Q8_0;
 }
 
 static size_t ggml_row_bytes(int type, int64_t k) { return (size_t)(k / GROUP_K) * group_src_bytes(type); }
@@ -335,13 +342,6 @@ static int check_mul_mat_args(int type, int64_t n, int64_t k, int64_t m) {
                  (long long)m);
     B200_REQUIRE(k % GROUP_K == 0, "mul_mat: k = %lld must be a multiple of 256", (long long)k);
     return B200_STATUS_SUCCESS;
-}
-
-// which activation quantizer a (type, route) reads
-static int act_kind_for(int type, int route, int64_t m) {
-    (void)route;
-    (void)m;
-    return is_k_quant(type) ? B200_ACT_Q8_K : B200_ACT_Q8_0;
 }
 
 int b200_mul_mat_q8(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, const void *dev_act, int act_kind,

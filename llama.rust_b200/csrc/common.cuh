@@ -127,6 +127,10 @@ int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint
 // scratch owned by the library (one growing allocation per device)
 int scratch_get(size_t bytes, void **ptr);
 
+// route the reference takes for (type, n, m), and the activation quantizer that route reads
+int pick_route(int type, int64_t n, int64_t m);
+int act_kind_for(int type, int route, int64_t m);
+
 // ---- device helpers ----------------------------------------------------------
 #ifdef __CUDACC__
 __device__ __forceinline__ float f16_bits_to_f32(uint16_t h) { return __half2float(__ushort_as_half(h)); }
