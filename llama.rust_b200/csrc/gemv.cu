@@ -11,6 +11,7 @@
 //   Q4_K 8x8 gemv   crates/ggml/src/repack.rs:1638-1688 (one fma per super-block
 //                   for the scale term and one for the min term, out = acc - accmin)
 #include "common.cuh"
+#include "gemv_types.cuh"
 
 namespace b200 {
 
@@ -139,6 +140,138 @@ static int launch_q4k(int64_t n, int nb, const uint8_t *tiles, ActView acts, flo
     return B200_STATUS_SUCCESS;
 }
 
+// ---------------------------------------------------------------------------
+// Generic decode kernel for the other (type, route) pairs, see gemv_types.cuh.
+// K is processed in windows of `win` groups so that the exchange array fits in
+// shared memory; the chain threads keep their accumulators in registers across
+// windows.  Chain threads: NCOL x CHAINS x 32, thread = (col, l, row).
+// ---------------------------------------------------------------------------
+template <class T, int NCOL>
+__global__ void __launch_bounds__(GEMV_MAX_WARPS * 32)
+gemv_generic_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *__restrict__ dst, int64_t lddst, int64_t n,
+                    int nb, int win) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    ActStage *stage = (ActStage *)smem + warp * NCOL;
+    float *fin = (float *)(smem + sizeof(ActStage) * nwarps * NCOL);       // [NCOL][8][32]
+    uint32_t *xch = (uint32_t *)(fin + NCOL * 8 * 32);                      // [NCOL][win][NW][32]
+    const int64_t tile = blockIdx.x;
+    const uint8_t *base = tiles + tile * (int64_t)nb * T::CHUNK;
+    const int ct = threadIdx.x;  // chain thread id
+    const bool is_chain = ct < NCOL * T::CHAINS * 32;
+    const int c_col = ct / (T::CHAINS * 32), c_l = (ct >> 5) % T::CHAINS, c_row = ct & 31;
+    float acc = 0.0f;
+
+    for (int w0 = 0; w0 < nb; w0 += win) {
+        const int wn = nb - w0 < win ? nb - w0 : win;
+        for (int g = warp; g < wn; g += nwarps) {
+            const int b = w0 + g;
+            typename T::Regs regs;
+            T::load(base + (int64_t)b * T::CHUNK, lane, regs);
+#pragma unroll
+            for (int col = 0; col < NCOL; col++) {
+                const int8_t *aq = acts.qs + (int64_t)col * acts.k + (int64_t)b * 256;
+                if (lane < 16) {
+                    stage[col].q[lane] = *(const uint4 *)(aq + lane * 16);
+                } else if (T::ACT_Q8K) {
+                    if (lane < 24) {
+                        const int j = lane - 16;
+                        const short2 s2 = *(const short2 *)(acts.bsums + (int64_t)col * (acts.k / 16) + (int64_t)b * 16 + 2 * j);
+                        stage[col].aux[2 * j] = s2.x;
+                        stage[col].aux[2 * j + 1] = s2.y;
+                    }
+                } else if (lane < 24) {
+                    const int blk = lane - 16;  // sum of the block's 32 quants
+                    const uint4 y0 = *(const uint4 *)(aq + blk * 32), y1 = *(const uint4 *)(aq + blk * 32 + 16);
+                    int sum = 0;
+                    sum = dp4(0x01010101u, y0.x, sum); sum = dp4(0x01010101u, y0.y, sum);
+                    sum = dp4(0x01010101u, y0.z, sum); sum = dp4(0x01010101u, y0.w, sum);
+                    sum = dp4(0x01010101u, y1.x, sum); sum = dp4(0x01010101u, y1.y, sum);
+                    sum = dp4(0x01010101u, y1.z, sum); sum = dp4(0x01010101u, y1.w, sum);
+                    stage[col].aux[8 + blk] = sum;
+                }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int col = 0; col < NCOL; col++)
+                T::compute(regs, stage[col], xch + ((int64_t)(col * win + g) * T::NW) * 32 + lane);
+            __syncwarp();
+        }
+        __syncthreads();
+        if (is_chain) {
+            for (int g = 0; g < wn; g++)
+                T::chain(acc, xch + ((int64_t)(c_col * win + g) * T::NW) * 32 + c_row, c_l, acts, c_col, w0 + g);
+        }
+        __syncthreads();
+    }
+    const int64_t row0 = tile * TILE_ROWS;
+    if (T::CHAINS == 1) {
+        if (is_chain && row0 + c_row < n) dst[(int64_t)c_col * lddst + row0 + c_row] = acc;
+    } else {
+        // hsum8 of the eight lane accumulators: crates/ggml/src/vec_dot.rs:564-572
+        if (is_chain) fin[(c_col * 8 + c_l) * 32 + c_row] = acc;
+        __syncthreads();
+        if (ct < NCOL * 32) {
+            const int col = ct >> 5, r = ct & 31;
+            const float *a = fin + col * 8 * 32 + r;
+            const float r0 = __fadd_rn(a[4 * 32], a[0]), r1 = __fadd_rn(a[5 * 32], a[32]);
+            const float r2 = __fadd_rn(a[6 * 32], a[2 * 32]), r3 = __fadd_rn(a[7 * 32], a[3 * 32]);
+            const float v = __fadd_rn(__fadd_rn(r0, r2), __fadd_rn(r1, r3));
+            if (row0 + r < n) dst[(int64_t)col * lddst + row0 + r] = v;
+        }
+    }
+}
+
+constexpr size_t GEMV_SMEM_LIMIT = 200 * 1024;
+
+template <class T, int NCOL>
+static int launch_generic(int64_t n, int nb, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
+                          cudaStream_t s) {
+    const size_t per_group = (size_t)NCOL * T::NW * 32 * 4;
+    // warps: enough chain threads, and an even split of the groups when possible
+    int nw = pick_warps(nb);
+    const int min_warps = NCOL * T::CHAINS;
+    if (nw < min_warps) nw = min_warps;
+    const size_t fixed = sizeof(ActStage) * nw * NCOL + (size_t)NCOL * 8 * 32 * 4;
+    int win = (int)((GEMV_SMEM_LIMIT - fixed) / per_group);
+    if (win > nb) win = nb;
+    if (win > nw && win % nw) win -= win % nw;  // whole rounds of warps per window
+    B200_REQUIRE(win >= 1, "gemv: shared memory too small for one group");
+    const size_t smem = fixed + per_group * win;
+    static bool attr_done = false;
+    if (!attr_done) {
+        B200_CUDA(cudaFuncSetAttribute(gemv_generic_kernel<T, NCOL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)GEMV_SMEM_LIMIT));
+        attr_done = true;
+    }
+    const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
+    gemv_generic_kernel<T, NCOL><<<(unsigned)tiles_n, nw * 32, smem, s>>>(tiles, acts, dst, lddst, n, nb, win);
+    B200_CUDA(cudaGetLastError());
+    return B200_STATUS_SUCCESS;
+}
+
+// columns in passes of at most MAXC; the weights are re-read per pass (decode shapes only)
+template <class T, int MAXC>
+static int run_generic(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
+                       cudaStream_t s) {
+    const int nb = (int)(k / GROUP_K);
+    for (int64_t c0 = 0; c0 < m; c0 += MAXC) {
+        const int nc = (int)(m - c0 < MAXC ? m - c0 : MAXC);
+        ActView a = acts;
+        a.qs += c0 * k;
+        if (a.d) a.d += c0 * nb;
+        if (a.bsums) a.bsums += c0 * (k / 16);
+        if (a.dh) a.dh += c0 * (k / 32);
+        float *o = dst + c0 * lddst;
+        int rc;
+        if (MAXC >= 2 && nc == 2) rc = launch_generic<T, (MAXC >= 2 ? 2 : 1)>(n, nb, tiles, a, o, lddst, s);
+        else if (nc == 1) rc = launch_generic<T, 1>(n, nb, tiles, a, o, lddst, s);
+        else rc = launch_generic<T, (MAXC >= 2 ? 2 : 1)>(n, nb, tiles, a, o, lddst, s);
+        if (rc != B200_STATUS_SUCCESS) return rc;
+    }
+    return B200_STATUS_SUCCESS;
+}
+
 int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst,
                 int64_t lddst, cudaStream_t s) {
     B200_REQUIRE(k % GROUP_K == 0, "gemv: k = %lld must be a multiple of 256", (long long)k);
@@ -159,7 +292,11 @@ int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint
         }
         return B200_STATUS_SUCCESS;
     }
-    B200_REQUIRE(false, "gemv: no kernel for type %d route %d", type, route);
+    if (type == B200_TYPE_Q6_K && route == B200_ROUTE_ROWDOT) return run_generic<TraitsQ6K, 1>(n, k, m, tiles, acts, dst, lddst, s);
+    if (type == B200_TYPE_Q8_0 && route == B200_ROUTE_ROWDOT) return run_generic<TraitsQ8_0, 1>(n, k, m, tiles, acts, dst, lddst, s);
+    if (type == B200_TYPE_Q4_0 && route == B200_ROUTE_REPACK) return run_generic<TraitsB32<false>, 2>(n, k, m, tiles, acts, dst, lddst, s);
+    if (type == B200_TYPE_MXFP4 && route == B200_ROUTE_REPACK) return run_generic<TraitsB32<true>, 2>(n, k, m, tiles, acts, dst, lddst, s);
+    B200_REQUIRE(false, "mul_mat: no kernel yet for weight type %d with route %d (m = %lld)", type, route, (long long)m);
 }
 
 }  // namespace b200

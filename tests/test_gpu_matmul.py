@@ -144,3 +144,43 @@ def test_empty_and_refused_shapes(dev):
     # all-zero activations give exact zeros
     z = dev.mul_mat(w, np.zeros((1, 256), dtype=np.float32))
     assert not z.any()
+
+
+# (type, route the reference takes, allowed m) for the other decode-shaped kernels
+OTHER_DECODE = [
+    (orc.Q6_K, orc.ROUTE_ROWDOT, [1, 2, 7]),     # row dot below 8 activation rows (compute.rs:1596)
+    (orc.Q8_0, orc.ROUTE_ROWDOT, [1, 3]),        # row dot; tinyBLAS gives the same values
+    (orc.Q4_0, orc.ROUTE_REPACK, [1, 2, 3]),     # 8x8 gemv == gemm per element
+    (orc.MXFP4, orc.ROUTE_REPACK, [1, 2, 5]),    # 8x8 gemv per activation row
+]
+
+
+@pytest.mark.parametrize("case", OTHER_DECODE, ids=lambda c: orc.TYPE_NAMES[c[0]])
+@pytest.mark.parametrize("shape", [(32, 256), (64, 512), (4096, 4096), (512, 14336), (40, 1024)], ids=str)
+def test_other_types_decode_mat_mul_bit_exact(dev, case, shape):
+    ty, route, ms = case
+    n, k = shape
+    W = synth.weights(ty, n, k, seed=15)
+    w = dev.Weight(ty, W, k)
+    for m in ms:
+        x = synth.activations(m, k, seed=16 + m)
+        want, r = orc.mul_mat(ty, W, x)
+        assert r == route
+        assert bits_equal(dev.mul_mat(w, x), want), f"m={m}"
+
+
+def test_golden_real_tensors_q6_K_and_mxfp4_blocks(dev, golden):
+    rt = golden("real_tensors")
+    ty, n, rows, cols, flags = (int(v) for v in rt["q6k_granite/hdr"])
+    got = dev.mul_mat(dev.Weight(ty, rt["q6k_granite/W"], n), rt["q6k_granite/act"])
+    assert bits_equal(got, rt["q6k_granite/plain_out"])
+    # the reference's hand-built MXFP4 blocks (every exponent, every code), tiled to 8 rows of 1024
+    q = golden("quants")
+    key = [k for k in q.files if k.startswith("MXFP4/raw/1024") and k.endswith("/q")][0]
+    W = np.tile(q[key].reshape(1, -1), (8, 1))
+    x = (synth.activations(1, 1024, seed=40) * 1e-3).astype(np.float32)
+    want, route = orc.mul_mat(orc.MXFP4, W, x)
+    assert route == orc.ROUTE_REPACK
+    got = dev.mul_mat(dev.Weight(orc.MXFP4, W, 1024), x)
+    same = (got.view(np.uint32) == want.view(np.uint32)) | (np.isnan(got) & np.isnan(want))
+    assert same.all()
