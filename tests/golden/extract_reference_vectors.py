@@ -11,7 +11,7 @@ not available.
     python tests/golden/extract_reference_vectors.py <reference_root>
 
 Outputs: quants.npz, mulmat.npz, repack.npz, real_tensors.npz, tiled.npz,
-fp16cvt.npz, flash_attn.npz.
+fp16cvt.npz, flash_attn.npz, flash_attn_probe.npz.
 """
 import os
 import struct
@@ -212,13 +212,55 @@ def extract_flash_attn(par, out):
     out["n_cases"] = np.array([kept], dtype=np.int64)
 
 
+def extract_flash_attn_probe(par, out):
+    """parity/fa_probe.bin (format: parity/ref_fa_probe.c:18-24): per probe the inputs, then records
+    (tag, t, nth, dst): tag 0 = the T-row run, 1 = the 1-row run of token t (split-KV from 512 KV
+    positions on, with nth chunks), 2 = rows 1..T-1.  Kept: the two S_kv = 600 probes."""
+    b = open(os.path.join(par, "fa_probe.bin"), "rb").read()
+    o, n = 0, len(b)
+
+    def sec():
+        nonlocal o
+        (ln,) = struct.unpack_from("<I", b, o)
+        s = b[o + 4:o + 4 + ln]
+        o += 4 + ln
+        return s
+
+    probe = -1
+    keep = False
+    while o < n:
+        (tag,) = struct.unpack_from("<I", b, o)
+        if tag == 0xF17E0001:
+            o += 4
+            probe += 1
+            geom = np.frombuffer(sec(), dtype=np.int64).copy()
+            knobs = f32(sec())
+            q, k, v, m, s = sec(), sec(), sec(), sec(), sec()
+            keep = int(geom[5]) >= 512
+            if keep:
+                key = f"probe{probe}"
+                out[key + "/geom"] = geom
+                out[key + "/knobs"] = knobs
+                out[key + "/q"] = f32(q)
+                out[key + "/k"] = np.frombuffer(k, dtype=np.uint16).copy()
+                out[key + "/v"] = np.frombuffer(v, dtype=np.uint16).copy()
+                out[key + "/mask"] = np.frombuffer(m, dtype=np.uint16).copy()
+                out[key + "/sinks"] = f32(s)
+            continue
+        tag, t, nth = struct.unpack_from("<III", b, o)
+        o += 12
+        d = sec()
+        if keep:
+            out[f"probe{probe}/rec/{tag}/{t}/{nth}"] = f32(d)
+
+
 def main():
     if len(sys.argv) != 2:
         sys.exit(__doc__)
     par = os.path.join(sys.argv[1], "parity")
     for name, fn in (("quants", extract_quants), ("mulmat", extract_mulmat), ("repack", extract_repack),
                      ("real_tensors", extract_real), ("tiled", extract_tiled), ("fp16cvt", extract_fp16cvt),
-                     ("flash_attn", extract_flash_attn)):
+                     ("flash_attn", extract_flash_attn), ("flash_attn_probe", extract_flash_attn_probe)):
         out = {}
         fn(par, out)
         path = os.path.join(HERE, name + ".npz")
