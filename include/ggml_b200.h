@@ -153,7 +153,13 @@ int b200_mul_mat_id(int type, int64_t n, int64_t k, int64_t n_expert, int64_t ne
 /* ---- FLASH_ATTN_EXT — crates/ggml/src/compute.rs:4563, flash_attn.rs:907,920, ops.rs:2430
  * q f32 [T][H][DK] by byte strides, k/v f16 by byte strides (KV-cache views,
  * crates/llama/src/kv_cache.rs:2528-2579), mask f16 [T][n_kv] or NULL,
- * dst f32 [T][H][DV] contiguous. */
+ * dst f32 [T][H][DV] contiguous.
+ * The CPU result for one query row over >= 512 positions depends on the CPU
+ * thread count (split-KV, flash_attn.rs:841-859): n_chunks names the thread
+ * count to reproduce (0 = 8, the count the reference's benchmark scripts use).
+ * mode 0 reproduces the CPU arithmetic (f16 accumulator order and all);
+ * mode 1 is the fast path with f32 accumulation (more accurate than the CPU,
+ * not bit-comparable to it). */
 struct b200_flash_attn_args {
     int64_t dk, dv, n_tok, n_head, n_head_kv, n_kv;
     const float *q;      int64_t q_nb1, q_nb2;     /* bytes per token, per head */
@@ -163,6 +169,8 @@ struct b200_flash_attn_args {
     const float *sinks;                            /* [n_head] or NULL */
     float scale, max_bias, logit_softcap;
     float *dst;
+    int32_t n_chunks;
+    int32_t mode;
 };
 int b200_flash_attn_ext(const struct b200_flash_attn_args *args, void *stream);
 

@@ -223,5 +223,68 @@ class Event:
             pass
 
 
+class FlashAttnArgs(C.Structure):
+    """struct b200_flash_attn_args"""
+    _fields_ = [
+        ("dk", C.c_int64), ("dv", C.c_int64), ("n_tok", C.c_int64), ("n_head", C.c_int64),
+        ("n_head_kv", C.c_int64), ("n_kv", C.c_int64),
+        ("q", C.c_void_p), ("q_nb1", C.c_int64), ("q_nb2", C.c_int64),
+        ("k", C.c_void_p), ("k_nb1", C.c_int64), ("k_nb2", C.c_int64),
+        ("v", C.c_void_p), ("v_nb1", C.c_int64), ("v_nb2", C.c_int64),
+        ("mask", C.c_void_p), ("mask_nb1", C.c_int64),
+        ("sinks", C.c_void_p),
+        ("scale", C.c_float), ("max_bias", C.c_float), ("logit_softcap", C.c_float),
+        ("dst", C.c_void_p),
+        ("n_chunks", C.c_int32), ("mode", C.c_int32),
+    ]
+
+
+class KvCacheView:
+    """K and V of one layer on the device, laid out like the reference's KV cache: position-major
+    rows of [n_head_kv * d] f16 (crates/llama/src/kv_cache.rs:2528-2579)."""
+
+    def __init__(self, k, v):
+        """k: uint16 (f16 bits) [n_head_kv, n_kv, dk]; v: [n_head_kv, n_kv, dv] (head-major on the host)."""
+        self.h_kv, self.n_kv, self.dk = k.shape
+        self.dv = v.shape[2]
+        kc = np.ascontiguousarray(np.transpose(k, (1, 0, 2)))  # [n_kv, h_kv, dk]
+        vc = np.ascontiguousarray(np.transpose(v, (1, 0, 2)))
+        self.k = device_array(kc)
+        self.v = device_array(vc)
+        self.k_nb1, self.k_nb2 = self.h_kv * self.dk * 2, self.dk * 2
+        self.v_nb1, self.v_nb2 = self.h_kv * self.dv * 2, self.dv * 2
+
+
+def flash_attn(q, kv, mask, scale, sinks=None, max_bias=0.0, softcap=0.0, n_chunks=0, mode=0, stream=None):
+    """q: f32 [H, T, DK] host; kv: KvCacheView; mask: uint16 (f16 bits) [T, n_kv] or None -> f32 [T, H, DV]."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    H, T, DK = q.shape
+    dq = device_array(q)
+    dst = DeviceBuffer(4 * T * H * kv.dv)
+    a = FlashAttnArgs()
+    a.dk, a.dv, a.n_tok, a.n_head, a.n_head_kv, a.n_kv = DK, kv.dv, T, H, kv.h_kv, kv.n_kv
+    a.q, a.q_nb1, a.q_nb2 = dq.ptr, DK * 4, T * DK * 4
+    a.k, a.k_nb1, a.k_nb2 = kv.k.ptr, kv.k_nb1, kv.k_nb2
+    a.v, a.v_nb1, a.v_nb2 = kv.v.ptr, kv.v_nb1, kv.v_nb2
+    keep = [dq, dst]
+    if mask is not None:
+        dm = device_array(np.ascontiguousarray(mask, dtype=np.uint16))
+        keep.append(dm)
+        a.mask, a.mask_nb1 = dm.ptr, kv.n_kv * 2
+    else:
+        a.mask, a.mask_nb1 = None, 0
+    if sinks is not None:
+        ds = device_array(np.ascontiguousarray(sinks, dtype=np.float32))
+        keep.append(ds)
+        a.sinks = ds.ptr
+    else:
+        a.sinks = None
+    a.scale, a.max_bias, a.logit_softcap = scale, max_bias, softcap
+    a.dst = dst.ptr
+    a.n_chunks, a.mode = n_chunks, mode
+    check(lib.b200_flash_attn_ext(C.byref(a), stream), "flash_attn_ext")
+    return dst.download(np.float32, T * H * kv.dv).reshape(T, H, kv.dv)
+
+
 def act_kind_for(ty):
     return ACT_Q8_K if ty in (Q4_K, Q6_K) else ACT_Q8_0

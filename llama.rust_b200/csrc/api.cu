@@ -406,9 +406,5 @@ int b200_mul_mat_id(int, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, c
     return B200_STATUS_BACKEND_ERROR;
 }
 
-int b200_flash_attn_ext(const struct b200_flash_attn_args *, void *) {
-    set_error("flash_attn_ext: not built yet");
-    return B200_STATUS_BACKEND_ERROR;
-}
 
 }  // extern "C"

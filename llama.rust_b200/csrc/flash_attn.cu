@@ -1,0 +1,366 @@
+// FLASH_ATTN_EXT over an F16 KV cache, decode-shaped (fewer than 64 query rows).
+//
+// "Faithful" mode reproduces the arithmetic of the CPU path exactly:
+//   * scores: the f16 dot of crates/ggml/src/vec_dot.rs:1982-2019 (q rounded to
+//     f16, 4 x 16 f32 FMA lanes over 64-element chunks, fixed fold and tree);
+//   * online softmax per row with the running maximum, the F16-V accumulator
+//     kept in f16 with one rounding per scale and per multiply-add, S updated
+//     with one FMA (crates/ggml/src/flash_attn.rs:482-694);
+//   * split-KV (one query row, n_kv >= 512): n_chunks independent chunk scans
+//     merged in chunk order (flash_attn.rs:744-859); the result depends on
+//     n_chunks exactly as the CPU result depends on its thread count;
+//   * expf: the table-driven double-precision algorithm the host libm uses, so
+//     ms / vs are the same bits (checked exhaustively against expf on the host).
+// Three kernels: scores (parallel over positions), rows (one CTA per (row,
+// chunk): prefix-max scan per 128-position tile, then the sequential f16
+// accumulation with one thread per value element), merge.
+#include <cmath>
+
+#include "common.cuh"
+
+namespace b200 {
+
+// ---------------------------------------------------------------------------
+// expf as the host libm computes it (x86-64 glibc, FMA variant): N = 32 table,
+// cubic in double precision.  Inputs here are <= 0 or small.
+// ---------------------------------------------------------------------------
+__device__ const double c_exp2_tab[32] = {
+    0x1.0000000000000p+0, 0x1.059b0d3158574p+0, 0x1.0b5586cf9890fp+0, 0x1.11301d0125b51p+0,
+    0x1.172b83c7d517bp+0, 0x1.1d4873168b9aap+0, 0x1.2387a6e756238p+0, 0x1.29e9df51fdee1p+0,
+    0x1.306fe0a31b715p+0, 0x1.371a7373aa9cbp+0, 0x1.3dea64c123422p+0, 0x1.44e086061892dp+0,
+    0x1.4bfdad5362a27p+0, 0x1.5342b569d4f82p+0, 0x1.5ab07dd485429p+0, 0x1.6247eb03a5585p+0,
+    0x1.6a09e667f3bcdp+0, 0x1.71f75e8ec5f74p+0, 0x1.7a11473eb0187p+0, 0x1.82589994cce13p+0,
+    0x1.8ace5422aa0dbp+0, 0x1.93737b0cdc5e5p+0, 0x1.9c49182a3f090p+0, 0x1.a5503b23e255dp+0,
+    0x1.ae89f995ad3adp+0, 0x1.b7f76f2fb5e47p+0, 0x1.c199bdd85529cp+0, 0x1.cb720dcef9069p+0,
+    0x1.d5818dcfba487p+0, 0x1.dfc97337b9b5fp+0, 0x1.ea4afa2a490dap+0, 0x1.f50765b6e4540p+0};
+
+__device__ __forceinline__ float libm_expf(float x) {
+    if (x != x) return x;
+    if (x < -0x1.9fe368p6f) return 0.0f;                 // below log(2^-150)
+    if (x > 0x1.62e42ep6f) return __int_as_float(0x7f800000);
+    const double N = 32.0;
+    const double invln2n = 0x1.71547652b82fep+0 * N;
+    const double shift = 0x1.8p+52;
+    const double c0 = 0x1.c6af84b912394p-5 / N / N / N, c1 = 0x1.ebfce50fac4f3p-3 / N / N, c2 = 0x1.62e42ff0c52d6p-1 / N;
+    double z = __dmul_rn(invln2n, (double)x);
+    double kd = __dadd_rn(z, shift);
+    const unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
+    kd = __dsub_rn(kd, shift);
+    const double r = __dsub_rn(z, kd);
+    unsigned long long t = (unsigned long long)__double_as_longlong(c_exp2_tab[ki & 31]);
+    t += (ki >> 5) << 52;   // == T[ki % N] + (ki << 47) with the table's own bias folded out
+    const double s = __longlong_as_double((long long)t);
+    z = __fma_rn(c0, r, c1);
+    const double r2 = __dmul_rn(r, r);
+    double y = __fma_rn(c2, r, 1.0);
+    y = __fma_rn(z, r2, y);
+    y = __dmul_rn(y, s);
+    return __double2float_rn(y);
+}
+
+__device__ __forceinline__ float r16(float v) { return __half2float(__float2half_rn(v)); }
+
+struct FaDims {
+    int dk, dv, T, H, H_kv;
+    int64_t n_kv;
+    int n_chunks;
+    int64_t chunk;      // positions per chunk
+};
+
+// ---------------------------------------------------------------------------
+// scores[(t*H + h)*n_kv + p] = dot(k[p], f16(q)) * kq_scale (softcap) + slope*mask,
+// or -inf for a masked position (the CPU skips those entirely).
+// One thread per position; the K row sits in registers and serves the
+// H/H_kv heads of its group and all T query rows.
+// ---------------------------------------------------------------------------
+template <int DK>
+__global__ void __launch_bounds__(128)
+fa_scores_kernel(b200_flash_attn_args a, FaDims d, float kq_scale, float *__restrict__ scores) {
+    extern __shared__ float q_s[];   // [rows in batch][DK], q rounded to f16
+    const int group = d.H / d.H_kv;
+    const int hkv = blockIdx.y;
+    const int64_t p = (int64_t)blockIdx.x * 128 + threadIdx.x;
+    const bool live = p < d.n_kv;
+    __half2 kr[DK / 2];
+    if (live) {
+        const uint4 *src = (const uint4 *)((const uint8_t *)a.k + p * a.k_nb1 + (int64_t)hkv * a.k_nb2);
+#pragma unroll
+        for (int i = 0; i < DK / 8; i++) {
+            const uint4 v = src[i];
+            kr[4 * i + 0] = *(const __half2 *)&v.x;
+            kr[4 * i + 1] = *(const __half2 *)&v.y;
+            kr[4 * i + 2] = *(const __half2 *)&v.z;
+            kr[4 * i + 3] = *(const __half2 *)&v.w;
+        }
+    }
+    const int rows_total = d.T * group;           // row = t * group + g
+    constexpr int RB = 8;
+    for (int r0 = 0; r0 < rows_total; r0 += RB) {
+        const int nr = rows_total - r0 < RB ? rows_total - r0 : RB;
+        __syncthreads();
+        for (int i = threadIdx.x; i < nr * DK; i += 128) {
+            const int r = r0 + i / DK, e = i % DK;
+            const int t = r / group, h = hkv * group + r % group;
+            const float *q = (const float *)((const uint8_t *)a.q + (int64_t)t * a.q_nb1 + (int64_t)h * a.q_nb2);
+            q_s[i] = r16(q[e]);
+        }
+        __syncthreads();
+        if (!live) continue;
+        for (int rr = 0; rr < nr; rr++) {
+            const int r = r0 + rr;
+            const int t = r / group, h = hkv * group + r % group;
+            const float *q = q_s + rr * DK;
+            float val[16];
+#pragma unroll
+            for (int l = 0; l < 16; l++) {
+                float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+#pragma unroll
+                for (int c = 0; c < DK / 64; c++) {
+                    const int e = 64 * c + l;
+                    const float k0 = (e & 1) ? __high2float(kr[e >> 1]) : __low2float(kr[e >> 1]);
+                    const float k1 = ((e + 16) & 1) ? __high2float(kr[(e + 16) >> 1]) : __low2float(kr[(e + 16) >> 1]);
+                    const float k2 = ((e + 32) & 1) ? __high2float(kr[(e + 32) >> 1]) : __low2float(kr[(e + 32) >> 1]);
+                    const float k3 = ((e + 48) & 1) ? __high2float(kr[(e + 48) >> 1]) : __low2float(kr[(e + 48) >> 1]);
+                    s0 = __fmaf_rn(q[e], k0, s0);
+                    s1 = __fmaf_rn(q[e + 16], k1, s1);
+                    s2 = __fmaf_rn(q[e + 32], k2, s2);
+                    s3 = __fmaf_rn(q[e + 48], k3, s3);
+                }
+                val[l] = __fadd_rn(__fadd_rn(s0, s2), __fadd_rn(s1, s3));
+            }
+#pragma unroll
+            for (int half = 8; half >= 1; half >>= 1)
+#pragma unroll
+                for (int i = 0; i < half; i++) val[i] = __fadd_rn(val[i], val[i + half]);
+            float s = __fmul_rn(val[0], kq_scale);
+            if (a.logit_softcap != 0.0f) s = __fmul_rn(a.logit_softcap, tanhf(s));
+            if (a.mask) {
+                const __half mh = ((const __half *)((const uint8_t *)a.mask + (int64_t)t * a.mask_nb1))[p];
+                float slope = 1.0f;
+                if (a.max_bias > 0.0f) {
+                    // ALiBi slope of head h: crates/ggml/src/flash_attn.rs:356-370
+                    const unsigned nl2 = 1u << (31 - __clz((unsigned)d.H));
+                    const float m0 = powf(2.0f, -a.max_bias / (float)nl2);
+                    const float m1 = powf(2.0f, -(a.max_bias / 2.0f) / (float)nl2);
+                    const float base = (unsigned)h < nl2 ? m0 : m1;
+                    const int ex = (unsigned)h < nl2 ? h + 1 : 2 * (h - (int)nl2) + 1;
+                    float acc = 1.0f, b = base;   // powi by repeated squaring
+                    for (int e2 = ex; e2 > 0; e2 >>= 1) {
+                        if (e2 & 1) acc = __fmul_rn(acc, b);
+                        b = __fmul_rn(b, b);
+                    }
+                    slope = acc;
+                }
+                const float mv = __fmul_rn(slope, __half2float(mh));
+                s = (mv == -INFINITY) ? -INFINITY : __fadd_rn(s, mv);
+            }
+            scores[((int64_t)t * d.H + h) * d.n_kv + p] = s;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// rows: grid (chunk, h, t), block = 128 value threads + 1 warp for the S chain.
+// Writes per (row, chunk): M, S, and the unnormalized accumulator (f32 view).
+// ---------------------------------------------------------------------------
+constexpr int FA_TILE = 128;
+
+__global__ void __launch_bounds__(160)
+fa_rows_kernel(b200_flash_attn_args a, FaDims d, const float *__restrict__ scores, float *__restrict__ partials) {
+    extern __shared__ __align__(16) unsigned char fsm[];
+    __half *v_s = (__half *)fsm;                                  // [FA_TILE][dv]
+    float *ms_s = (float *)(fsm + (size_t)FA_TILE * d.dv * 2);    // [FA_TILE]
+    float *vs_s = ms_s + FA_TILE;
+    float *wmax = vs_s + FA_TILE;                                 // [4] warp maxima
+    __shared__ float carry_M;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int c = blockIdx.x, h = blockIdx.y, t = blockIdx.z;
+    const int hkv = h / (d.H / d.H_kv);
+    const int64_t ic0 = (int64_t)c * d.chunk;
+    const int64_t ic1 = ic0 + d.chunk < d.n_kv ? ic0 + d.chunk : d.n_kv;
+    const int64_t row = (int64_t)t * d.H + h;
+    float *part = partials + (row * d.n_chunks + c) * (2 + d.dv);
+    if (ic0 >= d.n_kv) {   // out-of-range chunk: M = -inf, S = 0 (flash_attn.rs:757-764)
+        if (tid == 0) { part[0] = -INFINITY; part[1] = 0.0f; }
+        return;
+    }
+    const float *srow = scores + row * d.n_kv;
+    const uint8_t *vbase = (const uint8_t *)a.v + (int64_t)hkv * a.v_nb2;
+    if (tid == 0) carry_M = -INFINITY;
+    float x = 0.0f;      // value threads: accumulator element d = tid (f16-representable)
+    float S = 0.0f;      // S-chain lane
+    const bool is_val = tid < d.dv;
+    const bool is_s = tid == 128;
+    __syncthreads();
+    for (int64_t p0 = ic0; p0 < ic1; p0 += FA_TILE) {
+        const int np = ic1 - p0 < FA_TILE ? (int)(ic1 - p0) : FA_TILE;
+        // stage the V tile: np rows of dv halves, 16 bytes per load
+        const int chunks_per_row = d.dv / 8;
+        for (int i = tid; i < np * chunks_per_row; i += blockDim.x) {
+            const int pr = i / chunks_per_row, cc = i % chunks_per_row;
+            const uint4 v = *(const uint4 *)(vbase + (p0 + pr) * a.v_nb1 + cc * 16);
+            *(uint4 *)(v_s + pr * d.dv + cc * 8) = v;
+        }
+        // exclusive prefix maximum of the tile's scores (threads 0..127 = positions)
+        float s = -INFINITY;
+        if (tid < FA_TILE && tid < np) s = srow[p0 + tid];
+        float incl = s;
+        if (tid < FA_TILE) {
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float n = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl = fmaxf(incl, n);
+            }
+            if (lane == 31) wmax[warp] = incl;
+        }
+        __syncthreads();
+        if (tid < FA_TILE) {
+            float before = carry_M;
+            for (int w = 0; w < warp; w++) before = fmaxf(before, wmax[w]);
+            float excl = __shfl_up_sync(0xffffffffu, incl, 1);
+            if (lane == 0) excl = -INFINITY;
+            before = fmaxf(before, excl);
+            float ms = 1.0f, vs = 0.0f;
+            if (tid < np && s != -INFINITY) {
+                if (s > before) {
+                    ms = libm_expf(__fsub_rn(before, s));
+                    vs = 1.0f;
+                } else {
+                    vs = libm_expf(__fsub_rn(s, before));
+                }
+            } else {
+                ms = -1.0f;   // marks a skipped position
+            }
+            ms_s[tid] = ms;
+            vs_s[tid] = vs;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float m = carry_M;
+            for (int w = 0; w < 4; w++) m = fmaxf(m, wmax[w]);
+            carry_M = m;
+        }
+        if (is_val) {
+            for (int i = 0; i < np; i++) {
+                const float ms = ms_s[i];
+                if (ms < 0.0f) continue;
+                if (ms != 1.0f) x = r16(__fmul_rn(x, ms));
+                x = r16(__fmaf_rn(__half2float(v_s[i * d.dv + tid]), vs_s[i], x));
+            }
+        } else if (is_s) {
+            for (int i = 0; i < np; i++) {
+                const float ms = ms_s[i];
+                if (ms < 0.0f) continue;
+                S = __fmaf_rn(S, ms, vs_s[i]);
+            }
+        }
+        __syncthreads();
+    }
+    // sinks: only the chunk that starts at position 0 (flash_attn.rs:661-690), in f32
+    float M = carry_M;
+    if (a.sinks && ic0 == 0) {
+        const float sh = a.sinks[h];
+        float ms = 1.0f, vs = 1.0f;
+        if (sh > M) {
+            ms = libm_expf(__fsub_rn(M, sh));
+            if (is_val) x = __fmul_rn(x, ms);
+            M = sh;
+        } else {
+            vs = libm_expf(__fsub_rn(sh, M));
+        }
+        if (is_s) S = __fadd_rn(__fmul_rn(S, ms), vs);
+    }
+    if (is_val) part[2 + tid] = x;
+    if (is_s) { part[0] = M; part[1] = S; }
+}
+
+// merge of the chunk partials in chunk order + normalisation (flash_attn.rs:779-832);
+// with one chunk this is the plain one_chunk normalisation (S_inv = S == 0 ? 0 : 1/S).
+__global__ void fa_merge_kernel(FaDims d, const float *__restrict__ partials, float *__restrict__ dst, bool split) {
+    const int64_t row = blockIdx.x;
+    const int e = threadIdx.x;
+    if (e >= d.dv) return;
+    const float *p0 = partials + row * d.n_chunks * (2 + d.dv);
+    if (!split) {
+        const float S = p0[1];
+        const float s_inv = S == 0.0f ? 0.0f : __fdiv_rn(1.0f, S);
+        dst[row * d.dv + e] = __fmul_rn(p0[2 + e], s_inv);
+        return;
+    }
+    float fin = 0.0f, Mf = -INFINITY, Sf = 0.0f;
+    for (int c = 0; c < d.n_chunks; c++) {
+        if ((int64_t)c * d.chunk >= d.n_kv) continue;
+        const float *p = p0 + (int64_t)c * (2 + d.dv);
+        const float Mc = p[0], Sc = p[1];
+        if (Sc == 0.0f) continue;
+        const float Mn = fmaxf(Mf, Mc);
+        const float so = libm_expf(__fsub_rn(Mf, Mn)), sn = libm_expf(__fsub_rn(Mc, Mn));
+        fin = __fmaf_rn(fin, so, __fmul_rn(p[2 + e], sn));
+        Sf = __fmaf_rn(Sf, so, __fmul_rn(Sc, sn));
+        Mf = Mn;
+    }
+    if (Sf != 0.0f) fin = __fmul_rn(fin, __fdiv_rn(1.0f, Sf));
+    dst[row * d.dv + e] = fin;
+}
+
+static int check_args(const b200_flash_attn_args *a) {
+    B200_REQUIRE(a != nullptr, "flash_attn_ext: null argument block");
+    B200_REQUIRE(a->q && a->k && a->v && a->dst, "flash_attn_ext: null tensor pointer");
+    B200_REQUIRE(a->n_tok >= 0 && a->n_kv >= 0 && a->n_head > 0 && a->n_head_kv > 0, "flash_attn_ext: bad shape");
+    B200_REQUIRE(a->n_head % a->n_head_kv == 0, "flash_attn_ext: n_head %% n_head_kv != 0");
+    B200_REQUIRE(a->dk == 64 || a->dk == 128, "flash_attn_ext: head size dk = %lld is not supported (64, 128)",
+                 (long long)a->dk);
+    B200_REQUIRE(a->dv == 64 || a->dv == 128, "flash_attn_ext: value size dv = %lld is not supported (64, 128)",
+                 (long long)a->dv);
+    B200_REQUIRE(a->k_nb1 % 16 == 0 && a->k_nb2 % 16 == 0 && a->v_nb1 % 16 == 0 && a->v_nb2 % 16 == 0 &&
+                     ((uintptr_t)a->k & 15) == 0 && ((uintptr_t)a->v & 15) == 0,
+                 "flash_attn_ext: k/v rows must be 16-byte aligned");
+    B200_REQUIRE(!(a->max_bias > 0.0f) || a->mask, "flash_attn_ext: max_bias > 0 needs a mask");
+    return B200_STATUS_SUCCESS;
+}
+
+int flash_attn_faithful_rows(const b200_flash_attn_args *a, cudaStream_t s) {
+    FaDims d;
+    d.dk = (int)a->dk; d.dv = (int)a->dv; d.T = (int)a->n_tok; d.H = (int)a->n_head; d.H_kv = (int)a->n_head_kv;
+    d.n_kv = a->n_kv;
+    const bool split = a->n_tok == 1 && a->n_kv >= 512;   // flash_attn.rs:931-939
+    d.n_chunks = split ? (a->n_chunks > 0 ? a->n_chunks : 8) : 1;
+    d.chunk = (a->n_kv + d.n_chunks - 1) / d.n_chunks;
+    const int64_t rows = (int64_t)d.T * d.H;
+    if (rows == 0) return B200_STATUS_SUCCESS;
+    if (a->n_kv == 0) {
+        B200_CUDA(cudaMemsetAsync(a->dst, 0, (size_t)rows * d.dv * 4, s));
+        return B200_STATUS_SUCCESS;
+    }
+    B200_REQUIRE(d.T <= 65535 && d.H <= 65535, "flash_attn_ext: too many rows for one launch");
+    const size_t score_b = ((size_t)rows * d.n_kv * 4 + 255) / 256 * 256;
+    const size_t part_b = (size_t)rows * d.n_chunks * (2 + d.dv) * 4;
+    void *scratch = nullptr;
+    int rc = scratch_get(score_b + part_b, &scratch);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    float *scores = (float *)scratch;
+    float *partials = (float *)((uint8_t *)scratch + score_b);
+    const float kq_scale = a->logit_softcap != 0.0f ? a->scale / a->logit_softcap : a->scale;
+    dim3 g1((unsigned)((d.n_kv + 127) / 128), (unsigned)d.H_kv);
+    const size_t sm1 = (size_t)8 * d.dk * 4;
+    if (d.dk == 128) fa_scores_kernel<128><<<g1, 128, sm1, s>>>(*a, d, kq_scale, scores);
+    else fa_scores_kernel<64><<<g1, 128, sm1, s>>>(*a, d, kq_scale, scores);
+    B200_CUDA(cudaGetLastError());
+    dim3 g2((unsigned)d.n_chunks, (unsigned)d.H, (unsigned)d.T);
+    const size_t sm2 = (size_t)FA_TILE * d.dv * 2 + (2 * FA_TILE + 4) * 4;
+    fa_rows_kernel<<<g2, 160, sm2, s>>>(*a, d, scores, partials);
+    B200_CUDA(cudaGetLastError());
+    fa_merge_kernel<<<(unsigned)rows, 128, 0, s>>>(d, partials, a->dst, split);
+    B200_CUDA(cudaGetLastError());
+    return B200_STATUS_SUCCESS;
+}
+
+}  // namespace b200
+
+extern "C" int b200_flash_attn_ext(const struct b200_flash_attn_args *args, void *stream) {
+    using namespace b200;
+    int rc = check_args(args);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    if (args->n_tok < 64) return flash_attn_faithful_rows(args, (cudaStream_t)stream);
+    B200_REQUIRE(false, "flash_attn_ext: the 64-row tiled path is not built yet (n_tok = %lld)", (long long)args->n_tok);
+}
