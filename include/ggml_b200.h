@@ -48,7 +48,12 @@ enum b200_type {
  *   A1 quantize_row_q8_0       crates/ggml/src/quants.rs:331-362
  *   A2 quantize_row_q8_K       crates/ggml/src/quants.rs:615-654
  *   A3 quantize_mat_q8_K_4x8   crates/ggml/src/repack.rs:1561-1606 (values) */
-enum b200_act_quant { B200_ACT_Q8_0 = 1, B200_ACT_Q8_K = 2, B200_ACT_Q8_K_4X8 = 3 };
+enum b200_act_quant {
+    B200_ACT_Q8_0 = 1, B200_ACT_Q8_K = 2, B200_ACT_Q8_K_4X8 = 3,
+    /* what the Q4_K 8x8 route builds: A3 for the complete groups of 4 rows, A2 for the m % 4 tail
+     * (crates/ggml/src/compute.rs:5322-5400) */
+    B200_ACT_Q8_K_MIXED = 4,
+};
 
 /* Which CPU route's arithmetic a mat-mul reproduces (crates/ggml/src/compute.rs:1420-1841).
  * AUTO picks what the reference picks for (type, N, M). */

@@ -18,7 +18,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libggml-b200.so")
 
 F32, F16, Q4_0, Q8_0, Q4_K, Q6_K, Q8_K, MXFP4 = 0, 1, 2, 8, 12, 14, 15, 39
-ACT_Q8_0, ACT_Q8_K, ACT_Q8_K_4X8 = 1, 2, 3
+ACT_Q8_0, ACT_Q8_K, ACT_Q8_K_4X8, ACT_Q8_K_MIXED = 1, 2, 3, 4
 ROUTE_AUTO, ROUTE_ROWDOT, ROUTE_REPACK, ROUTE_TILED = 0, 1, 2, 3
 STATUS_SUCCESS = 0
 
@@ -286,5 +286,10 @@ def flash_attn(q, kv, mask, scale, sinks=None, max_bias=0.0, softcap=0.0, n_chun
     return dst.download(np.float32, T * H * kv.dv).reshape(T, H, kv.dv)
 
 
-def act_kind_for(ty):
-    return ACT_Q8_K if ty in (Q4_K, Q6_K) else ACT_Q8_0
+def act_kind_for(ty, n=8, m=1):
+    """The activation quantizer the reference's route for (type, n rows, m activation rows) reads."""
+    if ty not in (Q4_K, Q6_K):
+        return ACT_Q8_0
+    if ty == Q4_K and n % 8 == 0 and m >= 4:
+        return ACT_Q8_K_MIXED
+    return ACT_Q8_K

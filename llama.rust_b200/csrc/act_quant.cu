@@ -122,6 +122,21 @@ int launch_quantize_acts(int kind, int64_t m, int64_t k, const float *x, int64_t
         dim3 grid((unsigned)(k / 256), (unsigned)m);
         if (kind == B200_ACT_Q8_K) quantize_q8_K_kernel<false><<<grid, 256, 0, s>>>(x, ldx, out);
         else quantize_q8_K_kernel<true><<<grid, 256, 0, s>>>(x, ldx, out);
+    } else if (kind == B200_ACT_Q8_K_MIXED) {
+        B200_REQUIRE(k > 0 && k % 256 == 0, "quantize q8_K: k = %lld must be a positive multiple of 256", (long long)k);
+        const int64_t m4 = m - m % 4;
+        if (m4 > 0) {
+            dim3 grid((unsigned)(k / 256), (unsigned)m4);
+            quantize_q8_K_kernel<true><<<grid, 256, 0, s>>>(x, ldx, out);
+        }
+        if (m > m4) {
+            ActBuf tail = out;
+            tail.qs += m4 * k;
+            tail.d += m4 * (k / 256);
+            tail.bsums += m4 * (k / 16);
+            dim3 grid((unsigned)(k / 256), (unsigned)(m - m4));
+            quantize_q8_K_kernel<false><<<grid, 256, 0, s>>>(x + m4 * ldx, ldx, tail);
+        }
     } else {
         B200_REQUIRE(false, "quantize: unknown activation kind %d", kind);
     }

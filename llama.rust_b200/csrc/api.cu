@@ -73,9 +73,10 @@ int pick_route(int type, int64_t n, int64_t m) {
 
 // which activation quantizer a (type, route) reads
 int act_kind_for(int type, int route, int64_t m) {
-    (void)route;
-    (void)m;
-    return is_k_quant(type) ? B200_ACT_Q8_K : B200_ACT_Q8_0;
+    if (!is_k_quant(type)) return B200_ACT_Q8_0;
+    // the Q4_K 8x8 route quantizes whole groups of 4 rows with the 4x8 rule (compute.rs:5322-5400)
+    if (type == B200_TYPE_Q4_K && route == B200_ROUTE_REPACK && m >= 4) return B200_ACT_Q8_K_MIXED;
+    return B200_ACT_Q8_K;
 }
 
 static size_t ggml_row_bytes(int type, int64_t k) { return (size_t)(k / GROUP_K) * group_src_bytes(type); }
@@ -373,7 +374,7 @@ int b200_mul_mat(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, c
     int rc = scratch_get(act_scratch_bytes(m, k), &scratch);
     if (rc != B200_STATUS_SUCCESS) return rc;
     ActBuf a = act_carve(scratch, m, k);
-    const int kind = is_k_quant(type) ? B200_ACT_Q8_K : B200_ACT_Q8_0;
+    const int kind = act_kind_for(type, route, m);
     rc = launch_quantize_acts(kind, m, k, dev_x, ldx, a, s);
     if (rc != B200_STATUS_SUCCESS) return rc;
     return launch_gemv(type, route, n, k, m, (const uint8_t *)dev_w, a.view(), dev_dst, lddst, s);

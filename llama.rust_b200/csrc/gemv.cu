@@ -27,14 +27,19 @@ struct Q4KStage {
     int bp[8];     // bsums[2j] + bsums[2j+1]
 };
 
-template <int NCOL>
+// MODE selects the f32 chain of the mirrored CPU route:
+//   0  8x8 gemv  (repack.rs:1638-1688): one fma per super-block and term, out = acc - accmin
+//   1  8x8 gemm  (repack.rs:1692-1768): one fma per (super-block, sub-block pair) and term
+//   2  tiled     (tiled.rs:823-838):    r = d*f32(s1); r = fma(-dmin, f32(s2), r); out = fma(r, d_x, out)
+template <int NCOL, int MODE>
 __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32)
 gemv_q4_K_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *__restrict__ dst, int64_t lddst, int64_t n,
                  int nb) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     Q4KStage *stage = (Q4KStage *)smem + warp * NCOL;
-    int4 *xch = (int4 *)(smem + sizeof(Q4KStage) * nwarps * NCOL);  // [NCOL][nb][32], .w unused
+    constexpr int XW = MODE == 1 ? 3 : 1;                           // int4 words per (col, group, row)
+    int4 *xch = (int4 *)(smem + sizeof(Q4KStage) * nwarps * NCOL);  // [NCOL][nb][XW][32]
     const int64_t tile = blockIdx.x;
     const uint8_t *base = tiles + tile * (int64_t)nb * 4608;
 
@@ -65,6 +70,7 @@ gemv_q4_K_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *__restr
 #pragma unroll
         for (int col = 0; col < NCOL; col++) {
             int iacc = 0;
+            int ig[4], mg[4];
 #pragma unroll
             for (int g = 0; g < 4; g++) {
                 int dlo = 0, dhi = 0;
@@ -85,15 +91,25 @@ gemv_q4_K_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *__restr
                 const uint32_t s4 = g < 2 ? sc_lo4 : sc_hi4;
                 const int s_lo = (s4 >> (16 * (g & 1))) & 0xff;
                 const int s_hi = (s4 >> (16 * (g & 1) + 8)) & 0xff;
-                iacc += dlo * s_lo + dhi * s_hi;
+                ig[g] = dlo * s_lo + dhi * s_hi;
+                iacc += ig[g];
             }
             int imin = 0;
 #pragma unroll
             for (int j = 0; j < 8; j++) {
                 const uint32_t m4 = j < 4 ? mn_lo4 : mn_hi4;
-                imin += (int)((m4 >> (8 * (j & 3))) & 0xff) * stage[col].bp[j];
+                const int term = (int)((m4 >> (8 * (j & 3))) & 0xff) * stage[col].bp[j];
+                imin += term;
+                if (j & 1) mg[j >> 1] += term; else mg[j >> 1] = term;
             }
-            xch[((int64_t)col * nb + b) * 32 + lane] = make_int4(iacc, imin, (int)h.x, 0);
+            int4 *xe = xch + ((int64_t)col * nb + b) * XW * 32 + lane;
+            if (MODE == 1) {
+                xe[0] = make_int4(ig[0], ig[1], ig[2], ig[3]);
+                xe[32] = make_int4(mg[0], mg[1], mg[2], mg[3]);
+                xe[64] = make_int4((int)h.x, 0, 0, 0);
+            } else {
+                xe[0] = make_int4(iacc, imin, (int)h.x, 0);
+            }
         }
         __syncwarp();
     }
@@ -103,16 +119,35 @@ gemv_q4_K_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *__restr
         const int col = t >> 5, r = t & 31;
         const float *dx = acts.d + (int64_t)col * nb;
         float sumf = 0.0f, summin = 0.0f;
+#pragma unroll 4
         for (int b = 0; b < nb; b++) {
-            const int4 v = xch[((int64_t)col * nb + b) * 32 + r];
-            const float d = f16_bits_to_f32((uint16_t)((uint32_t)v.z & 0xffffu));
-            const float dmin = f16_bits_to_f32((uint16_t)((uint32_t)v.z >> 16));
+            const int4 *xe = xch + ((int64_t)col * nb + b) * XW * 32 + r;
             const float da = dx[b];
-            sumf = __fmaf_rn((float)v.x, __fmul_rn(d, da), sumf);
-            summin = __fmaf_rn((float)v.y, __fmul_rn(dmin, da), summin);
+            if (MODE == 1) {
+                const int4 vi = xe[0], vm = xe[32];
+                const uint32_t hd = (uint32_t)xe[64].x;
+                const float sd = __fmul_rn(f16_bits_to_f32((uint16_t)(hd & 0xffffu)), da);
+                const float sm = __fmul_rn(f16_bits_to_f32((uint16_t)(hd >> 16)), da);
+                sumf = __fmaf_rn((float)vi.x, sd, sumf); summin = __fmaf_rn((float)vm.x, sm, summin);
+                sumf = __fmaf_rn((float)vi.y, sd, sumf); summin = __fmaf_rn((float)vm.y, sm, summin);
+                sumf = __fmaf_rn((float)vi.z, sd, sumf); summin = __fmaf_rn((float)vm.z, sm, summin);
+                sumf = __fmaf_rn((float)vi.w, sd, sumf); summin = __fmaf_rn((float)vm.w, sm, summin);
+            } else {
+                const int4 v = xe[0];
+                const float d = f16_bits_to_f32((uint16_t)((uint32_t)v.z & 0xffffu));
+                const float dmin = f16_bits_to_f32((uint16_t)((uint32_t)v.z >> 16));
+                if (MODE == 0) {
+                    sumf = __fmaf_rn((float)v.x, __fmul_rn(d, da), sumf);
+                    summin = __fmaf_rn((float)v.y, __fmul_rn(dmin, da), summin);
+                } else {
+                    float rr = __fmul_rn(d, (float)v.x);
+                    rr = __fmaf_rn(-dmin, (float)v.y, rr);
+                    sumf = __fmaf_rn(rr, da, sumf);
+                }
+            }
         }
         const int64_t row = tile * TILE_ROWS + r;
-        if (row < n) dst[(int64_t)col * lddst + row] = __fsub_rn(sumf, summin);
+        if (row < n) dst[(int64_t)col * lddst + row] = MODE == 2 ? sumf : __fsub_rn(sumf, summin);
     }
 }
 
@@ -123,19 +158,19 @@ static int pick_warps(int nb) {
     return nb < GEMV_MAX_WARPS ? (nb < 1 ? 1 : nb) : GEMV_MAX_WARPS;
 }
 
-template <int NCOL>
+template <int NCOL, int MODE>
 static int launch_q4k(int64_t n, int nb, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
                       cudaStream_t s) {
     const int nw = pick_warps(nb);
-    const size_t smem = sizeof(Q4KStage) * nw * NCOL + sizeof(int4) * (size_t)NCOL * nb * 32;
-    B200_REQUIRE(smem <= 200 * 1024, "gemv q4_K: k too large for the shared-memory exchange (%zu bytes)", smem);
-    static bool attr_done[4] = {false, false, false, false};
-    if (!attr_done[NCOL]) {
-        B200_CUDA(cudaFuncSetAttribute(gemv_q4_K_kernel<NCOL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr_done[NCOL] = true;
+    const size_t smem = sizeof(Q4KStage) * nw * NCOL + sizeof(int4) * (size_t)NCOL * nb * 32 * (MODE == 1 ? 3 : 1);
+    B200_REQUIRE(smem <= 200 * 1024, "mul_mat q4_K: k too large for the shared-memory exchange (%zu bytes)", smem);
+    static bool attr_done = false;
+    if (!attr_done) {
+        B200_CUDA(cudaFuncSetAttribute(gemv_q4_K_kernel<NCOL, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_done = true;
     }
     const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
-    gemv_q4_K_kernel<NCOL><<<(unsigned)tiles_n, nw * 32, smem, s>>>(tiles, acts, dst, lddst, n, nb);
+    gemv_q4_K_kernel<NCOL, MODE><<<(unsigned)tiles_n, nw * 32, smem, s>>>(tiles, acts, dst, lddst, n, nb);
     B200_CUDA(cudaGetLastError());
     return B200_STATUS_SUCCESS;
 }
@@ -153,8 +188,8 @@ gemv_generic_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *__re
     extern __shared__ __align__(16) unsigned char smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     ActStage *stage = (ActStage *)smem + warp * NCOL;
-    float *fin = (float *)(smem + sizeof(ActStage) * nwarps * NCOL);       // [NCOL][8][32]
-    uint32_t *xch = (uint32_t *)(fin + NCOL * 8 * 32);                      // [NCOL][win][NW][32]
+    float *fin = (float *)(smem + sizeof(ActStage) * nwarps * NCOL);       // [NCOL][12][32]
+    uint32_t *xch = (uint32_t *)(fin + NCOL * 12 * 32);                     // [NCOL][win][NW][32]
     const int64_t tile = blockIdx.x;
     const uint8_t *base = tiles + tile * (int64_t)nb * T::CHUNK;
     const int ct = threadIdx.x;  // chain thread id
@@ -209,14 +244,19 @@ gemv_generic_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *__re
         if (is_chain && row0 + c_row < n) dst[(int64_t)c_col * lddst + row0 + c_row] = acc;
     } else {
         // hsum8 of the eight lane accumulators: crates/ggml/src/vec_dot.rs:564-572
-        if (is_chain) fin[(c_col * 8 + c_l) * 32 + c_row] = acc;
+        if (is_chain) fin[(c_col * 12 + c_l) * 32 + c_row] = acc;
         __syncthreads();
         if (ct < NCOL * 32) {
             const int col = ct >> 5, r = ct & 31;
-            const float *a = fin + col * 8 * 32 + r;
+            const float *a = fin + col * 12 * 32 + r;
             const float r0 = __fadd_rn(a[4 * 32], a[0]), r1 = __fadd_rn(a[5 * 32], a[32]);
             const float r2 = __fadd_rn(a[6 * 32], a[2 * 32]), r3 = __fadd_rn(a[7 * 32], a[3 * 32]);
-            const float v = __fadd_rn(__fadd_rn(r0, r2), __fadd_rn(r1, r3));
+            float v = __fadd_rn(__fadd_rn(r0, r2), __fadd_rn(r1, r3));
+            if (T::CHAINS == 12) {
+                // the four min lanes of the Q4_K row dot: (m0 + m2) + (m1 + m3), added last
+                const float m01 = __fadd_rn(__fadd_rn(a[8 * 32], a[10 * 32]), __fadd_rn(a[9 * 32], a[11 * 32]));
+                v = __fadd_rn(v, m01);
+            }
             if (row0 + r < n) dst[(int64_t)col * lddst + row0 + r] = v;
         }
     }
@@ -232,7 +272,7 @@ static int launch_generic(int64_t n, int nb, const uint8_t *tiles, ActView acts,
     int nw = pick_warps(nb);
     const int min_warps = NCOL * T::CHAINS;
     if (nw < min_warps) nw = min_warps;
-    const size_t fixed = sizeof(ActStage) * nw * NCOL + (size_t)NCOL * 8 * 32 * 4;
+    const size_t fixed = sizeof(ActStage) * nw * NCOL + (size_t)NCOL * 12 * 32 * 4;
     int win = (int)((GEMV_SMEM_LIMIT - fixed) / per_group);
     if (win > nb) win = nb;
     if (win > nw && win % nw) win -= win % nw;  // whole rounds of warps per window
@@ -276,22 +316,40 @@ int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint
                 int64_t lddst, cudaStream_t s) {
     B200_REQUIRE(k % GROUP_K == 0, "gemv: k = %lld must be a multiple of 256", (long long)k);
     const int nb = (int)(k / GROUP_K);
-    if (type == B200_TYPE_Q4_K && route == B200_ROUTE_REPACK) {
-        // columns are processed in passes of at most 3 (the CPU's gemv only ever sees the m % 4 tail rows)
-        for (int64_t c0 = 0; c0 < m; c0 += 3) {
-            const int nc = (int)(m - c0 < 3 ? m - c0 : 3);
+    if (type == B200_TYPE_Q4_K && (route == B200_ROUTE_REPACK || route == B200_ROUTE_TILED)) {
+        // REPACK: the caller quantized the first m - m % 4 rows with the 4x8 rule (gemm chain) and the
+        // tail rows the plain way (gemv chain), exactly as crates/ggml/src/compute.rs:5322-5447 does.
+        const int64_t m4 = route == B200_ROUTE_REPACK ? m - m % 4 : m;
+        const int maxc_main = route == B200_ROUTE_REPACK ? 2 : 3;
+        for (int64_t c0 = 0; c0 < m;) {
+            const bool main_part = c0 < m4;
+            const int64_t end = main_part ? m4 : m;
+            const int maxc = main_part ? maxc_main : 3;
+            const int nc = (int)(end - c0 < maxc ? end - c0 : maxc);
             ActView a = acts;
             a.qs += c0 * k;
             a.d += c0 * nb;
             a.bsums += c0 * (k / 16);
             float *o = dst + c0 * lddst;
-            int rc = nc == 1   ? launch_q4k<1>(n, nb, tiles, a, o, lddst, s)
-                     : nc == 2 ? launch_q4k<2>(n, nb, tiles, a, o, lddst, s)
-                               : launch_q4k<3>(n, nb, tiles, a, o, lddst, s);
+            int rc;
+            if (route == B200_ROUTE_TILED) {
+                rc = nc == 1 ? launch_q4k<1, 2>(n, nb, tiles, a, o, lddst, s)
+                   : nc == 2 ? launch_q4k<2, 2>(n, nb, tiles, a, o, lddst, s)
+                             : launch_q4k<3, 2>(n, nb, tiles, a, o, lddst, s);
+            } else if (main_part) {
+                rc = nc == 1 ? launch_q4k<1, 1>(n, nb, tiles, a, o, lddst, s) : launch_q4k<2, 1>(n, nb, tiles, a, o, lddst, s);
+            } else {
+                rc = nc == 1 ? launch_q4k<1, 0>(n, nb, tiles, a, o, lddst, s)
+                   : nc == 2 ? launch_q4k<2, 0>(n, nb, tiles, a, o, lddst, s)
+                             : launch_q4k<3, 0>(n, nb, tiles, a, o, lddst, s);
+            }
             if (rc != B200_STATUS_SUCCESS) return rc;
+            c0 += nc;
         }
         return B200_STATUS_SUCCESS;
     }
+    if (type == B200_TYPE_Q6_K && route == B200_ROUTE_TILED) return run_generic<TraitsQ6KTiled, 2>(n, k, m, tiles, acts, dst, lddst, s);
+    if (type == B200_TYPE_Q4_K && route == B200_ROUTE_ROWDOT) return run_generic<TraitsQ4KRowDot, 1>(n, k, m, tiles, acts, dst, lddst, s);
     if (type == B200_TYPE_Q6_K && route == B200_ROUTE_ROWDOT) return run_generic<TraitsQ6K, 1>(n, k, m, tiles, acts, dst, lddst, s);
     if (type == B200_TYPE_Q8_0 && route == B200_ROUTE_ROWDOT) return run_generic<TraitsQ8_0, 1>(n, k, m, tiles, acts, dst, lddst, s);
     if (type == B200_TYPE_Q4_0 && route == B200_ROUTE_REPACK) return run_generic<TraitsB32<false>, 2>(n, k, m, tiles, acts, dst, lddst, s);

@@ -219,4 +219,109 @@ struct TraitsB32 {
     }
 };
 
+// ---------------------------------------------------------------------------
+// Q6_K, tiled numerics (batch >= 8): crates/ggml/src/tiled.rs:723-839.
+// Per super-block s1 = sum_sub scale * (sum u8q*y - 32*bsum) (exact int32),
+// r = d_w * f32(s1), out = fma(r, d_x, out).  Same loads as the row-dot form.
+// ---------------------------------------------------------------------------
+struct TraitsQ6KTiled : TraitsQ6K {
+    static constexpr int NW = 2;
+    static constexpr int CHAINS = 1;
+    __device__ static __forceinline__ void compute(const Regs &r, const ActStage &a, uint32_t *xw) {
+        int s1 = 0;
+#pragma unroll
+        for (int n = 0; n < 2; n++)
+#pragma unroll
+            for (int l16 = 0; l16 < 2; l16++) {
+                const uint4 A = r.ql[4 * n + l16], B = r.ql[4 * n + 2 + l16], H = r.qh[2 * n + l16];
+                int d0 = 0, d1 = 0, d2 = 0, d3 = 0;
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    const uint32_t aw = word_of(A, w), bw = word_of(B, w), hw = word_of(H, w);
+                    d0 = dp4((aw & 0x0f0f0f0fu) | ((hw << 4) & 0x30303030u), word_of(a.q[8 * n + 0 + l16], w), d0);
+                    d1 = dp4((bw & 0x0f0f0f0fu) | ((hw << 2) & 0x30303030u), word_of(a.q[8 * n + 2 + l16], w), d1);
+                    d2 = dp4(((aw >> 4) & 0x0f0f0f0fu) | (hw & 0x30303030u), word_of(a.q[8 * n + 4 + l16], w), d2);
+                    d3 = dp4(((bw >> 4) & 0x0f0f0f0fu) | ((hw >> 2) & 0x30303030u), word_of(a.q[8 * n + 6 + l16], w), d3);
+                }
+                // each 16-element run is one sub-block: its scale and its bsum
+                s1 += scale_at(r.sc, 8 * n + 0 + l16) * (d0 - 32 * a.aux[8 * n + 0 + l16]);
+                s1 += scale_at(r.sc, 8 * n + 2 + l16) * (d1 - 32 * a.aux[8 * n + 2 + l16]);
+                s1 += scale_at(r.sc, 8 * n + 4 + l16) * (d2 - 32 * a.aux[8 * n + 4 + l16]);
+                s1 += scale_at(r.sc, 8 * n + 6 + l16) * (d3 - 32 * a.aux[8 * n + 6 + l16]);
+            }
+        xw[0] = (uint32_t)s1;
+        xw[32] = r.d;
+    }
+    __device__ static __forceinline__ void chain(float &acc, const uint32_t *xg, int, const ActView &acts, int64_t col,
+                                                 int64_t group) {
+        const float dx = acts.d[col * (acts.k / 256) + group];
+        const float r = __fmul_rn(f16_bits_to_f32((uint16_t)xg[32]), (float)(int)xg[0]);
+        acc = __fmaf_rn(r, dx, acc);
+    }
+};
+
+// ---------------------------------------------------------------------------
+// Q4_K, row-dot numerics (rows not a multiple of 8, fewer than 8 activation rows):
+// crates/ggml/src/vec_dot.rs:872-915.  Eight scale lanes and four min lanes.
+// ---------------------------------------------------------------------------
+struct TraitsQ4KRowDot {
+    static constexpr int TYPE = B200_TYPE_Q4_K;
+    static constexpr int CHUNK = 4608;
+    static constexpr int NW = 13;       // 8 lane sums, 4 min products, d|dmin
+    static constexpr int CHAINS = 12;
+    static constexpr bool ACT_Q8K = true;
+    struct Regs {
+        uint4 h, q[8];
+    };
+    __device__ static __forceinline__ void load(const uint8_t *chunk, int lane, Regs &r) {
+        r.h = ld_stream16(chunk + lane * 16);
+#pragma unroll
+        for (int c = 0; c < 8; c++) r.q[c] = ld_stream16(chunk + 512 + c * 512 + lane * 16);
+    }
+    __device__ static __forceinline__ void compute(const Regs &r, const ActStage &a, uint32_t *xw) {
+        const uint32_t u0 = r.h.y, u1 = r.h.z, u2 = r.h.w;
+        const uint32_t sc_lo4 = u0 & 0x3f3f3f3fu, mn_lo4 = u1 & 0x3f3f3f3fu;
+        const uint32_t sc_hi4 = (u2 & 0x0f0f0f0fu) | (((u0 >> 6) & 0x03030303u) << 4);
+        const uint32_t mn_hi4 = ((u2 >> 4) & 0x0f0f0f0fu) | (((u1 >> 6) & 0x03030303u) << 4);
+        int sumi[8];
+#pragma unroll
+        for (int l = 0; l < 8; l++) sumi[l] = 0;
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            const uint32_t s4 = g < 2 ? sc_lo4 : sc_hi4;
+            const int s_lo = (s4 >> (16 * (g & 1))) & 0xff, s_hi = (s4 >> (16 * (g & 1) + 8)) & 0xff;
+#pragma unroll
+            for (int hh = 0; hh < 2; hh++)
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    const uint32_t q = word_of(r.q[2 * g + hh], w);
+                    const int lo = dp4(q & 0x0f0f0f0fu, word_of(a.q[4 * g + hh], w), 0);
+                    const int hi = dp4((q >> 4) & 0x0f0f0f0fu, word_of(a.q[4 * g + 2 + hh], w), 0);
+                    sumi[4 * hh + w] += s_lo * lo + s_hi * hi;
+                }
+        }
+#pragma unroll
+        for (int l = 0; l < 8; l++) xw[l * 32] = (uint32_t)sumi[l];
+#pragma unroll
+        for (int l = 0; l < 4; l++) {
+            const uint32_t m4 = l < 2 ? mn_lo4 : mn_hi4;
+            const int m0 = (m4 >> (16 * (l & 1))) & 0xff, m1 = (m4 >> (16 * (l & 1) + 8)) & 0xff;
+            xw[(8 + l) * 32] = (uint32_t)(m0 * (a.aux[4 * l] + a.aux[4 * l + 1]) + m1 * (a.aux[4 * l + 2] + a.aux[4 * l + 3]));
+        }
+        xw[12 * 32] = r.h.x;
+    }
+    __device__ static __forceinline__ void chain(float &acc, const uint32_t *xg, int l, const ActView &acts, int64_t col,
+                                                 int64_t group) {
+        const float dx = acts.d[col * (acts.k / 256) + group];
+        const uint32_t hd = xg[12 * 32];
+        if (l < 8) {
+            const float d = __fmul_rn(dx, f16_bits_to_f32((uint16_t)(hd & 0xffffu)));
+            acc = __fmaf_rn(d, (float)(int)xg[l * 32], acc);
+        } else {
+            const float dmin = __fmul_rn(-dx, f16_bits_to_f32((uint16_t)(hd >> 16)));
+            acc = __fmaf_rn(dmin, (float)(int)xg[l * 32], acc);
+        }
+    }
+};
+
 }  // namespace b200

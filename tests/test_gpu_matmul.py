@@ -184,3 +184,44 @@ def test_golden_real_tensors_q6_K_and_mxfp4_blocks(dev, golden):
     got = dev.mul_mat(dev.Weight(orc.MXFP4, W, 1024), x)
     same = (got.view(np.uint32) == want.view(np.uint32)) | (np.isnan(got) & np.isnan(want))
     assert same.all()
+
+
+# ---- batched mat-mul: every route the reference takes for m >= 4 --------------------------------
+BATCHED = [
+    # (type, n, k, m, route)
+    (orc.Q4_K, 64, 512, 4, orc.ROUTE_REPACK),     # one 4-row group: 8x8 gemm numerics
+    (orc.Q4_K, 96, 1024, 9, orc.ROUTE_REPACK),    # two groups + a gemv tail row
+    (orc.Q4_K, 4096, 4096, 32, orc.ROUTE_REPACK),
+    (orc.Q4_K, 36, 512, 8, orc.ROUTE_TILED),      # rows not a multiple of 8: tiled from 8 columns on
+    (orc.Q4_K, 36, 512, 3, orc.ROUTE_ROWDOT),     # ... and the row dot below
+    (orc.Q6_K, 64, 512, 8, orc.ROUTE_TILED),
+    (orc.Q6_K, 1024, 4096, 33, orc.ROUTE_TILED),
+    (orc.Q8_0, 64, 512, 8, orc.ROUTE_ROWDOT),
+    (orc.Q4_0, 64, 512, 12, orc.ROUTE_REPACK),
+    (orc.MXFP4, 768, 2048, 8, orc.ROUTE_REPACK),
+]
+
+
+@pytest.mark.parametrize("case", BATCHED, ids=lambda c: f"{orc.TYPE_NAMES[c[0]]}-{c[1]}x{c[2]}-m{c[3]}")
+def test_batched_mat_mul_bit_exact(dev, case):
+    ty, n, k, m, route = case
+    W = synth.weights(ty, n, k, seed=51)
+    x = synth.activations(m, k, seed=52)
+    want, r = orc.mul_mat(ty, W, x)
+    assert r == route
+    assert bits_equal(dev.mul_mat(dev.Weight(ty, W, k), x), want)
+
+
+def test_golden_8x8_gemm_and_tiled_outputs(dev, golden):
+    g = golden("repack")
+    n, nrows, nr_gemv, nr_gemm, nc = (int(v) for v in g["Q4_K/dims"])
+    got = dev.mul_mat(dev.Weight(orc.Q4_K, g["Q4_K/src"].reshape(nrows, -1), n), g["Q4_K/gemm_act"])
+    assert bits_equal(got, g["Q4_K/gemm_out"])
+    t = golden("tiled")
+    names = {"Q4_K": orc.Q4_K, "Q6_K": orc.Q6_K}
+    for name, ty in names.items():
+        for shape in ("300x40", "300x12", "12x8", "188x300"):
+            key = f"mm/{name}/{shape}"
+            X = t[key + "/X"]
+            got = dev.mul_mat(dev.Weight(ty, t[key + "/W"], X.shape[1]), X)
+            assert bits_equal(got, t[key + "/dst"]), key
