@@ -223,6 +223,40 @@ class Event:
             pass
 
 
+class ExpertWeights:
+    """A quantized [n_expert, n, k] tensor on the device: one tile-layout matrix per expert, back to back."""
+
+    def __init__(self, ty, blocks, n, k):
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        self.ty, self.n, self.k = ty, int(n), int(k)
+        row_bytes = self.k // 256 * GROUP_BYTES[ty]
+        self.n_expert = blocks.size // (row_bytes * self.n)
+        assert blocks.size == self.n_expert * self.n * row_bytes
+        self.expert_bytes = lib.b200_weight_nbytes(ty, self.n, self.k)
+        self.buf = DeviceBuffer(self.expert_bytes * self.n_expert)
+        flat = blocks.reshape(self.n_expert, self.n * row_bytes)
+        for e in range(self.n_expert):
+            check(lib.b200_weight_upload(ty, self.n, self.k, flat[e].ctypes.data, self.buf.ptr + e * self.expert_bytes,
+                                         None), "weight_upload")
+
+    @property
+    def ptr(self):
+        return self.buf.ptr
+
+
+def mul_mat_id(w, b, ids):
+    """w: ExpertWeights; b: f32 [n_tok, ne11, k]; ids: i32 [n_tok, n_ids] -> f32 [n_tok, n_ids, n]."""
+    b = np.ascontiguousarray(b, dtype=np.float32)
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    n_tok, ne11, k = b.shape
+    n_ids = ids.shape[1]
+    db, dids = device_array(b), device_array(ids)
+    dst = DeviceBuffer(4 * n_tok * n_ids * w.n)
+    check(lib.b200_mul_mat_id(w.ty, w.n, k, w.n_expert, ne11, n_tok, n_ids, w.ptr, db.ptr, dids.ptr, dst.ptr, 0, None),
+          "mul_mat_id")
+    return dst.download(np.float32, n_tok * n_ids * w.n).reshape(n_tok, n_ids, w.n)
+
+
 class FlashAttnArgs(C.Structure):
     """struct b200_flash_attn_args"""
     _fields_ = [

@@ -401,11 +401,38 @@ int b200_mul_mat_host(int type, int64_t n, int64_t k, int64_t m, const void *dev
     return B200_STATUS_SUCCESS;
 }
 
-int b200_mul_mat_id(int, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, const void *, const float *,
-                    const int32_t *, float *, int, void *) {
-    set_error("mul_mat_id: not built yet");
-    return B200_STATUS_BACKEND_ERROR;
+int b200_mul_mat_id(int type, int64_t n, int64_t k, int64_t n_expert, int64_t ne11, int64_t n_tok, int64_t n_ids,
+                    const void *dev_as, const float *dev_b, const int32_t *dev_ids, float *dev_dst, int route,
+                    void *stream) {
+    (void)route;  // the route follows from the expert type and shape as in the reference
+    B200_REQUIRE(is_quant_type(type), "mul_mat_id: expert type %d is not supported", type);
+    B200_REQUIRE(n >= 0 && k > 0 && n_expert > 0 && ne11 > 0 && n_tok >= 0 && n_ids >= 0, "mul_mat_id: bad shape");
+    B200_REQUIRE(k % GROUP_K == 0, "mul_mat_id: k = %lld must be a multiple of 256", (long long)k);
+    if (n == 0 || n_tok == 0 || n_ids == 0) return B200_STATUS_SUCCESS;
+    B200_REQUIRE(dev_as && dev_b && dev_ids && dev_dst, "mul_mat_id: null pointer");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int64_t rows = ne11 * n_tok;   // every b row is quantized once (compute.rs:1952-1985)
+    const size_t act_b = act_scratch_bytes(rows, k);
+    void *scratch = nullptr;
+    int rc = scratch_get(act_b + sizeof(int) * (size_t)n_expert + 256, &scratch);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    ActBuf a = act_carve(scratch, rows, k);
+    int *counts = (int *)((uint8_t *)scratch + act_b);
+    // rows in passes of 65535 (one launch's grid.y limit)
+    for (int64_t r0 = 0; r0 < rows; r0 += 65535) {
+        const int64_t nr = rows - r0 < 65535 ? rows - r0 : 65535;
+        ActBuf ar = a;
+        ar.qs += r0 * k;
+        ar.d += r0 * (k / 256);
+        ar.bsums += r0 * (k / 16);
+        ar.dh += r0 * (k / 32);
+        rc = launch_quantize_acts(is_k_quant(type) ? B200_ACT_Q8_K : B200_ACT_Q8_0, nr, k, dev_b + r0 * k, k, ar, s);
+        if (rc != B200_STATUS_SUCCESS) return rc;
+    }
+    return launch_mul_mat_id(type, n, k, n_expert, ne11, n_tok, n_ids, (const uint8_t *)dev_as, a.view(), dev_ids, dev_dst,
+                             counts, s);
 }
+
 
 
 }  // extern "C"

@@ -124,6 +124,9 @@ int launch_dequantize(int type, int64_t n_rows, int64_t k, const uint8_t *tiles,
 int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts,
                 float *dst, int64_t lddst, cudaStream_t s);
 
+int launch_mul_mat_id(int type, int64_t n, int64_t k, int64_t n_expert, int64_t ne11, int64_t n_tok, int64_t n_ids,
+                      const uint8_t *tiles, ActView acts, const int32_t *ids, float *dst, int *counts, cudaStream_t s);
+
 // scratch owned by the library (one growing allocation per device)
 int scratch_get(size_t bytes, void **ptr);
 

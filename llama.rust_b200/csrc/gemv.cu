@@ -17,6 +17,39 @@ namespace b200 {
 
 constexpr int GEMV_MAX_WARPS = 16;
 
+// MUL_MAT_ID: blockIdx.y walks the (token, slot) pairs; each pair picks its expert's weights, its
+// activation row (slot % ne11 of its token) and its output row (crates/ggml/src/compute.rs:2104-2130).
+// counts/min_count/max_count let two launches with different chains split the pairs by how many rows
+// were routed to the pair's expert (the tiled chain from 8 rows on, the row dot below).
+struct PairMap {
+    const int32_t *ids;      // [n_tok][n_ids], null for plain MUL_MAT
+    int n_ids, ne11, n_expert;
+    int64_t expert_bytes;
+    const int *counts;       // rows routed to each expert, or null
+    int min_count, max_count;
+};
+
+__device__ __forceinline__ bool apply_pair(const PairMap &pm, const uint8_t *&tiles, ActView &acts, float *&dst,
+                                           int64_t lddst) {
+    if (!pm.ids) return true;
+    const int64_t pair = blockIdx.y;
+    const int e = pm.ids[pair];
+    if (e < 0 || e >= pm.n_expert) return false;
+    if (pm.counts) {
+        const int c = pm.counts[e];
+        if (c < pm.min_count || c > pm.max_count) return false;
+    }
+    const int64_t tok = pair / pm.n_ids, slot = pair % pm.n_ids;
+    const int64_t arow = tok * pm.ne11 + slot % pm.ne11;
+    tiles += (int64_t)e * pm.expert_bytes;
+    acts.qs += arow * acts.k;
+    if (acts.d) acts.d += arow * (acts.k / 256);
+    if (acts.bsums) acts.bsums += arow * (acts.k / 16);
+    if (acts.dh) acts.dh += arow * (acts.k / 32);
+    dst += pair * lddst;
+    return true;
+}
+
 // ---------------------------------------------------------------------------
 // Q4_K, route REPACK/gemv.  NCOL activation rows share one pass over the weights.
 // Shared memory: per warp staging of one activation group per column, and the
@@ -33,9 +66,9 @@ struct Q4KStage {
 //   2  tiled     (tiled.rs:823-838):    r = d*f32(s1); r = fma(-dmin, f32(s2), r); out = fma(r, d_x, out)
 template <int NCOL, int MODE>
 __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32)
-gemv_q4_K_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *__restrict__ dst, int64_t lddst, int64_t n,
-                 int nb) {
+gemv_q4_K_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, int64_t n, int nb, PairMap pm) {
     extern __shared__ __align__(16) unsigned char smem[];
+    if (!apply_pair(pm, tiles, acts, dst, lddst)) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     Q4KStage *stage = (Q4KStage *)smem + warp * NCOL;
     constexpr int XW = MODE == 1 ? 3 : 1;                           // int4 words per (col, group, row)
@@ -160,7 +193,7 @@ static int pick_warps(int nb) {
 
 template <int NCOL, int MODE>
 static int launch_q4k(int64_t n, int nb, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
-                      cudaStream_t s) {
+                      cudaStream_t s, PairMap pm = PairMap{}, int64_t pairs = 1) {
     const int nw = pick_warps(nb);
     const size_t smem = sizeof(Q4KStage) * nw * NCOL + sizeof(int4) * (size_t)NCOL * nb * 32 * (MODE == 1 ? 3 : 1);
     B200_REQUIRE(smem <= 200 * 1024, "mul_mat q4_K: k too large for the shared-memory exchange (%zu bytes)", smem);
@@ -170,7 +203,8 @@ static int launch_q4k(int64_t n, int nb, const uint8_t *tiles, ActView acts, flo
         attr_done = true;
     }
     const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
-    gemv_q4_K_kernel<NCOL, MODE><<<(unsigned)tiles_n, nw * 32, smem, s>>>(tiles, acts, dst, lddst, n, nb);
+    B200_REQUIRE(pairs >= 1 && pairs <= 65535, "mul_mat_id: %lld (token, slot) pairs exceed one launch", (long long)pairs);
+    gemv_q4_K_kernel<NCOL, MODE><<<dim3((unsigned)tiles_n, (unsigned)pairs), nw * 32, smem, s>>>(tiles, acts, dst, lddst, n, nb, pm);
     B200_CUDA(cudaGetLastError());
     return B200_STATUS_SUCCESS;
 }
@@ -183,9 +217,10 @@ static int launch_q4k(int64_t n, int nb, const uint8_t *tiles, ActView acts, flo
 // ---------------------------------------------------------------------------
 template <class T, int NCOL>
 __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32)
-gemv_generic_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *__restrict__ dst, int64_t lddst, int64_t n,
-                    int nb, int win) {
+gemv_generic_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, int64_t n, int nb, int win,
+                    PairMap pm) {
     extern __shared__ __align__(16) unsigned char smem[];
+    if (!apply_pair(pm, tiles, acts, dst, lddst)) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     ActStage *stage = (ActStage *)smem + warp * NCOL;
     float *fin = (float *)(smem + sizeof(ActStage) * nwarps * NCOL);       // [NCOL][12][32]
@@ -266,7 +301,7 @@ constexpr size_t GEMV_SMEM_LIMIT = 200 * 1024;
 
 template <class T, int NCOL>
 static int launch_generic(int64_t n, int nb, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
-                          cudaStream_t s) {
+                          cudaStream_t s, PairMap pm = PairMap{}, int64_t pairs = 1) {
     const size_t per_group = (size_t)NCOL * T::NW * 32 * 4;
     // warps: enough chain threads, and an even split of the groups when possible
     int nw = pick_warps(nb);
@@ -285,7 +320,8 @@ static int launch_generic(int64_t n, int nb, const uint8_t *tiles, ActView acts,
         attr_done = true;
     }
     const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
-    gemv_generic_kernel<T, NCOL><<<(unsigned)tiles_n, nw * 32, smem, s>>>(tiles, acts, dst, lddst, n, nb, win);
+    B200_REQUIRE(pairs >= 1 && pairs <= 65535, "mul_mat_id: %lld (token, slot) pairs exceed one launch", (long long)pairs);
+    gemv_generic_kernel<T, NCOL><<<dim3((unsigned)tiles_n, (unsigned)pairs), nw * 32, smem, s>>>(tiles, acts, dst, lddst, n, nb, win, pm);
     B200_CUDA(cudaGetLastError());
     return B200_STATUS_SUCCESS;
 }
@@ -355,6 +391,58 @@ int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint
     if (type == B200_TYPE_Q4_0 && route == B200_ROUTE_REPACK) return run_generic<TraitsB32<false>, 2>(n, k, m, tiles, acts, dst, lddst, s);
     if (type == B200_TYPE_MXFP4 && route == B200_ROUTE_REPACK) return run_generic<TraitsB32<true>, 2>(n, k, m, tiles, acts, dst, lddst, s);
     B200_REQUIRE(false, "mul_mat: no kernel yet for weight type %d with route %d (m = %lld)", type, route, (long long)m);
+}
+
+// rows routed to each expert (for the tiled / row-dot split of K-quant experts)
+__global__ void count_expert_rows_kernel(const int32_t *ids, int64_t n_pairs, int n_expert, int *counts) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_pairs) return;
+    const int e = ids[i];
+    if (e >= 0 && e < n_expert) atomicAdd(&counts[e], 1);
+}
+
+// MUL_MAT_ID: crates/ggml/src/compute.rs:1917-2202.  Experts whose row count is a multiple of 8
+// run the 8x8 gemv chain per pair (MXFP4, Q4_0, Q4_K); other K-quant experts take the tiled chain
+// when at least 8 rows were routed to them and the row dot otherwise; the rest is the row dot.
+int launch_mul_mat_id(int type, int64_t n, int64_t k, int64_t n_expert, int64_t ne11, int64_t n_tok, int64_t n_ids,
+                      const uint8_t *tiles, ActView acts, const int32_t *ids, float *dst, int *counts, cudaStream_t s) {
+    B200_REQUIRE(k % GROUP_K == 0, "mul_mat_id: k = %lld must be a multiple of 256", (long long)k);
+    const int nb = (int)(k / GROUP_K);
+    const int64_t pairs = n_tok * n_ids;
+    if (pairs == 0 || n == 0) return B200_STATUS_SUCCESS;
+    PairMap pm{};
+    pm.ids = ids;
+    pm.n_ids = (int)n_ids;
+    pm.ne11 = (int)ne11;
+    pm.n_expert = (int)n_expert;
+    pm.expert_bytes = (int64_t)((n + TILE_ROWS - 1) / TILE_ROWS) * nb * chunk_bytes(type);
+    pm.counts = nullptr;
+    pm.min_count = 0;
+    pm.max_count = 0x7fffffff;
+    const bool repack = n % 8 == 0;
+    if (type == B200_TYPE_MXFP4 && repack) return launch_generic<TraitsB32<true>, 1>(n, nb, tiles, acts, dst, n, s, pm, pairs);
+    if (type == B200_TYPE_Q4_0 && repack) return launch_generic<TraitsB32<false>, 1>(n, nb, tiles, acts, dst, n, s, pm, pairs);
+    if (type == B200_TYPE_Q4_K && repack) return launch_q4k<1, 0>(n, nb, tiles, acts, dst, n, s, pm, pairs);
+    if (type == B200_TYPE_Q8_0) return launch_generic<TraitsQ8_0, 1>(n, nb, tiles, acts, dst, n, s, pm, pairs);
+    if (type == B200_TYPE_Q4_K || type == B200_TYPE_Q6_K) {
+        B200_CUDA(cudaMemsetAsync(counts, 0, sizeof(int) * n_expert, s));
+        count_expert_rows_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, s>>>(ids, pairs, (int)n_expert, counts);
+        B200_CUDA(cudaGetLastError());
+        pm.counts = counts;
+        PairMap lo = pm, hi = pm;
+        lo.max_count = 7;
+        hi.min_count = 8;
+        int rc;
+        if (type == B200_TYPE_Q4_K) {
+            rc = launch_q4k<1, 2>(n, nb, tiles, acts, dst, n, s, hi, pairs);
+            if (rc == B200_STATUS_SUCCESS) rc = launch_generic<TraitsQ4KRowDot, 1>(n, nb, tiles, acts, dst, n, s, lo, pairs);
+        } else {
+            rc = launch_generic<TraitsQ6KTiled, 1>(n, nb, tiles, acts, dst, n, s, hi, pairs);
+            if (rc == B200_STATUS_SUCCESS) rc = launch_generic<TraitsQ6K, 1>(n, nb, tiles, acts, dst, n, s, lo, pairs);
+        }
+        return rc;
+    }
+    B200_REQUIRE(false, "mul_mat_id: no kernel for expert type %d with %lld rows per expert", type, (long long)n);
 }
 
 }  // namespace b200
