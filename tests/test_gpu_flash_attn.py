@@ -119,6 +119,39 @@ def test_fully_masked_rows_and_padded_cache(dev):
     assert not got[2].any()
 
 
+def test_reference_dump_cases_tiled(dev, golden):
+    """The 64-row-or-more cases of the reference's dump: plain, ragged KV tail, DV != DK, no mask,
+    sinks (bit-exact); softcap and ALiBi go through tanhf / powf and are held to the tolerance."""
+    g = golden("flash_attn")
+    seen = 0
+    for c in case_names(g):
+        d = load_case(g, c)
+        if d["T"] < 64 or d["q"].shape[2] not in (64, 128) or d["v"].shape[2] not in (64, 128):
+            continue
+        kv = dev.KvCacheView(d["k"], d["v"])
+        got = dev.flash_attn(d["q"], kv, d["mask"], d["scale"], sinks=d["sinks"], max_bias=d["max_bias"],
+                             softcap=d["softcap"])
+        if d["softcap"] == 0.0 and d["max_bias"] == 0.0:
+            assert bits_equal(got, d["dst"]), c
+        else:
+            scale = np.abs(d["dst"]).max(axis=-1, keepdims=True)
+            assert (np.abs(got - d["dst"]) <= REL_TOL * scale).all(), c
+        seen += 1
+    assert seen >= 8
+
+
+@pytest.mark.parametrize("shape", [(512, 512), (512, 4096), (100, 300), (64, 64)], ids=str)
+def test_prefill_gqa_head_dim_128(dev, shape):
+    """BASELINE shape (D 128, 32 heads over 8 KV heads, causal) through the tiled path."""
+    T, n_kv = shape
+    q, k, v, mask = synth_case(32, 8, 128, T, n_kv, seed=T + n_kv)
+    want, path = orc.flash_attn(q, k, v, mask, 1.0 / np.sqrt(128.0))
+    assert path == orc.FA_TILED
+    got = dev.flash_attn(q, dev.KvCacheView(k, v), mask, 1.0 / np.sqrt(128.0))
+    assert rel_err(got, want).max() <= REL_TOL
+    assert bits_equal(got, want)
+
+
 def test_softcap_and_sinks_within_tolerance(dev):
     q, k, v, mask = synth_case(8, 2, 64, 4, 333, seed=77)
     sinks = np.random.default_rng(3).standard_normal(8).astype(np.float32)
