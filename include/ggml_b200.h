@@ -66,6 +66,10 @@ int b200_set_device(int device);
 int b200_device_info(int device, char *name, size_t name_len, size_t *free_bytes, size_t *total_bytes,
                      int *sm_count, int *cc_major, int *cc_minor);
 int b200_synchronize(void *stream);
+/* Kernels that wait on barriers bound every wait; a wait that ran out records a non-zero code on the
+ * device instead of hanging it.  Reads and clears that code for the current device (0 = none).
+ * (Failure reporting of the kind ggml_backend_i.synchronize surfaces: crates/ggml/src/backend.rs:761-765.) */
+int b200_kernel_error(int *code);
 
 /* ---- device memory (cudaMalloc-backed; buffers of the backend use the same) */
 int b200_malloc(void **dev_ptr, size_t bytes);

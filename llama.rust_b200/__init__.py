@@ -92,6 +92,13 @@ def synchronize(stream=None):
     check(lib.b200_synchronize(stream), "synchronize")
 
 
+def kernel_error():
+    """Code left by a kernel whose bounded wait ran out (0 = none); cleared by the read."""
+    code = C.c_int(0)
+    check(lib.b200_kernel_error(C.byref(code)), "kernel_error")
+    return code.value
+
+
 class DeviceBuffer:
     """A cudaMalloc allocation owned by Python."""
 

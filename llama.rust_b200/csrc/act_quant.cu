@@ -37,6 +37,8 @@ ActBuf act_carve(void *scratch, int64_t m, int64_t k) {
 // A2 / A3: one CTA of 256 threads per (256-element block, row).
 template <bool A3>
 __global__ void __launch_bounds__(256) quantize_q8_K_kernel(const float *__restrict__ x, int64_t ldx, ActBuf out) {
+    pdl_trigger();
+    pdl_wait();   // x comes from the previous kernel; the scratch written here may still be read by it
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int64_t blk = blockIdx.x, row = blockIdx.y;
     const int64_t nb = out.k / 256;
@@ -92,6 +94,8 @@ __global__ void __launch_bounds__(256) quantize_q8_K_kernel(const float *__restr
 
 // A1: one warp per 32-element block, 8 blocks per CTA.
 __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float *__restrict__ x, int64_t ldx, ActBuf out) {
+    pdl_trigger();
+    pdl_wait();
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int64_t row = blockIdx.y;
     const int64_t blk = (int64_t)blockIdx.x * 8 + warp;
@@ -116,18 +120,19 @@ int launch_quantize_acts(int kind, int64_t m, int64_t k, const float *x, int64_t
     if (kind == B200_ACT_Q8_0) {
         B200_REQUIRE(k > 0 && k % 32 == 0, "quantize q8_0: k = %lld must be a positive multiple of 32", (long long)k);
         dim3 grid((unsigned)((k / 32 + 7) / 8), (unsigned)m);
-        quantize_q8_0_kernel<<<grid, 256, 0, s>>>(x, ldx, out);
+        return launch_pdl(quantize_q8_0_kernel, grid, dim3(256), 0, s, x, ldx, out);
     } else if (kind == B200_ACT_Q8_K || kind == B200_ACT_Q8_K_4X8) {
         B200_REQUIRE(k > 0 && k % 256 == 0, "quantize q8_K: k = %lld must be a positive multiple of 256", (long long)k);
         dim3 grid((unsigned)(k / 256), (unsigned)m);
-        if (kind == B200_ACT_Q8_K) quantize_q8_K_kernel<false><<<grid, 256, 0, s>>>(x, ldx, out);
-        else quantize_q8_K_kernel<true><<<grid, 256, 0, s>>>(x, ldx, out);
+        if (kind == B200_ACT_Q8_K) return launch_pdl(quantize_q8_K_kernel<false>, grid, dim3(256), 0, s, x, ldx, out);
+        return launch_pdl(quantize_q8_K_kernel<true>, grid, dim3(256), 0, s, x, ldx, out);
     } else if (kind == B200_ACT_Q8_K_MIXED) {
         B200_REQUIRE(k > 0 && k % 256 == 0, "quantize q8_K: k = %lld must be a positive multiple of 256", (long long)k);
         const int64_t m4 = m - m % 4;
         if (m4 > 0) {
             dim3 grid((unsigned)(k / 256), (unsigned)m4);
-            quantize_q8_K_kernel<true><<<grid, 256, 0, s>>>(x, ldx, out);
+            int rc = launch_pdl(quantize_q8_K_kernel<true>, grid, dim3(256), 0, s, x, ldx, out);
+            if (rc != B200_STATUS_SUCCESS) return rc;
         }
         if (m > m4) {
             ActBuf tail = out;
@@ -135,7 +140,8 @@ int launch_quantize_acts(int kind, int64_t m, int64_t k, const float *x, int64_t
             tail.d += m4 * (k / 256);
             tail.bsums += m4 * (k / 16);
             dim3 grid((unsigned)(k / 256), (unsigned)(m - m4));
-            quantize_q8_K_kernel<false><<<grid, 256, 0, s>>>(x + m4 * ldx, ldx, tail);
+            int rc = launch_pdl(quantize_q8_K_kernel<false>, grid, dim3(256), 0, s, x + m4 * ldx, ldx, tail);
+            if (rc != B200_STATUS_SUCCESS) return rc;
         }
     } else {
         B200_REQUIRE(false, "quantize: unknown activation kind %d", kind);

@@ -3,6 +3,7 @@
 // kernels are in the other translation units.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -24,6 +25,15 @@ int cuda_fail(cudaError_t e, const char *what, const char *file, int line) {
     set_error("CUDA error %d (%s) at %s:%d: %s", (int)e, cudaGetErrorString(e), file, line, what);
     if (e == cudaErrorMemoryAllocation) return B200_STATUS_ALLOC_FAILED;
     return B200_STATUS_BACKEND_ERROR;
+}
+
+bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
 }
 
 // ---- scratch: one growing allocation per device ------------------------------
@@ -128,6 +138,11 @@ int b200_device_info(int device, char *name, size_t name_len, size_t *free_bytes
 int b200_synchronize(void *stream) {
     B200_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     return B200_STATUS_SUCCESS;
+}
+
+int b200_kernel_error(int *code) {
+    B200_REQUIRE(code != nullptr, "kernel_error: null out pointer");
+    return gemv_stream_error(code);
 }
 
 int b200_malloc(void **dev_ptr, size_t bytes) {

@@ -124,6 +124,8 @@ int launch_dequantize(int type, int64_t n_rows, int64_t k, const uint8_t *tiles,
 int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts,
                 float *dst, int64_t lddst, cudaStream_t s);
 
+int launch_gemv_q4_K_stream(int64_t n, int64_t k, const uint8_t *tiles, ActView acts, float *dst, cudaStream_t s);
+int gemv_stream_error(int *code);
 int launch_mul_mat_id(int type, int64_t n, int64_t k, int64_t n_expert, int64_t ne11, int64_t n_tok, int64_t n_ids,
                       const uint8_t *tiles, ActView acts, const int32_t *ids, float *dst, int *counts, cudaStream_t s);
 
@@ -133,6 +135,33 @@ int scratch_get(size_t bytes, void **ptr);
 // route the reference takes for (type, n, m), and the activation quantizer that route reads
 int pick_route(int type, int64_t n, int64_t m);
 int act_kind_for(int type, int route, int64_t m);
+
+// ---- programmatic dependent launch ---------------------------------------------
+// Kernels launched through launch_pdl() may start while the previous kernel in the stream is still
+// running.  Each of them calls pdl_trigger() early (so that its own successor may start) and
+// pdl_wait() before it reads anything a previous kernel wrote or writes anything a previous kernel
+// reads; what they do before pdl_wait() (index set-up, streaming the weights in) overlaps the tail of
+// the previous kernel.  B200_PDL=0 in the environment turns the attribute off.
+bool pdl_enabled();
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    B200_CUDA(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+    return B200_STATUS_SUCCESS;
+}
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
 
 // ---- device helpers ----------------------------------------------------------
 #ifdef __CUDACC__

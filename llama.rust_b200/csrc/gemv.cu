@@ -10,6 +10,8 @@
 // exactly as the CPU route does, so the result is bit-identical to it:
 //   Q4_K 8x8 gemv   crates/ggml/src/repack.rs:1638-1688 (one fma per super-block
 //                   for the scale term and one for the min term, out = acc - accmin)
+#include <cstdlib>
+
 #include "common.cuh"
 #include "gemv_types.cuh"
 
@@ -68,7 +70,10 @@ template <int NCOL, int MODE>
 __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32)
 gemv_q4_K_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, int64_t n, int nb, PairMap pm) {
     extern __shared__ __align__(16) unsigned char smem[];
+    pdl_trigger();
+    if (pm.ids) pdl_wait();   // the expert ids come from a previous kernel
     if (!apply_pair(pm, tiles, acts, dst, lddst)) return;
+    bool waited = pm.ids != nullptr;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     Q4KStage *stage = (Q4KStage *)smem + warp * NCOL;
     constexpr int XW = MODE == 1 ? 3 : 1;                           // int4 words per (col, group, row)
@@ -82,6 +87,8 @@ gemv_q4_K_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, 
         uint4 q[8];
 #pragma unroll
         for (int c = 0; c < 8; c++) q[c] = ld_stream16(chunk + 512 + c * 512 + lane * 16);
+        // the weight loads above are in flight; the activations are the previous kernel's output
+        if (!waited) { pdl_wait(); waited = true; }
         // stage this group's activations for every column
 #pragma unroll
         for (int col = 0; col < NCOL; col++) {
@@ -146,6 +153,7 @@ gemv_q4_K_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, 
         }
         __syncwarp();
     }
+    if (!waited) pdl_wait();
     __syncthreads();
     // accumulation chains, ascending K: threads (col, row)
     for (int t = threadIdx.x; t < NCOL * 32; t += blockDim.x) {
@@ -204,9 +212,8 @@ static int launch_q4k(int64_t n, int nb, const uint8_t *tiles, ActView acts, flo
     }
     const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
     B200_REQUIRE(pairs >= 1 && pairs <= 65535, "mul_mat_id: %lld (token, slot) pairs exceed one launch", (long long)pairs);
-    gemv_q4_K_kernel<NCOL, MODE><<<dim3((unsigned)tiles_n, (unsigned)pairs), nw * 32, smem, s>>>(tiles, acts, dst, lddst, n, nb, pm);
-    B200_CUDA(cudaGetLastError());
-    return B200_STATUS_SUCCESS;
+    return launch_pdl(gemv_q4_K_kernel<NCOL, MODE>, dim3((unsigned)tiles_n, (unsigned)pairs), dim3(nw * 32), smem, s, tiles,
+                      acts, dst, lddst, n, nb, pm);
 }
 
 // ---------------------------------------------------------------------------
@@ -220,7 +227,10 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32)
 gemv_generic_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, int64_t n, int nb, int win,
                     PairMap pm) {
     extern __shared__ __align__(16) unsigned char smem[];
+    pdl_trigger();
+    if (pm.ids) pdl_wait();
     if (!apply_pair(pm, tiles, acts, dst, lddst)) return;
+    bool waited = pm.ids != nullptr;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     ActStage *stage = (ActStage *)smem + warp * NCOL;
     float *fin = (float *)(smem + sizeof(ActStage) * nwarps * NCOL);       // [NCOL][12][32]
@@ -238,6 +248,7 @@ gemv_generic_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t ldds
             const int b = w0 + g;
             typename T::Regs regs;
             T::load(base + (int64_t)b * T::CHUNK, lane, regs);
+            if (!waited) { pdl_wait(); waited = true; }
 #pragma unroll
             for (int col = 0; col < NCOL; col++) {
                 const int8_t *aq = acts.qs + (int64_t)col * acts.k + (int64_t)b * 256;
@@ -267,6 +278,7 @@ gemv_generic_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t ldds
                 T::compute(regs, stage[col], xch + ((int64_t)(col * win + g) * T::NW) * 32 + lane);
             __syncwarp();
         }
+        if (!waited) { pdl_wait(); waited = true; }
         __syncthreads();
         if (is_chain) {
             for (int g = 0; g < wn; g++)
@@ -321,9 +333,8 @@ static int launch_generic(int64_t n, int nb, const uint8_t *tiles, ActView acts,
     }
     const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
     B200_REQUIRE(pairs >= 1 && pairs <= 65535, "mul_mat_id: %lld (token, slot) pairs exceed one launch", (long long)pairs);
-    gemv_generic_kernel<T, NCOL><<<dim3((unsigned)tiles_n, (unsigned)pairs), nw * 32, smem, s>>>(tiles, acts, dst, lddst, n, nb, win, pm);
-    B200_CUDA(cudaGetLastError());
-    return B200_STATUS_SUCCESS;
+    return launch_pdl(gemv_generic_kernel<T, NCOL>, dim3((unsigned)tiles_n, (unsigned)pairs), dim3(nw * 32), smem, s,
+                      tiles, acts, dst, lddst, n, nb, win, pm);
 }
 
 // columns in passes of at most MAXC; the weights are re-read per pass (decode shapes only)
@@ -348,10 +359,37 @@ static int run_generic(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, Ac
     return B200_STATUS_SUCCESS;
 }
 
+// B200_GEMV_STREAM=0 in the environment selects the register-staged kernel instead of the
+// bulk-copy streaming one (for side-by-side measurements); read once.
+static bool gemv_stream_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_GEMV_STREAM");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+static int64_t gemv_stream_max_tiles() {
+    static int64_t v = -1;
+    if (v < 0) {
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            sms = 0;
+        v = sms;
+    }
+    return v;
+}
+
 int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst,
                 int64_t lddst, cudaStream_t s) {
     B200_REQUIRE(k % GROUP_K == 0, "gemv: k = %lld must be a multiple of 256", (long long)k);
     const int nb = (int)(k / GROUP_K);
+    // the bulk-copy streaming kernel wins while every CTA has at most one row tile (no second wave to
+    // overlap); beyond that the register-staged kernel with two CTAs per SM keeps more warps busy
+    if (type == B200_TYPE_Q4_K && route == B200_ROUTE_REPACK && m == 1 && gemv_stream_enabled() &&
+        (n + TILE_ROWS - 1) / TILE_ROWS <= gemv_stream_max_tiles())
+        return launch_gemv_q4_K_stream(n, k, tiles, acts, dst, s);
     if (type == B200_TYPE_Q4_K && (route == B200_ROUTE_REPACK || route == B200_ROUTE_TILED)) {
         // REPACK: the caller quantized the first m - m % 4 rows with the 4x8 rule (gemm chain) and the
         // tail rows the plain way (gemv chain), exactly as crates/ggml/src/compute.rs:5322-5447 does.
