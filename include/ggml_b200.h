@@ -183,6 +183,57 @@ struct b200_flash_attn_args {
 };
 int b200_flash_attn_ext(const struct b200_flash_attn_args *args, void *stream);
 
+/* ---- the f32 ops between the mat-muls of a decoder layer -------------------------------------------
+ * Each replaces one arm of the CPU engine's dispatch (crates/ggml/src/compute.rs:1026-1110) and performs
+ * the same rounded operations per element.  Pointers are device pointers; row strides count elements
+ * unless the name says nb (bytes).  Rows hold ne0 dense elements. */
+
+/* RMS_NORM, crates/ggml/src/compute.rs:2634-2683.  y may be null when only the weighted result is wanted.
+ * With weight != null also writes y_weighted = (x * scale) * weight[i], the MUL that follows the norm in
+ * every decoder (crates/llama/src/graph_arch.rs:1119-1122). */
+int b200_rms_norm(const float *x, int64_t x_stride, float *y, int64_t y_stride, const float *weight, float *y_weighted,
+                  int64_t y_weighted_stride, int64_t ne0, int64_t nrows, float eps, void *stream);
+
+/* ADD (op 0) / MUL (op 1) of F32 tensors with ggml's row broadcast, crates/ggml/src/compute.rs:1174-1330:
+ * y[r][i] = a[r][i] op b[r % b_rows][i % b_ne0]. */
+int b200_binary(int op, const float *a, int64_t a_stride, const float *b, int64_t b_stride, int64_t b_ne0, int64_t b_rows, float *y,
+                int64_t y_stride, int64_t ne0, int64_t nrows, void *stream);
+
+/* UNARY(SILU), crates/ggml/src/compute.rs:3109-3135 -> crates/ggml/src/simd_x86.rs:1012-1054.  wide != 0
+ * reproduces a host with AVX512F+DQ (16-lane chunks through the polynomial exp, the row tail through libm
+ * expf), wide == 0 a host without (libm throughout); b200_host_silu_is_wide() reports this host.  With
+ * gate != null also writes y_gated = silu(x) * gate, the MUL that follows in the FFN
+ * (crates/llama/src/graph_arch.rs:1150-1151). */
+int b200_silu(const float *x, int64_t x_stride, const float *gate, int64_t gate_stride, float *y, int64_t y_stride, float *y_gated,
+              int64_t y_gated_stride, int64_t ne0, int64_t nrows, int wide, void *stream);
+int b200_host_silu_is_wide(void);
+
+/* ROPE, crates/ggml/src/compute.rs:3679-3800, modes NORMAL (0) and NEOX (2), F32.
+ * b200_rope_table fills a HOST table [n_tok][ne0] of (cos, sin) pairs from HOST positions with the host
+ * libm, as rope_cache_init (:3539-3566) does; freq_factors is a host array of ne0/2 floats or null.
+ * b200_rope rotates x [ne0, n_head, n_tok] (byte strides nb1 per head, nb2 per token) into y with a copy
+ * of that table in device memory. */
+int b200_rope_table(const int32_t *pos, int64_t n_tok, int64_t ne0, const float *freq_factors, int n_dims, int n_ctx_orig,
+                    float freq_base, float freq_scale, float ext_factor, float attn_factor, float beta_fast, float beta_slow,
+                    float *table);
+int b200_rope(const float *x, int64_t x_nb1, int64_t x_nb2, float *y, int64_t y_nb1, int64_t y_nb2, const float *table, int64_t ne0,
+              int64_t n_head, int64_t n_tok, int n_dims, int mode, void *stream);
+
+/* SET_ROWS of F32 rows into an F16 destination with I64 indices (the KV-cache write),
+ * crates/ggml/src/compute.rs:4265-4338.  A row whose index is outside [0, dst_rows) is skipped and
+ * b200_kernel_error() reports code 2 afterwards (the CPU engine asserts). */
+int b200_set_rows_f16(const float *x, int64_t x_stride, const int64_t *idx, void *dst, int64_t dst_stride, int64_t dst_rows,
+                      int64_t ne0, int64_t nrows, void *stream);
+
+/* GET_ROWS to F32, crates/ggml/src/compute.rs:3842-3895.  table: F32 or F16 dense rows, or a quantized
+ * tensor in the tile layout of b200_weight_upload.  An id outside [0, table_rows) is skipped and
+ * b200_kernel_error() reports code 1 afterwards (the CPU engine asserts). */
+int b200_get_rows(int type, const void *table, int64_t ne0, int64_t table_rows, const int32_t *ids, int64_t n, float *y,
+                  int64_t y_stride, void *stream);
+
+/* ARGMAX per row, the last index among equal maxima, crates/ggml/src/compute.rs:4208-4228. */
+int b200_argmax(const float *x, int64_t x_stride, int64_t ne0, int64_t nrows, int32_t *out, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -30,11 +30,14 @@ extern "C" {
 
 /* enum ggml_op values of the pinned header (sysffi.rs:371-451) used by this backend */
 enum {
-    GGML_OP_NONE = 0, GGML_OP_ADD = 2, GGML_OP_MUL = 7, GGML_OP_RMS_NORM = 25, GGML_OP_MUL_MAT = 29,
+    GGML_OP_NONE = 0, GGML_OP_ADD = 2, GGML_OP_MUL = 7, GGML_OP_ARGMAX = 18, GGML_OP_RMS_NORM = 25, GGML_OP_MUL_MAT = 29,
     GGML_OP_MUL_MAT_ID = 30, GGML_OP_CPY = 34, GGML_OP_CONT = 35, GGML_OP_RESHAPE = 36, GGML_OP_VIEW = 37,
     GGML_OP_PERMUTE = 38, GGML_OP_TRANSPOSE = 39, GGML_OP_GET_ROWS = 40, GGML_OP_SET_ROWS = 42,
     GGML_OP_ROPE = 48, GGML_OP_FLASH_ATTN_EXT = 74, GGML_OP_UNARY = 91, GGML_OP_GLU = 100,
 };
+
+/* enum ggml_unary_op value carried in op_params[0] of a GGML_OP_UNARY node (crates/ggml/src/ops.rs:1632-1636) */
+enum { GGML_UNARY_OP_SILU = 10 };
 
 /* enum ggml_backend_dev_type (backend.rs:1513-1523) */
 enum { GGML_BACKEND_DEVICE_TYPE_CPU = 0, GGML_BACKEND_DEVICE_TYPE_GPU = 1, GGML_BACKEND_DEVICE_TYPE_IGPU = 2,
@@ -201,7 +204,11 @@ int ggml_backend_score(void);
 
 /* Names served by reg->iface.get_proc_address:
  *   "b200_backend_set_cpu_threads": void (*)(ggml_backend_t, int) — the CPU thread count whose split-KV
- *   attention arithmetic FLASH_ATTN_EXT reproduces (crates/ggml/src/flash_attn.rs:841-859); default 8. */
+ *   attention arithmetic FLASH_ATTN_EXT reproduces (crates/ggml/src/flash_attn.rs:841-859); default 8.
+ *   "b200_backend_get_stream": void *(*)(ggml_backend_t) — the cudaStream_t the backend launches on, for
+ *   callers that time graph_compute with events or order their own work after it.
+ * init_backend's params string takes "cpu_threads=<n>" and "silu_wide=<0|1>" (which host's SILU to
+ * reproduce, see b200_silu in ggml_b200.h; default: this host's). */
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,73 @@
+/* llama_b200.h — a Llama decode driver on top of the ggml backend plug-in of libggml-b200.so.
+ *
+ * It plays the part of the reference's DecodeContext for the llama architecture: weights in device
+ * buffers (crates/llama/src/context.rs:4511-4560 enable_gpu), one unified F16 KV cache
+ * (crates/llama/src/kv_cache.rs:1887-1917), per-step inputs (context.rs:6565-6640 step_inputs_pos_rows),
+ * the node list of crates/llama/src/graph_arch.rs:106-248 build_llama_forward with the flash-attention
+ * branch of attn_kv_cached (:1173-1240), and graph_compute through the backend vtable
+ * (context.rs:4611-4646 run_graph).  Every tensor operation goes through the plug-in face declared in
+ * ggml_b200_backend.h — the driver holds no kernels of its own — so it doubles as an executable
+ * description of the graphs the backend has to serve.
+ */
+#ifndef LLAMA_B200_H
+#define LLAMA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* crates/llama/src/graph.rs:24-60 AttnParams + the llama.* GGUF keys they come from */
+struct b200_llama_hparams {
+    int32_t n_vocab;
+    int32_t n_embd;
+    int32_t n_head;
+    int32_t n_head_kv;
+    int32_t n_embd_head;      /* key and value head size */
+    int32_t n_ff;
+    int32_t n_layer;
+    int32_t n_ctx_train;      /* rope n_ctx_orig */
+    int32_t rope_mode;        /* 0 = NORMAL (llama), 2 = NEOX */
+    float norm_rms_eps;
+    float rope_freq_base;
+    float rope_freq_scale;
+};
+
+typedef struct b200_llama b200_llama;
+
+/* All functions return a b200_status (0 = success); b200_last_error() has the message. */
+
+/* device: CUDA device index.  n_ctx: KV cache cells.  n_batch: most tokens one decode call may carry.
+ * cpu_threads: the CPU thread count whose attention arithmetic is reproduced (see ggml_b200_backend.h). */
+int b200_llama_new(const struct b200_llama_hparams *hp, int device, int32_t n_ctx, int32_t n_batch, int32_t cpu_threads,
+                   b200_llama **out);
+void b200_llama_free(b200_llama *ctx);
+
+/* One model tensor under its GGUF name (crates/llama/src/model.rs: token_embd.weight, output_norm.weight,
+ * output.weight, blk.N.{attn_norm,attn_q,attn_k,attn_v,attn_output,ffn_norm,ffn_gate,ffn_up,ffn_down}.weight).
+ * data: ggml blocks of `type`, ne1 rows of ne0 elements, in host memory.  output.weight may be left out
+ * when the model ties it to token_embd.weight. */
+int b200_llama_set_tensor(b200_llama *ctx, const char *name, int type, int64_t ne0, int64_t ne1, const void *data, size_t nbytes);
+
+/* DecodeContext::decode (crates/llama/src/context.rs:4648-4680): n_tokens tokens of one sequence at the
+ * given positions are appended to the cache; logits (host, n_vocab floats, may be null) receives the last
+ * token's row, argmax (may be null) the index of its largest logit computed on the device
+ * (last index among equals, crates/ggml/src/compute.rs:4208-4228). */
+int b200_llama_decode(b200_llama *ctx, const int32_t *tokens, const int32_t *pos, int32_t n_tokens, float *logits, int32_t *argmax);
+
+/* Forget every cached position (DecodeContext::kv_clear). */
+int b200_llama_kv_clear(b200_llama *ctx);
+/* Cells in use, and the padded cell count the next step's attention would span. */
+int32_t b200_llama_kv_used(const b200_llama *ctx);
+
+/* Re-runs the graph of the last decode call `reps` times on the backend's stream with the inputs that
+ * are already on the device, timed with events on that stream; *ms receives the total.  For measuring
+ * the device-side cost of a step without the input upload and the logits read-back. */
+int b200_llama_replay(b200_llama *ctx, int32_t reps, float *ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLAMA_B200_H */

@@ -17,7 +17,7 @@ OUT = os.path.join(HERE, "libggml-b200.so")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-ffp-contract=off", "--threads", "0",
     "-shared",
     "-I", os.path.join(ROOT, "include"), "-I", CSRC,
 ]

@@ -10,6 +10,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "common.cuh"
@@ -70,13 +71,31 @@ struct BufferCtx {
     int device;
     void *base;
     std::string error;   // set by the void-returning vtable entries, reported by graph_compute
+    // Host copies of the small I32 tensors written through set_tensor (token positions), keyed by the
+    // tensor's data pointer: ROPE builds its cos/sin table on the host from them without a read-back.
+    std::mutex mu;
+    std::unordered_map<const void *, std::vector<int32_t>> i32_shadow;
 };
 struct BackendCtx {
     int device;
     cudaStream_t stream;
     int cpu_threads;
     std::string name;
+    int silu_wide;                  // 1: reproduce an AVX512 host's SILU (crates/ggml/src/simd_x86.rs:1028-1038)
+    // the quantized activations of the last MUL_MAT, reused while the next ones read the same rows
+    void *act = nullptr;
+    size_t act_bytes = 0;
+    const void *act_src = nullptr;
+    int64_t act_m = 0, act_k = 0, act_ld = 0;
+    int act_kind = 0;
+    // the ROPE table of the last ROPE node, reused while positions and parameters repeat (q and k of
+    // every layer of one graph share it)
+    float *rope_dev = nullptr;
+    size_t rope_dev_floats = 0;
+    std::vector<float> rope_host;
+    std::vector<int32_t> rope_key;
 };
+constexpr size_t SHADOW_MAX_BYTES = 1 << 20;
 
 static std::mutex g_mu;
 static std::vector<ggml_backend_device *> g_devices;
@@ -101,9 +120,14 @@ static void buf_free(ggml_backend_buffer_t b) {
 static void *buf_get_base(ggml_backend_buffer_t b) { return bctx(b)->base; }
 static int buf_init_tensor(ggml_backend_buffer_t, ggml_tensor *) { return B200_STATUS_SUCCESS; }
 
+static void shadow_drop(BufferCtx *c, const void *data) {
+    std::lock_guard<std::mutex> lk(c->mu);
+    c->i32_shadow.erase(data);
+}
 static void buf_memset_tensor(ggml_backend_buffer_t b, ggml_tensor *t, uint8_t value, size_t offset, size_t size) {
     BufferCtx *c = bctx(b);
     cudaSetDevice(c->device);
+    if (t->type == B200_TYPE_I32) shadow_drop(c, t->data);
     if (b200_memset((uint8_t *)t->data + offset, value, size, nullptr) != B200_STATUS_SUCCESS) note(c, "memset_tensor");
     cudaStreamSynchronize(nullptr);
 }
@@ -154,6 +178,18 @@ static void buf_set_tensor(ggml_backend_buffer_t b, ggml_tensor *t, const void *
         if (tiled_io(t, const_cast<void *>(data), offset, size, true) != B200_STATUS_SUCCESS) note(c, "set_tensor");
         return;
     }
+    if (t->type == B200_TYPE_I32 && ggml_nbytes(t) <= SHADOW_MAX_BYTES && offset % 4 == 0 && size % 4 == 0 &&
+        offset + size <= ggml_nbytes(t) && is_contiguous(t)) {
+        std::lock_guard<std::mutex> lk(c->mu);
+        std::vector<int32_t> &sh = c->i32_shadow[t->data];
+        const bool fresh = sh.size() != ggml_nbytes(t) / 4;
+        if (fresh && (offset != 0 || size != ggml_nbytes(t))) {
+            c->i32_shadow.erase(t->data);   // a partial write into a tensor whose other values are unknown here
+        } else {
+            sh.resize(ggml_nbytes(t) / 4);
+            memcpy((uint8_t *)sh.data() + offset, data, size);
+        }
+    }
     if (b200_memcpy_h2d((uint8_t *)t->data + offset, data, size, nullptr) != B200_STATUS_SUCCESS) note(c, "set_tensor");
     cudaStreamSynchronize(nullptr);
 }
@@ -176,13 +212,19 @@ static bool buf_cpy_tensor(ggml_backend_buffer_t b, const ggml_tensor *src, ggml
     BufferCtx *c = bctx(b);
     if (bctx(src->buffer)->device != c->device) return false;
     cudaSetDevice(c->device);
+    if (dst->type == B200_TYPE_I32) shadow_drop(c, dst->data);
     const size_t n = is_tiled_tensor(src) ? tiled_expert_bytes(src) * src->ne[2] : ggml_nbytes(src);
     return cudaMemcpy(dst->data, src->data, n, cudaMemcpyDeviceToDevice) == cudaSuccess;
 }
 static void buf_clear(ggml_backend_buffer_t b, uint8_t value) {
     BufferCtx *c = bctx(b);
     cudaSetDevice(c->device);
+    {
+        std::lock_guard<std::mutex> lk(c->mu);
+        c->i32_shadow.clear();
+    }
     if (c->base) cudaMemset(c->base, value, b->size);
+    cudaStreamSynchronize(nullptr);   // backends run on their own streams: the fill must have landed before they start
 }
 
 // ---- buffer type ----------------------------------------------------------------------------------
@@ -207,7 +249,10 @@ static ggml_backend_buffer_t buft_alloc(ggml_backend_buffer_type_t t, size_t siz
     b->iface.cpy_tensor = buf_cpy_tensor;
     b->iface.clear = buf_clear;
     b->buft = t;
-    b->context = new BufferCtx{dev, p, std::string()};
+    BufferCtx *bc = new BufferCtx();
+    bc->device = dev;
+    bc->base = p;
+    b->context = bc;
     b->size = size;
     b->usage = GGML_BACKEND_BUFFER_USAGE_ANY;
     return b;
@@ -261,28 +306,109 @@ static bool supports_flash(const ggml_tensor *op, std::string *why) {
     return true;
 }
 
+// rows of an F32 tensor addressed as base + r * nb[1]: dims above 1 must stack contiguously on dim 1
+static bool f32_rows(const ggml_tensor *t) {
+    return t && t->type == B200_TYPE_F32 && t->nb[0] == 4 && t->nb[1] % 4 == 0 && t->nb[2] == t->nb[1] * (size_t)t->ne[1] &&
+           t->nb[3] == t->nb[2] * (size_t)t->ne[2];
+}
+static int64_t nrows_of(const ggml_tensor *t) { return t->ne[1] * t->ne[2] * t->ne[3]; }
+static bool same_shape(const ggml_tensor *a, const ggml_tensor *b) {
+    return a->ne[0] == b->ne[0] && a->ne[1] == b->ne[1] && a->ne[2] == b->ne[2] && a->ne[3] == b->ne[3];
+}
+
+static bool supports_glue(const ggml_tensor *op, std::string *why) {
+    auto no = [&](const char *m) { if (why) *why = m; return false; };
+    const ggml_tensor *a = op->src[0], *b = op->src[1];
+    switch (op->op) {
+        case GGML_OP_RMS_NORM:
+            if (!f32_rows(a) || !f32_rows(op) || !same_shape(a, op)) return no("rms_norm wants dense F32 rows");
+            return true;
+        case GGML_OP_ADD: case GGML_OP_MUL:
+            if (!f32_rows(a) || !f32_rows(b) || !f32_rows(op) || !same_shape(a, op)) return no("add/mul want dense F32 rows");
+            if (same_shape(a, b)) return true;
+            // one row (or one element per row position) broadcast over every row of a
+            if (b->ne[1] * b->ne[2] * b->ne[3] == 1 && a->ne[0] % b->ne[0] == 0) return true;
+            return no("add/mul: src1 must match src0 or be a single row");
+        case GGML_OP_UNARY:
+            if (op->op_params[0] != GGML_UNARY_OP_SILU) return no("only SILU of the unary ops");
+            if (!f32_rows(a) || !f32_rows(op) || !same_shape(a, op)) return no("silu wants dense F32 rows");
+            return true;
+        case GGML_OP_ROPE: {
+            if (!a || !b || a->type != B200_TYPE_F32 || op->type != B200_TYPE_F32 || a->nb[0] != 4 || op->nb[0] != 4) return no("rope wants F32");
+            if (!same_shape(a, op) || a->ne[3] != 1) return no("rope: shape");
+            if (b->type != B200_TYPE_I32 || b->ne[0] < a->ne[2] || !is_contiguous(b)) return no("rope: positions must be I32 [n_tokens]");
+            const int mode = op->op_params[2];
+            if (mode != 0 && mode != 2) return no("rope: only NORMAL and NEOX modes");
+            if (op->op_params[15] != 0) return no("rope: channel offset is not supported");
+            if (op->src[2] && (op->src[2]->type != B200_TYPE_F32 || op->src[2]->ne[0] < a->ne[0] / 2)) return no("rope: freq factors");
+            return true;
+        }
+        case GGML_OP_SET_ROWS:
+            if (!f32_rows(a) || a->ne[2] != 1 || a->ne[3] != 1) return no("set_rows wants a 2-d F32 source");
+            if (!b || b->type != B200_TYPE_I64 || !is_contiguous(b) || b->ne[0] != a->ne[1] || b->ne[1] * b->ne[2] != 1) return no("set_rows wants I64 [n_rows] indices");
+            if (op->type != B200_TYPE_F16 || op->nb[0] != 2 || op->nb[1] % 2 || op->ne[0] != a->ne[0] || op->ne[2] != 1 || op->ne[3] != 1)
+                return no("set_rows wants a 2-d F16 destination");
+            return true;
+        case GGML_OP_GET_ROWS:
+            if (!a || !b || b->type != B200_TYPE_I32 || !is_contiguous(b) || b->ne[1] * b->ne[2] * b->ne[3] != 1) return no("get_rows wants I32 [n] ids");
+            if (a->ne[2] != 1 || a->ne[3] != 1 || !f32_rows(op) || op->ne[0] != a->ne[0] || op->ne[1] != b->ne[0]) return no("get_rows: shape");
+            if (is_quant_type(a->type)) return is_tiled_tensor(a) && is_contiguous(a) ? true : no("get_rows: quantized table must be a whole tensor");
+            if ((a->type == B200_TYPE_F32 && a->nb[0] == 4 && a->nb[1] % 4 == 0) || (a->type == B200_TYPE_F16 && a->nb[0] == 2 && a->nb[1] % 2 == 0)) return true;
+            return no("get_rows: table type");
+        case GGML_OP_ARGMAX:
+            if (!f32_rows(a) || op->type != B200_TYPE_I32 || !is_contiguous(op) || op->ne[0] != nrows_of(a)) return no("argmax wants dense F32 rows");
+            return true;
+        default: return no("op is outside the quantized mat-mul / flash-attention path");
+    }
+}
+
 static bool op_supported(const ggml_tensor *op, std::string *why) {
     switch (op->op) {
         case GGML_OP_NONE: case GGML_OP_RESHAPE: case GGML_OP_VIEW: case GGML_OP_PERMUTE: case GGML_OP_TRANSPOSE:
             return true;
         case GGML_OP_MUL_MAT: case GGML_OP_MUL_MAT_ID: return supports_mul_mat(op, why);
         case GGML_OP_FLASH_ATTN_EXT: return supports_flash(op, why);
-        default:
-            if (why) *why = "op is outside the quantized mat-mul / flash-attention path";
-            return false;
+        default: return supports_glue(op, why);
     }
 }
 
 // ---- graph_compute ----------------------------------------------------------------------------------
+static bool ranges_overlap(const void *a, size_t an, const void *b, size_t bn) {
+    const uintptr_t a0 = (uintptr_t)a, b0 = (uintptr_t)b;
+    return a0 < b0 + bn && b0 < a0 + an;
+}
+
+// MUL_MAT over one 2-d slice; consecutive mat-muls that read the same rows with the same quantizer
+// (q, k, v of a layer; gate and up of an FFN) share one quantization pass.
+static int mul_mat_2d(BackendCtx *bc, const ggml_tensor *w, const float *x, int64_t ldx, int64_t m, float *dst, int64_t lddst) {
+    const int64_t k = w->ne[0], n = w->ne[1];
+    const int route = pick_route(w->type, n, m);
+    const int kind = act_kind_for(w->type, route, m);
+    if (bc->act_src && ranges_overlap(dst, (size_t)lddst * m * 4, bc->act_src, (size_t)bc->act_ld * bc->act_m * 4)) bc->act_src = nullptr;
+    if (!(bc->act_src == x && bc->act_m == m && bc->act_k == k && bc->act_ld == ldx && bc->act_kind == kind)) {
+        const size_t need = b200_act_scratch_nbytes(m, k);
+        if (need > bc->act_bytes) {
+            if (bc->act) B200_CUDA(cudaFree(bc->act));
+            bc->act = nullptr;
+            bc->act_bytes = 0;
+            B200_CUDA(cudaMalloc(&bc->act, need));
+            bc->act_bytes = need;
+        }
+        bc->act_src = nullptr;
+        int rc = b200_quantize_activations_device(kind, m, k, x, ldx, bc->act, bc->stream);
+        if (rc != B200_STATUS_SUCCESS) return rc;
+        bc->act_src = x; bc->act_m = m; bc->act_k = k; bc->act_ld = ldx; bc->act_kind = kind;
+    }
+    return b200_mul_mat_q8(w->type, n, k, m, w->data, bc->act, kind, dst, lddst, route, bc->stream);
+}
+
 static int compute_mul_mat(BackendCtx *bc, const ggml_tensor *op) {
     const ggml_tensor *w = op->src[0], *x = op->src[1];
-    const int64_t k = w->ne[0], n = w->ne[1], m = x->ne[1];
     for (int64_t i3 = 0; i3 < x->ne[3]; i3++)
         for (int64_t i2 = 0; i2 < x->ne[2]; i2++) {
             const float *xp = (const float *)((const uint8_t *)x->data + i2 * x->nb[2] + i3 * x->nb[3]);
             float *dp = (float *)((uint8_t *)op->data + i2 * op->nb[2] + i3 * op->nb[3]);
-            int rc = b200_mul_mat(w->type, n, k, m, w->data, xp, (int64_t)(x->nb[1] / 4), dp, (int64_t)(op->nb[1] / 4),
-                                  B200_ROUTE_AUTO, bc->stream);
+            int rc = mul_mat_2d(bc, w, xp, (int64_t)(x->nb[1] / 4), x->ne[1], dp, (int64_t)(op->nb[1] / 4));
             if (rc != B200_STATUS_SUCCESS) return rc;
         }
     return B200_STATUS_SUCCESS;
@@ -312,10 +438,140 @@ static int compute_flash(BackendCtx *bc, const ggml_tensor *op) {
     return b200_flash_attn_ext(&a, bc->stream);
 }
 
+static float param_f32(const ggml_tensor *op, int i) {
+    float f;
+    memcpy(&f, &op->op_params[i], 4);
+    return f;
+}
+
+// fused: when the node after an RMS_NORM multiplies it by a one-row weight, one kernel writes both
+static int compute_rms_norm(BackendCtx *bc, const ggml_tensor *op, const ggml_tensor *mul) {
+    const ggml_tensor *x = op->src[0];
+    const float *w = mul ? (const float *)mul->src[1]->data : nullptr;
+    return b200_rms_norm((const float *)x->data, (int64_t)(x->nb[1] / 4), (float *)op->data, (int64_t)(op->nb[1] / 4), w,
+                         mul ? (float *)mul->data : nullptr, mul ? (int64_t)(mul->nb[1] / 4) : 0, x->ne[0], nrows_of(x),
+                         param_f32(op, 0), bc->stream);
+}
+static bool fuses_norm_mul(const ggml_tensor *norm, const ggml_tensor *mul) {
+    return mul->op == GGML_OP_MUL && mul->src[0] == norm && supports_glue(mul, nullptr) && mul->src[1]->ne[0] == norm->ne[0] &&
+           nrows_of(mul->src[1]) == 1 && mul->src[1]->data != norm->data;
+}
+static int compute_binary(BackendCtx *bc, const ggml_tensor *op) {
+    const ggml_tensor *a = op->src[0], *b = op->src[1];
+    return b200_binary(op->op == GGML_OP_ADD ? 0 : 1, (const float *)a->data, (int64_t)(a->nb[1] / 4), (const float *)b->data,
+                       (int64_t)(b->nb[1] / 4), b->ne[0], nrows_of(b), (float *)op->data, (int64_t)(op->nb[1] / 4), a->ne[0],
+                       nrows_of(a), bc->stream);
+}
+// fused: when the node after a SILU multiplies it by a tensor of the same shape, one kernel writes both
+static int compute_silu(BackendCtx *bc, const ggml_tensor *op, const ggml_tensor *mul) {
+    const ggml_tensor *x = op->src[0];
+    const ggml_tensor *g = mul ? mul->src[1] : nullptr;
+    return b200_silu((const float *)x->data, (int64_t)(x->nb[1] / 4), g ? (const float *)g->data : nullptr,
+                     g ? (int64_t)(g->nb[1] / 4) : 0, (float *)op->data, (int64_t)(op->nb[1] / 4), mul ? (float *)mul->data : nullptr,
+                     mul ? (int64_t)(mul->nb[1] / 4) : 0, x->ne[0], nrows_of(x), bc->silu_wide, bc->stream);
+}
+static bool fuses_silu_mul(const ggml_tensor *silu, const ggml_tensor *mul) {
+    return mul->op == GGML_OP_MUL && mul->src[0] == silu && supports_glue(mul, nullptr) && same_shape(mul->src[1], silu);
+}
+
+static int compute_rope(BackendCtx *bc, const ggml_tensor *op) {
+    const ggml_tensor *x = op->src[0], *pos = op->src[1], *ff = op->src[2];
+    const int64_t ne0 = x->ne[0], n_head = x->ne[1], n_tok = x->ne[2];
+    if (n_tok == 0 || n_head == 0) return B200_STATUS_SUCCESS;
+    // positions: the host copy kept by set_tensor, else read back
+    std::vector<int32_t> p;
+    if (in_our_buffer(pos)) {
+        BufferCtx *c = bctx(pos->buffer);
+        std::lock_guard<std::mutex> lk(c->mu);
+        auto it = c->i32_shadow.find(pos->data);
+        if (it != c->i32_shadow.end() && (int64_t)it->second.size() >= n_tok) p.assign(it->second.begin(), it->second.begin() + n_tok);
+    }
+    if (p.empty()) {
+        p.resize(n_tok);
+        B200_CUDA(cudaStreamSynchronize(bc->stream));
+        B200_CUDA(cudaMemcpy(p.data(), pos->data, n_tok * 4, cudaMemcpyDeviceToHost));
+    }
+    std::vector<float> factors;
+    if (ff) {
+        factors.resize(ne0 / 2);
+        B200_CUDA(cudaStreamSynchronize(bc->stream));
+        B200_CUDA(cudaMemcpy(factors.data(), ff->data, factors.size() * 4, cudaMemcpyDeviceToHost));
+    }
+    // table key: parameters, head size, factor bits, positions
+    std::vector<int32_t> key(op->op_params, op->op_params + 16);
+    key.push_back((int32_t)ne0);
+    for (float f : factors) { int32_t b; memcpy(&b, &f, 4); key.push_back(b); }
+    key.insert(key.end(), p.begin(), p.end());
+    const size_t floats = (size_t)n_tok * ne0;
+    if (key != bc->rope_key || bc->rope_dev == nullptr) {
+        bc->rope_key.clear();
+        if (floats > bc->rope_dev_floats) {
+            if (bc->rope_dev) B200_CUDA(cudaFree(bc->rope_dev));
+            bc->rope_dev = nullptr;
+            bc->rope_dev_floats = 0;
+            B200_CUDA(cudaMalloc((void **)&bc->rope_dev, floats * 4));
+            bc->rope_dev_floats = floats;
+        }
+        bc->rope_host.resize(floats);
+        int rc = b200_rope_table(p.data(), n_tok, ne0, ff ? factors.data() : nullptr, op->op_params[1], op->op_params[4], param_f32(op, 5),
+                                 param_f32(op, 6), param_f32(op, 7), param_f32(op, 8), param_f32(op, 9), param_f32(op, 10),
+                                 bc->rope_host.data());
+        if (rc != B200_STATUS_SUCCESS) return rc;
+        // pageable source: the runtime has taken its copy of rope_host when this returns
+        B200_CUDA(cudaMemcpyAsync(bc->rope_dev, bc->rope_host.data(), floats * 4, cudaMemcpyHostToDevice, bc->stream));
+        bc->rope_key = key;
+    }
+    return b200_rope((const float *)x->data, (int64_t)x->nb[1], (int64_t)x->nb[2], (float *)op->data, (int64_t)op->nb[1],
+                     (int64_t)op->nb[2], bc->rope_dev, ne0, n_head, n_tok, op->op_params[1], op->op_params[2], bc->stream);
+}
+
+static int compute_set_rows(BackendCtx *bc, const ggml_tensor *op) {
+    const ggml_tensor *x = op->src[0], *idx = op->src[1];
+    return b200_set_rows_f16((const float *)x->data, (int64_t)(x->nb[1] / 4), (const int64_t *)idx->data, op->data,
+                             (int64_t)(op->nb[1] / 2), op->ne[1], x->ne[0], x->ne[1], bc->stream);
+}
+static int compute_get_rows(BackendCtx *bc, const ggml_tensor *op) {
+    const ggml_tensor *t = op->src[0], *ids = op->src[1];
+    if (!is_quant_type(t->type)) {
+        // dense tables may be row-strided views: pass the stride through the row length the kernel uses
+        const int64_t es = t->type == B200_TYPE_F32 ? 4 : 2;
+        B200_REQUIRE((int64_t)t->nb[1] == t->ne[0] * es, "get_rows: dense table rows must be packed");
+    }
+    return b200_get_rows(t->type, t->data, t->ne[0], t->ne[1], (const int32_t *)ids->data, ids->ne[0], (float *)op->data,
+                         (int64_t)(op->nb[1] / 4), bc->stream);
+}
+static int compute_argmax(BackendCtx *bc, const ggml_tensor *op) {
+    const ggml_tensor *x = op->src[0];
+    return b200_argmax((const float *)x->data, (int64_t)(x->nb[1] / 4), x->ne[0], nrows_of(x), (int32_t *)op->data, bc->stream);
+}
+
+// A SILU whose product with the up projection comes a few nodes later (the graph's depth-first order
+// puts the up mat-mul between them: crates/llama/src/graph_arch.rs:1137-1151) waits for that MUL, and one
+// kernel then writes both results.  Returns the MUL's index, or -1 when the SILU has to run on its own.
+static int find_silu_mul(const ggml_cgraph *g, int i) {
+    const ggml_tensor *silu = g->nodes[i];
+    for (int j = i + 1; j < g->n_nodes && j <= i + 4; j++) {
+        const ggml_tensor *n = g->nodes[j];
+        if (!n) return -1;
+        if (n->op == GGML_OP_MUL && fuses_silu_mul(silu, n)) return j;
+        if (n->view_src == silu) return -1;
+        for (int s = 0; s < GGML_MAX_SRC; s++)
+            if (n->src[s] == silu) return -1;
+        // a node that overwrites the SILU's input or output in place would change what the fused kernel reads
+        if (n->data && silu->src[0]->data &&
+            (ranges_overlap(n->data, ggml_nbytes(n), silu->src[0]->data, ggml_nbytes(silu->src[0])) ||
+             ranges_overlap(n->data, ggml_nbytes(n), silu->data, ggml_nbytes(silu))))
+            return -1;
+    }
+    return -1;
+}
+
 static int backend_graph_compute(ggml_backend_t be, ggml_cgraph *g) {
     BackendCtx *bc = (BackendCtx *)be->context;
     B200_REQUIRE(g != nullptr && (g->n_nodes == 0 || g->nodes != nullptr), "graph_compute: null graph");
     B200_CUDA(cudaSetDevice(bc->device));
+    bc->act_src = nullptr;   // tensors may have been rewritten between graphs
+    std::vector<int> silu_of(g->n_nodes, -1);   // silu_of[j] = i: MUL node j also computes SILU node i
     for (int i = 0; i < g->n_nodes; i++) {
         const ggml_tensor *op = g->nodes[i];
         B200_REQUIRE(op != nullptr, "graph_compute: node %d is null", i);
@@ -331,12 +587,51 @@ static int backend_graph_compute(ggml_backend_t be, ggml_cgraph *g) {
                 return B200_STATUS_BACKEND_ERROR;
             }
         }
+        const bool is_alias = op->op == GGML_OP_NONE || op->op == GGML_OP_RESHAPE || op->op == GGML_OP_VIEW ||
+                              op->op == GGML_OP_PERMUTE || op->op == GGML_OP_TRANSPOSE;
+        if (is_alias) continue;
+        const ggml_tensor *next = i + 1 < g->n_nodes ? g->nodes[i + 1] : nullptr;
+        // a node that writes over the rows whose quantized copy is cached ends that copy's life
+        if (bc->act_src && op->data && ranges_overlap(op->data, ggml_nbytes(op), bc->act_src, (size_t)bc->act_ld * bc->act_m * 4))
+            bc->act_src = nullptr;
+        if (op->type == B200_TYPE_I32 && in_our_buffer(op)) shadow_drop(bctx(op->buffer), op->data);
         int rc = B200_STATUS_SUCCESS;
         switch (op->op) {
             case GGML_OP_MUL_MAT: rc = compute_mul_mat(bc, op); break;
             case GGML_OP_MUL_MAT_ID: rc = compute_mul_mat_id(bc, op); break;
             case GGML_OP_FLASH_ATTN_EXT: rc = compute_flash(bc, op); break;
-            default: break;   // views and leaves: nothing to run
+            case GGML_OP_RMS_NORM:
+                if (next && fuses_norm_mul(op, next)) {
+                    if (bc->act_src && ranges_overlap(next->data, ggml_nbytes(next), bc->act_src, (size_t)bc->act_ld * bc->act_m * 4))
+                        bc->act_src = nullptr;
+                    rc = compute_rms_norm(bc, op, next);
+                    i++;
+                } else {
+                    rc = compute_rms_norm(bc, op, nullptr);
+                }
+                break;
+            case GGML_OP_UNARY: {
+                const int j = find_silu_mul(g, i);
+                if (j > 0) silu_of[j] = i;   // runs with node j
+                else rc = compute_silu(bc, op, nullptr);
+                break;
+            }
+            case GGML_OP_MUL:
+                if (silu_of[i] >= 0) {
+                    const ggml_tensor *silu = g->nodes[silu_of[i]];
+                    if (bc->act_src && ranges_overlap(silu->data, ggml_nbytes(silu), bc->act_src, (size_t)bc->act_ld * bc->act_m * 4))
+                        bc->act_src = nullptr;
+                    rc = compute_silu(bc, silu, op);
+                } else {
+                    rc = compute_binary(bc, op);
+                }
+                break;
+            case GGML_OP_ADD: rc = compute_binary(bc, op); break;
+            case GGML_OP_ROPE: rc = compute_rope(bc, op); break;
+            case GGML_OP_SET_ROWS: rc = compute_set_rows(bc, op); break;
+            case GGML_OP_GET_ROWS: rc = compute_get_rows(bc, op); break;
+            case GGML_OP_ARGMAX: rc = compute_argmax(bc, op); break;
+            default: break;
         }
         if (rc != B200_STATUS_SUCCESS) return rc;
     }
@@ -349,6 +644,9 @@ static void backend_free(ggml_backend_t be) {
     BackendCtx *bc = (BackendCtx *)be->context;
     cudaSetDevice(bc->device);
     cudaStreamSynchronize(bc->stream);
+    if (bc->act) cudaFree(bc->act);
+    if (bc->rope_dev) cudaFree(bc->rope_dev);
+    cudaStreamDestroy(bc->stream);
     delete bc;
     delete be;
 }
@@ -366,6 +664,7 @@ static void backend_synchronize(ggml_backend_t be) {
     cudaSetDevice(bc->device);
     cudaStreamSynchronize(bc->stream);
 }
+static void *backend_get_stream(ggml_backend_t be) { return be ? (void *)((BackendCtx *)be->context)->stream : nullptr; }
 static void backend_set_cpu_threads(ggml_backend_t be, int n) {
     if (be && n > 0) ((BackendCtx *)be->context)->cpu_threads = n;
 }
@@ -394,13 +693,25 @@ static ggml_backend_t dev_init_backend(ggml_backend_dev_t d, const char *params)
         set_error("init_backend: cannot select CUDA device %d", dev);
         return nullptr;
     }
-    BackendCtx *bc = new BackendCtx{dev, nullptr, 8, std::string("B200") + std::to_string(dev)};
+    BackendCtx *bc = new BackendCtx();
+    bc->device = dev;
+    bc->cpu_threads = 8;
+    bc->name = std::string("B200") + std::to_string(dev);
+    bc->silu_wide = b200_host_silu_is_wide();
+    if (cudaStreamCreateWithFlags(&bc->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        cudaGetLastError();
+        set_error("init_backend: cannot create a stream on device %d", dev);
+        delete bc;
+        return nullptr;
+    }
     if (params) {   // "cpu_threads=<n>"
         const char *p = strstr(params, "cpu_threads=");
         if (p) {
             int n = atoi(p + 12);
             if (n > 0) bc->cpu_threads = n;
         }
+        p = strstr(params, "silu_wide=");
+        if (p) bc->silu_wide = atoi(p + 10) != 0;
     }
     ggml_backend *be = new ggml_backend();
     memset(&be->iface, 0, sizeof(be->iface));
@@ -442,6 +753,7 @@ static size_t reg_get_device_count(ggml_backend_reg_t) { return g_devices.size()
 static ggml_backend_dev_t reg_get_device(ggml_backend_reg_t, size_t i) { return i < g_devices.size() ? g_devices[i] : nullptr; }
 static void *reg_get_proc_address(ggml_backend_reg_t, const char *name) {
     if (name && strcmp(name, "b200_backend_set_cpu_threads") == 0) return (void *)backend_set_cpu_threads;
+    if (name && strcmp(name, "b200_backend_get_stream") == 0) return (void *)backend_get_stream;
     return nullptr;
 }
 

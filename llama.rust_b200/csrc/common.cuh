@@ -126,8 +126,29 @@ int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint
 
 int launch_gemv_q4_K_stream(int64_t n, int64_t k, const uint8_t *tiles, ActView acts, float *dst, cudaStream_t s);
 int gemv_stream_error(int *code);
+int device_error_word(int **flag);
+int launch_get_rows_tiled(int type, int64_t table_rows, int64_t k, const uint8_t *tiles, const int32_t *ids, int64_t n,
+                          float *out, int64_t out_stride, int *err, cudaStream_t s);
 int launch_mul_mat_id(int type, int64_t n, int64_t k, int64_t n_expert, int64_t ne11, int64_t n_tok, int64_t n_ids,
                       const uint8_t *tiles, ActView acts, const int32_t *ids, float *dst, int *counts, cudaStream_t s);
+
+// glue ops (glue_ops.cu); strides in elements unless the name says nb (bytes)
+int launch_rms_norm(const float *x, int64_t x_stride, float *y, int64_t y_stride, const float *w, float *y_mul,
+                    int64_t y_mul_stride, int64_t ne0, int64_t nrows, float eps, cudaStream_t s);
+int launch_binary(int op, const float *a, int64_t a_stride, const float *b, int64_t b_stride, int64_t b_ne0, int64_t b_rows,
+                  float *y, int64_t y_stride, int64_t ne0, int64_t nrows, cudaStream_t s);
+int launch_silu(const float *x, int64_t x_stride, const float *g, int64_t g_stride, float *y, int64_t y_stride, float *y_mul,
+                int64_t y_mul_stride, int64_t ne0, int64_t nrows, int wide, cudaStream_t s);
+void rope_table_host(const int32_t *pos, int64_t n_tok, int64_t ne0, const float *freq_factors, int n_dims, int n_ctx_orig,
+                     float freq_base, float freq_scale, float ext_factor, float attn_factor, float beta_fast, float beta_slow,
+                     float *table);
+int launch_rope(const float *x, int64_t x_nb1, int64_t x_nb2, float *y, int64_t y_nb1, int64_t y_nb2, const float *table,
+                int64_t ne0, int64_t n_head, int64_t n_tok, int n_dims, int mode, cudaStream_t s);
+int launch_set_rows_f16(const float *x, int64_t x_stride, const int64_t *idx, void *dst, int64_t dst_stride, int64_t dst_rows,
+                        int64_t ne0, int64_t nrows, cudaStream_t s);
+int launch_get_rows(int type, const void *table, int64_t ne0, int64_t table_rows, const int32_t *ids, int64_t n, float *out,
+                    int64_t out_stride, cudaStream_t s);
+int launch_argmax(const float *x, int64_t x_stride, int64_t ne0, int64_t nrows, int32_t *out, cudaStream_t s);
 
 // scratch owned by the library (one growing allocation per device)
 int scratch_get(size_t bytes, void **ptr);

@@ -42,4 +42,19 @@ __device__ __forceinline__ float libm_expf(float x) {
     return __double2float_rn(y);
 }
 
+// one lane of ggml_v_expf (AVX512F+DQ branch): crates/ggml/src/flash_attn.rs:948-975
+__device__ __forceinline__ float v_expf(float x) {
+    const float R = __uint_as_float(0x4b400000u), LOG2E = __uint_as_float(0x3fb8aa3bu);
+    const float C1 = __uint_as_float(0x35bfbe8eu), C2 = __uint_as_float(0x3f317200u);
+    const float P1 = __uint_as_float(0x3c072010u), P2 = __uint_as_float(0x3d2b9f17u), P3 = __uint_as_float(0x3e2aaf33u);
+    const float P4 = __uint_as_float(0x3efffedbu), P5 = __uint_as_float(0x3f7ffff6u);
+    const float z = __fmaf_rn(x, LOG2E, R);
+    const float n = __fsub_rn(z, R);
+    const float b = __fmaf_rn(n, -C1, __fmaf_rn(n, -C2, x));
+    const float u = __fmul_rn(b, b);
+    const float j = __fmaf_rn(__fmaf_rn(__fmaf_rn(b, P1, P2), u, __fmaf_rn(b, P3, P4)), u, __fmaf_rn(b, P5, 1.0f));
+    if (fabsf(n) > 192.0f) return n <= 0.0f ? 0.0f : __int_as_float(0x7f800000);
+    return __double2float_rn(scalbn((double)j, (int)n));   // j * 2^n, rounded once
+}
+
 }  // namespace b200

@@ -296,6 +296,20 @@ gemv_q4_K_stream_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *
 // device-side error word of the streaming kernels (one per device)
 static int *g_err_flag[64] = {nullptr};
 
+// the current device's error word, allocated on first use; kernels that skip a bad index or give
+// up a wait store a non-zero code there and b200_kernel_error() reads and clears it
+int device_error_word(int **flag) {
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    B200_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
+    if (!g_err_flag[dev]) {
+        B200_CUDA(cudaMalloc((void **)&g_err_flag[dev], sizeof(int)));
+        B200_CUDA(cudaMemset(g_err_flag[dev], 0, sizeof(int)));
+    }
+    *flag = g_err_flag[dev];
+    return B200_STATUS_SUCCESS;
+}
+
 int launch_gemv_q4_K_stream(int64_t n, int64_t k, const uint8_t *tiles, ActView acts, float *dst, cudaStream_t s) {
     const int nb = (int)(k / GROUP_K);
     const int n_tiles = (int)((n + TILE_ROWS - 1) / TILE_ROWS);
@@ -310,8 +324,9 @@ int launch_gemv_q4_K_stream(int64_t n, int64_t k, const uint8_t *tiles, ActView 
         sm_count[dev] = p.multiProcessorCount;
         B200_CUDA(cudaFuncSetAttribute(gemv_q4_K_stream_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
 
-        B200_CUDA(cudaMalloc((void **)&g_err_flag[dev], sizeof(int)));
-        B200_CUDA(cudaMemset(g_err_flag[dev], 0, sizeof(int)));
+        int *flag = nullptr;
+        int rc = device_error_word(&flag);
+        if (rc != B200_STATUS_SUCCESS) return rc;
         attr_done[dev] = true;
     }
     // exchange buffers and ring stages: the ring may not run more than (xb - 1) tiles ahead of an

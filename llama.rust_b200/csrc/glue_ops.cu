@@ -1,0 +1,387 @@
+// The f32 ops between the quantized mat-muls of a decoder layer: RMS_NORM, ADD / MUL, SILU, ROPE,
+// SET_ROWS into an F16 cache, GET_ROWS, ARGMAX.  Each kernel performs the same rounded operations per
+// element as the reference's CPU engine, so a layer's activations reach the next mat-mul's quantizer
+// with the bits the CPU path would have given them.  All of them are bound by launch latency at one
+// token and by HBM at a prompt batch; rows are read and written with coalesced 16-byte accesses.
+#include <cmath>
+#include <cstring>
+
+#include "common.cuh"
+#include "fa_math.cuh"
+
+namespace b200 {
+
+// ---- RMS_NORM (+ optional weight MUL) -----------------------------------------------------------
+// crates/ggml/src/compute.rs:2634-2683: sum of the f32 squares in f64, mean narrowed to f32,
+// scale = 1 / sqrt(mean + eps), y = x * scale.  The f64 partial sums are combined in a tree instead of
+// element order; f64 keeps 29 more bits than the f32 mean needs, so the narrowed mean is the same.
+// With w != nullptr the kernel also emits (x * scale) * w[i] (crates/llama/src/graph_arch.rs:1119-1122),
+// each product rounded on its own.  One CTA per row.
+__global__ void __launch_bounds__(256)
+rms_norm_kernel(const float *__restrict__ x, int64_t x_stride, float *y, int64_t y_stride, const float *__restrict__ w,
+                float *y_mul, int64_t y_mul_stride, int ne0, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    const float *xr = x + (int64_t)blockIdx.x * x_stride;
+    double sum = 0.0;
+    for (int i = threadIdx.x; i < ne0; i += 256) {
+        const float v = xr[i];
+        sum += (double)__fmul_rn(v, v);
+    }
+    __shared__ double part[8];
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    double total = 0.0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) total += part[i];
+    const float mean = __double2float_rn(total / (double)ne0);
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+    for (int i = threadIdx.x; i < ne0; i += 256) {
+        const float n = __fmul_rn(xr[i], scale);
+        if (y) y[(int64_t)blockIdx.x * y_stride + i] = n;
+        if (w) y_mul[(int64_t)blockIdx.x * y_mul_stride + i] = __fmul_rn(n, w[i]);
+    }
+}
+
+int launch_rms_norm(const float *x, int64_t x_stride, float *y, int64_t y_stride, const float *w, float *y_mul,
+                    int64_t y_mul_stride, int64_t ne0, int64_t nrows, float eps, cudaStream_t s) {
+    B200_REQUIRE(ne0 > 0 && ne0 < (1 << 30), "rms_norm: bad row length %lld", (long long)ne0);
+    B200_REQUIRE(nrows < 0x7fffffffLL, "rms_norm: too many rows");
+    if (nrows == 0) return B200_STATUS_SUCCESS;
+    return launch_pdl(rms_norm_kernel, dim3((unsigned)nrows), dim3(256), 0, s, x, x_stride, y, y_stride, w, y_mul, y_mul_stride,
+                      (int)ne0, eps);
+}
+
+// ---- ADD / MUL -------------------------------------------------------------------------------------
+// crates/ggml/src/compute.rs:1174-1330, F32 operands: y[r][i] = a[r][i] op b[r % b_rows][i % b_ne0].
+template <int OP>
+__global__ void __launch_bounds__(256)
+binary_kernel(const float *__restrict__ a, int64_t a_stride, const float *__restrict__ b, int64_t b_stride, int b_ne0,
+              int64_t b_rows, float *y, int64_t y_stride, int ne0, int64_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= total) return;
+    const int64_t r = i / ne0;
+    const int c = (int)(i - r * ne0);
+    const float av = a[r * a_stride + c];
+    const float bv = b[(r % b_rows) * b_stride + (b_ne0 == ne0 ? c : c % b_ne0)];
+    y[r * y_stride + c] = OP == 0 ? __fadd_rn(av, bv) : __fmul_rn(av, bv);
+}
+
+int launch_binary(int op, const float *a, int64_t a_stride, const float *b, int64_t b_stride, int64_t b_ne0, int64_t b_rows,
+                  float *y, int64_t y_stride, int64_t ne0, int64_t nrows, cudaStream_t s) {
+    B200_REQUIRE(op == 0 || op == 1, "binary: op %d is neither add (0) nor mul (1)", op);
+    B200_REQUIRE(ne0 > 0 && ne0 < (1 << 30) && b_ne0 > 0 && ne0 % b_ne0 == 0 && b_rows > 0, "binary: operand shapes do not broadcast");
+    const int64_t total = ne0 * nrows;
+    if (total == 0) return B200_STATUS_SUCCESS;
+    const int64_t blocks = (total + 255) / 256;
+    B200_REQUIRE(blocks < 0x7fffffffLL, "binary: tensor too large for one launch");
+    if (op == 0)
+        return launch_pdl(binary_kernel<0>, dim3((unsigned)blocks), dim3(256), 0, s, a, a_stride, b, b_stride, (int)b_ne0, b_rows, y,
+                          y_stride, (int)ne0, total);
+    return launch_pdl(binary_kernel<1>, dim3((unsigned)blocks), dim3(256), 0, s, a, a_stride, b, b_stride, (int)b_ne0, b_rows, y,
+                      y_stride, (int)ne0, total);
+}
+
+// ---- SILU (+ optional gate MUL) --------------------------------------------------------------------
+// crates/ggml/src/simd_x86.rs:1012-1054: on a host with AVX512F+DQ the reference runs whole 16-lane
+// chunks of a row through x / (1 + v_expf(0 - x)) and the remaining lanes through x / (1 + expf(-x))
+// with the libm expf; on other hosts every lane takes the libm form.  wide selects which host is
+// being reproduced.  With g != nullptr the kernel also emits silu(x) * g
+// (crates/llama/src/graph_arch.rs:1150-1151).
+__global__ void __launch_bounds__(256)
+silu_kernel(const float *__restrict__ x, int64_t x_stride, const float *__restrict__ g, int64_t g_stride, float *y,
+            int64_t y_stride, float *y_mul, int64_t y_mul_stride, int ne0, int wide_end, int64_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= total) return;
+    const int64_t r = i / ne0;
+    const int c = (int)(i - r * ne0);
+    const float v = x[r * x_stride + c];
+    const float e = c < wide_end ? v_expf(__fsub_rn(0.0f, v)) : libm_expf(-v);
+    const float sv = __fdiv_rn(v, __fadd_rn(1.0f, e));
+    if (y) y[r * y_stride + c] = sv;
+    if (g) y_mul[r * y_mul_stride + c] = __fmul_rn(sv, g[r * g_stride + c]);
+}
+
+int launch_silu(const float *x, int64_t x_stride, const float *g, int64_t g_stride, float *y, int64_t y_stride, float *y_mul,
+                int64_t y_mul_stride, int64_t ne0, int64_t nrows, int wide, cudaStream_t s) {
+    B200_REQUIRE(ne0 > 0 && ne0 < (1 << 30), "silu: bad row length %lld", (long long)ne0);
+    const int64_t total = ne0 * nrows;
+    if (total == 0) return B200_STATUS_SUCCESS;
+    const int64_t blocks = (total + 255) / 256;
+    B200_REQUIRE(blocks < 0x7fffffffLL, "silu: tensor too large for one launch");
+    const int wide_end = wide ? (int)(ne0 & ~(int64_t)15) : 0;
+    return launch_pdl(silu_kernel, dim3((unsigned)blocks), dim3(256), 0, s, x, x_stride, g, g_stride, y, y_stride, y_mul, y_mul_stride,
+                      (int)ne0, wide_end, total);
+}
+
+// ---- ROPE --------------------------------------------------------------------------------------------
+// The (cos, sin) table of crates/ggml/src/compute.rs:3520-3566 (rope_yarn, rope_cache_init) and :3627-3635
+// (rope_yarn_corr_dims), computed on the host with the host's libm exactly as the reference computes it:
+// table[t][i0] = cos(theta) * mscale, table[t][i0 + 1] = sin(theta) * mscale, theta walking the row in
+// steps of theta_scale = powf(freq_base, -2 / n_dims) from the token's position.
+static float rope_yarn_ramp(float low, float high, int64_t i0) {
+    const float y = ((float)(i0 / 2) - low) / fmaxf(0.001f, high - low);
+    return 1.0f - fminf(1.0f, fmaxf(0.0f, y));
+}
+
+void rope_table_host(const int32_t *pos, int64_t n_tok, int64_t ne0, const float *freq_factors, int n_dims, int n_ctx_orig,
+                     float freq_base, float freq_scale, float ext_factor, float attn_factor, float beta_fast, float beta_slow,
+                     float *table) {
+    const float theta_scale = powf(freq_base, -2.0f / (float)n_dims);
+    auto corr_dim = [&](float n_rot) {
+        return (float)n_dims * logf((float)n_ctx_orig / (n_rot * 2.0f * 3.14159265358979323846f)) / (2.0f * logf(freq_base));
+    };
+    const float corr0 = fmaxf(0.0f, floorf(corr_dim(beta_fast)));
+    const float corr1 = fminf((float)(n_dims - 1), ceilf(corr_dim(beta_slow)));
+    for (int64_t t = 0; t < n_tok; t++) {
+        float theta = (float)pos[t];
+        float *c = table + t * ne0;
+        for (int64_t i0 = 0; i0 + 1 < ne0; i0 += 2) {
+            const float ff = freq_factors ? freq_factors[i0 / 2] : 1.0f;
+            const float theta_extrap = theta / ff;
+            const float theta_interp = freq_scale * theta_extrap;
+            float th = theta_interp, mscale = attn_factor;
+            if (ext_factor != 0.0f) {
+                const float ramp_mix = rope_yarn_ramp(corr0, corr1, i0) * ext_factor;
+                th = theta_interp * (1.0f - ramp_mix) + theta_extrap * ramp_mix;
+                mscale *= 1.0f + 0.1f * logf(1.0f / freq_scale);
+            }
+            c[i0] = cosf(th) * mscale;
+            c[i0 + 1] = sinf(th) * mscale;
+            theta *= theta_scale;
+        }
+    }
+}
+
+// crates/ggml/src/compute.rs:3663-3677 rotate_pairs_f32 and :3740-3775: one thread per channel pair of
+// one head of one token.  Pairs inside n_dims rotate (adjacent channels in mode 0, channels n_dims/2
+// apart in mode 2), the rest copy.
+__global__ void __launch_bounds__(256)
+rope_kernel(const float *__restrict__ x, int64_t x_nb1, int64_t x_nb2, float *y, int64_t y_nb1, int64_t y_nb2,
+            const float *__restrict__ table, int ne0, int n_head, int n_dims, int neox, int64_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= total) return;
+    const int half = ne0 / 2;
+    const int p = (int)(i % half);
+    const int64_t row = i / half;
+    const int h = (int)(row % n_head);
+    const int64_t t = row / n_head;
+    const float *src = (const float *)((const char *)x + h * x_nb1 + t * x_nb2);
+    float *dst = (float *)((char *)y + h * y_nb1 + t * y_nb2);
+    const int i0 = 2 * p;
+    if (i0 < n_dims) {
+        const int ic = neox ? p : i0;
+        const int off = neox ? n_dims / 2 : 1;
+        const float c = table[t * ne0 + i0], s = table[t * ne0 + i0 + 1];
+        const float x0 = src[ic], x1 = src[ic + off];
+        dst[ic] = __fmaf_rn(x0, c, -__fmul_rn(x1, s));
+        dst[ic + off] = __fmaf_rn(x0, s, __fmul_rn(x1, c));
+    } else {
+        dst[i0] = src[i0];
+        dst[i0 + 1] = src[i0 + 1];
+    }
+}
+
+int launch_rope(const float *x, int64_t x_nb1, int64_t x_nb2, float *y, int64_t y_nb1, int64_t y_nb2, const float *table,
+                int64_t ne0, int64_t n_head, int64_t n_tok, int n_dims, int mode, cudaStream_t s) {
+    B200_REQUIRE(mode == 0 || mode == 2, "rope: mode %d is neither NORMAL (0) nor NEOX (2)", mode);
+    B200_REQUIRE(ne0 > 0 && ne0 % 2 == 0 && n_dims > 0 && n_dims % 2 == 0 && n_dims <= ne0, "rope: bad head size %lld / n_dims %d",
+                 (long long)ne0, n_dims);
+    const int64_t total = n_tok * n_head * (ne0 / 2);
+    if (total == 0) return B200_STATUS_SUCCESS;
+    const int64_t blocks = (total + 255) / 256;
+    B200_REQUIRE(blocks < 0x7fffffffLL && n_head < (1 << 30) && ne0 < (1 << 30), "rope: tensor too large for one launch");
+    return launch_pdl(rope_kernel, dim3((unsigned)blocks), dim3(256), 0, s, x, x_nb1, x_nb2, y, y_nb1, y_nb2, table, (int)ne0,
+                      (int)n_head, n_dims, mode == 2 ? 1 : 0, total);
+}
+
+// ---- SET_ROWS into an F16 destination ----------------------------------------------------------------
+// crates/ggml/src/compute.rs:4265-4338: row r of the f32 source goes, rounded to nearest even, to row
+// idx[r] of the destination.  An index outside the destination is skipped and raises the error word.
+__global__ void __launch_bounds__(256)
+set_rows_f16_kernel(const float *__restrict__ x, int64_t x_stride, const int64_t *__restrict__ idx, __half *dst,
+                    int64_t dst_stride, int64_t dst_rows, int ne0, int64_t total, int *err) {
+    pdl_trigger();
+    pdl_wait();
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= total) return;
+    const int64_t r = i / ne0;
+    const int c = (int)(i - r * ne0);
+    const int64_t d = idx[r];
+    if (d < 0 || d >= dst_rows) {
+        if (c == 0) atomicExch(err, 2);
+        return;
+    }
+    dst[d * dst_stride + c] = __float2half_rn(x[r * x_stride + c]);
+}
+
+int launch_set_rows_f16(const float *x, int64_t x_stride, const int64_t *idx, void *dst, int64_t dst_stride, int64_t dst_rows,
+                        int64_t ne0, int64_t nrows, cudaStream_t s) {
+    B200_REQUIRE(ne0 > 0 && ne0 < (1 << 30), "set_rows: bad row length %lld", (long long)ne0);
+    const int64_t total = ne0 * nrows;
+    if (total == 0) return B200_STATUS_SUCCESS;
+    const int64_t blocks = (total + 255) / 256;
+    B200_REQUIRE(blocks < 0x7fffffffLL, "set_rows: tensor too large for one launch");
+    int *err = nullptr;
+    int rc = device_error_word(&err);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    return launch_pdl(set_rows_f16_kernel, dim3((unsigned)blocks), dim3(256), 0, s, x, x_stride, idx, (__half *)dst, dst_stride,
+                      dst_rows, (int)ne0, total, err);
+}
+
+// ---- GET_ROWS from F32 / F16 tables ------------------------------------------------------------------
+// crates/ggml/src/compute.rs:3842-3895 (the quantized tables go through get_rows_tiled_kernel).
+template <typename T>
+__global__ void __launch_bounds__(256)
+get_rows_plain_kernel(const T *__restrict__ table, int64_t table_stride, int64_t table_rows, const int32_t *__restrict__ ids,
+                      float *out, int64_t out_stride, int ne0, int64_t total, int *err) {
+    pdl_trigger();
+    pdl_wait();
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= total) return;
+    const int64_t r = i / ne0;
+    const int c = (int)(i - r * ne0);
+    const int64_t row = ids[r];
+    if (row < 0 || row >= table_rows) {
+        if (c == 0) atomicExch(err, 1);
+        return;
+    }
+    out[r * out_stride + c] = (float)table[row * table_stride + c];
+}
+
+int launch_get_rows(int type, const void *table, int64_t ne0, int64_t table_rows, const int32_t *ids, int64_t n, float *out,
+                    int64_t out_stride, cudaStream_t s) {
+    B200_REQUIRE(ne0 > 0 && ne0 < (1 << 30), "get_rows: bad row length %lld", (long long)ne0);
+    int *err = nullptr;
+    int rc = device_error_word(&err);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    if (is_quant_type(type)) return launch_get_rows_tiled(type, table_rows, ne0, (const uint8_t *)table, ids, n, out, out_stride, err, s);
+    B200_REQUIRE(type == B200_TYPE_F32 || type == B200_TYPE_F16, "get_rows: table type %d is not supported", type);
+    const int64_t total = ne0 * n;
+    if (total == 0) return B200_STATUS_SUCCESS;
+    const int64_t blocks = (total + 255) / 256;
+    B200_REQUIRE(blocks < 0x7fffffffLL, "get_rows: too many rows for one launch");
+    if (type == B200_TYPE_F32)
+        return launch_pdl(get_rows_plain_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, (const float *)table, ne0, table_rows,
+                          ids, out, out_stride, (int)ne0, total, err);
+    return launch_pdl(get_rows_plain_kernel<__half>, dim3((unsigned)blocks), dim3(256), 0, s, (const __half *)table, ne0, table_rows, ids,
+                      out, out_stride, (int)ne0, total, err);
+}
+
+// ---- ARGMAX --------------------------------------------------------------------------------------------
+// crates/ggml/src/compute.rs:4208-4228: the largest element of each row, the last one among equals;
+// a row of NaNs or of -inf gives the reference's answers too (max stays -inf; the last -inf matches).
+__global__ void __launch_bounds__(1024)
+argmax_kernel(const float *__restrict__ x, int64_t x_stride, int32_t *out, int ne0) {
+    pdl_trigger();
+    pdl_wait();
+    const float *xr = x + (int64_t)blockIdx.x * x_stride;
+    float best = -INFINITY;
+    int at = -1;   // -1: nothing equal to the running maximum seen yet
+    for (int i = threadIdx.x; i < ne0; i += 1024) {
+        const float v = xr[i];
+        if (v > best) { best = v; at = i; }
+        else if (v == best) at = i;
+    }
+    __shared__ float sb[32];
+    __shared__ int sa[32];
+    auto merge = [](float &b, int &a, float ob, int oa) {
+        if (ob > b || (ob == b && oa > a)) { b = ob; a = oa; }
+    };
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        merge(best, at, ob, oa);
+    }
+    if ((threadIdx.x & 31) == 0) { sb[threadIdx.x >> 5] = best; sa[threadIdx.x >> 5] = at; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = sb[threadIdx.x];
+        at = sa[threadIdx.x];
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            merge(best, at, ob, oa);
+        }
+        if (threadIdx.x == 0) out[blockIdx.x] = at < 0 ? 0 : at;
+    }
+}
+
+int launch_argmax(const float *x, int64_t x_stride, int64_t ne0, int64_t nrows, int32_t *out, cudaStream_t s) {
+    B200_REQUIRE(ne0 > 0 && ne0 < (1 << 30) && nrows < 0x7fffffffLL, "argmax: bad shape");
+    if (nrows == 0) return B200_STATUS_SUCCESS;
+    return launch_pdl(argmax_kernel, dim3((unsigned)nrows), dim3(1024), 0, s, x, x_stride, out, (int)ne0);
+}
+
+}  // namespace b200
+
+// ---- C ABI ---------------------------------------------------------------------------------------------
+using namespace b200;
+
+extern "C" {
+
+int b200_rms_norm(const float *x, int64_t x_stride, float *y, int64_t y_stride, const float *weight, float *y_weighted,
+                  int64_t y_weighted_stride, int64_t ne0, int64_t nrows, float eps, void *stream) {
+    B200_REQUIRE(x != nullptr && (y != nullptr || (weight != nullptr && y_weighted != nullptr)), "rms_norm: null operand");
+    B200_REQUIRE(weight == nullptr || y_weighted != nullptr, "rms_norm: weight given without y_weighted");
+    return launch_rms_norm(x, x_stride, y, y_stride, weight, y_weighted, y_weighted_stride, ne0, nrows, eps, (cudaStream_t)stream);
+}
+
+int b200_binary(int op, const float *a, int64_t a_stride, const float *b, int64_t b_stride, int64_t b_ne0, int64_t b_rows, float *y,
+                int64_t y_stride, int64_t ne0, int64_t nrows, void *stream) {
+    B200_REQUIRE(a != nullptr && b != nullptr && y != nullptr, "binary: null operand");
+    return launch_binary(op, a, a_stride, b, b_stride, b_ne0, b_rows, y, y_stride, ne0, nrows, (cudaStream_t)stream);
+}
+
+int b200_silu(const float *x, int64_t x_stride, const float *gate, int64_t gate_stride, float *y, int64_t y_stride, float *y_gated,
+              int64_t y_gated_stride, int64_t ne0, int64_t nrows, int wide, void *stream) {
+    B200_REQUIRE(x != nullptr && (y != nullptr || (gate != nullptr && y_gated != nullptr)), "silu: null operand");
+    B200_REQUIRE(gate == nullptr || y_gated != nullptr, "silu: gate given without y_gated");
+    return launch_silu(x, x_stride, gate, gate_stride, y, y_stride, y_gated, y_gated_stride, ne0, nrows, wide, (cudaStream_t)stream);
+}
+
+int b200_host_silu_is_wide(void) { return __builtin_cpu_supports("avx512f") && __builtin_cpu_supports("avx512dq") ? 1 : 0; }
+
+int b200_rope_table(const int32_t *pos, int64_t n_tok, int64_t ne0, const float *freq_factors, int n_dims, int n_ctx_orig,
+                    float freq_base, float freq_scale, float ext_factor, float attn_factor, float beta_fast, float beta_slow,
+                    float *table) {
+    B200_REQUIRE(pos != nullptr && table != nullptr, "rope_table: null operand");
+    B200_REQUIRE(ne0 > 0 && ne0 % 2 == 0 && n_dims > 0 && n_dims % 2 == 0 && n_dims <= ne0, "rope_table: bad head size %lld / n_dims %d",
+                 (long long)ne0, n_dims);
+    rope_table_host(pos, n_tok, ne0, freq_factors, n_dims, n_ctx_orig, freq_base, freq_scale, ext_factor, attn_factor, beta_fast,
+                    beta_slow, table);
+    return B200_STATUS_SUCCESS;
+}
+
+int b200_rope(const float *x, int64_t x_nb1, int64_t x_nb2, float *y, int64_t y_nb1, int64_t y_nb2, const float *table, int64_t ne0,
+              int64_t n_head, int64_t n_tok, int n_dims, int mode, void *stream) {
+    B200_REQUIRE(x != nullptr && y != nullptr && table != nullptr, "rope: null operand");
+    B200_REQUIRE(x_nb1 % 4 == 0 && x_nb2 % 4 == 0 && y_nb1 % 4 == 0 && y_nb2 % 4 == 0, "rope: strides must be multiples of 4 bytes");
+    return launch_rope(x, x_nb1, x_nb2, y, y_nb1, y_nb2, table, ne0, n_head, n_tok, n_dims, mode, (cudaStream_t)stream);
+}
+
+int b200_set_rows_f16(const float *x, int64_t x_stride, const int64_t *idx, void *dst, int64_t dst_stride, int64_t dst_rows,
+                      int64_t ne0, int64_t nrows, void *stream) {
+    B200_REQUIRE(x != nullptr && idx != nullptr && dst != nullptr, "set_rows: null operand");
+    return launch_set_rows_f16(x, x_stride, idx, dst, dst_stride, dst_rows, ne0, nrows, (cudaStream_t)stream);
+}
+
+int b200_get_rows(int type, const void *table, int64_t ne0, int64_t table_rows, const int32_t *ids, int64_t n, float *y,
+                  int64_t y_stride, void *stream) {
+    B200_REQUIRE(table != nullptr && ids != nullptr && y != nullptr, "get_rows: null operand");
+    return launch_get_rows(type, table, ne0, table_rows, ids, n, y, y_stride, (cudaStream_t)stream);
+}
+
+int b200_argmax(const float *x, int64_t x_stride, int64_t ne0, int64_t nrows, int32_t *out, void *stream) {
+    B200_REQUIRE(x != nullptr && out != nullptr, "argmax: null operand");
+    return launch_argmax(x, x_stride, ne0, nrows, out, (cudaStream_t)stream);
+}
+
+}  // extern "C"

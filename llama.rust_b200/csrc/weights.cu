@@ -91,10 +91,7 @@ __constant__ int8_t c_kvalues_mxfp4[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -
 
 // One thread per element.  Every product/sum is an explicit round-to-nearest
 // op so that nothing is contracted into an FMA the CPU path does not have.
-__global__ void dequantize_kernel(int type, int64_t n_rows, int64_t k, const uint8_t *tiles, float *out) {
-    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_rows * k) return;
-    const int64_t row = i / k, col = i % k;
+__device__ float dequantize_element(int type, int64_t k, const uint8_t *tiles, int64_t row, int64_t col) {
     const int64_t groups = k / GROUP_K;
     const int64_t tile = row / TILE_ROWS;
     const int r = (int)(row % TILE_ROWS);
@@ -151,7 +148,28 @@ __global__ void dequantize_kernel(int type, int64_t n_rows, int64_t k, const uin
         }
         default: break;
     }
-    out[i] = v;
+    return v;
+}
+
+__global__ void dequantize_kernel(int type, int64_t n_rows, int64_t k, const uint8_t *tiles, float *out) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_rows * k) return;
+    out[i] = dequantize_element(type, k, tiles, i / k, i % k);
+}
+
+// GET_ROWS over a tiled table (crates/ggml/src/compute.rs:3842-3895): row ids[r] to f32, one
+// thread per element; an id outside the table leaves the row untouched and raises the error flag.
+__global__ void get_rows_tiled_kernel(int type, int64_t table_rows, int64_t k, const uint8_t *tiles, const int32_t *ids,
+                                      int64_t n, float *out, int64_t out_stride, int *err) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n * k) return;
+    const int64_t r = i / k, col = i % k;
+    const int64_t row = ids[r];
+    if (row < 0 || row >= table_rows) {
+        if (col == 0) atomicExch(err, 1);
+        return;
+    }
+    out[r * out_stride + col] = dequantize_element(type, k, tiles, row, col);
 }
 
 int launch_dequantize(int type, int64_t n_rows, int64_t k, const uint8_t *tiles, float *out, cudaStream_t s) {
@@ -163,6 +181,19 @@ int launch_dequantize(int type, int64_t n_rows, int64_t k, const uint8_t *tiles,
     const int64_t blocks = (total + threads - 1) / threads;
     B200_REQUIRE(blocks < 0x7fffffffLL, "dequantize: tensor too large for one launch");
     dequantize_kernel<<<(unsigned)blocks, threads, 0, s>>>(type, n_rows, k, tiles, out);
+    B200_CUDA(cudaGetLastError());
+    return B200_STATUS_SUCCESS;
+}
+
+int launch_get_rows_tiled(int type, int64_t table_rows, int64_t k, const uint8_t *tiles, const int32_t *ids, int64_t n,
+                          float *out, int64_t out_stride, int *err, cudaStream_t s) {
+    B200_REQUIRE(group_src_bytes(type) != 0, "get_rows: type %d is not a supported quantized type", type);
+    B200_REQUIRE(k > 0 && k % GROUP_K == 0, "get_rows: k = %lld must be a positive multiple of 256", (long long)k);
+    if (n == 0) return B200_STATUS_SUCCESS;
+    const int threads = 256;
+    const int64_t blocks = (n * k + threads - 1) / threads;
+    B200_REQUIRE(blocks < 0x7fffffffLL, "get_rows: too many rows for one launch");
+    get_rows_tiled_kernel<<<(unsigned)blocks, threads, 0, s>>>(type, table_rows, k, tiles, ids, n, out, out_stride, err);
     B200_CUDA(cudaGetLastError());
     return B200_STATUS_SUCCESS;
 }

@@ -1,0 +1,107 @@
+"""ctypes wrapper of the Llama decode driver (include/llama_b200.h): weights in, tokens in, logits out.
+Everything runs in libggml-b200.so; this module only moves host arrays across the C ABI."""
+import ctypes as C
+
+import numpy as np
+
+from . import F32, check, lib
+
+vp, i32, i64, sz = C.c_void_p, C.c_int32, C.c_int64, C.c_size_t
+
+
+class HParams(C.Structure):
+    _fields_ = [("n_vocab", i32), ("n_embd", i32), ("n_head", i32), ("n_head_kv", i32), ("n_embd_head", i32), ("n_ff", i32),
+                ("n_layer", i32), ("n_ctx_train", i32), ("rope_mode", i32), ("norm_rms_eps", C.c_float),
+                ("rope_freq_base", C.c_float), ("rope_freq_scale", C.c_float)]
+
+
+lib.b200_llama_new.argtypes = [C.POINTER(HParams), i32, i32, i32, i32, C.POINTER(vp)]
+lib.b200_llama_free.argtypes = [vp]
+lib.b200_llama_free.restype = None
+lib.b200_llama_set_tensor.argtypes = [vp, C.c_char_p, i32, i64, i64, vp, sz]
+lib.b200_llama_decode.argtypes = [vp, vp, vp, i32, vp, vp]
+lib.b200_llama_kv_clear.argtypes = [vp]
+lib.b200_llama_kv_used.argtypes = [vp]
+lib.b200_llama_kv_used.restype = i32
+lib.b200_llama_replay.argtypes = [vp, i32, C.POINTER(C.c_float)]
+
+# Llama-3-8B (BASELINE configuration of the tokens/s metric)
+LLAMA3_8B = dict(n_vocab=128256, n_embd=4096, n_head=32, n_head_kv=8, n_embd_head=128, n_ff=14336, n_layer=32,
+                 n_ctx_train=8192, rope_mode=0, norm_rms_eps=1e-5, rope_freq_base=500000.0, rope_freq_scale=1.0)
+
+
+def use_more_bits(i_layer, n_layers):
+    """crates/llama/src/quant.rs:709-711"""
+    return i_layer < n_layers // 8 or i_layer >= 7 * n_layers // 8 or (i_layer - n_layers // 8) % 3 == 2
+
+
+def q4_k_m_type(name, n_layer):
+    """The tensor types of a Q4_K_M file (crates/llama/src/quant.rs:786-1000): Q6_K for output.weight and
+    for attn_v / ffn_down of the layers use_more_bits picks, Q4_K for the other matrices, F32 norms."""
+    from . import Q4_K, Q6_K
+    if name.endswith("_norm.weight"):
+        return F32
+    if name == "output.weight":
+        return Q6_K
+    if name.startswith("blk.") and (".attn_v." in name or ".ffn_down." in name):
+        return Q6_K if use_more_bits(int(name.split(".")[1]), n_layer) else Q4_K
+    return Q4_K
+
+
+def tensor_shapes(hp):
+    """{gguf name: (ne0, ne1)} of a llama-architecture model"""
+    E, FF, V = hp["n_embd"], hp["n_ff"], hp["n_vocab"]
+    EQ, EK = hp["n_head"] * hp["n_embd_head"], hp["n_head_kv"] * hp["n_embd_head"]
+    shapes = {"token_embd.weight": (E, V), "output_norm.weight": (E, 1), "output.weight": (E, V)}
+    for il in range(hp["n_layer"]):
+        p = f"blk.{il}."
+        shapes.update({p + "attn_norm.weight": (E, 1), p + "attn_q.weight": (E, EQ), p + "attn_k.weight": (E, EK),
+                       p + "attn_v.weight": (E, EK), p + "attn_output.weight": (EQ, E), p + "ffn_norm.weight": (E, 1),
+                       p + "ffn_gate.weight": (E, FF), p + "ffn_up.weight": (E, FF), p + "ffn_down.weight": (FF, E)})
+    return shapes
+
+
+class Llama:
+    def __init__(self, hp, n_ctx, n_batch, device=0, cpu_threads=8):
+        self.hp = dict(hp)
+        h = HParams(**self.hp)
+        p = vp()
+        check(lib.b200_llama_new(C.byref(h), device, n_ctx, n_batch, cpu_threads, C.byref(p)), "llama_new")
+        self.ptr = p.value
+
+    def set_tensor(self, name, ty, blocks, ne0, ne1):
+        blocks = np.ascontiguousarray(blocks)
+        check(lib.b200_llama_set_tensor(self.ptr, name.encode(), ty, ne0, ne1, blocks.ctypes.data, blocks.nbytes), f"set_tensor {name}")
+
+    def decode(self, tokens, pos, logits=True, argmax=False):
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        pos = np.ascontiguousarray(pos, dtype=np.int32)
+        out = np.empty(self.hp["n_vocab"], dtype=np.float32) if logits else None
+        am = C.c_int32(-1)
+        check(lib.b200_llama_decode(self.ptr, tokens.ctypes.data, pos.ctypes.data, tokens.size,
+                                    out.ctypes.data if logits else None, C.byref(am) if argmax else None), "llama_decode")
+        if logits and argmax:
+            return out, am.value
+        return out if logits else (am.value if argmax else None)
+
+    def kv_clear(self):
+        check(lib.b200_llama_kv_clear(self.ptr), "kv_clear")
+
+    def kv_used(self):
+        return lib.b200_llama_kv_used(self.ptr)
+
+    def replay(self, reps):
+        ms = C.c_float(0)
+        check(lib.b200_llama_replay(self.ptr, reps, C.byref(ms)), "llama_replay")
+        return ms.value
+
+    def close(self):
+        if self.ptr:
+            lib.b200_llama_free(self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -336,6 +336,9 @@ void tiled(const OrcFlashArgs *a) {
 // Dispatch of crates/ggml/src/flash_attn.rs:907-939: split-KV for a single
 // query row with n_kv >= 512, tiled from 64 query rows on, else one_chunk.
 // Returns the mode taken (1 one_chunk, 2 split-KV, 3 tiled) or -1.
+// one lane of the 16-wide polynomial exp, for the glue ops that share it (silu)
+extern "C" float orc_v_expf(float x) { return v_expf(x); }
+
 extern "C" int orc_flash_attn_ext(const OrcFlashArgs *a) {
     if (!a || a->dk <= 0 || a->dv <= 0 || a->H_kv <= 0 || a->H % a->H_kv != 0) return -1;
     if (a->max_bias > 0.0f && !a->mask) return -1;
