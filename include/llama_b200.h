@@ -62,6 +62,14 @@ int b200_llama_kv_clear(b200_llama *ctx);
 /* Cells in use, and the padded cell count the next step's attention would span. */
 int32_t b200_llama_kv_used(const b200_llama *ctx);
 
+/* Reads back a tensor of the last decode call's graph by name (the last one of that name; a layer's
+ * intermediates share memory with the next layer's, so only the last layer's survive): "inp_tokens",
+ * "attn_norm", "Kcur", "Kcur_rope", "Vcur", "Qcur", "Qcur_rope", "kqv_out", "attn_out", "ffn_inp",
+ * "ffn_norm", "ffn_gate", "ffn_up", "ffn_gate_par", "ffn_out", "l_out", "result_norm",
+ * "result_output".  For node-by-node comparisons in the manner of the reference's decode dumps
+ * (parity/ref_decode_dump.c). */
+int b200_llama_read_node(b200_llama *ctx, const char *name, void *out, size_t nbytes);
+
 /* Re-runs the graph of the last decode call `reps` times on the backend's stream with the inputs that
  * are already on the device, timed with events on that stream; *ms receives the total.  For measuring
  * the device-side cost of a step without the input upload and the logits read-back. */

@@ -176,6 +176,7 @@ static void buf_set_tensor(ggml_backend_buffer_t b, ggml_tensor *t, const void *
     if (size == 0) return;
     if (is_tiled_tensor(t)) {
         if (tiled_io(t, const_cast<void *>(data), offset, size, true) != B200_STATUS_SUCCESS) note(c, "set_tensor");
+        cudaStreamSynchronize(nullptr);   // set_tensor is synchronous: the re-ordering kernel has finished on return
         return;
     }
     if (t->type == B200_TYPE_I32 && ggml_nbytes(t) <= SHADOW_MAX_BYTES && offset % 4 == 0 && size % 4 == 0 &&

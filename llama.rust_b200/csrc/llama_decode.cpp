@@ -152,7 +152,14 @@ struct Builder {
     ggml_tensor *binary(int code, ggml_tensor *a, ggml_tensor *b, const char *name = "") {
         return op(alloc(B200_TYPE_F32, a->ne[0], a->ne[1], a->ne[2], name), code, a, b);
     }
-    ggml_tensor *binary_into(ggml_tensor *dst, int code, ggml_tensor *a, ggml_tensor *b) { return op(dst, code, a, b); }
+    // a new tensor over the bytes of `slot` (the residual stream alternates between two slots)
+    ggml_tensor *over(const ggml_tensor *slot, const char *name) {
+        ggml_tensor *t = fresh(slot->type, slot->ne[0], slot->ne[1], slot->ne[2]);
+        t->data = slot->data;
+        t->buffer = slot->buffer;
+        snprintf(t->name, sizeof(t->name), "%s", name);
+        return t;
+    }
     ggml_tensor *rms_norm(ggml_tensor *a, float eps) {
         ggml_tensor *t = op(alloc(B200_TYPE_F32, a->ne[0], a->ne[1], a->ne[2]), GGML_OP_RMS_NORM, a);
         memcpy(&t->op_params[0], &eps, 4);
@@ -207,11 +214,11 @@ int build_graph(b200_llama *c, Graph *g, uint8_t *base, int64_t n, int64_t n_kv)
     g->mask = b.alloc(B200_TYPE_F16, n_kv, n, 1, "kq_mask");
     g->row_idx = b.alloc(B200_TYPE_I64, n, 1, 1, "kv_idxs");
     g->out_ids = b.alloc(B200_TYPE_I32, 1, 1, 1, "inp_out_ids");
-    ggml_tensor *resid[2] = {b.alloc(B200_TYPE_F32, E, n, 1, "l_out_a"), b.alloc(B200_TYPE_F32, E, n, 1, "l_out_b")};
+    ggml_tensor *resid[2] = {b.alloc(B200_TYPE_F32, E, n, 1, "resid_a"), b.alloc(B200_TYPE_F32, E, n, 1, "resid_b")};
 
     ggml_tensor *tok_embd = weight(c, "token_embd.weight");
     B200_REQUIRE(tok_embd != nullptr, "llama: token_embd.weight has not been set");
-    ggml_tensor *inp = b.op(resid[0], GGML_OP_GET_ROWS, tok_embd, g->tokens);
+    ggml_tensor *inp = b.op(b.over(resid[0], "inp_embd"), GGML_OP_GET_ROWS, tok_embd, g->tokens);
     const size_t layer_base = b.off;
     const float kq_scale = 1.0f / sqrtf((float)HD);
 
@@ -248,7 +255,7 @@ int build_graph(b200_llama *c, Graph *g, uint8_t *base, int64_t n, int64_t n_kv)
         ggml_tensor *gate = b.silu(b.mul_mat(wg, cur, "ffn_gate"));
         ggml_tensor *up = b.mul_mat(wu, cur, "ffn_up");
         ggml_tensor *down = b.mul_mat(wd, b.binary(GGML_OP_MUL, gate, up, "ffn_gate_par"), "ffn_out");
-        inp = b.binary_into(resid[(il + 1) & 1], GGML_OP_ADD, down, ffn_inp);
+        inp = b.op(b.over(resid[(il + 1) & 1], "l_out"), GGML_OP_ADD, down, ffn_inp);
     }
     b.off = layer_base;
     ggml_tensor *on = weight(c, "output_norm.weight");
@@ -442,6 +449,19 @@ int b200_llama_decode(b200_llama *c, const int32_t *tokens, const int32_t *pos, 
     rc = b200_kernel_error(&code);
     if (rc != B200_STATUS_SUCCESS) return rc;
     B200_REQUIRE(code == 0, "llama_decode: a kernel reported error code %d", code);
+    return B200_STATUS_SUCCESS;
+}
+
+int b200_llama_read_node(b200_llama *c, const char *name, void *out, size_t nbytes) {
+    B200_REQUIRE(c != nullptr && name != nullptr && out != nullptr, "llama_read_node: null argument");
+    B200_REQUIRE(c->last != nullptr, "llama_read_node: no decode call yet");
+    const ggml_tensor *found = nullptr;
+    for (const ggml_tensor &t : c->last->tensors)
+        if (strcmp(t.name, name) == 0) found = &t;
+    B200_REQUIRE(found != nullptr, "llama_read_node: no tensor named %s", name);
+    B200_REQUIRE(nbytes <= found->nb[3], "llama_read_node: %s holds %zu bytes, %zu asked", name, found->nb[3], nbytes);
+    c->backend->iface.get_tensor_async(c->backend, found, out, 0, nbytes);
+    c->backend->iface.synchronize(c->backend);
     return B200_STATUS_SUCCESS;
 }
 
