@@ -212,12 +212,16 @@ int b200_host_silu_is_wide(void);
  * b200_rope_table fills a HOST table [n_tok][ne0] of (cos, sin) pairs from HOST positions with the host
  * libm, as rope_cache_init (:3539-3566) does; freq_factors is a host array of ne0/2 floats or null.
  * b200_rope rotates x [ne0, n_head, n_tok] (byte strides nb1 per head, nb2 per token) into y with a copy
- * of that table in device memory. */
+ * of that table in device memory: token t uses table row t, or, when table_rows (device, I32 [n_tok]) is
+ * given, row table_rows[t] of a table of table_n_rows rows — a table built once for positions
+ * 0 .. table_n_rows-1 then serves every step with the position tensor as the index.  An index outside
+ * the table skips the token and b200_kernel_error() reports code 3. */
 int b200_rope_table(const int32_t *pos, int64_t n_tok, int64_t ne0, const float *freq_factors, int n_dims, int n_ctx_orig,
                     float freq_base, float freq_scale, float ext_factor, float attn_factor, float beta_fast, float beta_slow,
                     float *table);
-int b200_rope(const float *x, int64_t x_nb1, int64_t x_nb2, float *y, int64_t y_nb1, int64_t y_nb2, const float *table, int64_t ne0,
-              int64_t n_head, int64_t n_tok, int n_dims, int mode, void *stream);
+int b200_rope(const float *x, int64_t x_nb1, int64_t x_nb2, float *y, int64_t y_nb1, int64_t y_nb2, const float *table,
+              const int32_t *table_rows, int64_t table_n_rows, int64_t ne0, int64_t n_head, int64_t n_tok, int n_dims, int mode,
+              void *stream);
 
 /* SET_ROWS of F32 rows into an F16 destination with I64 indices (the KV-cache write),
  * crates/ggml/src/compute.rs:4265-4338.  A row whose index is outside [0, dst_rows) is skipped and

@@ -43,6 +43,13 @@ struct Scratch {
 };
 static std::mutex g_scratch_mu;
 static Scratch g_scratch[64];
+static unsigned long long g_scratch_gen = 0;
+
+// bumped whenever a scratch block is replaced: a captured CUDA graph that baked the old address in is stale
+unsigned long long scratch_generation() {
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    return g_scratch_gen;
+}
 
 int scratch_get(size_t bytes, void **ptr) {
     int dev = 0;
@@ -62,6 +69,7 @@ int scratch_get(size_t bytes, void **ptr) {
         if (want < (size_t)8 << 20) want = (size_t)8 << 20;
         B200_CUDA(cudaMalloc(&s.ptr, want));
         s.bytes = want;
+        g_scratch_gen++;
     }
     *ptr = s.ptr;
     return B200_STATUS_SUCCESS;

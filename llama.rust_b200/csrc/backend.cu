@@ -6,6 +6,7 @@
 // write, graph_compute gets one split's nodes and returns a ggml status.  Quantized tensors that live
 // in a buffer of this backend are kept in the 32-row tile layout: set_tensor re-orders the ggml blocks
 // on the way in, get_tensor on the way out, get_alloc_size reports the padded size.
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -88,14 +89,40 @@ struct BackendCtx {
     const void *act_src = nullptr;
     int64_t act_m = 0, act_k = 0, act_ld = 0;
     int act_kind = 0;
-    // the ROPE table of the last ROPE node, reused while positions and parameters repeat (q and k of
-    // every layer of one graph share it)
+    // ROPE tables.  by_pos: one row per position 0 .. rows-1 for a parameter set, indexed on the device
+    // by the position tensor, so that a step's launches do not depend on the positions' values (a few
+    // parameter sets are kept).  per_tok: the fallback for positions such a table cannot hold, one row
+    // per token of the current node.
+    struct RopeTable {
+        std::vector<int32_t> key;   // op_params, head size, frequency-factor bits
+        float *dev = nullptr;
+        int64_t rows = 0;
+        uint64_t used = 0;
+    };
+    std::vector<RopeTable> rope_by_pos;
+    uint64_t rope_clock = 0;
     float *rope_dev = nullptr;
     size_t rope_dev_floats = 0;
     std::vector<float> rope_host;
     std::vector<int32_t> rope_key;
+    // CUDA graphs of node lists seen before: the second time a list comes by unchanged it is captured,
+    // afterwards replayed.  generation counts the re-allocations that make captured addresses stale.
+    struct CapturedGraph {
+        uint64_t key = 0;
+        cudaGraphExec_t exec = nullptr;
+        uint64_t generation = 0;
+        unsigned long long scratch_generation = 0;
+        bool refused = false;     // a capture attempt failed: run this list eagerly from now on
+        uint64_t used = 0;
+    };
+    std::vector<CapturedGraph> captured;
+    uint64_t generation = 0;
+    bool graphs_enabled = true;
+    bool capturable = true;       // cleared by a node that had to talk to the device while being issued
 };
 constexpr size_t SHADOW_MAX_BYTES = 1 << 20;
+constexpr int64_t ROPE_TABLE_MIN_ROWS = 4096, ROPE_TABLE_MAX_ROWS = 1 << 20;
+constexpr size_t ROPE_TABLES_KEPT = 4, GRAPHS_KEPT = 16;
 
 static std::mutex g_mu;
 static std::vector<ggml_backend_device *> g_devices;
@@ -394,6 +421,7 @@ static int mul_mat_2d(BackendCtx *bc, const ggml_tensor *w, const float *x, int6
             bc->act_bytes = 0;
             B200_CUDA(cudaMalloc(&bc->act, need));
             bc->act_bytes = need;
+            bc->generation++;
         }
         bc->act_src = nullptr;
         int rc = b200_quantize_activations_device(kind, m, k, x, ldx, bc->act, bc->stream);
@@ -475,55 +503,149 @@ static bool fuses_silu_mul(const ggml_tensor *silu, const ggml_tensor *mul) {
     return mul->op == GGML_OP_MUL && mul->src[0] == silu && supports_glue(mul, nullptr) && same_shape(mul->src[1], silu);
 }
 
-static int compute_rope(BackendCtx *bc, const ggml_tensor *op) {
-    const ggml_tensor *x = op->src[0], *pos = op->src[1], *ff = op->src[2];
-    const int64_t ne0 = x->ne[0], n_head = x->ne[1], n_tok = x->ne[2];
-    if (n_tok == 0 || n_head == 0) return B200_STATUS_SUCCESS;
-    // positions: the host copy kept by set_tensor, else read back
-    std::vector<int32_t> p;
+// The host's view of a ROPE node's positions: the copy set_tensor kept, else a read-back (which makes the
+// node list uncapturable: issuing it talks to the device).
+static int rope_positions(BackendCtx *bc, const ggml_tensor *op, std::vector<int32_t> *p) {
+    const ggml_tensor *pos = op->src[1];
+    const int64_t n_tok = op->src[0]->ne[2];
+    p->clear();
     if (in_our_buffer(pos)) {
         BufferCtx *c = bctx(pos->buffer);
         std::lock_guard<std::mutex> lk(c->mu);
         auto it = c->i32_shadow.find(pos->data);
-        if (it != c->i32_shadow.end() && (int64_t)it->second.size() >= n_tok) p.assign(it->second.begin(), it->second.begin() + n_tok);
+        if (it != c->i32_shadow.end() && (int64_t)it->second.size() >= n_tok) p->assign(it->second.begin(), it->second.begin() + n_tok);
     }
-    if (p.empty()) {
-        p.resize(n_tok);
+    if (p->empty() && n_tok > 0) {
+        bc->capturable = false;
+        p->resize(n_tok);
         B200_CUDA(cudaStreamSynchronize(bc->stream));
-        B200_CUDA(cudaMemcpy(p.data(), pos->data, n_tok * 4, cudaMemcpyDeviceToHost));
+        B200_CUDA(cudaMemcpy(p->data(), pos->data, n_tok * 4, cudaMemcpyDeviceToHost));
     }
-    std::vector<float> factors;
-    if (ff) {
-        factors.resize(ne0 / 2);
-        B200_CUDA(cudaStreamSynchronize(bc->stream));
-        B200_CUDA(cudaMemcpy(factors.data(), ff->data, factors.size() * 4, cudaMemcpyDeviceToHost));
-    }
-    // table key: parameters, head size, factor bits, positions
+    return B200_STATUS_SUCCESS;
+}
+static int rope_factors(BackendCtx *bc, const ggml_tensor *op, std::vector<float> *f) {
+    const ggml_tensor *ff = op->src[2];
+    f->clear();
+    if (!ff) return B200_STATUS_SUCCESS;
+    bc->capturable = false;
+    f->resize(op->src[0]->ne[0] / 2);
+    B200_CUDA(cudaStreamSynchronize(bc->stream));
+    B200_CUDA(cudaMemcpy(f->data(), ff->data, f->size() * 4, cudaMemcpyDeviceToHost));
+    return B200_STATUS_SUCCESS;
+}
+static std::vector<int32_t> rope_param_key(const ggml_tensor *op, const std::vector<float> &factors) {
     std::vector<int32_t> key(op->op_params, op->op_params + 16);
-    key.push_back((int32_t)ne0);
+    key.push_back((int32_t)op->src[0]->ne[0]);
     for (float f : factors) { int32_t b; memcpy(&b, &f, 4); key.push_back(b); }
+    return key;
+}
+static int rope_fill_host(BackendCtx *bc, const ggml_tensor *op, const int32_t *pos, int64_t rows, const std::vector<float> &factors) {
+    bc->rope_host.resize((size_t)rows * op->src[0]->ne[0]);
+    return b200_rope_table(pos, rows, op->src[0]->ne[0], factors.empty() ? nullptr : factors.data(), op->op_params[1], op->op_params[4],
+                           param_f32(op, 5), param_f32(op, 6), param_f32(op, 7), param_f32(op, 8), param_f32(op, 9), param_f32(op, 10),
+                           bc->rope_host.data());
+}
+
+// Before a node list is issued: every ROPE node's by-position table exists and reaches its largest
+// position.  All device work this needs (allocation, upload) happens here, outside any capture.
+static int rope_prepare(BackendCtx *bc, const ggml_tensor *op) {
+    std::vector<int32_t> p;
+    std::vector<float> factors;
+    int rc = rope_positions(bc, op, &p);
+    if (rc == B200_STATUS_SUCCESS) rc = rope_factors(bc, op, &factors);
+    if (rc != B200_STATUS_SUCCESS || p.empty()) return rc;
+    const int32_t pmin = *std::min_element(p.begin(), p.end()), pmax = *std::max_element(p.begin(), p.end());
+    if (pmin < 0 || pmax >= ROPE_TABLE_MAX_ROWS) {
+        bc->capturable = false;   // served by the per-token table, built while the node is issued
+        return B200_STATUS_SUCCESS;
+    }
+    const std::vector<int32_t> key = rope_param_key(op, factors);
+    BackendCtx::RopeTable *t = nullptr;
+    for (auto &cand : bc->rope_by_pos)
+        if (cand.key == key) t = &cand;
+    if (t && pmax < t->rows) {
+        t->used = ++bc->rope_clock;
+        return B200_STATUS_SUCCESS;
+    }
+    if (!t) {
+        if (bc->rope_by_pos.size() >= ROPE_TABLES_KEPT) {
+            auto lru = std::min_element(bc->rope_by_pos.begin(), bc->rope_by_pos.end(),
+                                        [](const BackendCtx::RopeTable &a, const BackendCtx::RopeTable &b) { return a.used < b.used; });
+            B200_CUDA(cudaStreamSynchronize(bc->stream));
+            if (lru->dev) B200_CUDA(cudaFree(lru->dev));
+            bc->rope_by_pos.erase(lru);
+            bc->generation++;
+        }
+        bc->rope_by_pos.emplace_back();
+        t = &bc->rope_by_pos.back();
+        t->key = key;
+    }
+    int64_t rows = ROPE_TABLE_MIN_ROWS;
+    while (rows <= pmax) rows *= 2;
+    std::vector<int32_t> all(rows);
+    for (int64_t i = 0; i < rows; i++) all[i] = (int32_t)i;
+    rc = rope_fill_host(bc, op, all.data(), rows, factors);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    B200_CUDA(cudaStreamSynchronize(bc->stream));   // launches in flight may still read the smaller table
+    if (t->dev) B200_CUDA(cudaFree(t->dev));
+    t->dev = nullptr;
+    t->rows = 0;
+    bc->generation++;
+    B200_CUDA(cudaMalloc((void **)&t->dev, bc->rope_host.size() * 4));
+    B200_CUDA(cudaMemcpy(t->dev, bc->rope_host.data(), bc->rope_host.size() * 4, cudaMemcpyHostToDevice));
+    t->rows = rows;
+    t->used = ++bc->rope_clock;
+    return B200_STATUS_SUCCESS;
+}
+
+static int compute_rope(BackendCtx *bc, const ggml_tensor *op) {
+    const ggml_tensor *x = op->src[0], *pos = op->src[1];
+    const int64_t ne0 = x->ne[0], n_head = x->ne[1], n_tok = x->ne[2];
+    if (n_tok == 0 || n_head == 0) return B200_STATUS_SUCCESS;
+    if (!op->src[2]) {
+        const std::vector<int32_t> key = rope_param_key(op, std::vector<float>());
+        for (auto &t : bc->rope_by_pos)
+            if (t.key == key && t.dev)   // rope_prepare made it cover this node's positions; the kernel checks again
+                return b200_rope((const float *)x->data, (int64_t)x->nb[1], (int64_t)x->nb[2], (float *)op->data, (int64_t)op->nb[1],
+                                 (int64_t)op->nb[2], t.dev, (const int32_t *)pos->data, t.rows, ne0, n_head, n_tok, op->op_params[1],
+                                 op->op_params[2], bc->stream);
+    }
+    // per-token table: frequency factors, or positions a by-position table cannot hold
+    std::vector<int32_t> p;
+    std::vector<float> factors;
+    int rc = rope_positions(bc, op, &p);
+    if (rc == B200_STATUS_SUCCESS) rc = rope_factors(bc, op, &factors);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    bc->capturable = false;
+    if (!factors.empty()) {
+        const std::vector<int32_t> key = rope_param_key(op, factors);
+        for (auto &t : bc->rope_by_pos)
+            if (t.key == key && t.dev && *std::min_element(p.begin(), p.end()) >= 0 && *std::max_element(p.begin(), p.end()) < t.rows)
+                return b200_rope((const float *)x->data, (int64_t)x->nb[1], (int64_t)x->nb[2], (float *)op->data, (int64_t)op->nb[1],
+                                 (int64_t)op->nb[2], t.dev, (const int32_t *)pos->data, t.rows, ne0, n_head, n_tok, op->op_params[1],
+                                 op->op_params[2], bc->stream);
+    }
+    std::vector<int32_t> key = rope_param_key(op, factors);
     key.insert(key.end(), p.begin(), p.end());
     const size_t floats = (size_t)n_tok * ne0;
     if (key != bc->rope_key || bc->rope_dev == nullptr) {
         bc->rope_key.clear();
         if (floats > bc->rope_dev_floats) {
+            B200_CUDA(cudaStreamSynchronize(bc->stream));
             if (bc->rope_dev) B200_CUDA(cudaFree(bc->rope_dev));
             bc->rope_dev = nullptr;
             bc->rope_dev_floats = 0;
             B200_CUDA(cudaMalloc((void **)&bc->rope_dev, floats * 4));
             bc->rope_dev_floats = floats;
         }
-        bc->rope_host.resize(floats);
-        int rc = b200_rope_table(p.data(), n_tok, ne0, ff ? factors.data() : nullptr, op->op_params[1], op->op_params[4], param_f32(op, 5),
-                                 param_f32(op, 6), param_f32(op, 7), param_f32(op, 8), param_f32(op, 9), param_f32(op, 10),
-                                 bc->rope_host.data());
+        rc = rope_fill_host(bc, op, p.data(), n_tok, factors);
         if (rc != B200_STATUS_SUCCESS) return rc;
         // pageable source: the runtime has taken its copy of rope_host when this returns
         B200_CUDA(cudaMemcpyAsync(bc->rope_dev, bc->rope_host.data(), floats * 4, cudaMemcpyHostToDevice, bc->stream));
         bc->rope_key = key;
     }
     return b200_rope((const float *)x->data, (int64_t)x->nb[1], (int64_t)x->nb[2], (float *)op->data, (int64_t)op->nb[1],
-                     (int64_t)op->nb[2], bc->rope_dev, ne0, n_head, n_tok, op->op_params[1], op->op_params[2], bc->stream);
+                     (int64_t)op->nb[2], bc->rope_dev, nullptr, 0, ne0, n_head, n_tok, op->op_params[1], op->op_params[2], bc->stream);
 }
 
 static int compute_set_rows(BackendCtx *bc, const ggml_tensor *op) {
@@ -567,10 +689,8 @@ static int find_silu_mul(const ggml_cgraph *g, int i) {
     return -1;
 }
 
-static int backend_graph_compute(ggml_backend_t be, ggml_cgraph *g) {
-    BackendCtx *bc = (BackendCtx *)be->context;
-    B200_REQUIRE(g != nullptr && (g->n_nodes == 0 || g->nodes != nullptr), "graph_compute: null graph");
-    B200_CUDA(cudaSetDevice(bc->device));
+// Issues the launches of every node, in order, on the backend's stream.
+static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
     bc->act_src = nullptr;   // tensors may have been rewritten between graphs
     std::vector<int> silu_of(g->n_nodes, -1);   // silu_of[j] = i: MUL node j also computes SILU node i
     for (int i = 0; i < g->n_nodes; i++) {
@@ -639,14 +759,123 @@ static int backend_graph_compute(ggml_backend_t be, ggml_cgraph *g) {
     return B200_STATUS_SUCCESS;
 }
 
+// ---- CUDA graphs over repeated node lists ---------------------------------------------------------------
+// A decode loop hands the same node list (same tensors, same addresses) to graph_compute once per token,
+// and at one token the list is launch-bound: some hundreds of kernels of a few microseconds each.  The
+// second time a list comes by unchanged its launches are captured into a CUDA graph (the programmatic
+// dependent-launch edges between the kernels included), and from then on one graph launch replays them.
+// What a launch reads from the host while being issued must therefore not depend on values that change
+// between tokens: positions reach ROPE through the position tensor on the device (rope_prepare), and the
+// key below covers everything else a node's launches are derived from.
+static uint64_t fnv(uint64_t h, const void *p, size_t n) {
+    const uint8_t *b = (const uint8_t *)p;
+    for (size_t i = 0; i < n; i++) h = (h ^ b[i]) * 0x100000001b3ull;
+    return h;
+}
+static uint64_t node_list_key(const BackendCtx *bc, const ggml_cgraph *g) {
+    uint64_t h = 0xcbf29ce484222325ull;
+    h = fnv(h, &bc->cpu_threads, sizeof(int));
+    h = fnv(h, &bc->silu_wide, sizeof(int));
+    h = fnv(h, &g->n_nodes, sizeof(int));
+    for (int i = 0; i < g->n_nodes; i++) {
+        const ggml_tensor *t = g->nodes[i];
+        if (!t) continue;
+        h = fnv(h, &t->type, sizeof(int32_t));
+        h = fnv(h, t->ne, sizeof(t->ne) + sizeof(t->nb));
+        h = fnv(h, &t->op, sizeof(int32_t) + sizeof(t->op_params));
+        h = fnv(h, &t->data, sizeof(void *));
+        for (int s = 0; s < GGML_MAX_SRC; s++) {
+            const ggml_tensor *src = t->src[s];
+            if (!src) continue;
+            h = fnv(h, &src->type, sizeof(int32_t));
+            h = fnv(h, src->ne, sizeof(src->ne) + sizeof(src->nb));
+            h = fnv(h, &src->data, sizeof(void *));
+        }
+    }
+    return h;
+}
+static void drop_captured(BackendCtx *bc) {
+    for (auto &c : bc->captured)
+        if (c.exec) cudaGraphExecDestroy(c.exec);
+    bc->captured.clear();
+}
+
+static int backend_graph_compute(ggml_backend_t be, ggml_cgraph *g) {
+    BackendCtx *bc = (BackendCtx *)be->context;
+    B200_REQUIRE(g != nullptr && (g->n_nodes == 0 || g->nodes != nullptr), "graph_compute: null graph");
+    B200_CUDA(cudaSetDevice(bc->device));
+    bc->capturable = true;
+    for (int i = 0; i < g->n_nodes; i++) {
+        const ggml_tensor *op = g->nodes[i];
+        if (op && op->op == GGML_OP_ROPE && supports_glue(op, nullptr)) {
+            int rc = rope_prepare(bc, op);
+            if (rc != B200_STATUS_SUCCESS) return rc;
+        }
+    }
+    if (!bc->graphs_enabled || !bc->capturable || g->n_nodes < 16) return run_nodes(bc, g);
+
+    const uint64_t key = node_list_key(bc, g);
+    const unsigned long long sgen = scratch_generation();
+    BackendCtx::CapturedGraph *c = nullptr;
+    for (auto &cand : bc->captured)
+        if (cand.key == key) c = &cand;
+    static uint64_t clock = 0;
+    if (!c) {   // first sight: run it eagerly (this also grows every scratch block to its working size)
+        if (bc->captured.size() >= GRAPHS_KEPT) {
+            auto lru = std::min_element(bc->captured.begin(), bc->captured.end(),
+                                        [](const BackendCtx::CapturedGraph &a, const BackendCtx::CapturedGraph &b) { return a.used < b.used; });
+            if (lru->exec) cudaGraphExecDestroy(lru->exec);
+            bc->captured.erase(lru);
+        }
+        bc->captured.emplace_back();
+        bc->captured.back().key = key;
+        bc->captured.back().used = ++clock;
+        return run_nodes(bc, g);
+    }
+    c->used = ++clock;
+    if (c->refused) return run_nodes(bc, g);
+    if (c->exec && (c->generation != bc->generation || c->scratch_generation != sgen)) {
+        cudaGraphExecDestroy(c->exec);   // an address it holds has been re-allocated since
+        c->exec = nullptr;
+    }
+    if (!c->exec) {
+        cudaGraph_t graph = nullptr;
+        B200_CUDA(cudaStreamBeginCapture(bc->stream, cudaStreamCaptureModeThreadLocal));
+        const int rc = run_nodes(bc, g);
+        const cudaError_t e = cudaStreamEndCapture(bc->stream, &graph);
+        if (rc != B200_STATUS_SUCCESS || e != cudaSuccess || !graph || !bc->capturable || scratch_generation() != sgen) {
+            if (graph) cudaGraphDestroy(graph);
+            cudaGetLastError();
+            c->refused = true;
+            if (rc != B200_STATUS_SUCCESS && e == cudaSuccess) return rc;   // the list itself is at fault
+            return run_nodes(bc, g);
+        }
+        const cudaError_t ei = cudaGraphInstantiate(&c->exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (ei != cudaSuccess) {
+            cudaGetLastError();
+            c->exec = nullptr;
+            c->refused = true;
+            return run_nodes(bc, g);
+        }
+        c->generation = bc->generation;
+        c->scratch_generation = sgen;
+    }
+    B200_CUDA(cudaGraphLaunch(c->exec, bc->stream));
+    return B200_STATUS_SUCCESS;
+}
+
 // ---- backend -------------------------------------------------------------------------------------
 static const char *backend_get_name(ggml_backend_t be) { return ((BackendCtx *)be->context)->name.c_str(); }
 static void backend_free(ggml_backend_t be) {
     BackendCtx *bc = (BackendCtx *)be->context;
     cudaSetDevice(bc->device);
     cudaStreamSynchronize(bc->stream);
+    drop_captured(bc);
     if (bc->act) cudaFree(bc->act);
     if (bc->rope_dev) cudaFree(bc->rope_dev);
+    for (auto &t : bc->rope_by_pos)
+        if (t.dev) cudaFree(t.dev);
     cudaStreamDestroy(bc->stream);
     delete bc;
     delete be;
@@ -699,6 +928,10 @@ static ggml_backend_t dev_init_backend(ggml_backend_dev_t d, const char *params)
     bc->cpu_threads = 8;
     bc->name = std::string("B200") + std::to_string(dev);
     bc->silu_wide = b200_host_silu_is_wide();
+    {
+        const char *e = getenv("B200_CUDA_GRAPHS");
+        if (e && e[0] == '0') bc->graphs_enabled = false;
+    }
     if (cudaStreamCreateWithFlags(&bc->stream, cudaStreamNonBlocking) != cudaSuccess) {
         cudaGetLastError();
         set_error("init_backend: cannot create a stream on device %d", dev);
@@ -713,6 +946,8 @@ static ggml_backend_t dev_init_backend(ggml_backend_dev_t d, const char *params)
         }
         p = strstr(params, "silu_wide=");
         if (p) bc->silu_wide = atoi(p + 10) != 0;
+        p = strstr(params, "cuda_graphs=");
+        if (p) bc->graphs_enabled = atoi(p + 12) != 0;
     }
     ggml_backend *be = new ggml_backend();
     memset(&be->iface, 0, sizeof(be->iface));

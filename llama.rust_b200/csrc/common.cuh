@@ -143,7 +143,8 @@ void rope_table_host(const int32_t *pos, int64_t n_tok, int64_t ne0, const float
                      float freq_base, float freq_scale, float ext_factor, float attn_factor, float beta_fast, float beta_slow,
                      float *table);
 int launch_rope(const float *x, int64_t x_nb1, int64_t x_nb2, float *y, int64_t y_nb1, int64_t y_nb2, const float *table,
-                int64_t ne0, int64_t n_head, int64_t n_tok, int n_dims, int mode, cudaStream_t s);
+                const int32_t *rows, int64_t n_rows, int64_t ne0, int64_t n_head, int64_t n_tok, int n_dims, int mode, cudaStream_t s);
+unsigned long long scratch_generation();
 int launch_set_rows_f16(const float *x, int64_t x_stride, const int64_t *idx, void *dst, int64_t dst_stride, int64_t dst_rows,
                         int64_t ne0, int64_t nrows, cudaStream_t s);
 int launch_get_rows(int type, const void *table, int64_t ne0, int64_t table_rows, const int32_t *ids, int64_t n, float *out,

@@ -160,10 +160,12 @@ void rope_table_host(const int32_t *pos, int64_t n_tok, int64_t ne0, const float
 
 // crates/ggml/src/compute.rs:3663-3677 rotate_pairs_f32 and :3740-3775: one thread per channel pair of
 // one head of one token.  Pairs inside n_dims rotate (adjacent channels in mode 0, channels n_dims/2
-// apart in mode 2), the rest copy.
+// apart in mode 2), the rest copy.  Token t reads row t of the table, or row rows[t] when the table holds
+// one row per position; a row index outside the table skips the token and raises the error word.
 __global__ void __launch_bounds__(256)
 rope_kernel(const float *__restrict__ x, int64_t x_nb1, int64_t x_nb2, float *y, int64_t y_nb1, int64_t y_nb2,
-            const float *__restrict__ table, int ne0, int n_head, int n_dims, int neox, int64_t total) {
+            const float *__restrict__ table, const int32_t *__restrict__ rows, int64_t n_rows, int ne0, int n_head, int n_dims,
+            int neox, int64_t total, int *err) {
     pdl_trigger();
     pdl_wait();
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
@@ -176,10 +178,15 @@ rope_kernel(const float *__restrict__ x, int64_t x_nb1, int64_t x_nb2, float *y,
     const float *src = (const float *)((const char *)x + h * x_nb1 + t * x_nb2);
     float *dst = (float *)((char *)y + h * y_nb1 + t * y_nb2);
     const int i0 = 2 * p;
+    const int64_t tr = rows ? (int64_t)rows[t] : t;
+    if (tr < 0 || tr >= n_rows) {
+        if (p == 0 && h == 0) atomicExch(err, 3);
+        return;
+    }
     if (i0 < n_dims) {
         const int ic = neox ? p : i0;
         const int off = neox ? n_dims / 2 : 1;
-        const float c = table[t * ne0 + i0], s = table[t * ne0 + i0 + 1];
+        const float c = table[tr * ne0 + i0], s = table[tr * ne0 + i0 + 1];
         const float x0 = src[ic], x1 = src[ic + off];
         dst[ic] = __fmaf_rn(x0, c, -__fmul_rn(x1, s));
         dst[ic + off] = __fmaf_rn(x0, s, __fmul_rn(x1, c));
@@ -190,7 +197,7 @@ rope_kernel(const float *__restrict__ x, int64_t x_nb1, int64_t x_nb2, float *y,
 }
 
 int launch_rope(const float *x, int64_t x_nb1, int64_t x_nb2, float *y, int64_t y_nb1, int64_t y_nb2, const float *table,
-                int64_t ne0, int64_t n_head, int64_t n_tok, int n_dims, int mode, cudaStream_t s) {
+                const int32_t *rows, int64_t n_rows, int64_t ne0, int64_t n_head, int64_t n_tok, int n_dims, int mode, cudaStream_t s) {
     B200_REQUIRE(mode == 0 || mode == 2, "rope: mode %d is neither NORMAL (0) nor NEOX (2)", mode);
     B200_REQUIRE(ne0 > 0 && ne0 % 2 == 0 && n_dims > 0 && n_dims % 2 == 0 && n_dims <= ne0, "rope: bad head size %lld / n_dims %d",
                  (long long)ne0, n_dims);
@@ -198,8 +205,11 @@ int launch_rope(const float *x, int64_t x_nb1, int64_t x_nb2, float *y, int64_t 
     if (total == 0) return B200_STATUS_SUCCESS;
     const int64_t blocks = (total + 255) / 256;
     B200_REQUIRE(blocks < 0x7fffffffLL && n_head < (1 << 30) && ne0 < (1 << 30), "rope: tensor too large for one launch");
-    return launch_pdl(rope_kernel, dim3((unsigned)blocks), dim3(256), 0, s, x, x_nb1, x_nb2, y, y_nb1, y_nb2, table, (int)ne0,
-                      (int)n_head, n_dims, mode == 2 ? 1 : 0, total);
+    int *err = nullptr;
+    int rc = device_error_word(&err);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    return launch_pdl(rope_kernel, dim3((unsigned)blocks), dim3(256), 0, s, x, x_nb1, x_nb2, y, y_nb1, y_nb2, table, rows,
+                      rows ? n_rows : n_tok, (int)ne0, (int)n_head, n_dims, mode == 2 ? 1 : 0, total, err);
 }
 
 // ---- SET_ROWS into an F16 destination ----------------------------------------------------------------
@@ -360,11 +370,14 @@ int b200_rope_table(const int32_t *pos, int64_t n_tok, int64_t ne0, const float 
     return B200_STATUS_SUCCESS;
 }
 
-int b200_rope(const float *x, int64_t x_nb1, int64_t x_nb2, float *y, int64_t y_nb1, int64_t y_nb2, const float *table, int64_t ne0,
-              int64_t n_head, int64_t n_tok, int n_dims, int mode, void *stream) {
+int b200_rope(const float *x, int64_t x_nb1, int64_t x_nb2, float *y, int64_t y_nb1, int64_t y_nb2, const float *table,
+              const int32_t *table_rows, int64_t table_n_rows, int64_t ne0, int64_t n_head, int64_t n_tok, int n_dims, int mode,
+              void *stream) {
     B200_REQUIRE(x != nullptr && y != nullptr && table != nullptr, "rope: null operand");
     B200_REQUIRE(x_nb1 % 4 == 0 && x_nb2 % 4 == 0 && y_nb1 % 4 == 0 && y_nb2 % 4 == 0, "rope: strides must be multiples of 4 bytes");
-    return launch_rope(x, x_nb1, x_nb2, y, y_nb1, y_nb2, table, ne0, n_head, n_tok, n_dims, mode, (cudaStream_t)stream);
+    B200_REQUIRE(table_rows == nullptr || table_n_rows > 0, "rope: a row index needs the table's row count");
+    return launch_rope(x, x_nb1, x_nb2, y, y_nb1, y_nb2, table, table_rows, table_n_rows, ne0, n_head, n_tok, n_dims, mode,
+                       (cudaStream_t)stream);
 }
 
 int b200_set_rows_f16(const float *x, int64_t x_stride, const int64_t *idx, void *dst, int64_t dst_stride, int64_t dst_rows,

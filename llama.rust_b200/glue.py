@@ -14,7 +14,7 @@ lib.b200_binary.argtypes = [i32, vp, i64, vp, i64, i64, i64, vp, i64, i64, i64, 
 lib.b200_silu.argtypes = [vp, i64, vp, i64, vp, i64, vp, i64, i64, i64, i32, vp]
 lib.b200_host_silu_is_wide.restype = i32
 lib.b200_rope_table.argtypes = [vp, i64, i64, vp, i32, i32, f32, f32, f32, f32, f32, f32, vp]
-lib.b200_rope.argtypes = [vp, i64, i64, vp, i64, i64, vp, i64, i64, i64, i32, i32, vp]
+lib.b200_rope.argtypes = [vp, i64, i64, vp, i64, i64, vp, vp, i64, i64, i64, i64, i32, i32, vp]
 lib.b200_set_rows_f16.argtypes = [vp, i64, vp, vp, i64, i64, i64, i64, vp]
 lib.b200_get_rows.argtypes = [i32, vp, i64, i64, vp, i64, vp, i64, vp]
 lib.b200_argmax.argtypes = [vp, i64, i64, i64, vp, vp]
@@ -82,13 +82,18 @@ def rope_table(pos, ne0, n_dims, freq_base=10000.0, freq_scale=1.0, n_ctx_orig=4
     return table
 
 
-def rope(x, pos, n_dims, mode, **kw):
-    """x: [n_tok, n_head, ne0]"""
+def rope(x, pos, n_dims, mode, by_position_rows=0, **kw):
+    """x: [n_tok, n_head, ne0].  by_position_rows > 0: one table of that many positions, indexed by pos on the device."""
     x = _f(x)
     n_tok, n_head, ne0 = x.shape
-    table = rope_table(pos, ne0, n_dims, **kw)
+    if by_position_rows:
+        table = rope_table(np.arange(by_position_rows), ne0, n_dims, **kw)
+        rows = device_array(np.ascontiguousarray(pos, dtype=np.int32))
+    else:
+        table, rows = rope_table(pos, ne0, n_dims, **kw), None
     dx, dt, dy = device_array(x), device_array(table), DeviceBuffer(x.nbytes)
-    check(lib.b200_rope(dx.ptr, ne0 * 4, n_head * ne0 * 4, dy.ptr, ne0 * 4, n_head * ne0 * 4, dt.ptr, ne0, n_head, n_tok, n_dims, mode, None))
+    check(lib.b200_rope(dx.ptr, ne0 * 4, n_head * ne0 * 4, dy.ptr, ne0 * 4, n_head * ne0 * 4, dt.ptr, rows.ptr if rows else None,
+                        by_position_rows, ne0, n_head, n_tok, n_dims, mode, None))
     return dy.download(np.float32, x.size).reshape(x.shape)
 
 

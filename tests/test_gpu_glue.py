@@ -106,6 +106,19 @@ def test_rope_decoder_sizes(g, mode, ne0, n_dims, heads, toks, base):
     assert bits_equal(g.rope(x, pos, n_dims, mode, **kw), orc_glue.rope(x, pos, n_dims, mode, **kw))
 
 
+def test_rope_table_indexed_by_device_positions(g):
+    m = b200.load()
+    rng = np.random.default_rng(21)
+    x = activations(rng, (9, 4, 128))
+    pos = [0, 1, 2, 511, 3, 100, 4095, 7, 7]
+    kw = dict(freq_base=500000.0, n_ctx_orig=8192)
+    got = g.rope(x, pos, 128, 0, by_position_rows=4096, **kw)
+    assert bits_equal(got, orc_glue.rope(x, pos, 128, 0, **kw))
+    assert m.kernel_error() == 0
+    g.rope(x, [0, 1, 2, 4096, 3, 100, 4095, 7, 7], 128, 0, by_position_rows=4096, **kw)
+    assert m.kernel_error() == 3   # position 4096 is outside a 4096-row table: skipped and reported
+
+
 def test_rope_table_matches_oracle_with_yarn_and_factors(g):
     kw = dict(freq_base=500000.0, freq_scale=0.25, n_ctx_orig=8192, ext_factor=1.0, attn_factor=1.2, beta_fast=32.0, beta_slow=1.0)
     t = g.rope_table([0, 1, 77, 100000], 128, 128, **kw)
