@@ -370,6 +370,17 @@ static bool gemv_stream_enabled() {
     return v == 1;
 }
 
+// B200_GEMM_MMA=0 keeps prompt batches on the column-pass kernels (for side-by-side measurements)
+constexpr int64_t GEMM_MMA_MIN_COLS = 8;
+static bool gemm_mma_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_GEMM_MMA");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
 static int64_t gemv_stream_max_tiles() {
     static int64_t v = -1;
     if (v < 0) {
@@ -395,7 +406,14 @@ int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint
         // tail rows the plain way (gemv chain), exactly as crates/ggml/src/compute.rs:5322-5447 does.
         const int64_t m4 = route == B200_ROUTE_REPACK ? m - m % 4 : m;
         const int maxc_main = route == B200_ROUTE_REPACK ? 2 : 3;
-        for (int64_t c0 = 0; c0 < m;) {
+        int64_t c_start = 0;
+        if (m4 >= GEMM_MMA_MIN_COLS && gemm_mma_enabled()) {
+            // enough activation rows to fill tensor-core patches: same chains, integer dots by mma
+            int rc = launch_gemm_mma(route == B200_ROUTE_REPACK ? 1 : 2, n, k, m4, tiles, acts, dst, lddst, s);
+            if (rc != B200_STATUS_SUCCESS) return rc;
+            c_start = m4;
+        }
+        for (int64_t c0 = c_start; c0 < m;) {
             const bool main_part = c0 < m4;
             const int64_t end = main_part ? m4 : m;
             const int maxc = main_part ? maxc_main : 3;
@@ -422,6 +440,8 @@ int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint
         }
         return B200_STATUS_SUCCESS;
     }
+    if (type == B200_TYPE_Q6_K && route == B200_ROUTE_TILED && m >= GEMM_MMA_MIN_COLS && gemm_mma_enabled())
+        return launch_gemm_mma(6, n, k, m, tiles, acts, dst, lddst, s);
     if (type == B200_TYPE_Q6_K && route == B200_ROUTE_TILED) return run_generic<TraitsQ6KTiled, 2>(n, k, m, tiles, acts, dst, lddst, s);
     if (type == B200_TYPE_Q4_K && route == B200_ROUTE_ROWDOT) return run_generic<TraitsQ4KRowDot, 1>(n, k, m, tiles, acts, dst, lddst, s);
     if (type == B200_TYPE_Q6_K && route == B200_ROUTE_ROWDOT) return run_generic<TraitsQ6K, 1>(n, k, m, tiles, acts, dst, lddst, s);
