@@ -1,17 +1,24 @@
 #!/usr/bin/env python3
-"""Benchmark of the hot path: Q4_K decode mat-mul (MUL_MAT with one activation row) over
-the four weight shapes of the quantized sweep, reported as HBM GB/s.
+"""Benchmark of the hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-llama]
 
-One step = one pass over the four shapes (4096x4096, 14336x4096, 4096x14336,
-128256x4096; 371 MB of Q4_K weights, more than L2, so no flush is needed between
-steps).  `value` has the activations resident in HBM; `e2e` goes through the
-host-buffer entry point (pinned host activations in, results out, every step).
-`--impl reference` times the CPU restatement of the reference's route on the host
-cores.  One JSON line is printed by rank 0.
+The JSON line's headline (`metric`, `value`, `roofline`, `e2e`) is the Q4_K decode mat-mul (MUL_MAT with
+one activation row) over the four weight shapes of the quantized sweep, in HBM GB/s: one step = one pass
+over 4096x4096, 14336x4096, 4096x14336 and 128256x4096 (371 MB of Q4_K weights, more than L2, so no
+flush is needed between steps).  `value` has the activations resident in HBM; `e2e` goes through the
+host-buffer entry point (host activations in, results out, every step).
+
+The second half of the metric rides in the same line under `llama_8b`: a Llama-3-8B-shaped decoder with
+synthetic Q4_K_M weights run by the decode driver (include/llama_b200.h) — a 512-token prompt (pp512)
+and 128 greedy steps after it (tg128), in tokens/s, end to end through the driver's host-buffer call
+(token ids in, argmax out, every step) and device-only (the step's graph replayed on the stream).
+
+`--impl reference` times the CPU restatement of the reference's routes on the host cores for the same
+workloads.  One JSON line is printed by rank 0.  `--case` runs one small case for a profiler.
 """
 import argparse
+import importlib
 import importlib.util
 import json
 import os
@@ -23,12 +30,11 @@ import time
 import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 Q4_K = 12
 SHAPES = [(4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096)]  # (n rows, k)
-DISTINCT_ROWS = 4096  # rows quantized for real; larger matrices repeat them (timing does not depend on values)
 METRIC = "q4_K_decode_mat_mul_hbm_gbs"
+PROMPT, GEN = 512, 128
 
 
 def algorithmic_bytes(n, k, m=1):
@@ -37,22 +43,26 @@ def algorithmic_bytes(n, k, m=1):
 
 
 def load_pkg():
-    spec = importlib.util.spec_from_file_location("llama_rust_b200", os.path.join(ROOT, "llama.rust_b200", "__init__.py"))
-    mod = importlib.util.module_from_spec(spec)
-    sys.modules["llama_rust_b200"] = mod
-    spec.loader.exec_module(mod)
-    return mod
+    if "llama_rust_b200" not in sys.modules:
+        spec = importlib.util.spec_from_file_location("llama_rust_b200", os.path.join(ROOT, "llama.rust_b200", "__init__.py"))
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules["llama_rust_b200"] = mod
+        spec.loader.exec_module(mod)
+    return sys.modules["llama_rust_b200"]
 
 
 def synth_weights(n, k, seed):
-    import orc  # the oracle's restatement of quantize_row_q4_K_ref makes the synthetic weights
-    rng = np.random.default_rng(seed)
-    rows = min(n, DISTINCT_ROWS)
-    w = (rng.standard_normal((rows, k)) * 0.02).astype(np.float32)
-    q = orc.quantize_rows(Q4_K, w)
-    if rows < n:
-        q = np.tile(q, ((n + rows - 1) // rows, 1))[:n]
-    return np.ascontiguousarray(q)
+    """random well-formed Q4_K blocks (llama.rust_b200/synth.py); timing does not depend on the values"""
+    load_pkg()
+    return importlib.import_module("llama_rust_b200.synth").blocks(Q4_K, n, k, seed=seed)
+
+
+def load_oracle():
+    """the CPU restatement under oracle/, for the reference arm and the cpu_baseline legs only"""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import orc
+    import orc_glue
+    return orc, orc_glue
 
 
 class ClockSampler:
@@ -127,15 +137,23 @@ def dist_setup(n_gpus):
     return rank, world, barrier, reduce_max
 
 
-def cpu_step(orc, reps_w, x_list, outs, threads):
-    for (ty, n, k, wrep), x, out in zip(reps_w, x_list, outs):
-        r = orc.lib().orc_mul_mat_repacked(ty, n, k, 1, wrep.ctypes.data, x.ctypes.data, out.ctypes.data, threads)
-        assert r > 0
+def peak_hbm():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
 
 
-def cpu_prepare(orc):
-    """weights in the CPU path's 8x8 interleaved layout, built before timing as the
-    reference's warm_repack does"""
+# ---- the decode mat-mul ---------------------------------------------------------------------------------
+def gemv_config():
+    return {"workload": "MUL_MAT Q4_K x f32, 1 activation row, shapes (n x k) " + ", ".join(f"{n}x{k}" for n, k in SHAPES),
+            "weights": "seeded random well-formed Q4_K blocks (decoded spread ~0.05)", "activations": "N(0,1), seeded",
+            "l2": "371 MB of weights per step exceed the 126 MB L2; no flush between steps",
+            "parallelism": "replicas"}
+
+
+def cpu_gemv_prepare(orc):
+    """weights in the CPU path's 8x8 interleaved layout, built before timing as the reference's warm_repack does"""
     reps, xs, outs = [], [], []
     for i, (n, k) in enumerate(SHAPES):
         W = synth_weights(n, k, seed=100 + i)
@@ -145,48 +163,27 @@ def cpu_prepare(orc):
     return reps, xs, outs
 
 
-def run_reference(args, rank, world):
-    """The CPU route the reference takes for this workload (8x8 interleaved Q4_K gemv on Q8_K
-    activations), restated in C++ because the Rust reference cannot be built here."""
-    if rank != 0:
-        return
-    import orc
+def cpu_gemv_step(orc, reps_w, x_list, outs, threads):
+    for (ty, n, k, wrep), x, out in zip(reps_w, x_list, outs):
+        r = orc.lib().orc_mul_mat_repacked(ty, n, k, 1, wrep.ctypes.data, x.ctypes.data, out.ctypes.data, threads)
+        assert r > 0
+
+
+def cpu_gemv_baseline(orc, seconds=10.0):
     threads = orc.lib().orc_num_threads()
-    reps, xs, outs = cpu_prepare(orc)
     total = sum(algorithmic_bytes(n, k) for n, k in SHAPES)
-    for _ in range(args.warmup):
-        cpu_step(orc, reps, xs, outs, threads)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        cpu_step(orc, reps, xs, outs, threads)
+    reps_w, xs, outs = cpu_gemv_prepare(orc)
+    cpu_gemv_step(orc, reps_w, xs, outs, threads)
+    n_rep, t0 = 0, time.perf_counter()
+    while n_rep < 3 or (time.perf_counter() - t0 < seconds and n_rep < 50):
+        cpu_gemv_step(orc, reps_w, xs, outs, threads)
+        n_rep += 1
     dt = time.perf_counter() - t0
-    gbs = total * args.steps / dt / 1e9
-    line = {
-        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "int8xint4 dot, f32 accumulate", "data": "synthetic",
-        "config": workload_config(),
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
-                         "sample": f"the full step (4 shapes, {total} algorithmic bytes) x {args.steps}"},
-        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }
-    print(json.dumps(line), flush=True)
+    return {"value": total * n_rep / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"the full step x {n_rep} repetitions ({dt:.1f} s)"}
 
 
-def workload_config():
-    return {"workload": "MUL_MAT Q4_K x f32, 1 activation row, shapes (n x k) " +
-                        ", ".join(f"{n}x{k}" for n, k in SHAPES),
-            "weights": "N(0,0.02) through quantize_row_q4_K_ref, seeded", "activations": "N(0,1), seeded",
-            "l2": "371 MB of weights per step exceed the 126 MB L2; no flush between steps",
-            "parallelism": "replicas"}
-
-
-def run_b200(args, rank, world, barrier, reduce_max):
-    b = load_pkg()
-    if b.device_count() == 0:
-        raise SystemExit("bench.py: no CUDA device; the CUDA library is the only compute path")
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    b.set_device(local)
+def run_gemv(b, args, rank, world, barrier, reduce_max, local):
     weights, dxs, douts, acts, hxs, houts = [], [], [], [], [], []
     for i, (n, k) in enumerate(SHAPES):
         weights.append(b.Weight(Q4_K, synth_weights(n, k, seed=100 + i), k))
@@ -204,11 +201,10 @@ def run_b200(args, rank, world, barrier, reduce_max):
 
     def step_host():
         for w, hx, ho in zip(weights, hxs, houts):
-            b.check(b.lib.b200_mul_mat_host(w.ty, w.n_rows, w.k, 1, w.ptr, hx.ctypes.data, ho.ctypes.data, 0, None),
-                    "mul_mat_host")
+            b.check(b.lib.b200_mul_mat_host(w.ty, w.n_rows, w.k, 1, w.ptr, hx.ctypes.data, ho.ctypes.data, 0, None), "mul_mat_host")
 
-    # ---- device-resident throughput -------------------------------------------------
-    for _ in range(max(args.warmup, 3)):
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
         step_device()
     b.synchronize()
     barrier()
@@ -225,10 +221,8 @@ def run_b200(args, rank, world, barrier, reduce_max):
     barrier()
     ms = reduce_max(ms)
 
-    # ---- the mat-mul kernel alone (activations already quantized): roofline ---------
-    # Per shape: back-to-back launches rotating over enough weight copies to exceed twice the L2, one
-    # pair of CUDA events around the batch (the stream is what a decode step looks like: launches queue
-    # behind each other and each kernel's weight prefetch overlaps the tail of the one before).
+    # the mat-mul kernel alone (activations already quantized), per shape: back-to-back launches rotating over
+    # enough weight copies to exceed twice the L2, one pair of CUDA events around the batch
     kern_ms, per_shape = [], {}
     launches = max(4 * args.steps, 100)
     for (n, k), w0, dx, do, act in zip(SHAPES, weights, dxs, douts, acts):
@@ -256,7 +250,6 @@ def run_b200(args, rank, world, barrier, reduce_max):
         del ws
     clocks = sampler.stop() if rank == 0 else None
 
-    # ---- end to end through the host-buffer entry point -------------------------------
     for _ in range(3):
         step_host()
     barrier()
@@ -265,50 +258,213 @@ def run_b200(args, rank, world, barrier, reduce_max):
         step_host()
     b.synchronize()
     e2e_s = reduce_max(time.perf_counter() - t0)
-
-    if rank != 0:
-        return
-    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(peaks_path):
-        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
-    else:
-        peak, peak_src = 6650.0, "fallback"
+    peak, peak_src = peak_hbm()
     kern_gbs = total / (sum(kern_ms) * 1e-3) / 1e9
-    value = world * total * args.steps / (ms * 1e-3) / 1e9
-    line = {
-        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8xint4 dot, f32 accumulate", "data": "synthetic", "config": workload_config(),
-        "clocks": clocks,
+    return {
+        "value": world * total * args.steps / (ms * 1e-3) / 1e9, "ms_per_step": ms / args.steps, "clocks": clocks, "warmup": warm,
         "e2e": {"value": world * total * args.steps / e2e_s / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": sum(4 * k for _, k in SHAPES), "d2h_bytes_per_step": sum(4 * n for n, _ in SHAPES)},
         "gpu_launches": args.steps * 2 * len(SHAPES),
         "roofline": {"bound": "hbm", "kernel": "gemv_q4_K_kernel<1,0> / gemv_q4_K_stream_kernel (Q4_K decode mat-mul)",
-                     "achieved": kern_gbs, "peak": peak,
-                     "peak_source": peak_src, "unit": "GB/s", "frac": kern_gbs / peak, "traffic": None,
-                     "per_shape": per_shape},
+                     "achieved": kern_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": kern_gbs / peak,
+                     "traffic": None, "per_shape": per_shape},
     }
-    # CPU baseline on the host cores: the same workload through the CPU route, a few repetitions
+
+
+# ---- the Llama-3-8B-shaped decoder ------------------------------------------------------------------------
+def llama_hparams(n_layer):
+    ll = importlib.import_module("llama_rust_b200.llama")
+    hp = dict(ll.LLAMA3_8B)
+    hp["n_layer"] = n_layer
+    return ll, hp
+
+
+def llama_weight_bytes(ll, hp):
+    """bytes of quantized weights one decode step streams: every matrix once, one row of token_embd"""
+    syn = importlib.import_module("llama_rust_b200.synth")
+    total = 0
+    for name, (ne0, ne1) in ll.tensor_shapes(hp).items():
+        ty = ll.q4_k_m_type(name, hp["n_layer"])
+        if ty == 0:
+            total += 4 * ne0
+        else:
+            per, size = syn.BLOCK[ty]
+            total += (1 if name == "token_embd.weight" else ne1) * (ne0 // per) * size
+    return total
+
+
+def build_llama(n_layer, n_ctx=1024, n_batch=PROMPT, keep_host=False):
+    ll, hp = llama_hparams(n_layer)
+    syn = importlib.import_module("llama_rust_b200.synth")
+    gpu = ll.Llama(hp, n_ctx, n_batch, cpu_threads=8)
+    host = {}
+    for name, ty, arr, ne0, ne1 in syn.llama_tensors(hp, lambda n: ll.q4_k_m_type(n, n_layer)):
+        gpu.set_tensor(name, ty, arr, ne0, ne1)
+        if keep_host:
+            host[name] = (ty, arr, ne0, ne1)
+    return ll, hp, gpu, host
+
+
+def run_llama(b, args, rank, world, barrier, reduce_max):
+    """pp512 + tg128, batch 1, one replica per rank"""
+    ll, hp, gpu, _ = build_llama(args.layers)
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, hp["n_vocab"], PROMPT).astype(np.int32)
+    pos = np.arange(PROMPT, dtype=np.int32)
+    launches = 0
+
+    def one_pass():
+        gpu.kv_clear()
+        t0 = time.perf_counter()
+        tok = gpu.decode(prompt, pos, logits=False, argmax=True)
+        t1 = time.perf_counter()
+        pp_dev = gpu.replay(1)
+        toks = []
+        t2 = time.perf_counter()
+        for i in range(GEN):
+            tok = gpu.decode([tok], [PROMPT + i], logits=False, argmax=True)
+            toks.append(tok)
+        t3 = time.perf_counter()
+        tg_dev = gpu.replay(GEN) / GEN
+        return t1 - t0, pp_dev * 1e-3, (t3 - t2) / GEN, tg_dev * 1e-3, toks
+
+    for _ in range(3):   # warm-up passes: allocations, graph capture
+        one_pass()
+    barrier()
+    res = [one_pass() for _ in range(3)]
+    barrier()
+    pp_e2e = reduce_max(statistics.median(r[0] for r in res))
+    pp_dev = reduce_max(statistics.median(r[1] for r in res))
+    tg_e2e = reduce_max(statistics.median(r[2] for r in res))
+    tg_dev = reduce_max(statistics.median(r[3] for r in res))
+    peak, peak_src = peak_hbm()
+    wbytes = llama_weight_bytes(ll, hp)
+    out = {
+        "config": {"workload": f"Llama-3-8B shape ({hp['n_layer']} layers, d_model 4096, 32/8 heads, FFN 14336, vocab 128256), "
+                               "Q4_K_M tensor types, F16 KV cache, batch 1: 512-token prompt then 128 greedy steps",
+                   "weights": "seeded random well-formed blocks", "tokens": "uniform random prompt ids, seeded"},
+        "pp512_tok_s": world * PROMPT / pp_dev, "pp512_e2e_tok_s": world * PROMPT / pp_e2e,
+        "tg128_tok_s": world / tg_dev, "tg128_e2e_tok_s": world / tg_e2e,
+        "pp512_ms": pp_dev * 1e3, "tg128_ms_per_token": tg_dev * 1e3,
+        "e2e_bytes_per_step": {"h2d": "token ids, positions, F16 mask, cache row indices", "d2h": "4 (argmax)"},
+        "roofline": {"bound": "hbm", "what": "tg128: quantized weight bytes one step streams / device time of the step",
+                     "bytes_per_token": wbytes, "achieved": wbytes / tg_dev / 1e9, "peak": peak, "peak_source": peak_src,
+                     "unit": "GB/s", "frac": wbytes / tg_dev / 1e9 / peak},
+        "greedy_tokens_head": [int(t) for t in res[-1][4][:8]],
+    }
+    gpu.close()
+    return out
+
+
+def cpu_llama_baseline(orc, orc_glue, n_layer, prompt_tokens=16, gen_tokens=4):
+    """The CPU restatement's Llama forward on the same shape: a prompt batch and a few single-token steps.
+    Weights are interleaved once, outside the timed region, as the reference does at load."""
+    load_pkg()
+    ll, hp = llama_hparams(n_layer)
+    syn = importlib.import_module("llama_rust_b200.synth")
+    tensors = {name: (ty, arr) for name, ty, arr, _, _ in syn.llama_tensors(hp, lambda n: ll.q4_k_m_type(n, n_layer))}
+    ohp = dict(n_vocab=hp["n_vocab"], n_embd=hp["n_embd"], n_head=hp["n_head"], n_head_kv=hp["n_head_kv"],
+               head_dim=hp["n_embd_head"], n_ff=hp["n_ff"], n_layer=n_layer, rope_mode=0, n_ctx_orig=hp["n_ctx_train"],
+               norm_eps=hp["norm_rms_eps"], freq_base=hp["rope_freq_base"], freq_scale=1.0)
+    threads = orc.lib().orc_num_threads()
+    cpu = orc_glue.Llama(ohp, tensors, 256)
+    rng = np.random.default_rng(0)
+
+    def fwd(toks, p0):
+        n = len(toks)
+        mask = np.full((n, 256), 0xFC00, dtype=np.uint16)
+        for i in range(n):
+            mask[i, :p0 + i + 1] = 0
+        return cpu.forward(toks, np.arange(p0, p0 + n), 256, mask, np.arange(p0, p0 + n), [n - 1], n_threads=threads,
+                           keep_repacked=True)
+
+    prompt = rng.integers(0, hp["n_vocab"], prompt_tokens).astype(np.int32)
+    fwd(prompt[:4], 0)            # interleaves every weight (untimed), like the reference's load
+    fwd(prompt[:1], 4)
+    t0 = time.perf_counter()
+    fwd(prompt, 0)
+    t1 = time.perf_counter()
+    for i in range(gen_tokens):
+        fwd(prompt[:1], prompt_tokens + i)
+    t2 = time.perf_counter()
+    orc_glue.L().orc_llama_drop_repacked()
+    return {"pp_tok_s": prompt_tokens / (t1 - t0), "tg_tok_s": gen_tokens / (t2 - t1), "unit": "tok/s", "cores": threads, "kind": "port",
+            "sample": f"{n_layer}-layer model of the same shape, one {prompt_tokens}-token prompt batch ({t1 - t0:.1f} s) and "
+                      f"{gen_tokens} single-token steps ({t2 - t1:.1f} s) at positions {prompt_tokens}.."}
+
+
+# ---- arms -------------------------------------------------------------------------------------------------
+def run_reference(args, rank, world):
+    """The CPU routes the reference takes for these workloads, restated in C++ because the Rust reference
+    cannot be built here; all host threads."""
+    if rank != 0:
+        return
+    orc, orc_glue = load_oracle()
+    threads = orc.lib().orc_num_threads()
+    reps, xs, outs = cpu_gemv_prepare(orc)
+    total = sum(algorithmic_bytes(n, k) for n, k in SHAPES)
+    for _ in range(args.warmup):
+        cpu_gemv_step(orc, reps, xs, outs, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_gemv_step(orc, reps, xs, outs, threads)
+    dt = time.perf_counter() - t0
+    gbs = total * args.steps / dt / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8xint4 dot, f32 accumulate", "data": "synthetic", "config": gemv_config(),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"the full step (4 shapes, {total} algorithmic bytes) x {args.steps}"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    if not args.no_llama:
+        del reps, xs, outs
+        try:
+            line["llama_8b"] = cpu_llama_baseline(orc, orc_glue, args.cpu_layers)
+        except Exception as exc:
+            line["llama_8b"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
+    print(json.dumps(line), flush=True)
+
+
+def run_b200(args, rank, world, barrier, reduce_max):
+    b = load_pkg()
+    if b.device_count() == 0:
+        raise SystemExit("bench.py: no CUDA device; the CUDA library is the only compute path")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    b.set_device(local)
+    g = run_gemv(b, args, rank, world, barrier, reduce_max, local)
+    llama = None
+    if not args.no_llama:
+        llama = run_llama(b, args, rank, world, barrier, reduce_max)
+    if rank != 0:
+        return
+    line = {
+        "metric": METRIC, "value": g["value"], "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": g["warmup"],
+        "ms_per_step": g["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8xint4 dot, f32 accumulate", "data": "synthetic", "config": gemv_config(), "clocks": g["clocks"],
+        "e2e": g["e2e"], "gpu_launches": g["gpu_launches"], "roofline": g["roofline"],
+    }
+    if llama is not None:
+        line["llama_8b"] = llama
+    # CPU baselines on the host cores: the same workloads through the CPU routes, bounded samples
     try:
-        import orc
-        threads = orc.lib().orc_num_threads()
-        reps_w, xs, outs = cpu_prepare(orc)
-        cpu_step(orc, reps_w, xs, outs, threads)
-        n_rep, t0 = 0, time.perf_counter()
-        while n_rep < 3 or (time.perf_counter() - t0 < 10.0 and n_rep < 50):
-            cpu_step(orc, reps_w, xs, outs, threads)
-            n_rep += 1
-        dt = time.perf_counter() - t0
-        line["cpu_baseline"] = {"value": total * n_rep / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
-                                "sample": f"the full step x {n_rep} repetitions ({dt:.1f} s)"}
+        orc, orc_glue = load_oracle()
+        line["cpu_baseline"] = cpu_gemv_baseline(orc)
+        if llama is not None:
+            try:
+                llama["cpu_baseline"] = cpu_llama_baseline(orc, orc_glue, args.cpu_layers)
+            except Exception as exc:
+                llama["cpu_baseline"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
     except Exception as exc:  # the baseline is a reported extra, never the measured path
         line["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": f"failed: {exc}"}
     print(json.dumps(line), flush=True)
 
 
-def run_profile_case(args):
-    """A small case for ncu: `--only NxK --launches R` runs R decode mat-muls of one shape,
-    rotating over enough weight copies to stay out of L2, and prints the event-timed mean."""
+# ---- small cases for a profiler --------------------------------------------------------------------------
+def case_gemv(args):
+    """`--case gemv --only NxK --launches R`: R decode mat-muls of one shape, rotating over enough weight
+    copies to stay out of L2; prints the event-timed mean."""
     b = load_pkg()
     b.set_device(0)
     n, k = (int(v) for v in args.only.lower().split("x"))
@@ -335,22 +491,52 @@ def run_profile_case(args):
     e1.record()
     e1.synchronize()
     us = e0.elapsed_ms(e1) * 1e3 / args.launches
-    print(json.dumps({"case": args.only, "copies": copies, "launches": args.launches, "us_per_launch": us,
+    print(json.dumps({"case": f"gemv {args.only}", "copies": copies, "launches": args.launches, "us_per_launch": us,
                       "gbs": algorithmic_bytes(n, k) / us / 1e3}), flush=True)
+
+
+def case_llama(args):
+    """`--case llama_tg|llama_pp --layers L [--launches R]`: an L-layer model of the 8B shape; one prompt
+    batch (llama_pp) or R single-token steps after a 16-token prompt (llama_tg), eager launches (no CUDA
+    graph) so that a profiler sees every kernel."""
+    os.environ["B200_CUDA_GRAPHS"] = "0"
+    b = load_pkg()
+    b.set_device(0)
+    ll, hp, gpu, _ = build_llama(args.layers)
+    rng = np.random.default_rng(0)
+    if args.case == "llama_pp":
+        prompt = rng.integers(0, hp["n_vocab"], PROMPT).astype(np.int32)
+        t0 = time.perf_counter()
+        gpu.decode(prompt, np.arange(PROMPT), logits=False, argmax=True)
+        print(json.dumps({"case": "llama_pp", "layers": args.layers, "ms": (time.perf_counter() - t0) * 1e3,
+                          "replay_ms": gpu.replay(1)}), flush=True)
+    else:
+        tok = gpu.decode(rng.integers(0, hp["n_vocab"], 16).astype(np.int32), np.arange(16), logits=False, argmax=True)
+        t0 = time.perf_counter()
+        for i in range(args.launches):
+            tok = gpu.decode([tok], [16 + i], logits=False, argmax=True)
+        print(json.dumps({"case": "llama_tg", "layers": args.layers, "steps": args.launches,
+                          "ms_per_token": (time.perf_counter() - t0) * 1e3 / args.launches}), flush=True)
+    gpu.close()
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default=None, help="profile case: one shape NxK, see --launches")
+    ap.add_argument("--case", default=None, choices=["gemv", "llama_tg", "llama_pp"], help="one small case for a profiler")
+    ap.add_argument("--only", default="4096x4096", help="--case gemv: the shape NxK")
     ap.add_argument("--launches", type=int, default=64)
+    ap.add_argument("--layers", type=int, default=32, help="layers of the 8B-shaped model (32 = the full model)")
+    ap.add_argument("--cpu-layers", type=int, default=32, help="layers of the model the CPU baseline times")
+    ap.add_argument("--no-llama", action="store_true", help="skip the Llama half of the metric")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     args = ap.parse_args()
-    if args.only:
-        run_profile_case(args)
-        return
+    if args.case == "gemv":
+        return case_gemv(args)
+    if args.case:
+        return case_llama(args)
     rank, world, barrier, reduce_max = dist_setup(args.gpus)
     if args.impl == "reference":
         run_reference(args, rank, world)

@@ -116,5 +116,6 @@ int orc_flash_attn_ext(const OrcFlashArgs *a);
 int orc_mul_mat_repacked(int type, int64_t N, int64_t K, int64_t M, const void *Wrep, const float *X,
                          float *out, int n_threads);
 int orc_num_threads();
+int orc_pick_route(int type, int64_t N, int64_t M);   // the route orc_mul_mat takes with ORC_ROUTE_AUTO
 
 }  // extern "C"

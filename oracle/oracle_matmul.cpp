@@ -447,6 +447,8 @@ static int pick_route(int type, int64_t N, int64_t M) {
     }
 }
 
+extern "C" int orc_pick_route(int type, int64_t N, int64_t M) { return pick_route(type, N, M); }
+
 static inline bool is_kquant(int type) { return type == ORC_Q4_K || type == ORC_Q6_K; }
 
 // Quantize M activation rows the plain way for `type` (A2 for K-quants, A1 else).

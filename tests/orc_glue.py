@@ -25,7 +25,7 @@ def L():
         lib.orc_get_rows.argtypes = [i32, vp, i64, i64, vp, i64, vp]
         lib.orc_argmax.argtypes = [vp, i64]
         lib.orc_argmax.restype = i32
-        lib.orc_llama_forward.argtypes = [vp, vp, vp, i64, i64, vp, vp, vp, i64, vp, i32, i32]
+        lib.orc_llama_forward.argtypes = [vp, vp, vp, i64, i64, vp, vp, vp, i64, vp, i32, i32, i32]
         _ready = True
     return lib
 
@@ -163,7 +163,7 @@ class Llama:
         m.kv_size = kv_size
         self.m = m
 
-    def forward(self, tokens, pos, n_kv, mask, row_idx, out_ids, n_threads=8, wide_silu=True):
+    def forward(self, tokens, pos, n_kv, mask, row_idx, out_ids, n_threads=8, wide_silu=True, keep_repacked=False):
         tokens = np.ascontiguousarray(tokens, dtype=np.int32)
         pos = np.ascontiguousarray(pos, dtype=np.int32)
         mask = np.ascontiguousarray(mask, dtype=np.uint16)
@@ -172,6 +172,6 @@ class Llama:
         logits = np.empty((out_ids.size, self.hp["n_vocab"]), dtype=np.float32)
         rc = L().orc_llama_forward(C.byref(self.m), tokens.ctypes.data, pos.ctypes.data, tokens.size, n_kv, mask.ctypes.data,
                                    row_idx.ctypes.data, out_ids.ctypes.data, out_ids.size, logits.ctypes.data, n_threads,
-                                   int(wide_silu))
+                                   int(wide_silu), int(keep_repacked))
         assert rc == 0, f"orc_llama_forward failed ({rc})"
         return logits
