@@ -127,6 +127,11 @@ int b200_mul_mat(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, c
  * b200_quantize_activations_device (act_kind must be the kind the route reads) */
 int b200_mul_mat_q8(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, const void *dev_act,
                     int act_kind, float *dev_dst, int64_t lddst, int route, void *stream);
+/* b200_mul_mat_q8 for one activation row that also writes dev_sum[i] = dst[i] + dev_addend[i] (one rounded
+ * f32 add per element): the residual ADD that follows attn_output and ffn_down in a decoder layer
+ * (crates/llama/src/graph_arch.rs:209,226; crates/ggml/src/compute.rs:1174) without a second kernel. */
+int b200_mul_mat_q8_add(int type, int64_t n, int64_t k, const void *dev_w, const void *dev_act, int act_kind, float *dev_dst,
+                        const float *dev_addend, float *dev_sum, int route, void *stream);
 /* same op with host activations / results: copies X in, runs, copies dst out */
 int b200_mul_mat_host(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, const float *host_x,
                       float *host_dst, int route, void *stream);
@@ -193,6 +198,16 @@ int b200_flash_attn_ext(const struct b200_flash_attn_args *args, void *stream);
  * every decoder (crates/llama/src/graph_arch.rs:1119-1122). */
 int b200_rms_norm(const float *x, int64_t x_stride, float *y, int64_t y_stride, const float *weight, float *y_weighted,
                   int64_t y_weighted_stride, int64_t ne0, int64_t nrows, float eps, void *stream);
+
+/* b200_rms_norm / b200_silu (below) that also leave the Q8_K quantization of their last result (the
+ * weighted norm, the gated product) in dev_act for the mat-muls that read it — the CPU engine quantizes
+ * that tensor at the head of each MUL_MAT (crates/ggml/src/compute.rs:1466-1500); here the producer does it
+ * once.  dev_act: b200_act_scratch_nbytes(nrows, ne0) bytes, 256-byte aligned; act_kind: one of the Q8_K
+ * kinds of enum b200_act_quant (what b200_mul_mat_q8 will be given); ne0 a multiple of 256. */
+int b200_rms_norm_q8(const float *x, int64_t x_stride, float *y, int64_t y_stride, const float *weight, float *y_weighted,
+                     int64_t y_weighted_stride, int64_t ne0, int64_t nrows, float eps, void *dev_act, int act_kind, void *stream);
+int b200_silu_q8(const float *x, int64_t x_stride, const float *gate, int64_t gate_stride, float *y, int64_t y_stride, float *y_gated,
+                 int64_t y_gated_stride, int64_t ne0, int64_t nrows, int wide, void *dev_act, int act_kind, void *stream);
 
 /* ADD (op 0) / MUL (op 1) of F32 tensors with ggml's row broadcast, crates/ggml/src/compute.rs:1174-1330:
  * y[r][i] = a[r][i] op b[r % b_rows][i % b_ne0]. */

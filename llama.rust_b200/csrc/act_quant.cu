@@ -6,6 +6,7 @@
 //      4-row interleaved storage is a CPU detail, the device keeps plain rows)
 // Every float op is an explicit round-to-nearest intrinsic: no FMA contraction.
 #include "common.cuh"
+#include "act_quant.cuh"
 
 namespace b200 {
 
@@ -34,62 +35,14 @@ ActBuf act_carve(void *scratch, int64_t m, int64_t k) {
     return a;
 }
 
-// A2 / A3: one CTA of 256 threads per (256-element block, row).
+// A2 / A3: one CTA of 256 threads per (256-element block, row); the block's arithmetic is q8_K_block_store
+// (act_quant.cuh), shared with the kernels that quantize what they have just computed.
 template <bool A3>
 __global__ void __launch_bounds__(256) quantize_q8_K_kernel(const float *__restrict__ x, int64_t ldx, ActBuf out) {
     pdl_trigger();
     pdl_wait();   // x comes from the previous kernel; the scratch written here may still be read by it
-    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int64_t blk = blockIdx.x, row = blockIdx.y;
-    const int64_t nb = out.k / 256;
-    const float v = x[row * ldx + blk * 256 + t];
-    __shared__ float s_a[8];
-    __shared__ int s_i[8];
-    __shared__ float s_x[256];
-    s_x[t] = v;
-    // largest |v|, first index on ties (the CPU scans with a strict '>')
-    float a = fabsf(v);
-    int idx = t;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        float a2 = __shfl_xor_sync(0xffffffffu, a, o);
-        int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (a2 > a || (a2 == a && i2 < idx)) { a = a2; idx = i2; }
-    }
-    if (lane == 0) { s_a[warp] = a; s_i[warp] = idx; }
-    __syncthreads();
-    a = s_a[0];
-    idx = s_i[0];
-#pragma unroll
-    for (int w = 1; w < 8; w++) {
-        float a2 = s_a[w];
-        if (a2 > a) { a = a2; idx = s_i[w]; }  // later warps have larger indices: strict '>' keeps the first
-    }
-    const float amax = a;
-    const float maxv = s_x[idx];
-    int q = 0;
-    float d = 0.0f;
-    if (amax != 0.0f) {
-        if (A3) {
-            const float iscale = __fdiv_rn(127.0f, amax);
-            q = __float2int_rn(__fmul_rn(iscale, v));  // round to nearest even
-            q = max(-128, min(127, q));
-            d = __fdiv_rn(1.0f, iscale);
-        } else {
-            const float iscale = __fdiv_rn(-127.0f, maxv);
-            // nearest_int(): crates/ggml/src/quants.rs:13-18
-            const float val = __fadd_rn(__fmul_rn(iscale, v), 12582912.0f);
-            q = (__float_as_int(val) & 0x007fffff) - 0x00400000;
-            q = min(127, q);
-            d = __fdiv_rn(1.0f, iscale);
-        }
-    }
-    out.qs[row * out.k + blk * 256 + t] = (int8_t)q;
-    int s = q;
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if ((t & 15) == 0) out.bsums[row * (out.k / 16) + blk * 16 + (t >> 4)] = (int16_t)s;
-    if (t == 0) out.d[row * nb + blk] = d;
+    q8_K_block_store<A3>(x[row * ldx + blk * 256 + threadIdx.x], out, row, blk);
 }
 
 // A1: one warp per 32-element block, 8 blocks per CTA.

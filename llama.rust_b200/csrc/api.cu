@@ -382,6 +382,20 @@ int b200_mul_mat_q8(int type, int64_t n, int64_t k, int64_t m, const void *dev_w
     return launch_gemv(type, route, n, k, m, (const uint8_t *)dev_w, a.view(), dev_dst, lddst, (cudaStream_t)stream);
 }
 
+int b200_mul_mat_q8_add(int type, int64_t n, int64_t k, const void *dev_w, const void *dev_act, int act_kind, float *dev_dst,
+                        const float *dev_addend, float *dev_sum, int route, void *stream) {
+    int rc = check_mul_mat_args(type, n, k, 1);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    if (n == 0) return B200_STATUS_SUCCESS;
+    B200_REQUIRE(dev_w && dev_act && dev_dst && dev_addend && dev_sum, "mul_mat_q8_add: null pointer");
+    if (route == B200_ROUTE_AUTO) route = pick_route(type, n, 1);
+    B200_REQUIRE(act_kind == act_kind_for(type, route, 1), "mul_mat_q8_add: activation kind %d does not fit type %d", act_kind, type);
+    ActView a = act_carve(const_cast<void *>(dev_act), 1, k).view();
+    a.addend = dev_addend;
+    a.sum = dev_sum;
+    return launch_gemv(type, route, n, k, 1, (const uint8_t *)dev_w, a, dev_dst, n, (cudaStream_t)stream);
+}
+
 int b200_mul_mat(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, const float *dev_x, int64_t ldx,
                  float *dev_dst, int64_t lddst, int route, void *stream) {
     B200_REQUIRE(is_quant_type(type), "mul_mat: weight type %d is not supported", type);

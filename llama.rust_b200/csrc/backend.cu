@@ -408,7 +408,8 @@ static bool ranges_overlap(const void *a, size_t an, const void *b, size_t bn) {
 
 // MUL_MAT over one 2-d slice; consecutive mat-muls that read the same rows with the same quantizer
 // (q, k, v of a layer; gate and up of an FFN) share one quantization pass.
-static int mul_mat_2d(BackendCtx *bc, const ggml_tensor *w, const float *x, int64_t ldx, int64_t m, float *dst, int64_t lddst) {
+static int mul_mat_2d(BackendCtx *bc, const ggml_tensor *w, const float *x, int64_t ldx, int64_t m, float *dst, int64_t lddst,
+                      const float *addend = nullptr, float *sum = nullptr) {
     const int64_t k = w->ne[0], n = w->ne[1];
     const int route = pick_route(w->type, n, m);
     const int kind = act_kind_for(w->type, route, m);
@@ -428,7 +429,23 @@ static int mul_mat_2d(BackendCtx *bc, const ggml_tensor *w, const float *x, int6
         if (rc != B200_STATUS_SUCCESS) return rc;
         bc->act_src = x; bc->act_m = m; bc->act_k = k; bc->act_ld = ldx; bc->act_kind = kind;
     }
+    if (sum) return b200_mul_mat_q8_add(w->type, n, k, w->data, bc->act, kind, dst, addend, sum, route, bc->stream);
     return b200_mul_mat_q8(w->type, n, k, m, w->data, bc->act, kind, dst, lddst, route, bc->stream);
+}
+
+// fused: a one-row mat-mul whose result the next node adds to a tensor of the same shape (the residual)
+static bool fuses_mul_mat_add(const ggml_tensor *mm, const ggml_tensor *add) {
+    if (add->op != GGML_OP_ADD || !supports_glue(add, nullptr) || mm->ne[1] != 1 || mm->ne[2] != 1 || mm->ne[3] != 1) return false;
+    const ggml_tensor *other = add->src[0] == mm ? add->src[1] : add->src[1] == mm ? add->src[0] : nullptr;
+    if (!other || other == mm || !same_shape(other, mm)) return false;
+    // the sum must not land on the mat-mul's activations or weights
+    return add->data != mm->src[1]->data && add->data != mm->data;
+}
+static int compute_mul_mat_add(BackendCtx *bc, const ggml_tensor *op, const ggml_tensor *add) {
+    const ggml_tensor *w = op->src[0], *x = op->src[1];
+    const ggml_tensor *other = add->src[0] == op ? add->src[1] : add->src[0];
+    return mul_mat_2d(bc, w, (const float *)x->data, (int64_t)(x->nb[1] / 4), 1, (float *)op->data, (int64_t)(op->nb[1] / 4),
+                      (const float *)other->data, (float *)add->data);
 }
 
 static int compute_mul_mat(BackendCtx *bc, const ggml_tensor *op) {
@@ -473,10 +490,55 @@ static float param_f32(const ggml_tensor *op, int i) {
     return f;
 }
 
-// fused: when the node after an RMS_NORM multiplies it by a one-row weight, one kernel writes both
-static int compute_rms_norm(BackendCtx *bc, const ggml_tensor *op, const ggml_tensor *mul) {
+// The Q8_K kind the first mat-mul among the nodes after `from` that reads t as its activations will ask
+// for (0: none, or not a Q8_K kind, or t is not a plain 2-d row block).  The producer of t then quantizes
+// it on the way out and the mat-mul finds the quantized copy in place.
+static int upcoming_q8_K_kind(const ggml_cgraph *g, int from, const ggml_tensor *t) {
+    if (t->ne[2] != 1 || t->ne[3] != 1 || t->ne[0] % GROUP_K || t->nb[1] % 4 || t->ne[1] > 65535) return 0;
+    for (int j = from + 1; j < g->n_nodes && j <= from + 24; j++) {
+        const ggml_tensor *n = g->nodes[j];
+        if (!n || n->op != GGML_OP_MUL_MAT || n->src[1] != t) continue;
+        if (!supports_mul_mat(n, nullptr)) return 0;
+        const ggml_tensor *w = n->src[0];
+        const int kind = act_kind_for(w->type, pick_route(w->type, w->ne[1], t->ne[1]), t->ne[1]);
+        return kind == B200_ACT_Q8_K || kind == B200_ACT_Q8_K_4X8 || kind == B200_ACT_Q8_K_MIXED ? kind : 0;
+    }
+    return 0;
+}
+static int act_reserve(BackendCtx *bc, int64_t m, int64_t k) {
+    const size_t need = b200_act_scratch_nbytes(m, k);
+    if (need > bc->act_bytes) {
+        B200_CUDA(cudaStreamSynchronize(bc->stream));
+        if (bc->act) B200_CUDA(cudaFree(bc->act));
+        bc->act = nullptr;
+        bc->act_bytes = 0;
+        bc->act_src = nullptr;
+        B200_CUDA(cudaMalloc(&bc->act, need));
+        bc->act_bytes = need;
+        bc->generation++;
+    }
+    return B200_STATUS_SUCCESS;
+}
+static void act_holds(BackendCtx *bc, const ggml_tensor *t, int kind) {
+    bc->act_src = t->data; bc->act_m = t->ne[1]; bc->act_k = t->ne[0]; bc->act_ld = (int64_t)(t->nb[1] / 4); bc->act_kind = kind;
+}
+
+// fused: when the node after an RMS_NORM multiplies it by a one-row weight, one kernel writes both; q8_kind != 0:
+// it also quantizes the last of them for the mat-muls to come
+static int compute_rms_norm(BackendCtx *bc, const ggml_tensor *op, const ggml_tensor *mul, int q8_kind) {
     const ggml_tensor *x = op->src[0];
     const float *w = mul ? (const float *)mul->src[1]->data : nullptr;
+    if (q8_kind) {
+        const ggml_tensor *last = mul ? mul : op;
+        int rc = act_reserve(bc, last->ne[1], last->ne[0]);
+        if (rc != B200_STATUS_SUCCESS) return rc;
+        bc->act_src = nullptr;
+        rc = b200_rms_norm_q8((const float *)x->data, (int64_t)(x->nb[1] / 4), (float *)op->data, (int64_t)(op->nb[1] / 4), w,
+                              mul ? (float *)mul->data : nullptr, mul ? (int64_t)(mul->nb[1] / 4) : 0, x->ne[0], nrows_of(x),
+                              param_f32(op, 0), bc->act, q8_kind, bc->stream);
+        if (rc == B200_STATUS_SUCCESS) act_holds(bc, last, q8_kind);
+        return rc;
+    }
     return b200_rms_norm((const float *)x->data, (int64_t)(x->nb[1] / 4), (float *)op->data, (int64_t)(op->nb[1] / 4), w,
                          mul ? (float *)mul->data : nullptr, mul ? (int64_t)(mul->nb[1] / 4) : 0, x->ne[0], nrows_of(x),
                          param_f32(op, 0), bc->stream);
@@ -492,9 +554,20 @@ static int compute_binary(BackendCtx *bc, const ggml_tensor *op) {
                        nrows_of(a), bc->stream);
 }
 // fused: when the node after a SILU multiplies it by a tensor of the same shape, one kernel writes both
-static int compute_silu(BackendCtx *bc, const ggml_tensor *op, const ggml_tensor *mul) {
+static int compute_silu(BackendCtx *bc, const ggml_tensor *op, const ggml_tensor *mul, int q8_kind) {
     const ggml_tensor *x = op->src[0];
     const ggml_tensor *g = mul ? mul->src[1] : nullptr;
+    if (q8_kind) {
+        const ggml_tensor *last = mul ? mul : op;
+        int rc = act_reserve(bc, last->ne[1], last->ne[0]);
+        if (rc != B200_STATUS_SUCCESS) return rc;
+        bc->act_src = nullptr;
+        rc = b200_silu_q8((const float *)x->data, (int64_t)(x->nb[1] / 4), g ? (const float *)g->data : nullptr,
+                          g ? (int64_t)(g->nb[1] / 4) : 0, (float *)op->data, (int64_t)(op->nb[1] / 4), mul ? (float *)mul->data : nullptr,
+                          mul ? (int64_t)(mul->nb[1] / 4) : 0, x->ne[0], nrows_of(x), bc->silu_wide, bc->act, q8_kind, bc->stream);
+        if (rc == B200_STATUS_SUCCESS) act_holds(bc, last, q8_kind);
+        return rc;
+    }
     return b200_silu((const float *)x->data, (int64_t)(x->nb[1] / 4), g ? (const float *)g->data : nullptr,
                      g ? (int64_t)(g->nb[1] / 4) : 0, (float *)op->data, (int64_t)(op->nb[1] / 4), mul ? (float *)mul->data : nullptr,
                      mul ? (int64_t)(mul->nb[1] / 4) : 0, x->ne[0], nrows_of(x), bc->silu_wide, bc->stream);
@@ -718,23 +791,32 @@ static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
         if (op->type == B200_TYPE_I32 && in_our_buffer(op)) shadow_drop(bctx(op->buffer), op->data);
         int rc = B200_STATUS_SUCCESS;
         switch (op->op) {
-            case GGML_OP_MUL_MAT: rc = compute_mul_mat(bc, op); break;
+            case GGML_OP_MUL_MAT:
+                if (next && fuses_mul_mat_add(op, next) && supports_mul_mat(op, nullptr)) {
+                    if (bc->act_src && ranges_overlap(next->data, ggml_nbytes(next), bc->act_src, (size_t)bc->act_ld * bc->act_m * 4))
+                        bc->act_src = nullptr;
+                    rc = compute_mul_mat_add(bc, op, next);
+                    i++;
+                } else {
+                    rc = compute_mul_mat(bc, op);
+                }
+                break;
             case GGML_OP_MUL_MAT_ID: rc = compute_mul_mat_id(bc, op); break;
             case GGML_OP_FLASH_ATTN_EXT: rc = compute_flash(bc, op); break;
             case GGML_OP_RMS_NORM:
                 if (next && fuses_norm_mul(op, next)) {
                     if (bc->act_src && ranges_overlap(next->data, ggml_nbytes(next), bc->act_src, (size_t)bc->act_ld * bc->act_m * 4))
                         bc->act_src = nullptr;
-                    rc = compute_rms_norm(bc, op, next);
+                    rc = compute_rms_norm(bc, op, next, upcoming_q8_K_kind(g, i + 1, next));
                     i++;
                 } else {
-                    rc = compute_rms_norm(bc, op, nullptr);
+                    rc = compute_rms_norm(bc, op, nullptr, upcoming_q8_K_kind(g, i, op));
                 }
                 break;
             case GGML_OP_UNARY: {
                 const int j = find_silu_mul(g, i);
                 if (j > 0) silu_of[j] = i;   // runs with node j
-                else rc = compute_silu(bc, op, nullptr);
+                else rc = compute_silu(bc, op, nullptr, upcoming_q8_K_kind(g, i, op));
                 break;
             }
             case GGML_OP_MUL:
@@ -742,7 +824,7 @@ static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
                     const ggml_tensor *silu = g->nodes[silu_of[i]];
                     if (bc->act_src && ranges_overlap(silu->data, ggml_nbytes(silu), bc->act_src, (size_t)bc->act_ld * bc->act_m * 4))
                         bc->act_src = nullptr;
-                    rc = compute_silu(bc, silu, op);
+                    rc = compute_silu(bc, silu, op, upcoming_q8_K_kind(g, i, op));
                 } else {
                     rc = compute_binary(bc, op);
                 }

@@ -104,6 +104,10 @@ struct ActView {
     const int16_t *bsums;  // Q8_K 16-element sums
     const uint16_t *dh;    // Q8_0 scales (f16 bits)
     int64_t k;
+    // decode mat-muls (one activation row) may also emit result + addend: the residual ADD that follows
+    // attn_output and ffn_down in a decoder layer (crates/llama/src/graph_arch.rs:209,226), one rounded add
+    const float *addend = nullptr;
+    float *sum = nullptr;
 };
 struct ActBuf {
     int8_t *qs;
@@ -111,7 +115,11 @@ struct ActBuf {
     int16_t *bsums;
     uint16_t *dh;
     int64_t k;
-    ActView view() const { return ActView{qs, d, bsums, dh, k}; }
+    ActView view() const {
+        ActView v;
+        v.qs = qs; v.d = d; v.bsums = bsums; v.dh = dh; v.k = k;
+        return v;
+    }
 };
 size_t act_scratch_bytes(int64_t m, int64_t k);
 ActBuf act_carve(void *scratch, int64_t m, int64_t k);
@@ -137,6 +145,10 @@ int launch_mul_mat_id(int type, int64_t n, int64_t k, int64_t n_expert, int64_t 
 // glue ops (glue_ops.cu); strides in elements unless the name says nb (bytes)
 int launch_rms_norm(const float *x, int64_t x_stride, float *y, int64_t y_stride, const float *w, float *y_mul,
                     int64_t y_mul_stride, int64_t ne0, int64_t nrows, float eps, cudaStream_t s);
+int launch_rms_norm_q8(const float *x, int64_t x_stride, float *y, int64_t y_stride, const float *w, float *y_mul,
+                       int64_t y_mul_stride, int64_t ne0, int64_t nrows, float eps, ActBuf act, int64_t m4, cudaStream_t s);
+int launch_silu_q8(const float *x, int64_t x_stride, const float *g, int64_t g_stride, float *y, int64_t y_stride, float *y_mul,
+                   int64_t y_mul_stride, int64_t ne0, int64_t nrows, int wide, ActBuf act, int64_t m4, cudaStream_t s);
 int launch_binary(int op, const float *a, int64_t a_stride, const float *b, int64_t b_stride, int64_t b_ne0, int64_t b_rows,
                   float *y, int64_t y_stride, int64_t ne0, int64_t nrows, cudaStream_t s);
 int launch_silu(const float *x, int64_t x_stride, const float *g, int64_t g_stride, float *y, int64_t y_stride, float *y_mul,

@@ -18,7 +18,7 @@ static __device__ const double c_exp2_tab[32] = {
     0x1.ae89f995ad3adp+0, 0x1.b7f76f2fb5e47p+0, 0x1.c199bdd85529cp+0, 0x1.cb720dcef9069p+0,
     0x1.d5818dcfba487p+0, 0x1.dfc97337b9b5fp+0, 0x1.ea4afa2a490dap+0, 0x1.f50765b6e4540p+0};
 
-__device__ __forceinline__ float libm_expf(float x) {
+__device__ __forceinline__ float libm_expf_tab(float x, const double *tab) {
     if (x != x) return x;
     if (x < -0x1.9fe368p6f) return 0.0f;                 // below log(2^-150)
     if (x > 0x1.62e42ep6f) return __int_as_float(0x7f800000);
@@ -31,7 +31,7 @@ __device__ __forceinline__ float libm_expf(float x) {
     const unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
     kd = __dsub_rn(kd, shift);
     const double r = __dsub_rn(z, kd);
-    unsigned long long t = (unsigned long long)__double_as_longlong(c_exp2_tab[ki & 31]);
+    unsigned long long t = (unsigned long long)__double_as_longlong(tab[ki & 31]);
     t += (ki >> 5) << 52;   // == T[ki % N] + (ki << 47) with the table's own bias folded out
     const double s = __longlong_as_double((long long)t);
     z = __fma_rn(c0, r, c1);
@@ -41,6 +41,8 @@ __device__ __forceinline__ float libm_expf(float x) {
     y = __dmul_rn(y, s);
     return __double2float_rn(y);
 }
+
+__device__ __forceinline__ float libm_expf(float x) { return libm_expf_tab(x, c_exp2_tab); }
 
 // one lane of ggml_v_expf (AVX512F+DQ branch): crates/ggml/src/flash_attn.rs:948-975
 __device__ __forceinline__ float v_expf(float x) {

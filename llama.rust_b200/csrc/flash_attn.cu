@@ -15,6 +15,7 @@
 // chunk): prefix-max scan per 128-position tile, then the sequential f16
 // accumulation with one thread per value element), merge.
 #include <cmath>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "fa_math.cuh"
@@ -22,6 +23,14 @@
 namespace b200 {
 
 __device__ __forceinline__ float r16(float v) { return __half2float(__float2half_rn(v)); }
+// r16 for the long dependent chains: in the normal f16 range [2^-14, 65520) rounding to nearest even at
+// bit 13 of the f32 pattern is three integer operations; everything else takes the conversion pair
+__device__ __forceinline__ float r16_fast(float v) {
+    const uint32_t b = __float_as_uint(v);
+    if (((b & 0x7fffffffu) - 0x38800000u) < (0x477ff000u - 0x38800000u))
+        return __uint_as_float((b + 0x0fffu + ((b >> 13) & 1u)) & 0xffffe000u);
+    return r16(v);
+}
 
 struct FaDims {
     int dk, dv, T, H, H_kv;
@@ -266,6 +275,253 @@ __global__ void fa_merge_kernel(FaDims d, const float *__restrict__ partials, fl
     dst[row * d.dv + e] = fin;
 }
 
+
+// ---------------------------------------------------------------------------
+// One query row (a decode step): scores, chunk scan and merge in ONE kernel.
+// Grid (chunk, head), block = 128 position / value threads + 1 warp for the S chain.  Per 128-position
+// tile a thread first computes its position's score (the K row sits in its registers), then the tile runs
+// exactly as in fa_rows_kernel.  The CTA that finishes a head's last chunk (a per-head counter tells)
+// merges the chunk partials in chunk order and writes the row.  Same operations in the same order as the
+// three-kernel path, so the same bits.
+// ---------------------------------------------------------------------------
+template <int DK>
+__global__ void __launch_bounds__(160)
+fa_decode_kernel(b200_flash_attn_args a, FaDims d, float kq_scale, float *__restrict__ partials, int *__restrict__ counters, bool split) {
+    extern __shared__ __align__(16) unsigned char fsm[];
+    __half *v_s = (__half *)fsm;                                  // [FA_TILE][dv]
+    float *ms_s = (float *)(fsm + (size_t)FA_TILE * d.dv * 2);    // [FA_TILE]
+    float *vs_s = ms_s + FA_TILE;
+    float *wmax = vs_s + FA_TILE;                                 // [4] warp maxima
+    float *q_s = wmax + 4;                                        // [DK], q rounded to f16
+    double *tab_s = (double *)(q_s + DK);                         // [32] the exp2 table of libm_expf
+    __shared__ float carry_M;
+    __shared__ int is_last;
+    pdl_trigger();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int c = blockIdx.x, h = blockIdx.y;
+    const int hkv = h / (d.H / d.H_kv);
+    const int64_t ic0 = (int64_t)c * d.chunk;
+    const int64_t ic1 = ic0 + d.chunk < d.n_kv ? ic0 + d.chunk : d.n_kv;
+    const int64_t row = h;
+    float *part = partials + (row * d.n_chunks + c) * (2 + d.dv);
+    const uint8_t *vbase = (const uint8_t *)a.v + (int64_t)hkv * a.v_nb2;
+    const uint8_t *kbase = (const uint8_t *)a.k + (int64_t)hkv * a.k_nb2;
+    float x = 0.0f, S = 0.0f;
+    const bool is_val = tid < d.dv;
+    const bool is_s = tid == 128;
+    pdl_wait();   // q, and the cache rows the previous kernels wrote
+    if (ic0 < d.n_kv) {
+        const float *q = (const float *)((const uint8_t *)a.q + (int64_t)h * a.q_nb2);
+        for (int i = tid; i < DK; i += blockDim.x) q_s[i] = r16(q[i]);
+        if (tid >= 128) tab_s[tid - 128] = c_exp2_tab[tid - 128];
+        if (tid == 0) carry_M = -INFINITY;
+        // ALiBi slope of head h: crates/ggml/src/flash_attn.rs:356-370
+        float slope = 1.0f;
+        if (a.mask && a.max_bias > 0.0f) {
+            const unsigned nl2 = 1u << (31 - __clz((unsigned)d.H));
+            const float m0 = powf(2.0f, -a.max_bias / (float)nl2);
+            const float m1 = powf(2.0f, -(a.max_bias / 2.0f) / (float)nl2);
+            const float base = (unsigned)h < nl2 ? m0 : m1;
+            const int ex = (unsigned)h < nl2 ? h + 1 : 2 * (h - (int)nl2) + 1;
+            float acc = 1.0f, b = base;   // powi by repeated squaring
+            for (int e2 = ex; e2 > 0; e2 >>= 1) {
+                if (e2 & 1) acc = __fmul_rn(acc, b);
+                b = __fmul_rn(b, b);
+            }
+            slope = acc;
+        }
+        __syncthreads();
+        for (int64_t p0 = ic0; p0 < ic1; p0 += FA_TILE) {
+            const int np = ic1 - p0 < FA_TILE ? (int)(ic1 - p0) : FA_TILE;
+            // stage the V tile: np rows of dv halves, 16 bytes per load
+            const int chunks_per_row = d.dv / 8;
+            for (int i = tid; i < np * chunks_per_row; i += blockDim.x) {
+                const int pr = i / chunks_per_row, cc = i % chunks_per_row;
+                // asynchronous 16-byte copies: they land while the scores are computed
+                const unsigned dst = (unsigned)__cvta_generic_to_shared(v_s + pr * d.dv + cc * 8);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(vbase + (p0 + pr) * a.v_nb1 + cc * 16) : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            // this thread's position: the f16 dot of crates/ggml/src/vec_dot.rs:1982-2019, scale, softcap, mask
+            float s = -INFINITY;
+            if (tid < FA_TILE && tid < np) {
+                const int64_t p = p0 + tid;
+                __half2 kr[DK / 2];
+                const uint4 *src = (const uint4 *)(kbase + p * a.k_nb1);
+#pragma unroll
+                for (int i = 0; i < DK / 8; i++) {
+                    const uint4 v = src[i];
+                    kr[4 * i + 0] = *(const __half2 *)&v.x;
+                    kr[4 * i + 1] = *(const __half2 *)&v.y;
+                    kr[4 * i + 2] = *(const __half2 *)&v.z;
+                    kr[4 * i + 3] = *(const __half2 *)&v.w;
+                }
+                float val[16];
+#pragma unroll
+                for (int l = 0; l < 16; l++) {
+                    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+#pragma unroll
+                    for (int cc = 0; cc < DK / 64; cc++) {
+                        const int e = 64 * cc + l;
+                        const float k0 = (e & 1) ? __high2float(kr[e >> 1]) : __low2float(kr[e >> 1]);
+                        const float k1 = ((e + 16) & 1) ? __high2float(kr[(e + 16) >> 1]) : __low2float(kr[(e + 16) >> 1]);
+                        const float k2 = ((e + 32) & 1) ? __high2float(kr[(e + 32) >> 1]) : __low2float(kr[(e + 32) >> 1]);
+                        const float k3 = ((e + 48) & 1) ? __high2float(kr[(e + 48) >> 1]) : __low2float(kr[(e + 48) >> 1]);
+                        s0 = __fmaf_rn(q_s[e], k0, s0);
+                        s1 = __fmaf_rn(q_s[e + 16], k1, s1);
+                        s2 = __fmaf_rn(q_s[e + 32], k2, s2);
+                        s3 = __fmaf_rn(q_s[e + 48], k3, s3);
+                    }
+                    val[l] = __fadd_rn(__fadd_rn(s0, s2), __fadd_rn(s1, s3));
+                }
+#pragma unroll
+                for (int half = 8; half >= 1; half >>= 1)
+#pragma unroll
+                    for (int i = 0; i < half; i++) val[i] = __fadd_rn(val[i], val[i + half]);
+                s = __fmul_rn(val[0], kq_scale);
+                if (a.logit_softcap != 0.0f) s = __fmul_rn(a.logit_softcap, tanhf(s));
+                if (a.mask) {
+                    const __half mh = ((const __half *)a.mask)[p];
+                    const float mv = __fmul_rn(slope, __half2float(mh));
+                    s = (mv == -INFINITY) ? -INFINITY : __fadd_rn(s, mv);
+                }
+            }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            // exclusive prefix maximum of the tile's scores (threads 0..127 = positions)
+            float incl = s;
+            if (tid < FA_TILE) {
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const float n = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl = fmaxf(incl, n);
+                }
+                if (lane == 31) wmax[warp] = incl;
+            }
+            __syncthreads();
+            if (tid < FA_TILE) {
+                float before = carry_M;
+                for (int w = 0; w < warp; w++) before = fmaxf(before, wmax[w]);
+                float excl = __shfl_up_sync(0xffffffffu, incl, 1);
+                if (lane == 0) excl = -INFINITY;
+                before = fmaxf(before, excl);
+                float ms = 1.0f, vs = 0.0f;
+                if (tid < np && s != -INFINITY) {
+                    if (s > before) {
+                        ms = libm_expf_tab(__fsub_rn(before, s), tab_s);
+                        vs = 1.0f;
+                    } else {
+                        vs = libm_expf_tab(__fsub_rn(s, before), tab_s);
+                    }
+                } else {
+                    ms = -1.0f;   // marks a skipped position
+                }
+                ms_s[tid] = ms;
+                vs_s[tid] = vs;
+            }
+            __syncthreads();
+            if (tid == 0) {
+                float m = carry_M;
+                for (int w = 0; w < 4; w++) m = fmaxf(m, wmax[w]);
+                carry_M = m;
+            }
+            if (is_val) {
+#pragma unroll 4
+                for (int i = 0; i < np; i++) {
+                    const float ms = ms_s[i], vs = vs_s[i];
+                    const float v = __half2float(v_s[i * d.dv + tid]);
+                    if (ms == 1.0f) {            // no new maximum: one fma, one rounding
+                        x = r16_fast(__fmaf_rn(v, vs, x));
+                    } else if (ms >= 0.0f) {
+                        x = r16(__fmul_rn(x, ms));
+                        x = r16(__fmaf_rn(v, vs, x));
+                    }                            // ms < 0: a skipped position
+                }
+            } else if (is_s) {
+                for (int i = 0; i < np; i++) {
+                    const float ms = ms_s[i];
+                    if (ms < 0.0f) continue;
+                    S = __fmaf_rn(S, ms, vs_s[i]);
+                }
+            }
+            __syncthreads();
+        }
+        // sinks: only the chunk that starts at position 0 (flash_attn.rs:661-690), in f32
+        float M = carry_M;
+        if (a.sinks && ic0 == 0) {
+            const float sh = a.sinks[h];
+            float ms = 1.0f, vs = 1.0f;
+            if (sh > M) {
+                ms = libm_expf(__fsub_rn(M, sh));
+                if (is_val) x = __fmul_rn(x, ms);
+                M = sh;
+            } else {
+                vs = libm_expf(__fsub_rn(sh, M));
+            }
+            if (is_s) S = __fadd_rn(__fmul_rn(S, ms), vs);
+        }
+        if (is_val) part[2 + tid] = x;
+        if (is_s) { part[0] = M; part[1] = S; }
+    } else if (tid == 0) {   // out-of-range chunk: M = -inf, S = 0 (flash_attn.rs:757-764)
+        part[0] = -INFINITY;
+        part[1] = 0.0f;
+    }
+    // the CTA that completes the head merges its chunks
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) is_last = atomicAdd(&counters[h], 1) == d.n_chunks - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (tid == 0) counters[h] = 0;   // ready for the next launch
+    const int e = tid;
+    if (e >= d.dv) return;
+    const volatile float *p0 = partials + row * d.n_chunks * (2 + d.dv);
+    if (!split) {
+        const float Sv = p0[1];
+        const float s_inv = Sv == 0.0f ? 0.0f : __fdiv_rn(1.0f, Sv);
+        a.dst[row * d.dv + e] = __fmul_rn(p0[2 + e], s_inv);
+        return;
+    }
+    float fin = 0.0f, Mf = -INFINITY, Sf = 0.0f;
+    for (int cc = 0; cc < d.n_chunks; cc++) {
+        if ((int64_t)cc * d.chunk >= d.n_kv) continue;
+        const volatile float *p = p0 + (int64_t)cc * (2 + d.dv);
+        const float Mc = p[0], Sc = p[1];
+        if (Sc == 0.0f) continue;
+        const float Mn = fmaxf(Mf, Mc);
+        const float so = libm_expf(__fsub_rn(Mf, Mn)), sn = libm_expf(__fsub_rn(Mc, Mn));
+        fin = __fmaf_rn(fin, so, __fmul_rn(p[2 + e], sn));
+        Sf = __fmaf_rn(Sf, so, __fmul_rn(Sc, sn));
+        Mf = Mn;
+    }
+    if (Sf != 0.0f) fin = __fmul_rn(fin, __fdiv_rn(1.0f, Sf));
+    a.dst[row * d.dv + e] = fin;
+}
+
+// per-device head counters of fa_decode_kernel (zero between launches)
+static int *g_fa_counters[64] = {nullptr};
+constexpr int FA_DECODE_MAX_HEADS = 4096;
+
+static int flash_attn_decode_one_kernel(const b200_flash_attn_args *a, const FaDims &d, bool split, cudaStream_t s) {
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    B200_REQUIRE(dev >= 0 && dev < 64, "flash_attn_ext: device index %d out of range", dev);
+    if (!g_fa_counters[dev]) {
+        B200_CUDA(cudaMalloc((void **)&g_fa_counters[dev], FA_DECODE_MAX_HEADS * sizeof(int)));
+        B200_CUDA(cudaMemset(g_fa_counters[dev], 0, FA_DECODE_MAX_HEADS * sizeof(int)));
+    }
+    const size_t part_b = (size_t)d.H * d.n_chunks * (2 + d.dv) * 4;
+    void *scratch = nullptr;
+    int rc = scratch_get(part_b, &scratch);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    const float kq_scale = a->logit_softcap != 0.0f ? a->scale / a->logit_softcap : a->scale;
+    const dim3 grid((unsigned)d.n_chunks, (unsigned)d.H);
+    const size_t smem = (size_t)FA_TILE * d.dv * 2 + (2 * FA_TILE + 4 + d.dk) * 4 + 32 * 8;
+    if (d.dk == 128)
+        return launch_pdl(fa_decode_kernel<128>, grid, dim3(160), smem, s, *a, d, kq_scale, (float *)scratch, g_fa_counters[dev], split);
+    return launch_pdl(fa_decode_kernel<64>, grid, dim3(160), smem, s, *a, d, kq_scale, (float *)scratch, g_fa_counters[dev], split);
+}
+
 static int check_args(const b200_flash_attn_args *a) {
     B200_REQUIRE(a != nullptr, "flash_attn_ext: null argument block");
     B200_REQUIRE(a->q && a->k && a->v && a->dst, "flash_attn_ext: null tensor pointer");
@@ -284,6 +540,16 @@ static int check_args(const b200_flash_attn_args *a) {
 
 int flash_attn_faithful_tiled(const b200_flash_attn_args *a, cudaStream_t s);   // flash_attn_tiled.cu
 
+// B200_FA_DECODE_FUSED=0 keeps single-row attention on the three-kernel path (for side-by-side measurements)
+static bool fa_decode_one_kernel_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_FA_DECODE_FUSED");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
 int flash_attn_faithful_rows(const b200_flash_attn_args *a, cudaStream_t s) {
     FaDims d;
     d.dk = (int)a->dk; d.dv = (int)a->dv; d.T = (int)a->n_tok; d.H = (int)a->n_head; d.H_kv = (int)a->n_head_kv;
@@ -298,6 +564,7 @@ int flash_attn_faithful_rows(const b200_flash_attn_args *a, cudaStream_t s) {
         return B200_STATUS_SUCCESS;
     }
     B200_REQUIRE(d.T <= 65535 && d.H <= 65535, "flash_attn_ext: too many rows for one launch");
+    if (d.T == 1 && d.H <= FA_DECODE_MAX_HEADS && fa_decode_one_kernel_enabled()) return flash_attn_decode_one_kernel(a, d, split, s);
     const size_t score_b = ((size_t)rows * d.n_kv * 4 + 255) / 256 * 256;
     const size_t part_b = (size_t)rows * d.n_chunks * (2 + d.dv) * 4;
     void *scratch = nullptr;

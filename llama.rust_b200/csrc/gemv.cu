@@ -188,7 +188,11 @@ gemv_q4_K_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, 
             }
         }
         const int64_t row = tile * TILE_ROWS + r;
-        if (row < n) dst[(int64_t)col * lddst + row] = MODE == 2 ? sumf : __fsub_rn(sumf, summin);
+        if (row < n) {
+            const float v = MODE == 2 ? sumf : __fsub_rn(sumf, summin);
+            dst[(int64_t)col * lddst + row] = v;
+            if (acts.sum && col == 0) acts.sum[row] = __fadd_rn(v, acts.addend[row]);
+        }
     }
 }
 
@@ -288,7 +292,10 @@ gemv_generic_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t ldds
     }
     const int64_t row0 = tile * TILE_ROWS;
     if (T::CHAINS == 1) {
-        if (is_chain && row0 + c_row < n) dst[(int64_t)c_col * lddst + row0 + c_row] = acc;
+        if (is_chain && row0 + c_row < n) {
+            dst[(int64_t)c_col * lddst + row0 + c_row] = acc;
+            if (acts.sum && c_col == 0) acts.sum[row0 + c_row] = __fadd_rn(acc, acts.addend[row0 + c_row]);
+        }
     } else {
         // hsum8 of the eight lane accumulators: crates/ggml/src/vec_dot.rs:564-572
         if (is_chain) fin[(c_col * 12 + c_l) * 32 + c_row] = acc;
@@ -304,7 +311,10 @@ gemv_generic_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t ldds
                 const float m01 = __fadd_rn(__fadd_rn(a[8 * 32], a[10 * 32]), __fadd_rn(a[9 * 32], a[11 * 32]));
                 v = __fadd_rn(v, m01);
             }
-            if (row0 + r < n) dst[(int64_t)col * lddst + row0 + r] = v;
+            if (row0 + r < n) {
+                dst[(int64_t)col * lddst + row0 + r] = v;
+                if (acts.sum && col == 0) acts.sum[row0 + r] = __fadd_rn(v, acts.addend[row0 + r]);
+            }
         }
     }
 }

@@ -265,7 +265,11 @@ gemv_q4_K_stream_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *
                         summin = __fmaf_rn((float)vm, __fmul_rn(dmin, da), summin);
                     }
                     const int64_t row = tile * TILE_ROWS + lane;
-                    if (row < n) dst[row] = __fsub_rn(sumf, summin);
+                    if (row < n) {
+                        const float v = __fsub_rn(sumf, summin);
+                        dst[row] = v;
+                        if (acts.sum) acts.sum[row] = __fadd_rn(v, acts.addend[row]);
+                    }
                     if (lane == 0) sm.tile_cnt[xi] = 0;
                     __syncwarp();
                 }

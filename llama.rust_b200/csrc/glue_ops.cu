@@ -7,6 +7,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "act_quant.cuh"
 #include "fa_math.cuh"
 
 namespace b200 {
@@ -51,6 +52,52 @@ int launch_rms_norm(const float *x, int64_t x_stride, float *y, int64_t y_stride
     if (nrows == 0) return B200_STATUS_SUCCESS;
     return launch_pdl(rms_norm_kernel, dim3((unsigned)nrows), dim3(256), 0, s, x, x_stride, y, y_stride, w, y_mul, y_mul_stride,
                       (int)ne0, eps);
+}
+
+// The same, followed by the Q8_K quantization of the result for the mat-muls that read it: grid
+// (ne0 / 256, rows), every CTA recomputes the row's sum (the row is a few KB and sits in L2) in the same
+// order, then owns one 256-element block: norm, weighted norm, and that block's quants, scale and
+// 16-element sums (act_quant.cuh).  Rows below m4 take the 4x8 value rule, the others the plain one.
+__global__ void __launch_bounds__(256)
+rms_norm_q8_kernel(const float *__restrict__ x, int64_t x_stride, float *y, int64_t y_stride, const float *__restrict__ w,
+                   float *y_mul, int64_t y_mul_stride, int ne0, float eps, ActBuf act, int64_t m4) {
+    pdl_trigger();
+    pdl_wait();
+    const int64_t row = blockIdx.y;
+    const float *xr = x + row * x_stride;
+    double sum = 0.0;
+    for (int i = threadIdx.x; i < ne0; i += 256) {
+        const float v = xr[i];
+        sum += (double)__fmul_rn(v, v);
+    }
+    __shared__ double part[8];
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    double total = 0.0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) total += part[i];
+    const float mean = __double2float_rn(total / (double)ne0);
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    const float n = __fmul_rn(xr[i], scale);
+    if (y) y[row * y_stride + i] = n;
+    float v = n;
+    if (w) {
+        v = __fmul_rn(n, w[i]);
+        y_mul[row * y_mul_stride + i] = v;
+    }
+    if (row < m4) q8_K_block_store<true>(v, act, row, blockIdx.x);
+    else q8_K_block_store<false>(v, act, row, blockIdx.x);
+}
+
+int launch_rms_norm_q8(const float *x, int64_t x_stride, float *y, int64_t y_stride, const float *w, float *y_mul,
+                       int64_t y_mul_stride, int64_t ne0, int64_t nrows, float eps, ActBuf act, int64_t m4, cudaStream_t s) {
+    B200_REQUIRE(ne0 > 0 && ne0 % 256 == 0 && ne0 < (1 << 30), "rms_norm + q8_K: row length %lld is not a multiple of 256", (long long)ne0);
+    B200_REQUIRE(nrows <= 65535, "rms_norm + q8_K: %lld rows exceed one launch", (long long)nrows);
+    if (nrows == 0) return B200_STATUS_SUCCESS;
+    return launch_pdl(rms_norm_q8_kernel, dim3((unsigned)(ne0 / 256), (unsigned)nrows), dim3(256), 0, s, x, x_stride, y, y_stride, w,
+                      y_mul, y_mul_stride, (int)ne0, eps, act, m4);
 }
 
 // ---- ADD / MUL -------------------------------------------------------------------------------------
@@ -117,6 +164,38 @@ int launch_silu(const float *x, int64_t x_stride, const float *g, int64_t g_stri
     const int wide_end = wide ? (int)(ne0 & ~(int64_t)15) : 0;
     return launch_pdl(silu_kernel, dim3((unsigned)blocks), dim3(256), 0, s, x, x_stride, g, g_stride, y, y_stride, y_mul, y_mul_stride,
                       (int)ne0, wide_end, total);
+}
+
+// The same, followed by the Q8_K quantization of the result (the gated product when g is given): grid
+// (ne0 / 256, rows), one 256-element block per CTA.
+__global__ void __launch_bounds__(256)
+silu_q8_kernel(const float *__restrict__ x, int64_t x_stride, const float *__restrict__ g, int64_t g_stride, float *y,
+               int64_t y_stride, float *y_mul, int64_t y_mul_stride, int wide_end, ActBuf act, int64_t m4) {
+    pdl_trigger();
+    pdl_wait();
+    const int64_t r = blockIdx.y;
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    const float v = x[r * x_stride + c];
+    const float e = c < wide_end ? v_expf(__fsub_rn(0.0f, v)) : libm_expf(-v);
+    const float sv = __fdiv_rn(v, __fadd_rn(1.0f, e));
+    if (y) y[r * y_stride + c] = sv;
+    float out = sv;
+    if (g) {
+        out = __fmul_rn(sv, g[r * g_stride + c]);
+        y_mul[r * y_mul_stride + c] = out;
+    }
+    if (r < m4) q8_K_block_store<true>(out, act, r, blockIdx.x);
+    else q8_K_block_store<false>(out, act, r, blockIdx.x);
+}
+
+int launch_silu_q8(const float *x, int64_t x_stride, const float *g, int64_t g_stride, float *y, int64_t y_stride, float *y_mul,
+                   int64_t y_mul_stride, int64_t ne0, int64_t nrows, int wide, ActBuf act, int64_t m4, cudaStream_t s) {
+    B200_REQUIRE(ne0 > 0 && ne0 % 256 == 0 && ne0 < (1 << 30), "silu + q8_K: row length %lld is not a multiple of 256", (long long)ne0);
+    B200_REQUIRE(nrows <= 65535, "silu + q8_K: %lld rows exceed one launch", (long long)nrows);
+    if (nrows == 0) return B200_STATUS_SUCCESS;
+    const int wide_end = wide ? (int)(ne0 & ~(int64_t)15) : 0;
+    return launch_pdl(silu_q8_kernel, dim3((unsigned)(ne0 / 256), (unsigned)nrows), dim3(256), 0, s, x, x_stride, g, g_stride, y, y_stride,
+                      y_mul, y_mul_stride, wide_end, act, m4);
 }
 
 // ---- ROPE --------------------------------------------------------------------------------------------
@@ -344,6 +423,26 @@ int b200_rms_norm(const float *x, int64_t x_stride, float *y, int64_t y_stride, 
     return launch_rms_norm(x, x_stride, y, y_stride, weight, y_weighted, y_weighted_stride, ne0, nrows, eps, (cudaStream_t)stream);
 }
 
+// rows below m4 of a MIXED result take the 4x8 value rule: what the Q4_K 8x8 route reads (see b200_act_quant)
+static int q8_K_rows_4x8(int act_kind, int64_t nrows, int64_t *m4) {
+    B200_REQUIRE(act_kind == B200_ACT_Q8_K || act_kind == B200_ACT_Q8_K_4X8 || act_kind == B200_ACT_Q8_K_MIXED,
+                 "fused quantization supports the Q8_K kinds only (kind %d)", act_kind);
+    *m4 = act_kind == B200_ACT_Q8_K ? 0 : act_kind == B200_ACT_Q8_K_4X8 ? nrows : nrows - nrows % 4;
+    return B200_STATUS_SUCCESS;
+}
+
+int b200_rms_norm_q8(const float *x, int64_t x_stride, float *y, int64_t y_stride, const float *weight, float *y_weighted,
+                     int64_t y_weighted_stride, int64_t ne0, int64_t nrows, float eps, void *dev_act, int act_kind, void *stream) {
+    B200_REQUIRE(x != nullptr && dev_act != nullptr, "rms_norm_q8: null operand");
+    B200_REQUIRE(weight == nullptr || y_weighted != nullptr, "rms_norm_q8: weight given without y_weighted");
+    B200_REQUIRE(((uintptr_t)dev_act & 255) == 0, "rms_norm_q8: scratch must be 256-byte aligned");
+    int64_t m4 = 0;
+    int rc = q8_K_rows_4x8(act_kind, nrows, &m4);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    return launch_rms_norm_q8(x, x_stride, y, y_stride, weight, y_weighted, y_weighted_stride, ne0, nrows, eps,
+                              act_carve(dev_act, nrows, ne0), m4, (cudaStream_t)stream);
+}
+
 int b200_binary(int op, const float *a, int64_t a_stride, const float *b, int64_t b_stride, int64_t b_ne0, int64_t b_rows, float *y,
                 int64_t y_stride, int64_t ne0, int64_t nrows, void *stream) {
     B200_REQUIRE(a != nullptr && b != nullptr && y != nullptr, "binary: null operand");
@@ -355,6 +454,18 @@ int b200_silu(const float *x, int64_t x_stride, const float *gate, int64_t gate_
     B200_REQUIRE(x != nullptr && (y != nullptr || (gate != nullptr && y_gated != nullptr)), "silu: null operand");
     B200_REQUIRE(gate == nullptr || y_gated != nullptr, "silu: gate given without y_gated");
     return launch_silu(x, x_stride, gate, gate_stride, y, y_stride, y_gated, y_gated_stride, ne0, nrows, wide, (cudaStream_t)stream);
+}
+
+int b200_silu_q8(const float *x, int64_t x_stride, const float *gate, int64_t gate_stride, float *y, int64_t y_stride, float *y_gated,
+                 int64_t y_gated_stride, int64_t ne0, int64_t nrows, int wide, void *dev_act, int act_kind, void *stream) {
+    B200_REQUIRE(x != nullptr && dev_act != nullptr, "silu_q8: null operand");
+    B200_REQUIRE(gate == nullptr || y_gated != nullptr, "silu_q8: gate given without y_gated");
+    B200_REQUIRE(((uintptr_t)dev_act & 255) == 0, "silu_q8: scratch must be 256-byte aligned");
+    int64_t m4 = 0;
+    int rc = q8_K_rows_4x8(act_kind, nrows, &m4);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    return launch_silu_q8(x, x_stride, gate, gate_stride, y, y_stride, y_gated, y_gated_stride, ne0, nrows, wide,
+                          act_carve(dev_act, nrows, ne0), m4, (cudaStream_t)stream);
 }
 
 int b200_host_silu_is_wide(void) { return __builtin_cpu_supports("avx512f") && __builtin_cpu_supports("avx512dq") ? 1 : 0; }

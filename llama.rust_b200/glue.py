@@ -122,3 +122,41 @@ def argmax(x):
     dx, do = device_array(x2), DeviceBuffer(x2.shape[0] * 4)
     check(lib.b200_argmax(dx.ptr, x2.shape[1], x2.shape[1], x2.shape[0], do.ptr, None))
     return do.download(np.int32, x2.shape[0])
+
+
+lib.b200_rms_norm_q8.argtypes = [vp, i64, vp, i64, vp, vp, i64, i64, i64, f32, vp, i32, vp]
+lib.b200_silu_q8.argtypes = [vp, i64, vp, i64, vp, i64, vp, i64, i64, i64, i32, vp, i32, vp]
+
+
+def _read_q8_K(dact, m, k):
+    """(qs int8 [m, k], d f32 [m, k/256], bsums i16 [m, k/16]) out of a device activation scratch"""
+    def up(v):
+        return (v + 255) // 256 * 256
+    o_d = up(m * k)
+    o_b = o_d + up(m * (k // 256) * 4)
+    qs = dact.download(np.int8, m * k).reshape(m, k)
+    d = dact.download(np.float32, m * (k // 256), offset=o_d).reshape(m, k // 256)
+    bs = dact.download(np.int16, m * (k // 16), offset=o_b).reshape(m, k // 16)
+    return qs, d, bs
+
+
+def rms_norm_q8(x, eps, weight, act_kind):
+    """-> (y, y * weight, (qs, d, bsums) of y * weight)"""
+    x = _f(x)
+    ne0, n = x.shape[-1], _rows(x)
+    dx, dy, dyw, dw = device_array(x), DeviceBuffer(x.nbytes), DeviceBuffer(x.nbytes), device_array(_f(weight))
+    dact = DeviceBuffer(lib.b200_act_scratch_nbytes(n, ne0))
+    check(lib.b200_rms_norm_q8(dx.ptr, ne0, dy.ptr, ne0, dw.ptr, dyw.ptr, ne0, ne0, n, eps, dact.ptr, act_kind, None))
+    return (dy.download(np.float32, x.size).reshape(x.shape), dyw.download(np.float32, x.size).reshape(x.shape),
+            _read_q8_K(dact, n, ne0))
+
+
+def silu_q8(x, gate, wide, act_kind):
+    """-> (silu(x), silu(x) * gate, (qs, d, bsums) of the product)"""
+    x, gate = _f(x), _f(gate)
+    ne0, n = x.shape[-1], _rows(x)
+    dx, dg, dy, dyg = device_array(x), device_array(gate), DeviceBuffer(x.nbytes), DeviceBuffer(x.nbytes)
+    dact = DeviceBuffer(lib.b200_act_scratch_nbytes(n, ne0))
+    check(lib.b200_silu_q8(dx.ptr, ne0, dg.ptr, ne0, dy.ptr, ne0, dyg.ptr, ne0, ne0, n, int(wide), dact.ptr, act_kind, None))
+    return (dy.download(np.float32, x.size).reshape(x.shape), dyg.download(np.float32, x.size).reshape(x.shape),
+            _read_q8_K(dact, n, ne0))

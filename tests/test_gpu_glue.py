@@ -192,3 +192,47 @@ def test_argmax_last_of_equals(g):
     got = g.argmax(x)
     want = [orc_glue.argmax(r) for r in x]
     assert list(got) == want and got[1] == 90000 and got[2] == 128255 and got[4] == 0
+
+
+def q8_K_parts(x, m4):
+    """the oracle's Q8_K blocks of each row as (qs, d, bsums): rows below m4 by the 4x8 rule, the rest plain"""
+    m, k = x.shape
+    qs, d, bs = np.empty((m, k), np.int8), np.empty((m, k // 256), np.float32), np.empty((m, k // 16), np.int16)
+    if m4:
+        blocks = orc.quantize_q8_K_4x8(x[:m4])        # [m4/4 groups] of block_q8_Kx4: d[4] f32, qs[1024] (8-byte interleave), bsums[64]
+        g = blocks.reshape(m4 // 4, k // 256, 4 * 292)
+        for r in range(m4):
+            grp, lane = r // 4, r % 4
+            for b in range(k // 256):
+                raw = g[grp, b]
+                d[r, b] = raw[:16].view(np.float32)[lane]
+                q = raw[16:16 + 1024].view(np.int8).reshape(32, 4, 8)[:, lane, :].reshape(256)
+                qs[r, b * 256:(b + 1) * 256] = q
+                bs[r, b * 16:(b + 1) * 16] = q.reshape(16, 16).sum(axis=1)
+    for r in range(m4, m):
+        blk = orc.quantize_q8_K(x[r]).reshape(k // 256, 292)
+        d[r] = blk[:, :4].copy().view(np.float32).ravel()
+        qs[r] = blk[:, 4:260].copy().view(np.int8).ravel()
+        bs[r] = blk[:, 260:292].copy().view(np.int16).ravel()
+    return qs, d, bs
+
+
+@pytest.mark.parametrize("rows,kind", [(1, 2), (3, 2), (8, 3), (7, 4), (16, 4)])
+def test_rms_norm_and_silu_leave_q8_K_activations(g, rows, kind):
+    m = b200.load()
+    rng = np.random.default_rng(rows * 10 + kind)
+    m4 = 0 if kind == 2 else rows if kind == 3 else rows - rows % 4
+    x = activations(rng, (rows, 1024))
+    w = (1.0 + 0.1 * rng.standard_normal(1024)).astype(np.float32)
+    y, yw, (qs, d, bs) = g.rms_norm_q8(x, 1e-5, w, kind)
+    want = orc_glue.mul(orc_glue.rms_norm(x, 1e-5), w[None, :])
+    assert bits_equal(y, orc_glue.rms_norm(x, 1e-5)) and bits_equal(yw, want)
+    wq, wd, wb = q8_K_parts(want, m4)
+    assert np.array_equal(qs, wq) and bits_equal(d, wd) and np.array_equal(bs, wb)
+    gate = activations(rng, (rows, 1024))
+    wide = bool(m.lib.b200_host_silu_is_wide())
+    s, sg, (qs, d, bs) = g.silu_q8(x, gate, wide, kind)
+    want = orc_glue.mul(orc_glue.silu(x, wide=wide), gate)
+    assert bits_equal(sg, want)
+    wq, wd, wb = q8_K_parts(want, m4)
+    assert np.array_equal(qs, wq) and bits_equal(d, wd) and np.array_equal(bs, wb)
