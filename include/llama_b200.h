@@ -45,6 +45,24 @@ int b200_llama_new(const struct b200_llama_hparams *hp, int device, int32_t n_ct
                    b200_llama **out);
 void b200_llama_free(b200_llama *ctx);
 
+/* ---- tensor parallelism across the GPUs of one node (one process per GPU) ------------------------------
+ * The reference has no multi-device path; this is the row-split of BASELINE's 70B configuration: attn_q/k/v,
+ * ffn_gate/up and output by rows (whole heads, FFN rows, vocabulary rows), attn_output and ffn_down by K with
+ * an NCCL all-reduce of the partial sums, norms and token_embd replicated, logits all-gathered.
+ *
+ * b200_tp_unique_id: rank 0 fills 128 bytes (an ncclUniqueId) that the host passes to every rank.
+ * b200_llama_new_tp: as b200_llama_new, for rank tp_rank of tp_size (n_head_kv, n_ff and n_vocab must divide).
+ *   b200_llama_set_tensor then takes the WHOLE tensor on every rank and keeps this rank's shard.
+ * b200_tp_shard_shape / b200_tp_shard_tensor: the cut itself, on host memory (split: 0 replicated, 1 rows,
+ *   2 K), for hosts that shard while loading and for tests. */
+int b200_tp_unique_id(void *id128);
+int b200_llama_new_tp(const struct b200_llama_hparams *hp, int device, int32_t n_ctx, int32_t n_batch, int32_t cpu_threads,
+                      int32_t tp_rank, int32_t tp_size, const void *id128, b200_llama **out);
+int b200_tp_shard_shape(const char *name, int type, int64_t ne0, int64_t ne1, int32_t tp_size, int32_t *split, int64_t *ne0_local,
+                        int64_t *ne1_local);
+int b200_tp_shard_tensor(const char *name, int type, int64_t ne0, int64_t ne1, const void *data, int32_t tp_rank, int32_t tp_size,
+                         void *out, size_t out_nbytes);
+
 /* One model tensor under its GGUF name (crates/llama/src/model.rs: token_embd.weight, output_norm.weight,
  * output.weight, blk.N.{attn_norm,attn_q,attn_k,attn_v,attn_output,ffn_norm,ffn_gate,ffn_up,ffn_down}.weight).
  * data: ggml blocks of `type`, ne1 rows of ne0 elements, in host memory.  output.weight may be left out

@@ -122,7 +122,7 @@ struct BackendCtx {
 };
 constexpr size_t SHADOW_MAX_BYTES = 1 << 20;
 constexpr int64_t ROPE_TABLE_MIN_ROWS = 4096, ROPE_TABLE_MAX_ROWS = 1 << 20;
-constexpr size_t ROPE_TABLES_KEPT = 4, GRAPHS_KEPT = 16;
+constexpr size_t ROPE_TABLES_KEPT = 4, GRAPHS_KEPT = 512;   // a tensor-parallel step is ~2 node lists per layer
 
 static std::mutex g_mu;
 static std::vector<ggml_backend_device *> g_devices;
@@ -894,7 +894,7 @@ static int backend_graph_compute(ggml_backend_t be, ggml_cgraph *g) {
             if (rc != B200_STATUS_SUCCESS) return rc;
         }
     }
-    if (!bc->graphs_enabled || !bc->capturable || g->n_nodes < 16) return run_nodes(bc, g);
+    if (!bc->graphs_enabled || !bc->capturable || g->n_nodes < 6) return run_nodes(bc, g);
 
     const uint64_t key = node_list_key(bc, g);
     const unsigned long long sgen = scratch_generation();

@@ -47,9 +47,20 @@ struct Graph {
     ggml_tensor *tokens = nullptr, *pos = nullptr, *mask = nullptr, *row_idx = nullptr, *out_ids = nullptr;
     ggml_tensor *logits = nullptr, *argmax = nullptr;
     size_t bytes = 0;                     // compute-buffer bytes the graph spans
+    // tensor parallel: after node index `after` (exclusive end of a segment) the ranks all-reduce t in place
+    // (gather == nullptr) or all-gather t into gather
+    struct Collective { int after; ggml_tensor *t; ggml_tensor *gather; };
+    std::vector<Collective> collectives;
 };
 
 }  // namespace
+
+namespace b200 {
+int tp_comm_init(int rank, int size, const void *id128, void **comm);
+void tp_comm_destroy(void *comm);
+int tp_all_reduce_sum(void *comm, float *buf, size_t count, void *stream);
+int tp_all_gather(void *comm, const float *send, float *recv, size_t count_per_rank, void *stream);
+}  // namespace b200
 
 struct b200_llama {
     b200_llama_hparams hp;
@@ -67,6 +78,11 @@ struct b200_llama {
     Graph *last = nullptr;
     std::vector<uint16_t> mask_host;
     std::vector<int64_t> idx_host;
+    // tensor parallel: this rank holds n_head / tp_size heads, n_head_kv / tp_size cache heads, the matching
+    // rows / columns of every matrix (tp.cpp) and 1 / tp_size of the vocabulary rows
+    int32_t tp_rank = 0, tp_size = 1;
+    void *comm = nullptr;
+    std::vector<uint8_t> shard_tmp;
 };
 
 namespace {
@@ -207,8 +223,10 @@ ggml_tensor *weight(b200_llama *c, const std::string &name) {
 // build_ffn_silu_par (:1128-1158).  base == nullptr only measures.
 int build_graph(b200_llama *c, Graph *g, uint8_t *base, int64_t n, int64_t n_kv) {
     const b200_llama_hparams &hp = c->hp;
-    const int64_t E = hp.n_embd, HD = hp.n_embd_head, H = hp.n_head, HK = hp.n_head_kv, EK = HK * HD;
+    const int64_t E = hp.n_embd, HD = hp.n_embd_head, H = hp.n_head / c->tp_size, HK = hp.n_head_kv / c->tp_size, EK = HK * HD;
+    const bool tp = c->tp_size > 1;
     Builder b{c, g, base};
+    g->collectives.clear();
     g->tokens = b.alloc(B200_TYPE_I32, n, 1, 1, "inp_tokens");
     g->pos = b.alloc(B200_TYPE_I32, n, 1, 1, "inp_pos");
     g->mask = b.alloc(B200_TYPE_F16, n_kv, n, 1, "kq_mask");
@@ -250,11 +268,13 @@ int build_graph(b200_llama *c, Graph *g, uint8_t *base, int64_t n, int64_t n_kv)
         ggml_tensor *fa = b.op(b.alloc(B200_TYPE_F32, HD, H, n, "kqv_out"), GGML_OP_FLASH_ATTN_EXT, q_fa, k_fa, v_fa, g->mask);
         memcpy(&fa->op_params[0], &kq_scale, 4);
         ggml_tensor *attn = b.mul_mat(wo, b.reshape_2d(fa, HD * H, n), "attn_out");
+        if (tp) g->collectives.push_back({(int)g->nodes.size(), attn, nullptr});   // partial sums over this rank's heads
         ggml_tensor *ffn_inp = b.binary(GGML_OP_ADD, attn, inp, "ffn_inp");
         cur = b.norm(ffn_inp, fn, hp.norm_rms_eps, "ffn_norm");
         ggml_tensor *gate = b.silu(b.mul_mat(wg, cur, "ffn_gate"));
         ggml_tensor *up = b.mul_mat(wu, cur, "ffn_up");
         ggml_tensor *down = b.mul_mat(wd, b.binary(GGML_OP_MUL, gate, up, "ffn_gate_par"), "ffn_out");
+        if (tp) g->collectives.push_back({(int)g->nodes.size(), down, nullptr});   // partial sums over this rank's FFN rows
         inp = b.op(b.over(resid[(il + 1) & 1], "l_out"), GGML_OP_ADD, down, ffn_inp);
     }
     b.off = layer_base;
@@ -265,6 +285,11 @@ int build_graph(b200_llama *c, Graph *g, uint8_t *base, int64_t n, int64_t n_kv)
     ggml_tensor *cur = b.norm(inp, on, hp.norm_rms_eps, "result_norm");
     cur = b.get_rows(cur, g->out_ids, "result_norm_rows");   // crates/llama/src/graph.rs:308-313 out_rows
     g->logits = b.mul_mat(ow, cur, "result_output");
+    if (tp && ow != tok_embd) {   // this rank's vocabulary rows: gather the full row on every rank
+        ggml_tensor *full = b.alloc(B200_TYPE_F32, ow->ne[1] * c->tp_size, 1, 1, "result_output_all");
+        g->collectives.push_back({(int)g->nodes.size(), g->logits, full});
+        g->logits = full;
+    }
     g->argmax = b.op(b.alloc(B200_TYPE_I32, 1, 1, 1, "argmax"), GGML_OP_ARGMAX, g->logits);
     g->bytes = b.high;
     return B200_STATUS_SUCCESS;
@@ -278,13 +303,48 @@ int64_t n_kv_for(const b200_llama *c, int32_t used) {
 
 void set_input(ggml_tensor *t, const void *data, size_t bytes) { t->buffer->iface.set_tensor(t->buffer, t, data, 0, bytes); }
 
+// graph_compute over the first `total` nodes, cut where the ranks of a tensor-parallel group exchange data
+int run_graph(b200_llama *c, Graph *g, int total) {
+    int start = 0;
+    auto compute = [&](int end) -> int {
+        if (end <= start) return B200_STATUS_SUCCESS;
+        ggml_cgraph cg;
+        memset(&cg, 0, sizeof(cg));
+        cg.size = cg.n_nodes = end - start;
+        cg.nodes = g->nodes.data() + start;
+        start = end;
+        return c->backend->iface.graph_compute(c->backend, &cg);
+    };
+    for (const Graph::Collective &col : g->collectives) {
+        if (col.after > total) break;
+        int rc = compute(col.after);
+        if (rc != B200_STATUS_SUCCESS) return rc;
+        const size_t count = (size_t)(col.t->nb[3] / 4);
+        rc = col.gather ? tp_all_gather(c->comm, (const float *)col.t->data, (float *)col.gather->data, count, c->stream)
+                        : tp_all_reduce_sum(c->comm, (float *)col.t->data, count, c->stream);
+        if (rc != B200_STATUS_SUCCESS) return rc;
+    }
+    return compute(total);
+}
+
 }  // namespace
 
 extern "C" {
 
 int b200_llama_new(const b200_llama_hparams *hp, int device, int32_t n_ctx, int32_t n_batch, int32_t cpu_threads, b200_llama **out) {
+    return b200_llama_new_tp(hp, device, n_ctx, n_batch, cpu_threads, 0, 1, nullptr, out);
+}
+
+int b200_llama_new_tp(const b200_llama_hparams *hp, int device, int32_t n_ctx, int32_t n_batch, int32_t cpu_threads, int32_t tp_rank,
+                      int32_t tp_size, const void *id128, b200_llama **out) {
     B200_REQUIRE(hp != nullptr && out != nullptr, "llama_new: null argument");
     *out = nullptr;
+    B200_REQUIRE(tp_size >= 1 && tp_rank >= 0 && tp_rank < tp_size, "llama_new: rank %d of %d", tp_rank, tp_size);
+    B200_REQUIRE(tp_size == 1 || id128 != nullptr, "llama_new: a tensor-parallel group needs the shared id");
+    B200_REQUIRE(hp->n_head % tp_size == 0 && hp->n_head_kv % tp_size == 0, "llama_new: %d / %d heads do not split %d ways", hp->n_head,
+                 hp->n_head_kv, tp_size);
+    B200_REQUIRE((hp->n_head / tp_size * hp->n_embd_head) % GROUP_K == 0 && (hp->n_ff / tp_size) % GROUP_K == 0 && hp->n_ff % tp_size == 0,
+                 "llama_new: a rank's share of the heads and of n_ff must be multiples of 256 elements");
     B200_REQUIRE(hp->n_vocab > 0 && hp->n_embd > 0 && hp->n_head > 0 && hp->n_head_kv > 0 && hp->n_layer > 0 && hp->n_ff > 0,
                  "llama_new: non-positive model dimension");
     B200_REQUIRE(hp->n_head % hp->n_head_kv == 0, "llama_new: n_head %d is not a multiple of n_head_kv %d", hp->n_head, hp->n_head_kv);
@@ -303,6 +363,8 @@ int b200_llama_new(const b200_llama_hparams *hp, int device, int32_t n_ctx, int3
     c->n_ctx = n_ctx;
     c->n_batch = n_batch;
     c->dev = dev;
+    c->tp_rank = tp_rank;
+    c->tp_size = tp_size;
     const std::string params = "cpu_threads=" + std::to_string(cpu_threads > 0 ? cpu_threads : 8);
     c->backend = dev->iface.init_backend(dev, params.c_str());
     if (!c->backend) return B200_STATUS_BACKEND_ERROR;
@@ -312,7 +374,7 @@ int b200_llama_new(const b200_llama_hparams *hp, int device, int32_t n_ctx, int3
     c->stream = get_stream ? get_stream(c->backend) : nullptr;
 
     // KV cache: per layer K and V, [n_embd_k_gqa, n_ctx] F16, zero-filled
-    const int64_t EK = (int64_t)hp->n_head_kv * hp->n_embd_head;
+    const int64_t EK = (int64_t)hp->n_head_kv / tp_size * hp->n_embd_head;
     const size_t per = ((size_t)EK * 2 * n_ctx + ALIGN - 1) / ALIGN * ALIGN;
     c->kv_buf = c->buft->iface.alloc_buffer(c->buft, per * 2 * hp->n_layer);
     if (!c->kv_buf) { b200_llama_free(c.release()); return B200_STATUS_ALLOC_FAILED; }
@@ -330,6 +392,11 @@ int b200_llama_new(const b200_llama_hparams *hp, int device, int32_t n_ctx, int3
         }
     }
     c->cell_pos.assign(n_ctx, -1);
+    if (tp_size > 1) {
+        B200_CUDA(cudaSetDevice(device));
+        int rc = tp_comm_init(tp_rank, tp_size, id128, &c->comm);
+        if (rc != B200_STATUS_SUCCESS) { b200_llama_free(c.release()); return rc; }
+    }
     *out = c.release();
     return B200_STATUS_SUCCESS;
 }
@@ -343,6 +410,7 @@ void b200_llama_free(b200_llama *c) {
     for (auto &kv : c->weights)
         if (kv.second->buf) kv.second->buf->iface.free_buffer(kv.second->buf);
     if (c->backend) c->backend->iface.free(c->backend);
+    if (c->comm) tp_comm_destroy(c->comm);
     delete c;
 }
 
@@ -355,6 +423,20 @@ int b200_llama_set_tensor(b200_llama *c, const char *name, int type, int64_t ne0
     std::unique_ptr<Weight> w(new Weight());
     init_tensor(&w->t, type, ne0, ne1);
     B200_REQUIRE(nbytes == w->t.nb[2], "llama_set_tensor: %s: %zu bytes given, %zu expected", name, nbytes, w->t.nb[2]);
+    if (c->tp_size > 1) {   // keep this rank's shard of the whole tensor
+        int32_t split = 0;
+        int64_t l0 = 0, l1 = 0;
+        int rc = b200_tp_shard_shape(name, type, ne0, ne1, c->tp_size, &split, &l0, &l1);
+        if (rc != B200_STATUS_SUCCESS) return rc;
+        if (split != 0) {
+            init_tensor(&w->t, type, l0, l1);
+            c->shard_tmp.resize(w->t.nb[2]);
+            rc = b200_tp_shard_tensor(name, type, ne0, ne1, data, c->tp_rank, c->tp_size, c->shard_tmp.data(), c->shard_tmp.size());
+            if (rc != B200_STATUS_SUCCESS) return rc;
+            data = c->shard_tmp.data();
+            nbytes = c->shard_tmp.size();
+        }
+    }
     snprintf(w->t.name, sizeof(w->t.name), "%s", name);
     w->buf = c->buft->iface.alloc_buffer(c->buft, c->buft->iface.get_alloc_size(c->buft, &w->t));
     if (!w->buf) return B200_STATUS_ALLOC_FAILED;
@@ -435,11 +517,7 @@ int b200_llama_decode(b200_llama *c, const int32_t *tokens, const int32_t *pos, 
     set_input(g->row_idx, c->idx_host.data(), (size_t)n * 8);
     set_input(g->out_ids, &out_id, 4);
 
-    ggml_cgraph cg;
-    memset(&cg, 0, sizeof(cg));
-    cg.size = cg.n_nodes = (int)g->nodes.size() - (argmax ? 0 : 1);   // the ARGMAX node is last
-    cg.nodes = g->nodes.data();
-    int rc = c->backend->iface.graph_compute(c->backend, &cg);
+    int rc = run_graph(c, g, (int)g->nodes.size() - (argmax ? 0 : 1));   // the ARGMAX node is last
     if (rc != B200_STATUS_SUCCESS) return rc;
     c->last = g;
     if (logits) c->backend->iface.get_tensor_async(c->backend, g->logits, logits, 0, (size_t)c->hp.n_vocab * 4);
@@ -469,15 +547,11 @@ int b200_llama_replay(b200_llama *c, int32_t reps, float *ms) {
     B200_REQUIRE(c != nullptr && ms != nullptr && reps > 0, "llama_replay: bad argument");
     B200_REQUIRE(c->last != nullptr, "llama_replay: no decode call to replay");
     Graph *g = c->last;
-    ggml_cgraph cg;
-    memset(&cg, 0, sizeof(cg));
-    cg.size = cg.n_nodes = (int)g->nodes.size() - 1;
-    cg.nodes = g->nodes.data();
     void *e0 = nullptr, *e1 = nullptr;
     int rc = b200_event_create(&e0);
     if (rc == B200_STATUS_SUCCESS) rc = b200_event_create(&e1);
     if (rc == B200_STATUS_SUCCESS) rc = b200_event_record(e0, c->stream);
-    for (int i = 0; i < reps && rc == B200_STATUS_SUCCESS; i++) rc = c->backend->iface.graph_compute(c->backend, &cg);
+    for (int i = 0; i < reps && rc == B200_STATUS_SUCCESS; i++) rc = run_graph(c, g, (int)g->nodes.size() - 1);
     if (rc == B200_STATUS_SUCCESS) rc = b200_event_record(e1, c->stream);
     if (rc == B200_STATUS_SUCCESS) rc = b200_event_synchronize(e1);
     if (rc == B200_STATUS_SUCCESS) rc = b200_event_elapsed_ms(e0, e1, ms);

@@ -24,6 +24,10 @@ lib.b200_llama_kv_clear.argtypes = [vp]
 lib.b200_llama_kv_used.argtypes = [vp]
 lib.b200_llama_kv_used.restype = i32
 lib.b200_llama_replay.argtypes = [vp, i32, C.POINTER(C.c_float)]
+lib.b200_llama_new_tp.argtypes = [C.POINTER(HParams), i32, i32, i32, i32, i32, i32, vp, C.POINTER(vp)]
+lib.b200_tp_unique_id.argtypes = [vp]
+lib.b200_tp_shard_shape.argtypes = [C.c_char_p, i32, i64, i64, i32, C.POINTER(i32), C.POINTER(i64), C.POINTER(i64)]
+lib.b200_tp_shard_tensor.argtypes = [C.c_char_p, i32, i64, i64, vp, i32, i32, vp, sz]
 
 # Llama-3-8B (BASELINE configuration of the tokens/s metric)
 LLAMA3_8B = dict(n_vocab=128256, n_embd=4096, n_head=32, n_head_kv=8, n_embd_head=128, n_ff=14336, n_layer=32,
@@ -61,12 +65,41 @@ def tensor_shapes(hp):
     return shapes
 
 
+def tp_unique_id():
+    """128 bytes (an ncclUniqueId) made on one rank, to be handed to every rank of a tensor-parallel group"""
+    buf = (C.c_uint8 * 128)()
+    check(lib.b200_tp_unique_id(buf), "tp_unique_id")
+    return bytes(buf)
+
+
+def tp_shard_shape(name, ty, ne0, ne1, tp_size):
+    """-> (split, ne0_local, ne1_local); split: 0 replicated, 1 rows, 2 K"""
+    split, l0, l1 = i32(0), i64(0), i64(0)
+    check(lib.b200_tp_shard_shape(name.encode(), ty, ne0, ne1, tp_size, C.byref(split), C.byref(l0), C.byref(l1)), f"tp_shard_shape {name}")
+    return split.value, l0.value, l1.value
+
+
+def tp_shard_tensor(name, ty, blocks, ne0, ne1, tp_rank, tp_size):
+    """this rank's shard of a whole tensor, as a uint8 array"""
+    blocks = np.ascontiguousarray(blocks)
+    _, l0, l1 = tp_shard_shape(name, ty, ne0, ne1, tp_size)
+    out = np.empty(blocks.nbytes // (ne0 * ne1) * (l0 * l1) if blocks.nbytes % (ne0 * ne1) == 0 else blocks.nbytes * l0 * l1 // (ne0 * ne1),
+                   dtype=np.uint8)
+    check(lib.b200_tp_shard_tensor(name.encode(), ty, ne0, ne1, blocks.ctypes.data, tp_rank, tp_size, out.ctypes.data, out.nbytes),
+          f"tp_shard_tensor {name}")
+    return out
+
+
 class Llama:
-    def __init__(self, hp, n_ctx, n_batch, device=0, cpu_threads=8):
+    def __init__(self, hp, n_ctx, n_batch, device=0, cpu_threads=8, tp_rank=0, tp_size=1, tp_id=None):
         self.hp = dict(hp)
         h = HParams(**self.hp)
         p = vp()
-        check(lib.b200_llama_new(C.byref(h), device, n_ctx, n_batch, cpu_threads, C.byref(p)), "llama_new")
+        if tp_size > 1:
+            idbuf = (C.c_uint8 * 128).from_buffer_copy(tp_id)
+            check(lib.b200_llama_new_tp(C.byref(h), device, n_ctx, n_batch, cpu_threads, tp_rank, tp_size, idbuf, C.byref(p)), "llama_new_tp")
+        else:
+            check(lib.b200_llama_new(C.byref(h), device, n_ctx, n_batch, cpu_threads, C.byref(p)), "llama_new")
         self.ptr = p.value
 
     def set_tensor(self, name, ty, blocks, ne0, ne1):
