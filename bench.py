@@ -65,6 +65,17 @@ def load_oracle():
     return orc, orc_glue
 
 
+def host_threads(orc):
+    """all host cores: torch.distributed.run exports OMP_NUM_THREADS=1 to its workers, which is not what the
+    CPU arm should run with (the oracle's entry points take the thread count and set it themselves)"""
+    return max(orc.lib().orc_num_threads(), len(os.sched_getaffinity(0)))
+
+
+def note(msg):
+    """progress on stderr, so that a run that stops short shows where"""
+    print(f"[bench {time.strftime('%H:%M:%S')}] {msg}", file=sys.stderr, flush=True)
+
+
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples while the timed region runs."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -127,7 +138,12 @@ def dist_setup(n_gpus):
     dev = torch.device("cuda", local) if backend == "nccl" else torch.device("cpu")
 
     def barrier():
-        dist.barrier()
+        # name the device: the CUDA library switches the process's current device as it works, and a barrier that
+        # guessed another device would try to build a second communicator there and wait for peers that never come
+        if backend == "nccl":
+            dist.barrier(device_ids=[local])
+        else:
+            dist.barrier()
 
     def reduce_max(v):
         t = torch.tensor([float(v)], dtype=torch.float64, device=dev)
@@ -170,7 +186,7 @@ def cpu_gemv_step(orc, reps_w, x_list, outs, threads):
 
 
 def cpu_gemv_baseline(orc, seconds=10.0):
-    threads = orc.lib().orc_num_threads()
+    threads = host_threads(orc)
     total = sum(algorithmic_bytes(n, k) for n, k in SHAPES)
     reps_w, xs, outs = cpu_gemv_prepare(orc)
     cpu_gemv_step(orc, reps_w, xs, outs, threads)
@@ -293,10 +309,10 @@ def llama_weight_bytes(ll, hp):
     return total
 
 
-def build_llama(n_layer, n_ctx=1024, n_batch=PROMPT, keep_host=False):
+def build_llama(n_layer, n_ctx=1024, n_batch=PROMPT, keep_host=False, device=0):
     ll, hp = llama_hparams(n_layer)
     syn = importlib.import_module("llama_rust_b200.synth")
-    gpu = ll.Llama(hp, n_ctx, n_batch, cpu_threads=8)
+    gpu = ll.Llama(hp, n_ctx, n_batch, device=device, cpu_threads=8)
     host = {}
     for name, ty, arr, ne0, ne1 in syn.llama_tensors(hp, lambda n: ll.q4_k_m_type(n, n_layer)):
         gpu.set_tensor(name, ty, arr, ne0, ne1)
@@ -307,11 +323,10 @@ def build_llama(n_layer, n_ctx=1024, n_batch=PROMPT, keep_host=False):
 
 def run_llama(b, args, rank, world, barrier, reduce_max):
     """pp512 + tg128, batch 1, one replica per rank"""
-    ll, hp, gpu, _ = build_llama(args.layers)
+    ll, hp, gpu, _ = build_llama(args.layers, device=int(os.environ.get("LOCAL_RANK", "0")))
     rng = np.random.default_rng(0)
     prompt = rng.integers(0, hp["n_vocab"], PROMPT).astype(np.int32)
     pos = np.arange(PROMPT, dtype=np.int32)
-    launches = 0
 
     def one_pass():
         gpu.kv_clear()
@@ -356,6 +371,61 @@ def run_llama(b, args, rank, world, barrier, reduce_max):
     return out
 
 
+def run_llama_tp(b, args, rank, world, local, barrier, reduce_max, shape):
+    """The same pp512 + tg128, one model split row-wise over all ranks (NCCL all-reduce after attn_output and
+    ffn_down, all-gather of the logits): tokens/s of the group, strong scaling.  Each rank makes its own
+    random shard, already cut."""
+    import torch
+    import torch.distributed as dist
+    ll = importlib.import_module("llama_rust_b200.llama")
+    syn = importlib.import_module("llama_rust_b200.synth")
+    hp = dict(ll.LLAMA3_70B if shape == "70b" else ll.LLAMA3_8B)
+    if args.layers != 32:   # a shortened model for a quick check of the multi-rank path
+        hp["n_layer"] = args.layers
+    ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
+    if rank == 0:
+        ident = torch.tensor(list(ll.tp_unique_id()), dtype=torch.uint8, device="cuda")
+    dist.broadcast(ident, 0)
+    gpu = ll.Llama(hp, 1024, PROMPT, device=local, cpu_threads=8, tp_rank=rank, tp_size=world, tp_id=bytes(ident.cpu().tolist()))
+    rng = np.random.default_rng(1000 + rank)
+    for i, (name, (ne0, ne1)) in enumerate(ll.tensor_shapes(hp).items()):
+        ty = ll.q4_k_m_type(name, hp["n_layer"])
+        _, l0, l1 = ll.tp_shard_shape(name, ty, ne0, ne1, world)
+        if ty == 0:
+            gpu.set_tensor_shard(name, ty, (1.0 + 0.1 * rng.standard_normal(l0)).astype(np.float32), l0, l1)
+        else:
+            gpu.set_tensor_shard(name, ty, syn.blocks(ty, l1, l0, seed=7919 * rank + i), l0, l1)
+    prompt = np.random.default_rng(0).integers(0, hp["n_vocab"], PROMPT).astype(np.int32)
+    pos = np.arange(PROMPT, dtype=np.int32)
+
+    def one_pass():
+        gpu.kv_clear()
+        barrier()
+        t0 = time.perf_counter()
+        tok = gpu.decode(prompt, pos, logits=False, argmax=True)
+        t1 = time.perf_counter()
+        pp_dev = gpu.replay(1)
+        barrier()
+        t2 = time.perf_counter()
+        for i in range(GEN):
+            tok = gpu.decode([tok], [PROMPT + i], logits=False, argmax=True)
+        t3 = time.perf_counter()
+        tg_dev = gpu.replay(GEN) / GEN
+        return t1 - t0, pp_dev * 1e-3, (t3 - t2) / GEN, tg_dev * 1e-3
+
+    for _ in range(3):
+        one_pass()
+    res = [one_pass() for _ in range(3)]
+    barrier()
+    pp_e2e, pp_dev, tg_e2e, tg_dev = (reduce_max(statistics.median(r[k] for r in res)) for k in range(4))
+    gpu.close()
+    return {"tp": world, "scaling": "strong", "shape": shape,
+            "config": {"workload": f"Llama-3-{shape.upper()} shape, Q4_K_M tensor types, row-split over {world} GPUs, batch 1: "
+                                   "512-token prompt then 128 greedy steps", "weights": "seeded random well-formed blocks, one shard per rank"},
+            "pp512_tok_s": PROMPT / pp_dev, "pp512_e2e_tok_s": PROMPT / pp_e2e, "tg128_tok_s": 1.0 / tg_dev, "tg128_e2e_tok_s": 1.0 / tg_e2e,
+            "pp512_ms": pp_dev * 1e3, "tg128_ms_per_token": tg_dev * 1e3}
+
+
 def cpu_llama_baseline(orc, orc_glue, n_layer, prompt_tokens=16, gen_tokens=4):
     """The CPU restatement's Llama forward on the same shape: a prompt batch and a few single-token steps.
     Weights are interleaved once, outside the timed region, as the reference does at load."""
@@ -366,7 +436,7 @@ def cpu_llama_baseline(orc, orc_glue, n_layer, prompt_tokens=16, gen_tokens=4):
     ohp = dict(n_vocab=hp["n_vocab"], n_embd=hp["n_embd"], n_head=hp["n_head"], n_head_kv=hp["n_head_kv"],
                head_dim=hp["n_embd_head"], n_ff=hp["n_ff"], n_layer=n_layer, rope_mode=0, n_ctx_orig=hp["n_ctx_train"],
                norm_eps=hp["norm_rms_eps"], freq_base=hp["rope_freq_base"], freq_scale=1.0)
-    threads = orc.lib().orc_num_threads()
+    threads = host_threads(orc)
     cpu = orc_glue.Llama(ohp, tensors, 256)
     rng = np.random.default_rng(0)
 
@@ -400,7 +470,7 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     orc, orc_glue = load_oracle()
-    threads = orc.lib().orc_num_threads()
+    threads = host_threads(orc)
     reps, xs, outs = cpu_gemv_prepare(orc)
     total = sum(algorithmic_bytes(n, k) for n, k in SHAPES)
     for _ in range(args.warmup):
@@ -433,10 +503,20 @@ def run_b200(args, rank, world, barrier, reduce_max):
         raise SystemExit("bench.py: no CUDA device; the CUDA library is the only compute path")
     local = int(os.environ.get("LOCAL_RANK", "0"))
     b.set_device(local)
+    note(f"rank {rank}: decode mat-mul")
     g = run_gemv(b, args, rank, world, barrier, reduce_max, local)
     llama = None
     if not args.no_llama:
+        note(f"rank {rank}: llama 8b replica")
         llama = run_llama(b, args, rank, world, barrier, reduce_max)
+    tp_runs = {}
+    if world > 1 and not args.no_llama:
+        for shape in ("8b", "70b"):
+            note(f"rank {rank}: llama {shape} tensor parallel x{world}")
+            try:
+                tp_runs[f"llama_{shape}_tp"] = run_llama_tp(b, args, rank, world, local, barrier, reduce_max, shape)
+            except Exception as exc:   # a shape that does not split this many ways, or no room: reported, not fatal
+                tp_runs[f"llama_{shape}_tp"] = {"tp": world, "unavailable": f"{type(exc).__name__}: {exc}"}
     if rank != 0:
         return
     line = {
@@ -447,7 +527,12 @@ def run_b200(args, rank, world, barrier, reduce_max):
     }
     if llama is not None:
         line["llama_8b"] = llama
+    line.update(tp_runs)
+    if world > 1:   # the CPU baseline is a single-GPU extra
+        print(json.dumps(line), flush=True)
+        return
     # CPU baselines on the host cores: the same workloads through the CPU routes, bounded samples
+    note("cpu baselines")
     try:
         orc, orc_glue = load_oracle()
         line["cpu_baseline"] = cpu_gemv_baseline(orc)

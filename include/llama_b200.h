@@ -62,6 +62,8 @@ int b200_tp_shard_shape(const char *name, int type, int64_t ne0, int64_t ne1, in
                         int64_t *ne1_local);
 int b200_tp_shard_tensor(const char *name, int type, int64_t ne0, int64_t ne1, const void *data, int32_t tp_rank, int32_t tp_size,
                          void *out, size_t out_nbytes);
+/* b200_llama_set_tensor for a rank that cut the tensor itself: data is this rank's shard, ne0 / ne1 its local shape. */
+int b200_llama_set_tensor_shard(b200_llama *ctx, const char *name, int type, int64_t ne0, int64_t ne1, const void *data, size_t nbytes);
 
 /* One model tensor under its GGUF name (crates/llama/src/model.rs: token_embd.weight, output_norm.weight,
  * output.weight, blk.N.{attn_norm,attn_q,attn_k,attn_v,attn_output,ffn_norm,ffn_gate,ffn_up,ffn_down}.weight).

@@ -414,7 +414,16 @@ void b200_llama_free(b200_llama *c) {
     delete c;
 }
 
+static int set_tensor_impl(b200_llama *c, const char *name, int type, int64_t ne0, int64_t ne1, const void *data, size_t nbytes, bool whole);
+
 int b200_llama_set_tensor(b200_llama *c, const char *name, int type, int64_t ne0, int64_t ne1, const void *data, size_t nbytes) {
+    return set_tensor_impl(c, name, type, ne0, ne1, data, nbytes, true);
+}
+int b200_llama_set_tensor_shard(b200_llama *c, const char *name, int type, int64_t ne0, int64_t ne1, const void *data, size_t nbytes) {
+    return set_tensor_impl(c, name, type, ne0, ne1, data, nbytes, false);
+}
+
+static int set_tensor_impl(b200_llama *c, const char *name, int type, int64_t ne0, int64_t ne1, const void *data, size_t nbytes, bool whole) {
     B200_REQUIRE(c != nullptr && name != nullptr && data != nullptr, "llama_set_tensor: null argument");
     B200_REQUIRE(ne0 > 0 && ne1 > 0, "llama_set_tensor: %s has an empty shape", name);
     const bool quant = is_quant_type(type);
@@ -423,7 +432,7 @@ int b200_llama_set_tensor(b200_llama *c, const char *name, int type, int64_t ne0
     std::unique_ptr<Weight> w(new Weight());
     init_tensor(&w->t, type, ne0, ne1);
     B200_REQUIRE(nbytes == w->t.nb[2], "llama_set_tensor: %s: %zu bytes given, %zu expected", name, nbytes, w->t.nb[2]);
-    if (c->tp_size > 1) {   // keep this rank's shard of the whole tensor
+    if (c->tp_size > 1 && whole) {   // keep this rank's shard of the whole tensor
         int32_t split = 0;
         int64_t l0 = 0, l1 = 0;
         int rc = b200_tp_shard_shape(name, type, ne0, ne1, c->tp_size, &split, &l0, &l1);

@@ -19,6 +19,7 @@ lib.b200_llama_new.argtypes = [C.POINTER(HParams), i32, i32, i32, i32, C.POINTER
 lib.b200_llama_free.argtypes = [vp]
 lib.b200_llama_free.restype = None
 lib.b200_llama_set_tensor.argtypes = [vp, C.c_char_p, i32, i64, i64, vp, sz]
+lib.b200_llama_set_tensor_shard.argtypes = [vp, C.c_char_p, i32, i64, i64, vp, sz]
 lib.b200_llama_decode.argtypes = [vp, vp, vp, i32, vp, vp]
 lib.b200_llama_kv_clear.argtypes = [vp]
 lib.b200_llama_kv_used.argtypes = [vp]
@@ -28,6 +29,10 @@ lib.b200_llama_new_tp.argtypes = [C.POINTER(HParams), i32, i32, i32, i32, i32, i
 lib.b200_tp_unique_id.argtypes = [vp]
 lib.b200_tp_shard_shape.argtypes = [C.c_char_p, i32, i64, i64, i32, C.POINTER(i32), C.POINTER(i64), C.POINTER(i64)]
 lib.b200_tp_shard_tensor.argtypes = [C.c_char_p, i32, i64, i64, vp, i32, i32, vp, sz]
+
+# Llama-3-70B shape (BASELINE's tensor-parallel configuration)
+LLAMA3_70B = dict(n_vocab=128256, n_embd=8192, n_head=64, n_head_kv=8, n_embd_head=128, n_ff=28672, n_layer=80,
+                  n_ctx_train=8192, rope_mode=0, norm_rms_eps=1e-5, rope_freq_base=500000.0, rope_freq_scale=1.0)
 
 # Llama-3-8B (BASELINE configuration of the tokens/s metric)
 LLAMA3_8B = dict(n_vocab=128256, n_embd=4096, n_head=32, n_head_kv=8, n_embd_head=128, n_ff=14336, n_layer=32,
@@ -83,8 +88,7 @@ def tp_shard_tensor(name, ty, blocks, ne0, ne1, tp_rank, tp_size):
     """this rank's shard of a whole tensor, as a uint8 array"""
     blocks = np.ascontiguousarray(blocks)
     _, l0, l1 = tp_shard_shape(name, ty, ne0, ne1, tp_size)
-    out = np.empty(blocks.nbytes // (ne0 * ne1) * (l0 * l1) if blocks.nbytes % (ne0 * ne1) == 0 else blocks.nbytes * l0 * l1 // (ne0 * ne1),
-                   dtype=np.uint8)
+    out = np.empty(blocks.nbytes * (l0 * l1) // (ne0 * ne1), dtype=np.uint8)
     check(lib.b200_tp_shard_tensor(name.encode(), ty, ne0, ne1, blocks.ctypes.data, tp_rank, tp_size, out.ctypes.data, out.nbytes),
           f"tp_shard_tensor {name}")
     return out
@@ -105,6 +109,12 @@ class Llama:
     def set_tensor(self, name, ty, blocks, ne0, ne1):
         blocks = np.ascontiguousarray(blocks)
         check(lib.b200_llama_set_tensor(self.ptr, name.encode(), ty, ne0, ne1, blocks.ctypes.data, blocks.nbytes), f"set_tensor {name}")
+
+    def set_tensor_shard(self, name, ty, blocks, ne0_local, ne1_local):
+        """a tensor-parallel rank's own shard, already cut (tp_shard_shape gives the local shape)"""
+        blocks = np.ascontiguousarray(blocks)
+        check(lib.b200_llama_set_tensor_shard(self.ptr, name.encode(), ty, ne0_local, ne1_local, blocks.ctypes.data, blocks.nbytes),
+              f"set_tensor_shard {name}")
 
     def decode(self, tokens, pos, logits=True, argmax=False):
         tokens = np.ascontiguousarray(tokens, dtype=np.int32)

@@ -1,5 +1,7 @@
 """Row-split tensor parallelism on real GPUs (needs at least two): a small Llama split over 2 GPUs gives
-the single-GPU logits within 1e-5 of their largest magnitude and the same greedy tokens on every rank."""
+the single-GPU logits to within the activation-quantization noise (the partial sums of a K-split are added in
+another order, and a last-bit difference can flip a Q8 rounding in the next layer; the per-op 1e-5 bound of the
+split itself is checked on the CPU in test_tp_sharding.py) and the same token on every rank."""
 import os
 import subprocess
 import sys
