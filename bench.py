@@ -321,9 +321,44 @@ def build_llama(n_layer, n_ctx=1024, n_batch=PROMPT, keep_host=False, device=0):
     return ll, hp, gpu, host
 
 
+N_SEQ = 16
+
+
+def run_llama_batch16(gpu, hp, world, barrier, reduce_max):
+    """16 parallel sequences in the unified cache: 16 prompts of 512 tokens (one sequence per call), then 128
+    steps of one token per sequence; tokens/s over all sequences, end to end through the driver call"""
+    rng = np.random.default_rng(1)
+    prompts = rng.integers(0, hp["n_vocab"], (N_SEQ, PROMPT)).astype(np.int32)
+    pos = np.arange(PROMPT, dtype=np.int32)
+    seqs = np.arange(N_SEQ, dtype=np.int32)
+
+    def one_pass():
+        gpu.kv_clear()
+        nxt = np.zeros(N_SEQ, dtype=np.int32)
+        t0 = time.perf_counter()
+        for s in range(N_SEQ):
+            _, am = gpu.decode_seqs(prompts[s], pos, np.full(PROMPT, s, dtype=np.int32), [PROMPT - 1], logits=False, argmax=True)
+            nxt[s] = am[0]
+        t1 = time.perf_counter()
+        for i in range(GEN):
+            _, am = gpu.decode_seqs(nxt, np.full(N_SEQ, PROMPT + i, dtype=np.int32), seqs, seqs, logits=False, argmax=True)
+            nxt = am.astype(np.int32)
+        t2 = time.perf_counter()
+        return t1 - t0, (t2 - t1) / GEN, gpu.replay(8) / 8 * 1e-3
+
+    one_pass()
+    barrier()
+    res = [one_pass() for _ in range(2)]
+    barrier()
+    pp, tg, tg_dev = (reduce_max(min(r[k] for r in res)) for k in range(3))
+    return {"sequences": N_SEQ, "pp512_e2e_tok_s": world * N_SEQ * PROMPT / pp, "tg128_e2e_tok_s": world * N_SEQ / tg,
+            "tg128_tok_s": world * N_SEQ / tg_dev, "tg128_ms_per_step": tg_dev * 1e3,
+            "cache": f"unified, {N_SEQ * (PROMPT + GEN)} cells in use at the end; a step's attention spans every cell and masks the other sequences'"}
+
+
 def run_llama(b, args, rank, world, barrier, reduce_max):
     """pp512 + tg128, batch 1, one replica per rank"""
-    ll, hp, gpu, _ = build_llama(args.layers, device=int(os.environ.get("LOCAL_RANK", "0")))
+    ll, hp, gpu, _ = build_llama(args.layers, n_ctx=N_SEQ * (PROMPT + GEN), device=int(os.environ.get("LOCAL_RANK", "0")))
     rng = np.random.default_rng(0)
     prompt = rng.integers(0, hp["n_vocab"], PROMPT).astype(np.int32)
     pos = np.arange(PROMPT, dtype=np.int32)
@@ -367,6 +402,7 @@ def run_llama(b, args, rank, world, barrier, reduce_max):
                      "unit": "GB/s", "frac": wbytes / tg_dev / 1e9 / peak},
         "greedy_tokens_head": [int(t) for t in res[-1][4][:8]],
     }
+    out["batch16"] = run_llama_batch16(gpu, hp, world, barrier, reduce_max)
     gpu.close()
     return out
 

@@ -77,6 +77,15 @@ int b200_llama_set_tensor(b200_llama *ctx, const char *name, int type, int64_t n
  * (last index among equals, crates/ggml/src/compute.rs:4208-4228). */
 int b200_llama_decode(b200_llama *ctx, const int32_t *tokens, const int32_t *pos, int32_t n_tokens, float *logits, int32_t *argmax);
 
+/* The batched form: tokens of several sequences in one step (one token each while generating, or one
+ * sequence's prompt).  seq_ids[i] names token i's sequence (null = all 0); the cache is the reference's
+ * unified one: every token takes the next free cell, a query sees the cells of its own sequence at positions
+ * up to its own (llama-kv-cache's mask rule as ported in crates/llama/src/graph.rs:592-724).  out_rows: the
+ * n_out batch rows whose logits are wanted (crates/llama/src/graph.rs:308-313 out_rows); logits receives
+ * n_out rows of n_vocab floats, argmax n_out indices. */
+int b200_llama_decode_seqs(b200_llama *ctx, const int32_t *tokens, const int32_t *pos, const int32_t *seq_ids, int32_t n_tokens,
+                           const int32_t *out_rows, int32_t n_out, float *logits, int32_t *argmax);
+
 /* Forget every cached position (DecodeContext::kv_clear). */
 int b200_llama_kv_clear(b200_llama *ctx);
 /* Cells in use, and the padded cell count the next step's attention would span. */

@@ -82,6 +82,11 @@ fa_scores_kernel(b200_flash_attn_args a, FaDims d, float kq_scale, float *__rest
             const int r = r0 + rr;
             const int t = r / group, h = hkv * group + r % group;
             const float *q = q_s + rr * DK;
+            // a position the mask hides scores -inf whatever the dot is (the CPU skips it before the dot too)
+            if (a.mask && __half2float(((const __half *)((const uint8_t *)a.mask + (int64_t)t * a.mask_nb1))[p]) == -INFINITY) {
+                scores[((int64_t)t * d.H + h) * d.n_kv + p] = -INFINITY;
+                continue;
+            }
             float val[16];
 #pragma unroll
             for (int l = 0; l < 16; l++) {
@@ -166,6 +171,10 @@ fa_rows_kernel(b200_flash_attn_args a, FaDims d, const float *__restrict__ score
     __syncthreads();
     for (int64_t p0 = ic0; p0 < ic1; p0 += FA_TILE) {
         const int np = ic1 - p0 < FA_TILE ? (int)(ic1 - p0) : FA_TILE;
+        float s = -INFINITY;
+        if (tid < FA_TILE && tid < np) s = srow[p0 + tid];
+        // a tile without a live position (another sequence's cells in a shared cache) changes nothing: skip it whole
+        if (!__syncthreads_or(s != -INFINITY)) continue;
         // stage the V tile: np rows of dv halves, 16 bytes per load
         const int chunks_per_row = d.dv / 8;
         for (int i = tid; i < np * chunks_per_row; i += blockDim.x) {
@@ -174,8 +183,6 @@ fa_rows_kernel(b200_flash_attn_args a, FaDims d, const float *__restrict__ score
             *(uint4 *)(v_s + pr * d.dv + cc * 8) = v;
         }
         // exclusive prefix maximum of the tile's scores (threads 0..127 = positions)
-        float s = -INFINITY;
-        if (tid < FA_TILE && tid < np) s = srow[p0 + tid];
         float incl = s;
         if (tid < FA_TILE) {
 #pragma unroll

@@ -73,6 +73,7 @@ struct b200_llama {
     ggml_backend_buffer_t kv_buf = nullptr, compute_buf = nullptr;
     std::vector<ggml_tensor> k_l, v_l;    // [n_embd_k_gqa, n_ctx] F16 per layer
     std::vector<int32_t> cell_pos;        // position held by each cache cell, -1 = empty
+    std::vector<int32_t> cell_seq;        // the sequence the cell belongs to
     int32_t used = 0;
     std::map<std::pair<int64_t, int64_t>, std::unique_ptr<Graph>> graphs;   // by (n_tokens, n_kv)
     Graph *last = nullptr;
@@ -221,7 +222,7 @@ ggml_tensor *weight(b200_llama *c, const std::string &name) {
 
 // crates/llama/src/graph_arch.rs:106-248 with attn_kv_cached's flash-attention branch (:1173-1240) and
 // build_ffn_silu_par (:1128-1158).  base == nullptr only measures.
-int build_graph(b200_llama *c, Graph *g, uint8_t *base, int64_t n, int64_t n_kv) {
+int build_graph(b200_llama *c, Graph *g, uint8_t *base, int64_t n, int64_t n_kv, int64_t n_out) {
     const b200_llama_hparams &hp = c->hp;
     const int64_t E = hp.n_embd, HD = hp.n_embd_head, H = hp.n_head / c->tp_size, HK = hp.n_head_kv / c->tp_size, EK = HK * HD;
     const bool tp = c->tp_size > 1;
@@ -231,7 +232,7 @@ int build_graph(b200_llama *c, Graph *g, uint8_t *base, int64_t n, int64_t n_kv)
     g->pos = b.alloc(B200_TYPE_I32, n, 1, 1, "inp_pos");
     g->mask = b.alloc(B200_TYPE_F16, n_kv, n, 1, "kq_mask");
     g->row_idx = b.alloc(B200_TYPE_I64, n, 1, 1, "kv_idxs");
-    g->out_ids = b.alloc(B200_TYPE_I32, 1, 1, 1, "inp_out_ids");
+    g->out_ids = b.alloc(B200_TYPE_I32, n_out, 1, 1, "inp_out_ids");
     ggml_tensor *resid[2] = {b.alloc(B200_TYPE_F32, E, n, 1, "resid_a"), b.alloc(B200_TYPE_F32, E, n, 1, "resid_b")};
 
     ggml_tensor *tok_embd = weight(c, "token_embd.weight");
@@ -286,11 +287,11 @@ int build_graph(b200_llama *c, Graph *g, uint8_t *base, int64_t n, int64_t n_kv)
     cur = b.get_rows(cur, g->out_ids, "result_norm_rows");   // crates/llama/src/graph.rs:308-313 out_rows
     g->logits = b.mul_mat(ow, cur, "result_output");
     if (tp && ow != tok_embd) {   // this rank's vocabulary rows: gather the full row on every rank
-        ggml_tensor *full = b.alloc(B200_TYPE_F32, ow->ne[1] * c->tp_size, 1, 1, "result_output_all");
+        ggml_tensor *full = b.alloc(B200_TYPE_F32, ow->ne[1] * c->tp_size, n_out, 1, "result_output_all");
         g->collectives.push_back({(int)g->nodes.size(), g->logits, full});
         g->logits = full;
     }
-    g->argmax = b.op(b.alloc(B200_TYPE_I32, 1, 1, 1, "argmax"), GGML_OP_ARGMAX, g->logits);
+    g->argmax = b.op(b.alloc(B200_TYPE_I32, n_out, 1, 1, "argmax"), GGML_OP_ARGMAX, g->logits);
     g->bytes = b.high;
     return B200_STATUS_SUCCESS;
 }
@@ -319,9 +320,13 @@ int run_graph(b200_llama *c, Graph *g, int total) {
         if (col.after > total) break;
         int rc = compute(col.after);
         if (rc != B200_STATUS_SUCCESS) return rc;
-        const size_t count = (size_t)(col.t->nb[3] / 4);
-        rc = col.gather ? tp_all_gather(c->comm, (const float *)col.t->data, (float *)col.gather->data, count, c->stream)
-                        : tp_all_reduce_sum(c->comm, (float *)col.t->data, count, c->stream);
+        if (col.gather) {   // row by row: every rank's slice of a row lands side by side, which is the whole row
+            for (int64_t r = 0; r < col.t->ne[1] && rc == B200_STATUS_SUCCESS; r++)
+                rc = tp_all_gather(c->comm, (const float *)col.t->data + r * col.t->ne[0], (float *)col.gather->data + r * col.gather->ne[0],
+                                   (size_t)col.t->ne[0], c->stream);
+        } else {
+            rc = tp_all_reduce_sum(c->comm, (float *)col.t->data, (size_t)(col.t->nb[3] / 4), c->stream);
+        }
         if (rc != B200_STATUS_SUCCESS) return rc;
     }
     return compute(total);
@@ -343,8 +348,6 @@ int b200_llama_new_tp(const b200_llama_hparams *hp, int device, int32_t n_ctx, i
     B200_REQUIRE(tp_size == 1 || id128 != nullptr, "llama_new: a tensor-parallel group needs the shared id");
     B200_REQUIRE(hp->n_head % tp_size == 0 && hp->n_head_kv % tp_size == 0, "llama_new: %d / %d heads do not split %d ways", hp->n_head,
                  hp->n_head_kv, tp_size);
-    B200_REQUIRE((hp->n_head / tp_size * hp->n_embd_head) % GROUP_K == 0 && (hp->n_ff / tp_size) % GROUP_K == 0 && hp->n_ff % tp_size == 0,
-                 "llama_new: a rank's share of the heads and of n_ff must be multiples of 256 elements");
     B200_REQUIRE(hp->n_vocab > 0 && hp->n_embd > 0 && hp->n_head > 0 && hp->n_head_kv > 0 && hp->n_layer > 0 && hp->n_ff > 0,
                  "llama_new: non-positive model dimension");
     B200_REQUIRE(hp->n_head % hp->n_head_kv == 0, "llama_new: n_head %d is not a multiple of n_head_kv %d", hp->n_head, hp->n_head_kv);
@@ -352,6 +355,8 @@ int b200_llama_new_tp(const b200_llama_hparams *hp, int device, int32_t n_ctx, i
     B200_REQUIRE(hp->n_embd % GROUP_K == 0 && hp->n_ff % GROUP_K == 0 && (hp->n_head * hp->n_embd_head) % GROUP_K == 0,
                  "llama_new: n_embd, n_ff and n_head * head size must be multiples of 256");
     B200_REQUIRE(hp->rope_mode == 0 || hp->rope_mode == 2, "llama_new: rope mode %d is neither NORMAL (0) nor NEOX (2)", hp->rope_mode);
+    B200_REQUIRE((hp->n_head / tp_size * hp->n_embd_head) % GROUP_K == 0 && (hp->n_ff / tp_size) % GROUP_K == 0 && hp->n_ff % tp_size == 0,
+                 "llama_new: a rank's share of the heads and of n_ff must be multiples of 256 elements");
     B200_REQUIRE(n_ctx > 0 && n_ctx % KV_PAD == 0, "llama_new: n_ctx %d must be a positive multiple of 256", n_ctx);
     B200_REQUIRE(n_batch > 0 && n_batch <= n_ctx, "llama_new: n_batch %d out of (0, n_ctx]", n_batch);
     ggml_backend_reg_t reg = ggml_backend_init();
@@ -392,6 +397,7 @@ int b200_llama_new_tp(const b200_llama_hparams *hp, int device, int32_t n_ctx, i
         }
     }
     c->cell_pos.assign(n_ctx, -1);
+    c->cell_seq.assign(n_ctx, -1);
     if (tp_size > 1) {
         B200_CUDA(cudaSetDevice(device));
         int rc = tp_comm_init(tp_rank, tp_size, id128, &c->comm);
@@ -470,6 +476,7 @@ int b200_llama_kv_clear(b200_llama *c) {
     c->backend->iface.synchronize(c->backend);
     c->kv_buf->iface.clear(c->kv_buf, 0);
     std::fill(c->cell_pos.begin(), c->cell_pos.end(), -1);
+    std::fill(c->cell_seq.begin(), c->cell_seq.end(), -1);
     c->used = 0;
     return B200_STATUS_SUCCESS;
 }
@@ -477,46 +484,60 @@ int b200_llama_kv_clear(b200_llama *c) {
 int32_t b200_llama_kv_used(const b200_llama *c) { return c ? c->used : 0; }
 
 int b200_llama_decode(b200_llama *c, const int32_t *tokens, const int32_t *pos, int32_t n, float *logits, int32_t *argmax) {
-    B200_REQUIRE(c != nullptr && tokens != nullptr && pos != nullptr, "llama_decode: null argument");
+    B200_REQUIRE(n > 0, "llama_decode: batch size %d out of (0, %d]", n, c ? c->n_batch : 0);
+    const int32_t last = n - 1;
+    return b200_llama_decode_seqs(c, tokens, pos, nullptr, n, &last, 1, logits, argmax);
+}
+
+int b200_llama_decode_seqs(b200_llama *c, const int32_t *tokens, const int32_t *pos, const int32_t *seq_ids, int32_t n,
+                           const int32_t *out_rows, int32_t n_out, float *logits, int32_t *argmax) {
+    B200_REQUIRE(c != nullptr && tokens != nullptr && pos != nullptr && out_rows != nullptr, "llama_decode: null argument");
     B200_REQUIRE(n > 0 && n <= c->n_batch, "llama_decode: batch size %d out of (0, %d]", n, c->n_batch);
+    B200_REQUIRE(n_out > 0 && n_out <= n, "llama_decode: %d output rows for %d tokens", n_out, n);
     B200_REQUIRE(c->used + n <= c->n_ctx, "llama_decode: kv cache full (%d used + %d > %d)", c->used, n, c->n_ctx);
     for (int i = 0; i < n; i++)
         B200_REQUIRE(tokens[i] >= 0 && tokens[i] < c->hp.n_vocab, "llama_decode: token %d out of range", tokens[i]);
+    for (int i = 0; i < n_out; i++) B200_REQUIRE(out_rows[i] >= 0 && out_rows[i] < n, "llama_decode: output row %d out of range", out_rows[i]);
 
-    // find_slot + assign for one sequence: the next free cells, in order
+    // find_slot + assign: the next free cells, in order; a cell remembers its sequence and position
     const int32_t head = c->used;
     const int64_t n_kv = n_kv_for(c, head + n);
 
-    // the graph for this (n, n_kv), sized and built once
-    auto key = std::make_pair((int64_t)n, n_kv);
+    // the graph for this (n, n_kv, n_out), sized and built once
+    auto key = std::make_pair((int64_t)n * 65536 + n_out, n_kv);
     auto it = c->graphs.find(key);
     if (it == c->graphs.end()) {
         if (!c->compute_buf) {
             Graph measure;
-            int rc = build_graph(c, &measure, nullptr, c->n_batch, c->n_ctx);
+            int rc = build_graph(c, &measure, nullptr, c->n_batch, c->n_ctx, c->n_batch);
             if (rc != B200_STATUS_SUCCESS) return rc;
             c->compute_buf = c->buft->iface.alloc_buffer(c->buft, measure.bytes + ALIGN);
             if (!c->compute_buf) return B200_STATUS_ALLOC_FAILED;
             c->compute_buf->usage = GGML_BACKEND_BUFFER_USAGE_COMPUTE;
         }
         std::unique_ptr<Graph> g(new Graph());
-        int rc = build_graph(c, g.get(), (uint8_t *)c->compute_buf->iface.get_base(c->compute_buf), n, n_kv);
+        int rc = build_graph(c, g.get(), (uint8_t *)c->compute_buf->iface.get_base(c->compute_buf), n, n_kv, n_out);
         if (rc != B200_STATUS_SUCCESS) return rc;
         B200_REQUIRE(g->bytes <= c->compute_buf->size, "llama_decode: graph needs %zu bytes, compute buffer has %zu", g->bytes, c->compute_buf->size);
         it = c->graphs.emplace(key, std::move(g)).first;
     }
     Graph *g = it->second.get();
 
-    for (int i = 0; i < n; i++) c->cell_pos[head + i] = pos[i];
+    for (int i = 0; i < n; i++) {
+        c->cell_pos[head + i] = pos[i];
+        c->cell_seq[head + i] = seq_ids ? seq_ids[i] : 0;
+    }
     c->used = head + n;
-    // crates/llama/src/graph.rs:704-724 fill_kq_mask_f16: 0 where the cell holds a position <= the query's, -inf elsewhere
+    // crates/llama/src/graph.rs:704-724 fill_kq_mask_f16 with the sequence test of llama-kv-cache's set_input_kq_mask:
+    // 0 where the cell belongs to the query's sequence and holds a position <= the query's, -inf elsewhere
     c->mask_host.assign((size_t)n * n_kv, 0xFC00);
-    for (int i = 0; i < n; i++)
+    for (int i = 0; i < n; i++) {
+        const int32_t s = seq_ids ? seq_ids[i] : 0;
         for (int64_t j = 0; j < c->used; j++)
-            if (c->cell_pos[j] >= 0 && c->cell_pos[j] <= pos[i]) c->mask_host[(size_t)i * n_kv + j] = 0;
+            if (c->cell_seq[j] == s && c->cell_pos[j] >= 0 && c->cell_pos[j] <= pos[i]) c->mask_host[(size_t)i * n_kv + j] = 0;
+    }
     c->idx_host.resize(n);
     for (int i = 0; i < n; i++) c->idx_host[i] = head + i;
-    const int32_t out_id = n - 1;
 
     // inputs land with synchronous copies after the previous step has drained
     c->backend->iface.synchronize(c->backend);
@@ -524,13 +545,13 @@ int b200_llama_decode(b200_llama *c, const int32_t *tokens, const int32_t *pos, 
     set_input(g->pos, pos, (size_t)n * 4);
     set_input(g->mask, c->mask_host.data(), c->mask_host.size() * 2);
     set_input(g->row_idx, c->idx_host.data(), (size_t)n * 8);
-    set_input(g->out_ids, &out_id, 4);
+    set_input(g->out_ids, out_rows, (size_t)n_out * 4);
 
     int rc = run_graph(c, g, (int)g->nodes.size() - (argmax ? 0 : 1));   // the ARGMAX node is last
     if (rc != B200_STATUS_SUCCESS) return rc;
     c->last = g;
-    if (logits) c->backend->iface.get_tensor_async(c->backend, g->logits, logits, 0, (size_t)c->hp.n_vocab * 4);
-    if (argmax) c->backend->iface.get_tensor_async(c->backend, g->argmax, argmax, 0, 4);
+    if (logits) c->backend->iface.get_tensor_async(c->backend, g->logits, logits, 0, (size_t)c->hp.n_vocab * n_out * 4);
+    if (argmax) c->backend->iface.get_tensor_async(c->backend, g->argmax, argmax, 0, (size_t)n_out * 4);
     c->backend->iface.synchronize(c->backend);
     int code = 0;
     rc = b200_kernel_error(&code);

@@ -21,6 +21,7 @@ lib.b200_llama_free.restype = None
 lib.b200_llama_set_tensor.argtypes = [vp, C.c_char_p, i32, i64, i64, vp, sz]
 lib.b200_llama_set_tensor_shard.argtypes = [vp, C.c_char_p, i32, i64, i64, vp, sz]
 lib.b200_llama_decode.argtypes = [vp, vp, vp, i32, vp, vp]
+lib.b200_llama_decode_seqs.argtypes = [vp, vp, vp, vp, i32, vp, i32, vp, vp]
 lib.b200_llama_kv_clear.argtypes = [vp]
 lib.b200_llama_kv_used.argtypes = [vp]
 lib.b200_llama_kv_used.restype = i32
@@ -126,6 +127,19 @@ class Llama:
         if logits and argmax:
             return out, am.value
         return out if logits else (am.value if argmax else None)
+
+    def decode_seqs(self, tokens, pos, seq_ids, out_rows, logits=True, argmax=False):
+        """several sequences in one step -> (logits [n_out, n_vocab] or None, argmax [n_out] or None)"""
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        pos = np.ascontiguousarray(pos, dtype=np.int32)
+        seq_ids = np.ascontiguousarray(seq_ids, dtype=np.int32)
+        out_rows = np.ascontiguousarray(out_rows, dtype=np.int32)
+        out = np.empty((out_rows.size, self.hp["n_vocab"]), dtype=np.float32) if logits else None
+        am = np.empty(out_rows.size, dtype=np.int32) if argmax else None
+        check(lib.b200_llama_decode_seqs(self.ptr, tokens.ctypes.data, pos.ctypes.data, seq_ids.ctypes.data, tokens.size,
+                                         out_rows.ctypes.data, out_rows.size, out.ctypes.data if logits else None,
+                                         am.ctypes.data if argmax else None), "llama_decode_seqs")
+        return out, am
 
     def kv_clear(self):
         check(lib.b200_llama_kv_clear(self.ptr), "kv_clear")
