@@ -65,6 +65,16 @@ int b200_tp_shard_tensor(const char *name, int type, int64_t ne0, int64_t ne1, c
 /* b200_llama_set_tensor for a rank that cut the tensor itself: data is this rank's shard, ne0 / ne1 its local shape. */
 int b200_llama_set_tensor_shard(b200_llama *ctx, const char *name, int type, int64_t ne0, int64_t ne1, const void *data, size_t nbytes);
 
+/* A llama-architecture GGUF file straight into a driver (Gguf::open + LlamaHparams::from_gguf + the tensor
+ * loop of crates/llama/src/model.rs): reads general.architecture, llama.block_count, embedding_length,
+ * feed_forward_length, attention.head_count(_kv), attention.key_length, attention.layer_norm_rms_epsilon,
+ * rope.freq_base, context_length, takes n_vocab from token_embd.weight, and sets every tensor.  The _tp form
+ * loads rank tp_rank's shards.  b200_llama_get_hparams reports what a driver was built with. */
+int b200_llama_load_gguf(const char *path, int device, int32_t n_ctx, int32_t n_batch, int32_t cpu_threads, b200_llama **out);
+int b200_llama_load_gguf_tp(const char *path, int device, int32_t n_ctx, int32_t n_batch, int32_t cpu_threads, int32_t tp_rank,
+                            int32_t tp_size, const void *id128, b200_llama **out);
+int b200_llama_get_hparams(const b200_llama *ctx, struct b200_llama_hparams *out);
+
 /* One model tensor under its GGUF name (crates/llama/src/model.rs: token_embd.weight, output_norm.weight,
  * output.weight, blk.N.{attn_norm,attn_q,attn_k,attn_v,attn_output,ffn_norm,ffn_gate,ffn_up,ffn_down}.weight).
  * data: ggml blocks of `type`, ne1 rows of ne0 elements, in host memory.  output.weight may be left out

@@ -483,6 +483,12 @@ int b200_llama_kv_clear(b200_llama *c) {
 
 int32_t b200_llama_kv_used(const b200_llama *c) { return c ? c->used : 0; }
 
+int b200_llama_get_hparams(const b200_llama *c, b200_llama_hparams *out) {
+    B200_REQUIRE(c != nullptr && out != nullptr, "llama_get_hparams: null argument");
+    *out = c->hp;
+    return B200_STATUS_SUCCESS;
+}
+
 int b200_llama_decode(b200_llama *c, const int32_t *tokens, const int32_t *pos, int32_t n, float *logits, int32_t *argmax) {
     B200_REQUIRE(n > 0, "llama_decode: batch size %d out of (0, %d]", n, c ? c->n_batch : 0);
     const int32_t last = n - 1;

@@ -125,6 +125,10 @@ def main():
     dest = Path(__file__).parent / "glue_nodes.npz"
     np.savez_compressed(dest, **out)
     print(count, dest, dest.stat().st_size)
+    # the reference GGUF writer's golden file (parity/ref_gguf_write.c), taken as it is: 416 bytes
+    gguf = Path(__file__).parent / "gguf_write_ref.bin"
+    gguf.write_bytes((ref / "parity" / "gguf_write_ref.bin").read_bytes())
+    print(gguf, gguf.stat().st_size)
 
 
 if __name__ == "__main__":

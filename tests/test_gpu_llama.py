@@ -148,3 +148,20 @@ def test_argument_errors_are_statuses(ll):
     bad = dict(SMALL, n_embd_head=80)
     with pytest.raises(m.B200Error, match="head size"):
         ll.Llama(bad, 256, 4)
+
+
+def test_gguf_file_loads_into_the_driver(ll, tmp_path):
+    """a model written as a GGUF file and loaded by b200_llama_load_gguf answers like the same tensors set by hand"""
+    gg = importlib.import_module("llama_rust_b200.gguf")
+    tensors = make_model(ll, SMALL, 21)
+    path = tmp_path / "small.gguf"
+    gg.write_llama(path, SMALL, [(n, ty, arr, ne0, ne1) for n, (ty, arr, ne0, ne1) in tensors.items()])
+    by_hand, _ = both(ll, SMALL, tensors, 256, 8)
+    from_file = gg.load_llama(path, 256, 8, cpu_threads=THREADS)
+    assert from_file.hp["n_layer"] == SMALL["n_layer"] and from_file.hp["n_vocab"] == SMALL["n_vocab"]
+    assert from_file.hp["n_head_kv"] == SMALL["n_head_kv"] and from_file.hp["n_embd_head"] == SMALL["n_embd_head"]
+    toks, pos = [3, 1, 4, 1, 5], [0, 1, 2, 3, 4]
+    assert bits_equal(from_file.decode(toks, pos), by_hand.decode(toks, pos))
+    assert bits_equal(from_file.decode([9], [5]), by_hand.decode([9], [5]))
+    by_hand.close()
+    from_file.close()
