@@ -134,6 +134,8 @@ int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint
 
 int launch_gemm_mma(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
                     cudaStream_t s);
+int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
+                        cudaStream_t s);
 int launch_gemv_q4_K_stream(int64_t n, int64_t k, const uint8_t *tiles, ActView acts, float *dst, cudaStream_t s);
 int gemv_stream_error(int *code);
 int device_error_word(int **flag);

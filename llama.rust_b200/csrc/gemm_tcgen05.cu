@@ -1,0 +1,340 @@
+// Prompt-shaped Q4_K mat-mul on the fifth-generation tensor cores: tcgen05.mma kind::i8 with the
+// sub-block dots accumulated in tensor memory, fed from shared memory by producer warps that unpack the
+// 4-bit weights to int8 on the way in, and drained by epilogue warps that run the CPU route's f32 chain.
+//
+// Arithmetic (identical to gemm_mma.cu, which computes the same dots with mma.sync): the CPU routes never add
+// two sub-blocks' integer dots before scaling them, so one MMA (M 128 weight rows x N 32 activation rows x
+// K 32) computes exactly one 32-element sub-block's dots, with the accumulator cleared, into its own 32
+// tensor-memory columns; eight MMAs cover a 256-element super-block and fill one 256-column stage.  The
+// epilogue thread that owns a weight row reads its dots back (tcgen05.ld), applies the 6-bit sub-block
+// scales in integer arithmetic and feeds
+//   8x8 gemm route (crates/ggml/src/repack.rs:1692-1768), per sub-block pair g:
+//         sumf = fma(f32(ig[g]), d*d_x, sumf); summin = fma(f32(mg[g]), dmin*d_x, summin); out = sumf - summin
+//   tiled route    (crates/ggml/src/tiled.rs:823-838), per super-block:
+//         r = d*f32(s1); r = fma(-dmin, f32(s2), r); out = fma(r, d_x, out)
+// so the result is bit-identical to the decode kernels' and to the CPU's.
+//
+// One CTA = 128 weight rows (four 32-row tiles of the device layout) x 32 activation rows, walking K one
+// super-block per pipeline step:
+//   warps 0-7   epilogue: warp w owns tensor-memory lanes 32 (w % 4) .. + 31 (weight rows) and activation
+//               rows 16 (w / 4) .. + 15; 8 warps keep two chains per scheduler in flight
+//   warps 8-11  producers: nibbles -> int8 into the A operand, int8 activation blocks into the B operand
+//               (both K-major, no swizzle: 8 rows x 16 bytes core matrices, K-adjacent ones 128 bytes apart,
+//               8-row groups 2048 bytes apart), pair sums of the activation bsums and the activation scales
+//   warp 12     tensor-memory allocation and, one lane, the MMA issue + commits
+// Shared memory holds three operand stages, tensor memory two accumulator stages; all hand-offs are
+// mbarriers.  Every wait is bounded: a wait that runs out raises the CTA's abort flag and the device error
+// word, every role leaves its loop, and the CTA frees its tensor memory and returns.
+#include "common.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int TC_ROWS = 128;                 // weight rows per CTA (MMA M)
+constexpr int TC_COLS = 32;                  // activation rows per CTA (MMA N)
+constexpr int TC_EPI_WARPS = 8, TC_PROD_WARPS = 4;
+constexpr int TC_THREADS = (TC_EPI_WARPS + TC_PROD_WARPS + 1) * 32;
+constexpr int TC_STAGES = 3;                 // shared-memory operand stages
+constexpr int TC_TSTAGES = 2;                // tensor-memory accumulator stages of 8 * TC_COLS columns
+constexpr int TC_A_BYTES = TC_ROWS * 256;    // one super-block of int8 weights
+constexpr int TC_B_BYTES = TC_COLS * 256;
+constexpr int TC_BP_BYTES = 4 * TC_COLS * 8; // [pair][column] (sum of low sub-block, sum of high sub-block)
+constexpr int TC_DA_BYTES = TC_COLS * 4;
+constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES + TC_BP_BYTES + TC_DA_BYTES;
+constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024;
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 20;
+constexpr int TC_ERR_WAIT = 4;               // device error word: a pipeline wait ran out
+
+// kind::i8 instruction descriptor: s32 accumulator, s8 x s8, both operands K-major, N = 32, M = 128
+constexpr uint32_t TC_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_COLS >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// shared-memory matrix descriptor, no swizzle: start address, 128 bytes between K-adjacent core matrices
+// (leading byte offset), 2048 bytes between 8-row groups (stride byte offset), descriptor version 1
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)(128 >> 4) << 16) | ((uint64_t)(2048 >> 4) << 32) | (1ull << 46);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(bar) : "memory");
+}
+// bounded wait for the phase of the given parity to complete; false when the CTA is giving up
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t it = 0; it < TC_WAIT_LIMIT; it++) {
+        uint32_t ok;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(ok)
+                     : "r"(bar), "r"(parity)
+                     : "memory");
+        if (ok) return true;
+        if ((it & 63) == 63) {
+            if (*abort_flag) return false;
+            __nanosleep(64);
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tmem_ld16(int (&v)[16], uint32_t taddr) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+                   "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                 : "r"(taddr)
+                 : "memory");
+}
+
+struct TcBars {
+    uint64_t full[TC_STAGES], empty[TC_STAGES], tfull[TC_TSTAGES], tempty[TC_TSTAGES];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+}  // namespace
+
+// MODE 1: 8x8 gemm chain, MODE 2: tiled chain (see the file comment)
+template <int MODE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_q4_K_tcgen05_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *dst, int64_t lddst, int64_t n, int nb, int64_t m, int *err) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ TcBars bars;
+    pdl_trigger();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t tile0 = (int64_t)blockIdx.y * (TC_ROWS / TILE_ROWS);   // first 32-row weight tile of this CTA
+    const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
+    const int64_t col0 = (int64_t)blockIdx.x * TC_COLS;
+    const int64_t K = acts.k;
+    volatile int *abort_flag = &bars.abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < TC_STAGES; i++) {
+            mbar_init(smem_u32(&bars.full[i]), TC_PROD_WARPS);
+            mbar_init(smem_u32(&bars.empty[i]), 1 + TC_EPI_WARPS);
+        }
+        for (int i = 0; i < TC_TSTAGES; i++) {
+            mbar_init(smem_u32(&bars.tfull[i]), 1);
+            mbar_init(smem_u32(&bars.tempty[i]), TC_EPI_WARPS);
+        }
+        bars.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == TC_EPI_WARPS + TC_PROD_WARPS) {
+        // all 512 columns: the CTA's shared memory already keeps a second CTA off this SM
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars.tmem_base)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = bars.tmem_base;
+    pdl_wait();
+
+    if (warp < TC_EPI_WARPS) {
+        // ---- epilogue: the f32 chains of weight row 32 q + lane over 16 activation rows ----
+        const int q = warp & 3, h = warp >> 2;
+        const int64_t tile = tile0 + q;
+        const bool row_ok = tile < tiles_n;
+        const bool any_col = col0 + 16 * h < m;
+        const uint8_t *hdr = tiles + (row_ok ? tile : 0) * (int64_t)nb * 4608 + lane * 16;
+        float sumf[16], summin[16];
+#pragma unroll
+        for (int c = 0; c < 16; c++) sumf[c] = summin[c] = 0.0f;
+        for (int b = 0; b < nb; b++) {
+            const int s = b % TC_STAGES, t = b % TC_TSTAGES;
+            const uint32_t sph = (uint32_t)(b / TC_STAGES) & 1u, tph = (uint32_t)(b / TC_TSTAGES) & 1u;
+            uint4 hd = make_uint4(0, 0, 0, 0);
+            if (row_ok) hd = *(const uint4 *)(hdr + (int64_t)b * 4608);
+            // the whole warp goes on or gives up together: tcgen05.ld below wants it converged
+            const bool ready = mbar_wait(smem_u32(&bars.full[s]), sph, abort_flag) && mbar_wait(smem_u32(&bars.tfull[t]), tph, abort_flag);
+            if (!__all_sync(0xffffffffu, ready)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint8_t *stage = smem + s * TC_STAGE_BYTES;
+            const int2 *bp = (const int2 *)(stage + TC_A_BYTES + TC_B_BYTES);             // [pair][column]
+            const float *da = (const float *)(stage + TC_A_BYTES + TC_B_BYTES + TC_BP_BYTES);
+            // 6-bit scales and mins, one per byte (crates/ggml/src/quants.rs:421-429)
+            uint32_t sc[2], mn[2];
+            sc[0] = hd.y & 0x3f3f3f3fu;
+            mn[0] = hd.z & 0x3f3f3f3fu;
+            sc[1] = (hd.w & 0x0f0f0f0fu) | (((hd.y >> 6) & 0x03030303u) << 4);
+            mn[1] = ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4);
+            const float dw = f16_bits_to_f32((uint16_t)(hd.x & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(hd.x >> 16));
+            int s1[16], s2[16];
+            if (MODE == 2) {
+#pragma unroll
+                for (int c = 0; c < 16; c++) s1[c] = s2[c] = 0;
+            }
+            const uint32_t trow = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(t * 8 * TC_COLS + 16 * h);
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+                int d0[16], d1[16];
+                tmem_ld16(d0, trow + (uint32_t)((2 * g) * TC_COLS));
+                tmem_ld16(d1, trow + (uint32_t)((2 * g + 1) * TC_COLS));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (g == 3) {
+                    // the accumulator stage is free again once every epilogue warp has read it
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bars.tempty[t]));
+                }
+                if (any_col) {
+                    const int sh = 16 * (g & 1);
+                    const int s_lo = (sc[g >> 1] >> sh) & 0xff, s_hi = (sc[g >> 1] >> (sh + 8)) & 0xff;
+                    const int m_lo = (mn[g >> 1] >> sh) & 0xff, m_hi = (mn[g >> 1] >> (sh + 8)) & 0xff;
+#pragma unroll
+                    for (int c = 0; c < 16; c++) {
+                        const int2 bs = bp[g * TC_COLS + 16 * h + c];
+                        const int ig = d0[c] * s_lo + d1[c] * s_hi;
+                        const int mg = m_lo * bs.x + m_hi * bs.y;
+                        if (MODE == 1) {
+                            const float dx = da[16 * h + c];
+                            sumf[c] = __fmaf_rn((float)ig, __fmul_rn(dw, dx), sumf[c]);
+                            summin[c] = __fmaf_rn((float)mg, __fmul_rn(dmw, dx), summin[c]);
+                        } else {
+                            s1[c] += ig;
+                            s2[c] += mg;
+                        }
+                    }
+                }
+            }
+            if (MODE == 2 && any_col) {
+#pragma unroll
+                for (int c = 0; c < 16; c++) {
+                    float rr = __fmul_rn(dw, (float)s1[c]);
+                    rr = __fmaf_rn(-dmw, (float)s2[c], rr);
+                    sumf[c] = __fmaf_rn(rr, da[16 * h + c], sumf[c]);
+                }
+            }
+            // this warp is done with the stage's column scales
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars.empty[s]));
+        }
+        const int64_t row = tile * TILE_ROWS + lane;
+        if (row_ok && row < n && !*abort_flag) {
+#pragma unroll
+            for (int c = 0; c < 16; c++) {
+                const int64_t col = col0 + 16 * h + c;
+                if (col < m) dst[col * lddst + row] = MODE == 1 ? __fsub_rn(sumf[c], summin[c]) : sumf[c];
+            }
+        }
+    } else if (warp < TC_EPI_WARPS + TC_PROD_WARPS) {
+        // ---- producers ----
+        const int pw = warp - TC_EPI_WARPS, p = pw * 32 + lane;
+        const int64_t tile = tile0 + pw;
+        const bool tile_ok = tile < tiles_n;
+        const uint8_t *wsrc = tiles + (tile_ok ? tile : 0) * (int64_t)nb * 4608 + 512 + lane * 16;
+        const int prow = pw * 32 + lane;
+        const uint32_t a_off = (uint32_t)((prow >> 3) * 2048 + (prow & 7) * 16);
+        // activation blocks: four 16-byte pieces per thread, 16 threads per column
+        int64_t bcol[4];
+        uint32_t b_off[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int i = p + 128 * j, col = i >> 4, kc = i & 15;
+            const int64_t c = col0 + col;
+            bcol[j] = (c < m ? c : m - 1) * K + kc * 16;
+            b_off[j] = (uint32_t)((col >> 3) * 2048 + kc * 128 + (col & 7) * 16);
+        }
+        const int64_t scol = col0 + (p >> 2) < m ? col0 + (p >> 2) : m - 1;   // bsums: column p / 4, pair p % 4
+        const int64_t dcol = col0 + lane < m ? col0 + lane : m - 1;
+        for (int b = 0; b < nb; b++) {
+            const int s = b % TC_STAGES;
+            const uint32_t sph = (uint32_t)(b / TC_STAGES) & 1u;
+            // issue the loads before waiting for the stage
+            uint4 w[8];
+#pragma unroll
+            for (int c = 0; c < 8; c++) w[c] = tile_ok ? ld_stream16(wsrc + (int64_t)b * 4608 + c * 512) : make_uint4(0, 0, 0, 0);
+            uint4 y[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) y[j] = *(const uint4 *)(acts.qs + bcol[j] + (int64_t)b * 256);
+            const short4 bs = *(const short4 *)(acts.bsums + scol * (K / 16) + (int64_t)b * 16 + 4 * (p & 3));
+            float dx = 0.0f;
+            if (pw == 0) dx = acts.d[dcol * nb + b];
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.empty[s]), sph ^ 1u, abort_flag))) break;
+            uint8_t *stage = smem + s * TC_STAGE_BYTES;
+            uint8_t *A = stage + a_off, *B = stage + TC_A_BYTES;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                // 16-byte piece c of the row: low nibbles = K chunk (c & 1) of sub-block 2 (c / 2), high nibbles of 2 (c / 2) + 1
+                const int kc_lo = 4 * (c >> 1) + (c & 1), kc_hi = kc_lo + 2;
+                uint4 lo, hi;
+                lo.x = w[c].x & 0x0f0f0f0fu; lo.y = w[c].y & 0x0f0f0f0fu; lo.z = w[c].z & 0x0f0f0f0fu; lo.w = w[c].w & 0x0f0f0f0fu;
+                hi.x = (w[c].x >> 4) & 0x0f0f0f0fu; hi.y = (w[c].y >> 4) & 0x0f0f0f0fu;
+                hi.z = (w[c].z >> 4) & 0x0f0f0f0fu; hi.w = (w[c].w >> 4) & 0x0f0f0f0fu;
+                *(uint4 *)(A + kc_lo * 128) = lo;
+                *(uint4 *)(A + kc_hi * 128) = hi;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) *(uint4 *)(B + b_off[j]) = y[j];
+            int2 *bp = (int2 *)(stage + TC_A_BYTES + TC_B_BYTES);
+            bp[(p & 3) * TC_COLS + (p >> 2)] = make_int2((int)bs.x + (int)bs.y, (int)bs.z + (int)bs.w);
+            if (pw == 0) ((float *)(stage + TC_A_BYTES + TC_B_BYTES + TC_BP_BYTES))[lane] = dx;
+            // make the stores visible to the tensor core's (async proxy) reads, then hand the stage over
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars.full[s]));
+        }
+    } else if (lane == 0) {
+        // ---- MMA issue ----
+        for (int b = 0; b < nb; b++) {
+            const int s = b % TC_STAGES, t = b % TC_TSTAGES;
+            const uint32_t sph = (uint32_t)(b / TC_STAGES) & 1u, tph = (uint32_t)(b / TC_TSTAGES) & 1u;
+            if (!mbar_wait(smem_u32(&bars.full[s]), sph, abort_flag)) break;
+            if (!mbar_wait(smem_u32(&bars.tempty[t]), tph ^ 1u, abort_flag)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_base = smem_u32(smem + s * TC_STAGE_BYTES), b_base = a_base + TC_A_BYTES;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const uint64_t adesc = smem_desc(a_base + j * 256), bdesc = smem_desc(b_base + j * 256);
+                const uint32_t d_tmem = tmem + (uint32_t)(t * 8 * TC_COLS + j * TC_COLS);
+                asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p; }" ::"r"(d_tmem),
+                             "l"(adesc), "l"(bdesc), "r"(TC_IDESC), "r"(0)
+                             : "memory");
+            }
+            // both arrive when the eight MMAs above have completed: operands consumed, accumulators ready
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars.empty[s])) : "memory");
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars.tfull[t])) : "memory");
+        }
+    }
+    // ---- teardown: every role has left its loop (finished, or gave up) ----
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == TC_EPI_WARPS + TC_PROD_WARPS) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+    if (threadIdx.x == 0 && bars.abort_flag) atomicExch(err, TC_ERR_WAIT);
+}
+
+// mode: 1 = Q4_K gemm chain, 2 = Q4_K tiled chain
+int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
+                        cudaStream_t s) {
+    B200_REQUIRE(k % GROUP_K == 0, "gemm: k = %lld must be a multiple of 256", (long long)k);
+    B200_REQUIRE(mode == 1 || mode == 2, "gemm: unknown mode %d", mode);
+    if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    B200_REQUIRE(dev >= 0 && dev < 64, "gemm: device index %d out of range", dev);
+    if (!attr_done[dev]) {
+        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
+        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
+        attr_done[dev] = true;
+    }
+    int *err = nullptr;
+    int rc = device_error_word(&err);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    const int nb = (int)(k / GROUP_K);
+    const int64_t gx = (m + TC_COLS - 1) / TC_COLS, gy = (n + TC_ROWS - 1) / TC_ROWS;
+    B200_REQUIRE(gx < 0x7fffffffLL && gy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);
+    const dim3 grid((unsigned)gx, (unsigned)gy), block(TC_THREADS);
+    if (mode == 1) return launch_pdl(gemm_q4_K_tcgen05_kernel<1>, grid, block, (size_t)TC_SMEM_BYTES, s, tiles, acts, dst, lddst, n, nb, m, err);
+    return launch_pdl(gemm_q4_K_tcgen05_kernel<2>, grid, block, (size_t)TC_SMEM_BYTES, s, tiles, acts, dst, lddst, n, nb, m, err);
+}
+
+}  // namespace b200

@@ -391,6 +391,18 @@ static bool gemm_mma_enabled() {
     return v == 1;
 }
 
+// B200_GEMM_TCGEN05=0 keeps Q4_K prompt batches on the mma.sync kernel; batches narrower than one
+// 32-column MMA tile stay there too
+constexpr int64_t GEMM_TCGEN05_MIN_COLS = 32;
+static bool gemm_tcgen05_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_GEMM_TCGEN05");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
 static int64_t gemv_stream_max_tiles() {
     static int64_t v = -1;
     if (v < 0) {
@@ -419,7 +431,9 @@ int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint
         int64_t c_start = 0;
         if (m4 >= GEMM_MMA_MIN_COLS && gemm_mma_enabled()) {
             // enough activation rows to fill tensor-core patches: same chains, integer dots by mma
-            int rc = launch_gemm_mma(route == B200_ROUTE_REPACK ? 1 : 2, n, k, m4, tiles, acts, dst, lddst, s);
+            const int mode = route == B200_ROUTE_REPACK ? 1 : 2;
+            int rc = m4 >= GEMM_TCGEN05_MIN_COLS && gemm_tcgen05_enabled() ? launch_gemm_tcgen05(mode, n, k, m4, tiles, acts, dst, lddst, s)
+                                                                           : launch_gemm_mma(mode, n, k, m4, tiles, acts, dst, lddst, s);
             if (rc != B200_STATUS_SUCCESS) return rc;
             c_start = m4;
         }

@@ -1,0 +1,56 @@
+"""The tcgen05 prompt mat-mul (Q4_K, 32 activation rows and up) against the CPU oracle and against the
+decode-shaped kernels: same chains, so every output has to agree bit for bit."""
+import numpy as np
+import pytest
+
+import b200
+import orc
+import synth
+from conftest import bits_equal
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    mod = b200.load()
+    assert mod.device_count() > 0, "no CUDA device"
+    mod.set_device(0)
+    return mod
+
+
+CASES = [
+    # (n, k, m, route)
+    (128, 256, 32, orc.ROUTE_REPACK),    # one CTA, one super-block: a single pipeline step
+    (128, 1024, 32, orc.ROUTE_REPACK),   # four steps: stage and accumulator rings wrap
+    (160, 2048, 45, orc.ROUTE_REPACK),   # rows: a partly filled 128-row block; columns: 44 by the gemm chain + 1 tail row
+    (256, 512, 96, orc.ROUTE_REPACK),
+    (36, 512, 40, orc.ROUTE_TILED),      # rows not a multiple of 8: tiled chain; 36 rows of a 128-row block
+    (300, 768, 64, orc.ROUTE_TILED),
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: f"{c[0]}x{c[1]}-m{c[2]}")
+def test_against_the_oracle(dev, case):
+    n, k, m, route = case
+    W = synth.weights(orc.Q4_K, n, k, seed=61)
+    x = synth.activations(m, k, seed=62)
+    want, r = orc.mul_mat(orc.Q4_K, W, x)
+    assert r == route
+    got = dev.mul_mat(dev.Weight(orc.Q4_K, W, k), x)
+    assert dev.kernel_error() == 0
+    assert bits_equal(got, want), f"max |d| = {np.abs(got - want).max()}"
+
+
+@pytest.mark.parametrize("shape", [(4096, 4096, 512), (1024, 14336, 200)], ids=str)
+def test_full_size_columns_agree_with_four_column_calls(dev, shape):
+    """512 activation rows in one call (tcgen05) = the same rows four at a time (the decode-shaped gemm kernel)"""
+    n, k, m = shape
+    W = synth.weights(orc.Q4_K, n, k, seed=63)
+    x = synth.activations(m, k, seed=64)
+    w = dev.Weight(orc.Q4_K, W, k)
+    whole = dev.mul_mat(w, x)
+    assert dev.kernel_error() == 0
+    for c0 in list(range(0, m, 52))[:6] + [m - 4]:
+        part = dev.mul_mat(w, x[c0:c0 + 4])
+        assert bits_equal(whole[c0:c0 + 4], part), f"columns {c0}..{c0 + 3}"
