@@ -616,6 +616,31 @@ def case_gemv(args):
                       "gbs": algorithmic_bytes(n, k) / us / 1e3}), flush=True)
 
 
+def case_gemm(args):
+    """`--case gemm --only NxK --cols M --launches R`: R prompt-shaped Q4_K mat-muls (M activation rows,
+    quantization included, device-resident f32 in and out); prints the event-timed mean and the integer
+    multiply-add rate."""
+    b = load_pkg()
+    b.set_device(0)
+    n, k = (int(v) for v in args.only.lower().split("x"))
+    m = args.cols
+    w = b.Weight(Q4_K, synth_weights(n, k, seed=7), k)
+    x = np.random.default_rng(8).standard_normal((m, k)).astype(np.float32)
+    dx, do = b.device_array(x), b.DeviceBuffer(4 * n * m)
+    for _ in range(3):
+        b.mul_mat_device(w, dx, m, do)
+    b.synchronize()
+    e0, e1 = b.Event(), b.Event()
+    e0.record()
+    for _ in range(args.launches):
+        b.mul_mat_device(w, dx, m, do)
+    e1.record()
+    e1.synchronize()
+    us = e0.elapsed_ms(e1) * 1e3 / args.launches
+    print(json.dumps({"case": f"gemm {args.only} x {m}", "launches": args.launches, "us_per_call": us,
+                      "tops": 2.0 * n * k * m / us / 1e6, "kernel_error": b.kernel_error()}), flush=True)
+
+
 def case_llama(args):
     """`--case llama_tg|llama_pp --layers L [--launches R]`: an L-layer model of the 8B shape; one prompt
     batch (llama_pp) or R single-token steps after a 16-token prompt (llama_tg), eager launches (no CUDA
@@ -643,8 +668,9 @@ def case_llama(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default=None, choices=["gemv", "llama_tg", "llama_pp"], help="one small case for a profiler")
-    ap.add_argument("--only", default="4096x4096", help="--case gemv: the shape NxK")
+    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "llama_tg", "llama_pp"], help="one small case for a profiler")
+    ap.add_argument("--only", default="4096x4096", help="--case gemv / gemm: the shape NxK")
+    ap.add_argument("--cols", type=int, default=512, help="--case gemm: activation rows")
     ap.add_argument("--launches", type=int, default=64)
     ap.add_argument("--layers", type=int, default=32, help="layers of the 8B-shaped model (32 = the full model)")
     ap.add_argument("--cpu-layers", type=int, default=32, help="layers of the model the CPU baseline times")
@@ -656,6 +682,8 @@ def main():
     args = ap.parse_args()
     if args.case == "gemv":
         return case_gemv(args)
+    if args.case == "gemm":
+        return case_gemm(args)
     if args.case:
         return case_llama(args)
     rank, world, barrier, reduce_max = dist_setup(args.gpus)

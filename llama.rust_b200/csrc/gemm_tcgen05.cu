@@ -43,7 +43,8 @@ constexpr int TC_BP_BYTES = 4 * TC_COLS * 8; // [pair][column] (sum of low sub-b
 constexpr int TC_DA_BYTES = TC_COLS * 4;
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES + TC_BP_BYTES + TC_DA_BYTES;
 constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024;
-constexpr uint32_t TC_WAIT_LIMIT = 1u << 20;
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 16;   // tries per wait, each up to TC_WAIT_HINT_NS long
+constexpr uint32_t TC_WAIT_HINT_NS = 20000;
 constexpr int TC_ERR_WAIT = 4;               // device error word: a pipeline wait ran out
 
 // kind::i8 instruction descriptor: s32 accumulator, s8 x s8, both operands K-major, N = 32, M = 128
@@ -67,15 +68,13 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     for (uint32_t it = 0; it < TC_WAIT_LIMIT; it++) {
         uint32_t ok;
-        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        // the thread sleeps in hardware until the phase completes or the time hint runs out: no issue slots spent
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
                      : "=r"(ok)
-                     : "r"(bar), "r"(parity)
+                     : "r"(bar), "r"(parity), "r"(TC_WAIT_HINT_NS)
                      : "memory");
         if (ok) return true;
-        if ((it & 63) == 63) {
-            if (*abort_flag) return false;
-            __nanosleep(64);
-        }
+        if (*abort_flag) return false;
     }
     *abort_flag = 1;
     return false;
@@ -311,6 +310,320 @@ gemm_q4_K_tcgen05_kernel(const uint8_t *__restrict__ tiles, ActView acts, float 
     if (threadIdx.x == 0 && bars.abort_flag) atomicExch(err, TC_ERR_WAIT);
 }
 
+// ---- the 8x8 gemm chain with the sub-block scales folded into the operands ----------------------------
+// The integer work of the chain above (two scale multiplies, two min multiplies and two int -> float
+// conversions per output element and sub-block pair) is what bounds the kernel, not the tensor pipe.  The
+// gemm route only ever needs, per pair g, the two integers
+//     ig = s_lo dot_lo + s_hi dot_hi      |ig| <= 2 * 32 * 15 * 127 * 63 < 2^23
+//     mg = m_lo bsum_lo + m_hi bsum_hi    |mg| <= 2 * 63 * 32 * 127      < 2^19
+// as f32.  Every term and every partial sum is an integer below 2^24, so an f16 x f16 -> f32 MMA whose
+// operands are the small integers  s * w  (at most 63 * 15 = 945 < 2048, exact in f16), the activation
+// bytes, the mins and the activation 16-element sums (at most 16 * 127 = 2032 < 2048) returns exactly
+// f32(ig) and f32(mg), in whatever order the tensor core adds: the producers fold the scales in once
+// per weight (one half2 fma per two weights, shared by all 32 activation rows) and the epilogue is left
+// with the two fmas of the chain.  The tiled chain sums a whole super-block (up to 2^25) before the
+// conversion, so it stays on the integer kernel above.
+//   A   [128 rows][256 f16]  s * w, K order within a pair: 16-byte piece p, (low | high) nibbles, bytes (0,2,1,3 ..)
+//   B   [32 columns][256 f16] activation bytes in the same order
+//   Am  [128 rows][16 f16]   slots 4g, 4g+1 = m_lo of pair g, 4g+2, 4g+3 = m_hi
+//   Bm  [4 pairs][32 columns][16 f16]  slots 4g .. 4g+3 = the pair's four 16-element activation sums, rest 0
+// per pair: four K = 16 MMAs accumulate ig into 32 tensor-memory columns, one K = 16 MMA writes mg.
+namespace {
+
+constexpr int TF_STAGES = 2;
+constexpr int TF_A_BYTES = TC_ROWS * 512;
+constexpr int TF_B_BYTES = TC_COLS * 512;
+constexpr int TF_AM_BYTES = TC_ROWS * 32;
+constexpr int TF_BM_BYTES = 4 * TC_COLS * 32;
+constexpr int TF_STAGE_BYTES = TF_A_BYTES + TF_B_BYTES + TF_AM_BYTES + TF_BM_BYTES;
+constexpr int TF_SMEM_BYTES = TF_STAGES * TF_STAGE_BYTES + 1024;
+// kind::f16 instruction descriptor: f32 accumulator, f16 x f16, both operands K-major, N = 32, M = 128
+constexpr uint32_t TF_IDESC = (1u << 4) | ((uint32_t)(TC_COLS >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);
+
+__device__ __forceinline__ uint64_t smem_desc_ls(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46);
+}
+__device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
+// nibbles at bit `shift` of bytes 0 and 2 of the word, times the scale: (1024 + w) s - 1024 s, exact
+__device__ __forceinline__ uint32_t scaled_nibbles(uint32_t word, int shift, __half2 s2, __half2 c2) {
+    return h2_bits(__hfma2(bits_h2(((word >> shift) & 0x000f000fu) | 0x64006400u), s2, c2));
+}
+// signed bytes 0 and 2 of the word (after the sign flip u = y ^ 0x80): (1024 + u) - 1152, exact
+__device__ __forceinline__ uint32_t signed_bytes(uint32_t u, int shift) {
+    return h2_bits(__hsub2(bits_h2(((u >> shift) & 0x00ff00ffu) | 0x64006400u), __float2half2_rn(1152.0f)));
+}
+__device__ __forceinline__ void tmem_ld16f(float (&v)[16], uint32_t taddr) {
+    int r[16];
+    tmem_ld16(r, taddr);
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = __int_as_float(r[i]);
+}
+
+constexpr int TF_PROD_WARPS = 8;                                // producer warps: a (tile, half row) each
+constexpr int TF_THREADS = (TC_EPI_WARPS + TF_PROD_WARPS) * 32;
+
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+
+struct TfBars {
+    uint64_t full[TF_STAGES], empty[TF_STAGES], tfull[TC_TSTAGES], tempty[TC_TSTAGES];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+}  // namespace
+
+// Roles: warps 0-7 epilogue (as above); warps 8-15 producers, warp 8 + (tile, half): each thread converts
+// half a weight row (two sub-block pairs) and two activation pieces per super-block, with the next
+// super-block's loads in flight meanwhile; lane 0 of warp 8 also issues the MMAs of a stage once all eight
+// producer warps have handed it over.  16 warps keep the CTA at 128 registers per thread.
+__global__ void __launch_bounds__(TF_THREADS, 1)
+gemm_q4_K_tcgen05_f16_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *dst, int64_t lddst, int64_t n, int nb, int64_t m, int *err) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ TfBars bars;
+    pdl_trigger();
+    const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t tile0 = (int64_t)blockIdx.y * (TC_ROWS / TILE_ROWS);
+    const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
+    const int64_t col0 = (int64_t)blockIdx.x * TC_COLS;
+    const int64_t K = acts.k;
+    volatile int *abort_flag = &bars.abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < TF_STAGES; i++) {
+            mbar_init(smem_u32(&bars.full[i]), TF_PROD_WARPS);
+            mbar_init(smem_u32(&bars.empty[i]), 1);
+        }
+        for (int i = 0; i < TC_TSTAGES; i++) {
+            mbar_init(smem_u32(&bars.tfull[i]), 1);
+            mbar_init(smem_u32(&bars.tempty[i]), TC_EPI_WARPS);
+        }
+        bars.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == TC_EPI_WARPS) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars.tmem_base)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = bars.tmem_base;
+    pdl_wait();
+
+    if (warp < TC_EPI_WARPS) {
+        // ---- epilogue: sumf = fma(f32(ig), d d_x, sumf); summin = fma(f32(mg), dmin d_x, summin) ----
+        const int q = warp & 3, h = warp >> 2;
+        const int64_t tile = tile0 + q;
+        const bool row_ok = tile < tiles_n;
+        const bool any_col = col0 + 16 * h < m;
+        const uint8_t *hdr = tiles + (row_ok ? tile : 0) * (int64_t)nb * 4608 + lane * 16;
+        const int64_t cbase = col0 + 16 * h;
+        float sumf[16], summin[16];
+#pragma unroll
+        for (int c = 0; c < 16; c++) sumf[c] = summin[c] = 0.0f;
+        for (int b = 0; b < nb; b++) {
+            const int t = b % TC_TSTAGES;
+            const uint32_t tph = (uint32_t)(b / TC_TSTAGES) & 1u;
+            const uint32_t dd = row_ok ? *(const uint32_t *)(hdr + (int64_t)b * 4608) : 0u;
+            const float dw = f16_bits_to_f32((uint16_t)(dd & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(dd >> 16));
+            float sd[16], sm[16];
+#pragma unroll
+            for (int c = 0; c < 16; c++) {
+                const int64_t col = cbase + c < m ? cbase + c : m - 1;
+                const float dx = acts.d[col * nb + b];
+                sd[c] = __fmul_rn(dw, dx);
+                sm[c] = __fmul_rn(dmw, dx);
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.tfull[t]), tph, abort_flag))) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t trow = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(t * 8 * TC_COLS + 16 * h);
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+                float ig[16], mg[16];
+                tmem_ld16f(ig, trow + (uint32_t)(g * TC_COLS));
+                tmem_ld16f(mg, trow + (uint32_t)((4 + g) * TC_COLS));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (g == 3) {
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bars.tempty[t]));
+                }
+                if (any_col) {
+#pragma unroll
+                    for (int c = 0; c < 16; c++) {
+                        sumf[c] = __fmaf_rn(ig[c], sd[c], sumf[c]);
+                        summin[c] = __fmaf_rn(mg[c], sm[c], summin[c]);
+                    }
+                }
+            }
+        }
+        const int64_t row = tile * TILE_ROWS + lane;
+        if (row_ok && row < n && !*abort_flag) {
+#pragma unroll
+            for (int c = 0; c < 16; c++) {
+                const int64_t col = col0 + 16 * h + c;
+                if (col < m) dst[col * lddst + row] = __fsub_rn(sumf[c], summin[c]);
+            }
+        }
+    } else {
+        // ---- producers ----
+        const int pw = warp - TC_EPI_WARPS, pt = pw * 32 + lane;
+        const int tt = pw & 3, half = pw >> 2;
+        const int64_t tile = tile0 + tt;
+        const bool tile_ok = tile < tiles_n;
+        const uint8_t *wsrc = tiles + (tile_ok ? tile : 0) * (int64_t)nb * 4608 + lane * 16;
+        const int prow = tt * 32 + lane;
+        const uint32_t a_off = (uint32_t)((prow >> 3) * 4096 + (prow & 7) * 16);
+        const uint32_t am_off = (uint32_t)(TF_A_BYTES + TF_B_BYTES + (prow >> 3) * 256 + (prow & 7) * 16);
+        int64_t bcol[2];
+        uint32_t b_off[2];
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int i = pt + 256 * j, col = i >> 4, kc = i & 15;
+            const int64_t c = col0 + col;
+            bcol[j] = (c < m ? c : m - 1) * K + kc * 16;
+            // 16-byte piece kc of the super-block: pair kc / 4, then (low p0, low p1, high p0, high p1) -> chunks 8 g + 4 p + 2 hi
+            const int chunk = 8 * (kc >> 2) + 4 * (kc & 1) + 2 * ((kc >> 1) & 1);
+            b_off[j] = (uint32_t)(TF_A_BYTES + (col >> 3) * 4096 + (col & 7) * 16 + chunk * 128);
+        }
+        // activation sums: threads 0..127 take column pt / 4, pair pt % 4
+        const bool has_sum = pt < 128;
+        const int sg = pt & 3, scol_i = (pt >> 2) & 31;
+        const int64_t scol = ((col0 + scol_i < m ? col0 + scol_i : m - 1)) * (K / 16) + 4 * sg;
+        const uint32_t bm_off = (uint32_t)(TF_A_BYTES + TF_B_BYTES + TF_AM_BYTES + sg * 1024 + (scol_i >> 3) * 256 + (scol_i & 7) * 16);
+
+        uint4 hd_n = make_uint4(0, 0, 0, 0), w_n[4], y_n[2];
+        short4 bs_n = make_short4(0, 0, 0, 0);
+#pragma unroll
+        for (int c = 0; c < 4; c++) w_n[c] = make_uint4(0, 0, 0, 0);
+        if (tile_ok) {
+            hd_n = *(const uint4 *)(wsrc);
+#pragma unroll
+            for (int c = 0; c < 4; c++) w_n[c] = ld_stream16(wsrc + 512 + (4 * half + c) * 512);
+        }
+#pragma unroll
+        for (int j = 0; j < 2; j++) y_n[j] = *(const uint4 *)(acts.qs + bcol[j]);
+        if (has_sum) bs_n = *(const short4 *)(acts.bsums + scol);
+        for (int b = 0; b < nb; b++) {
+            const int s = b % TF_STAGES, t = b % TC_TSTAGES;
+            const uint32_t sph = (uint32_t)(b / TF_STAGES) & 1u, tph = (uint32_t)(b / TC_TSTAGES) & 1u;
+            const uint4 hd = hd_n;
+            const short4 bs = bs_n;
+            uint4 w[4], y[2];
+#pragma unroll
+            for (int c = 0; c < 4; c++) w[c] = w_n[c];
+#pragma unroll
+            for (int j = 0; j < 2; j++) y[j] = y_n[j];
+            if (b + 1 < nb) {
+                if (tile_ok) {
+                    hd_n = *(const uint4 *)(wsrc + (int64_t)(b + 1) * 4608);
+#pragma unroll
+                    for (int c = 0; c < 4; c++) w_n[c] = ld_stream16(wsrc + (int64_t)(b + 1) * 4608 + 512 + (4 * half + c) * 512);
+                }
+#pragma unroll
+                for (int j = 0; j < 2; j++) y_n[j] = *(const uint4 *)(acts.qs + bcol[j] + (int64_t)(b + 1) * 256);
+                if (has_sum) bs_n = *(const short4 *)(acts.bsums + scol + (int64_t)(b + 1) * 16);
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.empty[s]), sph ^ 1u, abort_flag))) break;
+            const uint32_t stage = smem + (uint32_t)(s * TF_STAGE_BYTES);
+            // this half's scale and min words (pairs 2 half, 2 half + 1 = sub-blocks 4 half .. 4 half + 3)
+            const uint32_t sc = half ? ((hd.w & 0x0f0f0f0fu) | (((hd.y >> 6) & 0x03030303u) << 4)) : (hd.y & 0x3f3f3f3fu);
+            if (half == 0) {
+                const uint32_t mn0 = hd.z & 0x3f3f3f3fu, mn1 = ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4);
+                uint32_t mins[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) mins[j] = h2_bits(__half2half2(__int2half_rn((int)(((j < 4 ? mn0 : mn1) >> (8 * (j & 3))) & 0xff))));
+                sts128(stage + am_off, mins[0], mins[1], mins[2], mins[3]);
+                sts128(stage + am_off + 128, mins[4], mins[5], mins[6], mins[7]);
+            }
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const int gl = c >> 1, pp = c & 1;          // pair within this half, 16-byte piece within the pair
+                const int s_lo = (sc >> (16 * gl)) & 0xff, s_hi = (sc >> (16 * gl + 8)) & 0xff;
+                const __half2 sl = __half2half2(__int2half_rn(s_lo)), sh = __half2half2(__int2half_rn(s_hi));
+                const __half2 cl = __half2half2(__int2half_rn(-1024 * s_lo)), ch = __half2half2(__int2half_rn(-1024 * s_hi));
+                const uint32_t dstp = stage + a_off + (uint32_t)((8 * (2 * half + gl) + 4 * pp) * 128);
+                sts128(dstp, scaled_nibbles(w[c].x, 0, sl, cl), scaled_nibbles(w[c].x, 8, sl, cl), scaled_nibbles(w[c].y, 0, sl, cl),
+                       scaled_nibbles(w[c].y, 8, sl, cl));
+                sts128(dstp + 128, scaled_nibbles(w[c].z, 0, sl, cl), scaled_nibbles(w[c].z, 8, sl, cl), scaled_nibbles(w[c].w, 0, sl, cl),
+                       scaled_nibbles(w[c].w, 8, sl, cl));
+                sts128(dstp + 256, scaled_nibbles(w[c].x, 4, sh, ch), scaled_nibbles(w[c].x, 12, sh, ch), scaled_nibbles(w[c].y, 4, sh, ch),
+                       scaled_nibbles(w[c].y, 12, sh, ch));
+                sts128(dstp + 384, scaled_nibbles(w[c].z, 4, sh, ch), scaled_nibbles(w[c].z, 12, sh, ch), scaled_nibbles(w[c].w, 4, sh, ch),
+                       scaled_nibbles(w[c].w, 12, sh, ch));
+            }
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const uint32_t u0 = y[j].x ^ 0x80808080u, u1 = y[j].y ^ 0x80808080u, u2 = y[j].z ^ 0x80808080u, u3 = y[j].w ^ 0x80808080u;
+                sts128(stage + b_off[j], signed_bytes(u0, 0), signed_bytes(u0, 8), signed_bytes(u1, 0), signed_bytes(u1, 8));
+                sts128(stage + b_off[j] + 128, signed_bytes(u2, 0), signed_bytes(u2, 8), signed_bytes(u3, 0), signed_bytes(u3, 8));
+            }
+            if (has_sum) {
+                const uint32_t xy = h2_bits(__halves2half2(__short2half_rn(bs.x), __short2half_rn(bs.y)));
+                const uint32_t zw = h2_bits(__halves2half2(__short2half_rn(bs.z), __short2half_rn(bs.w)));
+                const bool odd = sg & 1, second = sg >> 1;
+                const uint32_t v0 = odd ? 0u : xy, v1 = odd ? 0u : zw, v2 = odd ? xy : 0u, v3 = odd ? zw : 0u;
+                sts128(stage + bm_off, second ? 0u : v0, second ? 0u : v1, second ? 0u : v2, second ? 0u : v3);
+                sts128(stage + bm_off + 128, second ? v0 : 0u, second ? v1 : 0u, second ? v2 : 0u, second ? v3 : 0u);
+            }
+            // make the stores visible to the tensor core's (async proxy) reads, then hand the stage over
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars.full[s]));
+            if (pw == 0 && lane == 0) {
+                // ---- MMA issue for this stage, once every producer warp has arrived and the accumulators are free ----
+                if (mbar_wait(smem_u32(&bars.full[s]), sph, abort_flag) && mbar_wait(smem_u32(&bars.tempty[t]), tph ^ 1u, abort_flag)) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_base = stage, b_base = a_base + TF_A_BYTES;
+                    const uint32_t am_base = b_base + TF_B_BYTES, bm_base = am_base + TF_AM_BYTES;
+#pragma unroll
+                    for (int g = 0; g < 4; g++) {
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const uint64_t adesc = smem_desc_ls(a_base + (8 * g + 2 * i) * 128, 128, 4096);
+                            const uint64_t bdesc = smem_desc_ls(b_base + (8 * g + 2 * i) * 128, 128, 4096);
+                            asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(
+                                             tmem + (uint32_t)(t * 8 * TC_COLS + g * TC_COLS)),
+                                         "l"(adesc), "l"(bdesc), "r"(TF_IDESC), "r"(i)
+                                         : "memory");
+                        }
+                        const uint64_t amdesc = smem_desc_ls(am_base, 128, 256), bmdesc = smem_desc_ls(bm_base + g * 1024, 128, 256);
+                        asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(
+                                         tmem + (uint32_t)(t * 8 * TC_COLS + (4 + g) * TC_COLS)),
+                                     "l"(amdesc), "l"(bmdesc), "r"(TF_IDESC), "r"(0)
+                                     : "memory");
+                    }
+                    // both arrive when the MMAs above have completed: operands consumed, accumulators ready
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars.empty[s])) : "memory");
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars.tfull[t])) : "memory");
+                }
+            }
+        }
+    }
+    // ---- teardown: every role has left its loop (finished, or gave up) ----
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == TC_EPI_WARPS) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+    if (threadIdx.x == 0 && bars.abort_flag) atomicExch(err, TC_ERR_WAIT);
+}
+
+// B200_GEMM_TCGEN05_F16=0 keeps the gemm chain on the integer kernel (for side-by-side measurements)
+static bool gemm_tcgen05_f16_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_GEMM_TCGEN05_F16");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
 // mode: 1 = Q4_K gemm chain, 2 = Q4_K tiled chain
 int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
                         cudaStream_t s) {
@@ -324,6 +637,7 @@ int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t
     if (!attr_done[dev]) {
         B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
         B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
+        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TF_SMEM_BYTES));
         attr_done[dev] = true;
     }
     int *err = nullptr;
@@ -333,6 +647,8 @@ int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t
     const int64_t gx = (m + TC_COLS - 1) / TC_COLS, gy = (n + TC_ROWS - 1) / TC_ROWS;
     B200_REQUIRE(gx < 0x7fffffffLL && gy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);
     const dim3 grid((unsigned)gx, (unsigned)gy), block(TC_THREADS);
+    if (mode == 1 && gemm_tcgen05_f16_enabled())
+        return launch_pdl(gemm_q4_K_tcgen05_f16_kernel, grid, dim3(TF_THREADS), (size_t)TF_SMEM_BYTES, s, tiles, acts, dst, lddst, n, nb, m, err);
     if (mode == 1) return launch_pdl(gemm_q4_K_tcgen05_kernel<1>, grid, block, (size_t)TC_SMEM_BYTES, s, tiles, acts, dst, lddst, n, nb, m, err);
     return launch_pdl(gemm_q4_K_tcgen05_kernel<2>, grid, block, (size_t)TC_SMEM_BYTES, s, tiles, acts, dst, lddst, n, nb, m, err);
 }

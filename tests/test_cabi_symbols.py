@@ -19,7 +19,7 @@ def declared_functions():
         # function declarations: a name followed by '(' and terminated by ');' at statement level
         for m in re.finditer(r"\b([A-Za-z_][A-Za-z0-9_]*)\s*\([^;{}()]*(?:\([^()]*\)[^;{}()]*)*\)\s*;", text):
             name = m.group(1)
-            if name.startswith(("b200_", "ggml_backend_")) and not name.endswith("_t"):
+            if name.startswith(("b200_", "ggml_")) and not name.endswith("_t"):
                 names.add(name)
     return names
 
@@ -29,6 +29,7 @@ def test_library_exports_every_declared_symbol():
     lib = ctypes.CDLL(mod.LIB_PATH)
     names = declared_functions()
     assert "b200_mul_mat" in names and "b200_flash_attn_ext" in names
+    assert "ggml_build_forward_expand" in names and "ggml_backend_sched_graph_compute" in names and "ggml_time_us" in names
     missing = [n for n in sorted(names) if not hasattr(lib, n)]
     assert not missing, f"declared in include/ but not exported: {missing}"
 

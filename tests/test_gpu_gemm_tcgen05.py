@@ -54,3 +54,27 @@ def test_full_size_columns_agree_with_four_column_calls(dev, shape):
     for c0 in list(range(0, m, 52))[:6] + [m - 4]:
         part = dev.mul_mat(w, x[c0:c0 + 4])
         assert bits_equal(whole[c0:c0 + 4], part), f"columns {c0}..{c0 + 3}"
+
+
+@pytest.mark.parametrize("signs", ["same", "random"])
+def test_largest_integers_stay_exact(dev, signs):
+    """every scale and min 63, every nibble 15, every activation byte +-127: the pair sums reach
+    2 * 32 * 15 * 127 * 63 = 7.68e6, the largest integers the f16 operands / f32 accumulators have to carry"""
+    n, k, m = 128, 1024, 32
+    blk = np.zeros(144, dtype=np.uint8)
+    blk[0:2] = np.frombuffer(np.float16(1.0).tobytes(), dtype=np.uint8)
+    blk[2:4] = np.frombuffer(np.float16(0.5).tobytes(), dtype=np.uint8)
+    blk[4:] = 0xFF
+    W = np.tile(blk, (n, k // 256))
+    rng = np.random.default_rng(71)
+    x = np.full((m, k), -3.0, dtype=np.float32)
+    if signs == "random":
+        x *= rng.choice([-1.0, 1.0], size=x.shape).astype(np.float32)
+        W = W.copy().reshape(n, k // 256, 144)
+        W[:, :, 16:] = rng.choice([0xFF, 0xF0, 0x0F, 0xFE], size=(n, k // 256, 128)).astype(np.uint8)
+        W = W.reshape(n, -1)
+    want, r = orc.mul_mat(orc.Q4_K, W, x)
+    assert r == orc.ROUTE_REPACK
+    got = dev.mul_mat(dev.Weight(orc.Q4_K, W, k), x)
+    assert dev.kernel_error() == 0
+    assert bits_equal(got, want), f"max |d| = {np.abs(got - want).max()}"
