@@ -451,6 +451,9 @@ ggml_backend_dev_t ggml_backend_dev_by_name(const char *name) {
     if (!name) return nullptr;
     for (ggml_backend_dev_t d : registry().devs)
         if (strcasecmp(ggml_backend_dev_name(d), name) == 0) return d;
+    // a registry's own name ("B200") stands for its first device ("B2000")
+    for (ggml_backend_dev_t d : registry().devs)
+        if (d->reg && d->reg->iface.get_name && strcasecmp(d->reg->iface.get_name(d->reg), name) == 0) return d;
     return nullptr;
 }
 ggml_backend_dev_t ggml_backend_dev_by_type(int type) {
