@@ -68,17 +68,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     for (uint32_t it = 0; it < TC_WAIT_LIMIT; it++) {
         uint32_t ok;
         // try_wait suspends the thread in hardware for a while before it reports "not yet"
-#if defined(B200_TC_EXPERIMENT) && (B200_TC_EXPERIMENT & 512)
-        asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-                     : "=r"(ok)
-                     : "r"(bar), "r"(parity)
-                     : "memory");
-#else
         asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
                      : "=r"(ok)
                      : "r"(bar), "r"(parity)
                      : "memory");
-#endif
         if (ok) return true;
         if ((it & 255) == 255 && *abort_flag) return false;
     }
@@ -397,15 +390,7 @@ __device__ __forceinline__ void tmem_ld8f(float (&v)[8], uint32_t taddr) {
     for (int i = 0; i < 8; i++) v[i] = __uint_as_float(r[i]);
 }
 
-#if defined(B200_TC_EXPERIMENT) && (B200_TC_EXPERIMENT & 8)
-// measuring aid: the converted values are folded into one word instead of being stored
-#define STS_A(addr, x_, y_, z_, w_) exp_dummy ^= (x_) ^ (y_) ^ (z_) ^ (w_)
-#elif defined(B200_TC_EXPERIMENT) && (B200_TC_EXPERIMENT & 16)
-// measuring aid: the stores happen, the conversion does not
-#define STS_A(addr, x_, y_, z_, w_) sts128(addr, w0.x, w0.y, w1.x, w1.y)
-#else
-#define STS_A(addr, x_, y_, z_, w_) sts128(addr, x_, y_, z_, w_)
-#endif
+#define sts128(addr, x_, y_, z_, w_) sts128(addr, x_, y_, z_, w_)
 
 struct TfBars {
     uint64_t full[TF_STAGES], empty[TF_STAGES], tfull[TC_TSTAGES], tempty[TC_TSTAGES];
@@ -484,7 +469,6 @@ gemm_q4_K_tcgen05_f16_kernel(const uint8_t *__restrict__ tiles, ActView acts, fl
         const bool any_col = col0 + 8 * h < m;
         const uint8_t *hdr = tiles + (row_ok ? tile0 + q : 0) * (int64_t)nb * 4608 + lane * 16;
         float sumf[8], summin[8];
-        uint32_t exp_dummy = 0;
 #pragma unroll
         for (int c = 0; c < 8; c++) sumf[c] = summin[c] = 0.0f;
 
@@ -508,13 +492,8 @@ gemm_q4_K_tcgen05_f16_kernel(const uint8_t *__restrict__ tiles, ActView acts, fl
             if (b < nb) {
                 const int s = b % TF_STAGES;
                 const uint32_t sph = (uint32_t)(b / TF_STAGES) & 1u;
-#if defined(B200_TC_EXPERIMENT) && (B200_TC_EXPERIMENT & 256)
-                const uint4 hd = make_uint4(b, tid, 3, 4), w0 = make_uint4(tid, b, 5, 6), w1 = make_uint4(7, tid, b, 8), y = make_uint4(b, 9, tid, 1);
-                const short4 bs = make_short4((short)b, (short)tid, 1, 2);
-#else
                 const uint4 hd = hd_n, w0 = w_n[0], w1 = w_n[1], y = y_n;
                 const short4 bs = bs_n;
-#endif
                 const float dx = dx_n;
                 dd = dd_n;
                 if (b + 1 < nb) {
@@ -530,15 +509,8 @@ gemm_q4_K_tcgen05_f16_kernel(const uint8_t *__restrict__ tiles, ActView acts, fl
                 }
                 if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.empty[s]), sph ^ 1u, abort_flag))) break;
                 const uint32_t stage = smem + (uint32_t)(s * TF_STAGE_BYTES);
-#ifdef B200_TC_EXPERIMENT
-                if (!(B200_TC_EXPERIMENT & 2)) {
-#endif
                 const uint32_t sc_lo = hd.y & 0x3f3f3f3fu, sc_hi = (hd.w & 0x0f0f0f0fu) | (((hd.y >> 6) & 0x03030303u) << 4);
-#if defined(B200_TC_EXPERIMENT) && (B200_TC_EXPERIMENT & 128)
-                if (hd.x == 0x12345678u)
-#else
                 if (c0 == 0)
-#endif
                 {
                     const uint32_t mn0 = hd.z & 0x3f3f3f3fu, mn1 = ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4);
                     uint32_t mins[8];
@@ -557,18 +529,15 @@ gemm_q4_K_tcgen05_f16_kernel(const uint8_t *__restrict__ tiles, ActView acts, fl
                     const __half2 sl = __half2half2(__int2half_rn(s_lo)), sh = __half2half2(__int2half_rn(s_hi));
                     const __half2 cl = __half2half2(__int2half_rn(-1024 * s_lo)), ch = __half2half2(__int2half_rn(-1024 * s_hi));
                     const uint32_t dstp = stage + a_off + (uint32_t)((8 * g + 4 * pp) * 128);
-                    STS_A(dstp, scaled_nibbles(w.x, 0, sl, cl), scaled_nibbles(w.x, 8, sl, cl), scaled_nibbles(w.y, 0, sl, cl),
+                    sts128(dstp, scaled_nibbles(w.x, 0, sl, cl), scaled_nibbles(w.x, 8, sl, cl), scaled_nibbles(w.y, 0, sl, cl),
                            scaled_nibbles(w.y, 8, sl, cl));
-                    STS_A(dstp + 128, scaled_nibbles(w.z, 0, sl, cl), scaled_nibbles(w.z, 8, sl, cl), scaled_nibbles(w.w, 0, sl, cl),
+                    sts128(dstp + 128, scaled_nibbles(w.z, 0, sl, cl), scaled_nibbles(w.z, 8, sl, cl), scaled_nibbles(w.w, 0, sl, cl),
                            scaled_nibbles(w.w, 8, sl, cl));
-                    STS_A(dstp + 256, scaled_nibbles(w.x, 4, sh, ch), scaled_nibbles(w.x, 12, sh, ch), scaled_nibbles(w.y, 4, sh, ch),
+                    sts128(dstp + 256, scaled_nibbles(w.x, 4, sh, ch), scaled_nibbles(w.x, 12, sh, ch), scaled_nibbles(w.y, 4, sh, ch),
                            scaled_nibbles(w.y, 12, sh, ch));
-                    STS_A(dstp + 384, scaled_nibbles(w.z, 4, sh, ch), scaled_nibbles(w.z, 12, sh, ch), scaled_nibbles(w.w, 4, sh, ch),
+                    sts128(dstp + 384, scaled_nibbles(w.z, 4, sh, ch), scaled_nibbles(w.z, 12, sh, ch), scaled_nibbles(w.w, 4, sh, ch),
                            scaled_nibbles(w.w, 12, sh, ch));
                 }
-#if defined(B200_TC_EXPERIMENT) && (B200_TC_EXPERIMENT & 64)
-                if (y.x == 0x12345678u)
-#endif
                 {
                     const uint32_t u0 = y.x ^ 0x80808080u, u1 = y.y ^ 0x80808080u, u2 = y.z ^ 0x80808080u, u3 = y.w ^ 0x80808080u;
                     sts128(stage + b_off, signed_bytes(u0, 0), signed_bytes(u0, 8), signed_bytes(u1, 0), signed_bytes(u1, 8));
@@ -584,14 +553,9 @@ gemm_q4_K_tcgen05_f16_kernel(const uint8_t *__restrict__ tiles, ActView acts, fl
                 }
                 // the activation scales of super-block b, read by every worker in the next iteration; slot b % 4 is
                 // rewritten in iteration b + 4, which no worker reaches before all have drained super-block b
-#ifdef B200_TC_EXPERIMENT
-                }
-#endif
                 if (has_da) bars.da[b % TF_DA_SLOTS][tid & 31] = dx;
                 // make the stores visible to the tensor core's (async proxy) reads, then hand the stage over
-#if !defined(B200_TC_EXPERIMENT) || !(B200_TC_EXPERIMENT & 32)
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#endif
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bars.full[s]));
             }
@@ -613,13 +577,6 @@ gemm_q4_K_tcgen05_f16_kernel(const uint8_t *__restrict__ tiles, ActView acts, fl
                     sm[c] = __fmul_rn(dmw, dxe);
                 }
                 const uint32_t trow = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(t * 8 * TC_COLS + 8 * h);
-#ifdef B200_TC_EXPERIMENT
-                if (B200_TC_EXPERIMENT & 4) {
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&bars.tempty[t]));
-                } else
-#endif
 #pragma unroll
                 for (int gp = 0; gp < 2; gp++) {
                     float ig0[8], mg0[8], ig1[8], mg1[8];
@@ -656,7 +613,6 @@ gemm_q4_K_tcgen05_f16_kernel(const uint8_t *__restrict__ tiles, ActView acts, fl
                 if (col < m) dst[col * lddst + row] = __fsub_rn(sumf[c], summin[c]);
             }
         }
-        if (exp_dummy == 0x12345678u) dst[0] = 1.0f;
     } else if (lane == 0) {
         // ---- MMA issue ----
         for (int b = 0; b < nb; b++) {
@@ -667,9 +623,6 @@ gemm_q4_K_tcgen05_f16_kernel(const uint8_t *__restrict__ tiles, ActView acts, fl
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a_base = smem + (uint32_t)(s * TF_STAGE_BYTES), b_base = a_base + TF_A_BYTES;
             const uint32_t am_base = b_base + TF_B_BYTES, bm_base = am_base + TF_AM_BYTES;
-#ifdef B200_TC_EXPERIMENT
-            if (!(B200_TC_EXPERIMENT & 1))
-#endif
 #pragma unroll
             for (int g = 0; g < 4; g++) {
 #pragma unroll
@@ -702,12 +655,15 @@ gemm_q4_K_tcgen05_f16_kernel(const uint8_t *__restrict__ tiles, ActView acts, fl
     if (threadIdx.x == 0 && bars.abort_flag) atomicExch(err, TC_ERR_WAIT);
 }
 
-// B200_GEMM_TCGEN05_F16=0 keeps the gemm chain on the integer kernel (for side-by-side measurements)
+// B200_GEMM_TCGEN05_F16=1 sends the gemm chain to the f16-operand kernel.  Measured on 4096 x 4096 x 512 it takes
+// 160 us against the integer kernel's 145 us: its epilogue is four times cheaper, but every worker converts,
+// hands over and drains in sequence, and the per-step hand-off and load latencies (2 operand stages of 88 KB
+// are all that fits) are not hidden.  It stays selectable until its pipeline is deeper.
 static bool gemm_tcgen05_f16_enabled() {
     static int v = -1;
     if (v < 0) {
         const char *e = getenv("B200_GEMM_TCGEN05_F16");
-        v = (e && e[0] == '0') ? 0 : 1;
+        v = (e && e[0] == '1') ? 1 : 0;
     }
     return v == 1;
 }

@@ -1,5 +1,11 @@
 """The tcgen05 prompt mat-mul (Q4_K, 32 activation rows and up) against the CPU oracle and against the
-decode-shaped kernels: same chains, so every output has to agree bit for bit."""
+decode-shaped kernels: same chains, so every output has to agree bit for bit.  The whole file runs twice:
+on the integer kernel (the default) and, in a child process with B200_GEMM_TCGEN05_F16=1, on the f16-operand
+kernel."""
+import os
+import subprocess
+import sys
+
 import numpy as np
 import pytest
 
@@ -78,3 +84,13 @@ def test_largest_integers_stay_exact(dev, signs):
     got = dev.mul_mat(dev.Weight(orc.Q4_K, W, k), x)
     assert dev.kernel_error() == 0
     assert bits_equal(got, want), f"max |d| = {np.abs(got - want).max()}"
+
+
+def test_f16_operand_kernel_passes_the_same_cases():
+    """the library reads B200_GEMM_TCGEN05_F16 once per process: run this file's other tests in a child with it set"""
+    if os.environ.get("B200_GEMM_TCGEN05_F16") == "1":
+        pytest.skip("already the child")
+    env = dict(os.environ, B200_GEMM_TCGEN05_F16="1")
+    r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-x", "-q", "-m", "gpu", "-p", "no:cacheprovider"], env=env,
+                       capture_output=True, text=True, timeout=1200)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
