@@ -34,6 +34,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 Q4_K = 12
 SHAPES = [(4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096)]  # (n rows, k)
 METRIC = "q4_K_decode_mat_mul_hbm_gbs"
+NCU_TRAFFIC_RATIO = 33.05 / 33.03   # measured DRAM bytes / algorithmic bytes of one decode mat-mul launch (see roofline.traffic)
 PROMPT, GEN = 512, 128
 
 
@@ -283,7 +284,11 @@ def run_gemv(b, args, rank, world, barrier, reduce_max, local):
         "gpu_launches": args.steps * 2 * len(SHAPES),
         "roofline": {"bound": "hbm", "kernel": "gemv_q4_K_kernel<1,0> / gemv_q4_K_stream_kernel (Q4_K decode mat-mul)",
                      "achieved": kern_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": kern_gbs / peak,
-                     "traffic": None, "per_shape": per_shape},
+                     # bytes per step (the four launches): the ncu capture of the 14336 x 4096 launch read and wrote
+                     # 33.05 MB of DRAM for 33.03 MB algorithmic (profiles/gemv_q4_K_decode_first_kernel.md); weights are
+                     # read once whatever the shape, so the step's traffic is its algorithmic bytes times that ratio
+                     "traffic": total * NCU_TRAFFIC_RATIO, "traffic_source": "ncu capture of one shape, scaled by algorithmic bytes",
+                     "per_shape": per_shape},
     }
 
 

@@ -132,6 +132,12 @@ int b200_mul_mat_q8(int type, int64_t n, int64_t k, int64_t m, const void *dev_w
  * (crates/llama/src/graph_arch.rs:209,226; crates/ggml/src/compute.rs:1174) without a second kernel. */
 int b200_mul_mat_q8_add(int type, int64_t n, int64_t k, const void *dev_w, const void *dev_act, int act_kind, float *dev_dst,
                         const float *dev_addend, float *dev_sum, int route, void *stream);
+/* b200_mul_mat_q8 for one activation row against up to three Q4_K matrices of the same k in one launch
+ * (dev_dst[i][n[i]] = W_i x): the k / v / q mat-muls of an attention block and the gate / up mat-muls of an
+ * FFN read the same normed row (crates/llama/src/graph_arch.rs:171-190,1137-1151), and at one token each of
+ * them is a few microseconds of launch latency.  Every n[i] must take the 8x8 gemv route (a multiple of 8). */
+int b200_mul_mat_q8_multi(int type, int64_t k, int count, const int64_t *n, const void *const *dev_w, const void *dev_act,
+                          int act_kind, float *const *dev_dst, void *stream);
 /* same op with host activations / results: copies X in, runs, copies dst out */
 int b200_mul_mat_host(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, const float *host_x,
                       float *host_dst, int route, void *stream);

@@ -208,7 +208,11 @@ int ggml_backend_score(void);
  *   "b200_backend_get_stream": void *(*)(ggml_backend_t) — the cudaStream_t the backend launches on, for
  *   callers that time graph_compute with events or order their own work after it.
  * init_backend's params string takes "cpu_threads=<n>" and "silu_wide=<0|1>" (which host's SILU to
- * reproduce, see b200_silu in ggml_b200.h; default: this host's). */
+ * reproduce, see b200_silu in ggml_b200.h; default: this host's), and three switches for launch-level
+ * fusions that change no result, for side-by-side measurements: "cuda_graphs=0" (no capture / replay of
+ * repeated node lists), "fuse_siblings=0" (one launch per one-row mat-mul even when several read the same
+ * activations), "fuse_glue=0" (one launch per ROPE / SET_ROWS node).  The environment variables
+ * B200_CUDA_GRAPHS, B200_FUSE_SIBLINGS and B200_FUSE_GLUE set to 0 do the same for every backend. */
 
 #ifdef __cplusplus
 }

@@ -382,6 +382,21 @@ int b200_mul_mat_q8(int type, int64_t n, int64_t k, int64_t m, const void *dev_w
     return launch_gemv(type, route, n, k, m, (const uint8_t *)dev_w, a.view(), dev_dst, lddst, (cudaStream_t)stream);
 }
 
+int b200_mul_mat_q8_multi(int type, int64_t k, int count, const int64_t *n, const void *const *dev_w, const void *dev_act, int act_kind,
+                          float *const *dev_dst, void *stream) {
+    B200_REQUIRE(type == B200_TYPE_Q4_K, "mul_mat_q8_multi: weight type %d is not supported (Q4_K only)", type);
+    B200_REQUIRE(count >= 1 && count <= 3 && n && dev_w && dev_dst && dev_act, "mul_mat_q8_multi: bad arguments");
+    for (int i = 0; i < count; i++) {
+        int rc = check_mul_mat_args(type, n[i], k, 1);
+        if (rc != B200_STATUS_SUCCESS) return rc;
+        B200_REQUIRE(pick_route(type, n[i], 1) == B200_ROUTE_REPACK, "mul_mat_q8_multi: matrix %d (%lld rows) does not take the 8x8 gemv route",
+                     i, (long long)n[i]);
+    }
+    B200_REQUIRE(act_kind == act_kind_for(type, B200_ROUTE_REPACK, 1), "mul_mat_q8_multi: activation kind %d does not fit type %d", act_kind, type);
+    ActView a = act_carve(const_cast<void *>(dev_act), 1, k).view();
+    return launch_gemv_q4_K_multi(count, n, (const uint8_t *const *)dev_w, dev_dst, k, a, (cudaStream_t)stream);
+}
+
 int b200_mul_mat_q8_add(int type, int64_t n, int64_t k, const void *dev_w, const void *dev_act, int act_kind, float *dev_dst,
                         const float *dev_addend, float *dev_sum, int route, void *stream) {
     int rc = check_mul_mat_args(type, n, k, 1);

@@ -118,6 +118,8 @@ struct BackendCtx {
     std::vector<CapturedGraph> captured;
     uint64_t generation = 0;
     bool graphs_enabled = true;
+    bool fuse_glue = true;          // one launch for neighbouring ROPE / SET_ROWS nodes (B200_FUSE_GLUE=0 / fuse_glue=0: off)
+    bool fuse_siblings = true;      // one launch for one-row Q4_K mat-muls over the same activations (B200_FUSE_SIBLINGS=0 / fuse_siblings=0: off)
     bool capturable = true;       // cleared by a node that had to talk to the device while being issued
 };
 constexpr size_t SHADOW_MAX_BYTES = 1 << 20;
@@ -406,6 +408,9 @@ static bool ranges_overlap(const void *a, size_t an, const void *b, size_t bn) {
     return a0 < b0 + bn && b0 < a0 + an;
 }
 
+static int quantized_acts(BackendCtx *bc, const float *x, int64_t ldx, int64_t m, int64_t k, int kind);
+static bool fuses_mul_mat_add(const ggml_tensor *mm, const ggml_tensor *add);
+
 // MUL_MAT over one 2-d slice; consecutive mat-muls that read the same rows with the same quantizer
 // (q, k, v of a layer; gate and up of an FFN) share one quantization pass.
 static int mul_mat_2d(BackendCtx *bc, const ggml_tensor *w, const float *x, int64_t ldx, int64_t m, float *dst, int64_t lddst,
@@ -414,6 +419,14 @@ static int mul_mat_2d(BackendCtx *bc, const ggml_tensor *w, const float *x, int6
     const int route = pick_route(w->type, n, m);
     const int kind = act_kind_for(w->type, route, m);
     if (bc->act_src && ranges_overlap(dst, (size_t)lddst * m * 4, bc->act_src, (size_t)bc->act_ld * bc->act_m * 4)) bc->act_src = nullptr;
+    int rc = quantized_acts(bc, x, ldx, m, k, kind);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    if (sum) return b200_mul_mat_q8_add(w->type, n, k, w->data, bc->act, kind, dst, addend, sum, route, bc->stream);
+    return b200_mul_mat_q8(w->type, n, k, m, w->data, bc->act, kind, dst, lddst, route, bc->stream);
+}
+
+// the quantized copy of activation rows x in bc->act, made now unless the previous mat-mul left the same one
+static int quantized_acts(BackendCtx *bc, const float *x, int64_t ldx, int64_t m, int64_t k, int kind) {
     if (!(bc->act_src == x && bc->act_m == m && bc->act_k == k && bc->act_ld == ldx && bc->act_kind == kind)) {
         const size_t need = b200_act_scratch_nbytes(m, k);
         if (need > bc->act_bytes) {
@@ -429,8 +442,67 @@ static int mul_mat_2d(BackendCtx *bc, const ggml_tensor *w, const float *x, int6
         if (rc != B200_STATUS_SUCCESS) return rc;
         bc->act_src = x; bc->act_m = m; bc->act_k = k; bc->act_ld = ldx; bc->act_kind = kind;
     }
-    if (sum) return b200_mul_mat_q8_add(w->type, n, k, w->data, bc->act, kind, dst, addend, sum, route, bc->stream);
-    return b200_mul_mat_q8(w->type, n, k, m, w->data, bc->act, kind, dst, lddst, route, bc->stream);
+    return B200_STATUS_SUCCESS;
+}
+
+// Sibling mat-muls: at one token the k, v and q projections of a layer (and the gate and up projections of its
+// FFN) read the same normed row, each through a launch of a few microseconds.  From a one-row Q4_K mat-mul at
+// node i, looks a few nodes ahead for other one-row Q4_K mat-muls over the same activation tensor that may run
+// early: no node in between touches the sibling's result memory (graph allocators recycle it) or rewrites the
+// activations, and the sibling is not itself waiting to be fused with a residual ADD.  Returns how many were
+// found (at most 2), their node indices in sib[].
+static bool multi_candidate(const ggml_tensor *mm) {
+    const ggml_tensor *w = mm->src[0], *x = mm->src[1];
+    return mm->op == GGML_OP_MUL_MAT && w && x && w->type == B200_TYPE_Q4_K && w->ne[2] == 1 && w->ne[3] == 1 && w->ne[1] % 8 == 0 &&
+           x->ne[1] == 1 && x->ne[2] == 1 && x->ne[3] == 1 && mm->data && supports_mul_mat(mm, nullptr);
+}
+static int find_sibling_mat_muls(const ggml_cgraph *g, int i, int *sib) {
+    const ggml_tensor *first = g->nodes[i];
+    if (!multi_candidate(first)) return 0;
+    const ggml_tensor *x = first->src[1];
+    int found = 0;
+    for (int j = i + 1; j < g->n_nodes && j <= i + 12 && found < 2; j++) {
+        const ggml_tensor *t = g->nodes[j];
+        if (!t) break;
+        const bool alias = t->op == GGML_OP_NONE || t->op == GGML_OP_RESHAPE || t->op == GGML_OP_VIEW || t->op == GGML_OP_PERMUTE ||
+                           t->op == GGML_OP_TRANSPOSE;
+        if (!alias && t->data && ranges_overlap(t->data, ggml_nbytes(t), x->data, ggml_nbytes(x))) break;   // the activations change here
+        if (alias || !multi_candidate(t) || t->src[1] != x) continue;
+        const ggml_tensor *after = j + 1 < g->n_nodes ? g->nodes[j + 1] : nullptr;
+        if (after && fuses_mul_mat_add(t, after)) continue;
+        if (ranges_overlap(t->data, ggml_nbytes(t), first->data, ggml_nbytes(first))) continue;
+        bool free_to_move = true;
+        for (int b = i + 1; b < j && free_to_move; b++) {
+            const ggml_tensor *mid = g->nodes[b];
+            if (!mid) continue;
+            if (mid->data && ranges_overlap(mid->data, ggml_nbytes(mid), t->data, ggml_nbytes(t))) free_to_move = false;
+            for (int s = 0; s < GGML_MAX_SRC && free_to_move; s++)
+                if (mid->src[s] && mid->src[s]->data && ranges_overlap(mid->src[s]->data, ggml_nbytes(mid->src[s]), t->data, ggml_nbytes(t)))
+                    free_to_move = false;
+        }
+        for (int e = 0; e < found && free_to_move; e++)
+            if (ranges_overlap(g->nodes[sib[e]]->data, ggml_nbytes(g->nodes[sib[e]]), t->data, ggml_nbytes(t))) free_to_move = false;
+        if (free_to_move) sib[found++] = j;
+    }
+    return found;
+}
+static int compute_mul_mat_multi(BackendCtx *bc, const ggml_cgraph *g, int i, const int *sib, int n_sib) {
+    const ggml_tensor *x = g->nodes[i]->src[1];
+    const int64_t k = x->ne[0];
+    const int kind = act_kind_for(B200_TYPE_Q4_K, B200_ROUTE_REPACK, 1);
+    int64_t n[3];
+    const void *w[3];
+    float *dst[3];
+    for (int e = 0; e <= n_sib; e++) {
+        const ggml_tensor *mm = g->nodes[e == 0 ? i : sib[e - 1]];
+        n[e] = mm->src[0]->ne[1];
+        w[e] = mm->src[0]->data;
+        dst[e] = (float *)mm->data;
+        if (bc->act_src && ranges_overlap(mm->data, ggml_nbytes(mm), bc->act_src, (size_t)bc->act_ld * bc->act_m * 4)) bc->act_src = nullptr;
+    }
+    int rc = quantized_acts(bc, (const float *)x->data, (int64_t)(x->nb[1] / 4), 1, k, kind);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    return b200_mul_mat_q8_multi(B200_TYPE_Q4_K, k, n_sib + 1, n, w, bc->act, kind, dst, bc->stream);
 }
 
 // fused: a one-row mat-mul whose result the next node adds to a tensor of the same shape (the residual)
@@ -726,6 +798,122 @@ static int compute_set_rows(BackendCtx *bc, const ggml_tensor *op) {
     return b200_set_rows_f16((const float *)x->data, (int64_t)(x->nb[1] / 4), (const int64_t *)idx->data, op->data,
                              (int64_t)(op->nb[1] / 2), op->ne[1], x->ne[0], x->ne[1], bc->stream);
 }
+// ---- ROPE / SET_ROWS nodes that share a launch (glue_batch_kernel) ------------------------------------------
+static bool is_alias_op(const ggml_tensor *t) {
+    return t->op == GGML_OP_NONE || t->op == GGML_OP_RESHAPE || t->op == GGML_OP_VIEW || t->op == GGML_OP_PERMUTE || t->op == GGML_OP_TRANSPOSE;
+}
+// a ROPE served from a by-position table (no frequency factors, positions the table covers: rope_prepare saw to it)
+static bool glue_rope_op(BackendCtx *bc, const ggml_tensor *op, GlueOp *o) {
+    const ggml_tensor *x = op->src[0], *pos = op->src[1];
+    if (op->src[2] || x->ne[0] == 0 || x->ne[1] == 0 || x->ne[2] == 0 || x->ne[3] != 1) return false;
+    const int mode = op->op_params[2];
+    if (mode != 0 && mode != 2) return false;
+    const std::vector<int32_t> key = rope_param_key(op, std::vector<float>());
+    for (auto &t : bc->rope_by_pos)
+        if (t.key == key && t.dev) {
+            *o = GlueOp{};
+            o->kind = GLUE_ROPE;
+            o->ne0 = (int)x->ne[0];
+            o->n_head = (int)x->ne[1];
+            o->n_dims = op->op_params[1];
+            o->neox = mode == 2;
+            o->total = x->ne[2] * x->ne[1] * (x->ne[0] / 2);
+            o->x = (const float *)x->data;
+            o->x_nb1 = (int64_t)x->nb[1];
+            o->x_nb2 = (int64_t)x->nb[2];
+            o->y = (float *)op->data;
+            o->y_nb1 = (int64_t)op->nb[1];
+            o->y_nb2 = (int64_t)op->nb[2];
+            o->table = t.dev;
+            o->rows = (const int32_t *)pos->data;
+            o->n_rows = t.rows;
+            return true;
+        }
+    return false;
+}
+static void glue_set_rows_op(const ggml_tensor *op, GlueOp *o) {
+    const ggml_tensor *x = op->src[0], *idx = op->src[1];
+    *o = GlueOp{};
+    o->kind = GLUE_SET_ROWS;
+    o->ne0 = (int)x->ne[0];
+    o->total = x->ne[0] * x->ne[1];
+    o->x = (const float *)x->data;
+    o->x_nb1 = (int64_t)(x->nb[1] / 4);
+    o->cache = op->data;
+    o->cache_stride = (int64_t)(op->nb[1] / 2);
+    o->cache_rows = op->ne[1];
+    o->cache_idx = (const int64_t *)idx->data;
+}
+// From node i (a ROPE or a SET_ROWS) on, the nodes that can run in one launch: ROPEs served from a table,
+// SET_ROWS that read one of those ROPEs' whole result (they ride with it) or something the batch does not write,
+// none of them reading or overwriting what an earlier member writes.  members[] = the node indices taken.
+struct TensorRange {
+    const void *p;
+    size_t n;
+};
+static int gather_glue_batch(BackendCtx *bc, const ggml_cgraph *g, int i, const std::vector<char> &done, GlueBatch *b, int *members) {
+    b->count = 0;
+    int n_members = 0;
+    std::vector<TensorRange> ins, outs;
+    const ggml_tensor *rope_node[GLUE_BATCH_MAX] = {nullptr, nullptr, nullptr, nullptr};
+    for (int j = i; j < g->n_nodes && n_members < 2 * GLUE_BATCH_MAX; j++) {
+        const ggml_tensor *t = g->nodes[j];
+        if (!t) break;
+        if (done[j] || is_alias_op(t)) continue;
+        if ((t->op != GGML_OP_ROPE && t->op != GGML_OP_SET_ROWS) || !op_supported(t, nullptr) || !t->data) break;
+        std::vector<TensorRange> t_in, t_out;
+        for (int s = 0; s < GGML_MAX_SRC; s++)
+            if (t->src[s] && t->src[s]->data) t_in.push_back({t->src[s]->data, ggml_nbytes(t->src[s])});
+        t_out.push_back({t->data, ggml_nbytes(t)});
+        int ride = -1;   // a SET_ROWS that takes a member ROPE's result as it is made
+        if (t->op == GGML_OP_SET_ROWS) {
+            const ggml_tensor *x = t->src[0];
+            for (int e = 0; e < b->count; e++) {
+                const GlueOp &r = b->op[e];
+                if (r.kind == GLUE_ROPE && !r.cache && rope_node[e] && x->data == rope_node[e]->data && x->ne[0] == (int64_t)r.ne0 * r.n_head &&
+                    (int64_t)x->nb[1] == x->ne[0] * 4 && r.y_nb1 == (int64_t)r.ne0 * 4 && r.y_nb2 == x->ne[0] * 4 &&
+                    x->ne[1] * x->ne[0] == r.total * 2)
+                    ride = e;
+            }
+        }
+        // what this node reads must not be written by the batch (other than the ROPE it rides with), and what it
+        // writes must not be read or written by the batch
+        bool clash = false;
+        for (const TensorRange &a : t_in)
+            for (const TensorRange &o : outs)
+                if (ranges_overlap(a.p, a.n, o.p, o.n) && !(ride >= 0 && o.p == rope_node[ride]->data)) clash = true;
+        for (const TensorRange &a : t_out) {
+            for (const TensorRange &o : outs)
+                if (ranges_overlap(a.p, a.n, o.p, o.n)) clash = true;
+            for (const TensorRange &o : ins)
+                if (ranges_overlap(a.p, a.n, o.p, o.n)) clash = true;
+        }
+        if (clash) break;
+        if (ride >= 0) {
+            GlueOp s;
+            glue_set_rows_op(t, &s);
+            b->op[ride].cache = s.cache;
+            b->op[ride].cache_stride = s.cache_stride;
+            b->op[ride].cache_rows = s.cache_rows;
+            b->op[ride].cache_idx = s.cache_idx;
+        } else {
+            if (b->count == GLUE_BATCH_MAX) break;
+            GlueOp o;
+            if (t->op == GGML_OP_ROPE) {
+                if (!glue_rope_op(bc, t, &o)) break;
+                rope_node[b->count] = t;
+            } else {
+                glue_set_rows_op(t, &o);
+            }
+            b->op[b->count++] = o;
+        }
+        ins.insert(ins.end(), t_in.begin(), t_in.end());
+        outs.insert(outs.end(), t_out.begin(), t_out.end());
+        members[n_members++] = j;
+    }
+    return n_members;
+}
+
 static int compute_get_rows(BackendCtx *bc, const ggml_tensor *op) {
     const ggml_tensor *t = op->src[0], *ids = op->src[1];
     if (!is_quant_type(t->type)) {
@@ -766,9 +954,11 @@ static int find_silu_mul(const ggml_cgraph *g, int i) {
 static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
     bc->act_src = nullptr;   // tensors may have been rewritten between graphs
     std::vector<int> silu_of(g->n_nodes, -1);   // silu_of[j] = i: MUL node j also computes SILU node i
+    std::vector<char> done(g->n_nodes, 0);      // mat-mul nodes that ran early, with a sibling
     for (int i = 0; i < g->n_nodes; i++) {
         const ggml_tensor *op = g->nodes[i];
         B200_REQUIRE(op != nullptr, "graph_compute: node %d is null", i);
+        if (done[i]) continue;
         std::string why;
         if (!op_supported(op, &why)) {
             set_error("graph_compute: node %d '%s' (op %d) is not supported: %s", i, op->name, op->op, why.c_str());
@@ -798,7 +988,14 @@ static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
                     rc = compute_mul_mat_add(bc, op, next);
                     i++;
                 } else {
-                    rc = compute_mul_mat(bc, op);
+                    int sib[2];
+                    const int n_sib = bc->fuse_siblings ? find_sibling_mat_muls(g, i, sib) : 0;
+                    if (n_sib > 0) {
+                        rc = compute_mul_mat_multi(bc, g, i, sib, n_sib);
+                        for (int e = 0; e < n_sib; e++) done[sib[e]] = 1;
+                    } else {
+                        rc = compute_mul_mat(bc, op);
+                    }
                 }
                 break;
             case GGML_OP_MUL_MAT_ID: rc = compute_mul_mat_id(bc, op); break;
@@ -830,8 +1027,24 @@ static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
                 }
                 break;
             case GGML_OP_ADD: rc = compute_binary(bc, op); break;
-            case GGML_OP_ROPE: rc = compute_rope(bc, op); break;
-            case GGML_OP_SET_ROWS: rc = compute_set_rows(bc, op); break;
+            case GGML_OP_ROPE:
+            case GGML_OP_SET_ROWS: {
+                GlueBatch gb;
+                int members[2 * GLUE_BATCH_MAX];
+                const int nm = bc->fuse_glue ? gather_glue_batch(bc, g, i, done, &gb, members) : 0;
+                if (nm >= 2) {
+                    for (int e = 0; e < nm; e++) {
+                        const ggml_tensor *mem = g->nodes[members[e]];
+                        if (bc->act_src && ranges_overlap(mem->data, ggml_nbytes(mem), bc->act_src, (size_t)bc->act_ld * bc->act_m * 4))
+                            bc->act_src = nullptr;
+                        if (members[e] != i) done[members[e]] = 1;
+                    }
+                    rc = launch_glue_batch(gb, bc->stream);
+                } else {
+                    rc = op->op == GGML_OP_ROPE ? compute_rope(bc, op) : compute_set_rows(bc, op);
+                }
+                break;
+            }
             case GGML_OP_GET_ROWS: rc = compute_get_rows(bc, op); break;
             case GGML_OP_ARGMAX: rc = compute_argmax(bc, op); break;
             default: break;
@@ -858,6 +1071,8 @@ static uint64_t node_list_key(const BackendCtx *bc, const ggml_cgraph *g) {
     uint64_t h = 0xcbf29ce484222325ull;
     h = fnv(h, &bc->cpu_threads, sizeof(int));
     h = fnv(h, &bc->silu_wide, sizeof(int));
+    h = fnv(h, &bc->fuse_siblings, sizeof(bool));
+    h = fnv(h, &bc->fuse_glue, sizeof(bool));
     h = fnv(h, &g->n_nodes, sizeof(int));
     for (int i = 0; i < g->n_nodes; i++) {
         const ggml_tensor *t = g->nodes[i];
@@ -1013,6 +1228,10 @@ static ggml_backend_t dev_init_backend(ggml_backend_dev_t d, const char *params)
     {
         const char *e = getenv("B200_CUDA_GRAPHS");
         if (e && e[0] == '0') bc->graphs_enabled = false;
+        const char *fs = getenv("B200_FUSE_SIBLINGS");
+        if (fs && fs[0] == '0') bc->fuse_siblings = false;
+        const char *fg = getenv("B200_FUSE_GLUE");
+        if (fg && fg[0] == '0') bc->fuse_glue = false;
     }
     if (cudaStreamCreateWithFlags(&bc->stream, cudaStreamNonBlocking) != cudaSuccess) {
         cudaGetLastError();
@@ -1030,6 +1249,10 @@ static ggml_backend_t dev_init_backend(ggml_backend_dev_t d, const char *params)
         if (p) bc->silu_wide = atoi(p + 10) != 0;
         p = strstr(params, "cuda_graphs=");
         if (p) bc->graphs_enabled = atoi(p + 12) != 0;
+        p = strstr(params, "fuse_siblings=");
+        if (p) bc->fuse_siblings = atoi(p + 14) != 0;
+        p = strstr(params, "fuse_glue=");
+        if (p) bc->fuse_glue = atoi(p + 10) != 0;
     }
     ggml_backend *be = new ggml_backend();
     memset(&be->iface, 0, sizeof(be->iface));

@@ -136,6 +136,32 @@ int launch_gemm_mma(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *ti
                     cudaStream_t s);
 int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
                         cudaStream_t s);
+// up to four ROPE / SET_ROWS (F32 -> F16) nodes for one launch, see glue_batch_kernel
+constexpr int GLUE_BATCH_MAX = 4;
+enum { GLUE_ROPE = 1, GLUE_SET_ROWS = 2 };
+struct GlueOp {
+    int kind;
+    int ne0;                 // ROPE: head size; SET_ROWS: row length
+    int n_head, n_dims, neox;
+    int64_t total;           // ROPE: tokens x heads x ne0 / 2 channel pairs; SET_ROWS: rows x ne0 elements
+    const float *x;          // source
+    int64_t x_nb1, x_nb2;    // ROPE: byte strides of head and token; SET_ROWS: x_nb1 = row stride in elements
+    float *y;                // ROPE result
+    int64_t y_nb1, y_nb2;
+    const float *table;      // ROPE (cos, sin) table, one row per position (rows != null) or per token
+    const int32_t *rows;
+    int64_t n_rows;
+    void *cache;            // SET_ROWS destination; ROPE: optional F16 rows that receive the rounded result
+    int64_t cache_stride, cache_rows;
+    const int64_t *cache_idx;
+};
+struct GlueBatch {
+    GlueOp op[GLUE_BATCH_MAX];
+    int count;
+};
+int launch_glue_batch(const GlueBatch &b, cudaStream_t s);
+int launch_gemv_q4_K_multi(int count, const int64_t *n, const uint8_t *const *tiles, float *const *dst, int64_t k, ActView acts,
+                           cudaStream_t s);
 int launch_gemv_q4_K_stream(int64_t n, int64_t k, const uint8_t *tiles, ActView acts, float *dst, cudaStream_t s);
 int gemv_stream_error(int *code);
 int device_error_word(int **flag);

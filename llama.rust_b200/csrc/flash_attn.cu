@@ -546,6 +546,7 @@ static int check_args(const b200_flash_attn_args *a) {
 }
 
 int flash_attn_faithful_tiled(const b200_flash_attn_args *a, cudaStream_t s);   // flash_attn_tiled.cu
+bool flash_attn_decode_head(const b200_flash_attn_args *a, int n_chunks, int64_t chunk, cudaStream_t s, int *rc);   // flash_attn_head.cu
 
 // B200_FA_DECODE_FUSED=0 keeps single-row attention on the three-kernel path (for side-by-side measurements)
 static bool fa_decode_one_kernel_enabled() {
@@ -571,6 +572,10 @@ int flash_attn_faithful_rows(const b200_flash_attn_args *a, cudaStream_t s) {
         return B200_STATUS_SUCCESS;
     }
     B200_REQUIRE(d.T <= 65535 && d.H <= 65535, "flash_attn_ext: too many rows for one launch");
+    if (d.T == 1 && split) {   // a chat-length context: one CTA per head, one warp per chunk
+        int rc = B200_STATUS_SUCCESS;
+        if (flash_attn_decode_head(a, d.n_chunks, d.chunk, s, &rc)) return rc;
+    }
     if (d.T == 1 && d.H <= FA_DECODE_MAX_HEADS && fa_decode_one_kernel_enabled()) return flash_attn_decode_one_kernel(a, d, split, s);
     const size_t score_b = ((size_t)rows * d.n_kv * 4 + 255) / 256 * 256;
     const size_t part_b = (size_t)rows * d.n_chunks * (2 + d.dv) * 4;

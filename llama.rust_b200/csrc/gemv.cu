@@ -29,6 +29,15 @@ struct PairMap {
     int64_t expert_bytes;
     const int *counts;       // rows routed to each expert, or null
     int min_count, max_count;
+    // plain MUL_MAT over several matrices that read the same activation row (k, v, q of a layer; gate and up of
+    // an FFN) in one launch: blockIdx.x walks the row tiles of all of them, segment 0 being the kernel's own
+    // tiles / dst / n arguments and segments 1.. the ones below
+    int seg_count;           // 0 or 1: a single matrix
+    int seg_end[2];          // first tile of segment 1 and of segment 2 (INT_MAX: no segment 2)
+    int seg_total;           // tiles of all segments
+    const uint8_t *seg_tiles[2];
+    float *seg_dst[2];
+    int64_t seg_n[2];
 };
 
 __device__ __forceinline__ bool apply_pair(const PairMap &pm, const uint8_t *&tiles, ActView &acts, float *&dst,
@@ -73,12 +82,25 @@ gemv_q4_K_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, 
     pdl_trigger();
     if (pm.ids) pdl_wait();   // the expert ids come from a previous kernel
     if (!apply_pair(pm, tiles, acts, dst, lddst)) return;
+    int tile = blockIdx.x;
+    if (pm.seg_count > 1) {   // constant indices only: the segment table stays in the parameter bank
+        if (tile >= pm.seg_end[1]) {
+            tile -= pm.seg_end[1];
+            tiles = pm.seg_tiles[1];
+            dst = pm.seg_dst[1];
+            n = pm.seg_n[1];
+        } else if (tile >= pm.seg_end[0]) {
+            tile -= pm.seg_end[0];
+            tiles = pm.seg_tiles[0];
+            dst = pm.seg_dst[0];
+            n = pm.seg_n[0];
+        }
+    }
     bool waited = pm.ids != nullptr;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     Q4KStage *stage = (Q4KStage *)smem + warp * NCOL;
     constexpr int XW = MODE == 1 ? 3 : 1;                           // int4 words per (col, group, row)
     int4 *xch = (int4 *)(smem + sizeof(Q4KStage) * nwarps * NCOL);  // [NCOL][nb][XW][32]
-    const int64_t tile = blockIdx.x;
     const uint8_t *base = tiles + tile * (int64_t)nb * 4608;
 
     for (int b = warp; b < nb; b += nwarps) {
@@ -187,7 +209,7 @@ gemv_q4_K_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, 
                 }
             }
         }
-        const int64_t row = tile * TILE_ROWS + r;
+        const int64_t row = (int64_t)tile * TILE_ROWS + r;
         if (row < n) {
             const float v = MODE == 2 ? sumf : __fsub_rn(sumf, summin);
             dst[(int64_t)col * lddst + row] = v;
@@ -214,10 +236,35 @@ static int launch_q4k(int64_t n, int nb, const uint8_t *tiles, ActView acts, flo
         B200_CUDA(cudaFuncSetAttribute(gemv_q4_K_kernel<NCOL, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_done = true;
     }
-    const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
+    const int64_t tiles_n = pm.seg_count > 1 ? pm.seg_total : (n + TILE_ROWS - 1) / TILE_ROWS;
     B200_REQUIRE(pairs >= 1 && pairs <= 65535, "mul_mat_id: %lld (token, slot) pairs exceed one launch", (long long)pairs);
     return launch_pdl(gemv_q4_K_kernel<NCOL, MODE>, dim3((unsigned)tiles_n, (unsigned)pairs), dim3(nw * 32), smem, s, tiles,
                       acts, dst, lddst, n, nb, pm);
+}
+
+// One activation row against up to three Q4_K matrices of the same K (8x8 gemv chain): one launch whose CTAs
+// walk the row tiles of all of them.  Every output element is computed exactly as by a launch of its own.
+int launch_gemv_q4_K_multi(int count, const int64_t *n, const uint8_t *const *tiles, float *const *dst, int64_t k, ActView acts,
+                           cudaStream_t s) {
+    B200_REQUIRE(count >= 1 && count <= 3, "mul_mat multi: %d matrices (1 to 3 fit one launch)", count);
+    B200_REQUIRE(k % GROUP_K == 0, "mul_mat multi: k = %lld must be a multiple of 256", (long long)k);
+    PairMap pm = PairMap{};
+    pm.seg_count = count;
+    pm.seg_end[1] = 0x7fffffff;   // "no third matrix"
+    int64_t end = 0;
+    for (int i = 0; i < count; i++) {
+        B200_REQUIRE(n[i] > 0 && tiles[i] && dst[i], "mul_mat multi: matrix %d is empty or null", i);
+        end += (n[i] + TILE_ROWS - 1) / TILE_ROWS;
+        B200_REQUIRE(end < 0x7fffffffLL, "mul_mat multi: too many rows for one launch");
+        if (i + 1 < count) pm.seg_end[i] = (int)end;
+        if (i > 0) {
+            pm.seg_tiles[i - 1] = tiles[i];
+            pm.seg_dst[i - 1] = dst[i];
+            pm.seg_n[i - 1] = n[i];
+        }
+    }
+    pm.seg_total = (int)end;
+    return launch_q4k<1, 0>(n[0], (int)(k / GROUP_K), tiles[0], acts, dst[0], n[0], s, pm);
 }
 
 // ---------------------------------------------------------------------------

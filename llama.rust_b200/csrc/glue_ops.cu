@@ -325,6 +325,92 @@ int launch_set_rows_f16(const float *x, int64_t x_stride, const int64_t *idx, vo
                       dst_rows, (int)ne0, total, err);
 }
 
+// ---- several ROPE / SET_ROWS nodes in one launch ------------------------------------------------------
+// At one token the attention block's glue is four kernels of a few thousand elements each: ROPE of K, SET_ROWS
+// of K into the cache, SET_ROWS of V, ROPE of Q (crates/llama/src/graph_arch.rs:171-190, 1173-1240).  They are
+// independent of one another once the SET_ROWS of K reads the rotated values straight from the ROPE that
+// made them, so blockIdx.y walks up to four of them.  Element for element the arithmetic is rope_kernel's and
+// set_rows_f16_kernel's: a ROPE with a cache attached stores the f32 result and its f16 rounding.
+__global__ void __launch_bounds__(256)
+glue_batch_kernel(GlueBatch b, int *err) {
+    pdl_trigger();
+    pdl_wait();
+    const GlueOp &o = b.op[blockIdx.y];
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= o.total) return;
+    if (o.kind == GLUE_SET_ROWS) {
+        const int64_t r = i / o.ne0;
+        const int c = (int)(i - r * o.ne0);
+        const int64_t d = o.cache_idx[r];
+        if (d < 0 || d >= o.cache_rows) {
+            if (c == 0) atomicExch(err, 2);
+            return;
+        }
+        ((__half *)o.cache)[d * o.cache_stride + c] = __float2half_rn(o.x[r * o.x_nb1 + c]);
+        return;
+    }
+    const int half = o.ne0 / 2;
+    const int p = (int)(i % half);
+    const int64_t row = i / half;
+    const int h = (int)(row % o.n_head);
+    const int64_t t = row / o.n_head;
+    const float *src = (const float *)((const char *)o.x + h * o.x_nb1 + t * o.x_nb2);
+    float *dst = (float *)((char *)o.y + h * o.y_nb1 + t * o.y_nb2);
+    const int i0 = 2 * p;
+    const int64_t tr = o.rows ? (int64_t)o.rows[t] : t;
+    if (tr < 0 || tr >= o.n_rows) {
+        if (p == 0 && h == 0) atomicExch(err, 3);
+        return;
+    }
+    float v0, v1;
+    int e0, e1;
+    if (i0 < o.n_dims) {
+        e0 = o.neox ? p : i0;
+        e1 = e0 + (o.neox ? o.n_dims / 2 : 1);
+        const float c = o.table[tr * o.ne0 + i0], s = o.table[tr * o.ne0 + i0 + 1];
+        const float x0 = src[e0], x1 = src[e1];
+        v0 = __fmaf_rn(x0, c, -__fmul_rn(x1, s));
+        v1 = __fmaf_rn(x0, s, __fmul_rn(x1, c));
+    } else {
+        e0 = i0;
+        e1 = i0 + 1;
+        v0 = src[e0];
+        v1 = src[e1];
+    }
+    dst[e0] = v0;
+    dst[e1] = v1;
+    if (o.cache) {
+        const int64_t d = o.cache_idx[t];
+        if (d < 0 || d >= o.cache_rows) {
+            if (p == 0 && h == 0) atomicExch(err, 2);
+            return;
+        }
+        __half *crow = (__half *)o.cache + d * o.cache_stride + (int64_t)h * o.ne0;
+        crow[e0] = __float2half_rn(v0);
+        crow[e1] = __float2half_rn(v1);
+    }
+}
+
+int launch_glue_batch(const GlueBatch &b, cudaStream_t s) {
+    B200_REQUIRE(b.count >= 1 && b.count <= GLUE_BATCH_MAX, "glue batch: %d operations", b.count);
+    int64_t most = 0;
+    for (int i = 0; i < b.count; i++) {
+        const GlueOp &o = b.op[i];
+        B200_REQUIRE(o.kind == GLUE_ROPE || o.kind == GLUE_SET_ROWS, "glue batch: operation %d has kind %d", i, o.kind);
+        B200_REQUIRE(o.ne0 > 0 && o.total >= 0, "glue batch: operation %d has a bad shape", i);
+        if (o.kind == GLUE_ROPE)
+            B200_REQUIRE(o.ne0 % 2 == 0 && o.n_dims > 0 && o.n_dims % 2 == 0 && o.n_dims <= o.ne0 && o.n_head > 0, "glue batch: bad rope shape");
+        most = o.total > most ? o.total : most;
+    }
+    if (most == 0) return B200_STATUS_SUCCESS;
+    const int64_t blocks = (most + 255) / 256;
+    B200_REQUIRE(blocks < 0x7fffffffLL, "glue batch: tensor too large for one launch");
+    int *err = nullptr;
+    int rc = device_error_word(&err);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    return launch_pdl(glue_batch_kernel, dim3((unsigned)blocks, (unsigned)b.count), dim3(256), 0, s, b, err);
+}
+
 // ---- GET_ROWS from F32 / F16 tables ------------------------------------------------------------------
 // crates/ggml/src/compute.rs:3842-3895 (the quantized tables go through get_rows_tiled_kernel).
 template <typename T>

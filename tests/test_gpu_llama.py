@@ -150,6 +150,29 @@ def test_argument_errors_are_statuses(ll):
         ll.Llama(bad, 256, 4)
 
 
+def test_launch_fusions_change_nothing(ll, monkeypatch):
+    """sibling mat-muls in one launch and ROPE / SET_ROWS in one launch (the defaults) against one launch per
+    node: the same logits, prompt batch and single-token steps, with and without CUDA graphs"""
+    tensors = make_model(ll, GQA128, 31)
+
+    def run():
+        gpu, _ = both(ll, GQA128, tensors, 512, 8)
+        outs = [gpu.decode([5, 6, 7, 8, 9], [0, 1, 2, 3, 4])]
+        for step in range(5):      # the third sight of a node list replays a captured graph
+            outs.append(gpu.decode([10 + step], [5 + step]))
+        gpu.close()
+        return outs
+
+    fused = run()
+    monkeypatch.setenv("B200_FUSE_SIBLINGS", "0")
+    monkeypatch.setenv("B200_FUSE_GLUE", "0")
+    plain = run()
+    monkeypatch.setenv("B200_CUDA_GRAPHS", "0")
+    eager = run()
+    for a, b, c in zip(fused, plain, eager):
+        assert bits_equal(a, b) and bits_equal(a, c)
+
+
 def test_gguf_file_loads_into_the_driver(ll, tmp_path):
     """a model written as a GGUF file and loaded by b200_llama_load_gguf answers like the same tensors set by hand"""
     gg = importlib.import_module("llama_rust_b200.gguf")

@@ -1,0 +1,55 @@
+"""b200_mul_mat_q8_multi: one activation row against several Q4_K matrices in one launch gives, element for
+element, what one launch per matrix gives (and so what the CPU route gives)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import b200
+import orc
+import synth
+from conftest import bits_equal
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    mod = b200.load()
+    assert mod.device_count() > 0, "no CUDA device"
+    mod.set_device(0)
+    return mod
+
+
+@pytest.mark.parametrize("rows", [(1024, 1024, 4096), (14336, 14336), (40, 8, 72), (4096,)], ids=str)
+def test_multi_equals_single_launches(dev, rows):
+    k = 4096 if max(rows) > 100 else 512
+    x = synth.activations(1, k, seed=5)
+    Ws = [synth.weights(orc.Q4_K, n, k, seed=10 + i, period=64) for i, n in enumerate(rows)]
+    ws = [dev.Weight(orc.Q4_K, W, k) for W in Ws]
+    dx = dev.device_array(x)
+    act = dev.DeviceBuffer(dev.lib.b200_act_scratch_nbytes(1, k))
+    dev.check(dev.lib.b200_quantize_activations_device(dev.ACT_Q8_K, 1, k, dx.ptr, k, act.ptr, None), "quantize")
+    outs = [dev.DeviceBuffer(4 * n) for n in rows]
+    count = len(rows)
+    n_arr = (C.c_int64 * count)(*rows)
+    w_arr = (C.c_void_p * count)(*[w.ptr for w in ws])
+    d_arr = (C.c_void_p * count)(*[o.ptr for o in outs])
+    dev.check(dev.lib.b200_mul_mat_q8_multi(orc.Q4_K, C.c_int64(k), count, n_arr, w_arr, C.c_void_p(act.ptr), dev.ACT_Q8_K, d_arr, None), "multi")
+    dev.synchronize()
+    for W, w, o, n in zip(Ws, ws, outs, rows):
+        got = o.download(np.float32, n)
+        single = dev.mul_mat(w, x)[0]
+        assert bits_equal(got, single)
+        if n <= 4096:
+            want, _ = orc.mul_mat(orc.Q4_K, W, x)
+            assert bits_equal(got, want[0])
+
+
+def test_refusals(dev):
+    n_arr = (C.c_int64 * 1)(36)
+    nul = (C.c_void_p * 1)(1)
+    rc = dev.lib.b200_mul_mat_q8_multi(orc.Q4_K, C.c_int64(512), 1, n_arr, nul, C.c_void_p(1), dev.ACT_Q8_K, nul, None)
+    assert rc != 0 and b"8x8 gemv route" in dev.lib.b200_last_error()
+    rc = dev.lib.b200_mul_mat_q8_multi(orc.Q6_K, C.c_int64(512), 1, n_arr, nul, C.c_void_p(1), dev.ACT_Q8_K, nul, None)
+    assert rc != 0 and b"Q4_K only" in dev.lib.b200_last_error()
