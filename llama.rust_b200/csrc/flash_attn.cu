@@ -481,25 +481,65 @@ fa_decode_kernel(b200_flash_attn_args a, FaDims d, float kq_scale, float *__rest
     __threadfence();
     if (tid == 0) counters[h] = 0;   // ready for the next launch
     const int e = tid;
-    if (e >= d.dv) return;
     const volatile float *p0 = partials + row * d.n_chunks * (2 + d.dv);
     if (!split) {
+        if (e >= d.dv) return;
         const float Sv = p0[1];
         const float s_inv = Sv == 0.0f ? 0.0f : __fdiv_rn(1.0f, Sv);
         a.dst[row * d.dv + e] = __fmul_rn(p0[2 + e], s_inv);
         return;
     }
+    // merge in chunk order (flash_attn.rs:744-859).  The exponentials depend only on the chunks' maxima: thread 0
+    // walks those (the running maximum before and after each chunk), thread c takes chunk c's two exponentials,
+    // and the value threads are left with the chain of fused multiply-adds.  so < 0 marks a chunk to skip.
+    float *so_s = ms_s, *sn_s = vs_s;   // the tile arrays are free now
+    const bool wide = d.n_chunks <= FA_TILE;
+    if (wide) {
+        if (tid == 0) {
+            float Mf = -INFINITY;
+            for (int cc = 0; cc < d.n_chunks; cc++) {
+                const volatile float *p = p0 + (int64_t)cc * (2 + d.dv);
+                const bool used = (int64_t)cc * d.chunk < d.n_kv && p[1] != 0.0f;
+                const float Mc = p[0];
+                const float Mn = used ? fmaxf(Mf, Mc) : Mf;
+                so_s[cc] = used ? __fsub_rn(Mf, Mn) : 1.0f;   // arguments of the exponentials; a positive one marks "skip"
+                sn_s[cc] = used ? __fsub_rn(Mc, Mn) : 1.0f;
+                Mf = Mn;
+            }
+        }
+        __syncthreads();
+        float eo = -1.0f, en = -1.0f;
+        if (tid < d.n_chunks && !(sn_s[tid] > 0.0f)) {
+            eo = libm_expf(so_s[tid]);
+            en = libm_expf(sn_s[tid]);
+        }
+        __syncthreads();
+        if (tid < d.n_chunks) {
+            so_s[tid] = eo;
+            sn_s[tid] = en;
+        }
+        __syncthreads();
+    }
+    if (e >= d.dv) return;
     float fin = 0.0f, Mf = -INFINITY, Sf = 0.0f;
     for (int cc = 0; cc < d.n_chunks; cc++) {
-        if ((int64_t)cc * d.chunk >= d.n_kv) continue;
         const volatile float *p = p0 + (int64_t)cc * (2 + d.dv);
-        const float Mc = p[0], Sc = p[1];
-        if (Sc == 0.0f) continue;
-        const float Mn = fmaxf(Mf, Mc);
-        const float so = libm_expf(__fsub_rn(Mf, Mn)), sn = libm_expf(__fsub_rn(Mc, Mn));
+        float so, sn;
+        if (wide) {
+            so = so_s[cc];
+            sn = sn_s[cc];
+            if (sn < 0.0f) continue;
+        } else {
+            if ((int64_t)cc * d.chunk >= d.n_kv) continue;
+            const float Mc = p[0];
+            if (p[1] == 0.0f) continue;
+            const float Mn = fmaxf(Mf, Mc);
+            so = libm_expf(__fsub_rn(Mf, Mn));
+            sn = libm_expf(__fsub_rn(Mc, Mn));
+            Mf = Mn;
+        }
         fin = __fmaf_rn(fin, so, __fmul_rn(p[2 + e], sn));
-        Sf = __fmaf_rn(Sf, so, __fmul_rn(Sc, sn));
-        Mf = Mn;
+        Sf = __fmaf_rn(Sf, so, __fmul_rn(p[1], sn));
     }
     if (Sf != 0.0f) fin = __fmul_rn(fin, __fdiv_rn(1.0f, Sf));
     a.dst[row * d.dv + e] = fin;

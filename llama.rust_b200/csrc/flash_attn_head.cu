@@ -243,12 +243,15 @@ fa_decode_head_kernel(b200_flash_attn_args a, int H, int H_kv, int64_t n_kv, int
     }
 }
 
-// B200_FA_DECODE_HEAD=0 keeps single-row split-KV attention on the CTA-per-chunk kernel
+// B200_FA_DECODE_HEAD=1 sends single-row split-KV attention here.  Measured inside the 8B-shaped decode step it
+// loses to the CTA-per-chunk kernel (2.79 against 2.40 ms per token at 768 cached positions): with one CTA per
+// head only 32 SMs work, and each lane's K row is 32 uncoalesced 16-byte loads that one SM's load pipe now
+// serves for all sixteen chunks.  It stays selectable until the K rows are staged through shared memory.
 static bool fa_decode_head_enabled() {
     static int v = -1;
     if (v < 0) {
         const char *e = getenv("B200_FA_DECODE_HEAD");
-        v = (e && e[0] == '0') ? 0 : 1;
+        v = (e && e[0] == '1') ? 1 : 0;
     }
     return v == 1;
 }

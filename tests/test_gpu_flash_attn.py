@@ -159,3 +159,17 @@ def test_softcap_and_sinks_within_tolerance(dev):
     got = dev.flash_attn(q, dev.KvCacheView(k, v), mask, 0.125, sinks=sinks, softcap=15.0)
     scale = np.abs(want).max(axis=-1, keepdims=True)
     assert (np.abs(got - want) <= REL_TOL * scale).all()
+
+
+def test_head_per_cta_kernel_passes_the_same_cases():
+    """the CTA-per-head split-KV kernel is selected by B200_FA_DECODE_HEAD=1, read once per process: run this
+    file's other tests in a child with it set"""
+    import os
+    import subprocess
+    import sys
+    if os.environ.get("B200_FA_DECODE_HEAD") == "1":
+        pytest.skip("already the child")
+    env = dict(os.environ, B200_FA_DECODE_HEAD="1")
+    r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-x", "-q", "-m", "gpu", "-p", "no:cacheprovider"], env=env,
+                       capture_output=True, text=True, timeout=1800)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
