@@ -25,6 +25,9 @@
 // Shared memory holds three operand stages, tensor memory two accumulator stages; all hand-offs are
 // mbarriers.  Every wait is bounded: a wait that runs out raises the CTA's abort flag and the device error
 // word, every role leaves its loop, and the CTA frees its tensor memory and returns.
+//
+// The second kernel in this file (gemm_q4_K_tcgen05_f16_kernel, further down) folds the sub-block scales into
+// f16 operands so that the MMA returns the chain's integers as f32 and the epilogue shrinks to two fmas.
 #include "common.cuh"
 
 namespace b200 {

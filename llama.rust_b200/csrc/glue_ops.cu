@@ -460,10 +460,25 @@ argmax_kernel(const float *__restrict__ x, int64_t x_stride, int32_t *out, int n
     const float *xr = x + (int64_t)blockIdx.x * x_stride;
     float best = -INFINITY;
     int at = -1;   // -1: nothing equal to the running maximum seen yet
-    for (int i = threadIdx.x; i < ne0; i += 1024) {
-        const float v = xr[i];
+    // (value, index) pairs merge the same way in any order (larger value, then larger index), so the row is
+    // read with 16-byte loads, several in flight per thread, when its length and address allow
+    auto take = [&](float v, int i) {
         if (v > best) { best = v; at = i; }
-        else if (v == best) at = i;
+        else if (v == best && i > at) at = i;
+    };
+    if ((ne0 & 3) == 0 && (((uintptr_t)xr) & 15) == 0) {
+        const float4 *x4 = (const float4 *)xr;
+        const int n4 = ne0 >> 2;
+#pragma unroll 4
+        for (int i = threadIdx.x; i < n4; i += 1024) {
+            const float4 v = x4[i];
+            take(v.x, 4 * i);
+            take(v.y, 4 * i + 1);
+            take(v.z, 4 * i + 2);
+            take(v.w, 4 * i + 3);
+        }
+    } else {
+        for (int i = threadIdx.x; i < ne0; i += 1024) take(xr[i], i);
     }
     __shared__ float sb[32];
     __shared__ int sa[32];
