@@ -42,7 +42,7 @@ struct Scratch {
     size_t bytes = 0;
 };
 static std::mutex g_scratch_mu;
-static Scratch g_scratch[64];
+static Scratch g_scratch[2][64];   // [0] general scratch, [1] the K-split exchange of the decode mat-mul (lives across the other's users)
 static unsigned long long g_scratch_gen = 0;
 
 // bumped whenever a scratch block is replaced: a captured CUDA graph that baked the old address in is stale
@@ -51,12 +51,15 @@ unsigned long long scratch_generation() {
     return g_scratch_gen;
 }
 
-int scratch_get(size_t bytes, void **ptr) {
+static int scratch_get_slot(int slot, size_t bytes, void **ptr);
+int scratch_get(size_t bytes, void **ptr) { return scratch_get_slot(0, bytes, ptr); }
+int scratch_get_kx(size_t bytes, void **ptr) { return scratch_get_slot(1, bytes, ptr); }
+static int scratch_get_slot(int slot, size_t bytes, void **ptr) {
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
     B200_REQUIRE(dev >= 0 && dev < 64, "scratch: device index %d out of range", dev);
     std::lock_guard<std::mutex> lk(g_scratch_mu);
-    Scratch &s = g_scratch[dev];
+    Scratch &s = g_scratch[slot][dev];
     if (s.bytes < bytes) {
         if (s.ptr) {
             // work queued on any stream may still read the old block
@@ -66,7 +69,7 @@ int scratch_get(size_t bytes, void **ptr) {
             s.bytes = 0;
         }
         size_t want = bytes + bytes / 4;
-        if (want < (size_t)8 << 20) want = (size_t)8 << 20;
+        if (want < (size_t)(slot == 0 ? 8 : 2) << 20) want = (size_t)(slot == 0 ? 8 : 2) << 20;
         B200_CUDA(cudaMalloc(&s.ptr, want));
         s.bytes = want;
         g_scratch_gen++;

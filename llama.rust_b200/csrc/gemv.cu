@@ -35,6 +35,12 @@ struct PairMap {
     int seg_count;           // 0 or 1: a single matrix
     int seg_end[2];          // first tile of segment 1 and of segment 2 (INT_MAX: no segment 2)
     int seg_total;           // tiles of all segments
+    // K split (one activation row, few row tiles): blockIdx.z walks ksplit ranges of super-blocks; every CTA leaves
+    // its integer partials in kx[tile][nb][32], and the last one to arrive at kcount[tile] runs the f32 chain over
+    // all of K in order, so the result does not depend on the split
+    int ksplit;              // 0 or 1: no split
+    int4 *kx;
+    int *kcount;
     const uint8_t *seg_tiles[2];
     float *seg_dst[2];
     int64_t seg_n[2];
@@ -102,8 +108,15 @@ gemv_q4_K_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, 
     constexpr int XW = MODE == 1 ? 3 : 1;                           // int4 words per (col, group, row)
     int4 *xch = (int4 *)(smem + sizeof(Q4KStage) * nwarps * NCOL);  // [NCOL][nb][XW][32]
     const uint8_t *base = tiles + tile * (int64_t)nb * 4608;
+    int b_first = 0, b_last = nb;
+    if (pm.ksplit > 1) {
+        const int per = (nb + pm.ksplit - 1) / pm.ksplit;
+        b_first = (int)blockIdx.z * per;
+        b_last = b_first + per < nb ? b_first + per : nb;
+    }
+    int4 *gx = pm.ksplit > 1 ? pm.kx + (int64_t)tile * nb * 32 : nullptr;
 
-    for (int b = warp; b < nb; b += nwarps) {
+    for (int b = b_first + warp; b < b_last; b += nwarps) {
         const uint8_t *chunk = base + (int64_t)b * 4608;
         const uint4 h = ld_stream16(chunk + lane * 16);
         uint4 q[8];
@@ -169,6 +182,8 @@ gemv_q4_K_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, 
                 xe[0] = make_int4(ig[0], ig[1], ig[2], ig[3]);
                 xe[32] = make_int4(mg[0], mg[1], mg[2], mg[3]);
                 xe[64] = make_int4((int)h.x, 0, 0, 0);
+            } else if (gx) {
+                gx[(int64_t)b * 32 + lane] = make_int4(iacc, imin, (int)h.x, 0);
             } else {
                 xe[0] = make_int4(iacc, imin, (int)h.x, 0);
             }
@@ -176,6 +191,17 @@ gemv_q4_K_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, 
         __syncwarp();
     }
     if (!waited) pdl_wait();
+    if (gx) {
+        // the last CTA of the tile to get here has every range's partials in front of it
+        __shared__ int is_last;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) is_last = atomicAdd(&pm.kcount[tile], 1) == pm.ksplit - 1;
+        __syncthreads();
+        if (!is_last) return;
+        __threadfence();
+        if (threadIdx.x == 0) pm.kcount[tile] = 0;   // ready for the next launch
+    }
     __syncthreads();
     // accumulation chains, ascending K: threads (col, row)
     for (int t = threadIdx.x; t < NCOL * 32; t += blockDim.x) {
@@ -196,7 +222,7 @@ gemv_q4_K_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, 
                 sumf = __fmaf_rn((float)vi.z, sd, sumf); summin = __fmaf_rn((float)vm.z, sm, summin);
                 sumf = __fmaf_rn((float)vi.w, sd, sumf); summin = __fmaf_rn((float)vm.w, sm, summin);
             } else {
-                const int4 v = xe[0];
+                const int4 v = gx ? __ldcg(gx + (int64_t)b * 32 + r) : xe[0];
                 const float d = f16_bits_to_f32((uint16_t)((uint32_t)v.z & 0xffffu));
                 const float dmin = f16_bits_to_f32((uint16_t)((uint32_t)v.z >> 16));
                 if (MODE == 0) {
@@ -228,8 +254,9 @@ static int pick_warps(int nb) {
 template <int NCOL, int MODE>
 static int launch_q4k(int64_t n, int nb, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
                       cudaStream_t s, PairMap pm = PairMap{}, int64_t pairs = 1) {
-    const int nw = pick_warps(nb);
-    const size_t smem = sizeof(Q4KStage) * nw * NCOL + sizeof(int4) * (size_t)NCOL * nb * 32 * (MODE == 1 ? 3 : 1);
+    const int splits = pm.ksplit > 1 ? pm.ksplit : 1;
+    const int nw = pick_warps(splits > 1 ? (nb + splits - 1) / splits : nb);
+    const size_t smem = sizeof(Q4KStage) * nw * NCOL + (splits > 1 ? 0 : sizeof(int4) * (size_t)NCOL * nb * 32 * (MODE == 1 ? 3 : 1));
     B200_REQUIRE(smem <= 200 * 1024, "mul_mat q4_K: k too large for the shared-memory exchange (%zu bytes)", smem);
     static bool attr_done = false;
     if (!attr_done) {
@@ -238,8 +265,41 @@ static int launch_q4k(int64_t n, int nb, const uint8_t *tiles, ActView acts, flo
     }
     const int64_t tiles_n = pm.seg_count > 1 ? pm.seg_total : (n + TILE_ROWS - 1) / TILE_ROWS;
     B200_REQUIRE(pairs >= 1 && pairs <= 65535, "mul_mat_id: %lld (token, slot) pairs exceed one launch", (long long)pairs);
-    return launch_pdl(gemv_q4_K_kernel<NCOL, MODE>, dim3((unsigned)tiles_n, (unsigned)pairs), dim3(nw * 32), smem, s, tiles,
-                      acts, dst, lddst, n, nb, pm);
+    return launch_pdl(gemv_q4_K_kernel<NCOL, MODE>, dim3((unsigned)tiles_n, (unsigned)pairs, (unsigned)splits), dim3(nw * 32), smem, s,
+                      tiles, acts, dst, lddst, n, nb, pm);
+}
+
+// B200_GEMV_KSPLIT=1 splits K over several CTAs per row tile for the few-tile decode mat-muls.  Measured it
+// loses to the streaming kernel (4096 x 4096: 5.95 against 5.31 us; 4096 x 14336: 13.9 against 11.5 us), whose
+// bulk copies already keep more bytes in flight per SM than four register-staged CTAs do; selectable only.
+static bool gemv_ksplit_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_GEMV_KSPLIT");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
+static int *g_kcount[64] = {nullptr};
+constexpr int KSPLIT_MAX_TILES = 1024;
+// One activation row, a matrix with fewer row tiles than the GPU has room for: split K over several CTAs per tile.
+static int launch_q4k_ksplit(int splits, int64_t n, int nb, const uint8_t *tiles, ActView acts, float *dst, cudaStream_t s) {
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    B200_REQUIRE(dev >= 0 && dev < 64, "gemv: device index %d out of range", dev);
+    if (!g_kcount[dev]) {
+        B200_CUDA(cudaMalloc((void **)&g_kcount[dev], KSPLIT_MAX_TILES * sizeof(int)));
+        B200_CUDA(cudaMemset(g_kcount[dev], 0, KSPLIT_MAX_TILES * sizeof(int)));
+    }
+    const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
+    void *kx = nullptr;
+    int rc = scratch_get_kx((size_t)tiles_n * nb * 32 * sizeof(int4), &kx);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    PairMap pm = PairMap{};
+    pm.ksplit = splits;
+    pm.kx = (int4 *)kx;
+    pm.kcount = g_kcount[dev];
+    return launch_q4k<1, 0>(n, nb, tiles, acts, dst, n, s, pm);
 }
 
 // One activation row against up to three Q4_K matrices of the same K (8x8 gemv chain): one launch whose CTAs
@@ -467,6 +527,12 @@ int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint
     const int nb = (int)(k / GROUP_K);
     // the bulk-copy streaming kernel wins while every CTA has at most one row tile (no second wave to
     // overlap); beyond that the register-staged kernel with two CTAs per SM keeps more warps busy
+    if (type == B200_TYPE_Q4_K && route == B200_ROUTE_REPACK && m == 1 && gemv_ksplit_enabled() && nb >= 8 &&
+        (n + TILE_ROWS - 1) / TILE_ROWS <= gemv_stream_max_tiles()) {
+        // at most one row tile per SM: four CTAs per tile (two for short rows), each a quarter of K
+        const int splits = nb >= 16 ? 4 : 2;
+        return launch_q4k_ksplit(splits, n, nb, tiles, acts, dst, s);
+    }
     if (type == B200_TYPE_Q4_K && route == B200_ROUTE_REPACK && m == 1 && gemv_stream_enabled() &&
         (n + TILE_ROWS - 1) / TILE_ROWS <= gemv_stream_max_tiles())
         return launch_gemv_q4_K_stream(n, k, tiles, acts, dst, s);

@@ -244,3 +244,17 @@ def test_golden_8x8_gemm_and_tiled_outputs(dev, golden):
             X = t[key + "/X"]
             got = dev.mul_mat(dev.Weight(ty, t[key + "/W"], X.shape[1]), X)
             assert bits_equal(got, t[key + "/dst"]), key
+
+
+def test_k_split_kernel_passes_the_same_cases():
+    """B200_GEMV_KSPLIT=1 (read once per process) splits K of the few-tile decode mat-muls over several CTAs, the
+    last arriver running the chain: run the Q4_K decode tests of this file in a child with it set"""
+    import os
+    import subprocess
+    import sys
+    if os.environ.get("B200_GEMV_KSPLIT") == "1":
+        pytest.skip("already the child")
+    env = dict(os.environ, B200_GEMV_KSPLIT="1")
+    r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-x", "-q", "-m", "gpu", "-p", "no:cacheprovider", "-k", "q4_K or streaming"],
+                       env=env, capture_output=True, text=True, timeout=1800)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
