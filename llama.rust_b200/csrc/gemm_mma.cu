@@ -281,6 +281,236 @@ gemm_q6_K_mma_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *dst
             }
 }
 
+// ---- a handful of activation rows (batched decode: 8 to 31) ----------------------------------------------
+// With 16 columns the kernel above has one warp per 32-row tile walk all of K: 128 warps on the whole GPU for a
+// 4096-row matrix.  Here a CTA owns one row tile x 16 columns and its 8 warps split K: in every window of 8
+// super-blocks warp w computes super-block w's sub-block dots with mma.sync, scales them (integers) and leaves
+// ig[pair][row][col] in shared memory with the rows' headers, the columns' activation sums and scales; after
+// a barrier 256 chain threads (two (row, col) each) run the 8x8 gemm chain over the window in K order, so
+// the result is the one the kernel above and the CPU produce.
+constexpr int SMALL_WIN = 8;
+struct SmallStage {
+    int ig[4][16][33];      // scaled pair dots [pair][column][row], rows padded to 33 words: the chain's lanes (rows) hit 32 banks
+    uint4 hdr[32];          // the rows' (d | dmin, 12 scale / min bytes)
+    int bp[16][8];          // the columns' sub-block sums
+    float da[16];           // the columns' super-block scales
+};
+__global__ void __launch_bounds__(SMALL_WIN * 32, 2)
+gemm_q4_K_small_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *dst, int64_t lddst, int64_t n, int nb, int64_t m) {
+    extern __shared__ __align__(16) unsigned char small_sm[];
+    SmallStage *st = (SmallStage *)small_sm;   // [SMALL_WIN]
+    pdl_trigger();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g8 = lane >> 2, t = lane & 3;
+    const int64_t tile = blockIdx.x;
+    const int64_t col0 = (int64_t)blockIdx.y * 16;
+    const int64_t K = acts.k;
+    // activation rows this lane loads fragments from (patch nt, column g8 of it), clamped to the last valid one
+    int64_t colb[2];
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++) {
+        const int64_t c = col0 + 8 * nt + g8;
+        colb[nt] = c < m ? c : m - 1;
+    }
+    const uint8_t *base = tiles + tile * (int64_t)nb * 4608;
+    // chain threads: row cr, columns cc and cc + 8
+    const int cr = threadIdx.x & 31, cc = threadIdx.x >> 5;
+    float sumf[2] = {0.0f, 0.0f}, summin[2] = {0.0f, 0.0f};
+    pdl_wait();
+    for (int w0 = 0; w0 < nb; w0 += SMALL_WIN) {
+        const int b = w0 + warp;
+        if (b < nb) {
+            SmallStage &s = st[warp];
+            const uint8_t *chunk = base + (int64_t)b * 4608;
+            s.hdr[lane] = *(const uint4 *)(chunk + lane * 16);
+            if (lane < 16) {
+                const int64_t c = col0 + lane < m ? col0 + lane : m - 1;
+                s.da[lane] = acts.d[c * nb + b];
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int i = lane + 32 * j, col = i >> 3, sub = i & 7;   // 16 columns x 8 sub-blocks
+                const int64_t c = col0 + col < m ? col0 + col : m - 1;
+                const short2 s2 = *(const short2 *)(acts.bsums + c * (K / 16) + (int64_t)b * 16 + 2 * sub);
+                s.bp[col][sub] = (int)s2.x + (int)s2.y;
+            }
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++) {
+                const int ra = 16 * mt + g8, rb = ra + 8;
+                const uint4 ha = *(const uint4 *)(chunk + ra * 16), hb = *(const uint4 *)(chunk + rb * 16);
+                uint32_t sc[2][2];   // [row a/b][sub-blocks 0..3 / 4..7], 6-bit scales one per byte (crates/ggml/src/quants.rs:421-429)
+                sc[0][0] = ha.y & 0x3f3f3f3fu;
+                sc[0][1] = (ha.w & 0x0f0f0f0fu) | (((ha.y >> 6) & 0x03030303u) << 4);
+                sc[1][0] = hb.y & 0x3f3f3f3fu;
+                sc[1][1] = (hb.w & 0x0f0f0f0fu) | (((hb.y >> 6) & 0x03030303u) << 4);
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    const uint8_t *wq = chunk + 512 + (2 * g + (t >> 1)) * 512 + 8 * (t & 1);
+                    const uint2 wa = ldg8(wq + ra * 16), wb = ldg8(wq + rb * 16);
+                    const int sh = 16 * (g & 1);
+#pragma unroll
+                    for (int nt = 0; nt < 2; nt++) {
+                        const int8_t *aq = acts.qs + colb[nt] * K + (int64_t)b * 256 + 64 * g + 8 * t;
+                        const uint2 y0 = ldg8(aq), y1 = ldg8(aq + 32);
+                        int d0[4], d1[4];
+                        mma_s8_k32(d0, wa.x & 0x0f0f0f0fu, wb.x & 0x0f0f0f0fu, wa.y & 0x0f0f0f0fu, wb.y & 0x0f0f0f0fu, y0.x, y0.y);
+                        mma_s8_k32(d1, (wa.x >> 4) & 0x0f0f0f0fu, (wb.x >> 4) & 0x0f0f0f0fu, (wa.y >> 4) & 0x0f0f0f0fu,
+                                   (wb.y >> 4) & 0x0f0f0f0fu, y1.x, y1.y);
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const int r = e >> 1;   // c0, c1: row a; c2, c3: row b
+                            const int s_lo = (sc[r][g >> 1] >> sh) & 0xff, s_hi = (sc[r][g >> 1] >> (sh + 8)) & 0xff;
+                            s.ig[g][8 * nt + 2 * t + (e & 1)][r ? rb : ra] = d0[e] * s_lo + d1[e] * s_hi;
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        const int wn = nb - w0 < SMALL_WIN ? nb - w0 : SMALL_WIN;
+        for (int w = 0; w < wn; w++) {
+            const SmallStage &s = st[w];
+            const uint4 hd = s.hdr[cr];
+            const uint32_t mn_lo = hd.z & 0x3f3f3f3fu, mn_hi = ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4);
+            const float dw = f16_bits_to_f32((uint16_t)(hd.x & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(hd.x >> 16));
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int c = cc + 8 * j;
+                const float da = s.da[c];
+                const float sd = __fmul_rn(dw, da), sm = __fmul_rn(dmw, da);
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    const uint32_t mw = g < 2 ? mn_lo : mn_hi;
+                    const int m_lo = (mw >> (16 * (g & 1))) & 0xff, m_hi = (mw >> (16 * (g & 1) + 8)) & 0xff;
+                    const int mg = m_lo * s.bp[c][2 * g] + m_hi * s.bp[c][2 * g + 1];
+                    sumf[j] = __fmaf_rn((float)s.ig[g][c][cr], sd, sumf[j]);
+                    summin[j] = __fmaf_rn((float)mg, sm, summin[j]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    const int64_t row = tile * TILE_ROWS + cr;
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        const int64_t col = col0 + cc + 8 * j;
+        if (row < n && col < m) dst[col * lddst + row] = __fsub_rn(sumf[j], summin[j]);
+    }
+}
+
+// The Q6_K tiled chain the same way: warp w leaves r = d * f32(s1) of super-block w for its 32 x 16 patch, the
+// chain threads add fma(r, d_x, out) in K order.
+struct SmallStageQ6 {
+    float rr[16][33];       // [column][row]
+    float da[16];
+};
+__global__ void __launch_bounds__(SMALL_WIN * 32, 2)
+gemm_q6_K_small_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *dst, int64_t lddst, int64_t n, int nb, int64_t m) {
+    __shared__ SmallStageQ6 st[SMALL_WIN];
+    pdl_trigger();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g8 = lane >> 2, t = lane & 3;
+    const int64_t tile = blockIdx.x;
+    const int64_t col0 = (int64_t)blockIdx.y * 16;
+    const int64_t K = acts.k;
+    int64_t colb[2];
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++) {
+        const int64_t c = col0 + 8 * nt + g8;
+        colb[nt] = c < m ? c : m - 1;
+    }
+    const uint8_t *base = tiles + tile * (int64_t)nb * 6720;
+    const int cr = threadIdx.x & 31, cc = threadIdx.x >> 5;
+    float out[2] = {0.0f, 0.0f};
+    pdl_wait();
+    for (int w0 = 0; w0 < nb; w0 += SMALL_WIN) {
+        const int b = w0 + warp;
+        if (b < nb) {
+            SmallStageQ6 &s = st[warp];
+            const uint8_t *chunk = base + (int64_t)b * 6720;
+            if (lane < 16) {
+                const int64_t c = col0 + lane < m ? col0 + lane : m - 1;
+                s.da[lane] = acts.d[c * nb + b];
+            }
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++) {
+                const int ra = 16 * mt + g8, rb = ra + 8;
+                const uint4 sa = *(const uint4 *)(chunk + 6144 + ra * 16), sb = *(const uint4 *)(chunk + 6144 + rb * 16);   // 16 int8 scales
+                const float dw[2] = {f16_bits_to_f32(*(const uint16_t *)(chunk + 6656 + ra * 2)),
+                                     f16_bits_to_f32(*(const uint16_t *)(chunk + 6656 + rb * 2))};
+                int s1[2][4];
+#pragma unroll
+                for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++) s1[nt][e] = 0;
+#pragma unroll
+                for (int nh = 0; nh < 4; nh++) {
+                    const int nn = nh >> 1, h = nh & 1;
+                    const uint8_t *pa = chunk + (4 * nn + h) * 512 + 4 * t, *pb = chunk + (4 * nn + 2 + h) * 512 + 4 * t;
+                    const uint8_t *ph = chunk + 4096 + (2 * nn + h) * 512 + 4 * t;
+                    const uint32_t Aa = ldg4(pa + ra * 16), Ba = ldg4(pb + ra * 16), Ha = ldg4(ph + ra * 16);
+                    const uint32_t Ab = ldg4(pa + rb * 16), Bb = ldg4(pb + rb * 16), Hb = ldg4(ph + rb * 16);
+                    uint32_t wa[4], wb[4];
+                    wa[0] = (Aa & 0x0f0f0f0fu) | ((Ha << 4) & 0x30303030u);
+                    wa[1] = (Ba & 0x0f0f0f0fu) | ((Ha << 2) & 0x30303030u);
+                    wa[2] = ((Aa >> 4) & 0x0f0f0f0fu) | (Ha & 0x30303030u);
+                    wa[3] = ((Ba >> 4) & 0x0f0f0f0fu) | ((Ha >> 2) & 0x30303030u);
+                    wb[0] = (Ab & 0x0f0f0f0fu) | ((Hb << 4) & 0x30303030u);
+                    wb[1] = (Bb & 0x0f0f0f0fu) | ((Hb << 2) & 0x30303030u);
+                    wb[2] = ((Ab >> 4) & 0x0f0f0f0fu) | (Hb & 0x30303030u);
+                    wb[3] = ((Bb >> 4) & 0x0f0f0f0fu) | ((Hb >> 2) & 0x30303030u);
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const uint32_t a0 = __vsub4(wa[q], 0x20202020u), a1 = __vsub4(wb[q], 0x20202020u);
+                        const int sub = 8 * nn + 2 * q + h;   // scale index = element / 16
+                        const int sca = (int)(int8_t)((sub < 4 ? sa.x : sub < 8 ? sa.y : sub < 12 ? sa.z : sa.w) >> (8 * (sub & 3)));
+                        const int scb = (int)(int8_t)((sub < 4 ? sb.x : sub < 8 ? sb.y : sub < 12 ? sb.z : sb.w) >> (8 * (sub & 3)));
+#pragma unroll
+                        for (int nt = 0; nt < 2; nt++) {
+                            const uint32_t y = ldg4(acts.qs + colb[nt] * K + (int64_t)b * 256 + 128 * nn + 32 * q + 16 * h + 4 * t);
+                            int d[4];
+                            mma_s8_k16(d, a0, a1, y);
+                            s1[nt][0] += sca * d[0];
+                            s1[nt][1] += sca * d[1];
+                            s1[nt][2] += scb * d[2];
+                            s1[nt][3] += scb * d[3];
+                        }
+                    }
+                }
+#pragma unroll
+                for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++)
+                        s.rr[8 * nt + 2 * t + (e & 1)][(e >> 1) ? rb : ra] = __fmul_rn(dw[e >> 1], (float)s1[nt][e]);
+            }
+        }
+        __syncthreads();
+        const int wn = nb - w0 < SMALL_WIN ? nb - w0 : SMALL_WIN;
+        for (int w = 0; w < wn; w++) {
+            const SmallStageQ6 &s = st[w];
+#pragma unroll
+            for (int j = 0; j < 2; j++) out[j] = __fmaf_rn(s.rr[cc + 8 * j][cr], s.da[cc + 8 * j], out[j]);
+        }
+        __syncthreads();
+    }
+    const int64_t row = tile * TILE_ROWS + cr;
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        const int64_t col = col0 + cc + 8 * j;
+        if (row < n && col < m) dst[col * lddst + row] = out[j];
+    }
+}
+
+// B200_GEMM_SMALL=0 keeps 8 to 31 activation rows on the one-warp-per-tile kernel
+static bool gemm_small_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_GEMM_SMALL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
 // mode: 1 = Q4_K gemm chain, 2 = Q4_K tiled chain, 6 = Q6_K tiled chain
 int launch_gemm_mma(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
                     cudaStream_t s) {
@@ -288,6 +518,25 @@ int launch_gemm_mma(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *ti
     if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
     const int nb = (int)(k / GROUP_K);
     const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
+    if (mode == 1 && m < 32 && gemm_small_enabled()) {
+        // a few activation rows: K split over the warps of a CTA
+        static bool attr_done = false;
+        const size_t smem = sizeof(SmallStage) * SMALL_WIN;
+        if (!attr_done) {
+            B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr_done = true;
+        }
+        const int64_t sy = (m + 15) / 16;
+        B200_REQUIRE(tiles_n < 0x7fffffffLL && sy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);
+        return launch_pdl(gemm_q4_K_small_kernel, dim3((unsigned)tiles_n, (unsigned)sy), dim3(SMALL_WIN * 32), smem, s, tiles, acts, dst, lddst,
+                          n, nb, m);
+    }
+    if (mode == 6 && m < 32 && gemm_small_enabled()) {
+        const int64_t sy = (m + 15) / 16;
+        B200_REQUIRE(tiles_n < 0x7fffffffLL && sy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);
+        return launch_pdl(gemm_q6_K_small_kernel, dim3((unsigned)tiles_n, (unsigned)sy), dim3(SMALL_WIN * 32), 0, s, tiles, acts, dst, lddst, n,
+                          nb, m);
+    }
     const int64_t gx = (tiles_n + 3) / 4, gy = (m + 2 * MMA_COLS - 1) / (2 * MMA_COLS);
     B200_REQUIRE(gx < 0x7fffffffLL && gy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);
     const dim3 grid((unsigned)gx, (unsigned)gy), block(MMA_WARPS * 32);

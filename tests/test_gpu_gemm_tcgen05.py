@@ -94,3 +94,37 @@ def test_f16_operand_kernel_passes_the_same_cases():
     r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-x", "-q", "-m", "gpu", "-p", "no:cacheprovider"], env=env,
                        capture_output=True, text=True, timeout=1200)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+
+
+SMALL_CASES = [
+    # (n, k, m): 8 to 31 activation rows take the K-split mma kernel (gemm chain)
+    (64, 512, 8), (96, 1024, 9), (4096, 4096, 16), (1024, 14336, 16), (160, 2304, 31), (4096, 4096, 13),
+]
+
+
+@pytest.mark.parametrize("case", SMALL_CASES, ids=lambda c: f"{c[0]}x{c[1]}-m{c[2]}")
+def test_small_batches_against_the_oracle_and_four_column_calls(dev, case):
+    n, k, m = case
+    W = synth.weights(orc.Q4_K, n, k, seed=65, period=256)
+    x = synth.activations(m, k, seed=66)
+    w = dev.Weight(orc.Q4_K, W, k)
+    got = dev.mul_mat(w, x)
+    assert dev.kernel_error() == 0
+    if n * k <= 1 << 22:
+        want, r = orc.mul_mat(orc.Q4_K, W, x)
+        assert r == orc.ROUTE_REPACK
+        assert bits_equal(got, want), f"max |d| = {np.abs(got - want).max()}"
+    m4 = m - m % 4
+    for c0 in range(0, m4, 4):
+        assert bits_equal(got[c0:c0 + 4], dev.mul_mat(w, x[c0:c0 + 4])), f"columns {c0}..{c0 + 3}"
+
+
+@pytest.mark.parametrize("case", [(64, 512, 8), (1024, 4096, 16), (300, 1024, 31), (96, 14336, 12)], ids=str)
+def test_q6_K_small_batches_against_the_oracle(dev, case):
+    n, k, m = case
+    W = synth.weights(orc.Q6_K, n, k, seed=67, period=128)
+    x = synth.activations(m, k, seed=68)
+    want, r = orc.mul_mat(orc.Q6_K, W, x)
+    assert r == orc.ROUTE_TILED
+    got = dev.mul_mat(dev.Weight(orc.Q6_K, W, k), x)
+    assert bits_equal(got, want), f"max |d| = {np.abs(got - want).max()}"
