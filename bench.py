@@ -647,14 +647,30 @@ def case_gemm(args):
 
 
 def case_llama(args):
-    """`--case llama_tg|llama_pp --layers L [--launches R]`: an L-layer model of the 8B shape; one prompt
-    batch (llama_pp) or R single-token steps after a 16-token prompt (llama_tg), eager launches (no CUDA
-    graph) so that a profiler sees every kernel."""
+    """`--case llama_tg|llama_pp|llama_b16 --layers L [--launches R]`: an L-layer model of the 8B shape; one prompt
+    batch (llama_pp), R single-token steps after a 16-token prompt (llama_tg) or R steps of 16 sequences after
+    512-token prompts (llama_b16), eager launches (no CUDA graph) so that a profiler sees every kernel."""
     os.environ["B200_CUDA_GRAPHS"] = "0"
     b = load_pkg()
     b.set_device(0)
-    ll, hp, gpu, _ = build_llama(args.layers)
+    ll, hp, gpu, _ = build_llama(args.layers, n_ctx=N_SEQ * (PROMPT + GEN) if args.case == "llama_b16" else 1024)
     rng = np.random.default_rng(0)
+    if args.case == "llama_b16":
+        # 16 sequences with 512-token prompts in the unified cache, then R steps of one token per sequence
+        seqs = np.arange(N_SEQ, dtype=np.int32)
+        nxt = np.zeros(N_SEQ, dtype=np.int32)
+        for s in range(N_SEQ):
+            _, am = gpu.decode_seqs(rng.integers(0, hp["n_vocab"], PROMPT).astype(np.int32), np.arange(PROMPT, dtype=np.int32),
+                                    np.full(PROMPT, s, dtype=np.int32), [PROMPT - 1], logits=False, argmax=True)
+            nxt[s] = am[0]
+        t0 = time.perf_counter()
+        for i in range(args.launches):
+            _, am = gpu.decode_seqs(nxt, np.full(N_SEQ, PROMPT + i, dtype=np.int32), seqs, seqs, logits=False, argmax=True)
+            nxt = am.astype(np.int32)
+        print(json.dumps({"case": "llama_b16", "layers": args.layers, "steps": args.launches,
+                          "ms_per_step": (time.perf_counter() - t0) * 1e3 / args.launches}), flush=True)
+        gpu.close()
+        return
     if args.case == "llama_pp":
         prompt = rng.integers(0, hp["n_vocab"], PROMPT).astype(np.int32)
         t0 = time.perf_counter()
@@ -673,7 +689,7 @@ def case_llama(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "llama_tg", "llama_pp"], help="one small case for a profiler")
+    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "llama_tg", "llama_pp", "llama_b16"], help="one small case for a profiler")
     ap.add_argument("--only", default="4096x4096", help="--case gemv / gemm: the shape NxK")
     ap.add_argument("--cols", type=int, default=512, help="--case gemm: activation rows")
     ap.add_argument("--launches", type=int, default=64)
