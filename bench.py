@@ -358,7 +358,7 @@ def run_llama_batch16(gpu, hp, world, barrier, reduce_max):
     pp, tg, tg_dev = (reduce_max(min(r[k] for r in res)) for k in range(3))
     return {"sequences": N_SEQ, "pp512_e2e_tok_s": world * N_SEQ * PROMPT / pp, "tg128_e2e_tok_s": world * N_SEQ / tg,
             "tg128_tok_s": world * N_SEQ / tg_dev, "tg128_ms_per_step": tg_dev * 1e3,
-            "cache": f"unified, {N_SEQ * (PROMPT + GEN)} cells in use at the end; a step's attention spans every cell and masks the other sequences'"}
+            "cache": f"unified, {N_SEQ * (PROMPT + GEN)} cells in use at the end; a row's mask hides the other sequences' cells"}
 
 
 def run_llama(b, args, rank, world, barrier, reduce_max):

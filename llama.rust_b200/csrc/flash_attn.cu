@@ -587,6 +587,7 @@ static int check_args(const b200_flash_attn_args *a) {
 
 int flash_attn_faithful_tiled(const b200_flash_attn_args *a, cudaStream_t s);   // flash_attn_tiled.cu
 bool flash_attn_decode_head(const b200_flash_attn_args *a, int n_chunks, int64_t chunk, cudaStream_t s, int *rc);   // flash_attn_head.cu
+bool flash_attn_rows_visible(const b200_flash_attn_args *a, cudaStream_t s, int *rc);                               // flash_attn_vis.cu
 
 // B200_FA_DECODE_FUSED=0 keeps single-row attention on the three-kernel path (for side-by-side measurements)
 static bool fa_decode_one_kernel_enabled() {
@@ -612,6 +613,10 @@ int flash_attn_faithful_rows(const b200_flash_attn_args *a, cudaStream_t s) {
         return B200_STATUS_SUCCESS;
     }
     B200_REQUIRE(d.T <= 65535 && d.H <= 65535, "flash_attn_ext: too many rows for one launch");
+    if (d.T >= 2) {   // a few rows over a masked cache (batched decode): walk each row's visible positions only
+        int rc = B200_STATUS_SUCCESS;
+        if (flash_attn_rows_visible(a, s, &rc)) return rc;
+    }
     if (d.T == 1 && split) {   // a chat-length context: one CTA per head, one warp per chunk
         int rc = B200_STATUS_SUCCESS;
         if (flash_attn_decode_head(a, d.n_chunks, d.chunk, s, &rc)) return rc;

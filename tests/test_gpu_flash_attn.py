@@ -161,6 +161,24 @@ def test_softcap_and_sinks_within_tolerance(dev):
     assert (np.abs(got - want) <= REL_TOL * scale).all()
 
 
+@pytest.mark.parametrize("D", [128, 64])
+def test_rows_over_a_cache_shared_by_sixteen_sequences(dev, D):
+    """batched decode over the unified cache: 16 rows, each seeing only its own sequence's cells (blocks of prompt
+    cells, then interleaved generated ones) among 3072; one row sees nothing"""
+    T, n_kv = 16, 3072
+    q, k, v, _ = synth_case(8, 2, D, T, n_kv, seed=77, causal=False)
+    m = np.full((T, n_kv), -np.inf, dtype=np.float16)
+    for t in range(T):
+        m[t, t * 128:(t + 1) * 128] = 0.0            # the sequence's prompt cells
+        m[t, 2048 + t:2048 + 16 * 40:16] = 0.0        # its generated tokens, one cell in sixteen
+    m[5, :] = -np.inf
+    mask = m.view(np.uint16)
+    want, _ = orc.flash_attn(q, k, v, mask, 0.0883883)
+    got = dev.flash_attn(q, dev.KvCacheView(k, v), mask, 0.0883883)
+    assert bits_equal(got, want)
+    assert not got[:, 5].any() if got.shape[1] == T else not got[5].any()
+
+
 def test_head_per_cta_kernel_passes_the_same_cases():
     """the CTA-per-head split-KV kernel is selected by B200_FA_DECODE_HEAD=1, read once per process: run this
     file's other tests in a child with it set"""
