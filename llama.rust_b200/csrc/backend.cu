@@ -953,6 +953,12 @@ static int find_silu_mul(const ggml_cgraph *g, int i) {
 // Issues the launches of every node, in order, on the backend's stream.
 static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
     bc->act_src = nullptr;   // tensors may have been rewritten between graphs
+    struct FaScope {         // one mask serves every layer of this node list: attention may reuse what it derives from it
+        FaScope() { flash_attn_graph_scope(true); }
+        ~FaScope() { flash_attn_graph_scope(false); }
+    } fa_scope;
+    const void *fa_mask = nullptr;   // the mask the attention nodes so far have read
+    size_t fa_mask_bytes = 0;
     std::vector<int> silu_of(g->n_nodes, -1);   // silu_of[j] = i: MUL node j also computes SILU node i
     std::vector<char> done(g->n_nodes, 0);      // mat-mul nodes that ran early, with a sibling
     for (int i = 0; i < g->n_nodes; i++) {
@@ -979,6 +985,15 @@ static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
         if (bc->act_src && op->data && ranges_overlap(op->data, ggml_nbytes(op), bc->act_src, (size_t)bc->act_ld * bc->act_m * 4))
             bc->act_src = nullptr;
         if (op->type == B200_TYPE_I32 && in_our_buffer(op)) shadow_drop(bctx(op->buffer), op->data);
+        if (op->op == GGML_OP_FLASH_ATTN_EXT) {
+            if (op->src[3] && op->src[3]->data) {
+                fa_mask = op->src[3]->data;
+                fa_mask_bytes = ggml_nbytes(op->src[3]);
+            }
+        } else if (fa_mask && op->data && ranges_overlap(op->data, ggml_nbytes(op), fa_mask, fa_mask_bytes)) {
+            flash_attn_graph_scope(true);   // a node rewrites the mask: what attention derived from it is stale
+            fa_mask = nullptr;
+        }
         int rc = B200_STATUS_SUCCESS;
         switch (op->op) {
             case GGML_OP_MUL_MAT:

@@ -196,6 +196,9 @@ int launch_argmax(const float *x, int64_t x_stride, int64_t ne0, int64_t nrows, 
 // scratch owned by the library (one growing allocation per device)
 int scratch_get(size_t bytes, void **ptr);
 int scratch_get_kx(size_t bytes, void **ptr);   // a second block, for the K-split exchange of the decode mat-mul
+int scratch_get_lists(size_t bytes, void **ptr);   // a third, for attention's visible-position lists
+// graph_compute brackets a node list with (true) / (false): inside, attention reuses the lists of an unchanged mask
+void flash_attn_graph_scope(bool enter);
 
 // route the reference takes for (type, n, m), and the activation quantizer that route reads
 int pick_route(int type, int64_t n, int64_t m);

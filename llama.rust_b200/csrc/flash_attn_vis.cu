@@ -20,6 +20,14 @@ namespace {
 constexpr int FV_TILE = 128;
 
 __device__ __forceinline__ float v_r16(float v) { return __half2float(__float2half_rn(v)); }
+// the same rounding for the long dependent chain: inside the normal f16 range, round to nearest even at bit 13 of
+// the f32 pattern with three integer operations; everything else takes the conversion pair
+__device__ __forceinline__ float v_r16_fast(float v) {
+    const uint32_t b = __float_as_uint(v);
+    if (((b & 0x7fffffffu) - 0x38800000u) < (0x477ff000u - 0x38800000u))
+        return __uint_as_float((b + 0x0fffu + ((b >> 13) & 1u)) & 0xffffe000u);
+    return v_r16(v);
+}
 
 // vis[t][0 .. nvis[t]) = the positions of mask row t that are not -inf, ascending
 __global__ void __launch_bounds__(256)
@@ -213,7 +221,7 @@ fa_rows_vis_kernel(b200_flash_attn_args a, int H, int H_kv, int dv, int64_t n_kv
                 const float ms = ms_s[i];
                 if (ms < 0.0f) continue;
                 if (ms != 1.0f) x = v_r16(__fmul_rn(x, ms));
-                x = v_r16(__fmaf_rn(__half2float(v_s[i * dv + tid]), vs_s[i], x));
+                x = v_r16_fast(__fmaf_rn(__half2float(v_s[i * dv + tid]), vs_s[i], x));
             }
         } else if (is_s) {
             for (int i = 0; i < np; i++) {
@@ -259,6 +267,20 @@ bool fa_visible_enabled() {
 
 }  // namespace
 
+// Inside one graph_compute every layer's attention reads the same mask: the lists made for the first layer serve
+// the others.  The backend brackets a node list with flash_attn_graph_scope(true / false); outside such a scope
+// (the op-level entry point, where a caller may rewrite a mask in place between calls) nothing is reused.
+static thread_local unsigned long long t_scope = 0;
+static unsigned long long g_scope_counter = 0;
+struct VisibleCache {
+    unsigned long long scope = 0;
+    const void *mask = nullptr;
+    int64_t nb1 = 0, n_kv = 0, T = 0;
+    int32_t *vis = nullptr, *nvis = nullptr;
+};
+static VisibleCache g_vis_cache[64];
+void flash_attn_graph_scope(bool enter) { t_scope = enter ? ++g_scope_counter : 0; }
+
 // true when the launches were made; false = not this path's case (the caller takes the other one)
 bool flash_attn_rows_visible(const b200_flash_attn_args *a, cudaStream_t s, int *rc) {
     *rc = B200_STATUS_SUCCESS;
@@ -268,15 +290,24 @@ bool flash_attn_rows_visible(const b200_flash_attn_args *a, cudaStream_t s, int 
     if (T > 65535 || H > 65535) return false;
     const size_t vis_b = ((size_t)T * n_kv * 4 + 255) / 256 * 256, nvis_b = ((size_t)T * 4 + 255) / 256 * 256;
     const size_t score_b = (size_t)T * H * n_kv * 4;
-    void *scratch = nullptr;
-    *rc = scratch_get(vis_b + nvis_b + score_b, &scratch);
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    void *scratch = nullptr, *lists = nullptr;
+    *rc = scratch_get(score_b, &scratch);
+    if (*rc == B200_STATUS_SUCCESS) *rc = scratch_get_lists(vis_b + nvis_b, &lists);   // its own block: the lists outlive this call
     if (*rc != B200_STATUS_SUCCESS) return true;
-    int32_t *vis = (int32_t *)scratch;
-    int32_t *nvis = (int32_t *)((uint8_t *)scratch + vis_b);
-    float *scores = (float *)((uint8_t *)scratch + vis_b + nvis_b);
+    int32_t *vis = (int32_t *)lists;
+    int32_t *nvis = (int32_t *)((uint8_t *)lists + vis_b);
+    float *scores = (float *)scratch;
     const float kq_scale = a->logit_softcap != 0.0f ? a->scale / a->logit_softcap : a->scale;
-    *rc = launch_pdl(fa_visible_kernel, dim3((unsigned)T), dim3(256), 0, s, (const uint8_t *)a->mask, a->mask_nb1, n_kv, vis, nvis);
-    if (*rc != B200_STATUS_SUCCESS) return true;
+    VisibleCache &vc = g_vis_cache[dev];
+    const bool reuse = t_scope != 0 && vc.scope == t_scope && vc.mask == a->mask && vc.nb1 == a->mask_nb1 && vc.n_kv == n_kv && vc.T == T &&
+                       vc.vis == vis && vc.nvis == nvis;
+    if (!reuse) {
+        *rc = launch_pdl(fa_visible_kernel, dim3((unsigned)T), dim3(256), 0, s, (const uint8_t *)a->mask, a->mask_nb1, n_kv, vis, nvis);
+        if (*rc != B200_STATUS_SUCCESS) return true;
+        vc.scope = t_scope; vc.mask = a->mask; vc.nb1 = a->mask_nb1; vc.n_kv = n_kv; vc.T = T; vc.vis = vis; vc.nvis = nvis;
+    }
     const int group = (int)(H / a->n_head_kv);
     const dim3 g1((unsigned)((n_kv + 127) / 128), (unsigned)a->n_head_kv, (unsigned)T);
     const size_t sm1 = (size_t)group * a->dk * 4;
