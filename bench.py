@@ -678,10 +678,11 @@ def case_llama(args):
         print(json.dumps({"case": "llama_pp", "layers": args.layers, "ms": (time.perf_counter() - t0) * 1e3,
                           "replay_ms": gpu.replay(1)}), flush=True)
     else:
-        tok = gpu.decode(rng.integers(0, hp["n_vocab"], 16).astype(np.int32), np.arange(16), logits=False, argmax=True)
+        np_ = max(1, min(args.prompt, PROMPT))   # --prompt 512: the split-KV attention of the bench's tg128 steps
+        tok = gpu.decode(rng.integers(0, hp["n_vocab"], np_).astype(np.int32), np.arange(np_), logits=False, argmax=True)
         t0 = time.perf_counter()
         for i in range(args.launches):
-            tok = gpu.decode([tok], [16 + i], logits=False, argmax=True)
+            tok = gpu.decode([tok], [np_ + i], logits=False, argmax=True)
         print(json.dumps({"case": "llama_tg", "layers": args.layers, "steps": args.launches,
                           "ms_per_token": (time.perf_counter() - t0) * 1e3 / args.launches}), flush=True)
     gpu.close()
@@ -692,6 +693,7 @@ def main():
     ap.add_argument("--case", default=None, choices=["gemv", "gemm", "llama_tg", "llama_pp", "llama_b16"], help="one small case for a profiler")
     ap.add_argument("--only", default="4096x4096", help="--case gemv / gemm: the shape NxK")
     ap.add_argument("--cols", type=int, default=512, help="--case gemm: activation rows")
+    ap.add_argument("--prompt", type=int, default=16, help="--case llama_tg: prompt tokens before the timed steps")
     ap.add_argument("--launches", type=int, default=64)
     ap.add_argument("--layers", type=int, default=32, help="layers of the 8B-shaped model (32 = the full model)")
     ap.add_argument("--cpu-layers", type=int, default=32, help="layers of the model the CPU baseline times")
