@@ -1077,9 +1077,18 @@ static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
 // What a launch reads from the host while being issued must therefore not depend on values that change
 // between tokens: positions reach ROPE through the position tensor on the device (rope_prepare), and the
 // key below covers everything else a node's launches are derived from.
+// the key is recomputed on every graph_compute, over a few hundred KB for a 32-layer decode step: eight bytes
+// per multiply (a byte-wise chain of dependent multiplies cost a third of a millisecond per token)
 static uint64_t fnv(uint64_t h, const void *p, size_t n) {
     const uint8_t *b = (const uint8_t *)p;
-    for (size_t i = 0; i < n; i++) h = (h ^ b[i]) * 0x100000001b3ull;
+    size_t i = 0;
+    for (; i + 8 <= n; i += 8) {
+        uint64_t w;
+        memcpy(&w, b + i, 8);
+        h = (h ^ w) * 0x9e3779b97f4a7c15ull;
+        h ^= h >> 32;
+    }
+    for (; i < n; i++) h = (h ^ b[i]) * 0x100000001b3ull;
     return h;
 }
 static uint64_t node_list_key(const BackendCtx *bc, const ggml_cgraph *g) {
