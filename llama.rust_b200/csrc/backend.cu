@@ -199,15 +199,8 @@ static int tiled_io(const ggml_tensor *t, void *host, size_t offset, size_t size
     return B200_STATUS_SUCCESS;
 }
 
-static void buf_set_tensor(ggml_backend_buffer_t b, ggml_tensor *t, const void *data, size_t offset, size_t size) {
-    BufferCtx *c = bctx(b);
-    cudaSetDevice(c->device);
-    if (size == 0) return;
-    if (is_tiled_tensor(t)) {
-        if (tiled_io(t, const_cast<void *>(data), offset, size, true) != B200_STATUS_SUCCESS) note(c, "set_tensor");
-        cudaStreamSynchronize(nullptr);   // set_tensor is synchronous: the re-ordering kernel has finished on return
-        return;
-    }
+// small I32 tensors (positions) keep a host copy of what was last written to them
+static void shadow_note_write(BufferCtx *c, const ggml_tensor *t, const void *data, size_t offset, size_t size) {
     if (t->type == B200_TYPE_I32 && ggml_nbytes(t) <= SHADOW_MAX_BYTES && offset % 4 == 0 && size % 4 == 0 &&
         offset + size <= ggml_nbytes(t) && is_contiguous(t)) {
         std::lock_guard<std::mutex> lk(c->mu);
@@ -220,6 +213,17 @@ static void buf_set_tensor(ggml_backend_buffer_t b, ggml_tensor *t, const void *
             memcpy((uint8_t *)sh.data() + offset, data, size);
         }
     }
+}
+static void buf_set_tensor(ggml_backend_buffer_t b, ggml_tensor *t, const void *data, size_t offset, size_t size) {
+    BufferCtx *c = bctx(b);
+    cudaSetDevice(c->device);
+    if (size == 0) return;
+    if (is_tiled_tensor(t)) {
+        if (tiled_io(t, const_cast<void *>(data), offset, size, true) != B200_STATUS_SUCCESS) note(c, "set_tensor");
+        cudaStreamSynchronize(nullptr);   // set_tensor is synchronous: the re-ordering kernel has finished on return
+        return;
+    }
+    shadow_note_write(c, t, data, offset, size);
     if (b200_memcpy_h2d((uint8_t *)t->data + offset, data, size, nullptr) != B200_STATUS_SUCCESS) note(c, "set_tensor");
     cudaStreamSynchronize(nullptr);
 }
@@ -1201,8 +1205,20 @@ static void backend_free(ggml_backend_t be) {
     delete bc;
     delete be;
 }
-static void backend_set_tensor_async(ggml_backend_t, ggml_tensor *t, const void *data, size_t offset, size_t size) {
-    if (t->buffer) t->buffer->iface.set_tensor(t->buffer, t, data, offset, size);
+// Ordered on the backend's stream, before the next graph_compute; the host memory may be reused on return (the
+// runtime stages a pageable source before it returns).  Quantized tensors take the synchronous path: they are
+// re-ordered by a kernel on the way in.
+static void backend_set_tensor_async(ggml_backend_t be, ggml_tensor *t, const void *data, size_t offset, size_t size) {
+    if (!t->buffer || size == 0) return;
+    if (is_tiled_tensor(t) || !in_our_buffer(t)) {
+        t->buffer->iface.set_tensor(t->buffer, t, data, offset, size);
+        return;
+    }
+    BackendCtx *bc = (BackendCtx *)be->context;
+    BufferCtx *c = bctx(t->buffer);
+    cudaSetDevice(bc->device);
+    shadow_note_write(c, t, data, offset, size);
+    if (b200_memcpy_h2d((uint8_t *)t->data + offset, data, size, bc->stream) != B200_STATUS_SUCCESS) note(c, "set_tensor_async");
 }
 static void backend_get_tensor_async(ggml_backend_t be, const ggml_tensor *t, void *data, size_t offset, size_t size) {
     BackendCtx *bc = (BackendCtx *)be->context;

@@ -303,6 +303,11 @@ int64_t n_kv_for(const b200_llama *c, int32_t used) {
 }
 
 void set_input(ggml_tensor *t, const void *data, size_t bytes) { t->buffer->iface.set_tensor(t->buffer, t, data, 0, bytes); }
+// the per-step inputs: ordered on the backend's stream ahead of the step's graph, no wait per copy
+void set_input_async(ggml_backend_t be, ggml_tensor *t, const void *data, size_t bytes) {
+    if (be->iface.set_tensor_async) be->iface.set_tensor_async(be, t, data, 0, bytes);
+    else set_input(t, data, bytes);
+}
 
 // graph_compute over the first `total` nodes, cut where the ranks of a tensor-parallel group exchange data
 int run_graph(b200_llama *c, Graph *g, int total) {
@@ -547,11 +552,11 @@ int b200_llama_decode_seqs(b200_llama *c, const int32_t *tokens, const int32_t *
 
     // inputs land with synchronous copies after the previous step has drained
     c->backend->iface.synchronize(c->backend);
-    set_input(g->tokens, tokens, (size_t)n * 4);
-    set_input(g->pos, pos, (size_t)n * 4);
-    set_input(g->mask, c->mask_host.data(), c->mask_host.size() * 2);
-    set_input(g->row_idx, c->idx_host.data(), (size_t)n * 8);
-    set_input(g->out_ids, out_rows, (size_t)n_out * 4);
+    set_input_async(c->backend, g->tokens, tokens, (size_t)n * 4);
+    set_input_async(c->backend, g->pos, pos, (size_t)n * 4);
+    set_input_async(c->backend, g->mask, c->mask_host.data(), c->mask_host.size() * 2);
+    set_input_async(c->backend, g->row_idx, c->idx_host.data(), (size_t)n * 8);
+    set_input_async(c->backend, g->out_ids, out_rows, (size_t)n_out * 4);
 
     int rc = run_graph(c, g, (int)g->nodes.size() - (argmax ? 0 : 1));   // the ARGMAX node is last
     if (rc != B200_STATUS_SUCCESS) return rc;
