@@ -136,6 +136,8 @@ int launch_gemm_mma(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *ti
                     cudaStream_t s);
 int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
                         cudaStream_t s);
+// Q4_K gemm chain with the scales folded into f16 operands, 128 x 64 per CTA (gemm_tcgen05_f16.cu)
+int launch_gemm_tcgen05_f16x64(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s);
 // up to four ROPE / SET_ROWS (F32 -> F16) nodes for one launch, see glue_batch_kernel
 constexpr int GLUE_BATCH_MAX = 4;
 enum { GLUE_ROPE = 1, GLUE_SET_ROWS = 2 };

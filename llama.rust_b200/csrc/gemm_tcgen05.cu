@@ -662,13 +662,14 @@ gemm_q4_K_tcgen05_f16_kernel(const uint8_t *__restrict__ tiles, ActView acts, fl
 // 160 us against the integer kernel's 145 us: its epilogue is four times cheaper, but every worker converts,
 // hands over and drains in sequence, and the per-step hand-off and load latencies (2 operand stages of 88 KB
 // are all that fits) are not hidden.  It stays selectable until its pipeline is deeper.
-static bool gemm_tcgen05_f16_enabled() {
+// B200_GEMM_TCGEN05_F16: 1 = the 32-column f16-operand kernel of this file, 2 = the 64-column one (gemm_tcgen05_f16.cu)
+static int gemm_tcgen05_f16_choice() {
     static int v = -1;
     if (v < 0) {
         const char *e = getenv("B200_GEMM_TCGEN05_F16");
-        v = (e && e[0] == '1') ? 1 : 0;
+        v = (e && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
     }
-    return v == 1;
+    return v;
 }
 
 // mode: 1 = Q4_K gemm chain, 2 = Q4_K tiled chain
@@ -677,6 +678,7 @@ int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t
     B200_REQUIRE(k % GROUP_K == 0, "gemm: k = %lld must be a multiple of 256", (long long)k);
     B200_REQUIRE(mode == 1 || mode == 2, "gemm: unknown mode %d", mode);
     if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
+    if (mode == 1 && gemm_tcgen05_f16_choice() == 2) return launch_gemm_tcgen05_f16x64(n, k, m, tiles, acts, dst, lddst, s);
     static bool attr_done[64] = {false};
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
@@ -694,7 +696,7 @@ int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t
     const int64_t gx = (m + TC_COLS - 1) / TC_COLS, gy = (n + TC_ROWS - 1) / TC_ROWS;
     B200_REQUIRE(gx < 0x7fffffffLL && gy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);
     const dim3 grid((unsigned)gx, (unsigned)gy), block(TC_THREADS);
-    if (mode == 1 && gemm_tcgen05_f16_enabled())
+    if (mode == 1 && gemm_tcgen05_f16_choice() == 1)
         return launch_pdl(gemm_q4_K_tcgen05_f16_kernel, grid, dim3(TF_THREADS), (size_t)TF_SMEM_BYTES, s, tiles, acts, dst, lddst, n, nb, m, err);
     if (mode == 1) return launch_pdl(gemm_q4_K_tcgen05_kernel<1>, grid, block, (size_t)TC_SMEM_BYTES, s, tiles, acts, dst, lddst, n, nb, m, err);
     return launch_pdl(gemm_q4_K_tcgen05_kernel<2>, grid, block, (size_t)TC_SMEM_BYTES, s, tiles, acts, dst, lddst, n, nb, m, err);

@@ -1,7 +1,7 @@
 """The tcgen05 prompt mat-mul (Q4_K, 32 activation rows and up) against the CPU oracle and against the
 decode-shaped kernels: same chains, so every output has to agree bit for bit.  The whole file runs twice:
-on the integer kernel (the default) and, in a child process with B200_GEMM_TCGEN05_F16=1, on the f16-operand
-kernel."""
+on the integer kernel (the default) and, in child processes with B200_GEMM_TCGEN05_F16=1 and =2, on the two
+f16-operand kernels (32 and 64 activation rows per CTA)."""
 import os
 import subprocess
 import sys
@@ -86,11 +86,12 @@ def test_largest_integers_stay_exact(dev, signs):
     assert bits_equal(got, want), f"max |d| = {np.abs(got - want).max()}"
 
 
-def test_f16_operand_kernel_passes_the_same_cases():
+@pytest.mark.parametrize("choice", ["1", "2"])
+def test_f16_operand_kernels_pass_the_same_cases(choice):
     """the library reads B200_GEMM_TCGEN05_F16 once per process: run this file's other tests in a child with it set"""
-    if os.environ.get("B200_GEMM_TCGEN05_F16") == "1":
+    if os.environ.get("B200_GEMM_TCGEN05_F16") in ("1", "2"):
         pytest.skip("already the child")
-    env = dict(os.environ, B200_GEMM_TCGEN05_F16="1")
+    env = dict(os.environ, B200_GEMM_TCGEN05_F16=choice)
     r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-x", "-q", "-m", "gpu", "-p", "no:cacheprovider"], env=env,
                        capture_output=True, text=True, timeout=1200)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
