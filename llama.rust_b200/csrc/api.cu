@@ -42,7 +42,7 @@ struct Scratch {
     size_t bytes = 0;
 };
 static std::mutex g_scratch_mu;
-static Scratch g_scratch[3][64];   // [0] general scratch, [1] the K-split exchange of the decode mat-mul (lives across the other's users)
+static Scratch g_scratch[4][64];   // [0] general scratch, [1] the K-split exchange of the decode mat-mul (lives across the other's users)
 static unsigned long long g_scratch_gen = 0;
 
 // bumped whenever a scratch block is replaced: a captured CUDA graph that baked the old address in is stale
@@ -55,6 +55,7 @@ static int scratch_get_slot(int slot, size_t bytes, void **ptr);
 int scratch_get(size_t bytes, void **ptr) { return scratch_get_slot(0, bytes, ptr); }
 int scratch_get_kx(size_t bytes, void **ptr) { return scratch_get_slot(1, bytes, ptr); }
 int scratch_get_lists(size_t bytes, void **ptr) { return scratch_get_slot(2, bytes, ptr); }   // attention's visible-position lists
+int scratch_get_images(size_t bytes, void **ptr) { return scratch_get_slot(3, bytes, ptr); }  // the prompt mat-mul's f16 operand images
 static int scratch_get_slot(int slot, size_t bytes, void **ptr) {
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));

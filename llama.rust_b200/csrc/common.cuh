@@ -138,6 +138,8 @@ int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t
                         cudaStream_t s);
 // Q4_K gemm chain with the scales folded into f16 operands, 128 x 64 per CTA (gemm_tcgen05_f16.cu)
 int launch_gemm_tcgen05_f16x64(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s);
+// the same chain in two passes: operands expanded to f16 images once, then a mat-mul that only copies, multiplies and drains (gemm_tcgen05_img.cu)
+int launch_gemm_tcgen05_img(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s);
 // up to four ROPE / SET_ROWS (F32 -> F16) nodes for one launch, see glue_batch_kernel
 constexpr int GLUE_BATCH_MAX = 4;
 enum { GLUE_ROPE = 1, GLUE_SET_ROWS = 2 };
@@ -199,6 +201,7 @@ int launch_argmax(const float *x, int64_t x_stride, int64_t ne0, int64_t nrows, 
 int scratch_get(size_t bytes, void **ptr);
 int scratch_get_kx(size_t bytes, void **ptr);   // a second block, for the K-split exchange of the decode mat-mul
 int scratch_get_lists(size_t bytes, void **ptr);   // a third, for attention's visible-position lists
+int scratch_get_images(size_t bytes, void **ptr);  // a fourth, for the prompt mat-mul's f16 operand images (the activations sit in the first)
 // graph_compute brackets a node list with (true) / (false): inside, attention reuses the lists of an unchanged mask
 void flash_attn_graph_scope(bool enter);
 

@@ -662,12 +662,13 @@ gemm_q4_K_tcgen05_f16_kernel(const uint8_t *__restrict__ tiles, ActView acts, fl
 // 160 us against the integer kernel's 145 us: its epilogue is four times cheaper, but every worker converts,
 // hands over and drains in sequence, and the per-step hand-off and load latencies (2 operand stages of 88 KB
 // are all that fits) are not hidden.  It stays selectable until its pipeline is deeper.
-// B200_GEMM_TCGEN05_F16: 1 = the 32-column f16-operand kernel of this file, 2 = the 64-column one (gemm_tcgen05_f16.cu)
+// B200_GEMM_TCGEN05_F16: 1 = the 32-column f16-operand kernel of this file, 2 = the 64-column one (gemm_tcgen05_f16.cu),
+// 3 = the two-pass one (gemm_tcgen05_img.cu)
 static int gemm_tcgen05_f16_choice() {
     static int v = -1;
     if (v < 0) {
         const char *e = getenv("B200_GEMM_TCGEN05_F16");
-        v = (e && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
+        v = (e && e[0] >= '1' && e[0] <= '3') ? e[0] - '0' : 0;
     }
     return v;
 }
@@ -679,6 +680,7 @@ int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t
     B200_REQUIRE(mode == 1 || mode == 2, "gemm: unknown mode %d", mode);
     if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
     if (mode == 1 && gemm_tcgen05_f16_choice() == 2) return launch_gemm_tcgen05_f16x64(n, k, m, tiles, acts, dst, lddst, s);
+    if (mode == 1 && gemm_tcgen05_f16_choice() == 3) return launch_gemm_tcgen05_img(n, k, m, tiles, acts, dst, lddst, s);
     static bool attr_done[64] = {false};
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));

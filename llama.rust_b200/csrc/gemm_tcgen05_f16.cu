@@ -55,8 +55,10 @@ __device__ __forceinline__ void x_mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void x_mbar_arrive(uint32_t bar) {
     asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(bar) : "memory");
 }
+template <int SLEEP = 0>
 __device__ __forceinline__ bool x_mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     for (uint32_t it = 0; it < FX_WAIT_LIMIT; it++) {
+        if (SLEEP > 0 && it > 0) __nanosleep(SLEEP);
         uint32_t ok;
         asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
                      : "=r"(ok)
@@ -82,9 +84,13 @@ __device__ __forceinline__ void x_tmem_ld8f(float (&v)[8], uint32_t taddr) {
 }
 __device__ __forceinline__ uint32_t x_h2_bits(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
 __device__ __forceinline__ __half2 x_bits_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
-// nibbles at bit `shift` of bytes 0 and 2 of the word, times the scale: (1024 + w) s - 1024 s, exact
-__device__ __forceinline__ uint32_t x_scaled(uint32_t word, int shift, __half2 s2, __half2 c2) {
-    return x_h2_bits(__hfma2(x_bits_h2(((word >> shift) & 0x000f000fu) | 0x64006400u), s2, c2));
+// low nibbles of bytes 0 and 2 of the word, times the scale: (1024 + w) s - 1024 s, one rounding, exact
+__device__ __forceinline__ uint32_t x_scaled_lo(uint32_t word, __half2 s2, __half2 c2) {
+    return x_h2_bits(__hfma2(x_bits_h2((word & 0x000f000fu) | 0x64006400u), s2, c2));
+}
+// high nibbles, left where they are: (1024 + 16 w) (s / 16) - 64 s; s / 16 and 64 s are exact in f16
+__device__ __forceinline__ uint32_t x_scaled_hi(uint32_t word, __half2 s16, __half2 c16) {
+    return x_h2_bits(__hfma2(x_bits_h2((word & 0x00f000f0u) | 0x64006400u), s16, c16));
 }
 // an integer 0 .. 1023 in both halves: (1024 + v) - 1024 on the FMA pipe, no integer-to-float conversion
 __device__ __forceinline__ __half2 x_small2(uint32_t v) {
@@ -95,7 +101,7 @@ __device__ __forceinline__ uint32_t x_signed(uint32_t u, int shift) {
     return x_h2_bits(__hsub2(x_bits_h2(((u >> shift) & 0x00ff00ffu) | 0x64006400u), __float2half2_rn(1152.0f)));
 }
 
-struct FxBars {
+struct alignas(16) FxBars {
     uint64_t full[FX_STAGES], empty[FX_STAGES], tfull[FX_TSTAGES], tempty[FX_TSTAGES];
     float da[FX_DA_SLOTS][FX_COLS];
     uint32_t tmem_base;
@@ -104,6 +110,7 @@ struct FxBars {
 
 }  // namespace
 
+template <int SLEEP>
 __global__ void __launch_bounds__(FX_THREADS, 1)
 gemm_q4_K_tcgen05_f16x64_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *dst, int64_t lddst, int64_t n, int nb, int64_t m, int *err) {
     extern __shared__ uint8_t fx_raw[];
@@ -193,7 +200,7 @@ gemm_q4_K_tcgen05_f16x64_kernel(const uint8_t *__restrict__ tiles, ActView acts,
                 const short4 bs = bs_n;
                 const float dx = dx_n;
                 dd_cur = hd.x;
-                if (!__all_sync(0xffffffffu, x_mbar_wait(x_smem_u32(&bars.empty[s]), sph ^ 1u, abort_flag))) break;
+                if (!__all_sync(0xffffffffu, x_mbar_wait<SLEEP>(x_smem_u32(&bars.empty[s]), sph ^ 1u, abort_flag))) break;
                 const uint32_t stage = smem + (uint32_t)(s * FX_STAGE_BYTES);
                 if (aj == 0) {
                     const uint32_t mn0 = hd.z & 0x3f3f3f3fu, mn1 = ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4);
@@ -210,12 +217,14 @@ gemm_q4_K_tcgen05_f16x64_kernel(const uint8_t *__restrict__ tiles, ActView acts,
                     const uint32_t s_lo = (scw >> (16 * (g & 1))) & 0xffu, s_hi = (scw >> (16 * (g & 1) + 8)) & 0xffu;
                     const __half2 sl = x_small2(s_lo), sh = x_small2(s_hi);
                     // -1024 s <= 64512 in magnitude: a multiple of 1024 below 65504, exact in f16
-                    const __half2 cl = __hmul2(sl, __float2half2_rn(-1024.0f)), ch = __hmul2(sh, __float2half2_rn(-1024.0f));
+                    const __half2 cl = __hmul2(sl, __float2half2_rn(-1024.0f)), ch = __hmul2(sh, __float2half2_rn(-64.0f));
+                    const __half2 sh16 = __hmul2(sh, __float2half2_rn(0.0625f));
+                    const uint32_t x8 = w.x >> 8, y8 = w.y >> 8, z8 = w.z >> 8, w8 = w.w >> 8;   // bytes 1 and 3
                     const uint32_t dstp = stage + a_off;
-                    x_sts128(dstp, x_scaled(w.x, 0, sl, cl), x_scaled(w.x, 8, sl, cl), x_scaled(w.y, 0, sl, cl), x_scaled(w.y, 8, sl, cl));
-                    x_sts128(dstp + 128, x_scaled(w.z, 0, sl, cl), x_scaled(w.z, 8, sl, cl), x_scaled(w.w, 0, sl, cl), x_scaled(w.w, 8, sl, cl));
-                    x_sts128(dstp + 256, x_scaled(w.x, 4, sh, ch), x_scaled(w.x, 12, sh, ch), x_scaled(w.y, 4, sh, ch), x_scaled(w.y, 12, sh, ch));
-                    x_sts128(dstp + 384, x_scaled(w.z, 4, sh, ch), x_scaled(w.z, 12, sh, ch), x_scaled(w.w, 4, sh, ch), x_scaled(w.w, 12, sh, ch));
+                    x_sts128(dstp, x_scaled_lo(w.x, sl, cl), x_scaled_lo(x8, sl, cl), x_scaled_lo(w.y, sl, cl), x_scaled_lo(y8, sl, cl));
+                    x_sts128(dstp + 128, x_scaled_lo(w.z, sl, cl), x_scaled_lo(z8, sl, cl), x_scaled_lo(w.w, sl, cl), x_scaled_lo(w8, sl, cl));
+                    x_sts128(dstp + 256, x_scaled_hi(w.x, sh16, ch), x_scaled_hi(x8, sh16, ch), x_scaled_hi(w.y, sh16, ch), x_scaled_hi(y8, sh16, ch));
+                    x_sts128(dstp + 384, x_scaled_hi(w.z, sh16, ch), x_scaled_hi(z8, sh16, ch), x_scaled_hi(w.w, sh16, ch), x_scaled_hi(w8, sh16, ch));
                 }
                 {
                     const uint32_t u0 = y.x ^ 0x80808080u, u1 = y.y ^ 0x80808080u, u2 = y.z ^ 0x80808080u, u3 = y.w ^ 0x80808080u;
@@ -256,12 +265,12 @@ gemm_q4_K_tcgen05_f16x64_kernel(const uint8_t *__restrict__ tiles, ActView acts,
                 const int e = hb - 1, t = e % FX_TSTAGES, be = e >> 1;
                 const uint32_t tph = (uint32_t)(e / FX_TSTAGES) & 1u;
                 // full[] of that step completed long ago; waiting on it orders this warp's reads of da[] after the store
-                const bool ready = x_mbar_wait(x_smem_u32(&bars.full[e % FX_STAGES]), (uint32_t)(e / FX_STAGES) & 1u, abort_flag) &&
-                                   x_mbar_wait(x_smem_u32(&bars.tfull[t]), tph, abort_flag);
+                const bool ready = x_mbar_wait<SLEEP>(x_smem_u32(&bars.full[e % FX_STAGES]), (uint32_t)(e / FX_STAGES) & 1u, abort_flag) &&
+                                   x_mbar_wait<SLEEP>(x_smem_u32(&bars.tfull[t]), tph, abort_flag);
                 if (!__all_sync(0xffffffffu, ready)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const float dw = f16_bits_to_f32((uint16_t)(de & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(de >> 16));
-                const float *das = bars.da[be % FX_DA_SLOTS] + 16 * h4;
+                const float4 *das = reinterpret_cast<const float4 *>(bars.da[be % FX_DA_SLOTS] + 16 * h4);
                 const uint32_t trow = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(t * 256 + 16 * h4);
 #pragma unroll
                 for (int pc = 0; pc < 4; pc++) {
@@ -278,10 +287,15 @@ gemm_q4_K_tcgen05_f16x64_kernel(const uint8_t *__restrict__ tiles, ActView acts,
                     }
                     if (any_col) {
 #pragma unroll
-                        for (int c = 0; c < 8; c++) {
-                            const float dxe = das[c0 + c];
-                            sumf[c0 + c] = __fmaf_rn(ig[c], __fmul_rn(dw, dxe), sumf[c0 + c]);
-                            summin[c0 + c] = __fmaf_rn(mg[c], __fmul_rn(dmw, dxe), summin[c0 + c]);
+                        for (int h = 0; h < 2; h++) {
+                            const float4 dq = das[c0 / 4 + h];
+                            const float dxs[4] = {dq.x, dq.y, dq.z, dq.w};
+#pragma unroll
+                            for (int c4 = 0; c4 < 4; c4++) {
+                                const int c = 4 * h + c4;
+                                sumf[c0 + c] = __fmaf_rn(ig[c], __fmul_rn(dw, dxs[c4]), sumf[c0 + c]);
+                                summin[c0 + c] = __fmaf_rn(mg[c], __fmul_rn(dmw, dxs[c4]), summin[c0 + c]);
+                            }
                         }
                     }
                 }
@@ -346,7 +360,9 @@ int launch_gemm_tcgen05_f16x64(int64_t n, int64_t k, int64_t m, const uint8_t *t
     B200_CUDA(cudaGetDevice(&dev));
     B200_REQUIRE(dev >= 0 && dev < 64, "gemm: device index %d out of range", dev);
     if (!attr_done[dev]) {
-        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_f16x64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FX_SMEM_BYTES));
+        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_f16x64_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, FX_SMEM_BYTES));
+        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_f16x64_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, FX_SMEM_BYTES));
+        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_f16x64_kernel<100>, cudaFuncAttributeMaxDynamicSharedMemorySize, FX_SMEM_BYTES));
         attr_done[dev] = true;
     }
     int *err = nullptr;
@@ -355,7 +371,9 @@ int launch_gemm_tcgen05_f16x64(int64_t n, int64_t k, int64_t m, const uint8_t *t
     const int nb = (int)(k / GROUP_K);
     const int64_t gx = (m + FX_COLS - 1) / FX_COLS, gy = (n + FX_ROWS - 1) / FX_ROWS;
     B200_REQUIRE(gx < 0x7fffffffLL && gy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);
-    return launch_pdl(gemm_q4_K_tcgen05_f16x64_kernel, dim3((unsigned)gx, (unsigned)gy), dim3(FX_THREADS), (size_t)FX_SMEM_BYTES, s, tiles, acts,
+    static const int sleep_ns = getenv("B200_FX_SLEEP") ? atoi(getenv("B200_FX_SLEEP")) : 0;
+    auto kern = sleep_ns >= 100 ? gemm_q4_K_tcgen05_f16x64_kernel<100> : sleep_ns > 0 ? gemm_q4_K_tcgen05_f16x64_kernel<32> : gemm_q4_K_tcgen05_f16x64_kernel<0>;
+    return launch_pdl(kern, dim3((unsigned)gx, (unsigned)gy), dim3(FX_THREADS), (size_t)FX_SMEM_BYTES, s, tiles, acts,
                       dst, lddst, n, nb, m, err);
 }
 
