@@ -662,15 +662,30 @@ gemm_q4_K_tcgen05_f16_kernel(const uint8_t *__restrict__ tiles, ActView acts, fl
 // 160 us against the integer kernel's 145 us: its epilogue is four times cheaper, but every worker converts,
 // hands over and drains in sequence, and the per-step hand-off and load latencies (2 operand stages of 88 KB
 // are all that fits) are not hidden.  It stays selectable until its pipeline is deeper.
-// B200_GEMM_TCGEN05_F16: 1 = the 32-column f16-operand kernel of this file, 2 = the 64-column one (gemm_tcgen05_f16.cu),
-// 3 = the two-pass one (gemm_tcgen05_img.cu)
+// B200_GEMM_TCGEN05_F16 picks the kernel of the gemm chain: 0 = the integer kernel of this file, 1 = its 32-column
+// f16-operand kernel, 2 = the 64-column one (gemm_tcgen05_f16.cu), 3 = the two-pass one (gemm_tcgen05_img.cu);
+// unset = by estimated time, integer or two-pass (gemm_chain_prefers_images below).
 static int gemm_tcgen05_f16_choice() {
-    static int v = -1;
-    if (v < 0) {
+    static int v = -2;
+    if (v == -2) {
         const char *e = getenv("B200_GEMM_TCGEN05_F16");
-        v = (e && e[0] >= '1' && e[0] <= '3') ? e[0] - '0' : 0;
+        v = (e && e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : -1;
     }
     return v;
+}
+
+// Both kernels run one CTA per SM and take the same time per wave of CTAs at a given K (measured at K = 4096:
+// 37 us); the integer kernel covers 128 x 32 outputs per CTA, the two-pass one 128 x 64 after expanding the
+// operands (8.7 us per 4096 x 4096 weights, 5.2 us per 512 x 4096 activations: 0.235 and 0.14 of a wave).
+static bool gemm_chain_prefers_images(int64_t n, int64_t m) {
+    static int sms[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    if (sms[dev] == 0 && (cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms[dev] <= 0)) sms[dev] = 148;
+    const int64_t gy = (n + 127) / 128, g32 = (m + 31) / 32, g64 = (m + 63) / 64;
+    const double waves_int = (double)((gy * g32 + sms[dev] - 1) / sms[dev]);
+    const double waves_img = (double)((gy * g64 + sms[dev] - 1) / sms[dev]) + 0.235 * (double)gy / 32.0 + 0.14 * (double)g64 / 8.0 + 0.05;
+    return waves_img < waves_int;
 }
 
 // mode: 1 = Q4_K gemm chain, 2 = Q4_K tiled chain
@@ -679,8 +694,9 @@ int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t
     B200_REQUIRE(k % GROUP_K == 0, "gemm: k = %lld must be a multiple of 256", (long long)k);
     B200_REQUIRE(mode == 1 || mode == 2, "gemm: unknown mode %d", mode);
     if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
-    if (mode == 1 && gemm_tcgen05_f16_choice() == 2) return launch_gemm_tcgen05_f16x64(n, k, m, tiles, acts, dst, lddst, s);
-    if (mode == 1 && gemm_tcgen05_f16_choice() == 3) return launch_gemm_tcgen05_img(n, k, m, tiles, acts, dst, lddst, s);
+    const int choice = gemm_tcgen05_f16_choice();
+    if (mode == 1 && choice == 2) return launch_gemm_tcgen05_f16x64(n, k, m, tiles, acts, dst, lddst, s);
+    if (mode == 1 && (choice == 3 || (choice < 0 && gemm_chain_prefers_images(n, m)))) return launch_gemm_tcgen05_img(n, k, m, tiles, acts, dst, lddst, s);
     static bool attr_done[64] = {false};
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
@@ -698,7 +714,7 @@ int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t
     const int64_t gx = (m + TC_COLS - 1) / TC_COLS, gy = (n + TC_ROWS - 1) / TC_ROWS;
     B200_REQUIRE(gx < 0x7fffffffLL && gy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);
     const dim3 grid((unsigned)gx, (unsigned)gy), block(TC_THREADS);
-    if (mode == 1 && gemm_tcgen05_f16_choice() == 1)
+    if (mode == 1 && choice == 1)
         return launch_pdl(gemm_q4_K_tcgen05_f16_kernel, grid, dim3(TF_THREADS), (size_t)TF_SMEM_BYTES, s, tiles, acts, dst, lddst, n, nb, m, err);
     if (mode == 1) return launch_pdl(gemm_q4_K_tcgen05_kernel<1>, grid, block, (size_t)TC_SMEM_BYTES, s, tiles, acts, dst, lddst, n, nb, m, err);
     return launch_pdl(gemm_q4_K_tcgen05_kernel<2>, grid, block, (size_t)TC_SMEM_BYTES, s, tiles, acts, dst, lddst, n, nb, m, err);

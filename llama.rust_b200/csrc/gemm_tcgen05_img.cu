@@ -256,7 +256,8 @@ gemm_q4_K_tcgen05_img_kernel(const uint8_t *__restrict__ tiles, const uint8_t *_
         const bool any_col = col0 + 16 * h4 < m;
         // (d, dmin) of this thread's row, one word per super-block, fetched one super-block ahead
         const uint8_t *hdr = tiles + (row_ok ? tile0 + q : 0) * (int64_t)nb * 4608 + lane * 16;
-        uint32_t dd_next = row_ok ? *(const uint32_t *)(hdr) : 0u, de = 0;
+        uint32_t dd_next = row_ok ? *(const uint32_t *)(hdr) : 0u;
+        float dw = 0.0f, dmw = 0.0f;
         float sumf[16], summin[16];
 #pragma unroll
         for (int c = 0; c < 16; c++) sumf[c] = summin[c] = 0.0f;
@@ -265,26 +266,27 @@ gemm_q4_K_tcgen05_img_kernel(const uint8_t *__restrict__ tiles, const uint8_t *_
         for (int e = 0; e < nh; e++) {
             const int t = e % IM_TSTAGES, be = e >> 1;
             if ((e & 1) == 0) {
-                de = dd_next;
+                dw = f16_bits_to_f32((uint16_t)(dd_next & 0xffffu));
+                dmw = f16_bits_to_f32((uint16_t)(dd_next >> 16));
                 if (be + 1 < nb && row_ok) dd_next = *(const uint32_t *)(hdr + (int64_t)(be + 1) * 4608);
             }
             // the accumulators of step e are complete; so are the copies the MMAs waited for, the scales among them
             if (!__all_sync(0xffffffffu, i_mbar_wait(i_smem_u32(&bars.tfull[t]), (uint32_t)(e / IM_TSTAGES) & 1u, abort_flag))) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float dw = f16_bits_to_f32((uint16_t)(de & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(de >> 16));
             const float4 *das = reinterpret_cast<const float4 *>(bars.da[be % IM_DA_SLOTS] + 16 * h4);
             const uint32_t trow = trow0 + (uint32_t)(t * 256);
-            // four rounds (pair gl, columns c0 .. c0 + 7), the next round's loads in flight while this one's
-            // multiply-adds run:  sumf = fma(f32(ig), d d_x, sumf);  summin = fma(f32(mg), dmin d_x, summin)
-            float ig[2][8], mg[2][8];
+            // four rounds (columns c0 .. c0 + 7, pair gl), the next round's loads in flight while this one's
+            // multiply-adds run:  sumf = fma(f32(ig), d d_x, sumf);  summin = fma(f32(mg), dmin d_x, summin).
+            // The two pairs of a column group follow each other so that the products d d_x, dmin d_x are made once.
+            float ig[2][8], mg[2][8], pd[8], pm[8];
             i_tmem_ld8f(ig[0], trow);
             i_tmem_ld8f(mg[0], trow + 128);
 #pragma unroll
             for (int r = 0; r < 4; r++) {
-                const int c0 = 8 * (r & 1);
+                const int c0 = 8 * (r >> 1);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (r < 3) {
-                    const int gl1 = (r + 1) >> 1, c1 = 8 * ((r + 1) & 1);
+                    const int gl1 = (r + 1) & 1, c1 = 8 * ((r + 1) >> 1);
                     i_tmem_ld8f(ig[(r + 1) & 1], trow + (uint32_t)(gl1 * IM_COLS + c1));
                     i_tmem_ld8f(mg[(r + 1) & 1], trow + (uint32_t)(128 + gl1 * IM_COLS + c1));
                 } else {
@@ -294,16 +296,22 @@ gemm_q4_K_tcgen05_img_kernel(const uint8_t *__restrict__ tiles, const uint8_t *_
                     if (lane == 0) i_mbar_arrive(i_smem_u32(&bars.tempty[t]));
                 }
                 if (any_col) {
+                    if ((r & 1) == 0) {
 #pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        const float4 dq = das[c0 / 4 + h];
-                        const float dxs[4] = {dq.x, dq.y, dq.z, dq.w};
+                        for (int h = 0; h < 2; h++) {
+                            const float4 dq = das[c0 / 4 + h];
+                            const float dxs[4] = {dq.x, dq.y, dq.z, dq.w};
 #pragma unroll
-                        for (int c4 = 0; c4 < 4; c4++) {
-                            const int c = 4 * h + c4;
-                            sumf[c0 + c] = __fmaf_rn(ig[r & 1][c], __fmul_rn(dw, dxs[c4]), sumf[c0 + c]);
-                            summin[c0 + c] = __fmaf_rn(mg[r & 1][c], __fmul_rn(dmw, dxs[c4]), summin[c0 + c]);
+                            for (int c4 = 0; c4 < 4; c4++) {
+                                pd[4 * h + c4] = __fmul_rn(dw, dxs[c4]);
+                                pm[4 * h + c4] = __fmul_rn(dmw, dxs[c4]);
+                            }
                         }
+                    }
+#pragma unroll
+                    for (int c = 0; c < 8; c++) {
+                        sumf[c0 + c] = __fmaf_rn(ig[r & 1][c], pd[c], sumf[c0 + c]);
+                        summin[c0 + c] = __fmaf_rn(mg[r & 1][c], pm[c], summin[c0 + c]);
                     }
                 }
             }
