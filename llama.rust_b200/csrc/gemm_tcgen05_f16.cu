@@ -55,10 +55,8 @@ __device__ __forceinline__ void x_mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void x_mbar_arrive(uint32_t bar) {
     asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(bar) : "memory");
 }
-template <int SLEEP = 0>
 __device__ __forceinline__ bool x_mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     for (uint32_t it = 0; it < FX_WAIT_LIMIT; it++) {
-        if (SLEEP > 0 && it > 0) __nanosleep(SLEEP);
         uint32_t ok;
         asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
                      : "=r"(ok)
@@ -110,7 +108,6 @@ struct alignas(16) FxBars {
 
 }  // namespace
 
-template <int SLEEP>
 __global__ void __launch_bounds__(FX_THREADS, 1)
 gemm_q4_K_tcgen05_f16x64_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *dst, int64_t lddst, int64_t n, int nb, int64_t m, int *err) {
     extern __shared__ uint8_t fx_raw[];
@@ -200,7 +197,7 @@ gemm_q4_K_tcgen05_f16x64_kernel(const uint8_t *__restrict__ tiles, ActView acts,
                 const short4 bs = bs_n;
                 const float dx = dx_n;
                 dd_cur = hd.x;
-                if (!__all_sync(0xffffffffu, x_mbar_wait<SLEEP>(x_smem_u32(&bars.empty[s]), sph ^ 1u, abort_flag))) break;
+                if (!__all_sync(0xffffffffu, x_mbar_wait(x_smem_u32(&bars.empty[s]), sph ^ 1u, abort_flag))) break;
                 const uint32_t stage = smem + (uint32_t)(s * FX_STAGE_BYTES);
                 if (aj == 0) {
                     const uint32_t mn0 = hd.z & 0x3f3f3f3fu, mn1 = ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4);
@@ -265,8 +262,8 @@ gemm_q4_K_tcgen05_f16x64_kernel(const uint8_t *__restrict__ tiles, ActView acts,
                 const int e = hb - 1, t = e % FX_TSTAGES, be = e >> 1;
                 const uint32_t tph = (uint32_t)(e / FX_TSTAGES) & 1u;
                 // full[] of that step completed long ago; waiting on it orders this warp's reads of da[] after the store
-                const bool ready = x_mbar_wait<SLEEP>(x_smem_u32(&bars.full[e % FX_STAGES]), (uint32_t)(e / FX_STAGES) & 1u, abort_flag) &&
-                                   x_mbar_wait<SLEEP>(x_smem_u32(&bars.tfull[t]), tph, abort_flag);
+                const bool ready = x_mbar_wait(x_smem_u32(&bars.full[e % FX_STAGES]), (uint32_t)(e / FX_STAGES) & 1u, abort_flag) &&
+                                   x_mbar_wait(x_smem_u32(&bars.tfull[t]), tph, abort_flag);
                 if (!__all_sync(0xffffffffu, ready)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const float dw = f16_bits_to_f32((uint16_t)(de & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(de >> 16));
@@ -360,9 +357,7 @@ int launch_gemm_tcgen05_f16x64(int64_t n, int64_t k, int64_t m, const uint8_t *t
     B200_CUDA(cudaGetDevice(&dev));
     B200_REQUIRE(dev >= 0 && dev < 64, "gemm: device index %d out of range", dev);
     if (!attr_done[dev]) {
-        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_f16x64_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, FX_SMEM_BYTES));
-        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_f16x64_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, FX_SMEM_BYTES));
-        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_f16x64_kernel<100>, cudaFuncAttributeMaxDynamicSharedMemorySize, FX_SMEM_BYTES));
+        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_f16x64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FX_SMEM_BYTES));
         attr_done[dev] = true;
     }
     int *err = nullptr;
@@ -371,9 +366,7 @@ int launch_gemm_tcgen05_f16x64(int64_t n, int64_t k, int64_t m, const uint8_t *t
     const int nb = (int)(k / GROUP_K);
     const int64_t gx = (m + FX_COLS - 1) / FX_COLS, gy = (n + FX_ROWS - 1) / FX_ROWS;
     B200_REQUIRE(gx < 0x7fffffffLL && gy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);
-    static const int sleep_ns = getenv("B200_FX_SLEEP") ? atoi(getenv("B200_FX_SLEEP")) : 0;
-    auto kern = sleep_ns >= 100 ? gemm_q4_K_tcgen05_f16x64_kernel<100> : sleep_ns > 0 ? gemm_q4_K_tcgen05_f16x64_kernel<32> : gemm_q4_K_tcgen05_f16x64_kernel<0>;
-    return launch_pdl(kern, dim3((unsigned)gx, (unsigned)gy), dim3(FX_THREADS), (size_t)FX_SMEM_BYTES, s, tiles, acts,
+    return launch_pdl(gemm_q4_K_tcgen05_f16x64_kernel, dim3((unsigned)gx, (unsigned)gy), dim3(FX_THREADS), (size_t)FX_SMEM_BYTES, s, tiles, acts,
                       dst, lddst, n, nb, m, err);
 }
 

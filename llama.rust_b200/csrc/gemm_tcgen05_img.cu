@@ -36,7 +36,8 @@ namespace {
 
 constexpr int IM_ROWS = 128, IM_COLS = 64;
 constexpr int IM_EPI_WARPS = 16, IM_MMA_WARP = 16, IM_LOAD_WARP = 17;
-constexpr int IM_THREADS = 18 * 32;
+constexpr int IM_THREADS = 20 * 32;   // four epilogue warp groups + one for the two single-thread roles (two warps idle)
+constexpr int IM_REGS_EPI = 112, IM_REGS_CTL = 32;   // 512 x 112 + 128 x 32 = 640 x 96, what the CTA is launched with
 constexpr int IM_EXPAND_THREADS = 512;
 constexpr int IM_STAGES = 3, IM_TSTAGES = 2;
 constexpr int IM_A_BYTES = IM_ROWS * 256, IM_AM_BYTES = IM_ROWS * 32;
@@ -248,9 +249,11 @@ gemm_q4_K_tcgen05_img_kernel(const uint8_t *__restrict__ tiles, const uint8_t *_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = bars.tmem_base;
-    pdl_wait();   // the images are the two previous kernels' output
-
+    // A CTA of 20 warps starts with 96 registers per thread (five warps share a scheduler's 16384).  The control
+    // warp group gives 64 of them back and the epilogue warp groups take 16 more each: the pool balances exactly.
     if (warp < IM_EPI_WARPS) {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(IM_REGS_EPI));
+        pdl_wait();   // the images are the two previous kernels' output
         const int q = warp & 3, h4 = warp >> 2;
         const bool row_ok = tile0 + q < tiles_n;
         const bool any_col = col0 + 16 * h4 < m;
@@ -275,22 +278,23 @@ gemm_q4_K_tcgen05_img_kernel(const uint8_t *__restrict__ tiles, const uint8_t *_
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float4 *das = reinterpret_cast<const float4 *>(bars.da[be % IM_DA_SLOTS] + 16 * h4);
             const uint32_t trow = trow0 + (uint32_t)(t * 256);
-            // four rounds (columns c0 .. c0 + 7, pair gl), the next round's loads in flight while this one's
-            // multiply-adds run:  sumf = fma(f32(ig), d d_x, sumf);  summin = fma(f32(mg), dmin d_x, summin).
-            // The two pairs of a column group follow each other so that the products d d_x, dmin d_x are made once.
-            float ig[2][8], mg[2][8], pd[8], pm[8];
-            i_tmem_ld8f(ig[0], trow);
-            i_tmem_ld8f(mg[0], trow + 128);
+            // four rounds r = (columns c0 = 8 (r / 2) .. + 7, pair gl = r % 2): sumf = fma(f32(ig), d d_x, sumf);
+            // summin = fma(f32(mg), dmin d_x, summin).  Three rounds' loads go out together, the fourth reuses the
+            // first one's registers and lands while rounds 1 and 2 are computed; the two pairs of a column group
+            // follow each other so that the products d d_x, dmin d_x are made once per group.
+            float ig[3][8], mg[3][8], pd[8], pm[8];
+#pragma unroll
+            for (int r = 0; r < 3; r++) {
+                i_tmem_ld8f(ig[r], trow + (uint32_t)((r & 1) * IM_COLS + 8 * (r >> 1)));
+                i_tmem_ld8f(mg[r], trow + (uint32_t)(128 + (r & 1) * IM_COLS + 8 * (r >> 1)));
+            }
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
             for (int r = 0; r < 4; r++) {
-                const int c0 = 8 * (r >> 1);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (r < 3) {
-                    const int gl1 = (r + 1) & 1, c1 = 8 * ((r + 1) >> 1);
-                    i_tmem_ld8f(ig[(r + 1) & 1], trow + (uint32_t)(gl1 * IM_COLS + c1));
-                    i_tmem_ld8f(mg[(r + 1) & 1], trow + (uint32_t)(128 + gl1 * IM_COLS + c1));
-                } else {
+                const int c0 = 8 * (r >> 1), buf = r == 3 ? 0 : r;
+                if (r == 3) {
                     // every value of the stage is in registers: hand it back to the MMA thread
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) i_mbar_arrive(i_smem_u32(&bars.tempty[t]));
@@ -310,9 +314,14 @@ gemm_q4_K_tcgen05_img_kernel(const uint8_t *__restrict__ tiles, const uint8_t *_
                     }
 #pragma unroll
                     for (int c = 0; c < 8; c++) {
-                        sumf[c0 + c] = __fmaf_rn(ig[r & 1][c], pd[c], sumf[c0 + c]);
-                        summin[c0 + c] = __fmaf_rn(mg[r & 1][c], pm[c], summin[c0 + c]);
+                        sumf[c0 + c] = __fmaf_rn(ig[buf][c], pd[c], sumf[c0 + c]);
+                        summin[c0 + c] = __fmaf_rn(mg[buf][c], pm[c], summin[c0 + c]);
                     }
+                }
+                if (r == 0) {
+                    // round 3 into round 0's registers, now consumed
+                    i_tmem_ld8f(ig[0], trow + (uint32_t)(IM_COLS + 8));
+                    i_tmem_ld8f(mg[0], trow + (uint32_t)(128 + IM_COLS + 8));
                 }
             }
         }
@@ -324,7 +333,10 @@ gemm_q4_K_tcgen05_img_kernel(const uint8_t *__restrict__ tiles, const uint8_t *_
                 if (col < m) dst[col * lddst + row] = __fsub_rn(sumf[c], summin[c]);
             }
         }
-    } else if (warp == IM_MMA_WARP) {
+    } else {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(IM_REGS_CTL));
+      pdl_wait();
+      if (warp == IM_MMA_WARP) {
         if (lane == 0) {
             // per step: two pairs x (four K = 16 MMAs for ig, one for mg)
             for (int hb = 0; hb < nh; hb++) {
@@ -357,7 +369,7 @@ gemm_q4_K_tcgen05_img_kernel(const uint8_t *__restrict__ tiles, const uint8_t *_
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(i_smem_u32(&bars.tfull[t])) : "memory");
             }
         }
-    } else if (warp == IM_LOAD_WARP && lane == 0) {
+      } else if (warp == IM_LOAD_WARP && lane == 0) {
         // ---- loader: the images of step hb into stage hb % 3, the scales of a super-block with its first step ----
         const uint8_t *asrc = aimg + rb * nh * (int64_t)IM_AIMG, *bsrc = bimg + cb * nh * (int64_t)IM_BIMG;
         const float *dsrc = daimg + cb * nb * (int64_t)IM_COLS;
@@ -377,6 +389,7 @@ gemm_q4_K_tcgen05_img_kernel(const uint8_t *__restrict__ tiles, const uint8_t *_
         }
         // gave up somewhere: let the copies already in flight land before the CTA's shared memory goes away
         if (*abort_flag && issued >= 0) i_mbar_wait(i_smem_u32(&bars.full[issued % IM_STAGES]), (uint32_t)(issued / IM_STAGES) & 1u, abort_flag);
+      }
     }
     // ---- teardown: every role has left its loop (finished, or gave up) ----
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
