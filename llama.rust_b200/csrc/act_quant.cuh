@@ -62,4 +62,54 @@ __device__ __forceinline__ void q8_K_block_store(float v, const ActBuf &out, int
     __syncthreads();   // the shared arrays may be reused by a following call
 }
 
+// The same block handled by one warp: lane l holds elements 8 l .. 8 l + 7 of the 256.  No shared memory and no
+// CTA barrier: warps of a CTA work on different blocks.  Same values as q8_K_block_store: the first largest |v|
+// in index order, the same scale and rounding rules.
+template <bool A3>
+__device__ __forceinline__ void q8_K_block_store_warp(const float (&v)[8], const ActBuf &out, int64_t row, int64_t blk) {
+    const int lane = threadIdx.x & 31;
+    const int64_t nb = out.k / 256;
+    float a = fabsf(v[0]), mv = v[0];
+    int idx = 8 * lane;
+#pragma unroll
+    for (int j = 1; j < 8; j++) {
+        const float aj = fabsf(v[j]);
+        if (aj > a) { a = aj; mv = v[j]; idx = 8 * lane + j; }   // strict '>': the first of equals stays
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float a2 = __shfl_xor_sync(0xffffffffu, a, o), m2 = __shfl_xor_sync(0xffffffffu, mv, o);
+        const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (a2 > a || (a2 == a && i2 < idx)) { a = a2; mv = m2; idx = i2; }
+    }
+    const float amax = a, maxv = mv;
+    int q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    float d = 0.0f;
+    if (amax != 0.0f) {
+        if (A3) {
+            const float iscale = __fdiv_rn(127.0f, amax);
+#pragma unroll
+            for (int j = 0; j < 8; j++) q[j] = max(-128, min(127, __float2int_rn(__fmul_rn(iscale, v[j]))));
+            d = __fdiv_rn(1.0f, iscale);
+        } else {
+            const float iscale = __fdiv_rn(-127.0f, maxv);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                // nearest_int(): crates/ggml/src/quants.rs:13-18
+                const float val = __fadd_rn(__fmul_rn(iscale, v[j]), 12582912.0f);
+                q[j] = min(127, (__float_as_int(val) & 0x007fffff) - 0x00400000);
+            }
+            d = __fdiv_rn(1.0f, iscale);
+        }
+    }
+    uint2 packed;
+    packed.x = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
+    packed.y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+    *reinterpret_cast<uint2 *>(out.qs + row * out.k + blk * 256 + 8 * lane) = packed;
+    int s = q[0] + q[1] + q[2] + q[3] + q[4] + q[5] + q[6] + q[7];
+    s += __shfl_xor_sync(0xffffffffu, s, 1);   // a 16-element sum is two lanes
+    if ((lane & 1) == 0) out.bsums[row * (out.k / 16) + blk * 16 + (lane >> 1)] = (int16_t)s;
+    if (lane == 0) out.d[row * nb + blk] = d;
+}
+
 }  // namespace b200

@@ -140,6 +140,7 @@ int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t
 int launch_gemm_tcgen05_f16x64(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s);
 // the same chain in two passes: operands expanded to f16 images once, then a mat-mul that only copies, multiplies and drains (gemm_tcgen05_img.cu)
 int launch_gemm_tcgen05_img(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s);
+int launch_gemm_tcgen05_img128(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s);   // 128 activation rows per CTA
 // up to four ROPE / SET_ROWS (F32 -> F16) nodes for one launch, see glue_batch_kernel
 constexpr int GLUE_BATCH_MAX = 4;
 enum { GLUE_ROPE = 1, GLUE_SET_ROWS = 2 };

@@ -664,28 +664,31 @@ gemm_q4_K_tcgen05_f16_kernel(const uint8_t *__restrict__ tiles, ActView acts, fl
 // are all that fits) are not hidden.  It stays selectable until its pipeline is deeper.
 // B200_GEMM_TCGEN05_F16 picks the kernel of the gemm chain: 0 = the integer kernel of this file, 1 = its 32-column
 // f16-operand kernel, 2 = the 64-column one (gemm_tcgen05_f16.cu), 3 = the two-pass one (gemm_tcgen05_img.cu);
-// unset = by estimated time, integer or two-pass (gemm_chain_prefers_images below).
+// 4 = the two-pass one with 128 activation rows per CTA; unset = by estimated time among 0, 3 and 4 (gemm_chain_pick below).
 static int gemm_tcgen05_f16_choice() {
     static int v = -2;
     if (v == -2) {
         const char *e = getenv("B200_GEMM_TCGEN05_F16");
-        v = (e && e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : -1;
+        v = (e && e[0] >= '0' && e[0] <= '4') ? e[0] - '0' : -1;
     }
     return v;
 }
 
-// Both kernels run one CTA per SM and take the same time per wave of CTAs at a given K (measured at K = 4096:
-// 37 us); the integer kernel covers 128 x 32 outputs per CTA, the two-pass one 128 x 64 after expanding the
-// operands (8.7 us per 4096 x 4096 weights, 5.2 us per 512 x 4096 activations: 0.235 and 0.14 of a wave).
-static bool gemm_chain_prefers_images(int64_t n, int64_t m) {
+// One CTA per SM in every kernel.  Measured at K = 4096: a wave of CTAs takes 37 us in the integer kernel (128 x 32
+// outputs per CTA) and in the 64-column two-pass kernel (128 x 64), 1.85 times that in the 128-column one
+// (128 x 128); expanding the operands costs 8.7 us per 4096 x 4096 weights and 5.2 us per 512 x 4096 activations
+// (0.235 and 0.14 of a wave).  Returns 0 = integer kernel, 3 = two-pass with 64 columns, 4 = with 128.
+static int gemm_chain_pick(int64_t n, int64_t m) {
     static int sms[64] = {0};
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
     if (sms[dev] == 0 && (cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms[dev] <= 0)) sms[dev] = 148;
-    const int64_t gy = (n + 127) / 128, g32 = (m + 31) / 32, g64 = (m + 63) / 64;
-    const double waves_int = (double)((gy * g32 + sms[dev] - 1) / sms[dev]);
-    const double waves_img = (double)((gy * g64 + sms[dev] - 1) / sms[dev]) + 0.235 * (double)gy / 32.0 + 0.14 * (double)g64 / 8.0 + 0.05;
-    return waves_img < waves_int;
+    const int64_t gy = (n + 127) / 128, g32 = (m + 31) / 32, g64 = (m + 63) / 64, g128 = (m + 127) / 128;
+    const auto waves = [&](int64_t ctas) { return (double)((ctas + sms[dev] - 1) / sms[dev]); };
+    const double expand = 0.235 * (double)gy / 32.0 + 0.14 * (double)g64 / 8.0 + 0.05;
+    const double t_int = waves(gy * g32), t_64 = waves(gy * g64) + expand, t_128 = 1.85 * waves(gy * g128) + expand;
+    if (t_int <= t_64 && t_int <= t_128) return 0;
+    return t_128 < t_64 ? 4 : 3;
 }
 
 // mode: 1 = Q4_K gemm chain, 2 = Q4_K tiled chain
@@ -694,9 +697,11 @@ int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t
     B200_REQUIRE(k % GROUP_K == 0, "gemm: k = %lld must be a multiple of 256", (long long)k);
     B200_REQUIRE(mode == 1 || mode == 2, "gemm: unknown mode %d", mode);
     if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
-    const int choice = gemm_tcgen05_f16_choice();
+    int choice = gemm_tcgen05_f16_choice();
+    if (mode == 1 && choice < 0) choice = gemm_chain_pick(n, m);
     if (mode == 1 && choice == 2) return launch_gemm_tcgen05_f16x64(n, k, m, tiles, acts, dst, lddst, s);
-    if (mode == 1 && (choice == 3 || (choice < 0 && gemm_chain_prefers_images(n, m)))) return launch_gemm_tcgen05_img(n, k, m, tiles, acts, dst, lddst, s);
+    if (mode == 1 && choice == 3) return launch_gemm_tcgen05_img(n, k, m, tiles, acts, dst, lddst, s);
+    if (mode == 1 && choice == 4) return launch_gemm_tcgen05_img128(n, k, m, tiles, acts, dst, lddst, s);
     static bool attr_done[64] = {false};
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));

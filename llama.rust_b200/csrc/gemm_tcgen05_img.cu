@@ -401,7 +401,285 @@ gemm_q4_K_tcgen05_img_kernel(const uint8_t *__restrict__ tiles, const uint8_t *_
     if (threadIdx.x == 0 && bars.abort_flag) atomicExch(err, IM_ERR_WAIT);
 }
 
-int launch_gemm_tcgen05_img(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s) {
+// ---- 128 activation rows per CTA, one sub-block pair per step ------------------------------------------------
+// The 64-column kernel above is bound by shared-memory bandwidth: each of a step's 18 MMAs re-reads its 4 KB of A
+// for 64 columns while the bulk copies write the next images (164 KB through a 128 B/cycle port per step).  With
+// N = 128 an MMA's A read serves twice the columns.  Tensor memory holds two stages of (ig, mg) x 128 columns only
+// if a step is one pair, so the images are cut per pair: A [128 rows][64 f16] 16 KB + Am 4 KB, B [128 rows][64 f16]
+// 16 KB + Bm [128 rows][16 f16] 4 KB, five 40 KB stages.
+namespace {
+constexpr int IW_COLS = 128;
+constexpr int IW_STAGES = 5;
+constexpr int IW_A_BYTES = IM_ROWS * 128, IW_AM_BYTES = IM_ROWS * 32;
+constexpr int IW_B_BYTES = IW_COLS * 128, IW_BM_BYTES = IW_COLS * 32;
+constexpr int IW_AIMG = IW_A_BYTES + IW_AM_BYTES;   // 20480
+constexpr int IW_BIMG = IW_B_BYTES + IW_BM_BYTES;   // 20480
+constexpr int IW_STAGE_BYTES = IW_AIMG + IW_BIMG;   // 40960
+constexpr int IW_SMEM_BYTES = IW_STAGES * IW_STAGE_BYTES + 1024;
+constexpr int IW_DA_BYTES = IW_COLS * 4;
+constexpr uint32_t IW_IDESC = (1u << 4) | ((uint32_t)(IW_COLS >> 3) << 17) | ((uint32_t)(IM_ROWS >> 4) << 24);
+struct alignas(16) IwBars {
+    uint64_t full[IW_STAGES], empty[IW_STAGES], tfull[IM_TSTAGES], tempty[IM_TSTAGES];
+    float da[IM_DA_SLOTS][IW_COLS];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+}  // namespace
+
+// Weights of one 128-row block and one super-block -> the A / Am images of its four steps.  Warp (tt, aj): row
+// (tile tt, lane), 16-byte pieces aj and 4 + aj of the row's 128 nibble bytes, and the Am image of step aj.
+__global__ void __launch_bounds__(IM_EXPAND_THREADS) expand_q4_K_weights_pair_kernel(const uint8_t *__restrict__ tiles, uint8_t *aimg, int64_t tiles_n, int nb) {
+    pdl_trigger();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tt = warp & 3, aj = warp >> 2;
+    const int b = blockIdx.x;
+    const int64_t rb = blockIdx.y, tile = rb * 4 + tt;
+    const bool tile_ok = tile < tiles_n;
+    const uint8_t *src = tiles + ((tile_ok ? tile : 0) * (int64_t)nb + b) * 4608 + lane * 16;
+    uint4 hd = make_uint4(0, 0, 0, 0), wq[2] = {hd, hd};
+    if (tile_ok) {
+        hd = *(const uint4 *)(src);
+        wq[0] = ld_stream16(src + 512 + aj * 512);
+        wq[1] = ld_stream16(src + 512 + (4 + aj) * 512);
+    }
+    pdl_wait();   // the previous mat-mul may still be reading the images
+    const int prow = tt * 32 + lane;
+    uint8_t *img0 = aimg + (rb * 4 * nb + 4 * b) * (int64_t)IW_AIMG;
+    {
+        // all eight mins into the Am image of step aj (Bm selects the pair)
+        const uint32_t mn0 = hd.z & 0x3f3f3f3fu, mn1 = ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4);
+        uint32_t mins[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) mins[j] = i_h2_bits(i_small2(((j < 4 ? mn0 : mn1) >> (8 * (j & 3))) & 0xffu));
+        uint8_t *am = img0 + aj * (int64_t)IW_AIMG + IW_A_BYTES + (prow >> 3) * 256 + (prow & 7) * 16;
+        i_stg128(am, mins[0], mins[1], mins[2], mins[3]);
+        i_stg128(am + 128, mins[4], mins[5], mins[6], mins[7]);
+    }
+    // piece within the pair pp = aj % 2: chunks 4 pp + {0, 1 low | 2, 3 high}
+    const int a_off = (prow >> 3) * 1024 + (prow & 7) * 16 + 4 * (aj & 1) * 128;
+#pragma unroll
+    for (int hs = 0; hs < 2; hs++) {
+        // piece c = 4 hs + aj of the row: pair g = c / 2 (sub-blocks 2 g, 2 g + 1)
+        const int g = 2 * hs + (aj >> 1);
+        const uint4 w = wq[hs];
+        const uint32_t scw = g < 2 ? (hd.y & 0x3f3f3f3fu) : ((hd.w & 0x0f0f0f0fu) | (((hd.y >> 6) & 0x03030303u) << 4));
+        const uint32_t s_lo = (scw >> (16 * (g & 1))) & 0xffu, s_hi = (scw >> (16 * (g & 1) + 8)) & 0xffu;
+        const __half2 sl = i_small2(s_lo), sh = i_small2(s_hi);
+        const __half2 cl = __hmul2(sl, __float2half2_rn(-1024.0f)), ch = __hmul2(sh, __float2half2_rn(-64.0f));
+        const __half2 sh16 = __hmul2(sh, __float2half2_rn(0.0625f));
+        const uint32_t x8 = w.x >> 8, y8 = w.y >> 8, z8 = w.z >> 8, w8 = w.w >> 8;   // bytes 1 and 3
+        uint8_t *dstp = img0 + g * (int64_t)IW_AIMG + a_off;
+        i_stg128(dstp, i_scaled_lo(w.x, sl, cl), i_scaled_lo(x8, sl, cl), i_scaled_lo(w.y, sl, cl), i_scaled_lo(y8, sl, cl));
+        i_stg128(dstp + 128, i_scaled_lo(w.z, sl, cl), i_scaled_lo(z8, sl, cl), i_scaled_lo(w.w, sl, cl), i_scaled_lo(w8, sl, cl));
+        i_stg128(dstp + 256, i_scaled_hi(w.x, sh16, ch), i_scaled_hi(x8, sh16, ch), i_scaled_hi(w.y, sh16, ch), i_scaled_hi(y8, sh16, ch));
+        i_stg128(dstp + 384, i_scaled_hi(w.z, sh16, ch), i_scaled_hi(z8, sh16, ch), i_scaled_hi(w.w, sh16, ch), i_scaled_hi(w8, sh16, ch));
+    }
+}
+
+// Q8_K activations of one 128-row block and one super-block -> the B / Bm images of its four steps and the scales.
+__global__ void __launch_bounds__(IM_EXPAND_THREADS) expand_q8_K_acts_pair_kernel(ActView acts, uint8_t *bimg, float *daimg, int64_t m, int nb) {
+    pdl_trigger();
+    pdl_wait();   // the activations come from the previous kernel
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
+    const int b = blockIdx.x;
+    const int64_t cb = blockIdx.y, K = acts.k;
+    uint8_t *img0 = bimg + (cb * 4 * nb + 4 * b) * (int64_t)IW_BIMG;
+    // a warp reads 64 contiguous bytes (one pair) of 8 activation rows; each quarter warp writes one 128-byte row group
+    const int bc = warp * 8 + (lane & 7), r = lane >> 3;
+    const int64_t col = cb * IW_COLS + bc;
+    // piece r of the pair: (low p0, low p1, high p0, high p1) -> chunks 4 p + 2 hi
+    const int b_off = (bc >> 3) * 1024 + (bc & 7) * 16 + (4 * (r & 1) + 2 * (r >> 1)) * 128;
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+        uint4 y = make_uint4(0, 0, 0, 0);
+        if (col < m) y = *(const uint4 *)(acts.qs + col * K + (int64_t)b * 256 + g * 64 + r * 16);
+        const uint32_t u0 = y.x ^ 0x80808080u, u1 = y.y ^ 0x80808080u, u2 = y.z ^ 0x80808080u, u3 = y.w ^ 0x80808080u;
+        uint8_t *img = img0 + g * (int64_t)IW_BIMG;
+        i_stg128(img + b_off, i_signed(u0, 0), i_signed(u0, 8), i_signed(u1, 0), i_signed(u1, 8));
+        i_stg128(img + b_off + 128, i_signed(u2, 0), i_signed(u2, 8), i_signed(u3, 0), i_signed(u3, 8));
+    }
+    {
+        // sums: thread (row tid / 4, pair tid % 4); the pair's four sums sit in slots 4 g .. 4 g + 3 of the 16
+        const int scol_i = tid >> 2, g = tid & 3;
+        const int64_t scol = cb * IW_COLS + scol_i;
+        short4 bs = make_short4(0, 0, 0, 0);
+        if (scol < m) bs = *(const short4 *)(acts.bsums + scol * (K / 16) + (int64_t)b * 16 + 4 * g);
+        const uint32_t xy = i_h2_bits(__halves2half2(__short2half_rn(bs.x), __short2half_rn(bs.y)));
+        const uint32_t zw = i_h2_bits(__halves2half2(__short2half_rn(bs.z), __short2half_rn(bs.w)));
+        const bool odd = g & 1, second = g >> 1;
+        const uint32_t v0 = odd ? 0u : xy, v1 = odd ? 0u : zw, v2 = odd ? xy : 0u, v3 = odd ? zw : 0u;
+        uint8_t *bm = img0 + g * (int64_t)IW_BIMG + IW_B_BYTES + (scol_i >> 3) * 256 + (scol_i & 7) * 16;
+        i_stg128(bm, second ? 0u : v0, second ? 0u : v1, second ? 0u : v2, second ? 0u : v3);
+        i_stg128(bm + 128, second ? v0 : 0u, second ? v1 : 0u, second ? v2 : 0u, second ? v3 : 0u);
+    }
+    if (tid < IW_COLS) {
+        const int64_t dcol = cb * IW_COLS + tid;
+        daimg[(cb * nb + b) * IW_COLS + tid] = dcol < m ? acts.d[dcol * nb + b] : 0.0f;
+    }
+}
+
+// 128 x 128 outputs per CTA.  Roles as in the 64-column kernel; epilogue warp w owns rows 32 (w % 4) .. + 31 and
+// columns 32 (w / 4) .. + 31.
+__global__ void __launch_bounds__(IM_THREADS, 1)
+gemm_q4_K_tcgen05_img128_kernel(const uint8_t *__restrict__ tiles, const uint8_t *__restrict__ aimg, const uint8_t *__restrict__ bimg,
+                                const float *__restrict__ daimg, float *dst, int64_t lddst, int64_t n, int nb, int64_t m, int *err) {
+    extern __shared__ uint8_t iw_raw[];
+    __shared__ IwBars bars;
+    pdl_trigger();
+    const uint32_t smem = (i_smem_u32(iw_raw) + 1023u) & ~1023u;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t rb = blockIdx.y, cb = blockIdx.x;
+    const int64_t tile0 = rb * (IM_ROWS / TILE_ROWS), tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
+    const int64_t col0 = cb * IW_COLS;
+    const int np = 4 * nb;   // pipeline steps: sub-block pairs
+    volatile int *abort_flag = &bars.abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < IW_STAGES; i++) {
+            i_mbar_init(i_smem_u32(&bars.full[i]), 1);
+            i_mbar_init(i_smem_u32(&bars.empty[i]), 1);
+        }
+        for (int i = 0; i < IM_TSTAGES; i++) {
+            i_mbar_init(i_smem_u32(&bars.tfull[i]), 1);
+            i_mbar_init(i_smem_u32(&bars.tempty[i]), IM_EPI_WARPS);
+        }
+        bars.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == IM_MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(i_smem_u32(&bars.tmem_base)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = bars.tmem_base;
+
+    if (warp < IM_EPI_WARPS) {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(IM_REGS_EPI));
+        pdl_wait();
+        const int q = warp & 3, h4 = warp >> 2;
+        const bool row_ok = tile0 + q < tiles_n;
+        const bool any_col = col0 + 32 * h4 < m;
+        const uint8_t *hdr = tiles + (row_ok ? tile0 + q : 0) * (int64_t)nb * 4608 + lane * 16;
+        uint32_t dd_next = row_ok ? *(const uint32_t *)(hdr) : 0u;
+        float dw = 0.0f, dmw = 0.0f;
+        float sumf[32], summin[32];
+#pragma unroll
+        for (int c = 0; c < 32; c++) sumf[c] = summin[c] = 0.0f;
+        const uint32_t trow0 = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * h4);
+
+        for (int e = 0; e < np; e++) {
+            const int t = e % IM_TSTAGES, be = e >> 2;
+            if ((e & 3) == 0) {
+                dw = f16_bits_to_f32((uint16_t)(dd_next & 0xffffu));
+                dmw = f16_bits_to_f32((uint16_t)(dd_next >> 16));
+                if (be + 1 < nb && row_ok) dd_next = *(const uint32_t *)(hdr + (int64_t)(be + 1) * 4608);
+            }
+            if (!__all_sync(0xffffffffu, i_mbar_wait(i_smem_u32(&bars.tfull[t]), (uint32_t)(e / IM_TSTAGES) & 1u, abort_flag))) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float4 *das = reinterpret_cast<const float4 *>(bars.da[be % IM_DA_SLOTS] + 32 * h4);
+            const uint32_t trow = trow0 + (uint32_t)(t * 256);
+            // four rounds of eight columns, the next round's loads in flight while this one's multiply-adds run:
+            //   sumf = fma(f32(ig), d d_x, sumf);  summin = fma(f32(mg), dmin d_x, summin)
+            float ig[2][8], mg[2][8];
+            i_tmem_ld8f(ig[0], trow);
+            i_tmem_ld8f(mg[0], trow + 128);
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+                const int c0 = 8 * r;
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (r < 3) {
+                    i_tmem_ld8f(ig[(r + 1) & 1], trow + (uint32_t)(c0 + 8));
+                    i_tmem_ld8f(mg[(r + 1) & 1], trow + (uint32_t)(128 + c0 + 8));
+                } else {
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) i_mbar_arrive(i_smem_u32(&bars.tempty[t]));
+                }
+                if (any_col) {
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const float4 dq = das[c0 / 4 + h];
+                        const float dxs[4] = {dq.x, dq.y, dq.z, dq.w};
+#pragma unroll
+                        for (int c4 = 0; c4 < 4; c4++) {
+                            const int c = 4 * h + c4;
+                            sumf[c0 + c] = __fmaf_rn(ig[r & 1][c], __fmul_rn(dw, dxs[c4]), sumf[c0 + c]);
+                            summin[c0 + c] = __fmaf_rn(mg[r & 1][c], __fmul_rn(dmw, dxs[c4]), summin[c0 + c]);
+                        }
+                    }
+                }
+            }
+        }
+        const int64_t row = (tile0 + q) * TILE_ROWS + lane;
+        if (row_ok && row < n && !*abort_flag) {
+#pragma unroll
+            for (int c = 0; c < 32; c++) {
+                const int64_t col = col0 + 32 * h4 + c;
+                if (col < m) dst[col * lddst + row] = __fsub_rn(sumf[c], summin[c]);
+            }
+        }
+    } else {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(IM_REGS_CTL));
+        pdl_wait();
+        if (warp == IM_MMA_WARP) {
+            if (lane == 0) {
+                // per step: four K = 16 MMAs for ig, one for mg, N = 128
+                for (int p = 0; p < np; p++) {
+                    const int s = p % IW_STAGES, t = p % IM_TSTAGES;
+                    if (!i_mbar_wait(i_smem_u32(&bars.full[s]), (uint32_t)(p / IW_STAGES) & 1u, abort_flag)) break;
+                    if (!i_mbar_wait(i_smem_u32(&bars.tempty[t]), ((uint32_t)(p / IM_TSTAGES) & 1u) ^ 1u, abort_flag)) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_base = smem + (uint32_t)(s * IW_STAGE_BYTES), am_base = a_base + IW_A_BYTES;
+                    const uint32_t b_base = a_base + IW_AIMG, bm_base = b_base + IW_B_BYTES;
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const uint64_t adesc = i_desc(a_base + 2 * i * 128, 128, 1024), bdesc = i_desc(b_base + 2 * i * 128, 128, 1024);
+                        asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(
+                                         tmem + (uint32_t)(t * 256)),
+                                     "l"(adesc), "l"(bdesc), "r"(IW_IDESC), "r"(i)
+                                     : "memory");
+                    }
+                    const uint64_t amdesc = i_desc(am_base, 128, 256), bmdesc = i_desc(bm_base, 128, 256);
+                    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(
+                                     tmem + (uint32_t)(t * 256 + 128)),
+                                 "l"(amdesc), "l"(bmdesc), "r"(IW_IDESC), "r"(0)
+                                 : "memory");
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(i_smem_u32(&bars.empty[s])) : "memory");
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(i_smem_u32(&bars.tfull[t])) : "memory");
+                }
+            }
+        } else if (warp == IM_LOAD_WARP && lane == 0) {
+            const uint8_t *asrc = aimg + rb * np * (int64_t)IW_AIMG, *bsrc = bimg + cb * np * (int64_t)IW_BIMG;
+            const float *dsrc = daimg + cb * nb * (int64_t)IW_COLS;
+            int issued = -1;
+            for (int p = 0; p < np; p++) {
+                const int s = p % IW_STAGES;
+                if (!i_mbar_wait(i_smem_u32(&bars.empty[s]), ((uint32_t)(p / IW_STAGES) & 1u) ^ 1u, abort_flag)) break;
+                const uint32_t bar = i_smem_u32(&bars.full[s]), stage = smem + (uint32_t)(s * IW_STAGE_BYTES);
+                const bool first = (p & 3) == 0;
+                i_mbar_expect(bar, (uint32_t)(IW_STAGE_BYTES + (first ? IW_DA_BYTES : 0)));
+                i_bulk_load(stage, asrc + (int64_t)p * IW_AIMG, IW_AIMG, bar);
+                i_bulk_load(stage + IW_AIMG, bsrc + (int64_t)p * IW_BIMG, IW_BIMG, bar);
+                // slot b % 4 is rewritten 16 steps later; the stage this step reuses (5 steps old) was released by
+                // MMAs that had waited for the drain of every step of that older super-block
+                if (first) i_bulk_load(i_smem_u32(bars.da[(p >> 2) % IM_DA_SLOTS]), dsrc + (int64_t)(p >> 2) * IW_COLS, IW_DA_BYTES, bar);
+                issued = p;
+            }
+            if (*abort_flag && issued >= 0) i_mbar_wait(i_smem_u32(&bars.full[issued % IW_STAGES]), (uint32_t)(issued / IW_STAGES) & 1u, abort_flag);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == IM_MMA_WARP) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+    if (threadIdx.x == 0 && bars.abort_flag) atomicExch(err, IM_ERR_WAIT);
+}
+
+static int launch_images(bool wide, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s) {
     B200_REQUIRE(k % GROUP_K == 0, "gemm: k = %lld must be a multiple of 256", (long long)k);
     if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
     static bool attr_done[64] = {false};
@@ -410,28 +688,48 @@ int launch_gemm_tcgen05_img(int64_t n, int64_t k, int64_t m, const uint8_t *tile
     B200_REQUIRE(dev >= 0 && dev < 64, "gemm: device index %d out of range", dev);
     if (!attr_done[dev]) {
         B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_img_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_SMEM_BYTES));
+        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_img128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, IW_SMEM_BYTES));
         attr_done[dev] = true;
     }
     int *err = nullptr;
     int rc = device_error_word(&err);
     if (rc != B200_STATUS_SUCCESS) return rc;
     const int nb = (int)(k / GROUP_K);
+    const int cols = wide ? IW_COLS : IM_COLS;
     const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
-    const int64_t gx = (m + IM_COLS - 1) / IM_COLS, gy = (n + IM_ROWS - 1) / IM_ROWS;
+    const int64_t gx = (m + cols - 1) / cols, gy = (n + IM_ROWS - 1) / IM_ROWS;
     B200_REQUIRE(gx <= 65535 && gy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);
     // one block for the images of this mat-mul: weights, activations, activation scales
-    const size_t a_bytes = (size_t)gy * 2 * nb * IM_AIMG, b_bytes = (size_t)gx * 2 * nb * IM_BIMG, d_bytes = (size_t)gx * nb * IM_DA_BYTES;
+    // (per super-block and row or column block: 2 steps of 36 / 20 KB, or 4 steps of 20 / 20 KB)
+    const size_t a_bytes = (size_t)gy * nb * (wide ? 4 * IW_AIMG : 2 * IM_AIMG), b_bytes = (size_t)gx * nb * (wide ? 4 * IW_BIMG : 2 * IM_BIMG);
+    const size_t d_bytes = (size_t)gx * nb * (wide ? IW_DA_BYTES : IM_DA_BYTES);
     void *block = nullptr;
     rc = scratch_get_images(a_bytes + b_bytes + d_bytes, &block);
     if (rc != B200_STATUS_SUCCESS) return rc;
     uint8_t *aimg = (uint8_t *)block, *bimg = aimg + a_bytes;
     float *daimg = (float *)(bimg + b_bytes);
-    rc = launch_pdl(expand_q4_K_weights_kernel, dim3((unsigned)nb, (unsigned)gy), dim3(IM_EXPAND_THREADS), (size_t)0, s, tiles, aimg, tiles_n, nb);
+    const dim3 ga((unsigned)nb, (unsigned)gy), gb((unsigned)nb, (unsigned)gx), gg((unsigned)gx, (unsigned)gy);
+    if (wide) {
+        rc = launch_pdl(expand_q4_K_weights_pair_kernel, ga, dim3(IM_EXPAND_THREADS), (size_t)0, s, tiles, aimg, tiles_n, nb);
+        if (rc != B200_STATUS_SUCCESS) return rc;
+        rc = launch_pdl(expand_q8_K_acts_pair_kernel, gb, dim3(IM_EXPAND_THREADS), (size_t)0, s, acts, bimg, daimg, m, nb);
+        if (rc != B200_STATUS_SUCCESS) return rc;
+        return launch_pdl(gemm_q4_K_tcgen05_img128_kernel, gg, dim3(IM_THREADS), (size_t)IW_SMEM_BYTES, s, tiles, (const uint8_t *)aimg,
+                          (const uint8_t *)bimg, (const float *)daimg, dst, lddst, n, nb, m, err);
+    }
+    rc = launch_pdl(expand_q4_K_weights_kernel, ga, dim3(IM_EXPAND_THREADS), (size_t)0, s, tiles, aimg, tiles_n, nb);
     if (rc != B200_STATUS_SUCCESS) return rc;
-    rc = launch_pdl(expand_q8_K_acts_kernel, dim3((unsigned)nb, (unsigned)gx), dim3(IM_EXPAND_THREADS), (size_t)0, s, acts, bimg, daimg, m, nb);
+    rc = launch_pdl(expand_q8_K_acts_kernel, gb, dim3(IM_EXPAND_THREADS), (size_t)0, s, acts, bimg, daimg, m, nb);
     if (rc != B200_STATUS_SUCCESS) return rc;
-    return launch_pdl(gemm_q4_K_tcgen05_img_kernel, dim3((unsigned)gx, (unsigned)gy), dim3(IM_THREADS), (size_t)IM_SMEM_BYTES, s, tiles,
-                      (const uint8_t *)aimg, (const uint8_t *)bimg, (const float *)daimg, dst, lddst, n, nb, m, err);
+    return launch_pdl(gemm_q4_K_tcgen05_img_kernel, gg, dim3(IM_THREADS), (size_t)IM_SMEM_BYTES, s, tiles, (const uint8_t *)aimg, (const uint8_t *)bimg,
+                      (const float *)daimg, dst, lddst, n, nb, m, err);
+}
+
+int launch_gemm_tcgen05_img(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s) {
+    return launch_images(false, n, k, m, tiles, acts, dst, lddst, s);
+}
+int launch_gemm_tcgen05_img128(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s) {
+    return launch_images(true, n, k, m, tiles, acts, dst, lddst, s);
 }
 
 }  // namespace b200

@@ -54,12 +54,13 @@ int launch_rms_norm(const float *x, int64_t x_stride, float *y, int64_t y_stride
                       (int)ne0, eps);
 }
 
-// The same, followed by the Q8_K quantization of the result for the mat-muls that read it: grid
+// Few rows (single-token and small-batch steps, where latency counts and there are not enough rows to fill the GPU
+// with one CTA each): the same, followed by the Q8_K quantization of the result for the mat-muls that read it: grid
 // (ne0 / 256, rows), every CTA recomputes the row's sum (the row is a few KB and sits in L2) in the same
 // order, then owns one 256-element block: norm, weighted norm, and that block's quants, scale and
 // 16-element sums (act_quant.cuh).  Rows below m4 take the 4x8 value rule, the others the plain one.
 __global__ void __launch_bounds__(256)
-rms_norm_q8_kernel(const float *__restrict__ x, int64_t x_stride, float *y, int64_t y_stride, const float *__restrict__ w,
+rms_norm_q8_few_kernel(const float *__restrict__ x, int64_t x_stride, float *y, int64_t y_stride, const float *__restrict__ w,
                    float *y_mul, int64_t y_mul_stride, int ne0, float eps, ActBuf act, int64_t m4) {
     pdl_trigger();
     pdl_wait();
@@ -91,13 +92,86 @@ rms_norm_q8_kernel(const float *__restrict__ x, int64_t x_stride, float *y, int6
     else q8_K_block_store<false>(v, act, row, blockIdx.x);
 }
 
+// eight consecutive floats, as two 16-byte accesses when every operand of the launch allows it (vec), else one by one
+__device__ __forceinline__ void load8(const float *p, bool vec, float (&v)[8]) {
+    if (vec) {
+        const float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[j] = p[j];
+    }
+}
+__device__ __forceinline__ void store8(float *p, bool vec, const float (&v)[8]) {
+    if (vec) {
+        *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4 *>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++) p[j] = v[j];
+    }
+}
+
+// Many rows (prompt batches): the same with one CTA per row:
+// the row's sum in the same order as above, then warp w takes the 256-element blocks w, w + 8, ..: lane l
+// holds elements 8 l .. 8 l + 7, writes norm and weighted norm with 16-byte stores and the block's quants,
+// scale and 16-element sums (act_quant.cuh).  Rows below m4 take the 4x8 value rule, the others the plain one.
+__global__ void __launch_bounds__(256)
+rms_norm_q8_kernel(const float *__restrict__ x, int64_t x_stride, float *y, int64_t y_stride, const float *__restrict__ w,
+                   float *y_mul, int64_t y_mul_stride, int ne0, float eps, ActBuf act, int64_t m4, bool vec) {
+    pdl_trigger();
+    pdl_wait();
+    const int64_t row = blockIdx.x;
+    const float *xr = x + row * x_stride;
+    double sum = 0.0;
+    for (int i = threadIdx.x; i < ne0; i += 256) {
+        const float v = xr[i];
+        sum += (double)__fmul_rn(v, v);
+    }
+    __shared__ double part[8];
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    double total = 0.0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) total += part[i];
+    const float mean = __double2float_rn(total / (double)ne0);
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int blk = warp; blk < ne0 / 256; blk += 8) {
+        const int i = blk * 256 + 8 * lane;
+        float v[8];
+        load8(xr + i, vec, v);
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[j] = __fmul_rn(v[j], scale);
+        if (y) store8(y + row * y_stride + i, vec, v);
+        if (w) {
+            float ws[8];
+            load8(w + i, vec, ws);
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = __fmul_rn(v[j], ws[j]);
+            store8(y_mul + row * y_mul_stride + i, vec, v);
+        }
+        if (row < m4) q8_K_block_store_warp<true>(v, act, row, blk);
+        else q8_K_block_store_warp<false>(v, act, row, blk);
+    }
+}
+
+// up to this many rows the one-CTA-per-block kernels are used (measured: a single-token step loses 4 % with the row kernels)
+constexpr int64_t FEW_ROWS = 32;
+static bool aligned16(const void *p, int64_t stride_elems) { return ((uintptr_t)p & 15) == 0 && stride_elems % 4 == 0; }
+
 int launch_rms_norm_q8(const float *x, int64_t x_stride, float *y, int64_t y_stride, const float *w, float *y_mul,
                        int64_t y_mul_stride, int64_t ne0, int64_t nrows, float eps, ActBuf act, int64_t m4, cudaStream_t s) {
     B200_REQUIRE(ne0 > 0 && ne0 % 256 == 0 && ne0 < (1 << 30), "rms_norm + q8_K: row length %lld is not a multiple of 256", (long long)ne0);
-    B200_REQUIRE(nrows <= 65535, "rms_norm + q8_K: %lld rows exceed one launch", (long long)nrows);
+    B200_REQUIRE(nrows < 0x7fffffffLL, "rms_norm + q8_K: too many rows");
+    const bool vec = aligned16(x, x_stride) && (!y || aligned16(y, y_stride)) && (!w || (aligned16(w, 4) && aligned16(y_mul, y_mul_stride)));
     if (nrows == 0) return B200_STATUS_SUCCESS;
-    return launch_pdl(rms_norm_q8_kernel, dim3((unsigned)(ne0 / 256), (unsigned)nrows), dim3(256), 0, s, x, x_stride, y, y_stride, w,
-                      y_mul, y_mul_stride, (int)ne0, eps, act, m4);
+    if (nrows <= FEW_ROWS)
+        return launch_pdl(rms_norm_q8_few_kernel, dim3((unsigned)(ne0 / 256), (unsigned)nrows), dim3(256), 0, s, x, x_stride, y, y_stride, w,
+                          y_mul, y_mul_stride, (int)ne0, eps, act, m4);
+    return launch_pdl(rms_norm_q8_kernel, dim3((unsigned)nrows), dim3(256), 0, s, x, x_stride, y, y_stride, w, y_mul, y_mul_stride,
+                      (int)ne0, eps, act, m4, vec);
 }
 
 // ---- ADD / MUL -------------------------------------------------------------------------------------
@@ -166,10 +240,10 @@ int launch_silu(const float *x, int64_t x_stride, const float *g, int64_t g_stri
                       (int)ne0, wide_end, total);
 }
 
-// The same, followed by the Q8_K quantization of the result (the gated product when g is given): grid
+// Few rows: the same, followed by the Q8_K quantization of the result (the gated product when g is given): grid
 // (ne0 / 256, rows), one 256-element block per CTA.
 __global__ void __launch_bounds__(256)
-silu_q8_kernel(const float *__restrict__ x, int64_t x_stride, const float *__restrict__ g, int64_t g_stride, float *y,
+silu_q8_few_kernel(const float *__restrict__ x, int64_t x_stride, const float *__restrict__ g, int64_t g_stride, float *y,
                int64_t y_stride, float *y_mul, int64_t y_mul_stride, int wide_end, ActBuf act, int64_t m4) {
     pdl_trigger();
     pdl_wait();
@@ -188,14 +262,51 @@ silu_q8_kernel(const float *__restrict__ x, int64_t x_stride, const float *__res
     else q8_K_block_store<false>(out, act, r, blockIdx.x);
 }
 
+// Many rows: one warp per
+// 256-element block, lane l holding elements 8 l .. 8 l + 7 (16-byte loads and stores, no CTA barrier).
+__global__ void __launch_bounds__(256)
+silu_q8_kernel(const float *__restrict__ x, int64_t x_stride, const float *__restrict__ g, int64_t g_stride, float *y,
+               int64_t y_stride, float *y_mul, int64_t y_mul_stride, int wide_end, int nblk, int64_t nwork, ActBuf act, int64_t m4, bool vec) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int64_t wg = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (wg >= nwork) return;
+    const int64_t r = wg / nblk;
+    const int blk = (int)(wg - r * nblk);
+    const int c = blk * 256 + 8 * lane;
+    float xs[8], v[8];
+    load8(x + r * x_stride + c, vec, xs);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const float e = c + j < wide_end ? v_expf(__fsub_rn(0.0f, xs[j])) : libm_expf(-xs[j]);
+        v[j] = __fdiv_rn(xs[j], __fadd_rn(1.0f, e));
+    }
+    if (y) store8(y + r * y_stride + c, vec, v);
+    if (g) {
+        float gs[8];
+        load8(g + r * g_stride + c, vec, gs);
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[j] = __fmul_rn(v[j], gs[j]);
+        store8(y_mul + r * y_mul_stride + c, vec, v);
+    }
+    if (r < m4) q8_K_block_store_warp<true>(v, act, r, blk);
+    else q8_K_block_store_warp<false>(v, act, r, blk);
+}
+
 int launch_silu_q8(const float *x, int64_t x_stride, const float *g, int64_t g_stride, float *y, int64_t y_stride, float *y_mul,
                    int64_t y_mul_stride, int64_t ne0, int64_t nrows, int wide, ActBuf act, int64_t m4, cudaStream_t s) {
     B200_REQUIRE(ne0 > 0 && ne0 % 256 == 0 && ne0 < (1 << 30), "silu + q8_K: row length %lld is not a multiple of 256", (long long)ne0);
-    B200_REQUIRE(nrows <= 65535, "silu + q8_K: %lld rows exceed one launch", (long long)nrows);
+    const bool vec = aligned16(x, x_stride) && (!y || aligned16(y, y_stride)) && (!g || (aligned16(g, g_stride) && aligned16(y_mul, y_mul_stride)));
     if (nrows == 0) return B200_STATUS_SUCCESS;
+    const int64_t nblk = ne0 / 256, nwork = nblk * nrows, blocks = (nwork + 7) / 8;
+    B200_REQUIRE(blocks < 0x7fffffffLL, "silu + q8_K: tensor too large for one launch");
     const int wide_end = wide ? (int)(ne0 & ~(int64_t)15) : 0;
-    return launch_pdl(silu_q8_kernel, dim3((unsigned)(ne0 / 256), (unsigned)nrows), dim3(256), 0, s, x, x_stride, g, g_stride, y, y_stride,
-                      y_mul, y_mul_stride, wide_end, act, m4);
+    if (nrows <= FEW_ROWS)
+        return launch_pdl(silu_q8_few_kernel, dim3((unsigned)(ne0 / 256), (unsigned)nrows), dim3(256), 0, s, x, x_stride, g, g_stride, y, y_stride,
+                          y_mul, y_mul_stride, wide_end, act, m4);
+    return launch_pdl(silu_q8_kernel, dim3((unsigned)blocks), dim3(256), 0, s, x, x_stride, g, g_stride, y, y_stride, y_mul, y_mul_stride,
+                      wide_end, (int)nblk, nwork, act, m4, vec);
 }
 
 // ---- ROPE --------------------------------------------------------------------------------------------

@@ -1,8 +1,8 @@
 """The tcgen05 prompt mat-mul (Q4_K, 32 activation rows and up) against the CPU oracle and against the
 decode-shaped kernels: same chains, so every output has to agree bit for bit.  The whole file runs with the
 library choosing between the integer and the two-pass kernel by size (the default) and, in child processes with
-B200_GEMM_TCGEN05_F16=0 .. 3, on each kernel alone: the integer one, the f16-operand ones with 32 and 64 activation
-rows per CTA that convert their own operands, and the two-pass one."""
+B200_GEMM_TCGEN05_F16=0 .. 4, on each kernel alone: the integer one, the f16-operand ones with 32 and 64 activation
+rows per CTA that convert their own operands, and the two-pass ones (64 and 128 activation rows per CTA)."""
 import os
 import subprocess
 import sys
@@ -87,10 +87,10 @@ def test_largest_integers_stay_exact(dev, signs):
     assert bits_equal(got, want), f"max |d| = {np.abs(got - want).max()}"
 
 
-@pytest.mark.parametrize("choice", ["0", "1", "2", "3"])
+@pytest.mark.parametrize("choice", ["0", "1", "2", "3", "4"])
 def test_f16_operand_kernels_pass_the_same_cases(choice):
     """the library reads B200_GEMM_TCGEN05_F16 once per process: run this file's other tests in a child with it set"""
-    if os.environ.get("B200_GEMM_TCGEN05_F16") in ("0", "1", "2", "3"):
+    if os.environ.get("B200_GEMM_TCGEN05_F16") in ("0", "1", "2", "3", "4"):
         pytest.skip("already the child")
     env = dict(os.environ, B200_GEMM_TCGEN05_F16=choice)
     r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-x", "-q", "-m", "gpu", "-p", "no:cacheprovider"], env=env,

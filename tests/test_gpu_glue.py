@@ -217,8 +217,9 @@ def q8_K_parts(x, m4):
     return qs, d, bs
 
 
-@pytest.mark.parametrize("rows,kind", [(1, 2), (3, 2), (8, 3), (7, 4), (16, 4)])
+@pytest.mark.parametrize("rows,kind", [(1, 2), (3, 2), (8, 3), (7, 4), (16, 4), (37, 2), (64, 3), (45, 4)])
 def test_rms_norm_and_silu_leave_q8_K_activations(g, rows, kind):
+    """up to 32 rows: one CTA per 256-element block; above: one CTA per row (norm), one warp per block (silu)"""
     m = b200.load()
     rng = np.random.default_rng(rows * 10 + kind)
     m4 = 0 if kind == 2 else rows if kind == 3 else rows - rows % 4
