@@ -45,6 +45,37 @@ __global__ void __launch_bounds__(256) quantize_q8_K_kernel(const float *__restr
     q8_K_block_store<A3>(x[row * ldx + blk * 256 + threadIdx.x], out, row, blk);
 }
 
+// The same for prompt batches (more than 32 rows): one warp per block, lane l holding elements 8 l .. 8 l + 7, no
+// CTA barrier (q8_K_block_store_warp); 16-byte loads when the rows allow it.
+template <bool A3>
+__global__ void __launch_bounds__(256) quantize_q8_K_rows_kernel(const float *__restrict__ x, int64_t ldx, ActBuf out, int nblk, int64_t nwork, bool vec) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int64_t wg = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (wg >= nwork) return;
+    const int64_t row = wg / nblk, blk = wg - row * nblk;
+    const float *p = x + row * ldx + blk * 256 + 8 * lane;
+    float v[8];
+    if (vec) {
+        const float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[j] = p[j];
+    }
+    q8_K_block_store_warp<A3>(v, out, row, blk);
+}
+
+template <bool A3>
+static int launch_q8_K(int64_t m, int64_t k, const float *x, int64_t ldx, ActBuf out, cudaStream_t s) {
+    if (m <= 32) return launch_pdl(quantize_q8_K_kernel<A3>, dim3((unsigned)(k / 256), (unsigned)m), dim3(256), 0, s, x, ldx, out);
+    const int64_t nblk = k / 256, nwork = nblk * m, blocks = (nwork + 7) / 8;
+    B200_REQUIRE(blocks < 0x7fffffffLL, "quantize q8_K: tensor too large for one launch");
+    const bool vec = ((uintptr_t)x & 15) == 0 && ldx % 4 == 0;
+    return launch_pdl(quantize_q8_K_rows_kernel<A3>, dim3((unsigned)blocks), dim3(256), 0, s, x, ldx, out, (int)nblk, nwork, vec);
+}
+
 // A1: one warp per 32-element block, 8 blocks per CTA.
 __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float *__restrict__ x, int64_t ldx, ActBuf out) {
     pdl_trigger();
@@ -76,15 +107,13 @@ int launch_quantize_acts(int kind, int64_t m, int64_t k, const float *x, int64_t
         return launch_pdl(quantize_q8_0_kernel, grid, dim3(256), 0, s, x, ldx, out);
     } else if (kind == B200_ACT_Q8_K || kind == B200_ACT_Q8_K_4X8) {
         B200_REQUIRE(k > 0 && k % 256 == 0, "quantize q8_K: k = %lld must be a positive multiple of 256", (long long)k);
-        dim3 grid((unsigned)(k / 256), (unsigned)m);
-        if (kind == B200_ACT_Q8_K) return launch_pdl(quantize_q8_K_kernel<false>, grid, dim3(256), 0, s, x, ldx, out);
-        return launch_pdl(quantize_q8_K_kernel<true>, grid, dim3(256), 0, s, x, ldx, out);
+        if (kind == B200_ACT_Q8_K) return launch_q8_K<false>(m, k, x, ldx, out, s);
+        return launch_q8_K<true>(m, k, x, ldx, out, s);
     } else if (kind == B200_ACT_Q8_K_MIXED) {
         B200_REQUIRE(k > 0 && k % 256 == 0, "quantize q8_K: k = %lld must be a positive multiple of 256", (long long)k);
         const int64_t m4 = m - m % 4;
         if (m4 > 0) {
-            dim3 grid((unsigned)(k / 256), (unsigned)m4);
-            int rc = launch_pdl(quantize_q8_K_kernel<true>, grid, dim3(256), 0, s, x, ldx, out);
+            int rc = launch_q8_K<true>(m4, k, x, ldx, out, s);
             if (rc != B200_STATUS_SUCCESS) return rc;
         }
         if (m > m4) {
@@ -92,8 +121,7 @@ int launch_quantize_acts(int kind, int64_t m, int64_t k, const float *x, int64_t
             tail.qs += m4 * k;
             tail.d += m4 * (k / 256);
             tail.bsums += m4 * (k / 16);
-            dim3 grid((unsigned)(k / 256), (unsigned)(m - m4));
-            int rc = launch_pdl(quantize_q8_K_kernel<false>, grid, dim3(256), 0, s, x + m4 * ldx, ldx, tail);
+            int rc = launch_q8_K<false>(m - m4, k, x + m4 * ldx, ldx, tail, s);
             if (rc != B200_STATUS_SUCCESS) return rc;
         }
     } else {

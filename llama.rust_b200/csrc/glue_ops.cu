@@ -191,12 +191,42 @@ binary_kernel(const float *__restrict__ a, int64_t a_stride, const float *__rest
     y[r * y_stride + c] = OP == 0 ? __fadd_rn(av, bv) : __fmul_rn(av, bv);
 }
 
+// four elements per thread with 16-byte accesses: rows of a multiple of 4 floats, 16-byte aligned, b not broadcast along a row
+template <int OP>
+__global__ void __launch_bounds__(256)
+binary_vec_kernel(const float *__restrict__ a, int64_t a_stride, const float *__restrict__ b, int64_t b_stride, int64_t b_rows, float *y,
+                  int64_t y_stride, int ne0_4, int64_t total4) {
+    pdl_trigger();
+    pdl_wait();
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= total4) return;
+    const int64_t r = i / ne0_4;
+    const int c = 4 * (int)(i - r * ne0_4);
+    const float4 av = *reinterpret_cast<const float4 *>(a + r * a_stride + c), bv = *reinterpret_cast<const float4 *>(b + (r % b_rows) * b_stride + c);
+    float4 o;
+    o.x = OP == 0 ? __fadd_rn(av.x, bv.x) : __fmul_rn(av.x, bv.x);
+    o.y = OP == 0 ? __fadd_rn(av.y, bv.y) : __fmul_rn(av.y, bv.y);
+    o.z = OP == 0 ? __fadd_rn(av.z, bv.z) : __fmul_rn(av.z, bv.z);
+    o.w = OP == 0 ? __fadd_rn(av.w, bv.w) : __fmul_rn(av.w, bv.w);
+    *reinterpret_cast<float4 *>(y + r * y_stride + c) = o;
+}
+
 int launch_binary(int op, const float *a, int64_t a_stride, const float *b, int64_t b_stride, int64_t b_ne0, int64_t b_rows,
                   float *y, int64_t y_stride, int64_t ne0, int64_t nrows, cudaStream_t s) {
     B200_REQUIRE(op == 0 || op == 1, "binary: op %d is neither add (0) nor mul (1)", op);
     B200_REQUIRE(ne0 > 0 && ne0 < (1 << 30) && b_ne0 > 0 && ne0 % b_ne0 == 0 && b_rows > 0, "binary: operand shapes do not broadcast");
     const int64_t total = ne0 * nrows;
     if (total == 0) return B200_STATUS_SUCCESS;
+    const auto al = [](const void *p, int64_t stride) { return ((uintptr_t)p & 15) == 0 && (stride & 3) == 0; };
+    if (nrows > 1 && b_ne0 == ne0 && ne0 % 4 == 0 && al(a, a_stride) && al(b, b_stride) && al(y, y_stride)) {
+        const int64_t total4 = total / 4, blocks4 = (total4 + 255) / 256;
+        B200_REQUIRE(blocks4 < 0x7fffffffLL, "binary: tensor too large for one launch");
+        if (op == 0)
+            return launch_pdl(binary_vec_kernel<0>, dim3((unsigned)blocks4), dim3(256), 0, s, a, a_stride, b, b_stride, b_rows, y, y_stride,
+                              (int)(ne0 / 4), total4);
+        return launch_pdl(binary_vec_kernel<1>, dim3((unsigned)blocks4), dim3(256), 0, s, a, a_stride, b, b_stride, b_rows, y, y_stride,
+                          (int)(ne0 / 4), total4);
+    }
     const int64_t blocks = (total + 255) / 256;
     B200_REQUIRE(blocks < 0x7fffffffLL, "binary: tensor too large for one launch");
     if (op == 0)

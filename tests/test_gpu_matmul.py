@@ -58,7 +58,7 @@ def test_dequantize_golden_blocks(dev, golden):
 
 
 @pytest.mark.parametrize("kind", ["q8_0", "q8_K", "q8_K_4x8"])
-@pytest.mark.parametrize("shape", [(1, 4096), (4, 256), (8, 1024), (12, 14336)], ids=str)
+@pytest.mark.parametrize("shape", [(1, 4096), (4, 256), (8, 1024), (12, 14336), (40, 1024), (68, 512)], ids=str)  # above 32 rows: the warp-per-block kernels
 def test_activation_blocks_bit_exact(dev, kind, shape):
     m, k = shape
     x = synth.activations(m, k, seed=11)
