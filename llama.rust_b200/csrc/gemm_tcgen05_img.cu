@@ -110,6 +110,68 @@ __device__ __forceinline__ uint32_t i_signed(uint32_t u, int shift) {
 }
 __device__ __forceinline__ void i_stg128(uint8_t *p, uint32_t x, uint32_t y, uint32_t z, uint32_t w) { *reinterpret_cast<uint4 *>(p) = make_uint4(x, y, z, w); }
 
+// All MMAs of one 64-column step in one statement, so that the issuing thread spends three instructions per MMA
+// (two descriptor adds and the MMA) instead of rebuilding descriptors and predicates each time.  Descriptor start
+// addresses count 16-byte units: K step i is + 16 (two 128-byte core-matrix columns), pair gl + 64; Bm of pair gl
+// + 128 (2048 bytes).  d0 = the tensor-memory stage: ig of pair gl at + 64 gl, mg at + 128 + 64 gl.
+__device__ __forceinline__ void i_issue_step64(uint32_t d0, uint64_t adesc0, uint64_t bdesc0, uint64_t amdesc, uint64_t bmdesc0, uint32_t idesc) {
+    asm volatile(
+        "{\n"
+        ".reg .pred pn, py;\n"
+        ".reg .b64 a, b;\n"
+        ".reg .b32 d;\n"
+        "setp.ne.b32 pn, 0, 0;\n"
+        "setp.eq.b32 py, 0, 0;\n"
+        // pair 0
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %5, pn;\n"
+        "add.u64 a, %1, 16;  add.u64 b, %2, 16;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %5, py;\n"
+        "add.u64 a, %1, 32;  add.u64 b, %2, 32;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %5, py;\n"
+        "add.u64 a, %1, 48;  add.u64 b, %2, 48;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %5, py;\n"
+        "add.u32 d, %0, 128;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [d], %3, %4, %5, pn;\n"
+        // pair 1
+        "add.u32 d, %0, 64;\n"
+        "add.u64 a, %1, 64;  add.u64 b, %2, 64;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [d], a, b, %5, pn;\n"
+        "add.u64 a, %1, 80;  add.u64 b, %2, 80;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [d], a, b, %5, py;\n"
+        "add.u64 a, %1, 96;  add.u64 b, %2, 96;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [d], a, b, %5, py;\n"
+        "add.u64 a, %1, 112; add.u64 b, %2, 112;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [d], a, b, %5, py;\n"
+        "add.u32 d, %0, 192;\n"
+        "add.u64 b, %4, 128;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [d], %3, b, %5, pn;\n"
+        "}\n" ::"r"(d0),
+        "l"(adesc0), "l"(bdesc0), "l"(amdesc), "l"(bmdesc0), "r"(idesc)
+        : "memory");
+}
+// The five MMAs of one 128-column step (one pair): ig at d0, mg at d0 + 128.
+__device__ __forceinline__ void i_issue_step128(uint32_t d0, uint64_t adesc0, uint64_t bdesc0, uint64_t amdesc, uint64_t bmdesc, uint32_t idesc) {
+    asm volatile(
+        "{\n"
+        ".reg .pred pn, py;\n"
+        ".reg .b64 a, b;\n"
+        ".reg .b32 d;\n"
+        "setp.ne.b32 pn, 0, 0;\n"
+        "setp.eq.b32 py, 0, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %5, pn;\n"
+        "add.u64 a, %1, 16;  add.u64 b, %2, 16;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %5, py;\n"
+        "add.u64 a, %1, 32;  add.u64 b, %2, 32;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %5, py;\n"
+        "add.u64 a, %1, 48;  add.u64 b, %2, 48;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %5, py;\n"
+        "add.u32 d, %0, 128;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [d], %3, %4, %5, pn;\n"
+        "}\n" ::"r"(d0),
+        "l"(adesc0), "l"(bdesc0), "l"(amdesc), "l"(bmdesc), "r"(idesc)
+        : "memory");
+}
+
 struct alignas(16) ImBars {
     uint64_t full[IM_STAGES], empty[IM_STAGES], tfull[IM_TSTAGES], tempty[IM_TSTAGES];
     float da[IM_DA_SLOTS][IM_COLS];
@@ -346,24 +408,9 @@ gemm_q4_K_tcgen05_img_kernel(const uint8_t *__restrict__ tiles, const uint8_t *_
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t a_base = smem + (uint32_t)(s * IM_STAGE_BYTES), am_base = a_base + IM_A_BYTES;
                 const uint32_t b_base = a_base + IM_AIMG, bm_base = b_base + IM_B_BYTES;
-#pragma unroll
-                for (int gl = 0; gl < 2; gl++) {
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const uint64_t adesc = i_desc(a_base + (8 * gl + 2 * i) * 128, 128, 2048);
-                        const uint64_t bdesc = i_desc(b_base + (8 * gl + 2 * i) * 128, 128, 2048);
-                        asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(
-                                         tmem + (uint32_t)(t * 256 + gl * IM_COLS)),
-                                     "l"(adesc), "l"(bdesc), "r"(IM_IDESC), "r"(i)
-                                     : "memory");
-                    }
-                    // Am holds the mins of all four pairs, Bm is zero outside the slots of global pair 2 hs + gl
-                    const uint64_t amdesc = i_desc(am_base, 128, 256), bmdesc = i_desc(bm_base + gl * 2048, 128, 256);
-                    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(
-                                     tmem + (uint32_t)(t * 256 + 128 + gl * IM_COLS)),
-                                 "l"(amdesc), "l"(bmdesc), "r"(IM_IDESC), "r"(0)
-                                 : "memory");
-                }
+                // Am holds the mins of all four pairs, Bm is zero outside the slots of global pair 2 hs + gl
+                i_issue_step64(tmem + (uint32_t)(t * 256), i_desc(a_base, 128, 2048), i_desc(b_base, 128, 2048), i_desc(am_base, 128, 256),
+                               i_desc(bm_base, 128, 256), IM_IDESC);
                 // both arrive when the MMAs above have completed: images consumed, accumulators ready
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(i_smem_u32(&bars.empty[s])) : "memory");
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(i_smem_u32(&bars.tfull[t])) : "memory");
@@ -633,19 +680,8 @@ gemm_q4_K_tcgen05_img128_kernel(const uint8_t *__restrict__ tiles, const uint8_t
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t a_base = smem + (uint32_t)(s * IW_STAGE_BYTES), am_base = a_base + IW_A_BYTES;
                     const uint32_t b_base = a_base + IW_AIMG, bm_base = b_base + IW_B_BYTES;
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const uint64_t adesc = i_desc(a_base + 2 * i * 128, 128, 1024), bdesc = i_desc(b_base + 2 * i * 128, 128, 1024);
-                        asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(
-                                         tmem + (uint32_t)(t * 256)),
-                                     "l"(adesc), "l"(bdesc), "r"(IW_IDESC), "r"(i)
-                                     : "memory");
-                    }
-                    const uint64_t amdesc = i_desc(am_base, 128, 256), bmdesc = i_desc(bm_base, 128, 256);
-                    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(
-                                     tmem + (uint32_t)(t * 256 + 128)),
-                                 "l"(amdesc), "l"(bmdesc), "r"(IW_IDESC), "r"(0)
-                                 : "memory");
+                    i_issue_step128(tmem + (uint32_t)(t * 256), i_desc(a_base, 128, 1024), i_desc(b_base, 128, 1024), i_desc(am_base, 128, 256),
+                                    i_desc(bm_base, 128, 256), IW_IDESC);
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(i_smem_u32(&bars.empty[s])) : "memory");
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(i_smem_u32(&bars.tfull[t])) : "memory");
                 }
