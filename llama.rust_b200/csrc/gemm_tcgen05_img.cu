@@ -65,7 +65,7 @@ __device__ __forceinline__ void i_mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void i_mbar_expect(uint32_t bar, uint32_t bytes) {
     asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(bar), "r"(bytes) : "memory");
 }
-// global -> shared bulk copy (no multicast); both addresses 16-byte aligned, size a multiple of 16
+// global -> shared bulk copy, one destination CTA; both addresses 16-byte aligned, size a multiple of 16
 __device__ __forceinline__ void i_bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
