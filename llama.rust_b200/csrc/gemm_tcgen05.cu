@@ -675,7 +675,7 @@ static int gemm_tcgen05_f16_choice() {
 }
 
 // One CTA per SM in every kernel.  Measured at K = 4096: a wave of CTAs takes 37 us in the integer kernel (128 x 32
-// outputs per CTA) and in the 64-column two-pass kernel (128 x 64), 1.85 times that in the 128-column one
+// outputs per CTA) and in the 64-column two-pass kernel (128 x 64), 1.6 times that in the 128-column one
 // (128 x 128); expanding the operands costs 8.7 us per 4096 x 4096 weights and 5.2 us per 512 x 4096 activations
 // (0.235 and 0.14 of a wave).  Returns 0 = integer kernel, 3 = two-pass with 64 columns, 4 = with 128.
 static int gemm_chain_pick(int64_t n, int64_t m) {
@@ -686,7 +686,7 @@ static int gemm_chain_pick(int64_t n, int64_t m) {
     const int64_t gy = (n + 127) / 128, g32 = (m + 31) / 32, g64 = (m + 63) / 64, g128 = (m + 127) / 128;
     const auto waves = [&](int64_t ctas) { return (double)((ctas + sms[dev] - 1) / sms[dev]); };
     const double expand = 0.235 * (double)gy / 32.0 + 0.14 * (double)g64 / 8.0 + 0.05;
-    const double t_int = waves(gy * g32), t_64 = waves(gy * g64) + expand, t_128 = 1.85 * waves(gy * g128) + expand;
+    const double t_int = waves(gy * g32), t_64 = waves(gy * g64) + expand, t_128 = 1.6 * waves(gy * g128) + expand;
     if (t_int <= t_64 && t_int <= t_128) return 0;
     return t_128 < t_64 ? 4 : 3;
 }
