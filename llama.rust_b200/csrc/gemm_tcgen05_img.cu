@@ -381,7 +381,7 @@ gemm_q4_K_tcgen05_img_kernel(const uint8_t *__restrict__ tiles, const uint8_t *_
                     }
                 }
                 if (r == 0) {
-                    // round 3 into round 0's registers, now consumed
+                    // the fourth group of loads goes into the first group's registers, now consumed
                     i_tmem_ld8f(ig[0], trow + (uint32_t)(IM_COLS + 8));
                     i_tmem_ld8f(mg[0], trow + (uint32_t)(128 + IM_COLS + 8));
                 }
