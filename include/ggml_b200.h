@@ -70,6 +70,11 @@ int b200_synchronize(void *stream);
  * device instead of hanging it.  Reads and clears that code for the current device (0 = none).
  * (Failure reporting of the kind ggml_backend_i.synchronize surfaces: crates/ggml/src/backend.rs:761-765.) */
 int b200_kernel_error(int *code);
+/* Which kernel a Q4_K prompt mat-mul (8x8 gemm route, n weight rows, m >= 32 activation rows) takes on a GPU with
+ * sm_count SMs: 0 = integer tcgen05 kernel, 3 / 4 = the two-pass f16-image kernels with 64 / 128 activation rows
+ * per CTA.  Pure host arithmetic (CTA waves times measured time per wave, plus the expansion); no CUDA call.
+ * (The reference's own choice among its gemm kernels by shape: crates/ggml/src/compute.rs:1420-1841.) */
+int b200_prompt_kernel_choice(int64_t n, int64_t m, int sm_count);
 
 /* ---- device memory (cudaMalloc-backed; buffers of the backend use the same) */
 int b200_malloc(void **dev_ptr, size_t bytes);

@@ -158,6 +158,8 @@ int b200_kernel_error(int *code) {
     return gemv_stream_error(code);
 }
 
+int b200_prompt_kernel_choice(int64_t n, int64_t m, int sm_count) { return gemm_chain_pick_for(n, m, sm_count); }
+
 int b200_malloc(void **dev_ptr, size_t bytes) {
     B200_REQUIRE(dev_ptr != nullptr, "malloc: null out pointer");
     *dev_ptr = nullptr;

@@ -136,6 +136,8 @@ int launch_gemm_mma(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *ti
                     cudaStream_t s);
 int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
                         cudaStream_t s);
+// which Q4_K gemm-chain prompt kernel the time model prefers on a GPU of sm_count SMs: 0 integer, 3 / 4 two-pass with 64 / 128 columns
+int gemm_chain_pick_for(int64_t n, int64_t m, int sm_count);
 // Q4_K gemm chain with the scales folded into f16 operands, 128 x 64 per CTA (gemm_tcgen05_f16.cu)
 int launch_gemm_tcgen05_f16x64(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s);
 // the same chain in two passes: operands expanded to f16 images once, then a mat-mul that only copies, multiplies and drains (gemm_tcgen05_img.cu)

@@ -678,17 +678,21 @@ static int gemm_tcgen05_f16_choice() {
 // outputs per CTA) and in the 64-column two-pass kernel (128 x 64), 1.6 times that in the 128-column one
 // (128 x 128); expanding the operands costs 8.7 us per 4096 x 4096 weights and 5.2 us per 512 x 4096 activations
 // (0.235 and 0.14 of a wave).  Returns 0 = integer kernel, 3 = two-pass with 64 columns, 4 = with 128.
+int gemm_chain_pick_for(int64_t n, int64_t m, int sm_count) {
+    if (sm_count <= 0) sm_count = 148;
+    const int64_t gy = (n + 127) / 128, g32 = (m + 31) / 32, g64 = (m + 63) / 64, g128 = (m + 127) / 128;
+    const auto waves = [&](int64_t ctas) { return (double)((ctas + sm_count - 1) / sm_count); };
+    const double expand = 0.235 * (double)gy / 32.0 + 0.14 * (double)g64 / 8.0 + 0.05;
+    const double t_int = waves(gy * g32), t_64 = waves(gy * g64) + expand, t_128 = 1.6 * waves(gy * g128) + expand;
+    if (t_int <= t_64 && t_int <= t_128) return 0;
+    return t_128 < t_64 ? 4 : 3;
+}
 static int gemm_chain_pick(int64_t n, int64_t m) {
     static int sms[64] = {0};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
     if (sms[dev] == 0 && (cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms[dev] <= 0)) sms[dev] = 148;
-    const int64_t gy = (n + 127) / 128, g32 = (m + 31) / 32, g64 = (m + 63) / 64, g128 = (m + 127) / 128;
-    const auto waves = [&](int64_t ctas) { return (double)((ctas + sms[dev] - 1) / sms[dev]); };
-    const double expand = 0.235 * (double)gy / 32.0 + 0.14 * (double)g64 / 8.0 + 0.05;
-    const double t_int = waves(gy * g32), t_64 = waves(gy * g64) + expand, t_128 = 1.6 * waves(gy * g128) + expand;
-    if (t_int <= t_64 && t_int <= t_128) return 0;
-    return t_128 < t_64 ? 4 : 3;
+    return gemm_chain_pick_for(n, m, sms[dev]);
 }
 
 // mode: 1 = Q4_K gemm chain, 2 = Q4_K tiled chain

@@ -44,3 +44,21 @@ def test_argument_errors_are_statuses_not_aborts():
     assert rc == 3 and b"not supported" in mod.lib.b200_last_error()
     rc = mod.lib.b200_mul_mat(mod.Q4_K, 8, 100, 1, None, None, 100, None, 8, 0, None)
     assert rc == 3 and b"multiple of 256" in mod.lib.b200_last_error()
+
+
+def test_prompt_kernel_choice_follows_cta_waves():
+    """host arithmetic only: which Q4_K prompt kernel the library takes for (weight rows, activation rows) on 148 SMs"""
+    lib = ctypes.CDLL(b200.load().LIB_PATH)
+    f = lib.b200_prompt_kernel_choice
+    f.restype = ctypes.c_int
+    f.argtypes = [ctypes.c_int64, ctypes.c_int64, ctypes.c_int]
+    # one wave of the integer kernel (128 x 32 per CTA) is never beaten by a kernel that first expands its operands
+    assert f(4096, 64, 148) == 0 and f(4096, 128, 148) == 0 and f(1024, 512, 148) == 0
+    # 192 CTAs of the integer kernel are two waves; 96 of the 64-column two-pass kernel are one
+    assert f(4096, 192, 148) == 3 and f(4096, 256, 148) == 3
+    # 512 activation rows on 4096 weight rows: 128 CTAs of the 128-column kernel are a single wave
+    assert f(4096, 512, 148) == 4
+    # ffn shapes at 512 rows: 448 CTAs x 1.6 against 896 CTAs: four long waves against seven short ones
+    assert f(14336, 512, 148) == 4
+    # a small GPU changes the wave counts, not the rule; sm_count <= 0 means 148
+    assert f(4096, 64, 16) in (3, 4) and f(4096, 512, 0) == 4
