@@ -70,6 +70,13 @@ int b200_synchronize(void *stream);
  * device instead of hanging it.  Reads and clears that code for the current device (0 = none).
  * (Failure reporting of the kind ggml_backend_i.synchronize surfaces: crates/ggml/src/backend.rs:761-765.) */
 int b200_kernel_error(int *code);
+/* Test hooks (no counterpart in the reference).  b200_debug_alloc_count: device allocations the library has made
+ * for its own scratch blocks so far in this process.  b200_debug_stream_wait: the next launches of the streaming
+ * decode kernel poll each wait at most spin_limit times (0 = the normal limit) and their producer leaves ring unit
+ * skip_unit unfilled (-1 = none), so that a test can watch a bounded wait run out: the kernel returns, its output
+ * rows stay unwritten and b200_kernel_error reports code 1 (producer) or 2 (consumer). */
+unsigned long long b200_debug_alloc_count(void);
+void b200_debug_stream_wait(int spin_limit, int skip_unit);
 /* Which kernel a Q4_K prompt mat-mul (8x8 gemm route, n weight rows, m >= 32 activation rows) takes on a GPU with
  * sm_count SMs: 0 = integer tcgen05 kernel, 3 / 4 = the two-pass f16-image kernels with 64 / 128 activation rows
  * per CTA.  Pure host arithmetic (CTA waves times measured time per wave, plus the expansion); no CUDA call.
@@ -155,7 +162,10 @@ int b200_mul_mat_host(int type, int64_t n, int64_t k, int64_t m, const void *dev
  * that call from a point where the allocator is out of reach use this form
  * instead: its scratch is a fixed 256 KiB array inside the loaded module
  * (b200_static_scratch_nbytes), one copy per device for the life of the
- * process, and the call performs no allocation of any kind.
+ * process, and the call performs no allocation of any kind: the kernels' error
+ * word and counters are module variables as well, and where b200_mul_mat would
+ * pick a kernel that needs a further scratch block (the two-pass prompt kernels)
+ * this entry point runs the one-pass kernel that gives the same bits.
  *  - m x k activations whose quantized form exceeds the array are refused with
  *    B200_STATUS_BACKEND_ERROR and a message; nothing is launched.
  *  - The first call on a device resolves the array's device address (that

@@ -69,6 +69,9 @@ def _load():
     L.b200_mul_mat_host.argtypes = [i32, i64, i64, i64, vp, vp, vp, i32, vp]
     L.b200_mul_mat_id.argtypes = [i32, i64, i64, i64, i64, i64, i64, vp, vp, vp, vp, i32, vp]
     L.b200_flash_attn_ext.argtypes = [vp, vp]
+    L.b200_debug_alloc_count.restype = C.c_ulonglong
+    L.b200_debug_stream_wait.argtypes = [i32, i32]
+    L.b200_debug_stream_wait.restype = None
     return L
 
 

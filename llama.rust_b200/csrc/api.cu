@@ -42,6 +42,15 @@ struct Scratch {
     size_t bytes = 0;
 };
 static std::mutex g_scratch_mu;
+static unsigned long long g_alloc_count = 0;
+static thread_local int g_no_scratch = 0;
+NoScratchScope::NoScratchScope() { g_no_scratch++; }
+NoScratchScope::~NoScratchScope() { g_no_scratch--; }
+bool no_scratch_mode() { return g_no_scratch > 0; }
+unsigned long long library_alloc_count() {
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    return g_alloc_count;
+}
 static Scratch g_scratch[4][64];   // [0] general scratch, [1] the K-split exchange of the decode mat-mul (lives across the other's users)
 static unsigned long long g_scratch_gen = 0;
 
@@ -60,6 +69,8 @@ static int scratch_get_slot(int slot, size_t bytes, void **ptr) {
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
     B200_REQUIRE(dev >= 0 && dev < 64, "scratch: device index %d out of range", dev);
+    B200_REQUIRE(!no_scratch_mode(), "a route that needs library scratch (%zu bytes, block %d) was taken inside an entry point that may not allocate",
+                 bytes, slot);
     std::lock_guard<std::mutex> lk(g_scratch_mu);
     Scratch &s = g_scratch[slot][dev];
     if (s.bytes < bytes) {
@@ -75,6 +86,7 @@ static int scratch_get_slot(int slot, size_t bytes, void **ptr) {
         B200_CUDA(cudaMalloc(&s.ptr, want));
         s.bytes = want;
         g_scratch_gen++;
+        g_alloc_count++;
     }
     *ptr = s.ptr;
     return B200_STATUS_SUCCESS;
@@ -157,6 +169,10 @@ int b200_kernel_error(int *code) {
     B200_REQUIRE(code != nullptr, "kernel_error: null out pointer");
     return gemv_stream_error(code);
 }
+
+unsigned long long b200_debug_alloc_count(void) { return library_alloc_count(); }
+
+void b200_debug_stream_wait(int spin_limit, int skip_unit) { gemv_stream_debug_wait(spin_limit, skip_unit); }
 
 int b200_prompt_kernel_choice(int64_t n, int64_t m, int sm_count) { return gemm_chain_pick_for(n, m, sm_count); }
 

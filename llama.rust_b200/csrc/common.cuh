@@ -208,6 +208,17 @@ int scratch_get_images(size_t bytes, void **ptr);  // a fourth, for the prompt m
 // graph_compute brackets a node list with (true) / (false): inside, attention reuses the lists of an unchanged mask
 void flash_attn_graph_scope(bool enter);
 
+// b200_mul_mat_static_scratch brackets its launches with this scope: inside it no route that needs a library
+// scratch block is taken, and scratch_get* refuse instead of allocating (thread-local)
+struct NoScratchScope {
+    NoScratchScope();
+    ~NoScratchScope();
+};
+bool no_scratch_mode();
+// device allocations the library itself has made so far (scratch blocks); exported as b200_debug_alloc_count
+unsigned long long library_alloc_count();
+void gemv_stream_debug_wait(int spin_limit, int skip_unit);
+
 // route the reference takes for (type, n, m), and the activation quantizer that route reads
 int pick_route(int type, int64_t n, int64_t m);
 int act_kind_for(int type, int route, int64_t m);

@@ -256,10 +256,13 @@ fa_tiled_kernel(b200_flash_attn_args a, TiledDims d, float kq_scale) {
 template <int DK, int DV>
 static int launch_tiled(const b200_flash_attn_args *a, const TiledDims &d, float kq_scale, cudaStream_t s) {
     const size_t smem = (size_t)(DK * QT + DK * KT + KT * DV + KT * QT + QT * KT) * 4;
-    static bool done = false;
-    if (!done) {
+    static bool done[64] = {false};   // the attribute belongs to the (function, device) pair
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    B200_REQUIRE(dev >= 0 && dev < 64, "flash_attn_ext: device index %d out of range", dev);
+    if (!done[dev]) {
         B200_CUDA(cudaFuncSetAttribute(fa_tiled_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        done = true;
+        done[dev] = true;
     }
     dim3 grid((unsigned)((d.T + QT - 1) / QT), (unsigned)d.H);
     fa_tiled_kernel<DK, DV><<<grid, 256, smem, s>>>(*a, d, kq_scale);

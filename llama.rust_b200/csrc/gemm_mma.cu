@@ -520,11 +520,14 @@ int launch_gemm_mma(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *ti
     const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
     if (mode == 1 && m < 32 && gemm_small_enabled()) {
         // a few activation rows: K split over the warps of a CTA
-        static bool attr_done = false;
+        static bool attr_done[64] = {false};   // the attribute belongs to the (function, device) pair
         const size_t smem = sizeof(SmallStage) * SMALL_WIN;
-        if (!attr_done) {
+        int dev = 0;
+        B200_CUDA(cudaGetDevice(&dev));
+        B200_REQUIRE(dev >= 0 && dev < 64, "gemm: device index %d out of range", dev);
+        if (!attr_done[dev]) {
             B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr_done = true;
+            attr_done[dev] = true;
         }
         const int64_t sy = (m + 15) / 16;
         B200_REQUIRE(tiles_n < 0x7fffffffLL && sy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);

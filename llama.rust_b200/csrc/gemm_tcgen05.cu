@@ -703,6 +703,7 @@ int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t
     if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
     int choice = gemm_tcgen05_f16_choice();
     if (mode == 1 && choice < 0) choice = gemm_chain_pick(n, m);
+    if (no_scratch_mode() && (choice == 3 || choice == 4)) choice = 0;   // the two-pass kernels need the image block
     if (mode == 1 && choice == 2) return launch_gemm_tcgen05_f16x64(n, k, m, tiles, acts, dst, lddst, s);
     if (mode == 1 && choice == 3) return launch_gemm_tcgen05_img(n, k, m, tiles, acts, dst, lddst, s);
     if (mode == 1 && choice == 4) return launch_gemm_tcgen05_img128(n, k, m, tiles, acts, dst, lddst, s);

@@ -258,10 +258,14 @@ static int launch_q4k(int64_t n, int nb, const uint8_t *tiles, ActView acts, flo
     const int nw = pick_warps(splits > 1 ? (nb + splits - 1) / splits : nb);
     const size_t smem = sizeof(Q4KStage) * nw * NCOL + (splits > 1 ? 0 : sizeof(int4) * (size_t)NCOL * nb * 32 * (MODE == 1 ? 3 : 1));
     B200_REQUIRE(smem <= 200 * 1024, "mul_mat q4_K: k too large for the shared-memory exchange (%zu bytes)", smem);
-    static bool attr_done = false;
-    if (!attr_done) {
+    // the attribute belongs to the (function, device) pair: one flag per device
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    B200_REQUIRE(dev >= 0 && dev < 64, "gemv: device index %d out of range", dev);
+    if (!attr_done[dev]) {
         B200_CUDA(cudaFuncSetAttribute(gemv_q4_K_kernel<NCOL, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr_done = true;
+        attr_done[dev] = true;
     }
     const int64_t tiles_n = pm.seg_count > 1 ? pm.seg_total : (n + TILE_ROWS - 1) / TILE_ROWS;
     B200_REQUIRE(pairs >= 1 && pairs <= 65535, "mul_mat_id: %lld (token, slot) pairs exceed one launch", (long long)pairs);
@@ -280,18 +284,24 @@ static bool gemv_ksplit_enabled() {
     }
     return v == 1;
 }
-static int *g_kcount[64] = {nullptr};
 constexpr int KSPLIT_MAX_TILES = 1024;
+// arrival counters of the K split, one per row tile, zero between launches: a file-scope device array (one
+// zero-initialized copy per device that loads the module), addressed through cudaGetSymbolAddress
+static __device__ int g_kcount_dev[KSPLIT_MAX_TILES];
+static int *g_kcount[64] = {nullptr};
 // One activation row, a matrix with fewer row tiles than the GPU has room for: split K over several CTAs per tile.
 static int launch_q4k_ksplit(int splits, int64_t n, int nb, const uint8_t *tiles, ActView acts, float *dst, cudaStream_t s) {
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
     B200_REQUIRE(dev >= 0 && dev < 64, "gemv: device index %d out of range", dev);
     if (!g_kcount[dev]) {
-        B200_CUDA(cudaMalloc((void **)&g_kcount[dev], KSPLIT_MAX_TILES * sizeof(int)));
-        B200_CUDA(cudaMemset(g_kcount[dev], 0, KSPLIT_MAX_TILES * sizeof(int)));
+        void *p = nullptr;
+        B200_CUDA(cudaGetSymbolAddress(&p, g_kcount_dev));
+        B200_REQUIRE(p != nullptr, "gemv: the device reported no address for the K-split counters");
+        g_kcount[dev] = (int *)p;
     }
     const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
+    B200_REQUIRE(tiles_n <= KSPLIT_MAX_TILES, "gemv: %lld row tiles exceed the K-split counters", (long long)tiles_n);
     void *kx = nullptr;
     int rc = scratch_get_kx((size_t)tiles_n * nb * 32 * sizeof(int4), &kx);
     if (rc != B200_STATUS_SUCCESS) return rc;
@@ -442,11 +452,14 @@ static int launch_generic(int64_t n, int nb, const uint8_t *tiles, ActView acts,
     if (win > nw && win % nw) win -= win % nw;  // whole rounds of warps per window
     B200_REQUIRE(win >= 1, "gemv: shared memory too small for one group");
     const size_t smem = fixed + per_group * win;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    B200_REQUIRE(dev >= 0 && dev < 64, "gemv: device index %d out of range", dev);
+    if (!attr_done[dev]) {
         B200_CUDA(cudaFuncSetAttribute(gemv_generic_kernel<T, NCOL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)GEMV_SMEM_LIMIT));
-        attr_done = true;
+        attr_done[dev] = true;
     }
     const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
     B200_REQUIRE(pairs >= 1 && pairs <= 65535, "mul_mat_id: %lld (token, slot) pairs exceed one launch", (long long)pairs);
@@ -511,14 +524,11 @@ static bool gemm_tcgen05_enabled() {
 }
 
 static int64_t gemv_stream_max_tiles() {
-    static int64_t v = -1;
-    if (v < 0) {
-        int dev = 0, sms = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-            sms = 0;
-        v = sms;
-    }
-    return v;
+    static int sms[64] = {0};   // per device: a process may drive GPUs with different SM counts
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (sms[dev] == 0 && cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms[dev] = 0;
+    return sms[dev];
 }
 
 int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst,
@@ -527,7 +537,7 @@ int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint
     const int nb = (int)(k / GROUP_K);
     // the bulk-copy streaming kernel wins while every CTA has at most one row tile (no second wave to
     // overlap); beyond that the register-staged kernel with two CTAs per SM keeps more warps busy
-    if (type == B200_TYPE_Q4_K && route == B200_ROUTE_REPACK && m == 1 && gemv_ksplit_enabled() && nb >= 8 &&
+    if (type == B200_TYPE_Q4_K && route == B200_ROUTE_REPACK && m == 1 && gemv_ksplit_enabled() && !no_scratch_mode() && nb >= 8 &&
         (n + TILE_ROWS - 1) / TILE_ROWS <= gemv_stream_max_tiles()) {
         // at most one row tile per SM: four CTAs per tile (two for short rows), each a quarter of K
         const int splits = nb >= 16 ? 4 : 2;

@@ -54,9 +54,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // bounded wait for the phase with the given parity; false on expiry
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity, unsigned limit = SPIN_LIMIT) {
     const uint32_t a = smem_u32(bar);
-    for (unsigned i = 0; i < SPIN_LIMIT; i++) {
+    for (unsigned i = 0; i < limit; i++) {
         unsigned ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -118,7 +118,7 @@ __device__ __forceinline__ StreamSmem carve(unsigned char *base, int stages, int
 template <int CONSUMER_WARPS>
 __global__ void __launch_bounds__((CONSUMER_WARPS + 1) * 32, 1)
 gemv_q4_K_stream_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *__restrict__ dst, int64_t n, int nb,
-                        int n_tiles, int stages, int xb, int *err_flag) {
+                        int n_tiles, int stages, int xb, int *err_flag, unsigned spin_limit, int skip_unit) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     StreamSmem sm = carve(smem_raw, stages, nb, xb);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -139,6 +139,9 @@ gemv_q4_K_stream_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *
     // let the next kernel in the stream begin its own prologue
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
+    // the producer lane's record of what it put in flight: stages used at least once, and the parity of the last
+    // phase it started on each (read again in the wind-down)
+    unsigned issued_mask = 0, issued_parity = 0;
     if (warp == CONSUMER_WARPS) {
         // ---------------- producer: weights do not depend on the previous kernel in the stream
         if (lane == 0) {
@@ -148,16 +151,20 @@ gemv_q4_K_stream_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *
             unsigned ph = 0;
             int64_t tile = blockIdx.x;
             for (int64_t u = 0; u < units; u++) {
-                if (u >= stages && !mbar_wait(&sm.empty[st], ph ^ 1)) {
+                if (u >= stages && !mbar_wait(&sm.empty[st], ph ^ 1, spin_limit)) {
                     atomicExch(err_flag, 1);
                     *(volatile int *)sm.abort_flag = 1;
                     break;
                 }
                 if (*(volatile int *)sm.abort_flag) break;
                 const int ng = nb - sg < STAGE_GROUPS ? nb - sg : STAGE_GROUPS;
-                mbar_expect_tx(&sm.full[st], (unsigned)ng * CHUNK);
-                bulk_load(sm.ring + (size_t)st * STAGE_BYTES, tiles + (tile * nb + sg) * (int64_t)CHUNK, (unsigned)ng * CHUNK,
-                          &sm.full[st]);
+                if (u != skip_unit) {   // skip_unit >= 0 only in the wait-expiry test: that stage is never filled
+                    mbar_expect_tx(&sm.full[st], (unsigned)ng * CHUNK);
+                    bulk_load(sm.ring + (size_t)st * STAGE_BYTES, tiles + (tile * nb + sg) * (int64_t)CHUNK, (unsigned)ng * CHUNK,
+                              &sm.full[st]);
+                    issued_mask |= 1u << st;
+                    issued_parity = (issued_parity & ~(1u << st)) | (ph << st);
+                }
                 if (++st == stages) { st = 0; ph ^= 1; }
                 sg += STAGE_GROUPS;
                 if (sg >= nb) { sg = 0; tile += gridDim.x; }
@@ -190,7 +197,7 @@ gemv_q4_K_stream_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *
         }
         for (int64_t u = set; u < units; u += NSETS) {
             bool ok = true;
-            if (lane == 0) ok = mbar_wait(&sm.full[st], ph);
+            if (lane == 0) ok = mbar_wait(&sm.full[st], ph, spin_limit);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok || *(volatile int *)sm.abort_flag) {
                 if (lane == 0 && !ok) {
@@ -285,30 +292,43 @@ gemv_q4_K_stream_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *
             }
         }
     }
-    // wind-down: every bulk copy this CTA issued must have landed before shared memory is released
+    // wind-down: every bulk copy this CTA issued must have landed before shared memory is released.  On the
+    // normal path the consumers have waited for each of them; after an abort the producer lane waits (bounded)
+    // for the last phase it started on every stage.
     __syncthreads();
-    if (*(volatile int *)sm.abort_flag && tid == 0) {
-        for (int i = 0; i < stages; i++) {
-            // a stage whose copy is still in flight completes its current phase; poll both parities, bounded
-            if (!mbar_wait(&sm.full[i], 0)) mbar_wait(&sm.full[i], 1);
-        }
+    if (*(volatile int *)sm.abort_flag && warp == CONSUMER_WARPS && lane == 0) {
+        for (int i = 0; i < stages; i++)
+            if (issued_mask & (1u << i)) mbar_wait(&sm.full[i], (issued_parity >> i) & 1u, spin_limit < 4096u ? 4096u : spin_limit);
     }
 }
 
 }  // namespace
 
-// device-side error word of the streaming kernels (one per device)
+// Device-side error word of the kernels: a file-scope device variable (every device that loads the module holds
+// its own zero-initialized copy), so finding it takes no allocation.  In host code the name is only a handle for
+// cudaGetSymbolAddress; g_err_flag[dev] is the address kernels get.
+static __device__ int g_err_word_dev;
 static int *g_err_flag[64] = {nullptr};
+// test hook (b200_debug_stream_wait): a poll limit for the streaming kernel's waits and a ring unit its producer
+// leaves unfilled, so that a test can watch a wait run out and the kernel return with an error code
+static int g_wait_limit_override = 0;
+static int g_skip_unit_override = -1;
+void gemv_stream_debug_wait(int spin_limit, int skip_unit) {
+    g_wait_limit_override = spin_limit > 0 ? spin_limit : 0;
+    g_skip_unit_override = skip_unit >= 0 ? skip_unit : -1;
+}
 
-// the current device's error word, allocated on first use; kernels that skip a bad index or give
-// up a wait store a non-zero code there and b200_kernel_error() reads and clears it
+// the current device's error word; kernels that skip a bad index or give up a wait store a non-zero code there
+// and b200_kernel_error() reads and clears it
 int device_error_word(int **flag) {
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
     B200_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
     if (!g_err_flag[dev]) {
-        B200_CUDA(cudaMalloc((void **)&g_err_flag[dev], sizeof(int)));
-        B200_CUDA(cudaMemset(g_err_flag[dev], 0, sizeof(int)));
+        void *p = nullptr;
+        B200_CUDA(cudaGetSymbolAddress(&p, g_err_word_dev));
+        B200_REQUIRE(p != nullptr, "the device reported no address for the error word");
+        g_err_flag[dev] = (int *)p;
     }
     *flag = g_err_flag[dev];
     return B200_STATUS_SUCCESS;
@@ -361,7 +381,8 @@ int launch_gemv_q4_K_stream(int64_t n, int64_t k, const uint8_t *tiles, ActView 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    B200_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4_K_stream_kernel<cw>, tiles, acts, dst, n, nb, n_tiles, stages, xb, g_err_flag[dev]));
+    B200_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4_K_stream_kernel<cw>, tiles, acts, dst, n, nb, n_tiles, stages, xb, g_err_flag[dev],
+                                 g_wait_limit_override > 0 ? (unsigned)g_wait_limit_override : SPIN_LIMIT, g_skip_unit_override));
     return B200_STATUS_SUCCESS;
 }
 

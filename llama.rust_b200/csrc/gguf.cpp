@@ -185,6 +185,10 @@ int b200_gguf_open(const char *path, b200_gguf **out) {
         std::string key;
         Value v;
         if (!c.str(&key)) return fail("truncated key");
+        // the reference refuses empty and repeated keys (crates/ggml/src/gguf.rs:509-512)
+        if (key.empty()) return fail("empty key");
+        for (auto &o : g->kv)
+            if (o.first == key) return fail("duplicate key");
         const uint32_t type = c.get<uint32_t>();
         if (!read_value(c, type, &v, 0)) return fail("truncated or malformed value");
         g->kv.emplace_back(std::move(key), v);
@@ -198,20 +202,29 @@ int b200_gguf_open(const char *path, b200_gguf **out) {
         if (!c.str(&t.name)) return fail("truncated tensor name");
         t.n_dims = (int)c.get<uint32_t>();
         if (!c.ok || t.n_dims < 1 || t.n_dims > 4) return fail("tensor with a bad dimension count");
-        for (int d = 0; d < t.n_dims; d++) t.ne[d] = (int64_t)c.get<uint64_t>();
+        for (int d = 0; d < t.n_dims; d++) {
+            t.ne[d] = (int64_t)c.get<uint64_t>();
+            if (t.ne[d] < 0) return fail("tensor with a negative dimension");   // crates/ggml/src/gguf.rs:554
+        }
         t.type = (int)c.get<uint32_t>();
         t.offset = c.get<uint64_t>();
         if (!c.ok) return fail("truncated tensor info");
         for (auto &o : g->tensors)
             if (o.name == t.name) return fail("duplicate tensor name");
         const size_t rs = gguf_row_size(t.type, t.ne[0]);
-        t.nbytes = rs * (size_t)t.ne[1] * (size_t)t.ne[2] * (size_t)t.ne[3];   // 0 for types this library does not know
+        // 0 for types this library does not know; a product that does not fit size_t cannot be a tensor of this file
+        size_t nb = rs;
+        for (int d = 1; d < 4; d++)
+            if (__builtin_mul_overflow(nb, (size_t)t.ne[d], &nb)) return fail("tensor size overflows");
+        t.nbytes = nb;
         g->tensors.push_back(std::move(t));
     }
     const uint64_t meta = (uint64_t)(c.p - g->map);
     g->data_offset = (meta + g->alignment - 1) / g->alignment * g->alignment;
-    for (auto &t : g->tensors)
-        if (t.offset % g->alignment || g->data_offset + t.offset + t.nbytes > g->size) return fail("tensor data outside the file or misaligned");
+    if (g->data_offset > g->size) return fail("metadata runs past the end of the file");
+    const uint64_t data_size = g->size - g->data_offset;
+    for (auto &t : g->tensors)   // subtractions only: no sum that a huge offset could wrap
+        if (t.offset % g->alignment || t.offset > data_size || t.nbytes > data_size - t.offset) return fail("tensor data outside the file or misaligned");
     *out = g.release();
     return B200_STATUS_SUCCESS;
 }

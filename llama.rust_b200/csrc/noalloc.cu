@@ -7,7 +7,11 @@
 // manager that owns every device allocation, or code that runs while the
 // allocator is unavailable to it.  For them this entry point does the same
 // quantize-then-multiply with the scratch placed in a fixed array that is part
-// of the loaded module itself, so no allocation call of any kind happens here.
+// of the loaded module itself, so no allocation call of any kind happens here:
+// the kernels' error word and counters are file-scope device variables too, and
+// for the shapes where b200_mul_mat would pick a kernel that needs a further
+// scratch block (the two-pass prompt mat-mul with its operand images) this entry
+// point runs the one-pass kernel that computes the same bits without it.
 //
 // Consequences a caller has to know:
 //  * the array is B200_STATIC_SCRATCH_BYTES (256 KiB) large and every device
@@ -79,6 +83,9 @@ int b200_mul_mat_static_scratch(int type, int64_t n, int64_t k, int64_t m, const
     if (rc != B200_STATUS_SUCCESS) return rc;
     if (route == B200_ROUTE_AUTO) route = pick_route(type, n, m);
     cudaStream_t s = (cudaStream_t)stream;
+    // inside this scope the launchers take only routes that need no further scratch block (the two-pass prompt
+    // kernels and the K split are skipped), and any request for library scratch is refused instead of served
+    NoScratchScope no_scratch;
     ActBuf a = act_carve(scratch, m, k);
     rc = launch_quantize_acts(act_kind_for(type, route, m), m, k, dev_x, ldx, a, s);
     if (rc != B200_STATUS_SUCCESS) return rc;

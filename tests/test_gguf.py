@@ -100,3 +100,46 @@ def test_malformed_files_are_refused(gg, tmp_path):
     w.add_tensor("t", F32, (4,), np.zeros(4, dtype=np.float32))
     with pytest.raises(m.B200Error, match="duplicate"):
         w.add_tensor("t", F32, (4,), np.zeros(4, dtype=np.float32))
+
+
+def crafted(kvs, tensors, alignment_pad=True, data=b""):
+    """a GGUF v3 file written by hand: kvs = [(key, u32 value)], tensors = [(name, dims, type, offset)]"""
+    out = bytearray(b"GGUF" + struct.pack("<IQQ", 3, len(tensors), len(kvs)))
+    for key, val in kvs:
+        kb = key.encode()
+        out += struct.pack("<Q", len(kb)) + kb + struct.pack("<II", 4, val)   # type 4 = u32
+    for name, dims, ty, off in tensors:
+        nb = name.encode()
+        out += struct.pack("<Q", len(nb)) + nb + struct.pack("<I", len(dims))
+        for d in dims:
+            out += struct.pack("<Q", d & 0xFFFFFFFFFFFFFFFF)
+        out += struct.pack("<IQ", ty, off & 0xFFFFFFFFFFFFFFFF)
+    if alignment_pad:
+        out += b"\0" * (-len(out) % 32)
+    return bytes(out) + data
+
+
+def test_crafted_tensor_infos_are_refused(gg, tmp_path):
+    """sizes and offsets from an untrusted file may not wrap around: a negative dimension, a byte count that
+    overflows, an aligned offset near 2^64 whose sum with the data start wraps; empty and repeated keys
+    (refused by the reference's reader too, crates/ggml/src/gguf.rs:509-512,554)"""
+    m = b200.load()
+    good = crafted([("a", 1)], [("t", (8,), F32, 0)], data=b"\0" * 32)
+    p = tmp_path / "good.gguf"
+    p.write_bytes(good)
+    r = gg.Reader(p)
+    assert [t[0] for t in r.tensors()] == ["t"]
+    r.close()
+    bad = {
+        "negative dimension": crafted([], [("t", (-8,), F32, 0)], data=b"\0" * 32),
+        "overflows": crafted([], [("t", (1 << 40, 1 << 40), F32, 0)], data=b"\0" * 32),
+        "outside the file": crafted([], [("t", (8,), F32, 0xFFFFFFFFFFFFFFE0)], data=b"\0" * 32),
+        "outside the file ": crafted([], [("t", (64,), F32, 0)], data=b"\0" * 32),
+        "empty key": crafted([("", 1)], [], data=b""),
+        "duplicate key": crafted([("a", 1), ("a", 2)], [], data=b""),
+    }
+    for why, blob in bad.items():
+        p = tmp_path / "bad.gguf"
+        p.write_bytes(blob)
+        with pytest.raises(m.B200Error, match=why.strip()):
+            gg.Reader(p)

@@ -1,0 +1,73 @@
+"""A bounded wait that runs out: the kernel returns, reports a code, and the device stays usable.
+
+Every wait inside the library's kernels has a poll limit.  This test makes one run out without faulting or
+hanging anything: through the library's test hook the streaming decode kernel gets a short poll limit and a
+producer that leaves the first ring unit of every CTA unfilled, so the consumers of that unit give up.  The
+launch must return, b200_kernel_error must report code 1 (producer gave up) or 2 (a consumer did), no output
+row may have been written (a row tile's results are stored only after all of its K groups arrived), and the
+next normal launch must be bit-exact with the CPU oracle.
+"""
+import numpy as np
+import pytest
+
+import b200
+import orc
+import synth
+from conftest import bits_equal
+
+pytestmark = pytest.mark.gpu
+
+
+def test_streaming_kernel_wait_expiry_reports_a_code_and_the_next_launch_is_exact():
+    dev = b200.load()
+    assert dev.device_count() > 0
+    dev.set_device(0)
+    n, k = 4096, 4096   # 128 row tiles: the streaming kernel, one tile (two ring units) per CTA
+    W = synth.weights(orc.Q4_K, n, k, seed=71, period=512)
+    w = dev.Weight(orc.Q4_K, W, k)
+    x = synth.activations(1, k, seed=72)
+    dx = dev.device_array(x)
+    out = dev.DeviceBuffer(4 * n)
+    want, _ = orc.mul_mat(orc.Q4_K, W, x)
+
+    dev.mul_mat_device(w, dx, 1, out)   # a normal launch first: the kernel is the streaming one and works
+    dev.synchronize()
+    assert dev.kernel_error() == 0
+    assert bits_equal(out.download(np.float32, n), want.ravel())
+
+    dev.check(dev.lib.b200_memset(out.ptr, 0xFF, 4 * n, None), "memset")
+    dev.synchronize()
+    dev.lib.b200_debug_stream_wait(2000, 0)
+    try:
+        dev.mul_mat_device(w, dx, 1, out)
+        dev.synchronize()           # returns: the waits gave up after 2000 polls
+    finally:
+        dev.lib.b200_debug_stream_wait(0, -1)
+    assert dev.kernel_error() in (1, 2)
+    assert dev.kernel_error() == 0   # the read cleared it
+    assert (out.download(np.uint32, n) == 0xFFFFFFFF).all(), "an aborted row tile must not store results"
+
+    dev.mul_mat_device(w, dx, 1, out)
+    dev.synchronize()
+    assert dev.kernel_error() == 0
+    assert bits_equal(out.download(np.float32, n), want.ravel())
+
+
+def test_second_device_in_the_same_process():
+    """Kernels that need more than 48 KB of dynamic shared memory set a per-(function, device) attribute: after
+    device 0 has run them, device 1 must get its own."""
+    dev = b200.load()
+    if dev.device_count() < 2:
+        pytest.skip("needs two devices")
+    cases = [(orc.Q4_K, 256, 4096, 3), (orc.Q6_K, 256, 4096, 1), (orc.Q4_K, 256, 2048, 16)]
+    try:
+        for d in (0, 1):
+            dev.set_device(d)
+            for ty, n, k, m in cases:
+                W = synth.weights(ty, n, k, seed=81)
+                x = synth.activations(m, k, seed=82)
+                want, _ = orc.mul_mat(ty, W, x)
+                assert bits_equal(dev.mul_mat(dev.Weight(ty, W, k), x), want), (d, ty, m)
+            assert dev.kernel_error() == 0
+    finally:
+        dev.set_device(0)
