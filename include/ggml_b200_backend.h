@@ -36,6 +36,13 @@ enum {
     GGML_OP_ROPE = 48, GGML_OP_FLASH_ATTN_EXT = 74, GGML_OP_UNARY = 91, GGML_OP_GLU = 100,
 };
 
+/* Ops outside ggml's enum, served only by a backend that has a tensor-parallel group attached (the decode driver
+ * of llama_b200.h emits them; the reference has no multi-device graph).  TP_ALL_REDUCE: the node aliases src[0]
+ * (dense F32) and holds, afterwards, the sum of src[0] over the ranks, added in rank order.  TP_ALL_GATHER:
+ * src[0] is [n_local, rows], the node [n_local * ranks, rows] with rank r's slice of every row at column
+ * r * n_local; src[1] is a scratch tensor of the node's size. */
+enum { B200_OP_TP_ALL_REDUCE = 0x4200, B200_OP_TP_ALL_GATHER = 0x4201 };
+
 /* enum ggml_unary_op value carried in op_params[0] of a GGML_OP_UNARY node (crates/ggml/src/ops.rs:1632-1636) */
 enum { GGML_UNARY_OP_SILU = 10 };
 

@@ -48,7 +48,9 @@ void b200_llama_free(b200_llama *ctx);
 /* ---- tensor parallelism across the GPUs of one node (one process per GPU) ------------------------------
  * The reference has no multi-device path; this is the row-split of BASELINE's 70B configuration: attn_q/k/v,
  * ffn_gate/up and output by rows (whole heads, FFN rows, vocabulary rows), attn_output and ffn_down by K with
- * an NCCL all-reduce of the partial sums, norms and token_embd replicated, logits all-gathered.
+ * an all-reduce of the partial sums, norms and token_embd replicated, logits all-gathered.  Collectives of up
+ * to 131072 floats per rank (every collective of a decode step) run as one kernel of this library over
+ * peer-mapped memory, with the partial sums added in rank order; larger ones (prompt batches) go to NCCL.
  *
  * b200_tp_unique_id: rank 0 fills 128 bytes (an ncclUniqueId) that the host passes to every rank.
  * b200_llama_new_tp: as b200_llama_new, for rank tp_rank of tp_size (n_head_kv, n_ff and n_vocab must divide).
@@ -56,6 +58,20 @@ void b200_llama_free(b200_llama *ctx);
  * b200_tp_shard_shape / b200_tp_shard_tensor: the cut itself, on host memory (split: 0 replicated, 1 rows,
  *   2 K), for hosts that shard while loading and for tests. */
 int b200_tp_unique_id(void *id128);
+/* A rank whose collectives are carried out by the host instead of by NCCL / peer memory, for tests that play
+ * several ranks on one GPU (one thread per rank): the driver calls the hook with its stream drained.
+ *   kind 0, all-reduce: dev_buf holds `count` floats, this rank's partial sums; on return it must hold the sum over
+ *           the ranks, added in rank order.
+ *   kind 1, all-gather: dev_buf holds rows x n_local floats (count of them); dev_dst [rows][n_local * size] must
+ *           receive every rank's slice of every row, rank r's at column r * n_local.
+ * A non-zero return fails the decode call.  No counterpart in the reference (which has no multi-device path). */
+typedef int (*b200_tp_hook_fn)(void *user, int kind, int rank, int size, float *dev_buf, int64_t count, float *dev_dst,
+                               int64_t n_local, int64_t rows);
+int b200_llama_new_tp_hook(const struct b200_llama_hparams *hp, int device, int32_t n_ctx, int32_t n_batch, int32_t cpu_threads,
+                           int32_t tp_rank, int32_t tp_size, b200_tp_hook_fn hook, void *user, b200_llama **out);
+/* How the group's small collectives travel: 1 = the library's single-kernel exchange over peer-mapped memory,
+ * 0 = NCCL (a rank could not map a peer's buffer, or B200_TP_LL=0), -1 = not a tensor-parallel driver / hook. */
+int b200_llama_tp_exchange_kind(const b200_llama *ctx);
 int b200_llama_new_tp(const struct b200_llama_hparams *hp, int device, int32_t n_ctx, int32_t n_batch, int32_t cpu_threads,
                       int32_t tp_rank, int32_t tp_size, const void *id128, b200_llama **out);
 int b200_tp_shard_shape(const char *name, int type, int64_t ne0, int64_t ne1, int32_t tp_size, int32_t *split, int64_t *ne0_local,

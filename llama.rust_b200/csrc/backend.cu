@@ -16,6 +16,7 @@
 
 #include "common.cuh"
 #include "ggml_b200_backend.h"
+#include "tp.h"
 
 namespace b200 {
 namespace {
@@ -121,6 +122,7 @@ struct BackendCtx {
     bool fuse_glue = true;          // one launch for neighbouring ROPE / SET_ROWS nodes (B200_FUSE_GLUE=0 / fuse_glue=0: off)
     bool fuse_siblings = true;      // one launch for one-row Q4_K mat-muls over the same activations (B200_FUSE_SIBLINGS=0 / fuse_siblings=0: off)
     bool capturable = true;       // cleared by a node that had to talk to the device while being issued
+    TpGroup *tp = nullptr;        // the tensor-parallel group whose collectives the TP_* nodes run (owned by the driver)
 };
 constexpr size_t SHADOW_MAX_BYTES = 1 << 20;
 constexpr int64_t ROPE_TABLE_MIN_ROWS = 4096, ROPE_TABLE_MAX_ROWS = 1 << 20;
@@ -396,8 +398,20 @@ static bool supports_glue(const ggml_tensor *op, std::string *why) {
     }
 }
 
+static bool dense_f32(const ggml_tensor *t) { return t && t->type == B200_TYPE_F32 && is_contiguous(t); }
+static bool supports_tp(const ggml_tensor *op, std::string *why) {
+    auto no = [&](const char *m) { if (why) *why = m; return false; };
+    const ggml_tensor *a = op->src[0];
+    if (!dense_f32(a) || !dense_f32(op)) return no("tensor-parallel collectives want dense F32 tensors");
+    if (op->op == B200_OP_TP_ALL_REDUCE) return op->data == a->data && same_shape(a, op) ? true : no("all-reduce node must alias its source");
+    if (a->ne[2] != 1 || a->ne[3] != 1 || op->ne[1] != a->ne[1] || op->ne[0] % a->ne[0] || op->ne[0] / a->ne[0] < 2) return no("all-gather: shape");
+    if (op->src[1] && (!dense_f32(op->src[1]) || ggml_nbytes(op->src[1]) < ggml_nbytes(op))) return no("all-gather: scratch tensor too small");
+    return true;
+}
+
 static bool op_supported(const ggml_tensor *op, std::string *why) {
     switch (op->op) {
+        case B200_OP_TP_ALL_REDUCE: case B200_OP_TP_ALL_GATHER: return supports_tp(op, why);
         case GGML_OP_NONE: case GGML_OP_RESHAPE: case GGML_OP_VIEW: case GGML_OP_PERMUTE: case GGML_OP_TRANSPOSE:
             return true;
         case GGML_OP_MUL_MAT: case GGML_OP_MUL_MAT_ID: return supports_mul_mat(op, why);
@@ -1066,6 +1080,13 @@ static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
             }
             case GGML_OP_GET_ROWS: rc = compute_get_rows(bc, op); break;
             case GGML_OP_ARGMAX: rc = compute_argmax(bc, op); break;
+            case B200_OP_TP_ALL_REDUCE:
+                rc = tp_all_reduce(bc->tp, (float *)op->data, (int64_t)(ggml_nbytes(op) / 4), bc->stream, &bc->capturable);
+                break;
+            case B200_OP_TP_ALL_GATHER:
+                rc = tp_all_gather_rows(bc->tp, (const float *)op->src[0]->data, (float *)op->data, op->src[0]->ne[0], op->src[0]->ne[1],
+                                        op->src[1] ? (float *)op->src[1]->data : nullptr, bc->stream, &bc->capturable);
+                break;
             default: break;
         }
         if (rc != B200_STATUS_SUCCESS) return rc;
@@ -1135,6 +1156,10 @@ static int backend_graph_compute(ggml_backend_t be, ggml_cgraph *g) {
         if (op && op->op == GGML_OP_ROPE && supports_glue(op, nullptr)) {
             int rc = rope_prepare(bc, op);
             if (rc != B200_STATUS_SUCCESS) return rc;
+        }
+        if (op && (op->op == B200_OP_TP_ALL_REDUCE || op->op == B200_OP_TP_ALL_GATHER)) {
+            B200_REQUIRE(bc->tp != nullptr, "graph_compute: node %d is a tensor-parallel collective, but no group is attached to this backend", i);
+            if (bc->tp->hook) bc->capturable = false;   // the exchange happens on the host
         }
     }
     if (!bc->graphs_enabled || !bc->capturable || g->n_nodes < 6) return run_nodes(bc, g);
@@ -1232,6 +1257,12 @@ static void backend_synchronize(ggml_backend_t be) {
     cudaStreamSynchronize(bc->stream);
 }
 static void *backend_get_stream(ggml_backend_t be) { return be ? (void *)((BackendCtx *)be->context)->stream : nullptr; }
+static void backend_set_tp(ggml_backend_t be, void *group) {
+    if (!be) return;
+    BackendCtx *bc = (BackendCtx *)be->context;
+    bc->tp = (TpGroup *)group;
+    bc->generation++;   // captured graphs hold the old group's buffers
+}
 static void backend_set_cpu_threads(ggml_backend_t be, int n) {
     if (be && n > 0) ((BackendCtx *)be->context)->cpu_threads = n;
 }
@@ -1335,6 +1366,7 @@ static ggml_backend_dev_t reg_get_device(ggml_backend_reg_t, size_t i) { return 
 static void *reg_get_proc_address(ggml_backend_reg_t, const char *name) {
     if (name && strcmp(name, "b200_backend_set_cpu_threads") == 0) return (void *)backend_set_cpu_threads;
     if (name && strcmp(name, "b200_backend_get_stream") == 0) return (void *)backend_get_stream;
+    if (name && strcmp(name, "b200_backend_set_tp") == 0) return (void *)backend_set_tp;
     return nullptr;
 }
 

@@ -18,6 +18,7 @@
 #include "common.cuh"
 #include "ggml_b200_backend.h"
 #include "llama_b200.h"
+#include "tp.h"
 
 using namespace b200;
 
@@ -47,20 +48,9 @@ struct Graph {
     ggml_tensor *tokens = nullptr, *pos = nullptr, *mask = nullptr, *row_idx = nullptr, *out_ids = nullptr;
     ggml_tensor *logits = nullptr, *argmax = nullptr;
     size_t bytes = 0;                     // compute-buffer bytes the graph spans
-    // tensor parallel: after node index `after` (exclusive end of a segment) the ranks all-reduce t in place
-    // (gather == nullptr) or all-gather t into gather
-    struct Collective { int after; ggml_tensor *t; ggml_tensor *gather; };
-    std::vector<Collective> collectives;
 };
 
 }  // namespace
-
-namespace b200 {
-int tp_comm_init(int rank, int size, const void *id128, void **comm);
-void tp_comm_destroy(void *comm);
-int tp_all_reduce_sum(void *comm, float *buf, size_t count, void *stream);
-int tp_all_gather(void *comm, const float *send, float *recv, size_t count_per_rank, void *stream);
-}  // namespace b200
 
 struct b200_llama {
     b200_llama_hparams hp;
@@ -82,7 +72,7 @@ struct b200_llama {
     // tensor parallel: this rank holds n_head / tp_size heads, n_head_kv / tp_size cache heads, the matching
     // rows / columns of every matrix (tp.cpp) and 1 / tp_size of the vocabulary rows
     int32_t tp_rank = 0, tp_size = 1;
-    void *comm = nullptr;
+    TpGroup *tp = nullptr;
     std::vector<uint8_t> shard_tmp;
 };
 
@@ -210,6 +200,16 @@ struct Builder {
         t->buffer = cache->buffer;
         return op(t, GGML_OP_SET_ROWS, rows, idx);
     }
+    // the sum of a over the ranks of the tensor-parallel group, in place: the node aliases a
+    ggml_tensor *tp_all_reduce(ggml_tensor *a, const char *name) {
+        ggml_tensor *t = fresh(a->type, a->ne[0], a->ne[1], a->ne[2]);
+        t->data = a->data;
+        t->buffer = a->buffer;
+        t->view_src = a->view_src ? a->view_src : a;
+        t->view_offs = a->view_offs;
+        snprintf(t->name, sizeof(t->name), "%s", name);
+        return op(t, B200_OP_TP_ALL_REDUCE, a);
+    }
     ggml_tensor *get_rows(ggml_tensor *table, ggml_tensor *ids, const char *name = "") {
         return op(alloc(B200_TYPE_F32, table->ne[0], ids->ne[0], 1, name), GGML_OP_GET_ROWS, table, ids);
     }
@@ -227,7 +227,6 @@ int build_graph(b200_llama *c, Graph *g, uint8_t *base, int64_t n, int64_t n_kv,
     const int64_t E = hp.n_embd, HD = hp.n_embd_head, H = hp.n_head / c->tp_size, HK = hp.n_head_kv / c->tp_size, EK = HK * HD;
     const bool tp = c->tp_size > 1;
     Builder b{c, g, base};
-    g->collectives.clear();
     g->tokens = b.alloc(B200_TYPE_I32, n, 1, 1, "inp_tokens");
     g->pos = b.alloc(B200_TYPE_I32, n, 1, 1, "inp_pos");
     g->mask = b.alloc(B200_TYPE_F16, n_kv, n, 1, "kq_mask");
@@ -269,13 +268,13 @@ int build_graph(b200_llama *c, Graph *g, uint8_t *base, int64_t n, int64_t n_kv,
         ggml_tensor *fa = b.op(b.alloc(B200_TYPE_F32, HD, H, n, "kqv_out"), GGML_OP_FLASH_ATTN_EXT, q_fa, k_fa, v_fa, g->mask);
         memcpy(&fa->op_params[0], &kq_scale, 4);
         ggml_tensor *attn = b.mul_mat(wo, b.reshape_2d(fa, HD * H, n), "attn_out");
-        if (tp) g->collectives.push_back({(int)g->nodes.size(), attn, nullptr});   // partial sums over this rank's heads
+        if (tp) attn = b.tp_all_reduce(attn, "attn_out_sum");   // attn holds the partial sums over this rank's heads
         ggml_tensor *ffn_inp = b.binary(GGML_OP_ADD, attn, inp, "ffn_inp");
         cur = b.norm(ffn_inp, fn, hp.norm_rms_eps, "ffn_norm");
         ggml_tensor *gate = b.silu(b.mul_mat(wg, cur, "ffn_gate"));
         ggml_tensor *up = b.mul_mat(wu, cur, "ffn_up");
         ggml_tensor *down = b.mul_mat(wd, b.binary(GGML_OP_MUL, gate, up, "ffn_gate_par"), "ffn_out");
-        if (tp) g->collectives.push_back({(int)g->nodes.size(), down, nullptr});   // partial sums over this rank's FFN rows
+        if (tp) down = b.tp_all_reduce(down, "ffn_out_sum");   // down holds the partial sums over this rank's FFN rows
         inp = b.op(b.over(resid[(il + 1) & 1], "l_out"), GGML_OP_ADD, down, ffn_inp);
     }
     b.off = layer_base;
@@ -287,9 +286,8 @@ int build_graph(b200_llama *c, Graph *g, uint8_t *base, int64_t n, int64_t n_kv,
     cur = b.get_rows(cur, g->out_ids, "result_norm_rows");   // crates/llama/src/graph.rs:308-313 out_rows
     g->logits = b.mul_mat(ow, cur, "result_output");
     if (tp && ow != tok_embd) {   // this rank's vocabulary rows: gather the full row on every rank
-        ggml_tensor *full = b.alloc(B200_TYPE_F32, ow->ne[1] * c->tp_size, n_out, 1, "result_output_all");
-        g->collectives.push_back({(int)g->nodes.size(), g->logits, full});
-        g->logits = full;
+        ggml_tensor *staging = b.alloc(B200_TYPE_F32, ow->ne[1] * c->tp_size, n_out, 1, "result_output_staging");
+        g->logits = b.op(b.alloc(B200_TYPE_F32, ow->ne[1] * c->tp_size, n_out, 1, "result_output_all"), B200_OP_TP_ALL_GATHER, g->logits, staging);
     }
     g->argmax = b.op(b.alloc(B200_TYPE_I32, n_out, 1, 1, "argmax"), GGML_OP_ARGMAX, g->logits);
     g->bytes = b.high;
@@ -309,32 +307,14 @@ void set_input_async(ggml_backend_t be, ggml_tensor *t, const void *data, size_t
     else set_input(t, data, bytes);
 }
 
-// graph_compute over the first `total` nodes, cut where the ranks of a tensor-parallel group exchange data
+// graph_compute over the first `total` nodes: the whole step is one node list, the collectives of a tensor-parallel
+// group are nodes of it (B200_OP_TP_*), so the backend can capture and replay the step as one CUDA graph
 int run_graph(b200_llama *c, Graph *g, int total) {
-    int start = 0;
-    auto compute = [&](int end) -> int {
-        if (end <= start) return B200_STATUS_SUCCESS;
-        ggml_cgraph cg;
-        memset(&cg, 0, sizeof(cg));
-        cg.size = cg.n_nodes = end - start;
-        cg.nodes = g->nodes.data() + start;
-        start = end;
-        return c->backend->iface.graph_compute(c->backend, &cg);
-    };
-    for (const Graph::Collective &col : g->collectives) {
-        if (col.after > total) break;
-        int rc = compute(col.after);
-        if (rc != B200_STATUS_SUCCESS) return rc;
-        if (col.gather) {   // row by row: every rank's slice of a row lands side by side, which is the whole row
-            for (int64_t r = 0; r < col.t->ne[1] && rc == B200_STATUS_SUCCESS; r++)
-                rc = tp_all_gather(c->comm, (const float *)col.t->data + r * col.t->ne[0], (float *)col.gather->data + r * col.gather->ne[0],
-                                   (size_t)col.t->ne[0], c->stream);
-        } else {
-            rc = tp_all_reduce_sum(c->comm, (float *)col.t->data, (size_t)(col.t->nb[3] / 4), c->stream);
-        }
-        if (rc != B200_STATUS_SUCCESS) return rc;
-    }
-    return compute(total);
+    ggml_cgraph cg;
+    memset(&cg, 0, sizeof(cg));
+    cg.size = cg.n_nodes = total;
+    cg.nodes = g->nodes.data();
+    return c->backend->iface.graph_compute(c->backend, &cg);
 }
 
 }  // namespace
@@ -345,12 +325,31 @@ int b200_llama_new(const b200_llama_hparams *hp, int device, int32_t n_ctx, int3
     return b200_llama_new_tp(hp, device, n_ctx, n_batch, cpu_threads, 0, 1, nullptr, out);
 }
 
+static int llama_new_impl(const b200_llama_hparams *hp, int device, int32_t n_ctx, int32_t n_batch, int32_t cpu_threads, int32_t tp_rank,
+                          int32_t tp_size, const void *id128, b200_tp_hook_fn hook, void *hook_user, b200_llama **out);
+
 int b200_llama_new_tp(const b200_llama_hparams *hp, int device, int32_t n_ctx, int32_t n_batch, int32_t cpu_threads, int32_t tp_rank,
                       int32_t tp_size, const void *id128, b200_llama **out) {
+    return llama_new_impl(hp, device, n_ctx, n_batch, cpu_threads, tp_rank, tp_size, id128, nullptr, nullptr, out);
+}
+
+int b200_llama_new_tp_hook(const b200_llama_hparams *hp, int device, int32_t n_ctx, int32_t n_batch, int32_t cpu_threads, int32_t tp_rank,
+                           int32_t tp_size, b200_tp_hook_fn hook, void *user, b200_llama **out) {
+    B200_REQUIRE(hook != nullptr && tp_size >= 2, "llama_new_tp_hook: needs a hook and at least two ranks");
+    return llama_new_impl(hp, device, n_ctx, n_batch, cpu_threads, tp_rank, tp_size, nullptr, hook, user, out);
+}
+
+int b200_llama_tp_exchange_kind(const b200_llama *c) {
+    if (!c || !c->tp || c->tp->hook) return -1;
+    return c->tp->ll_ready ? 1 : 0;
+}
+
+static int llama_new_impl(const b200_llama_hparams *hp, int device, int32_t n_ctx, int32_t n_batch, int32_t cpu_threads, int32_t tp_rank,
+                          int32_t tp_size, const void *id128, b200_tp_hook_fn hook, void *hook_user, b200_llama **out) {
     B200_REQUIRE(hp != nullptr && out != nullptr, "llama_new: null argument");
     *out = nullptr;
     B200_REQUIRE(tp_size >= 1 && tp_rank >= 0 && tp_rank < tp_size, "llama_new: rank %d of %d", tp_rank, tp_size);
-    B200_REQUIRE(tp_size == 1 || id128 != nullptr, "llama_new: a tensor-parallel group needs the shared id");
+    B200_REQUIRE(tp_size == 1 || id128 != nullptr || hook != nullptr, "llama_new: a tensor-parallel group needs the shared id");
     B200_REQUIRE(hp->n_head % tp_size == 0 && hp->n_head_kv % tp_size == 0, "llama_new: %d / %d heads do not split %d ways", hp->n_head,
                  hp->n_head_kv, tp_size);
     B200_REQUIRE(hp->n_vocab > 0 && hp->n_embd > 0 && hp->n_head > 0 && hp->n_head_kv > 0 && hp->n_layer > 0 && hp->n_ff > 0,
@@ -404,9 +403,12 @@ int b200_llama_new_tp(const b200_llama_hparams *hp, int device, int32_t n_ctx, i
     c->cell_pos.assign(n_ctx, -1);
     c->cell_seq.assign(n_ctx, -1);
     if (tp_size > 1) {
-        B200_CUDA(cudaSetDevice(device));
-        int rc = tp_comm_init(tp_rank, tp_size, id128, &c->comm);
+        int rc = tp_group_create(tp_rank, tp_size, device, id128, hook, hook_user, &c->tp);
         if (rc != B200_STATUS_SUCCESS) { b200_llama_free(c.release()); return rc; }
+        typedef void (*set_tp_fn)(ggml_backend_t, void *);
+        set_tp_fn set_tp = (set_tp_fn)reg->iface.get_proc_address(reg, "b200_backend_set_tp");
+        if (!set_tp) { b200_llama_free(c.release()); B200_REQUIRE(false, "llama_new: the backend has no tensor-parallel entry"); }
+        set_tp(c->backend, c->tp);
     }
     *out = c.release();
     return B200_STATUS_SUCCESS;
@@ -421,7 +423,7 @@ void b200_llama_free(b200_llama *c) {
     for (auto &kv : c->weights)
         if (kv.second->buf) kv.second->buf->iface.free_buffer(kv.second->buf);
     if (c->backend) c->backend->iface.free(c->backend);
-    if (c->comm) tp_comm_destroy(c->comm);
+    if (c->tp) tp_group_destroy(c->tp);
     delete c;
 }
 

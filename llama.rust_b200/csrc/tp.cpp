@@ -18,12 +18,14 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
 
 #include "common.cuh"
 #include "llama_b200.h"
+#include "tp.h"
 
 using namespace b200;
 
@@ -104,7 +106,7 @@ int tp_split_kind(const char *name) {
     return 0;
 }
 
-int tp_comm_init(int rank, int size, const void *id128, void **comm) {
+static int tp_comm_init(int rank, int size, const void *id128, void **comm) {
     int rc = nccl_load();
     if (rc != B200_STATUS_SUCCESS) return rc;
     ncclUniqueId id;
@@ -115,16 +117,153 @@ int tp_comm_init(int rank, int size, const void *id128, void **comm) {
     *comm = c;
     return B200_STATUS_SUCCESS;
 }
-void tp_comm_destroy(void *comm) {
-    if (comm && g_nccl.CommDestroy) g_nccl.CommDestroy((ncclComm_t)comm);
+
+// B200_TP_LL=0 keeps every collective on NCCL (for side-by-side measurements); read once
+static bool tp_ll_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_TP_LL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
 }
-int tp_all_reduce_sum(void *comm, float *buf, size_t count, void *stream) {
-    B200_NCCL(g_nccl.AllReduce(buf, buf, count, ncclFloat, ncclSum, (ncclComm_t)comm, (cudaStream_t)stream));
+
+// The exchange buffers of the single-kernel collectives: every rank allocates one receive buffer with cudaMalloc,
+// hands its IPC handle round through an NCCL all-gather, and maps every peer's buffer (one process per GPU).
+// Whether the group uses them is decided together: one rank that could not map a peer sends everybody to NCCL.
+static int tp_exchange_setup(TpGroup *g) {
+    const size_t words = (size_t)TP_LL_SLOTS * g->size * (size_t)TP_LL_MAX_ELEMS;
+    const size_t bytes = words * 8 + 256;
+    int ok = 1;
+    if (!tp_ll_enabled() || cudaMalloc(&g->ll_alloc, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        g->ll_alloc = nullptr;
+        ok = 0;
+    }
+    cudaIpcMemHandle_t mine;
+    memset(&mine, 0, sizeof(mine));
+    if (ok && (cudaMemset(g->ll_alloc, 0, bytes) != cudaSuccess || cudaIpcGetMemHandle(&mine, g->ll_alloc) != cudaSuccess)) {
+        cudaGetLastError();
+        ok = 0;
+    }
+    // handles (64 bytes each) and the ranks' verdicts travel through the communicator
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "cudaIpcMemHandle_t is 64 bytes");
+    uint8_t *dev = nullptr;
+    B200_CUDA(cudaMalloc((void **)&dev, (size_t)64 * g->size + 64));
+    int *dev_ok = (int *)(dev + (size_t)64 * g->size);
+    B200_CUDA(cudaMemcpy(dev + (size_t)64 * g->rank, &mine, 64, cudaMemcpyHostToDevice));
+    cudaStream_t s = nullptr;
+    auto gather_handles = [&]() -> int {
+        B200_NCCL(g_nccl.AllGather(dev + (size_t)64 * g->rank, dev, 64, ncclChar, (ncclComm_t)g->comm, s));
+        B200_CUDA(cudaStreamSynchronize(s));
+        return B200_STATUS_SUCCESS;
+    };
+    int rc = gather_handles();
+    if (rc != B200_STATUS_SUCCESS) { cudaFree(dev); return rc; }
+    std::string handles((size_t)64 * g->size, '\0');
+    B200_CUDA(cudaMemcpy(&handles[0], dev, handles.size(), cudaMemcpyDeviceToHost));
+    for (int r = 0; r < g->size && ok; r++) {
+        if (r == g->rank) { g->peer_mapped[r] = nullptr; continue; }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, &handles[(size_t)64 * r], 64);
+        void *p = nullptr;
+        if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            cudaGetLastError();
+            ok = 0;
+        } else {
+            g->peer_mapped[r] = p;
+        }
+    }
+    B200_CUDA(cudaMemcpy(dev_ok, &ok, sizeof(int), cudaMemcpyHostToDevice));
+    auto agree = [&]() -> int {
+        B200_NCCL(g_nccl.AllReduce(dev_ok, dev_ok, 1, ncclInt, ncclMin, (ncclComm_t)g->comm, s));
+        B200_CUDA(cudaStreamSynchronize(s));
+        return B200_STATUS_SUCCESS;
+    };
+    rc = agree();
+    if (rc != B200_STATUS_SUCCESS) { cudaFree(dev); return rc; }
+    int all_ok = 0;
+    B200_CUDA(cudaMemcpy(&all_ok, dev_ok, sizeof(int), cudaMemcpyDeviceToHost));
+    cudaFree(dev);
+    g->ll_ready = all_ok == 1;
+    if (!g->ll_ready) return B200_STATUS_SUCCESS;   // NCCL serves every collective
+    TpExchange &x = g->x;
+    x.rank = g->rank;
+    x.size = g->size;
+    x.recv = (unsigned long long *)g->ll_alloc;
+    for (int r = 0; r < g->size; r++) x.peer[r] = r == g->rank ? x.recv : (unsigned long long *)g->peer_mapped[r];
+    x.seq = (unsigned *)((uint8_t *)g->ll_alloc + words * 8);
+    x.done = x.seq + 1;
+    return device_error_word(&x.err);
+}
+
+int tp_group_create(int rank, int size, int device, const void *id128, b200_tp_hook_fn hook, void *hook_user, TpGroup **out) {
+    *out = nullptr;
+    B200_REQUIRE(size >= 2 && size <= TP_MAX_RANKS && rank >= 0 && rank < size, "tensor parallel: rank %d of %d (2 to %d ranks)", rank, size,
+                 TP_MAX_RANKS);
+    B200_REQUIRE(hook != nullptr || id128 != nullptr, "tensor parallel: a group needs the shared id (or an exchange hook)");
+    B200_CUDA(cudaSetDevice(device));
+    TpGroup *g = new TpGroup();
+    g->rank = rank;
+    g->size = size;
+    g->device = device;
+    g->hook = hook;
+    g->hook_user = hook_user;
+    if (!hook) {
+        int rc = tp_comm_init(rank, size, id128, &g->comm);
+        if (rc == B200_STATUS_SUCCESS) rc = tp_exchange_setup(g);
+        if (rc != B200_STATUS_SUCCESS) { tp_group_destroy(g); return rc; }
+    }
+    *out = g;
     return B200_STATUS_SUCCESS;
 }
-int tp_all_gather(void *comm, const float *send, float *recv, size_t count_per_rank, void *stream) {
-    B200_NCCL(g_nccl.AllGather(send, recv, count_per_rank, ncclFloat, (ncclComm_t)comm, (cudaStream_t)stream));
+
+void tp_group_destroy(TpGroup *g) {
+    if (!g) return;
+    cudaSetDevice(g->device);
+    cudaDeviceSynchronize();
+    for (int r = 0; r < TP_MAX_RANKS; r++)
+        if (g->peer_mapped[r]) cudaIpcCloseMemHandle(g->peer_mapped[r]);
+    if (g->comm && g_nccl.CommDestroy) g_nccl.CommDestroy((ncclComm_t)g->comm);   // peers may still be writing until here
+    if (g->ll_alloc) cudaFree(g->ll_alloc);
+    cudaGetLastError();
+    delete g;
+}
+
+int tp_all_reduce(TpGroup *g, float *buf, int64_t count, cudaStream_t s, bool *capturable) {
+    B200_REQUIRE(g != nullptr, "tensor parallel: no group attached to this backend");
+    if (count == 0) return B200_STATUS_SUCCESS;
+    if (g->hook) {
+        if (capturable) *capturable = false;
+        B200_CUDA(cudaStreamSynchronize(s));
+        const int rc = g->hook(g->hook_user, 0, g->rank, g->size, buf, count, nullptr, 0, 0);
+        B200_REQUIRE(rc == 0, "tensor parallel: the exchange hook failed (%d)", rc);
+        return B200_STATUS_SUCCESS;
+    }
+    if (g->ll_ready && count <= TP_LL_MAX_ELEMS) return launch_tp_ll_all_reduce(g->x, buf, count, g->spin_limit, s);
+    B200_NCCL(g_nccl.AllReduce(buf, buf, (size_t)count, ncclFloat, ncclSum, (ncclComm_t)g->comm, s));
     return B200_STATUS_SUCCESS;
+}
+
+int tp_all_gather_rows(TpGroup *g, const float *send, float *dst, int64_t n_local, int64_t rows, float *staging, cudaStream_t s,
+                       bool *capturable) {
+    B200_REQUIRE(g != nullptr, "tensor parallel: no group attached to this backend");
+    if (n_local * rows == 0) return B200_STATUS_SUCCESS;
+    if (g->hook) {
+        if (capturable) *capturable = false;
+        B200_CUDA(cudaStreamSynchronize(s));
+        const int rc = g->hook(g->hook_user, 1, g->rank, g->size, const_cast<float *>(send), n_local * rows, dst, n_local, rows);
+        B200_REQUIRE(rc == 0, "tensor parallel: the exchange hook failed (%d)", rc);
+        return B200_STATUS_SUCCESS;
+    }
+    if (g->ll_ready && n_local * rows <= TP_LL_MAX_ELEMS) return launch_tp_ll_all_gather(g->x, send, dst, n_local, rows, g->spin_limit, s);
+    if (rows == 1) {   // the ranks' slices side by side are the whole row
+        B200_NCCL(g_nccl.AllGather(send, dst, (size_t)n_local, ncclFloat, (ncclComm_t)g->comm, s));
+        return B200_STATUS_SUCCESS;
+    }
+    B200_REQUIRE(staging != nullptr, "tensor parallel: all-gather of %lld rows needs a staging block", (long long)rows);
+    B200_NCCL(g_nccl.AllGather(send, staging, (size_t)(n_local * rows), ncclFloat, (ncclComm_t)g->comm, s));
+    return launch_tp_reorder_gathered(staging, dst, n_local, rows, g->size, s);
 }
 
 }  // namespace b200

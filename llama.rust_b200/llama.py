@@ -27,6 +27,9 @@ lib.b200_llama_kv_used.argtypes = [vp]
 lib.b200_llama_kv_used.restype = i32
 lib.b200_llama_replay.argtypes = [vp, i32, C.POINTER(C.c_float)]
 lib.b200_llama_new_tp.argtypes = [C.POINTER(HParams), i32, i32, i32, i32, i32, i32, vp, C.POINTER(vp)]
+TP_HOOK = C.CFUNCTYPE(C.c_int, vp, C.c_int, C.c_int, C.c_int, vp, i64, vp, i64, i64)
+lib.b200_llama_new_tp_hook.argtypes = [C.POINTER(HParams), i32, i32, i32, i32, i32, i32, TP_HOOK, vp, C.POINTER(vp)]
+lib.b200_llama_tp_exchange_kind.argtypes = [vp]
 lib.b200_tp_unique_id.argtypes = [vp]
 lib.b200_tp_shard_shape.argtypes = [C.c_char_p, i32, i64, i64, i32, C.POINTER(i32), C.POINTER(i64), C.POINTER(i64)]
 lib.b200_tp_shard_tensor.argtypes = [C.c_char_p, i32, i64, i64, vp, i32, i32, vp, sz]
@@ -96,11 +99,18 @@ def tp_shard_tensor(name, ty, blocks, ne0, ne1, tp_rank, tp_size):
 
 
 class Llama:
-    def __init__(self, hp, n_ctx, n_batch, device=0, cpu_threads=8, tp_rank=0, tp_size=1, tp_id=None):
+    def __init__(self, hp, n_ctx, n_batch, device=0, cpu_threads=8, tp_rank=0, tp_size=1, tp_id=None, tp_hook=None):
+        """tp_hook(kind, rank, size, dev_buf, count, dev_dst, n_local, rows) -> 0: a tensor-parallel rank whose
+        collectives the host carries out (b200_llama_new_tp_hook), for tests that play several ranks on one GPU"""
         self.hp = dict(hp)
         h = HParams(**self.hp)
         p = vp()
-        if tp_size > 1:
+        if tp_size > 1 and tp_hook is not None:
+            self._hook = TP_HOOK(lambda user, kind, rank, size, buf, count, dst, n_local, rows:
+                                 int(tp_hook(kind, rank, size, buf, count, dst, n_local, rows)))
+            check(lib.b200_llama_new_tp_hook(C.byref(h), device, n_ctx, n_batch, cpu_threads, tp_rank, tp_size, self._hook, None, C.byref(p)),
+                  "llama_new_tp_hook")
+        elif tp_size > 1:
             idbuf = (C.c_uint8 * 128).from_buffer_copy(tp_id)
             check(lib.b200_llama_new_tp(C.byref(h), device, n_ctx, n_batch, cpu_threads, tp_rank, tp_size, idbuf, C.byref(p)), "llama_new_tp")
         else:
@@ -140,6 +150,10 @@ class Llama:
                                          out_rows.ctypes.data, out_rows.size, out.ctypes.data if logits else None,
                                          am.ctypes.data if argmax else None), "llama_decode_seqs")
         return out, am
+
+    def tp_exchange_kind(self):
+        """1: the library's single-kernel exchange over peer memory, 0: NCCL, -1: not tensor parallel (or a hook)"""
+        return lib.b200_llama_tp_exchange_kind(self.ptr)
 
     def kv_clear(self):
         check(lib.b200_llama_kv_clear(self.ptr), "kv_clear")

@@ -226,9 +226,54 @@ static int llama_mm(int type, int64_t N, int64_t K, int64_t M, const void *W, co
 
 // tokens / pos: [n_tok]; row_idx: [n_tok] cache cells to write; mask: F16 [n_tok][n_kv];
 // out_ids: [n_out] token rows whose logits are wanted; logits: [n_out][n_vocab].
+// Row-split tensor parallelism, restated on one host: attn_output and ffn_down are cut along K into tp slices on
+// 256-element boundaries; slice r multiplies the matching columns of the activations (its own Q8 blocks: the cut
+// is block-aligned, so they are the blocks the unsplit row would have), and the tp partial results are added in
+// rank order, ((p0 + p1) + p2) + ..., each add rounded to f32.  Every other mat-mul is split by rows, which
+// changes no output element.  partials, if given, receives the tp partial results [tp][M][N] before the sum.
+static int llama_mm_ksplit(int type, int64_t N, int64_t K, int64_t M, const void *W, const float *X, float *out, int n_threads, int tp,
+                           float *partials) {
+    const size_t rb = orc_row_size(type, K);
+    if (tp < 1 || K % tp != 0 || rb % (size_t)tp != 0 || (K / tp) % 256 != 0) return -1;
+    const int64_t Ks = K / tp;
+    const size_t srb = rb / (size_t)tp;
+    std::vector<uint8_t> ws(srb * (size_t)N);
+    std::vector<float> xs((size_t)M * Ks), part((size_t)M * N);
+    for (int r = 0; r < tp; r++) {
+        for (int64_t n = 0; n < N; n++) std::memcpy(ws.data() + (size_t)n * srb, (const uint8_t *)W + (size_t)n * rb + (size_t)r * srb, srb);
+        for (int64_t i = 0; i < M; i++) std::memcpy(xs.data() + (size_t)i * Ks, X + (size_t)i * K + (size_t)r * Ks, (size_t)Ks * 4);
+        if (orc_mul_mat(type, N, Ks, M, ws.data(), xs.data(), part.data(), ORC_ROUTE_AUTO, n_threads) < 0) return -1;
+        if (partials) std::memcpy(partials + (size_t)r * M * N, part.data(), (size_t)M * N * 4);
+        if (r == 0) std::memcpy(out, part.data(), (size_t)M * N * 4);
+        else orc_add(out, part.data(), out, N, M, N, M);
+    }
+    return 1;
+}
+
+static int llama_forward_impl(const OrcLlamaModel *m, const int32_t *tokens, const int32_t *pos, int64_t n_tok, int64_t n_kv,
+                              const uint16_t *mask, const int64_t *row_idx, const int32_t *out_ids, int64_t n_out, float *logits,
+                              int n_threads, int wide_silu, int keep_repacked, int tp, float *attn_partials0, float *ffn_partials0);
+
 int orc_llama_forward(const OrcLlamaModel *m, const int32_t *tokens, const int32_t *pos, int64_t n_tok, int64_t n_kv,
                       const uint16_t *mask, const int64_t *row_idx, const int32_t *out_ids, int64_t n_out, float *logits,
                       int n_threads, int wide_silu, int keep_repacked) {
+    return llama_forward_impl(m, tokens, pos, n_tok, n_kv, mask, row_idx, out_ids, n_out, logits, n_threads, wide_silu, keep_repacked, 1,
+                              nullptr, nullptr);
+}
+
+// The same forward pass as a group of tp tensor-parallel ranks computes it (see llama_mm_ksplit).  attn_partials0 /
+// ffn_partials0, if given, receive layer 0's per-rank partial results of attn_output / ffn_down, [tp][n_tok][n_embd].
+int orc_llama_forward_tp(const OrcLlamaModel *m, const int32_t *tokens, const int32_t *pos, int64_t n_tok, int64_t n_kv,
+                         const uint16_t *mask, const int64_t *row_idx, const int32_t *out_ids, int64_t n_out, float *logits,
+                         int n_threads, int wide_silu, int tp, float *attn_partials0, float *ffn_partials0) {
+    if (tp < 1 || m->n_head % tp || m->n_head_kv % tp || m->n_ff % tp) return -7;
+    return llama_forward_impl(m, tokens, pos, n_tok, n_kv, mask, row_idx, out_ids, n_out, logits, n_threads, wide_silu, 0, tp,
+                              attn_partials0, ffn_partials0);
+}
+
+static int llama_forward_impl(const OrcLlamaModel *m, const int32_t *tokens, const int32_t *pos, int64_t n_tok, int64_t n_kv,
+                              const uint16_t *mask, const int64_t *row_idx, const int32_t *out_ids, int64_t n_out, float *logits,
+                              int n_threads, int wide_silu, int keep_repacked, int tp, float *attn_partials0, float *ffn_partials0) {
     const int64_t E = m->n_embd, HD = m->head_dim, H = m->n_head, HK = m->n_head_kv, FF = m->n_ff, T = n_tok;
     const int64_t EK = HK * HD;
     std::vector<float> inp(T * E), cur(T * E), q(T * H * HD), k(T * EK), v(T * EK), qr(T * H * HD), kr(T * EK);
@@ -259,7 +304,9 @@ int orc_llama_forward(const OrcLlamaModel *m, const int32_t *tokens, const int32
         fa.dst = att.data();
         fa.mode = 0; fa.n_chunks = n_threads; fa.n_threads = n_threads;
         if (orc_flash_attn_ext(&fa) <= 0) return -5;
-        if (llama_mm(L.to, E, H * HD, T, L.wo, att.data(), proj.data(), n_threads, keep_repacked) < 0) return -2;
+        if (tp > 1) {
+            if (llama_mm_ksplit(L.to, E, H * HD, T, L.wo, att.data(), proj.data(), n_threads, tp, il == 0 ? attn_partials0 : nullptr) < 0) return -2;
+        } else if (llama_mm(L.to, E, H * HD, T, L.wo, att.data(), proj.data(), n_threads, keep_repacked) < 0) return -2;
         orc_add(proj.data(), inp.data(), ffn_inp.data(), E, T, E, T);
         orc_rms_norm(ffn_inp.data(), cur.data(), E, T, m->norm_eps);
         orc_mul(cur.data(), L.ffn_norm, cur.data(), E, T, E, 1);
@@ -267,7 +314,9 @@ int orc_llama_forward(const OrcLlamaModel *m, const int32_t *tokens, const int32
         if (llama_mm(L.tu, FF, E, T, L.up, cur.data(), u.data(), n_threads, keep_repacked) < 0) return -2;
         orc_silu(g.data(), g.data(), FF, T, wide_silu);
         orc_mul(g.data(), u.data(), g.data(), FF, T, FF, T);
-        if (llama_mm(L.td, E, FF, T, L.down, g.data(), proj.data(), n_threads, keep_repacked) < 0) return -2;
+        if (tp > 1) {
+            if (llama_mm_ksplit(L.td, E, FF, T, L.down, g.data(), proj.data(), n_threads, tp, il == 0 ? ffn_partials0 : nullptr) < 0) return -2;
+        } else if (llama_mm(L.td, E, FF, T, L.down, g.data(), proj.data(), n_threads, keep_repacked) < 0) return -2;
         orc_add(proj.data(), ffn_inp.data(), inp.data(), E, T, E, T);
     }
     orc_rms_norm(inp.data(), cur.data(), E, T, m->norm_eps);

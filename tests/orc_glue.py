@@ -26,6 +26,7 @@ def L():
         lib.orc_argmax.argtypes = [vp, i64]
         lib.orc_argmax.restype = i32
         lib.orc_llama_forward.argtypes = [vp, vp, vp, i64, i64, vp, vp, vp, i64, vp, i32, i32, i32]
+        lib.orc_llama_forward_tp.argtypes = [vp, vp, vp, i64, i64, vp, vp, vp, i64, vp, i32, i32, i32, vp, vp]
         _ready = True
     return lib
 
@@ -175,3 +176,21 @@ class Llama:
                                    int(wide_silu), int(keep_repacked))
         assert rc == 0, f"orc_llama_forward failed ({rc})"
         return logits
+
+    def forward_tp(self, tokens, pos, n_kv, mask, row_idx, out_ids, tp, n_threads=8, wide_silu=True, partials=False):
+        """The forward pass as tp tensor-parallel ranks compute it: attn_output and ffn_down cut along K, the
+        partial results added in rank order.  With partials=True also returns layer 0's per-rank partial results
+        of attn_output and ffn_down, each [tp, n_tok, n_embd]."""
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        pos = np.ascontiguousarray(pos, dtype=np.int32)
+        mask = np.ascontiguousarray(mask, dtype=np.uint16)
+        row_idx = np.ascontiguousarray(row_idx, dtype=np.int64)
+        out_ids = np.ascontiguousarray(out_ids, dtype=np.int32)
+        logits = np.empty((out_ids.size, self.hp["n_vocab"]), dtype=np.float32)
+        pa = np.zeros((tp, tokens.size, self.hp["n_embd"]), dtype=np.float32) if partials else None
+        pf = np.zeros((tp, tokens.size, self.hp["n_embd"]), dtype=np.float32) if partials else None
+        rc = L().orc_llama_forward_tp(C.byref(self.m), tokens.ctypes.data, pos.ctypes.data, tokens.size, n_kv, mask.ctypes.data,
+                                      row_idx.ctypes.data, out_ids.ctypes.data, out_ids.size, logits.ctypes.data, n_threads,
+                                      int(wide_silu), tp, pa.ctypes.data if partials else None, pf.ctypes.data if partials else None)
+        assert rc == 0, f"orc_llama_forward_tp failed ({rc})"
+        return (logits, pa, pf) if partials else logits

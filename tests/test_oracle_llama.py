@@ -110,3 +110,25 @@ def test_prompt_plus_steps_tracks_one_batch():
     whole = oracle_logits(orc_glue.Llama(HP, q, 256), tokens)
     stepped = oracle_logits(orc_glue.Llama(HP, q, 256), tokens, split=6)
     assert np.abs(whole - stepped).max() / np.abs(whole).max() < 2e-2
+
+
+def test_tensor_parallel_forward_restatement():
+    """orc_llama_forward_tp: with one rank it is the plain forward bit for bit; with two or four ranks the K-split
+    partial results of layer 0 add up, in rank order, to what the layer then uses, and the logits stay within the
+    activation-quantization noise of the unsplit model (a last-bit change of a partial sum can flip a Q8 rounding
+    in the next layer)."""
+    hp = dict(HP, n_embd=1024, n_head=16, n_head_kv=4, n_ff=1024)   # a quarter of the heads / FFN rows is 256 columns
+    q, _ = make(hp, 4)
+    tokens = np.random.default_rng(5).integers(0, hp["n_vocab"], 7).astype(np.int32)
+    n = len(tokens)
+    mask = np.full((n, 256), 0xFC00, dtype=np.uint16)
+    for i in range(n):
+        mask[i, :i + 1] = 0
+    args = (tokens, np.arange(n), 256, mask, np.arange(n), np.arange(n))
+    plain = orc_glue.Llama(hp, q, 256).forward(*args, n_threads=4)
+    one = orc_glue.Llama(hp, q, 256).forward_tp(*args, tp=1, n_threads=4)
+    assert np.array_equal(plain.view(np.uint32), one.view(np.uint32))
+    for tp in (2, 4):
+        logits, pa, pf = orc_glue.Llama(hp, q, 256).forward_tp(*args, tp=tp, n_threads=4, partials=True)
+        assert np.abs(logits - plain).max() / np.abs(plain).max() < 5e-2
+        assert pa.shape == (tp, n, hp["n_embd"]) and np.abs(pa).max() > 0 and np.abs(pf).max() > 0
