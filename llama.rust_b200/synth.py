@@ -7,7 +7,8 @@ matrices repeat `period` distinct rows.  (Tests that compare values quantize rea
 CPU oracle instead.)"""
 import numpy as np
 
-from . import F32, MXFP4, Q4_0, Q4_K, Q6_K, Q8_0
+# ggml type ids (this module imports nothing of the package at load time: a CPU-only process can load it by path)
+F32, Q4_0, Q8_0, Q4_K, Q6_K, MXFP4 = 0, 2, 8, 12, 14, 39
 
 BLOCK = {Q4_K: (256, 144), Q6_K: (256, 210), Q8_0: (32, 34), Q4_0: (32, 18), MXFP4: (32, 17)}
 
@@ -43,9 +44,10 @@ def blocks(ty, rows, ne0, seed=0, period=4096):
     return np.ascontiguousarray(q)
 
 
-def llama_tensors(hp, type_of, seed=0, period=4096):
+def llama_tensors(hp, type_of, seed=0, period=4096, tensor_shapes=None):
     """yields (name, type, array, ne0, ne1) for every tensor of a llama-architecture model"""
-    from .llama import tensor_shapes
+    if tensor_shapes is None:
+        from .shapes import tensor_shapes
     rng = np.random.default_rng(seed)
     for i, (name, (ne0, ne1)) in enumerate(tensor_shapes(hp).items()):
         ty = type_of(name)
