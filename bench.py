@@ -617,8 +617,9 @@ def case_gemv(args):
     e1.record()
     e1.synchronize()
     us = e0.elapsed_ms(e1) * 1e3 / args.launches
-    print(json.dumps({"case": f"gemv {args.only}", "copies": copies, "launches": args.launches, "us_per_launch": us,
-                      "gbs": algorithmic_bytes(n, k) / us / 1e3}), flush=True)
+    us_graph = b.bench_mul_mat_q8(weights, act, b.ACT_Q8_K, do, 1, args.launches)
+    print(json.dumps({"case": f"gemv {args.only}", "copies": copies, "launches": args.launches, "us_per_launch_host_loop": us,
+                      "us_per_launch": us_graph, "gbs": algorithmic_bytes(n, k) / us_graph / 1e3}), flush=True)
 
 
 def case_gemm(args):

@@ -66,15 +66,25 @@ int b200_set_device(int device);
 int b200_device_info(int device, char *name, size_t name_len, size_t *free_bytes, size_t *total_bytes,
                      int *sm_count, int *cc_major, int *cc_minor);
 int b200_synchronize(void *stream);
+/* Numerics policy.  B200_NUMERICS_EXACT: every kernel reproduces, bit for bit, the arithmetic of the CPU route the
+ * reference takes for the op (activation blocks, integer block dots, the f32 chains in their order, the f16
+ * attention accumulator).  B200_NUMERICS_FAST (the start value unless the environment says B200_NUMERICS=exact):
+ * ops for which a tolerance-mode kernel exists use it, within the tolerances asked of this path (1e-5 of
+ * sum |w x| per mat-mul output, 1e-3 for F16-KV attention); the others stay exact.  Process-wide; takes effect at the
+ * next call.  (The reference's own routes for one op differ by about 1e-6: crates/llama/tests/gpt_oss_e2e.rs:63-64.) */
+enum b200_numerics { B200_NUMERICS_EXACT = 0, B200_NUMERICS_FAST = 1 };
+void b200_set_numerics(int mode);
+int b200_get_numerics(void);
 /* Kernels that wait on barriers bound every wait; a wait that ran out records a non-zero code on the
  * device instead of hanging it.  Reads and clears that code for the current device (0 = none).
  * (Failure reporting of the kind ggml_backend_i.synchronize surfaces: crates/ggml/src/backend.rs:761-765.) */
 int b200_kernel_error(int *code);
 /* Test hooks (no counterpart in the reference).  b200_debug_alloc_count: device allocations the library has made
- * for its own scratch blocks so far in this process.  b200_debug_stream_wait: the next launches of the streaming
- * decode kernel poll each wait at most spin_limit times (0 = the normal limit) and their producer leaves ring unit
- * skip_unit unfilled (-1 = none), so that a test can watch a bounded wait run out: the kernel returns, its output
- * rows stay unwritten and b200_kernel_error reports code 1 (producer) or 2 (consumer). */
+ * for its own scratch blocks so far in this process.  b200_debug_stream_wait: while spin_limit > 0, one-row Q4_K
+ * mat-muls of few row tiles take the bulk-copy streaming kernel (selectable otherwise with B200_GEMV_STREAM=1),
+ * its waits poll at most spin_limit times, and its producer leaves ring unit skip_unit unfilled (-1 = none), so
+ * that a test can watch a bounded wait run out: the kernel returns, its output rows stay unwritten and
+ * b200_kernel_error reports code 1 (producer) or 2 (consumer).  spin_limit 0 disarms the hook. */
 unsigned long long b200_debug_alloc_count(void);
 void b200_debug_stream_wait(int spin_limit, int skip_unit);
 /* Which kernel a Q4_K prompt mat-mul (8x8 gemm route, n weight rows, m >= 32 activation rows) takes on a GPU with
@@ -144,12 +154,43 @@ int b200_mul_mat_q8(int type, int64_t n, int64_t k, int64_t m, const void *dev_w
  * (crates/llama/src/graph_arch.rs:209,226; crates/ggml/src/compute.rs:1174) without a second kernel. */
 int b200_mul_mat_q8_add(int type, int64_t n, int64_t k, const void *dev_w, const void *dev_act, int act_kind, float *dev_dst,
                         const float *dev_addend, float *dev_sum, int route, void *stream);
+/* Measurement helper (no counterpart in the reference): `reps` launches of b200_mul_mat_q8 over n_w rotating copies
+ * of the weights (so that they come from HBM, not L2), captured into one CUDA graph and replayed, timed with events
+ * on the launching stream.  This is what the kernel costs inside a decode step, where a replayed graph issues the
+ * launches back to back; a host loop over b200_mul_mat_q8 measures the host's launch rate for small matrices. */
+int b200_bench_mul_mat_q8(int type, int64_t n, int64_t k, int64_t m, const void *const *dev_w, int n_w, const void *dev_act,
+                          int act_kind, float *dev_dst, int reps, float *us_per_launch);
 /* b200_mul_mat_q8 for one activation row against up to three Q4_K matrices of the same k in one launch
  * (dev_dst[i][n[i]] = W_i x): the k / v / q mat-muls of an attention block and the gate / up mat-muls of an
  * FFN read the same normed row (crates/llama/src/graph_arch.rs:171-190,1137-1151), and at one token each of
  * them is a few microseconds of launch latency.  Every n[i] must take the 8x8 gemv route (a multiple of 8). */
 int b200_mul_mat_q8_multi(int type, int64_t k, int count, const int64_t *n, const void *const *dev_w, const void *dev_act,
                           int act_kind, float *const *dev_dst, void *stream);
+/* One-row Q4_K mat-mul(s) with the f32 op in front of them and the Q8_K quantization of its result run inside the
+ * mat-mul kernel (at one token each of those ops is a launch of a few microseconds for a few KB of work):
+ *   B200_ACT_PRO_PLAIN  act = q8_K(x)                          — a mat-mul whose activations are not quantized yet
+ *   B200_ACT_PRO_NORM   y = x * rms_scale(x, eps); y_mul = y * w; act = q8_K(y_mul)
+ *                       — RMS_NORM + MUL in front of q/k/v and gate/up (crates/llama/src/graph_arch.rs:1119-1122)
+ *   B200_ACT_PRO_SILU   y = silu(x); y_mul = y * w; act = q8_K(y_mul)
+ *                       — SILU + MUL in front of ffn_down (crates/llama/src/graph_arch.rs:1137-1151); wide as in b200_silu
+ * Element for element the arithmetic is that of b200_rms_norm / b200_silu, quantize_row_q8_K and b200_mul_mat_q8
+ * (bit-identical results); y (may be null) and y_mul are written as the separate ops would write them, and
+ * dev_act_out (may be null; b200_act_scratch_nbytes(1, k) bytes) receives the quantized row for later mat-muls.
+ * Up to three matrices of the same k share the launch (dev_dst[i][n[i]]); with one matrix, dev_sum[n] (if given)
+ * receives dst + dev_addend, the residual ADD that follows attn_output and ffn_down. */
+enum { B200_ACT_PRO_PLAIN = 1, B200_ACT_PRO_NORM = 2, B200_ACT_PRO_SILU = 3 };
+struct b200_act_prologue {
+    int mode;
+    const float *x;
+    const float *w;
+    float eps;
+    int wide;
+    float *y;
+    float *y_mul;
+    void *dev_act_out;
+};
+int b200_mul_mat_row_fused(int type, int64_t k, int count, const int64_t *n, const void *const *dev_w, float *const *dev_dst,
+                           const struct b200_act_prologue *pro, const float *dev_addend, float *dev_sum, void *stream);
 /* same op with host activations / results: copies X in, runs, copies dst out */
 int b200_mul_mat_host(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, const float *host_x,
                       float *host_dst, int route, void *stream);
@@ -192,9 +233,10 @@ int b200_mul_mat_id(int type, int64_t n, int64_t k, int64_t n_expert, int64_t ne
  * The CPU result for one query row over >= 512 positions depends on the CPU
  * thread count (split-KV, flash_attn.rs:841-859): n_chunks names the thread
  * count to reproduce (0 = 8, the count the reference's benchmark scripts use).
- * mode 0 reproduces the CPU arithmetic (f16 accumulator order and all);
- * mode 1 is the fast path with f32 accumulation (more accurate than the CPU,
- * not bit-comparable to it). */
+ * mode 0 follows the library's numerics policy (b200_set_numerics); mode 2 reproduces the CPU arithmetic
+ * (f16 accumulator order and all); mode 1 is the fast path with f32 accumulation (more accurate than the
+ * CPU, not bit-comparable to it; shapes it does not cover — sinks, ALiBi, softcap, dk != dv — take the
+ * exact kernels). */
 struct b200_flash_attn_args {
     int64_t dk, dv, n_tok, n_head, n_head_kv, n_kv;
     const float *q;      int64_t q_nb1, q_nb2;     /* bytes per token, per head */

@@ -69,6 +69,9 @@ def _load():
     L.b200_mul_mat_host.argtypes = [i32, i64, i64, i64, vp, vp, vp, i32, vp]
     L.b200_mul_mat_id.argtypes = [i32, i64, i64, i64, i64, i64, i64, vp, vp, vp, vp, i32, vp]
     L.b200_flash_attn_ext.argtypes = [vp, vp]
+    L.b200_bench_mul_mat_q8.argtypes = [i32, i64, i64, i64, C.POINTER(vp), i32, vp, i32, vp, i32, C.POINTER(C.c_float)]
+    L.b200_set_numerics.argtypes = [i32]
+    L.b200_set_numerics.restype = None
     L.b200_debug_alloc_count.restype = C.c_ulonglong
     L.b200_debug_stream_wait.argtypes = [i32, i32]
     L.b200_debug_stream_wait.restype = None
@@ -93,6 +96,18 @@ def set_device(i):
 
 def synchronize(stream=None):
     check(lib.b200_synchronize(stream), "synchronize")
+
+
+EXACT, FAST = 0, 1
+
+
+def set_numerics(mode):
+    """EXACT: bit-exact reproduction of the CPU routes; FAST: tolerance-mode kernels where they exist"""
+    lib.b200_set_numerics(mode)
+
+
+def get_numerics():
+    return lib.b200_get_numerics()
 
 
 def kernel_error():
@@ -203,6 +218,15 @@ def mul_mat_device(w, dx, m, ddst, route=ROUTE_AUTO, stream=None):
     xp = dx.ptr if isinstance(dx, DeviceBuffer) else dx
     dp = ddst.ptr if isinstance(ddst, DeviceBuffer) else ddst
     check(lib.b200_mul_mat(w.ty, w.n_rows, w.k, m, w.ptr, xp, w.k, dp, w.n_rows, route, stream), "mul_mat")
+
+
+def bench_mul_mat_q8(weights, act, act_kind, dst, m=1, reps=200):
+    """event-timed microseconds per launch of b200_mul_mat_q8 over the given Weight copies, replayed as one CUDA graph"""
+    arr = (C.c_void_p * len(weights))(*[w.ptr for w in weights])
+    us = C.c_float(0)
+    w = weights[0]
+    check(lib.b200_bench_mul_mat_q8(w.ty, w.n_rows, w.k, m, arr, len(weights), act.ptr, act_kind, dst.ptr, reps, C.byref(us)), "bench_mul_mat_q8")
+    return us.value
 
 
 class Event:

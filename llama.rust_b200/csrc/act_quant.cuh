@@ -112,4 +112,40 @@ __device__ __forceinline__ void q8_K_block_store_warp(const float (&v)[8], const
     if (lane == 0) out.d[row * nb + blk] = d;
 }
 
+// quantize_row_q8_K (the plain rule) on the block a warp holds in registers, lane l: elements 8 l .. 8 l + 7.  Returns
+// the lane's eight quants packed in element order, the block scale d, and the sum of the lane's eight quants (two
+// lanes make one of the block's 16-element sums).  Same values as q8_K_block_store_warp<false>.
+__device__ __forceinline__ void q8_K_block_regs(const float (&v)[8], uint2 *packed, float *d_out, int *sum8) {
+    const int lane = threadIdx.x & 31;
+    float a = fabsf(v[0]), mv = v[0];
+    int idx = 8 * lane;
+#pragma unroll
+    for (int j = 1; j < 8; j++) {
+        const float aj = fabsf(v[j]);
+        if (aj > a) { a = aj; mv = v[j]; idx = 8 * lane + j; }   // strict '>': the first of equals stays
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float a2 = __shfl_xor_sync(0xffffffffu, a, o), m2 = __shfl_xor_sync(0xffffffffu, mv, o);
+        const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (a2 > a || (a2 == a && i2 < idx)) { a = a2; mv = m2; idx = i2; }
+    }
+    int q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    float d = 0.0f;
+    if (a != 0.0f) {
+        const float iscale = __fdiv_rn(-127.0f, mv);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            // nearest_int(): crates/ggml/src/quants.rs:13-18
+            const float val = __fadd_rn(__fmul_rn(iscale, v[j]), 12582912.0f);
+            q[j] = min(127, (__float_as_int(val) & 0x007fffff) - 0x00400000);
+        }
+        d = __fdiv_rn(1.0f, iscale);
+    }
+    packed->x = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
+    packed->y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+    *d_out = d;
+    *sum8 = q[0] + q[1] + q[2] + q[3] + q[4] + q[5] + q[6] + q[7];
+}
+
 }  // namespace b200

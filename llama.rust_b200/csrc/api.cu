@@ -27,6 +27,19 @@ int cuda_fail(cudaError_t e, const char *what, const char *file, int line) {
     return B200_STATUS_BACKEND_ERROR;
 }
 
+// Numerics policy of the library: 1 = fast (tolerance-mode kernels where they exist: f32-accumulating attention,
+// ...), 0 = exact (every kernel reproduces the reference CPU route's arithmetic bit for bit).  B200_NUMERICS=exact|fast
+// sets the start value (fast when unset); b200_set_numerics changes it at run time.
+static int g_numerics = -1;
+int numerics_mode() {
+    if (g_numerics < 0) {
+        const char *e = getenv("B200_NUMERICS");
+        g_numerics = (e && (e[0] == 'e' || e[0] == 'E' || e[0] == '0')) ? 0 : 1;
+    }
+    return g_numerics;
+}
+void set_numerics_mode(int mode) { g_numerics = mode ? 1 : 0; }
+
 bool pdl_enabled() {
     static int v = -1;
     if (v < 0) {
@@ -169,6 +182,9 @@ int b200_kernel_error(int *code) {
     B200_REQUIRE(code != nullptr, "kernel_error: null out pointer");
     return gemv_stream_error(code);
 }
+
+void b200_set_numerics(int mode) { set_numerics_mode(mode); }
+int b200_get_numerics(void) { return numerics_mode(); }
 
 unsigned long long b200_debug_alloc_count(void) { return library_alloc_count(); }
 
@@ -405,6 +421,50 @@ int b200_mul_mat_q8(int type, int64_t n, int64_t k, int64_t m, const void *dev_w
     return launch_gemv(type, route, n, k, m, (const uint8_t *)dev_w, a.view(), dev_dst, lddst, (cudaStream_t)stream);
 }
 
+// Times `reps` back-to-back launches of b200_mul_mat_q8 that rotate over n_w copies of the weights, as one replayed
+// CUDA graph: what a kernel costs inside a decode step, where a captured graph issues the launches and no host
+// call sits between them.  *us_per_launch receives the event-timed mean.
+int b200_bench_mul_mat_q8(int type, int64_t n, int64_t k, int64_t m, const void *const *dev_w, int n_w, const void *dev_act, int act_kind,
+                          float *dev_dst, int reps, float *us_per_launch) {
+    B200_REQUIRE(dev_w && n_w > 0 && reps > 0 && us_per_launch, "bench_mul_mat_q8: bad arguments");
+    cudaStream_t s = nullptr;
+    B200_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    int rc = B200_STATUS_SUCCESS;
+    for (int i = 0; i < n_w && rc == B200_STATUS_SUCCESS; i++)   // eager first: attributes, error word, scratch
+        rc = b200_mul_mat_q8(type, n, k, m, dev_w[i], dev_act, act_kind, dev_dst, n, B200_ROUTE_AUTO, s);
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    cudaError_t e = cudaSuccess;
+    if (rc == B200_STATUS_SUCCESS) e = cudaStreamSynchronize(s);
+    if (rc == B200_STATUS_SUCCESS && e == cudaSuccess) e = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal);
+    if (rc == B200_STATUS_SUCCESS && e == cudaSuccess) {
+        for (int i = 0; i < reps && rc == B200_STATUS_SUCCESS; i++)
+            rc = b200_mul_mat_q8(type, n, k, m, dev_w[i % n_w], dev_act, act_kind, dev_dst, n, B200_ROUTE_AUTO, s);
+        e = cudaStreamEndCapture(s, &graph);
+    }
+    if (rc == B200_STATUS_SUCCESS && e == cudaSuccess) e = cudaGraphInstantiate(&exec, graph, 0);
+    if (rc == B200_STATUS_SUCCESS && e == cudaSuccess) e = cudaEventCreate(&e0);
+    if (rc == B200_STATUS_SUCCESS && e == cudaSuccess) e = cudaEventCreate(&e1);
+    if (rc == B200_STATUS_SUCCESS && e == cudaSuccess) e = cudaGraphLaunch(exec, s);   // warm
+    if (rc == B200_STATUS_SUCCESS && e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (rc == B200_STATUS_SUCCESS && e == cudaSuccess) e = cudaEventRecord(e0, s);
+    if (rc == B200_STATUS_SUCCESS && e == cudaSuccess) e = cudaGraphLaunch(exec, s);
+    if (rc == B200_STATUS_SUCCESS && e == cudaSuccess) e = cudaEventRecord(e1, s);
+    if (rc == B200_STATUS_SUCCESS && e == cudaSuccess) e = cudaEventSynchronize(e1);
+    float ms = 0.0f;
+    if (rc == B200_STATUS_SUCCESS && e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+    if (exec) cudaGraphExecDestroy(exec);
+    if (graph) cudaGraphDestroy(graph);
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    cudaStreamDestroy(s);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    B200_CUDA(e);
+    *us_per_launch = ms * 1e3f / (float)reps;
+    return B200_STATUS_SUCCESS;
+}
+
 int b200_mul_mat_q8_multi(int type, int64_t k, int count, const int64_t *n, const void *const *dev_w, const void *dev_act, int act_kind,
                           float *const *dev_dst, void *stream) {
     B200_REQUIRE(type == B200_TYPE_Q4_K, "mul_mat_q8_multi: weight type %d is not supported (Q4_K only)", type);
@@ -418,6 +478,40 @@ int b200_mul_mat_q8_multi(int type, int64_t k, int count, const int64_t *n, cons
     B200_REQUIRE(act_kind == act_kind_for(type, B200_ROUTE_REPACK, 1), "mul_mat_q8_multi: activation kind %d does not fit type %d", act_kind, type);
     ActView a = act_carve(const_cast<void *>(dev_act), 1, k).view();
     return launch_gemv_q4_K_multi(count, n, (const uint8_t *const *)dev_w, dev_dst, k, a, (cudaStream_t)stream);
+}
+
+int b200_mul_mat_row_fused(int type, int64_t k, int count, const int64_t *n, const void *const *dev_w, float *const *dev_dst,
+                           const struct b200_act_prologue *pro, const float *dev_addend, float *dev_sum, void *stream) {
+    B200_REQUIRE(type == B200_TYPE_Q4_K, "mul_mat_row_fused: weight type %d is not supported (Q4_K only)", type);
+    B200_REQUIRE(count >= 1 && count <= 3 && n && dev_w && dev_dst && pro, "mul_mat_row_fused: bad arguments");
+    B200_REQUIRE(pro->mode >= B200_ACT_PRO_PLAIN && pro->mode <= B200_ACT_PRO_SILU && pro->x, "mul_mat_row_fused: bad prologue");
+    B200_REQUIRE(pro->mode == B200_ACT_PRO_PLAIN || (pro->w && pro->y_mul), "mul_mat_row_fused: the prologue needs its second operand and its result tensor");
+    B200_REQUIRE((dev_addend == nullptr) == (dev_sum == nullptr) && (dev_sum == nullptr || count == 1), "mul_mat_row_fused: the residual add goes with a single matrix");
+    const auto al16 = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
+    B200_REQUIRE(al16(pro->x) && al16(pro->w) && al16(pro->y) && al16(pro->y_mul), "mul_mat_row_fused: prologue rows must be 16-byte aligned");
+    for (int i = 0; i < count; i++) {
+        int rc = check_mul_mat_args(type, n[i], k, 1);
+        if (rc != B200_STATUS_SUCCESS) return rc;
+        B200_REQUIRE(pick_route(type, n[i], 1) == B200_ROUTE_REPACK, "mul_mat_row_fused: matrix %d (%lld rows) does not take the 8x8 gemv route", i,
+                     (long long)n[i]);
+    }
+    ActPrologue p;
+    p.mode = pro->mode;
+    p.x = pro->x;
+    p.w = pro->w;
+    p.eps = pro->eps;
+    p.wide_end = pro->wide ? (int)(k & ~(int64_t)15) : 0;
+    p.y = pro->y;
+    p.y_mul = pro->y_mul;
+    if (pro->dev_act_out) {
+        B200_REQUIRE(((uintptr_t)pro->dev_act_out & 255) == 0, "mul_mat_row_fused: the activation scratch must be 256-byte aligned");
+        p.act_out = act_carve(pro->dev_act_out, 1, k);
+    }
+    ActView a;
+    a.qs = nullptr; a.d = nullptr; a.bsums = nullptr; a.dh = nullptr; a.k = k;
+    a.addend = dev_addend;
+    a.sum = dev_sum;
+    return launch_gemv_q4_K_row_fused(count, n, (const uint8_t *const *)dev_w, dev_dst, k, a, p, (cudaStream_t)stream);
 }
 
 int b200_mul_mat_q8_add(int type, int64_t n, int64_t k, const void *dev_w, const void *dev_act, int act_kind, float *dev_dst,

@@ -121,6 +121,7 @@ struct BackendCtx {
     bool graphs_enabled = true;
     bool fuse_glue = true;          // one launch for neighbouring ROPE / SET_ROWS nodes (B200_FUSE_GLUE=0 / fuse_glue=0: off)
     bool fuse_siblings = true;      // one launch for one-row Q4_K mat-muls over the same activations (B200_FUSE_SIBLINGS=0 / fuse_siblings=0: off)
+    bool fuse_prologue = true;      // the norm / silu / quantization in front of a one-row Q4_K mat-mul inside its kernel (B200_FUSE_PROLOGUE=0 / fuse_prologue=0: off)
     bool capturable = true;       // cleared by a node that had to talk to the device while being issued
     TpGroup *tp = nullptr;        // the tensor-parallel group whose collectives the TP_* nodes run (owned by the driver)
 };
@@ -968,6 +969,69 @@ static int find_silu_mul(const ggml_cgraph *g, int i) {
     return -1;
 }
 
+// A norm / silu whose result's first reader is the very next non-alias node, a one-row Q4_K mat-mul on the 8x8 gemv
+// route: the op and the quantization of its result run inside that mat-mul's kernel (b200_mul_mat_row_fused).
+// Returns the mat-mul's node index, or -1.
+static int fusable_row_mat_mul(const ggml_cgraph *g, int from, const ggml_tensor *t) {
+    if (t->ne[1] != 1 || t->ne[2] != 1 || t->ne[3] != 1 || t->ne[0] % GROUP_K || ((uintptr_t)t->data & 15)) return -1;
+    for (int j = from + 1; j < g->n_nodes; j++) {
+        const ggml_tensor *n = g->nodes[j];
+        if (!n) return -1;
+        if (is_alias_op(n)) continue;
+        return n->op == GGML_OP_MUL_MAT && n->src[1] == t && multi_candidate(n) ? j : -1;
+    }
+    return -1;
+}
+// which prologues ride inside the mat-mul kernels: bit 0 quantization only, bit 1 norm in front of at most two row
+// tiles per SM, bit 2 silu, bit 3 norm in front of any number of row tiles (B200_FUSE_PROLOGUE_MASK, read once)
+static int prologue_mask() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_FUSE_PROLOGUE_MASK");
+        v = e ? atoi(e) : 7;
+    }
+    return v;
+}
+static int64_t row_tiles_of(const ggml_cgraph *g, int j) {
+    // the row tiles a fused launch starting at mat-mul j would span: the mat-mul and the siblings that may join it
+    const ggml_tensor *first = g->nodes[j];
+    int64_t tiles = (first->src[0]->ne[1] + TILE_ROWS - 1) / TILE_ROWS;
+    int sib[2];
+    const int n_sib = find_sibling_mat_muls(g, j, sib);
+    for (int e = 0; e < n_sib; e++) tiles += (g->nodes[sib[e]]->src[0]->ne[1] + TILE_ROWS - 1) / TILE_ROWS;
+    return tiles;
+}
+struct PendingPrologue {
+    bool active = false;
+    b200_act_prologue pro;
+    const ggml_tensor *act_tensor = nullptr;   // the tensor whose quantized row the mat-mul's kernel leaves in bc->act
+};
+
+// One-row Q4_K mat-mul(s) with a prologue: node i and its siblings (or node i and the residual ADD after it).
+static int compute_mul_mat_row_fused(BackendCtx *bc, const ggml_cgraph *g, int i, const int *sib, int n_sib, const ggml_tensor *add,
+                                     b200_act_prologue pro, const ggml_tensor *act_tensor) {
+    const ggml_tensor *first = g->nodes[i];
+    const int64_t k = first->src[0]->ne[0];
+    int64_t n[3];
+    const void *w[3];
+    float *dst[3];
+    for (int e = 0; e <= n_sib; e++) {
+        const ggml_tensor *mm = g->nodes[e == 0 ? i : sib[e - 1]];
+        n[e] = mm->src[0]->ne[1];
+        w[e] = mm->src[0]->data;
+        dst[e] = (float *)mm->data;
+    }
+    int rc = act_reserve(bc, 1, k);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    bc->act_src = nullptr;
+    pro.dev_act_out = bc->act;
+    const ggml_tensor *other = add ? (add->src[0] == first ? add->src[1] : add->src[0]) : nullptr;
+    rc = b200_mul_mat_row_fused(B200_TYPE_Q4_K, k, n_sib + 1, n, w, dst, &pro, other ? (const float *)other->data : nullptr,
+                                add ? (float *)add->data : nullptr, bc->stream);
+    if (rc == B200_STATUS_SUCCESS) act_holds(bc, act_tensor, B200_ACT_Q8_K);
+    return rc;
+}
+
 // Issues the launches of every node, in order, on the backend's stream.
 static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
     bc->act_src = nullptr;   // tensors may have been rewritten between graphs
@@ -979,6 +1043,7 @@ static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
     size_t fa_mask_bytes = 0;
     std::vector<int> silu_of(g->n_nodes, -1);   // silu_of[j] = i: MUL node j also computes SILU node i
     std::vector<char> done(g->n_nodes, 0);      // mat-mul nodes that ran early, with a sibling
+    PendingPrologue pending;                    // a norm / silu that rides with the mat-mul that follows it
     for (int i = 0; i < g->n_nodes; i++) {
         const ggml_tensor *op = g->nodes[i];
         B200_REQUIRE(op != nullptr, "graph_compute: node %d is null", i);
@@ -1015,7 +1080,33 @@ static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
         int rc = B200_STATUS_SUCCESS;
         switch (op->op) {
             case GGML_OP_MUL_MAT:
-                if (next && fuses_mul_mat_add(op, next) && supports_mul_mat(op, nullptr)) {
+                if (pending.active || (bc->fuse_prologue && (prologue_mask() & 1) && multi_candidate(op) && ((uintptr_t)op->src[1]->data & 15) == 0 &&
+                                       !(bc->act_src == op->src[1]->data && bc->act_m == 1 && bc->act_k == op->src[1]->ne[0] &&
+                                         bc->act_kind == B200_ACT_Q8_K))) {
+                    // the op in front of this mat-mul (or just the quantization of its activations) runs in its kernel
+                    b200_act_prologue pro;
+                    const ggml_tensor *act_tensor = op->src[1];
+                    if (pending.active) {
+                        pro = pending.pro;
+                        act_tensor = pending.act_tensor;
+                        pending.active = false;
+                    } else {
+                        memset(&pro, 0, sizeof(pro));
+                        pro.mode = B200_ACT_PRO_PLAIN;
+                        pro.x = (const float *)op->src[1]->data;
+                    }
+                    if (next && fuses_mul_mat_add(op, next)) {
+                        if (bc->act_src && ranges_overlap(next->data, ggml_nbytes(next), bc->act_src, (size_t)bc->act_ld * bc->act_m * 4))
+                            bc->act_src = nullptr;
+                        rc = compute_mul_mat_row_fused(bc, g, i, nullptr, 0, next, pro, act_tensor);
+                        i++;
+                    } else {
+                        int sib[2];
+                        const int n_sib = bc->fuse_siblings ? find_sibling_mat_muls(g, i, sib) : 0;
+                        rc = compute_mul_mat_row_fused(bc, g, i, sib, n_sib, nullptr, pro, act_tensor);
+                        for (int e = 0; e < n_sib; e++) done[sib[e]] = 1;
+                    }
+                } else if (next && fuses_mul_mat_add(op, next) && supports_mul_mat(op, nullptr)) {
                     if (bc->act_src && ranges_overlap(next->data, ggml_nbytes(next), bc->act_src, (size_t)bc->act_ld * bc->act_m * 4))
                         bc->act_src = nullptr;
                     rc = compute_mul_mat_add(bc, op, next);
@@ -1037,7 +1128,23 @@ static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
                 if (next && fuses_norm_mul(op, next)) {
                     if (bc->act_src && ranges_overlap(next->data, ggml_nbytes(next), bc->act_src, (size_t)bc->act_ld * bc->act_m * 4))
                         bc->act_src = nullptr;
-                    rc = compute_rms_norm(bc, op, next, upcoming_q8_K_kind(g, i + 1, next));
+                    const ggml_tensor *x = op->src[0];
+                    const bool al = (((uintptr_t)x->data | (uintptr_t)op->data | (uintptr_t)next->data | (uintptr_t)next->src[1]->data) & 15) == 0;
+                    const int jm = bc->fuse_prologue && al && (prologue_mask() & 10) ? fusable_row_mat_mul(g, i + 1, next) : -1;
+                    // every CTA of the mat-mul redoes the norm: worth it while the launch is a wave or two of CTAs
+                    if (jm >= 0 && ((prologue_mask() & 8) || row_tiles_of(g, jm) <= 2 * 148)) {
+                        memset(&pending.pro, 0, sizeof(pending.pro));
+                        pending.pro.mode = B200_ACT_PRO_NORM;
+                        pending.pro.x = (const float *)x->data;
+                        pending.pro.w = (const float *)next->src[1]->data;
+                        pending.pro.eps = param_f32(op, 0);
+                        pending.pro.y = (float *)op->data;
+                        pending.pro.y_mul = (float *)next->data;
+                        pending.act_tensor = next;
+                        pending.active = true;
+                    } else {
+                        rc = compute_rms_norm(bc, op, next, upcoming_q8_K_kind(g, i + 1, next));
+                    }
                     i++;
                 } else {
                     rc = compute_rms_norm(bc, op, nullptr, upcoming_q8_K_kind(g, i, op));
@@ -1054,7 +1161,20 @@ static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
                     const ggml_tensor *silu = g->nodes[silu_of[i]];
                     if (bc->act_src && ranges_overlap(silu->data, ggml_nbytes(silu), bc->act_src, (size_t)bc->act_ld * bc->act_m * 4))
                         bc->act_src = nullptr;
-                    rc = compute_silu(bc, silu, op, upcoming_q8_K_kind(g, i, op));
+                    const bool al = (((uintptr_t)silu->src[0]->data | (uintptr_t)silu->data | (uintptr_t)op->data | (uintptr_t)op->src[1]->data) & 15) == 0;
+                    if (bc->fuse_prologue && (prologue_mask() & 4) && al && fusable_row_mat_mul(g, i, op) >= 0) {
+                        memset(&pending.pro, 0, sizeof(pending.pro));
+                        pending.pro.mode = B200_ACT_PRO_SILU;
+                        pending.pro.x = (const float *)silu->src[0]->data;
+                        pending.pro.w = (const float *)op->src[1]->data;
+                        pending.pro.wide = bc->silu_wide;
+                        pending.pro.y = (float *)silu->data;
+                        pending.pro.y_mul = (float *)op->data;
+                        pending.act_tensor = op;
+                        pending.active = true;
+                    } else {
+                        rc = compute_silu(bc, silu, op, upcoming_q8_K_kind(g, i, op));
+                    }
                 } else {
                     rc = compute_binary(bc, op);
                 }
@@ -1122,6 +1242,9 @@ static uint64_t node_list_key(const BackendCtx *bc, const ggml_cgraph *g) {
     h = fnv(h, &bc->silu_wide, sizeof(int));
     h = fnv(h, &bc->fuse_siblings, sizeof(bool));
     h = fnv(h, &bc->fuse_glue, sizeof(bool));
+    h = fnv(h, &bc->fuse_prologue, sizeof(bool));
+    const int numerics = numerics_mode();
+    h = fnv(h, &numerics, sizeof(int));
     h = fnv(h, &g->n_nodes, sizeof(int));
     for (int i = 0; i < g->n_nodes; i++) {
         const ggml_tensor *t = g->nodes[i];
@@ -1303,6 +1426,8 @@ static ggml_backend_t dev_init_backend(ggml_backend_dev_t d, const char *params)
         if (fs && fs[0] == '0') bc->fuse_siblings = false;
         const char *fg = getenv("B200_FUSE_GLUE");
         if (fg && fg[0] == '0') bc->fuse_glue = false;
+        const char *fp = getenv("B200_FUSE_PROLOGUE");
+        if (fp && fp[0] == '0') bc->fuse_prologue = false;
     }
     if (cudaStreamCreateWithFlags(&bc->stream, cudaStreamNonBlocking) != cudaSuccess) {
         cudaGetLastError();
@@ -1324,6 +1449,8 @@ static ggml_backend_t dev_init_backend(ggml_backend_dev_t d, const char *params)
         if (p) bc->fuse_siblings = atoi(p + 14) != 0;
         p = strstr(params, "fuse_glue=");
         if (p) bc->fuse_glue = atoi(p + 10) != 0;
+        p = strstr(params, "fuse_prologue=");
+        if (p) bc->fuse_prologue = atoi(p + 14) != 0;
     }
     ggml_backend *be = new ggml_backend();
     memset(&be->iface, 0, sizeof(be->iface));

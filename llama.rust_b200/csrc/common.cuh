@@ -121,6 +121,19 @@ struct ActBuf {
         return v;
     }
 };
+// The f32 op in front of a one-row mat-mul, run inside the mat-mul's CTAs together with the Q8_K quantization of its
+// result (see gemv_q4_K_row_kernel).
+enum { ACT_PRO_NONE = 0, ACT_PRO_PLAIN = 1, ACT_PRO_NORM = 2, ACT_PRO_SILU = 3 };
+struct ActPrologue {
+    int mode = ACT_PRO_NONE;
+    const float *x = nullptr;     // PLAIN, NORM: the row; SILU: the row silu is applied to
+    const float *w = nullptr;     // NORM: the norm weight; SILU: the row the result is multiplied by
+    float eps = 0.0f;             // NORM
+    int wide_end = 0;             // SILU: elements below this index take the 16-lane polynomial exp, the rest libm's
+    float *y = nullptr;           // NORM: x * rms_scale; SILU: silu(x) (either may be null)
+    float *y_mul = nullptr;       // NORM: y * w; SILU: silu(x) * w
+    ActBuf act_out = {nullptr, nullptr, nullptr, nullptr, 0};   // the quantized row, for later kernels (qs null: not wanted)
+};
 size_t act_scratch_bytes(int64_t m, int64_t k);
 ActBuf act_carve(void *scratch, int64_t m, int64_t k);
 
@@ -169,6 +182,8 @@ struct GlueBatch {
 int launch_glue_batch(const GlueBatch &b, cudaStream_t s);
 int launch_gemv_q4_K_multi(int count, const int64_t *n, const uint8_t *const *tiles, float *const *dst, int64_t k, ActView acts,
                            cudaStream_t s);
+int launch_gemv_q4_K_row_fused(int count, const int64_t *n, const uint8_t *const *tiles, float *const *dst, int64_t k, ActView acts,
+                               const ActPrologue &pro, cudaStream_t s);
 int launch_gemv_q4_K_stream(int64_t n, int64_t k, const uint8_t *tiles, ActView acts, float *dst, cudaStream_t s);
 int gemv_stream_error(int *code);
 int device_error_word(int **flag);
@@ -230,6 +245,9 @@ int act_kind_for(int type, int route, int64_t m);
 // reads; what they do before pdl_wait() (index set-up, streaming the weights in) overlaps the tail of
 // the previous kernel.  B200_PDL=0 in the environment turns the attribute off.
 bool pdl_enabled();
+// 1 = tolerance-mode kernels where they exist, 0 = bit-exact reproduction of the CPU routes (b200_set_numerics)
+int numerics_mode();
+void set_numerics_mode(int mode);
 #ifdef __CUDACC__
 template <typename... KArgs, typename... Args>
 inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {

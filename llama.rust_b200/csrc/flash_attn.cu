@@ -588,6 +588,7 @@ static int check_args(const b200_flash_attn_args *a) {
 int flash_attn_faithful_tiled(const b200_flash_attn_args *a, cudaStream_t s);   // flash_attn_tiled.cu
 bool flash_attn_decode_head(const b200_flash_attn_args *a, int n_chunks, int64_t chunk, cudaStream_t s, int *rc);   // flash_attn_head.cu
 bool flash_attn_rows_visible(const b200_flash_attn_args *a, cudaStream_t s, int *rc);                               // flash_attn_vis.cu
+bool flash_attn_fast_rows(const b200_flash_attn_args *a, cudaStream_t s, int *rc);                                  // flash_attn_fast.cu
 
 // B200_FA_DECODE_FUSED=0 keeps single-row attention on the three-kernel path (for side-by-side measurements)
 static bool fa_decode_one_kernel_enabled() {
@@ -650,6 +651,10 @@ extern "C" int b200_flash_attn_ext(const struct b200_flash_attn_args *args, void
     using namespace b200;
     int rc = check_args(args);
     if (rc != B200_STATUS_SUCCESS) return rc;
+    const bool fast = args->mode == 1 || (args->mode == 0 && numerics_mode() == 1);
+    if (fast && args->n_tok < 64) {
+        if (flash_attn_fast_rows(args, (cudaStream_t)stream, &rc)) return rc;
+    }
     if (args->n_tok < 64) return flash_attn_faithful_rows(args, (cudaStream_t)stream);
     return flash_attn_faithful_tiled(args, (cudaStream_t)stream);
 }

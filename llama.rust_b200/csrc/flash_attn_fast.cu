@@ -1,0 +1,302 @@
+// FLASH_ATTN_EXT, fast mode, few query rows (single-token and small-batch decode): flash-decoding.
+//
+// The faithful kernels (flash_attn.cu) reproduce the CPU path's arithmetic bit for bit, including the f16
+// accumulator that is rounded once per cached position: a dependent chain as long as the context.  This file is
+// the mode for hosts that accept the tolerance asked of F16-KV attention (1e-3): the same function
+//   softmax(q k^T * scale + mask) v        (crates/ggml/src/flash_attn.rs:482-736)
+// with f32 accumulation and no ordered chain, so it can be cut freely:
+//   * grid (splits, KV heads, row blocks): a CTA takes one KV head, a range of cached positions and up to 16 of the
+//     query rows that read that KV head (the n_head / n_head_kv query heads of every token share the K / V tiles a
+//     CTA stages: GQA head sharing), so the cache is read once per row block;
+//   * K and V tiles of 32 positions are staged in shared memory with 16-byte cp.async copies (every cached row is
+//     contiguous), double buffered; lane = position for the scores, lane = 4 value elements for P V;
+//   * q stays in f32 (the CPU rounds it to f16 before its dot, flash_attn.rs:433), scores and P V accumulate in
+//     f32, softmax runs online per row with exp2;
+//   * every CTA leaves (max, sum, accumulator) per row; the last CTA of a (KV head, row block) to finish merges the
+//     splits and writes the rows.
+// Masked positions (-inf in the F16 mask) are skipped as the CPU skips them; a (row, tile) pair with nothing
+// visible costs one mask read.  Not handled here (the caller falls back to the faithful kernels): sinks, ALiBi,
+// softcap, dk != dv.
+#include "common.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int FF_TILE = 32;          // positions per tile
+constexpr int FF_ROWS = 16;          // query rows per CTA
+constexpr int FF_WARPS = 4;
+constexpr int FF_MAX_SPLITS = 64;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct FastDims {
+    int T, H, H_kv, group;
+    int64_t n_kv;
+    int n_splits;
+    int tiles_per_split;
+};
+
+__device__ __forceinline__ void cp_async16(void *dst_smem, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// partial[(((hk * row_blocks + rb) * n_splits + split) * FF_ROWS + r) * (2 + D)] = {m, l, acc[D]}
+template <int D>
+__global__ void __launch_bounds__(FF_WARPS * 32)
+fa_fast_rows_kernel(b200_flash_attn_args a, FastDims d, float scale_log2, float *__restrict__ partial, int *__restrict__ counters) {
+    constexpr int KSTRIDE = D * 2 + 16;                      // bytes per staged row: 16 bytes of padding keep lanes on different banks
+    constexpr int VEC = D / 32;                              // value elements per lane
+    extern __shared__ __align__(16) unsigned char smem[];
+    unsigned char *ks = smem;                                // [2][FF_TILE][KSTRIDE]
+    unsigned char *vs = ks + 2 * FF_TILE * KSTRIDE;          // [2][FF_TILE][KSTRIDE]
+    float *qs = (float *)(vs + 2 * FF_TILE * KSTRIDE);       // [FF_ROWS][D]
+    float *ps = qs + FF_ROWS * D;                            // [FF_ROWS][FF_TILE]; the merge reuses it as [FF_ROWS][FF_MAX_SPLITS]
+    __shared__ int is_last;
+
+    pdl_trigger();
+    const int split = blockIdx.x, hk = blockIdx.y, rb = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int rows_total = d.T * d.group;                    // rows that read this KV head: row = t * group + g
+    const int row0 = rb * FF_ROWS;
+    const int nrows = rows_total - row0 < FF_ROWS ? rows_total - row0 : FF_ROWS;
+    const int64_t tile0 = (int64_t)split * d.tiles_per_split;
+    const int64_t n_tiles_all = (d.n_kv + FF_TILE - 1) / FF_TILE;
+    int64_t tile1 = tile0 + d.tiles_per_split;
+    if (tile1 > n_tiles_all) tile1 = n_tiles_all;
+    const unsigned char *kbase = (const unsigned char *)a.k + (int64_t)hk * a.k_nb2;
+    const unsigned char *vbase = (const unsigned char *)a.v + (int64_t)hk * a.v_nb2;
+
+    pdl_wait();   // q, the cache rows of this step and the mask come from earlier kernels / copies
+    for (int i = tid; i < nrows * D; i += FF_WARPS * 32) {
+        const int r = row0 + i / D, e = i % D;
+        const int t = r / d.group, h = hk * d.group + r % d.group;
+        const float *q = (const float *)((const unsigned char *)a.q + (int64_t)t * a.q_nb1 + (int64_t)h * a.q_nb2);
+        qs[i] = q[e];
+    }
+
+    auto stage = [&](int64_t tile, int buf) {
+        // FF_TILE rows of D halves each for K and V: D / 8 16-byte pieces per row
+        constexpr int PIECES = D / 8;
+        for (int i = tid; i < FF_TILE * PIECES; i += FF_WARPS * 32) {
+            const int p = i / PIECES, c = i % PIECES;
+            int64_t pos = tile * FF_TILE + p;
+            if (pos >= d.n_kv) pos = d.n_kv - 1;   // a ragged last tile re-reads the last row; its scores are masked below
+            cp_async16(ks + ((size_t)buf * FF_TILE + p) * KSTRIDE + c * 16, kbase + pos * a.k_nb1 + c * 16);
+            cp_async16(vs + ((size_t)buf * FF_TILE + p) * KSTRIDE + c * 16, vbase + pos * a.v_nb1 + c * 16);
+        }
+        cp_async_commit();
+    };
+
+    // per warp: rows warp, warp + 4, ...; per row the running max (in log2 units), sum and VEC accumulator elements per lane
+    constexpr int RPW = FF_ROWS / FF_WARPS;
+    float m_run[RPW], l_run[RPW], acc[RPW][VEC];
+#pragma unroll
+    for (int i = 0; i < RPW; i++) {
+        m_run[i] = -INFINITY;
+        l_run[i] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VEC; j++) acc[i][j] = 0.0f;
+    }
+
+    if (tile0 < tile1) stage(tile0, 0);
+    for (int64_t tile = tile0; tile < tile1; tile++) {
+        const int buf = (int)((tile - tile0) & 1);
+        const int64_t pos = tile * FF_TILE + lane;
+        // this tile's mask values travel while the K / V copies do: one round trip instead of two in a row
+        float mvals[RPW];
+#pragma unroll
+        for (int i = 0; i < RPW; i++) {
+            const int rl = warp + i * FF_WARPS;
+            mvals[i] = 0.0f;
+            if (rl < nrows && a.mask && pos < d.n_kv) {
+                const int t = (row0 + rl) / d.group;
+                mvals[i] = __half2float(((const __half *)((const unsigned char *)a.mask + (int64_t)t * a.mask_nb1))[pos]);
+            }
+        }
+        if (tile + 1 < tile1) {
+            stage(tile + 1, buf ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const unsigned char *krow = ks + ((size_t)buf * FF_TILE + lane) * KSTRIDE;
+#pragma unroll
+        for (int i = 0; i < RPW; i++) {
+            const int rl = warp + i * FF_WARPS;        // row within the block
+            if (rl >= nrows) break;
+            // mask first: a hidden position is skipped, a row with nothing visible in this tile skips the tile
+            const float mval = mvals[i];
+            const bool visible = pos < d.n_kv && mval != -INFINITY;
+            if (__ballot_sync(0xffffffffu, visible) == 0u) continue;
+            float s = -INFINITY;
+            if (visible) {
+                const float *q = qs + rl * D;
+                float dot = 0.0f;
+#pragma unroll
+                for (int c = 0; c < D / 8; c++) {
+                    const uint4 kv = *(const uint4 *)(krow + c * 16);
+                    const float4 q0 = *(const float4 *)(q + c * 8), q1 = *(const float4 *)(q + c * 8 + 4);
+                    const float2 k0 = __half22float2(*(const __half2 *)&kv.x), k1 = __half22float2(*(const __half2 *)&kv.y);
+                    const float2 k2 = __half22float2(*(const __half2 *)&kv.z), k3 = __half22float2(*(const __half2 *)&kv.w);
+                    dot = fmaf(q0.x, k0.x, dot); dot = fmaf(q0.y, k0.y, dot); dot = fmaf(q0.z, k1.x, dot); dot = fmaf(q0.w, k1.y, dot);
+                    dot = fmaf(q1.x, k2.x, dot); dot = fmaf(q1.y, k2.y, dot); dot = fmaf(q1.z, k3.x, dot); dot = fmaf(q1.w, k3.y, dot);
+                }
+                s = fmaf(dot, scale_log2, mval * LOG2E);   // log2 units: exp(x) = exp2(x * log2 e)
+            }
+            float tmax = s;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+            const float m_new = fmaxf(m_run[i], tmax);
+            const float alpha = m_run[i] == -INFINITY ? 0.0f : exp2f(m_run[i] - m_new);
+            const float p = visible ? exp2f(s - m_new) : 0.0f;
+            float psum = p;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+            l_run[i] = fmaf(l_run[i], alpha, psum);
+            m_run[i] = m_new;
+            ps[rl * FF_TILE + lane] = p;
+            __syncwarp();
+            // P V: lane owns value elements VEC * lane ..
+            float o_[VEC];
+#pragma unroll
+            for (int j = 0; j < VEC; j++) o_[j] = acc[i][j] * alpha;
+            const unsigned char *vcol = vs + (size_t)buf * FF_TILE * KSTRIDE + lane * VEC * 2;
+#pragma unroll 8
+            for (int pp = 0; pp < FF_TILE; pp++) {
+                const float w = ps[rl * FF_TILE + pp];
+                if (VEC == 4) {
+                    const uint2 vv = *(const uint2 *)(vcol + (size_t)pp * KSTRIDE);
+                    const float2 v0 = __half22float2(*(const __half2 *)&vv.x), v1 = __half22float2(*(const __half2 *)&vv.y);
+                    o_[0] = fmaf(w, v0.x, o_[0]); o_[1] = fmaf(w, v0.y, o_[1]); o_[VEC - 2] = fmaf(w, v1.x, o_[VEC - 2]); o_[VEC - 1] = fmaf(w, v1.y, o_[VEC - 1]);
+                } else {
+                    const float2 v0 = __half22float2(*(const __half2 *)(vcol + (size_t)pp * KSTRIDE));
+                    o_[0] = fmaf(w, v0.x, o_[0]); o_[VEC - 1] = fmaf(w, v0.y, o_[VEC - 1]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < VEC; j++) acc[i][j] = o_[j];
+            __syncwarp();
+        }
+        __syncthreads();   // the buffer staged two tiles ago is free again
+    }
+
+    // this CTA's partials
+    const int row_blocks = gridDim.z;
+    float *mine = partial + (((int64_t)hk * row_blocks + rb) * d.n_splits + split) * FF_ROWS * (2 + D);
+#pragma unroll
+    for (int i = 0; i < RPW; i++) {
+        const int rl = warp + i * FF_WARPS;
+        if (rl >= nrows) break;
+        float *pr = mine + (int64_t)rl * (2 + D);
+        if (lane == 0) { pr[0] = m_run[i]; pr[1] = l_run[i]; }
+#pragma unroll
+        for (int j = 0; j < VEC; j++) pr[2 + lane * VEC + j] = acc[i][j];
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) is_last = atomicAdd(&counters[hk * row_blocks + rb], 1) == d.n_splits - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (tid == 0) counters[hk * row_blocks + rb] = 0;   // ready for the next launch
+    // merge the splits.  The (max, sum) pairs of every (row, split) come into shared memory with independent loads,
+    // the per-split weights exp2(m - M) are made once, and the accumulators are then summed with loads that do not
+    // depend on one another (the compiler batches them), thread = value element, rows in turn.
+    const float *all = partial + ((int64_t)hk * row_blocks + rb) * d.n_splits * FF_ROWS * (2 + D);
+    float *mw = ps;                       // [FF_ROWS][FF_MAX_SPLITS] maxima, then weights; ps is free now
+    float *lw = qs;                       // [FF_ROWS][FF_MAX_SPLITS] sums; qs is free too (FF_ROWS * D >= FF_ROWS * FF_MAX_SPLITS)
+    __shared__ float lsum[FF_ROWS];
+    for (int i = tid; i < nrows * d.n_splits; i += FF_WARPS * 32) {
+        const int rl = i / d.n_splits, sp = i - rl * d.n_splits;
+        const float *pr = all + ((int64_t)sp * FF_ROWS + rl) * (2 + D);
+        mw[rl * FF_MAX_SPLITS + sp] = __ldcg(pr);
+        lw[rl * FF_MAX_SPLITS + sp] = __ldcg(pr + 1);
+    }
+    __syncthreads();
+    if (tid < nrows) {
+        float M = -INFINITY;
+        for (int sp = 0; sp < d.n_splits; sp++) M = fmaxf(M, mw[tid * FF_MAX_SPLITS + sp]);
+        float L = 0.0f;
+        for (int sp = 0; sp < d.n_splits; sp++) {
+            const float ms = mw[tid * FF_MAX_SPLITS + sp];
+            const float w = ms == -INFINITY ? 0.0f : exp2f(ms - M);
+            mw[tid * FF_MAX_SPLITS + sp] = w;
+            L = fmaf(lw[tid * FF_MAX_SPLITS + sp], w, L);
+        }
+        lsum[tid] = L;
+    }
+    __syncthreads();
+    for (int i = tid; i < nrows * D; i += FF_WARPS * 32) {
+        const int rl = i / D, e = i - rl * D;
+        const float *pr = all + (int64_t)rl * (2 + D) + 2 + e;
+        float o = 0.0f;
+#pragma unroll 8
+        for (int sp = 0; sp < d.n_splits; sp++) o = fmaf(__ldcg(pr + (int64_t)sp * FF_ROWS * (2 + D)), mw[rl * FF_MAX_SPLITS + sp], o);
+        const int r = row0 + rl, t = r / d.group, h = hk * d.group + r % d.group;
+        const float L = lsum[rl];
+        a.dst[((int64_t)t * d.H + h) * D + e] = L > 0.0f ? o / L : 0.0f;   // a row that sees nothing gives zeros, as on the CPU
+    }
+}
+
+int *g_fast_counters[64] = {nullptr};
+__device__ int g_fast_counters_dev[4096];
+
+}  // namespace
+
+// true: the fast path took the call (*rc is its status); false: not a shape it handles
+bool flash_attn_fast_rows(const b200_flash_attn_args *a, cudaStream_t s, int *rc) {
+    *rc = B200_STATUS_SUCCESS;
+    if (a->sinks || a->max_bias != 0.0f || a->logit_softcap != 0.0f || a->dk != a->dv || a->n_tok >= 64 || a->n_kv == 0 || a->n_tok == 0)
+        return false;
+    if (a->q_nb1 % 4 || a->q_nb2 % 4) return false;
+    FastDims d;
+    d.T = (int)a->n_tok; d.H = (int)a->n_head; d.H_kv = (int)a->n_head_kv; d.group = d.H / d.H_kv;
+    d.n_kv = a->n_kv;
+    const int rows_total = d.T * d.group;
+    const int row_blocks = (rows_total + FF_ROWS - 1) / FF_ROWS;
+    if (d.H_kv > 65535 || row_blocks > 65535 || d.H_kv * row_blocks > 4096) return false;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        *rc = cuda_fail(cudaGetLastError(), "flash_attn fast: device query", __FILE__, __LINE__);
+        return true;
+    }
+    const int64_t n_tiles = (d.n_kv + FF_TILE - 1) / FF_TILE;
+    // enough CTAs for two per SM, at least two tiles per CTA once the context is long, at most FF_MAX_SPLITS
+    int64_t want = (2 * (int64_t)sms + (int64_t)d.H_kv * row_blocks - 1) / ((int64_t)d.H_kv * row_blocks);
+    if (want > FF_MAX_SPLITS) want = FF_MAX_SPLITS;
+    if (want > n_tiles) want = n_tiles;
+    if (want < 1) want = 1;
+    d.tiles_per_split = (int)((n_tiles + want - 1) / want);
+    d.n_splits = (int)((n_tiles + d.tiles_per_split - 1) / d.tiles_per_split);
+    if (!g_fast_counters[dev]) {   // a module variable: no allocation, zero-initialized on every device
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_fast_counters_dev);
+        if (e != cudaSuccess) { *rc = cuda_fail(e, "cudaGetSymbolAddress", __FILE__, __LINE__); return true; }
+        g_fast_counters[dev] = (int *)p;
+    }
+    const int D = (int)a->dk;
+    const size_t part_b = (size_t)d.H_kv * row_blocks * d.n_splits * FF_ROWS * (2 + D) * 4;
+    void *scratch = nullptr;
+    *rc = scratch_get(part_b, &scratch);
+    if (*rc != B200_STATUS_SUCCESS) return true;
+    const size_t smem = (size_t)4 * FF_TILE * (D * 2 + 16) + (size_t)FF_ROWS * D * 4 + (size_t)FF_ROWS * FF_MAX_SPLITS * 4;
+    const dim3 grid((unsigned)d.n_splits, (unsigned)d.H_kv, (unsigned)row_blocks);
+    const float scale_log2 = a->scale * LOG2E;
+    static bool attr_done[64][2] = {};
+    if (!attr_done[dev][D == 128]) {
+        cudaError_t e = D == 128 ? cudaFuncSetAttribute(fa_fast_rows_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                                 : cudaFuncSetAttribute(fa_fast_rows_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { *rc = cuda_fail(e, "cudaFuncSetAttribute", __FILE__, __LINE__); return true; }
+        attr_done[dev][D == 128] = true;
+    }
+    if (D == 128) *rc = launch_pdl(fa_fast_rows_kernel<128>, grid, dim3(FF_WARPS * 32), smem, s, *a, d, scale_log2, (float *)scratch, g_fast_counters[dev]);
+    else *rc = launch_pdl(fa_fast_rows_kernel<64>, grid, dim3(FF_WARPS * 32), smem, s, *a, d, scale_log2, (float *)scratch, g_fast_counters[dev]);
+    return true;
+}
+
+}  // namespace b200

@@ -13,6 +13,8 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "act_quant.cuh"
+#include "fa_math.cuh"
 #include "gemv_types.cuh"
 
 namespace b200 {
@@ -81,7 +83,9 @@ struct Q4KStage {
 //   0  8x8 gemv  (repack.rs:1638-1688): one fma per super-block and term, out = acc - accmin
 //   1  8x8 gemm  (repack.rs:1692-1768): one fma per (super-block, sub-block pair) and term
 //   2  tiled     (tiled.rs:823-838):    r = d*f32(s1); r = fma(-dmin, f32(s2), r); out = fma(r, d_x, out)
-template <int NCOL, int MODE>
+// PF: a warp that walks several groups of K (long rows, few row tiles: one CTA per SM anyway) issues the loads of
+// its next group before it computes the current one; costs 36 registers, so only such shapes are launched with it.
+template <int NCOL, int MODE, bool PF = false>
 __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32)
 gemv_q4_K_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, int64_t n, int nb, PairMap pm) {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -116,12 +120,31 @@ gemv_q4_K_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, 
     }
     int4 *gx = pm.ksplit > 1 ? pm.kx + (int64_t)tile * nb * 32 : nullptr;
 
+    uint4 h_n = make_uint4(0, 0, 0, 0), q_n[8];
+    if (PF && b_first + warp < b_last) {
+        const uint8_t *chunk = base + (int64_t)(b_first + warp) * 4608;
+        h_n = ld_stream16(chunk + lane * 16);
+#pragma unroll
+        for (int c = 0; c < 8; c++) q_n[c] = ld_stream16(chunk + 512 + c * 512 + lane * 16);
+    }
     for (int b = b_first + warp; b < b_last; b += nwarps) {
         const uint8_t *chunk = base + (int64_t)b * 4608;
-        const uint4 h = ld_stream16(chunk + lane * 16);
-        uint4 q[8];
+        uint4 h, q[8];
+        if (PF) {
+            h = h_n;
 #pragma unroll
-        for (int c = 0; c < 8; c++) q[c] = ld_stream16(chunk + 512 + c * 512 + lane * 16);
+            for (int c = 0; c < 8; c++) q[c] = q_n[c];
+            if (b + nwarps < b_last) {
+                const uint8_t *next = chunk + (int64_t)nwarps * 4608;
+                h_n = ld_stream16(next + lane * 16);
+#pragma unroll
+                for (int c = 0; c < 8; c++) q_n[c] = ld_stream16(next + 512 + c * 512 + lane * 16);
+            }
+        } else {
+            h = ld_stream16(chunk + lane * 16);
+#pragma unroll
+            for (int c = 0; c < 8; c++) q[c] = ld_stream16(chunk + 512 + c * 512 + lane * 16);
+        }
         // the weight loads above are in flight; the activations are the previous kernel's output
         if (!waited) { pdl_wait(); waited = true; }
         // stage this group's activations for every column
@@ -244,6 +267,224 @@ gemv_q4_K_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, 
     }
 }
 
+// ---------------------------------------------------------------------------
+// Q4_K, 8x8 gemv chain, ONE activation row: the decode kernel.  The arithmetic of gemv_q4_K_kernel<1, 0>, plus an
+// activation prologue: the f32 op that feeds the mat-mul in a decoder layer and the Q8_K quantization of its result
+// run inside the mat-mul's CTAs instead of in a kernel of their own (at one token each of those kernels is a few
+// microseconds of launch latency for a few KB of work):
+//   ACT_PRO_NONE   the activations arrive quantized (ActView)
+//   ACT_PRO_PLAIN  quantize x                                         (attention output -> attn_output)
+//   ACT_PRO_NORM   quantize (x * rms_scale(x)) * w                    (RMS_NORM + MUL -> q/k/v, gate/up)
+//   ACT_PRO_SILU   quantize silu(x) * w                               (SILU + MUL -> ffn_down)
+// Every CTA redoes the prologue for the groups of K its warps walk (the row is a few KB and sits in L2); a warp
+// quantizes the 256-element block it is about to multiply, with the value rules of quantize_row_q8_K
+// (crates/ggml/src/quants.rs:615-654), so the integers that meet the weights are the ones the separate kernels
+// would have produced.  The CTA of row tile 0 also writes the prologue's node outputs (norm, weighted norm / silu,
+// gated product) and the quantized row, for whatever else reads them.  For ACT_PRO_NORM the CTA first sums the
+// row's squares in f64 (crates/ggml/src/compute.rs:2634-2683), while its first weight loads are in flight.
+// blockIdx.x walks the row tiles of up to three matrices (PairMap segments), blockIdx.y the (token, slot) pairs of a
+// MUL_MAT_ID.  PF: a warp that walks several groups issues the loads of its next group before the current one's
+// arithmetic.
+// ---------------------------------------------------------------------------
+template <bool PF, int PRO>
+__global__ void __launch_bounds__(GEMV_MAX_WARPS * 32)
+gemv_q4_K_row_kernel(const uint8_t *tiles, ActView acts, float *dst, int64_t n, int nb, PairMap pm, ActPrologue pro) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    pdl_trigger();
+    if (pm.ids) pdl_wait();   // the expert ids come from a previous kernel
+    if (!apply_pair(pm, tiles, acts, dst, n)) return;
+    int tile = blockIdx.x;
+    const bool writer = PRO != ACT_PRO_NONE && blockIdx.x == 0 && blockIdx.y == 0;   // materializes the prologue's outputs
+    if (pm.seg_count > 1) {   // constant indices only: the segment table stays in the parameter bank
+        if (tile >= pm.seg_end[1]) {
+            tile -= pm.seg_end[1];
+            tiles = pm.seg_tiles[1];
+            dst = pm.seg_dst[1];
+            n = pm.seg_n[1];
+        } else if (tile >= pm.seg_end[0]) {
+            tile -= pm.seg_end[0];
+            tiles = pm.seg_tiles[0];
+            dst = pm.seg_dst[0];
+            n = pm.seg_n[0];
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    Q4KStage *stage = (Q4KStage *)smem + warp;
+    int4 *xch = (int4 *)(smem + sizeof(Q4KStage) * nwarps);   // [nb][32]
+    float *dx_s = (float *)(xch + (size_t)nb * 32);           // [nb] activation block scales
+    __shared__ double sq_part[GEMV_MAX_WARPS];
+    const uint8_t *base = tiles + tile * (int64_t)nb * 4608;
+
+    uint4 h_n = make_uint4(0, 0, 0, 0), q_n[8];
+    if (warp < nb) {
+        const uint8_t *chunk = base + (int64_t)warp * 4608;
+        h_n = ld_stream16(chunk + lane * 16);
+#pragma unroll
+        for (int c = 0; c < 8; c++) q_n[c] = ld_stream16(chunk + 512 + c * 512 + lane * 16);
+    }
+    if (!pm.ids) pdl_wait();   // everything below reads what earlier kernels wrote
+    float rms_scale = 1.0f;
+    if (PRO == ACT_PRO_NORM) {
+        double sum = 0.0;
+        for (int b = warp; b < nb; b += nwarps) {
+            const float4 a0 = *(const float4 *)(pro.x + (int64_t)b * 256 + 8 * lane), a1 = *(const float4 *)(pro.x + (int64_t)b * 256 + 8 * lane + 4);
+            sum += (double)__fmul_rn(a0.x, a0.x); sum += (double)__fmul_rn(a0.y, a0.y);
+            sum += (double)__fmul_rn(a0.z, a0.z); sum += (double)__fmul_rn(a0.w, a0.w);
+            sum += (double)__fmul_rn(a1.x, a1.x); sum += (double)__fmul_rn(a1.y, a1.y);
+            sum += (double)__fmul_rn(a1.z, a1.z); sum += (double)__fmul_rn(a1.w, a1.w);
+        }
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) sq_part[warp] = sum;
+        __syncthreads();
+        double total = 0.0;
+        for (int i = 0; i < nwarps; i++) total += sq_part[i];
+        const float mean = __double2float_rn(total / (double)(nb * 256));
+        rms_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, pro.eps)));
+    }
+
+    for (int b = warp; b < nb; b += nwarps) {
+        uint4 h = h_n, q[8];
+#pragma unroll
+        for (int c = 0; c < 8; c++) q[c] = q_n[c];
+        if (PF && b + nwarps < nb) {
+            const uint8_t *next = base + (int64_t)(b + nwarps) * 4608;
+            h_n = ld_stream16(next + lane * 16);
+#pragma unroll
+            for (int c = 0; c < 8; c++) q_n[c] = ld_stream16(next + 512 + c * 512 + lane * 16);
+        }
+        // this group's activations into the warp's stage
+        if (PRO == ACT_PRO_NONE) {
+            if (lane < 16) {
+                stage->q[lane] = *(const uint4 *)(acts.qs + (int64_t)b * 256 + lane * 16);
+            } else if (lane < 24) {
+                const int j = lane - 16;
+                const short2 s2 = *(const short2 *)(acts.bsums + (int64_t)b * 16 + 2 * j);
+                stage->bp[j] = (int)s2.x + (int)s2.y;
+            } else if (lane == 24) {
+                dx_s[b] = acts.d[b];
+            }
+        } else {
+            const int64_t e0 = (int64_t)b * 256 + 8 * lane;
+            float v[8];
+            {
+                const float4 a0 = *(const float4 *)(pro.x + e0), a1 = *(const float4 *)(pro.x + e0 + 4);
+                v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w; v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
+            }
+            if (PRO == ACT_PRO_NORM) {
+                const float4 w0 = *(const float4 *)(pro.w + e0), w1 = *(const float4 *)(pro.w + e0 + 4);
+                const float ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                float nv[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    nv[j] = __fmul_rn(v[j], rms_scale);
+                    v[j] = __fmul_rn(nv[j], ws[j]);
+                }
+                if (writer) {
+                    if (pro.y) {
+                        *(float4 *)(pro.y + e0) = make_float4(nv[0], nv[1], nv[2], nv[3]);
+                        *(float4 *)(pro.y + e0 + 4) = make_float4(nv[4], nv[5], nv[6], nv[7]);
+                    }
+                    *(float4 *)(pro.y_mul + e0) = make_float4(v[0], v[1], v[2], v[3]);
+                    *(float4 *)(pro.y_mul + e0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+                }
+            } else if (PRO == ACT_PRO_SILU) {
+                const float4 g0 = *(const float4 *)(pro.w + e0), g1 = *(const float4 *)(pro.w + e0 + 4);
+                const float gs[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                float sv[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const float e = (int)(e0 + j) < pro.wide_end ? v_expf(__fsub_rn(0.0f, v[j])) : libm_expf(-v[j]);
+                    sv[j] = __fdiv_rn(v[j], __fadd_rn(1.0f, e));
+                    v[j] = __fmul_rn(sv[j], gs[j]);
+                }
+                if (writer) {
+                    if (pro.y) {
+                        *(float4 *)(pro.y + e0) = make_float4(sv[0], sv[1], sv[2], sv[3]);
+                        *(float4 *)(pro.y + e0 + 4) = make_float4(sv[4], sv[5], sv[6], sv[7]);
+                    }
+                    *(float4 *)(pro.y_mul + e0) = make_float4(v[0], v[1], v[2], v[3]);
+                    *(float4 *)(pro.y_mul + e0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+                }
+            }
+            // quantize_row_q8_K on the block the warp holds (lane l: elements 8 l .. 8 l + 7)
+            uint2 packed;
+            float d;
+            int s8;
+            q8_K_block_regs(v, &packed, &d, &s8);
+            *(uint2 *)((unsigned char *)stage->q + 8 * lane) = packed;
+            int s16 = s8 + __shfl_xor_sync(0xffffffffu, s8, 1);        // a 16-element sum is two lanes
+            const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);  // bsums[2j] + bsums[2j+1] is four lanes
+            if ((lane & 3) == 0) stage->bp[lane >> 2] = s32;
+            if (lane == 0) dx_s[b] = d;
+            if (writer && pro.act_out.qs) {
+                *(uint2 *)(pro.act_out.qs + e0) = packed;
+                if ((lane & 1) == 0) pro.act_out.bsums[(int64_t)b * 16 + (lane >> 1)] = (int16_t)s16;
+                if (lane == 0) pro.act_out.d[b] = d;
+            }
+        }
+        __syncwarp();
+        // 6-bit scales and mins: crates/ggml/src/quants.rs:421-429 (get_scale_min_k4)
+        const uint32_t u0 = h.y, u1 = h.z, u2 = h.w;
+        const uint32_t sc_lo4 = u0 & 0x3f3f3f3fu, mn_lo4 = u1 & 0x3f3f3f3fu;
+        const uint32_t sc_hi4 = (u2 & 0x0f0f0f0fu) | (((u0 >> 6) & 0x03030303u) << 4);
+        const uint32_t mn_hi4 = ((u2 >> 4) & 0x0f0f0f0fu) | (((u1 >> 6) & 0x03030303u) << 4);
+        int iacc = 0;
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            int dlo = 0, dhi = 0;
+#pragma unroll
+            for (int hh = 0; hh < 2; hh++) {
+                const uint4 w = q[2 * g + hh];
+                const uint4 alo = stage->q[4 * g + hh], ahi = stage->q[4 * g + 2 + hh];
+                dlo = __dp4a((int)(w.x & 0x0f0f0f0fu), (int)alo.x, dlo);
+                dlo = __dp4a((int)(w.y & 0x0f0f0f0fu), (int)alo.y, dlo);
+                dlo = __dp4a((int)(w.z & 0x0f0f0f0fu), (int)alo.z, dlo);
+                dlo = __dp4a((int)(w.w & 0x0f0f0f0fu), (int)alo.w, dlo);
+                dhi = __dp4a((int)((w.x >> 4) & 0x0f0f0f0fu), (int)ahi.x, dhi);
+                dhi = __dp4a((int)((w.y >> 4) & 0x0f0f0f0fu), (int)ahi.y, dhi);
+                dhi = __dp4a((int)((w.z >> 4) & 0x0f0f0f0fu), (int)ahi.z, dhi);
+                dhi = __dp4a((int)((w.w >> 4) & 0x0f0f0f0fu), (int)ahi.w, dhi);
+            }
+            const uint32_t s4 = g < 2 ? sc_lo4 : sc_hi4;
+            iacc += dlo * (int)((s4 >> (16 * (g & 1))) & 0xff) + dhi * (int)((s4 >> (16 * (g & 1) + 8)) & 0xff);
+        }
+        int imin = 0;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const uint32_t m4 = j < 4 ? mn_lo4 : mn_hi4;
+            imin += (int)((m4 >> (8 * (j & 3))) & 0xff) * stage->bp[j];
+        }
+        xch[b * 32 + lane] = make_int4(iacc, imin, (int)h.x, 0);
+        __syncwarp();
+        if (!PF && b + nwarps < nb) {   // without the prefetch the next group is loaded only now
+            const uint8_t *next = base + (int64_t)(b + nwarps) * 4608;
+            h_n = ld_stream16(next + lane * 16);
+#pragma unroll
+            for (int c = 0; c < 8; c++) q_n[c] = ld_stream16(next + 512 + c * 512 + lane * 16);
+        }
+    }
+    __syncthreads();
+    // accumulation chain, ascending K: one warp, lane = row
+    if (warp == 0) {
+        float sumf = 0.0f, summin = 0.0f;
+#pragma unroll 4
+        for (int bb = 0; bb < nb; bb++) {
+            const int4 v = xch[bb * 32 + lane];
+            const float d = f16_bits_to_f32((uint16_t)((uint32_t)v.z & 0xffffu));
+            const float dmin = f16_bits_to_f32((uint16_t)((uint32_t)v.z >> 16));
+            const float da = dx_s[bb];
+            sumf = __fmaf_rn((float)v.x, __fmul_rn(d, da), sumf);
+            summin = __fmaf_rn((float)v.y, __fmul_rn(dmin, da), summin);
+        }
+        const int64_t row = (int64_t)tile * TILE_ROWS + lane;
+        if (row < n) {
+            const float v = __fsub_rn(sumf, summin);
+            dst[row] = v;
+            if (acts.sum) acts.sum[row] = __fadd_rn(v, acts.addend[row]);
+        }
+    }
+}
+
 static int pick_warps(int nb) {
     // the largest warp count <= 16 that divides the group count keeps every warp equally loaded
     for (int w = GEMV_MAX_WARPS; w >= 8; w--)
@@ -251,7 +492,7 @@ static int pick_warps(int nb) {
     return nb < GEMV_MAX_WARPS ? (nb < 1 ? 1 : nb) : GEMV_MAX_WARPS;
 }
 
-template <int NCOL, int MODE>
+template <int NCOL, int MODE, bool PF = false>
 static int launch_q4k(int64_t n, int nb, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
                       cudaStream_t s, PairMap pm = PairMap{}, int64_t pairs = 1) {
     const int splits = pm.ksplit > 1 ? pm.ksplit : 1;
@@ -264,13 +505,73 @@ static int launch_q4k(int64_t n, int nb, const uint8_t *tiles, ActView acts, flo
     B200_CUDA(cudaGetDevice(&dev));
     B200_REQUIRE(dev >= 0 && dev < 64, "gemv: device index %d out of range", dev);
     if (!attr_done[dev]) {
-        B200_CUDA(cudaFuncSetAttribute(gemv_q4_K_kernel<NCOL, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        B200_CUDA(cudaFuncSetAttribute(gemv_q4_K_kernel<NCOL, MODE, PF>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_done[dev] = true;
     }
     const int64_t tiles_n = pm.seg_count > 1 ? pm.seg_total : (n + TILE_ROWS - 1) / TILE_ROWS;
     B200_REQUIRE(pairs >= 1 && pairs <= 65535, "mul_mat_id: %lld (token, slot) pairs exceed one launch", (long long)pairs);
-    return launch_pdl(gemv_q4_K_kernel<NCOL, MODE>, dim3((unsigned)tiles_n, (unsigned)pairs, (unsigned)splits), dim3(nw * 32), smem, s,
+    return launch_pdl(gemv_q4_K_kernel<NCOL, MODE, PF>, dim3((unsigned)tiles_n, (unsigned)pairs, (unsigned)splits), dim3(nw * 32), smem, s,
                       tiles, acts, dst, lddst, n, nb, pm);
+}
+
+// B200_GEMV_PREFETCH=0 turns the prefetching form of the one-row Q4_K kernel off (for side-by-side measurements)
+static bool gemv_prefetch_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_GEMV_PREFETCH");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+// B200_GEMV_ROW=0 keeps one-row Q4_K mat-muls on gemv_q4_K_kernel<1, 0> (for side-by-side measurements)
+static bool gemv_row_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_GEMV_ROW");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+static int64_t gemv_stream_max_tiles();
+template <bool PF>
+static int launch_q4k_row_pf(dim3 grid, dim3 block, size_t smem, cudaStream_t s, const uint8_t *tiles, ActView acts, float *dst, int64_t n,
+                             int nb, PairMap pm, const ActPrologue &pro) {
+    switch (pro.mode) {
+        case ACT_PRO_PLAIN: return launch_pdl(gemv_q4_K_row_kernel<PF, ACT_PRO_PLAIN>, grid, block, smem, s, tiles, acts, dst, n, nb, pm, pro);
+        case ACT_PRO_NORM: return launch_pdl(gemv_q4_K_row_kernel<PF, ACT_PRO_NORM>, grid, block, smem, s, tiles, acts, dst, n, nb, pm, pro);
+        case ACT_PRO_SILU: return launch_pdl(gemv_q4_K_row_kernel<PF, ACT_PRO_SILU>, grid, block, smem, s, tiles, acts, dst, n, nb, pm, pro);
+        default: return launch_pdl(gemv_q4_K_row_kernel<PF, ACT_PRO_NONE>, grid, block, smem, s, tiles, acts, dst, n, nb, pm, pro);
+    }
+}
+static int launch_q4k_row(int64_t n, int nb, const uint8_t *tiles, ActView acts, float *dst, cudaStream_t s, PairMap pm = PairMap{},
+                          int64_t pairs = 1, const ActPrologue &pro = ActPrologue{}) {
+    const int nw = pick_warps(nb);
+    const size_t smem = sizeof(Q4KStage) * nw + (size_t)nb * 32 * sizeof(int4) + (size_t)nb * sizeof(float);
+    B200_REQUIRE(smem <= 200 * 1024, "mul_mat q4_K: k too large for the shared-memory exchange (%zu bytes)", smem);
+    const int64_t tiles_n = pm.seg_count > 1 ? pm.seg_total : (n + TILE_ROWS - 1) / TILE_ROWS;
+    // long rows and at most a row tile per SM: the prefetching form (it needs the registers of a whole SM)
+    const bool pf = nb > nw && tiles_n * pairs <= gemv_stream_max_tiles() && gemv_prefetch_enabled();
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    B200_REQUIRE(dev >= 0 && dev < 64, "gemv: device index %d out of range", dev);
+    if (!attr_done[dev]) {
+        B200_CUDA(cudaFuncSetAttribute(gemv_q4_K_row_kernel<false, ACT_PRO_NONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        B200_CUDA(cudaFuncSetAttribute(gemv_q4_K_row_kernel<false, ACT_PRO_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        B200_CUDA(cudaFuncSetAttribute(gemv_q4_K_row_kernel<false, ACT_PRO_NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        B200_CUDA(cudaFuncSetAttribute(gemv_q4_K_row_kernel<false, ACT_PRO_SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        B200_CUDA(cudaFuncSetAttribute(gemv_q4_K_row_kernel<true, ACT_PRO_NONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        B200_CUDA(cudaFuncSetAttribute(gemv_q4_K_row_kernel<true, ACT_PRO_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        B200_CUDA(cudaFuncSetAttribute(gemv_q4_K_row_kernel<true, ACT_PRO_NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        B200_CUDA(cudaFuncSetAttribute(gemv_q4_K_row_kernel<true, ACT_PRO_SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_done[dev] = true;
+    }
+    B200_REQUIRE(pairs >= 1 && pairs <= 65535, "mul_mat_id: %lld (token, slot) pairs exceed one launch", (long long)pairs);
+    B200_REQUIRE(pro.mode == ACT_PRO_NONE || pairs == 1, "mul_mat_id takes no activation prologue");
+    const dim3 grid((unsigned)tiles_n, (unsigned)pairs), block(nw * 32);
+    if (pf) return launch_q4k_row_pf<true>(grid, block, smem, s, tiles, acts, dst, n, nb, pm, pro);
+    return launch_q4k_row_pf<false>(grid, block, smem, s, tiles, acts, dst, n, nb, pm, pro);
 }
 
 // B200_GEMV_KSPLIT=1 splits K over several CTAs per row tile for the few-tile decode mat-muls.  Measured it
@@ -316,8 +617,16 @@ static int launch_q4k_ksplit(int splits, int64_t n, int nb, const uint8_t *tiles
 // walk the row tiles of all of them.  Every output element is computed exactly as by a launch of its own.
 int launch_gemv_q4_K_multi(int count, const int64_t *n, const uint8_t *const *tiles, float *const *dst, int64_t k, ActView acts,
                            cudaStream_t s) {
+    return launch_gemv_q4_K_row_fused(count, n, tiles, dst, k, acts, ActPrologue{}, s);
+}
+
+// The same with an activation prologue (see gemv_q4_K_row_kernel): acts.qs may be null when pro.mode != ACT_PRO_NONE;
+// acts.addend / acts.sum (one matrix only) add the residual in the epilogue.
+int launch_gemv_q4_K_row_fused(int count, const int64_t *n, const uint8_t *const *tiles, float *const *dst, int64_t k, ActView acts,
+                               const ActPrologue &pro, cudaStream_t s) {
     B200_REQUIRE(count >= 1 && count <= 3, "mul_mat multi: %d matrices (1 to 3 fit one launch)", count);
     B200_REQUIRE(k % GROUP_K == 0, "mul_mat multi: k = %lld must be a multiple of 256", (long long)k);
+    B200_REQUIRE(count == 1 || acts.sum == nullptr, "mul_mat multi: the residual add goes with a single matrix");
     PairMap pm = PairMap{};
     pm.seg_count = count;
     pm.seg_end[1] = 0x7fffffff;   // "no third matrix"
@@ -334,6 +643,8 @@ int launch_gemv_q4_K_multi(int count, const int64_t *n, const uint8_t *const *ti
         }
     }
     pm.seg_total = (int)end;
+    if (count == 1) pm.seg_count = 0;
+    if (gemv_row_enabled() || pro.mode != ACT_PRO_NONE) return launch_q4k_row(n[0], (int)(k / GROUP_K), tiles[0], acts, dst[0], s, pm, 1, pro);
     return launch_q4k<1, 0>(n[0], (int)(k / GROUP_K), tiles[0], acts, dst[0], n[0], s, pm);
 }
 
@@ -489,15 +800,19 @@ static int run_generic(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, Ac
     return B200_STATUS_SUCCESS;
 }
 
-// B200_GEMV_STREAM=0 in the environment selects the register-staged kernel instead of the
-// bulk-copy streaming one (for side-by-side measurements); read once.
+// Which kernel a one-row Q4_K mat-mul of at most one row tile per SM takes.  Timed inside a replayed CUDA graph (the
+// way a decode step runs them) the register-staged kernel wins on every shape: 4096 x 4096 3.3 against 4.3 us,
+// 4096 x 14336 10.2 against 11.4 us; the bulk-copy streaming kernel only looked faster when a host loop issued the
+// launches and the host's launch rate was what was being measured.  B200_GEMV_STREAM=1 selects the streaming kernel
+// (read once), and so does the wait test hook while it is armed.
+bool gemv_stream_forced();   // gemv_stream.cu
 static bool gemv_stream_enabled() {
     static int v = -1;
     if (v < 0) {
         const char *e = getenv("B200_GEMV_STREAM");
-        v = (e && e[0] == '0') ? 0 : 1;
+        v = (e && e[0] == '1') ? 1 : 0;
     }
-    return v == 1;
+    return v == 1 || gemv_stream_forced();
 }
 
 // B200_GEMM_MMA=0 keeps prompt batches on the column-pass kernels (for side-by-side measurements)
@@ -523,12 +838,22 @@ static bool gemm_tcgen05_enabled() {
     return v == 1;
 }
 
+// B200_STREAM_TILES_MULT=<m>: matrices of up to m row tiles per SM take the streaming kernel (default 1)
+static int gemv_stream_tiles_mult() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_STREAM_TILES_MULT");
+        v = e ? atoi(e) : 1;
+        if (v < 1) v = 1;
+    }
+    return v;
+}
 static int64_t gemv_stream_max_tiles() {
     static int sms[64] = {0};   // per device: a process may drive GPUs with different SM counts
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
     if (sms[dev] == 0 && cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms[dev] = 0;
-    return sms[dev];
+    return (int64_t)sms[dev] * gemv_stream_tiles_mult();
 }
 
 int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst,
@@ -578,7 +903,10 @@ int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint
             } else if (main_part) {
                 rc = nc == 1 ? launch_q4k<1, 1>(n, nb, tiles, a, o, lddst, s) : launch_q4k<2, 1>(n, nb, tiles, a, o, lddst, s);
             } else {
-                rc = nc == 1 ? launch_q4k<1, 0>(n, nb, tiles, a, o, lddst, s)
+                // one activation row, long rows and at most a row tile per SM: the prefetching form
+                const bool pf = nc == 1 && nb > GEMV_MAX_WARPS && (n + TILE_ROWS - 1) / TILE_ROWS <= gemv_stream_max_tiles() && gemv_prefetch_enabled();
+                rc = nc == 1 && m == 1 && gemv_row_enabled() ? launch_q4k_row(n, nb, tiles, a, o, s)
+                   : nc == 1 ? (pf ? launch_q4k<1, 0, true>(n, nb, tiles, a, o, lddst, s) : launch_q4k<1, 0>(n, nb, tiles, a, o, lddst, s))
                    : nc == 2 ? launch_q4k<2, 0>(n, nb, tiles, a, o, lddst, s)
                              : launch_q4k<3, 0>(n, nb, tiles, a, o, lddst, s);
             }
@@ -627,7 +955,8 @@ int launch_mul_mat_id(int type, int64_t n, int64_t k, int64_t n_expert, int64_t 
     const bool repack = n % 8 == 0;
     if (type == B200_TYPE_MXFP4 && repack) return launch_generic<TraitsB32<true>, 1>(n, nb, tiles, acts, dst, n, s, pm, pairs);
     if (type == B200_TYPE_Q4_0 && repack) return launch_generic<TraitsB32<false>, 1>(n, nb, tiles, acts, dst, n, s, pm, pairs);
-    if (type == B200_TYPE_Q4_K && repack) return launch_q4k<1, 0>(n, nb, tiles, acts, dst, n, s, pm, pairs);
+    if (type == B200_TYPE_Q4_K && repack)
+        return gemv_row_enabled() ? launch_q4k_row(n, nb, tiles, acts, dst, s, pm, pairs) : launch_q4k<1, 0>(n, nb, tiles, acts, dst, n, s, pm, pairs);
     if (type == B200_TYPE_Q8_0) return launch_generic<TraitsQ8_0, 1>(n, nb, tiles, acts, dst, n, s, pm, pairs);
     if (type == B200_TYPE_Q4_K || type == B200_TYPE_Q6_K) {
         B200_CUDA(cudaMemsetAsync(counts, 0, sizeof(int) * n_expert, s));

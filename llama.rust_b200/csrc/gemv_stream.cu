@@ -317,6 +317,8 @@ void gemv_stream_debug_wait(int spin_limit, int skip_unit) {
     g_wait_limit_override = spin_limit > 0 ? spin_limit : 0;
     g_skip_unit_override = skip_unit >= 0 ? skip_unit : -1;
 }
+// while the hook is armed (a poll limit is set) one-row Q4_K mat-muls take the streaming kernel
+bool gemv_stream_forced() { return g_wait_limit_override > 0; }
 
 // the current device's error word; kernels that skip a bad index or give up a wait store a non-zero code there
 // and b200_kernel_error() reads and clears it
@@ -334,7 +336,21 @@ int device_error_word(int **flag) {
     return B200_STATUS_SUCCESS;
 }
 
-int launch_gemv_q4_K_stream(int64_t n, int64_t k, const uint8_t *tiles, ActView acts, float *dst, cudaStream_t s) {
+// B200_STREAM_VARIANT: 0 (default) = 16 consumer warps, up to 216 KB of shared memory, one CTA per SM;
+// 1 = 8 consumer warps and at most 104 KB, so that two CTAs (of this launch, or of this launch and the next one in
+// the stream, which starts its weight prefetch early under programmatic dependent launch) share an SM.
+int gemv_stream_variant() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_STREAM_VARIANT");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v;
+}
+
+template <int CW>
+static int launch_stream_variant(int64_t n, int64_t k, const uint8_t *tiles, ActView acts, float *dst, cudaStream_t s, size_t budget,
+                                 int ctas_per_sm) {
     const int nb = (int)(k / GROUP_K);
     const int n_tiles = (int)((n + TILE_ROWS - 1) / TILE_ROWS);
     int dev = 0;
@@ -346,7 +362,7 @@ int launch_gemv_q4_K_stream(int64_t n, int64_t k, const uint8_t *tiles, ActView 
         cudaDeviceProp p;
         B200_CUDA(cudaGetDeviceProperties(&p, dev));
         sm_count[dev] = p.multiProcessorCount;
-        B200_CUDA(cudaFuncSetAttribute(gemv_q4_K_stream_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+        B200_CUDA(cudaFuncSetAttribute(gemv_q4_K_stream_kernel<CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
 
         int *flag = nullptr;
         int rc = device_error_word(&flag);
@@ -354,26 +370,27 @@ int launch_gemv_q4_K_stream(int64_t n, int64_t k, const uint8_t *tiles, ActView 
         attr_done[dev] = true;
     }
     // exchange buffers and ring stages: the ring may not run more than (xb - 1) tiles ahead of an
-    // unfinished tile (see the kernel), and everything has to fit in 216 KB of shared memory
+    // unfinished tile (see the kernel), and everything has to fit in the shared-memory budget
+    constexpr int NSETS = CW / STAGE_GROUPS;
     const int spt = (nb + STAGE_GROUPS - 1) / STAGE_GROUPS;
     int xb = 2, stages = 0;
     for (int cand = MAX_XB; cand >= 2; cand--) {
         const size_t fixed = stream_fixed_bytes(nb, cand);
-        if (fixed + (size_t)2 * STAGE_BYTES > 216 * 1024) continue;
-        int st = (int)((216 * 1024 - fixed) / STAGE_BYTES);
+        if (fixed + (size_t)2 * STAGE_BYTES > budget) continue;
+        int st = (int)((budget - fixed) / STAGE_BYTES);
         if (st > (cand - 1) * spt) st = (cand - 1) * spt;
         if (st > MAX_STAGES) st = MAX_STAGES;
-        st -= st % 2;   // a multiple of the consumer set count (16 warps / 8 groups per stage)
+        st -= st % NSETS;   // a multiple of the consumer set count
         if (st > stages) { stages = st; xb = cand; }
     }
-    B200_REQUIRE(stages >= 2, "gemv stream: k = %lld leaves no room for the copy ring", (long long)k);
+    B200_REQUIRE(stages >= 2 && stages >= NSETS, "gemv stream: k = %lld leaves no room for the copy ring", (long long)k);
     const size_t smem = stream_fixed_bytes(nb, xb) + (size_t)stages * STAGE_BYTES;
-    const int grid = n_tiles < sm_count[dev] ? n_tiles : sm_count[dev];
+    const int max_ctas = sm_count[dev] * ctas_per_sm;
+    const int grid = n_tiles < max_ctas ? n_tiles : max_ctas;
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    constexpr int cw = 16;
-    cfg.blockDim = dim3((cw + 1) * 32);
+    cfg.blockDim = dim3((CW + 1) * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
@@ -381,9 +398,14 @@ int launch_gemv_q4_K_stream(int64_t n, int64_t k, const uint8_t *tiles, ActView 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    B200_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4_K_stream_kernel<cw>, tiles, acts, dst, n, nb, n_tiles, stages, xb, g_err_flag[dev],
+    B200_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4_K_stream_kernel<CW>, tiles, acts, dst, n, nb, n_tiles, stages, xb, g_err_flag[dev],
                                  g_wait_limit_override > 0 ? (unsigned)g_wait_limit_override : SPIN_LIMIT, g_skip_unit_override));
     return B200_STATUS_SUCCESS;
+}
+
+int launch_gemv_q4_K_stream(int64_t n, int64_t k, const uint8_t *tiles, ActView acts, float *dst, cudaStream_t s) {
+    if (gemv_stream_variant() == 1) return launch_stream_variant<8>(n, k, tiles, acts, dst, s, (size_t)104 * 1024, 2);
+    return launch_stream_variant<16>(n, k, tiles, acts, dst, s, (size_t)216 * 1024, 1);
 }
 
 // 0 = no streaming kernel has given up a wait on this device since the last call

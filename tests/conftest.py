@@ -5,6 +5,10 @@ import numpy as np
 import pytest
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+# The tests compare with the CPU oracle bit for bit unless they say otherwise: the library starts in its exact
+# numerics mode here (read when it is loaded, inherited by child processes); tolerance-mode tests switch to fast
+# around their own calls.
+os.environ.setdefault("B200_NUMERICS", "exact")
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 

@@ -1,0 +1,109 @@
+"""FLASH_ATTN_EXT in the library's fast numerics mode (f32 accumulation, no ordered f16 chain) against the CPU
+oracle and against a float64 evaluation of softmax(q k^T scale + mask) v (-m gpu).
+
+Tolerance asked of F16-KV attention: 1e-3, applied per output row relative to the row's largest magnitude (an
+element near zero has no meaningful relative error of its own).  Three distances are measured and printed for
+every case: GPU - CPU, GPU - f64 and CPU - f64.  The CPU path itself sits 2e-3 (512 cached positions) to 1.6e-2
+(32768) away from f64: with F16 values it keeps its accumulator in f16 and rounds it once per position
+(crates/ggml/src/flash_attn.rs:583-641; the reference's own test allows 1e-2 there, :1631-1636).  No kernel that
+computes the function accurately can therefore be within 1e-3 of the CPU's bits at those lengths; what is
+required here is that the fast kernel is within 1e-3 of f64, and no further from f64 than the CPU path is, which
+bounds its distance from the CPU by the CPU's own error.  (The exact kernels of the other test files reproduce
+the CPU's bits, f16 chain included.)"""
+import numpy as np
+import pytest
+
+import b200
+import orc
+from test_gpu_flash_attn import synth_case
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+@pytest.fixture(scope="module")
+def dev():
+    mod = b200.load()
+    assert mod.device_count() > 0
+    mod.set_device(0)
+    return mod
+
+
+def ref64(q, k, v, mask, scale):
+    """q f32 [H, T, D]; k, v f16 bits [Hkv, n_kv, D]; mask f16 bits [T, n_kv] -> f64 [T, H, D]"""
+    H, T, D = q.shape
+    G = H // k.shape[0]
+    kf, vf = k.view(np.float16).astype(np.float64), v.view(np.float16).astype(np.float64)
+    m = np.zeros((T, k.shape[1])) if mask is None else mask.view(np.float16).astype(np.float64)
+    out = np.zeros((T, H, v.shape[2]))
+    for h in range(H):
+        s = q[h].astype(np.float64) @ kf[h // G].T * scale + m
+        s = s - s.max(axis=1, keepdims=True)
+        p = np.exp(s)
+        out[:, h] = (p / p.sum(axis=1, keepdims=True)) @ vf[h // G]
+    return out
+
+
+def row_rel(a, b):
+    """largest |a - b| per output row over the row's largest |b|"""
+    return float((np.abs(a - b).max(axis=-1) / np.maximum(np.abs(b).max(axis=-1), 1e-30)).max())
+
+
+def run_fast(dev, q, k, v, mask, scale, **kw):
+    dev.set_numerics(dev.FAST)
+    try:
+        return dev.flash_attn(q, dev.KvCacheView(k, v), mask, scale, **kw)
+    finally:
+        dev.set_numerics(dev.EXACT)
+
+
+@pytest.mark.parametrize("n_kv", [512, 768, 4096, 32768])
+def test_decode_one_row_gqa_128(dev, n_kv):
+    """the benchmark's decode shape: 32 query heads on 8 KV heads of 128, one query row, causal mask"""
+    scale = 1.0 / np.sqrt(128.0)
+    q, k, v, mask = synth_case(32, 8, 128, 1, n_kv, seed=n_kv + 1)
+    cpu, _ = orc.flash_attn(q, k, v, mask, scale, n_chunks=8)
+    want = ref64(q, k, v, mask, scale)
+    got = run_fast(dev, q, k, v, mask, scale)
+    d_gc, d_g64, d_c64 = row_rel(got, cpu), row_rel(got, want), row_rel(cpu, want)
+    print(f"decode n_kv={n_kv}: GPU-CPU {d_gc:.2e}  GPU-f64 {d_g64:.2e}  CPU-f64 {d_c64:.2e}")
+    assert d_g64 <= TOL
+    assert d_g64 <= max(d_c64, 1e-5)
+    assert d_gc <= 1.05 * (d_c64 + d_g64) + 1e-6
+
+
+@pytest.mark.parametrize("shape", [(16, 3072, 128), (5, 300, 64), (2, 700, 128), (63, 200, 128)], ids=str)
+def test_few_rows_with_ragged_masks(dev, shape):
+    """several rows, each with its own visible cells (batched decode over a shared cache), a row that sees nothing,
+    a context that is not a multiple of the tile"""
+    T, n_kv, D = shape
+    q, k, v, _ = synth_case(8, 2, D, T, n_kv, seed=T * 7 + n_kv, causal=False)
+    rng = np.random.default_rng(T)
+    m = np.full((T, n_kv), -np.inf, dtype=np.float16)
+    for t in range(T):
+        lo = int(rng.integers(0, n_kv // 2))
+        m[t, lo:lo + max(1, n_kv // (T + 1))] = 0.0
+        m[t, n_kv - 1 - t % 3] = 0.0
+    if T > 2:
+        m[2, :] = -np.inf
+    mask = m.view(np.uint16)
+    scale = 1.0 / np.sqrt(float(D))
+    cpu, _ = orc.flash_attn(q, k, v, mask, scale)
+    got = run_fast(dev, q, k, v, mask, scale)
+    if T > 2:
+        assert not got[2].any() and not cpu[2].any()
+    live = [t for t in range(T) if not (T > 2 and t == 2)]
+    with np.errstate(invalid="ignore"):
+        want = ref64(q, k, v, mask, scale)
+    d_gc, d_g64, d_c64 = row_rel(got[live], cpu[live]), row_rel(got[live], want[live]), row_rel(cpu[live], want[live])
+    print(f"rows {shape}: GPU-CPU {d_gc:.2e}  GPU-f64 {d_g64:.2e}  CPU-f64 {d_c64:.2e}")
+    assert d_g64 <= TOL and d_g64 <= max(d_c64, 1e-5)
+
+
+def test_unsupported_variants_fall_back_to_the_exact_kernels(dev):
+    """sinks and softcap are not in the fast kernel: the call still succeeds and gives the exact path's bits"""
+    q, k, v, mask = synth_case(8, 2, 64, 1, 600, seed=5)
+    sinks = np.random.default_rng(3).standard_normal(8).astype(np.float32)
+    want, _ = orc.flash_attn(q, k, v, mask, 0.125, sinks=sinks, n_chunks=8)
+    got = run_fast(dev, q, k, v, mask, 0.125, sinks=sinks, n_chunks=8)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))

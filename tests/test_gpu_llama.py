@@ -151,8 +151,9 @@ def test_argument_errors_are_statuses(ll):
 
 
 def test_launch_fusions_change_nothing(ll, monkeypatch):
-    """sibling mat-muls in one launch and ROPE / SET_ROWS in one launch (the defaults) against one launch per
-    node: the same logits, prompt batch and single-token steps, with and without CUDA graphs"""
+    """sibling mat-muls in one launch, ROPE / SET_ROWS in one launch and the norm / silu / quantization in front of a
+    one-row mat-mul inside its kernel (the defaults) against one launch per node: the same logits, prompt batch and
+    single-token steps, with and without CUDA graphs"""
     tensors = make_model(ll, GQA128, 31)
 
     def run():
@@ -166,6 +167,7 @@ def test_launch_fusions_change_nothing(ll, monkeypatch):
     fused = run()
     monkeypatch.setenv("B200_FUSE_SIBLINGS", "0")
     monkeypatch.setenv("B200_FUSE_GLUE", "0")
+    monkeypatch.setenv("B200_FUSE_PROLOGUE", "0")
     plain = run()
     monkeypatch.setenv("B200_CUDA_GRAPHS", "0")
     eager = run()

@@ -139,16 +139,20 @@ def test_q4_K_full_size_periodic_rows(dev):
 def test_streaming_kernel_many_launches_no_wait_expired(dev):
     """Back-to-back launches of the bulk-copy streaming kernel (the second launch starts its weight
     prefetch while the first still runs); all bit-exact, and no bounded wait ran out."""
-    n, k = 14336, 4096
+    n, k = 4096, 4096
     W = synth.weights(orc.Q4_K, n, k, seed=33, period=1024)
     w = dev.Weight(orc.Q4_K, W, k)
     xs = [synth.activations(1, k, seed=100 + i) for i in range(3)]
     dxs = [dev.device_array(x) for x in xs]
     outs = [dev.DeviceBuffer(4 * n) for _ in xs]
-    for _ in range(5):
-        for dx, do in zip(dxs, outs):
-            dev.mul_mat_device(w, dx, 1, do)
-    dev.synchronize()
+    dev.lib.b200_debug_stream_wait(1 << 20, -1)   # select the streaming kernel (the normal poll limit, nothing skipped)
+    try:
+        for _ in range(5):
+            for dx, do in zip(dxs, outs):
+                dev.mul_mat_device(w, dx, 1, do)
+        dev.synchronize()
+    finally:
+        dev.lib.b200_debug_stream_wait(0, -1)
     assert dev.kernel_error() == 0
     for x, do in zip(xs, outs):
         want, _ = orc.mul_mat(orc.Q4_K, W, x)

@@ -30,8 +30,12 @@ def test_streaming_kernel_wait_expiry_reports_a_code_and_the_next_launch_is_exac
     out = dev.DeviceBuffer(4 * n)
     want, _ = orc.mul_mat(orc.Q4_K, W, x)
 
-    dev.mul_mat_device(w, dx, 1, out)   # a normal launch first: the kernel is the streaming one and works
-    dev.synchronize()
+    dev.lib.b200_debug_stream_wait(1 << 20, -1)   # the streaming kernel with its normal poll limit, nothing skipped
+    try:
+        dev.mul_mat_device(w, dx, 1, out)         # a normal launch first: the kernel works
+        dev.synchronize()
+    finally:
+        dev.lib.b200_debug_stream_wait(0, -1)
     assert dev.kernel_error() == 0
     assert bits_equal(out.download(np.float32, n), want.ravel())
 
@@ -47,8 +51,12 @@ def test_streaming_kernel_wait_expiry_reports_a_code_and_the_next_launch_is_exac
     assert dev.kernel_error() == 0   # the read cleared it
     assert (out.download(np.uint32, n) == 0xFFFFFFFF).all(), "an aborted row tile must not store results"
 
-    dev.mul_mat_device(w, dx, 1, out)
-    dev.synchronize()
+    dev.lib.b200_debug_stream_wait(1 << 20, -1)
+    try:
+        dev.mul_mat_device(w, dx, 1, out)         # the same kernel again, undisturbed
+        dev.synchronize()
+    finally:
+        dev.lib.b200_debug_stream_wait(0, -1)
     assert dev.kernel_error() == 0
     assert bits_equal(out.download(np.float32, n), want.ravel())
 
