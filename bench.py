@@ -34,7 +34,11 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 Q4_K = 12
 SHAPES = [(4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096)]  # (n rows, k)
 METRIC = "q4_K_decode_mat_mul_hbm_gbs"
-NCU_TRAFFIC_RATIO = 33.05 / 33.03   # measured DRAM bytes / algorithmic bytes of one decode mat-mul launch (see roofline.traffic)
+CPU_KIND = "port"   # the CPU arm is the oracle's C++ restatement of the reference's routes (no Rust toolchain here)
+# measured DRAM bytes / algorithmic bytes of one launch of the decode kernel in use (gemv_q4_K_row_kernel on
+# 14336 x 4096: dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture summarized in
+# profiles/gemv_q4_K_row_kernel_decode.md); weights are read once whatever the shape
+NCU_TRAFFIC_RATIO = 33.11 / 33.03
 PROMPT, GEN = 512, 128
 
 
@@ -52,10 +56,21 @@ def load_pkg():
     return sys.modules["llama_rust_b200"]
 
 
-def synth_weights(n, k, seed):
-    """random well-formed Q4_K blocks (llama.rust_b200/synth.py); timing does not depend on the values"""
-    load_pkg()
-    return importlib.import_module("llama_rust_b200.synth").blocks(Q4_K, n, k, seed=seed)
+def load_standalone(name):
+    """llama.rust_b200/<name>.py loaded by path, WITHOUT the package (and so without libggml-b200.so): the CPU arms
+    build the same synthetic inputs as the GPU arm and map nothing but the oracle"""
+    key = f"_b200_standalone_{name}"
+    if key not in sys.modules:
+        spec = importlib.util.spec_from_file_location(key, os.path.join(ROOT, "llama.rust_b200", name + ".py"))
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[key] = mod
+        spec.loader.exec_module(mod)
+    return sys.modules[key]
+
+
+def synth_weights(n, k, seed, ty=Q4_K):
+    """random well-formed blocks (llama.rust_b200/synth.py); timing does not depend on the values"""
+    return load_standalone("synth").blocks(ty, n, k, seed=seed)
 
 
 def load_oracle():
@@ -238,8 +253,10 @@ def run_gemv(b, args, rank, world, barrier, reduce_max, local):
     barrier()
     ms = reduce_max(ms)
 
-    # the mat-mul kernel alone (activations already quantized), per shape: back-to-back launches rotating over
-    # enough weight copies to exceed twice the L2, one pair of CUDA events around the batch
+    # the mat-mul kernel alone (activations already quantized), per shape: launches rotating over enough weight copies
+    # to exceed twice the L2, captured into ONE CUDA graph and replayed, CUDA events around the replay on the launching
+    # stream (b200_bench_mul_mat_q8): what the kernel costs inside a decode step, where a replayed graph issues the
+    # launches; a host loop over the entry point measures the host's launch rate for the small shapes
     kern_ms, per_shape = [], {}
     launches = max(4 * args.steps, 100)
     for (n, k), w0, dx, do, act in zip(SHAPES, weights, dxs, douts, acts):
@@ -247,22 +264,9 @@ def run_gemv(b, args, rank, world, barrier, reduce_max, local):
         wbytes = n * k * 144 // 256
         copies = max(2, min(32, (300 << 20) // wbytes + 1))
         ws = [w0] + [b.Weight(Q4_K, w0.download(), k) for _ in range(copies - 1)]
-
-        def launch(i):
-            w = ws[i % copies]
-            b.check(b.lib.b200_mul_mat_q8(Q4_K, n, k, 1, w.ptr, act.ptr, b.ACT_Q8_K, do.ptr, n, 0, None), "mul_mat_q8")
-
-        for i in range(copies):
-            launch(i)
-        b.synchronize()
-        a, z = b.Event(), b.Event()
-        a.record()
-        for i in range(launches):
-            launch(i)
-        z.record()
-        z.synchronize()
-        t = a.elapsed_ms(z) / launches
-        per_shape[f"{n}x{k}"] = {"us": t * 1e3, "gbs": algorithmic_bytes(n, k) / (t * 1e-3) / 1e9, "copies": copies}
+        t = b.bench_mul_mat_q8(ws, act, b.ACT_Q8_K, do, 1, launches) * 1e-3
+        per_shape[f"{n}x{k}"] = {"us": t * 1e3, "gbs": algorithmic_bytes(n, k) / (t * 1e-3) / 1e9, "frac": algorithmic_bytes(n, k) / (t * 1e-3) / 1e9 / peak_hbm()[0],
+                                 "copies": copies}
         kern_ms.append(t)
         del ws
     clocks = sampler.stop() if rank == 0 else None
@@ -282,27 +286,27 @@ def run_gemv(b, args, rank, world, barrier, reduce_max, local):
         "e2e": {"value": world * total * args.steps / e2e_s / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": sum(4 * k for _, k in SHAPES), "d2h_bytes_per_step": sum(4 * n for n, _ in SHAPES)},
         "gpu_launches": args.steps * 2 * len(SHAPES),
-        "roofline": {"bound": "hbm", "kernel": "gemv_q4_K_kernel<1,0> / gemv_q4_K_stream_kernel (Q4_K decode mat-mul)",
+        "roofline": {"bound": "hbm", "kernel": "gemv_q4_K_row_kernel (Q4_K decode mat-mul, one activation row)",
                      "achieved": kern_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": kern_gbs / peak,
-                     # bytes per step (the four launches): the ncu capture of the 14336 x 4096 launch read and wrote
-                     # 33.05 MB of DRAM for 33.03 MB algorithmic (profiles/gemv_q4_K_decode_first_kernel.md); weights are
-                     # read once whatever the shape, so the step's traffic is its algorithmic bytes times that ratio
-                     "traffic": total * NCU_TRAFFIC_RATIO, "traffic_source": "ncu capture of one shape, scaled by algorithmic bytes",
+                     "timing": "per shape: launches over rotating weight copies (> 2 x L2) replayed as one CUDA graph, CUDA events on the launching stream",
+                     # bytes per step (the four launches)
+                     "traffic": total * NCU_TRAFFIC_RATIO, "traffic_source": "ncu capture of this kernel on 14336x4096 (profiles/), scaled by algorithmic bytes",
                      "per_shape": per_shape},
     }
 
 
 # ---- the Llama-3-8B-shaped decoder ------------------------------------------------------------------------
-def llama_hparams(n_layer):
-    ll = importlib.import_module("llama_rust_b200.llama")
-    hp = dict(ll.LLAMA3_8B)
+def llama_hparams(n_layer, shape="8b"):
+    """(shapes module, hyper-parameters); pure Python, no library"""
+    sh = load_standalone("shapes")
+    hp = dict(sh.LLAMA3_70B if shape == "70b" else sh.LLAMA3_8B)
     hp["n_layer"] = n_layer
-    return ll, hp
+    return sh, hp
 
 
 def llama_weight_bytes(ll, hp):
     """bytes of quantized weights one decode step streams: every matrix once, one row of token_embd"""
-    syn = importlib.import_module("llama_rust_b200.synth")
+    syn = load_standalone("synth")
     total = 0
     for name, (ne0, ne1) in ll.tensor_shapes(hp).items():
         ty = ll.q4_k_m_type(name, hp["n_layer"])
@@ -314,12 +318,14 @@ def llama_weight_bytes(ll, hp):
     return total
 
 
-def build_llama(n_layer, n_ctx=1024, n_batch=PROMPT, keep_host=False, device=0):
-    ll, hp = llama_hparams(n_layer)
-    syn = importlib.import_module("llama_rust_b200.synth")
+def build_llama(n_layer, n_ctx=1024, n_batch=PROMPT, keep_host=False, device=0, shape="8b"):
+    load_pkg()
+    sh, hp = llama_hparams(n_layer, shape)
+    ll = importlib.import_module("llama_rust_b200.llama")
+    syn = load_standalone("synth")
     gpu = ll.Llama(hp, n_ctx, n_batch, device=device, cpu_threads=8)
     host = {}
-    for name, ty, arr, ne0, ne1 in syn.llama_tensors(hp, lambda n: ll.q4_k_m_type(n, n_layer)):
+    for name, ty, arr, ne0, ne1 in syn.llama_tensors(hp, lambda n: sh.q4_k_m_type(n, n_layer), tensor_shapes=sh.tensor_shapes):
         gpu.set_tensor(name, ty, arr, ne0, ne1)
         if keep_host:
             host[name] = (ty, arr, ne0, ne1)
@@ -361,11 +367,9 @@ def run_llama_batch16(gpu, hp, world, barrier, reduce_max):
             "cache": f"unified, {N_SEQ * (PROMPT + GEN)} cells in use at the end; a row's mask hides the other sequences' cells"}
 
 
-def run_llama(b, args, rank, world, barrier, reduce_max):
-    """pp512 + tg128, batch 1, one replica per rank"""
-    ll, hp, gpu, _ = build_llama(args.layers, n_ctx=N_SEQ * (PROMPT + GEN), device=int(os.environ.get("LOCAL_RANK", "0")))
-    rng = np.random.default_rng(0)
-    prompt = rng.integers(0, hp["n_vocab"], PROMPT).astype(np.int32)
+def time_llama_passes(gpu, hp, world, barrier, reduce_max, warm=2, reps=3):
+    """pp512 + tg128 of one driver in the library's current numerics mode -> (pp_e2e, pp_dev, tg_e2e, tg_dev, tokens)"""
+    prompt = np.random.default_rng(0).integers(0, hp["n_vocab"], PROMPT).astype(np.int32)
     pos = np.arange(PROMPT, dtype=np.int32)
 
     def one_pass():
@@ -383,33 +387,94 @@ def run_llama(b, args, rank, world, barrier, reduce_max):
         tg_dev = gpu.replay(GEN) / GEN
         return t1 - t0, pp_dev * 1e-3, (t3 - t2) / GEN, tg_dev * 1e-3, toks
 
-    for _ in range(3):   # warm-up passes: allocations, graph capture
+    for _ in range(warm):   # warm-up passes: allocations, graph capture
         one_pass()
     barrier()
-    res = [one_pass() for _ in range(3)]
+    res = [one_pass() for _ in range(reps)]
     barrier()
-    pp_e2e = reduce_max(statistics.median(r[0] for r in res))
-    pp_dev = reduce_max(statistics.median(r[1] for r in res))
-    tg_e2e = reduce_max(statistics.median(r[2] for r in res))
-    tg_dev = reduce_max(statistics.median(r[3] for r in res))
+    return tuple(reduce_max(statistics.median(r[k] for r in res)) for k in range(4)) + (res[-1][4],)
+
+
+PARITY_PROMPT, PARITY_STEPS = 16, 4
+
+
+def gpu_greedy_trace(gpu, hp):
+    """the logits of a 16-token prompt's last token and of 4 greedy steps after it, with the tokens fed (the same
+    prompt the CPU leg of the benchmark runs)"""
+    prompt = np.random.default_rng(0).integers(0, hp["n_vocab"], PARITY_PROMPT).astype(np.int32)
+    gpu.kv_clear()
+    logits, tok = gpu.decode(prompt, np.arange(PARITY_PROMPT), logits=True, argmax=True)
+    trace, toks = [logits], [int(tok)]
+    for i in range(PARITY_STEPS):
+        logits, tok = gpu.decode([toks[-1]], [PARITY_PROMPT + i], logits=True, argmax=True)
+        trace.append(logits)
+        toks.append(int(tok))
+    return trace, toks
+
+
+def compare_greedy(gpu_trace, gpu_toks, cpu_trace, cpu_toks):
+    """greedy-stream parity of a GPU run against the CPU port: are the token streams identical, where do they first
+    differ, and how far apart are the logits while the streams still agree"""
+    first, worst, bits = None, 0.0, True
+    for i, (g, c) in enumerate(zip(gpu_trace, cpu_trace)):
+        worst = max(worst, float(np.abs(g - c).max() / max(float(np.abs(c).max()), 1e-30)))
+        bits = bits and bool(np.array_equal(g.view(np.uint32), c.view(np.uint32)))
+        if gpu_toks[i] != cpu_toks[i]:
+            first = i
+            break
+    return {"identical": first is None, "first_divergence": first, "steps_compared": len(gpu_trace) if first is None else first + 1,
+            "max_rel_logit_err": worst, "logits_bit_identical": bits if first is None else False,
+            "tokens": gpu_toks, "cpu_tokens": cpu_toks}
+
+
+def run_llama(b, args, rank, world, barrier, reduce_max):
+    """pp512 + tg128, batch 1, one replica per rank; the fast numerics mode (the library's default) and the exact one"""
+    ll, hp, gpu, _ = build_llama(args.layers, n_ctx=N_SEQ * (PROMPT + GEN), device=int(os.environ.get("LOCAL_RANK", "0")))
     peak, peak_src = peak_hbm()
     wbytes = llama_weight_bytes(ll, hp)
-    out = {
-        "config": {"workload": f"Llama-3-8B shape ({hp['n_layer']} layers, d_model 4096, 32/8 heads, FFN 14336, vocab 128256), "
-                               "Q4_K_M tensor types, F16 KV cache, batch 1: 512-token prompt then 128 greedy steps",
-                   "weights": "seeded random well-formed blocks", "tokens": "uniform random prompt ids, seeded"},
-        "pp512_tok_s": world * PROMPT / pp_dev, "pp512_e2e_tok_s": world * PROMPT / pp_e2e,
-        "tg128_tok_s": world / tg_dev, "tg128_e2e_tok_s": world / tg_e2e,
-        "pp512_ms": pp_dev * 1e3, "tg128_ms_per_token": tg_dev * 1e3,
-        "e2e_bytes_per_step": {"h2d": "token ids, positions, F16 mask, cache row indices", "d2h": "4 (argmax)"},
-        "roofline": {"bound": "hbm", "what": "tg128: quantized weight bytes one step streams / device time of the step",
-                     "bytes_per_token": wbytes, "achieved": wbytes / tg_dev / 1e9, "peak": peak, "peak_source": peak_src,
-                     "unit": "GB/s", "frac": wbytes / tg_dev / 1e9 / peak},
-        "greedy_tokens_head": [int(t) for t in res[-1][4][:8]],
-    }
-    out["batch16"] = run_llama_batch16(gpu, hp, world, barrier, reduce_max)
+    out = {"config": {"workload": f"Llama-3-8B shape ({hp['n_layer']} layers, d_model 4096, 32/8 heads, FFN 14336, vocab 128256), "
+                                  "Q4_K_M tensor types, F16 KV cache, batch 1: 512-token prompt then 128 greedy steps",
+                      "weights": "seeded random well-formed blocks", "tokens": "uniform random prompt ids, seeded",
+                      "device_time": "tg128_tok_s / pp512_tok_s: the step's captured CUDA graph replayed on the stream with the last "
+                                     "step's inputs (kernel time of a step); *_e2e_*: the driver call per step, host ids in, argmax out"}}
+    traces = {}
+    for mode, name in ((b.FAST, "fast"), (b.EXACT, "exact")):
+        b.set_numerics(mode)
+        pp_e2e, pp_dev, tg_e2e, tg_dev, toks = time_llama_passes(gpu, hp, world, barrier, reduce_max, warm=2 if name == "fast" else 1,
+                                                                 reps=3 if name == "fast" else 2)
+        res = {"pp512_tok_s": world * PROMPT / pp_dev, "pp512_e2e_tok_s": world * PROMPT / pp_e2e,
+               "tg128_tok_s": world / tg_dev, "tg128_e2e_tok_s": world / tg_e2e,
+               "pp512_ms": pp_dev * 1e3, "tg128_ms_per_token": tg_dev * 1e3,
+               "roofline": {"bound": "hbm", "what": "tg128: quantized weight bytes one step streams / device time of the step",
+                            "bytes_per_token": wbytes, "achieved": wbytes / tg_dev / 1e9, "peak": peak, "peak_source": peak_src,
+                            "unit": "GB/s", "frac": wbytes / tg_dev / 1e9 / peak},
+               "greedy_tokens_head": [int(t) for t in toks[:8]]}
+        if name == "fast":
+            out.update(res)
+            out["numerics"] = "fast (the library's default: attention accumulates in f32, 1e-6 from float64; every mat-mul bit-exact)"
+            out["e2e_bytes_per_step"] = {"h2d": "token ids, positions, F16 mask, cache row indices", "d2h": "4 (argmax)"}
+            out["batch16"] = run_llama_batch16(gpu, hp, world, barrier, reduce_max)
+        else:
+            out["exact_numerics"] = res
+        if world == 1:
+            traces[name] = gpu_greedy_trace(gpu, hp)
+    b.set_numerics(b.FAST)
     gpu.close()
-    return out
+    return out, traces
+
+
+def run_llama_70b_one_gpu(b, args):
+    """the 70B shape on ONE GPU (40 GB of Q4_K_M weights fit): the base of the tensor-parallel strong-scaling curve"""
+    ll, hp, gpu, _ = build_llama(80 if args.layers == 32 else args.layers, n_ctx=1024, shape="70b")
+    ident = lambda v: v
+    pp_e2e, pp_dev, tg_e2e, tg_dev, _ = time_llama_passes(gpu, hp, 1, (lambda: None), ident, warm=1, reps=2)
+    wbytes = llama_weight_bytes(ll, hp)
+    peak, peak_src = peak_hbm()
+    gpu.close()
+    return {"tp": 1, "shape": "70b", "pp512_tok_s": PROMPT / pp_dev, "pp512_e2e_tok_s": PROMPT / pp_e2e, "tg128_tok_s": 1.0 / tg_dev,
+            "tg128_e2e_tok_s": 1.0 / tg_e2e, "pp512_ms": pp_dev * 1e3, "tg128_ms_per_token": tg_dev * 1e3,
+            "roofline": {"bound": "hbm", "bytes_per_token": wbytes, "achieved": wbytes / tg_dev / 1e9, "peak": peak, "peak_source": peak_src,
+                         "unit": "GB/s", "frac": wbytes / tg_dev / 1e9 / peak}}
 
 
 def run_llama_tp(b, args, rank, world, local, barrier, reduce_max, shape):
@@ -419,7 +484,7 @@ def run_llama_tp(b, args, rank, world, local, barrier, reduce_max, shape):
     import torch
     import torch.distributed as dist
     ll = importlib.import_module("llama_rust_b200.llama")
-    syn = importlib.import_module("llama_rust_b200.synth")
+    syn = load_standalone("synth")
     hp = dict(ll.LLAMA3_70B if shape == "70b" else ll.LLAMA3_8B)
     if args.layers != 32:   # a shortened model for a quick check of the multi-rank path
         hp["n_layer"] = args.layers
@@ -454,32 +519,36 @@ def run_llama_tp(b, args, rank, world, local, barrier, reduce_max, shape):
         tg_dev = gpu.replay(GEN) / GEN
         return t1 - t0, pp_dev * 1e-3, (t3 - t2) / GEN, tg_dev * 1e-3
 
-    for _ in range(3):
+    kind = gpu.tp_exchange_kind()
+    for _ in range(2):
         one_pass()
     res = [one_pass() for _ in range(3)]
     barrier()
     pp_e2e, pp_dev, tg_e2e, tg_dev = (reduce_max(statistics.median(r[k] for r in res)) for k in range(4))
     gpu.close()
     return {"tp": world, "scaling": "strong", "shape": shape,
+            "collectives": ("decode steps: one kernel of the library per all-reduce / all-gather over peer-mapped memory (NVLink), partial sums "
+                            "added in rank order, inside the step's CUDA graph; prompt batches (> 131072 floats per rank): NCCL")
+                           if kind == 1 else "NCCL (the peer-memory exchange was not available or was switched off)",
             "config": {"workload": f"Llama-3-{shape.upper()} shape, Q4_K_M tensor types, row-split over {world} GPUs, batch 1: "
                                    "512-token prompt then 128 greedy steps", "weights": "seeded random well-formed blocks, one shard per rank"},
             "pp512_tok_s": PROMPT / pp_dev, "pp512_e2e_tok_s": PROMPT / pp_e2e, "tg128_tok_s": 1.0 / tg_dev, "tg128_e2e_tok_s": 1.0 / tg_e2e,
             "pp512_ms": pp_dev * 1e3, "tg128_ms_per_token": tg_dev * 1e3}
 
 
-def cpu_llama_baseline(orc, orc_glue, n_layer, prompt_tokens=16, gen_tokens=4):
-    """The CPU restatement's Llama forward on the same shape: a prompt batch and a few single-token steps.
-    Weights are interleaved once, outside the timed region, as the reference does at load."""
-    load_pkg()
-    ll, hp = llama_hparams(n_layer)
-    syn = importlib.import_module("llama_rust_b200.synth")
-    tensors = {name: (ty, arr) for name, ty, arr, _, _ in syn.llama_tensors(hp, lambda n: ll.q4_k_m_type(n, n_layer))}
+def cpu_llama_baseline(orc, orc_glue, n_layer, prompt_tokens=PARITY_PROMPT, gen_tokens=PARITY_STEPS):
+    """The CPU restatement's Llama forward on the same shape: a prompt batch and a few greedy single-token steps.
+    Weights are interleaved once, outside the timed region, as the reference does at load.  Also returns the logits
+    and tokens of the run (the greedy-stream parity check of the GPU arm compares with them)."""
+    sh, hp = llama_hparams(n_layer)
+    syn = load_standalone("synth")
+    tensors = {name: (ty, arr) for name, ty, arr, _, _ in syn.llama_tensors(hp, lambda n: sh.q4_k_m_type(n, n_layer), tensor_shapes=sh.tensor_shapes)}
     ohp = dict(n_vocab=hp["n_vocab"], n_embd=hp["n_embd"], n_head=hp["n_head"], n_head_kv=hp["n_head_kv"],
                head_dim=hp["n_embd_head"], n_ff=hp["n_ff"], n_layer=n_layer, rope_mode=0, n_ctx_orig=hp["n_ctx_train"],
                norm_eps=hp["norm_rms_eps"], freq_base=hp["rope_freq_base"], freq_scale=1.0)
     threads = host_threads(orc)
     cpu = orc_glue.Llama(ohp, tensors, 256)
-    rng = np.random.default_rng(0)
+    wide = bool(__builtin_cpu_wide_silu())
 
     def fwd(toks, p0):
         n = len(toks)
@@ -487,27 +556,155 @@ def cpu_llama_baseline(orc, orc_glue, n_layer, prompt_tokens=16, gen_tokens=4):
         for i in range(n):
             mask[i, :p0 + i + 1] = 0
         return cpu.forward(toks, np.arange(p0, p0 + n), 256, mask, np.arange(p0, p0 + n), [n - 1], n_threads=threads,
-                           keep_repacked=True)
+                           wide_silu=wide, keep_repacked=True)[0]
 
-    prompt = rng.integers(0, hp["n_vocab"], prompt_tokens).astype(np.int32)
+    prompt = np.random.default_rng(0).integers(0, hp["n_vocab"], prompt_tokens).astype(np.int32)
     fwd(prompt[:4], 0)            # interleaves every weight (untimed), like the reference's load
     fwd(prompt[:1], 4)
     t0 = time.perf_counter()
-    fwd(prompt, 0)
+    trace = [fwd(prompt, 0)]
     t1 = time.perf_counter()
+    toks = [int(orc_glue.argmax(trace[-1]))]
     for i in range(gen_tokens):
-        fwd(prompt[:1], prompt_tokens + i)
+        trace.append(fwd(np.array([toks[-1]], dtype=np.int32), prompt_tokens + i))
+        toks.append(int(orc_glue.argmax(trace[-1])))
     t2 = time.perf_counter()
     orc_glue.L().orc_llama_drop_repacked()
-    return {"pp_tok_s": prompt_tokens / (t1 - t0), "tg_tok_s": gen_tokens / (t2 - t1), "unit": "tok/s", "cores": threads, "kind": "port",
-            "sample": f"{n_layer}-layer model of the same shape, one {prompt_tokens}-token prompt batch ({t1 - t0:.1f} s) and "
-                      f"{gen_tokens} single-token steps ({t2 - t1:.1f} s) at positions {prompt_tokens}.."}
+    res = {"pp_tok_s": prompt_tokens / (t1 - t0), "tg_tok_s": gen_tokens / (t2 - t1), "unit": "tok/s", "cores": threads, "kind": CPU_KIND,
+           "sample": f"{n_layer}-layer model of the same shape, one {prompt_tokens}-token prompt batch ({t1 - t0:.1f} s) and "
+                     f"{gen_tokens} greedy single-token steps ({t2 - t1:.1f} s) at positions {prompt_tokens}.."}
+    return res, trace, toks
+
+
+def __builtin_cpu_wide_silu():
+    """does this host take the 16-lane SILU (AVX512F + DQ)?  Read from /proc/cpuinfo: the CPU arm loads no GPU library"""
+    try:
+        flags = open("/proc/cpuinfo").read()
+        return "avx512f" in flags and "avx512dq" in flags
+    except OSError:
+        return False
+
+
+# ---- the quantized mat-mul sweep, MUL_MAT_ID and FLASH_ATTN_EXT configurations ---------------------------------
+SWEEP_TYPES = {"Q8_0": (8, 34, 32), "Q4_K": (12, 144, 256), "Q6_K": (14, 210, 256), "MXFP4": (39, 17, 32)}   # id, block bytes, block elements
+
+
+def peak_tensor():
+    """dense int8 peak taken as twice the measured sustained bf16 GEMM rate (the int8 MMA rate is twice the bf16 one)"""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["bf16_tflops_sustained"]), "measured"
+    return 1400.0, "fallback"
+
+
+def event_time(b, fn, reps, warm=2):
+    for _ in range(warm):
+        fn()
+    b.synchronize()
+    e0, e1 = b.Event(), b.Event()
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    e1.synchronize()
+    return e0.elapsed_ms(e1) / reps
+
+
+def run_sweep(b):
+    """BASELINE's mat-mul sweep (one weight shape per regime), the MUL_MAT_ID configuration and the FLASH_ATTN_EXT
+    configurations, each with its roofline: HBM for the decode-shaped cases, the tensor pipe for the prompt-shaped ones"""
+    hbm, hbm_src = peak_hbm()
+    tc, tc_src = peak_tensor()
+    out = {"peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "bf16_tflops_sustained": tc, "tensor_source": tc_src,
+                     "int8_dense_tops": 2 * tc, "note": "int8 dense peak taken as 2 x the measured sustained bf16 GEMM rate"}}
+    mm = {}
+    for name, (ty, bb, be) in SWEEP_TYPES.items():
+        entry = {}
+        # decode-shaped and small batches: the 128256 x 4096 weights (279 to 558 MB: more than L2, nothing to flush)
+        n, k = 128256, 4096
+        w = b.Weight(ty, synth_weights(n, k, seed=50 + ty, ty=ty), k)
+        for m in (1, 8, 32):
+            x = np.random.default_rng(60 + m).standard_normal((m, k)).astype(np.float32)
+            dx, do = b.device_array(x), b.DeviceBuffer(4 * n * m)
+            ms = event_time(b, lambda: b.mul_mat_device(w, dx, m, do), 20)
+            byts = n * k * bb // be + 4 * m * k + 4 * m * n
+            entry[f"m{m}"] = {"shape": f"{n}x{k}", "us": ms * 1e3, "gbs": byts / ms / 1e6, "frac_hbm": byts / ms / 1e6 / hbm,
+                              "includes": "activation quantization + mat-mul, device-resident f32 in and out"}
+        del w
+        # prompt-shaped: 14336 x 4096 (the FFN up shape)
+        n, k = 14336, 4096
+        w = b.Weight(ty, synth_weights(n, k, seed=51 + ty, ty=ty), k)
+        for m in (512, 2048):
+            x = np.random.default_rng(61 + m).standard_normal((m, k)).astype(np.float32)
+            dx, do = b.device_array(x), b.DeviceBuffer(4 * n * m)
+            ms = event_time(b, lambda: b.mul_mat_device(w, dx, m, do), 5 if name in ("Q8_0", "MXFP4") and m == 2048 else 10)
+            tops = 2.0 * n * k * m / ms / 1e9
+            entry[f"m{m}"] = {"shape": f"{n}x{k}", "us": ms * 1e3, "tops": tops, "frac_int8_peak": tops / (2 * tc),
+                              "includes": "activation quantization + mat-mul, device-resident f32 in and out"}
+        del w
+        mm[name] = entry
+    out["mul_mat"] = mm
+    out["kernel_error_after_mul_mat"] = b.kernel_error()
+
+    # MUL_MAT_ID: 128 experts of 768 x 2048 MXFP4, 512 tokens, top-8 ids drawn without replacement per token
+    ne, n, k, n_tok, top = 128, 768, 2048, 512, 8
+    w = b.ExpertWeights(39, synth_weights(ne * n, k, seed=70, ty=39), n, k)
+    rng = np.random.default_rng(71)
+    ids = np.stack([rng.permutation(ne)[:top] for _ in range(n_tok)]).astype(np.int32)
+    for ne11, label in ((1, "gate_up_form_b_2048x1x512"), (top, "down_form_b_2048x8x512")):
+        xb = rng.standard_normal((n_tok, ne11, k)).astype(np.float32)
+        db, dids, dst = b.device_array(xb), b.device_array(ids), b.DeviceBuffer(4 * n_tok * top * n)
+        ms = event_time(b, lambda: b.check(b.lib.b200_mul_mat_id(39, n, k, ne, ne11, n_tok, top, w.ptr, db.ptr, dids.ptr, dst.ptr, 0, None),
+                                           "mul_mat_id"), 10)
+        byts = ne * n * k * 17 // 32 + 4 * n_tok * ne11 * k + 4 * n_tok * top * n
+        out.setdefault("mul_mat_id", {})[label] = {"us": ms * 1e3, "algorithmic_bytes": byts, "gbs": byts / ms / 1e6, "frac_hbm": byts / ms / 1e6 / hbm,
+                                                   "gflop": 2.0 * n_tok * top * n * k / 1e9, "tops": 2.0 * n_tok * top * n * k / ms / 1e9}
+    del w
+
+    # FLASH_ATTN_EXT: D 128, 32 query heads on 8 KV heads, causal mask, F16 cache laid out like the KV cache
+    H, HK, D = 32, 8, 128
+    fa = {}
+    for n_kv in (512, 4096, 32768):
+        rng = np.random.default_rng(80 + n_kv)
+        kk = rng.standard_normal((HK, n_kv, D)).astype(np.float16).view(np.uint16)
+        vv = rng.standard_normal((HK, n_kv, D)).astype(np.float16).view(np.uint16)
+        kv = b.KvCacheView(kk, vv)
+        for T in (1, 512):
+            q = rng.standard_normal((H, T, D)).astype(np.float32)
+            mask = np.where(np.arange(n_kv)[None, :] <= np.arange(T)[:, None] + (n_kv - T), 0.0, -np.inf).astype(np.float16).view(np.uint16)
+            dq, dm, dst = b.device_array(q), b.device_array(mask), b.DeviceBuffer(4 * T * H * D)
+            a = b.FlashAttnArgs()
+            a.dk, a.dv, a.n_tok, a.n_head, a.n_head_kv, a.n_kv = D, D, T, H, HK, n_kv
+            a.q, a.q_nb1, a.q_nb2 = dq.ptr, D * 4, T * D * 4
+            a.k, a.k_nb1, a.k_nb2 = kv.k.ptr, kv.k_nb1, kv.k_nb2
+            a.v, a.v_nb1, a.v_nb2 = kv.v.ptr, kv.v_nb1, kv.v_nb2
+            a.mask, a.mask_nb1, a.sinks = dm.ptr, n_kv * 2, None
+            a.scale, a.max_bias, a.logit_softcap, a.dst, a.n_chunks = 1.0 / np.sqrt(D), 0.0, 0.0, dst.ptr, 8
+            modes = ((0, "fast"), (2, "exact")) if T == 1 else ((0, "default"),)
+            for mode, label in modes:
+                a.mode = mode
+                import ctypes
+                ms = event_time(b, lambda: b.check(b.lib.b200_flash_attn_ext(ctypes.byref(a), None), "flash_attn_ext"), 20 if T == 1 else 3)
+                visible = sum(min(n_kv, t + n_kv - T + 1) for t in range(T))
+                byts = 2 * n_kv * HK * D * 2 + 2 * n_kv * T + 2 * 4 * T * H * D
+                flops = 4.0 * D * H * visible
+                e = {"us": ms * 1e3}
+                if T == 1:
+                    e.update({"algorithmic_bytes": byts, "gbs": byts / ms / 1e6, "frac_hbm": byts / ms / 1e6 / hbm,
+                              "note": "16.8 MB (n_kv 4096) and smaller caches sit in the 126 MB L2 across repetitions" if n_kv < 32768 else "134 MB of K/V per call: more than L2"})
+                else:
+                    e.update({"gflop": flops / 1e9, "tflops": flops / ms / 1e9, "frac_bf16_peak": flops / ms / 1e9 / tc})
+                fa[f"n_kv{n_kv}_T{T}_{label}"] = e
+    out["flash_attn"] = fa
+    out["kernel_error"] = b.kernel_error()
+    return out
 
 
 # ---- arms -------------------------------------------------------------------------------------------------
 def run_reference(args, rank, world):
     """The CPU routes the reference takes for these workloads, restated in C++ because the Rust reference
-    cannot be built here; all host threads."""
+    cannot be built here; all host threads.  This arm maps the oracle only: the synthetic inputs are made by
+    modules loaded without the CUDA library."""
     if rank != 0:
         return
     orc, orc_glue = load_oracle()
@@ -525,14 +722,14 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8xint4 dot, f32 accumulate", "data": "synthetic", "config": gemv_config(),
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": CPU_KIND,
                          "sample": f"the full step (4 shapes, {total} algorithmic bytes) x {args.steps}"},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     if not args.no_llama:
         del reps, xs, outs
         try:
-            line["llama_8b"] = cpu_llama_baseline(orc, orc_glue, args.cpu_layers)
+            line["llama_8b"] = cpu_llama_baseline(orc, orc_glue, args.cpu_layers)[0]
         except Exception as exc:
             line["llama_8b"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
     print(json.dumps(line), flush=True)
@@ -546,10 +743,10 @@ def run_b200(args, rank, world, barrier, reduce_max):
     b.set_device(local)
     note(f"rank {rank}: decode mat-mul")
     g = run_gemv(b, args, rank, world, barrier, reduce_max, local)
-    llama = None
+    llama, traces = None, {}
     if not args.no_llama:
         note(f"rank {rank}: llama 8b replica")
-        llama = run_llama(b, args, rank, world, barrier, reduce_max)
+        llama, traces = run_llama(b, args, rank, world, barrier, reduce_max)
     tp_runs = {}
     if world > 1 and not args.no_llama:
         for shape in ("8b", "70b"):
@@ -558,18 +755,41 @@ def run_b200(args, rank, world, barrier, reduce_max):
                 tp_runs[f"llama_{shape}_tp"] = run_llama_tp(b, args, rank, world, local, barrier, reduce_max, shape)
             except Exception as exc:   # a shape that does not split this many ways, or no room: reported, not fatal
                 tp_runs[f"llama_{shape}_tp"] = {"tp": world, "unavailable": f"{type(exc).__name__}: {exc}"}
+    if world == 1 and not args.no_llama and not args.no_70b:
+        note("llama 70b on one GPU")
+        try:
+            tp_runs["llama_70b_tp"] = run_llama_70b_one_gpu(b, args)
+        except Exception as exc:
+            tp_runs["llama_70b_tp"] = {"tp": 1, "unavailable": f"{type(exc).__name__}: {exc}"}
+    sweep = None
+    if world == 1 and not args.no_sweep:
+        note("mat-mul sweep, mul_mat_id, flash_attn")
+        try:
+            sweep = run_sweep(b)
+        except Exception as exc:
+            sweep = {"unavailable": f"{type(exc).__name__}: {exc}"}
     if rank != 0:
         return
+    config = gemv_config()
+    # the other halves of the metric, where the driver's record keeps them: tokens/s of the Llama shapes
+    measured = {}
+    if llama is not None:
+        measured["llama_8b_one_gpu_replicas"] = {k: llama[k] for k in ("tg128_tok_s", "pp512_tok_s", "tg128_e2e_tok_s", "pp512_e2e_tok_s")}
+        measured["llama_8b_one_gpu_replicas"]["tg128_frac_hbm"] = llama["roofline"]["frac"] if world == 1 else None
+    for key, r in tp_runs.items():
+        if "unavailable" not in r:
+            measured[f"{key}{r['tp']}"] = {k: r[k] for k in ("tg128_tok_s", "pp512_tok_s", "tg128_e2e_tok_s", "tg128_ms_per_token")}
+    config["measured"] = measured
     line = {
         "metric": METRIC, "value": g["value"], "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": g["warmup"],
         "ms_per_step": g["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8xint4 dot, f32 accumulate", "data": "synthetic", "config": gemv_config(), "clocks": g["clocks"],
+        "dtype": "int8xint4 dot, f32 accumulate", "data": "synthetic", "config": config, "clocks": g["clocks"],
         "e2e": g["e2e"], "gpu_launches": g["gpu_launches"], "roofline": g["roofline"],
     }
-    if llama is not None:
-        line["llama_8b"] = llama
-    line.update(tp_runs)
     if world > 1:   # the CPU baseline is a single-GPU extra
+        if llama is not None:
+            line["llama_8b"] = llama
+        line.update(tp_runs)
         print(json.dumps(line), flush=True)
         return
     # CPU baselines on the host cores: the same workloads through the CPU routes, bounded samples
@@ -579,11 +799,24 @@ def run_b200(args, rank, world, barrier, reduce_max):
         line["cpu_baseline"] = cpu_gemv_baseline(orc)
         if llama is not None:
             try:
-                llama["cpu_baseline"] = cpu_llama_baseline(orc, orc_glue, args.cpu_layers)
+                llama["cpu_baseline"], cpu_trace, cpu_toks = cpu_llama_baseline(orc, orc_glue, args.cpu_layers)
+                # greedy-stream parity: the same 16-token prompt and 4 greedy steps on the GPU (both numerics modes) and on the CPU port
+                if args.cpu_layers == args.layers:
+                    llama["greedy_parity"] = {name: compare_greedy(tr, tk, cpu_trace, cpu_toks) for name, (tr, tk) in traces.items()}
+                    llama["greedy_parity"]["what"] = (f"{PARITY_PROMPT}-token prompt + {PARITY_STEPS} greedy steps of the full model, GPU against the CPU port "
+                                                      "on the same synthetic weights: token streams, first divergence, logits while the streams agree")
+                    config["measured"]["greedy_parity_exact_identical"] = llama["greedy_parity"].get("exact", {}).get("identical")
+                    config["measured"]["greedy_parity_fast_first_divergence"] = llama["greedy_parity"].get("fast", {}).get("first_divergence")
             except Exception as exc:
                 llama["cpu_baseline"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
     except Exception as exc:  # the baseline is a reported extra, never the measured path
-        line["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": f"failed: {exc}"}
+        line["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": 0, "kind": CPU_KIND, "sample": f"failed: {exc}"}
+    # extras last (the tail of the line is what a truncated log keeps): sweep first, the Llama numbers at the very end
+    if sweep is not None:
+        line["sweep"] = sweep
+    line.update(tp_runs)
+    if llama is not None:
+        line["llama_8b"] = llama
     print(json.dumps(line), flush=True)
 
 
@@ -699,6 +932,8 @@ def main():
     ap.add_argument("--layers", type=int, default=32, help="layers of the 8B-shaped model (32 = the full model)")
     ap.add_argument("--cpu-layers", type=int, default=32, help="layers of the model the CPU baseline times")
     ap.add_argument("--no-llama", action="store_true", help="skip the Llama half of the metric")
+    ap.add_argument("--no-70b", action="store_true", help="skip the 70B shape on one GPU (N = 1)")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the mat-mul sweep / MUL_MAT_ID / FLASH_ATTN_EXT entries (N = 1)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)

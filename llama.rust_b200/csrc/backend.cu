@@ -984,13 +984,35 @@ static int fusable_row_mat_mul(const ggml_cgraph *g, int from, const ggml_tensor
 }
 // which prologues ride inside the mat-mul kernels: bit 0 quantization only, bit 1 norm in front of at most two row
 // tiles per SM, bit 2 silu, bit 3 norm in front of any number of row tiles (B200_FUSE_PROLOGUE_MASK, read once)
+// Measured on the 8B-shape single-token step: only the quantization-only prologue pays (every CTA of the mat-mul
+// redoes a norm or silu prologue, and that costs more than the launch it saves), so that is the default.
 static int prologue_mask() {
     static int v = -1;
     if (v < 0) {
         const char *e = getenv("B200_FUSE_PROLOGUE_MASK");
-        v = e ? atoi(e) : 7;
+        v = e ? atoi(e) : 1;
     }
     return v;
+}
+// B200_DEBUG_SKIP: a comma-separated list of node classes whose launches are left out (fa, rms, silu, glue, add,
+// getrows, argmax, mm:<rows>x<k>), for measuring what a class of kernels costs inside a replayed step by taking it
+// out.  The step's results are meaningless with it; never set outside a measurement.
+static bool debug_skip(const ggml_tensor *op) {
+    static std::string list = [] { const char *e = getenv("B200_DEBUG_SKIP"); return std::string(e ? e : ""); }();
+    if (list.empty()) return false;
+    auto has = [&](const std::string &tok) { return ("," + list + ",").find("," + tok + ",") != std::string::npos; };
+    switch (op->op) {
+        case GGML_OP_FLASH_ATTN_EXT: return has("fa");
+        case GGML_OP_RMS_NORM: return has("rms");
+        case GGML_OP_UNARY: return has("silu");
+        case GGML_OP_ROPE: case GGML_OP_SET_ROWS: return has("glue");
+        case GGML_OP_ADD: return has("add");
+        case GGML_OP_GET_ROWS: return has("getrows");
+        case GGML_OP_ARGMAX: return has("argmax");
+        case GGML_OP_MUL_MAT:
+            return has("mm:" + std::to_string(op->src[0]->ne[1]) + "x" + std::to_string(op->src[0]->ne[0])) || has("mm");
+        default: return false;
+    }
 }
 static int64_t row_tiles_of(const ggml_cgraph *g, int j) {
     // the row tiles a fused launch starting at mat-mul j would span: the mat-mul and the siblings that may join it
@@ -1078,6 +1100,7 @@ static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
             fa_mask = nullptr;
         }
         int rc = B200_STATUS_SUCCESS;
+        if (debug_skip(op)) continue;
         switch (op->op) {
             case GGML_OP_MUL_MAT:
                 if (pending.active || (bc->fuse_prologue && (prologue_mask() & 1) && multi_candidate(op) && ((uintptr_t)op->src[1]->data & 15) == 0 &&

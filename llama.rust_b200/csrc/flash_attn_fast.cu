@@ -43,7 +43,7 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// partial[(((hk * row_blocks + rb) * n_splits + split) * FF_ROWS + r) * (2 + D)] = {m, l, acc[D]}
+// partial[(((hk * row_blocks + rb) * n_splits + split) * FF_ROWS + r) * (D + 4)] = {acc[D], m, l, -, -}
 template <int D>
 __global__ void __launch_bounds__(FF_WARPS * 32)
 fa_fast_rows_kernel(b200_flash_attn_args a, FastDims d, float scale_log2, float *__restrict__ partial, int *__restrict__ counters) {
@@ -186,15 +186,16 @@ fa_fast_rows_kernel(b200_flash_attn_args a, FastDims d, float scale_log2, float 
 
     // this CTA's partials
     const int row_blocks = gridDim.z;
-    float *mine = partial + (((int64_t)hk * row_blocks + rb) * d.n_splits + split) * FF_ROWS * (2 + D);
+    constexpr int PSTRIDE = D + 4;
+    float *mine = partial + (((int64_t)hk * row_blocks + rb) * d.n_splits + split) * FF_ROWS * PSTRIDE;
 #pragma unroll
     for (int i = 0; i < RPW; i++) {
         const int rl = warp + i * FF_WARPS;
         if (rl >= nrows) break;
-        float *pr = mine + (int64_t)rl * (2 + D);
-        if (lane == 0) { pr[0] = m_run[i]; pr[1] = l_run[i]; }
+        float *pr = mine + (int64_t)rl * PSTRIDE;
+        if (lane == 0) { pr[D] = m_run[i]; pr[D + 1] = l_run[i]; }
 #pragma unroll
-        for (int j = 0; j < VEC; j++) pr[2 + lane * VEC + j] = acc[i][j];
+        for (int j = 0; j < VEC; j++) pr[lane * VEC + j] = acc[i][j];
     }
     __threadfence();
     __syncthreads();
@@ -203,42 +204,50 @@ fa_fast_rows_kernel(b200_flash_attn_args a, FastDims d, float scale_log2, float 
     if (!is_last) return;
     __threadfence();
     if (tid == 0) counters[hk * row_blocks + rb] = 0;   // ready for the next launch
-    // merge the splits.  The (max, sum) pairs of every (row, split) come into shared memory with independent loads,
-    // the per-split weights exp2(m - M) are made once, and the accumulators are then summed with loads that do not
-    // depend on one another (the compiler batches them), thread = value element, rows in turn.
-    const float *all = partial + ((int64_t)hk * row_blocks + rb) * d.n_splits * FF_ROWS * (2 + D);
+    // merge the splits: a short serial tail on one CTA, so every step is laid out for few memory round trips.
+    // (1) the (max, sum) pairs of every (row, split) come into shared memory with independent loads; (2) one warp per
+    // row turns them into weights exp2(m - M) and the merged sum; (3) every thread sums four consecutive accumulator
+    // elements of one row over the splits with 16-byte loads that do not depend on one another.
+    const float *all = partial + ((int64_t)hk * row_blocks + rb) * d.n_splits * FF_ROWS * PSTRIDE;
     float *mw = ps;                       // [FF_ROWS][FF_MAX_SPLITS] maxima, then weights; ps is free now
     float *lw = qs;                       // [FF_ROWS][FF_MAX_SPLITS] sums; qs is free too (FF_ROWS * D >= FF_ROWS * FF_MAX_SPLITS)
     __shared__ float lsum[FF_ROWS];
     for (int i = tid; i < nrows * d.n_splits; i += FF_WARPS * 32) {
         const int rl = i / d.n_splits, sp = i - rl * d.n_splits;
-        const float *pr = all + ((int64_t)sp * FF_ROWS + rl) * (2 + D);
-        mw[rl * FF_MAX_SPLITS + sp] = __ldcg(pr);
-        lw[rl * FF_MAX_SPLITS + sp] = __ldcg(pr + 1);
+        const float2 ml = __ldcg((const float2 *)(all + ((int64_t)sp * FF_ROWS + rl) * PSTRIDE + D));
+        mw[rl * FF_MAX_SPLITS + sp] = ml.x;
+        lw[rl * FF_MAX_SPLITS + sp] = ml.y;
     }
     __syncthreads();
-    if (tid < nrows) {
-        float M = -INFINITY;
-        for (int sp = 0; sp < d.n_splits; sp++) M = fmaxf(M, mw[tid * FF_MAX_SPLITS + sp]);
+    for (int rl = warp; rl < nrows; rl += FF_WARPS) {   // FF_MAX_SPLITS = 64: two splits per lane
+        const float m0 = lane < d.n_splits ? mw[rl * FF_MAX_SPLITS + lane] : -INFINITY;
+        const float m1 = lane + 32 < d.n_splits ? mw[rl * FF_MAX_SPLITS + lane + 32] : -INFINITY;
+        float M = fmaxf(m0, m1);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        const float w0 = m0 == -INFINITY ? 0.0f : exp2f(m0 - M), w1 = m1 == -INFINITY ? 0.0f : exp2f(m1 - M);
         float L = 0.0f;
-        for (int sp = 0; sp < d.n_splits; sp++) {
-            const float ms = mw[tid * FF_MAX_SPLITS + sp];
-            const float w = ms == -INFINITY ? 0.0f : exp2f(ms - M);
-            mw[tid * FF_MAX_SPLITS + sp] = w;
-            L = fmaf(lw[tid * FF_MAX_SPLITS + sp], w, L);
-        }
-        lsum[tid] = L;
+        if (lane < d.n_splits) { mw[rl * FF_MAX_SPLITS + lane] = w0; L = lw[rl * FF_MAX_SPLITS + lane] * w0; }
+        if (lane + 32 < d.n_splits) { mw[rl * FF_MAX_SPLITS + lane + 32] = w1; L = fmaf(lw[rl * FF_MAX_SPLITS + lane + 32], w1, L); }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+        if (lane == 0) lsum[rl] = L;
     }
     __syncthreads();
-    for (int i = tid; i < nrows * D; i += FF_WARPS * 32) {
-        const int rl = i / D, e = i - rl * D;
-        const float *pr = all + (int64_t)rl * (2 + D) + 2 + e;
-        float o = 0.0f;
+    for (int i = tid; i < nrows * (D / 4); i += FF_WARPS * 32) {
+        const int rl = i / (D / 4), e = 4 * (i - rl * (D / 4));
+        const float *pr = all + (int64_t)rl * PSTRIDE + e;
+        float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll 8
-        for (int sp = 0; sp < d.n_splits; sp++) o = fmaf(__ldcg(pr + (int64_t)sp * FF_ROWS * (2 + D)), mw[rl * FF_MAX_SPLITS + sp], o);
+        for (int sp = 0; sp < d.n_splits; sp++) {
+            const float4 v = __ldcg((const float4 *)(pr + (int64_t)sp * FF_ROWS * PSTRIDE));
+            const float w = mw[rl * FF_MAX_SPLITS + sp];
+            o.x = fmaf(v.x, w, o.x); o.y = fmaf(v.y, w, o.y); o.z = fmaf(v.z, w, o.z); o.w = fmaf(v.w, w, o.w);
+        }
         const int r = row0 + rl, t = r / d.group, h = hk * d.group + r % d.group;
         const float L = lsum[rl];
-        a.dst[((int64_t)t * d.H + h) * D + e] = L > 0.0f ? o / L : 0.0f;   // a row that sees nothing gives zeros, as on the CPU
+        const float inv = L > 0.0f ? 1.0f / L : 0.0f;   // a row that sees nothing gives zeros, as on the CPU
+        *(float4 *)(a.dst + ((int64_t)t * d.H + h) * D + e) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
     }
 }
 
@@ -252,7 +261,7 @@ bool flash_attn_fast_rows(const b200_flash_attn_args *a, cudaStream_t s, int *rc
     *rc = B200_STATUS_SUCCESS;
     if (a->sinks || a->max_bias != 0.0f || a->logit_softcap != 0.0f || a->dk != a->dv || a->n_tok >= 64 || a->n_kv == 0 || a->n_tok == 0)
         return false;
-    if (a->q_nb1 % 4 || a->q_nb2 % 4) return false;
+    if (a->q_nb1 % 4 || a->q_nb2 % 4 || ((uintptr_t)a->dst & 15)) return false;
     FastDims d;
     d.T = (int)a->n_tok; d.H = (int)a->n_head; d.H_kv = (int)a->n_head_kv; d.group = d.H / d.H_kv;
     d.n_kv = a->n_kv;
@@ -280,7 +289,7 @@ bool flash_attn_fast_rows(const b200_flash_attn_args *a, cudaStream_t s, int *rc
         g_fast_counters[dev] = (int *)p;
     }
     const int D = (int)a->dk;
-    const size_t part_b = (size_t)d.H_kv * row_blocks * d.n_splits * FF_ROWS * (2 + D) * 4;
+    const size_t part_b = (size_t)d.H_kv * row_blocks * d.n_splits * FF_ROWS * (D + 4) * 4;
     void *scratch = nullptr;
     *rc = scratch_get(part_b, &scratch);
     if (*rc != B200_STATUS_SUCCESS) return true;
