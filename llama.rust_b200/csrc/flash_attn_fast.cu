@@ -27,6 +27,7 @@ constexpr int FF_TILE = 32;          // positions per tile
 constexpr int FF_ROWS = 16;          // query rows per CTA
 constexpr int FF_WARPS = 4;
 constexpr int FF_MAX_SPLITS = 64;
+constexpr int FF_MAX_LIST = 2048;    // most tiles one CTA may walk when it first lists the visible ones
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct FastDims {
@@ -101,9 +102,44 @@ fa_fast_rows_kernel(b200_flash_attn_args a, FastDims d, float scale_log2, float 
         for (int j = 0; j < VEC; j++) acc[i][j] = 0.0f;
     }
 
-    if (tile0 < tile1) stage(tile0, 0);
-    for (int64_t tile = tile0; tile < tile1; tile++) {
-        const int buf = (int)((tile - tile0) & 1);
+    // Several tokens per step over a shared cache (batched decode): every row sees a small part of the cells.  The
+    // CTA first lists the tiles of its range in which any of its rows sees anything (one mask read per row and
+    // tile), and stages K / V for those only.
+    __shared__ unsigned short vis_list[FF_MAX_LIST];
+    __shared__ int n_vis_s;
+    const bool listed = a.mask != nullptr && d.T > 1;
+    int n_walk = (int)(tile1 - tile0);
+    if (listed) {
+        const int t_lo = row0 / d.group, t_hi = (row0 + nrows - 1) / d.group;
+        unsigned char *flags = (unsigned char *)ps;   // [tiles of the range], ps is not in use yet
+        for (int64_t tl = warp; tl < tile1 - tile0; tl += FF_WARPS) {
+            const int64_t p = (tile0 + tl) * FF_TILE + lane;
+            bool any = false;
+            for (int t = t_lo; t <= t_hi && !any; t++)
+                any = p < d.n_kv && __half2float(((const __half *)((const unsigned char *)a.mask + (int64_t)t * a.mask_nb1))[p]) != -INFINITY;
+            const unsigned hit = __ballot_sync(0xffffffffu, any);
+            if (lane == 0) flags[tl] = hit != 0u;
+        }
+        __syncthreads();
+        if (warp == 0) {   // ordered compaction, 32 tiles at a time
+            int count = 0;
+            for (int64_t base = 0; base < tile1 - tile0; base += 32) {
+                const bool f = base + lane < tile1 - tile0 && flags[base + lane];
+                const unsigned bal = __ballot_sync(0xffffffffu, f);
+                if (f) vis_list[count + __popc(bal & ((1u << lane) - 1u))] = (unsigned short)(base + lane);
+                count += __popc(bal);
+            }
+            if (lane == 0) n_vis_s = count;
+        }
+        __syncthreads();
+        n_walk = n_vis_s;
+    }
+    auto tile_at = [&](int i) -> int64_t { return tile0 + (listed ? (int64_t)vis_list[i] : (int64_t)i); };
+
+    if (n_walk > 0) stage(tile_at(0), 0);
+    for (int it = 0; it < n_walk; it++) {
+        const int64_t tile = tile_at(it);
+        const int buf = it & 1;
         const int64_t pos = tile * FF_TILE + lane;
         // this tile's mask values travel while the K / V copies do: one round trip instead of two in a row
         float mvals[RPW];
@@ -116,8 +152,8 @@ fa_fast_rows_kernel(b200_flash_attn_args a, FastDims d, float scale_log2, float 
                 mvals[i] = __half2float(((const __half *)((const unsigned char *)a.mask + (int64_t)t * a.mask_nb1))[pos]);
             }
         }
-        if (tile + 1 < tile1) {
-            stage(tile + 1, buf ^ 1);
+        if (it + 1 < n_walk) {
+            stage(tile_at(it + 1), buf ^ 1);
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
@@ -282,6 +318,7 @@ bool flash_attn_fast_rows(const b200_flash_attn_args *a, cudaStream_t s, int *rc
     if (want < 1) want = 1;
     d.tiles_per_split = (int)((n_tiles + want - 1) / want);
     d.n_splits = (int)((n_tiles + d.tiles_per_split - 1) / d.tiles_per_split);
+    if (d.T > 1 && d.tiles_per_split > FF_MAX_LIST) return false;   // the visible-tile list of a CTA is bounded
     if (!g_fast_counters[dev]) {   // a module variable: no allocation, zero-initialized on every device
         void *p = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&p, g_fast_counters_dev);

@@ -50,9 +50,24 @@ def row_rel(a, b):
 
 
 def run_fast(dev, q, k, v, mask, scale, **kw):
+    """mode 1: the fast kernel wherever it applies (the numerics policy alone sends only single query rows to it)"""
+    return dev.flash_attn(q, dev.KvCacheView(k, v), mask, scale, mode=1, **kw)
+
+
+def test_fast_policy_takes_single_rows(dev):
+    """under the fast numerics policy a single query row takes the f32 kernel (not the CPU's bits), several rows
+    keep the exact kernels"""
+    scale = 1.0 / np.sqrt(128.0)
     dev.set_numerics(dev.FAST)
     try:
-        return dev.flash_attn(q, dev.KvCacheView(k, v), mask, scale, **kw)
+        q, k, v, mask = synth_case(8, 2, 128, 1, 768, seed=9)
+        cpu, _ = orc.flash_attn(q, k, v, mask, scale, n_chunks=8)
+        got = dev.flash_attn(q, dev.KvCacheView(k, v), mask, scale, n_chunks=8)
+        assert not np.array_equal(got.view(np.uint32), cpu.view(np.uint32)) and row_rel(got, ref64(q, k, v, mask, scale)) <= 1e-5
+        q, k, v, mask = synth_case(8, 2, 128, 3, 300, seed=10)
+        cpu, _ = orc.flash_attn(q, k, v, mask, scale)
+        got = dev.flash_attn(q, dev.KvCacheView(k, v), mask, scale)
+        assert np.array_equal(got.view(np.uint32), cpu.view(np.uint32))
     finally:
         dev.set_numerics(dev.EXACT)
 
