@@ -583,10 +583,11 @@ int b200_mul_mat_id(int type, int64_t n, int64_t k, int64_t n_expert, int64_t ne
     const int64_t rows = ne11 * n_tok;   // every b row is quantized once (compute.rs:1952-1985)
     const size_t act_b = act_scratch_bytes(rows, k);
     void *scratch = nullptr;
-    int rc = scratch_get(act_b + sizeof(int) * (size_t)n_expert + 256, &scratch);
+    const size_t lists_b = mmid_grouped_scratch_bytes(n_expert, n_tok * n_ids);   // covers the per-expert counters of the per-pair path too
+    int rc = scratch_get(act_b + lists_b + 256, &scratch);
     if (rc != B200_STATUS_SUCCESS) return rc;
     ActBuf a = act_carve(scratch, rows, k);
-    int *counts = (int *)((uint8_t *)scratch + act_b);
+    int *counts = (int *)((uint8_t *)scratch + (act_b + 255) / 256 * 256);
     // rows in passes of 65535 (one launch's grid.y limit)
     for (int64_t r0 = 0; r0 < rows; r0 += 65535) {
         const int64_t nr = rows - r0 < 65535 ? rows - r0 : 65535;

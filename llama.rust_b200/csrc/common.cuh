@@ -152,6 +152,10 @@ int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t
 // Q8_0 / Q4_0 / MXFP4 / Q6_K prompt mat-muls on tcgen05 kind::i8 (gemm_tcgen05_i8.cu)
 int launch_gemm_tcgen05_i8(int type, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
                            cudaStream_t s);
+// MUL_MAT_ID with the pairs grouped by expert on the device (MXFP4 / Q4_0 experts on the 8x8 route): gemm_tcgen05_i8.cu
+size_t mmid_grouped_scratch_bytes(int64_t n_expert, int64_t n_pairs);
+int launch_mul_mat_id_grouped(int type, int64_t n, int64_t k, int64_t n_expert, int64_t ne11, int64_t n_tok, int64_t n_ids, const uint8_t *tiles,
+                              ActView acts, const int32_t *ids, float *dst, void *lists, cudaStream_t s);
 // which Q4_K gemm-chain prompt kernel the time model prefers on a GPU of sm_count SMs: 0 integer, 3 / 4 two-pass with 64 / 128 columns
 int gemm_chain_pick_for(int64_t n, int64_t m, int sm_count);
 // Q4_K gemm chain with the scales folded into f16 operands, 128 x 64 per CTA (gemm_tcgen05_f16.cu)

@@ -105,6 +105,17 @@ __device__ __forceinline__ uint32_t mxfp4_lut4(uint32_t x) {
 // four nibbles (one per byte) minus 8, as signed bytes: no borrow between bytes ((n | 0x80) - 8 keeps bit 7 set, then flip it)
 __device__ __forceinline__ uint32_t nibbles_minus8(uint32_t x) { return ((x | 0x80808080u) - 0x08080808u) ^ 0x80808080u; }
 
+// MUL_MAT_ID, grouped by expert: CTA column blockIdx.x is work item w = up to 32 (token, slot) pairs routed to one
+// expert.  work_expert[w] names the expert (-1: an unused item, the CTA leaves at once), col_act[32 w + c] the
+// quantized activation row of column c and col_out[32 w + c] the output row (pair index), -1 for the unused columns
+// of a short item.  Null work_expert: a plain mat-mul.
+struct GroupMap {
+    const int *work_expert;
+    const int *col_act;
+    const int *col_out;
+    int64_t expert_bytes;
+};
+
 struct TiBars {
     uint64_t full[3], empty[3], tfull[TI_TSTAGES], tempty[TI_TSTAGES];
     uint32_t tmem_base;
@@ -135,7 +146,8 @@ __device__ __forceinline__ void q6_planes(const uint4 &v, int sc, uint4 *hi, uin
 
 template <int TYPE>
 __global__ void __launch_bounds__(TI_THREADS, 1)
-gemm_i8_tcgen05_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *dst, int64_t lddst, int64_t n, int nb, int64_t m, int *err) {
+gemm_i8_tcgen05_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *dst, int64_t lddst, int64_t n, int nb, int64_t m, int *err,
+                       GroupMap gm) {
     using T = TiTraits<TYPE>;
     constexpr bool Q6 = TYPE == B200_TYPE_Q6_K;
     constexpr int STAGE_BYTES = TiSizes<TYPE>::STAGE_BYTES;
@@ -143,13 +155,29 @@ gemm_i8_tcgen05_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *d
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     __shared__ TiBars bars;
+    __shared__ int col_act_s[TI_COLS], col_out_s[TI_COLS];
     pdl_trigger();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t tile0 = (int64_t)blockIdx.y * (TI_ROWS / TILE_ROWS);
     const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
-    const int64_t col0 = (int64_t)blockIdx.x * TI_COLS;
+    int64_t col0 = (int64_t)blockIdx.x * TI_COLS;
     const int64_t K = acts.k;
     volatile int *abort_flag = &bars.abort_flag;
+    const bool grouped = gm.work_expert != nullptr;
+    if (grouped) {
+        pdl_wait();   // the work list is a previous kernel's output
+        const int e = gm.work_expert[blockIdx.x];
+        if (e < 0) return;   // every thread of the CTA: nothing has been allocated yet
+        tiles += (int64_t)e * gm.expert_bytes;
+        if (threadIdx.x < TI_COLS) {
+            col_act_s[threadIdx.x] = gm.col_act[(int64_t)blockIdx.x * TI_COLS + threadIdx.x];
+            col_out_s[threadIdx.x] = gm.col_out[(int64_t)blockIdx.x * TI_COLS + threadIdx.x];
+        }
+        // columns are addressed through the two tables from here on: column c reads activation row col_act_s[c]
+        // (the first column's row stands in for unused columns) and writes output row col_out_s[c]
+        col0 = 0;
+        m = TI_COLS;
+    }
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < T::STAGES; i++) {
@@ -171,7 +199,7 @@ gemm_i8_tcgen05_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *d
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = bars.tmem_base;
-    pdl_wait();
+    if (!grouped) pdl_wait();
 
     if (warp < TI_EPI_WARPS) {
         // ---- epilogue: the f32 chain of weight row 32 q + lane over 16 activation rows ----
@@ -250,7 +278,12 @@ gemm_i8_tcgen05_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *d
 #pragma unroll
             for (int c = 0; c < 16; c++) {
                 const int64_t col = col0 + 16 * h + c;
-                if (col < m) dst[col * lddst + row] = acc[c];
+                if (grouped) {
+                    const int orow = col_out_s[16 * h + c];
+                    if (orow >= 0) dst[(int64_t)orow * lddst + row] = acc[c];
+                } else if (col < m) {
+                    dst[col * lddst + row] = acc[c];
+                }
             }
         }
     } else if (warp < TI_EPI_WARPS + TI_PROD_WARPS) {
@@ -264,16 +297,23 @@ gemm_i8_tcgen05_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *d
         int64_t bcol[4];
         uint32_t b_off[4];
 #pragma unroll
+        auto act_row = [&](int col) -> int64_t {
+            if (grouped) {
+                const int r = col_act_s[col];
+                return r >= 0 ? r : col_act_s[0];
+            }
+            const int64_t c = col0 + col;
+            return c < m ? c : m - 1;
+        };
         for (int j = 0; j < 4; j++) {
             const int i = p + 128 * j, col = i & 31, kc = i >> 5;
-            const int64_t c = col0 + col;
-            bcol[j] = (c < m ? c : m - 1) * K + kc * 16;
+            bcol[j] = act_row(col) * K + kc * 16;
             b_off[j] = (uint32_t)((col >> 3) * 2048 + kc * 128 + (col & 7) * 16);
         }
         // activation scales: 32-element types: 8 blocks x 32 columns, two per thread; Q6_K: 32 columns (warp 0 of the producers)
         const int sblk = p >> 4, scol2 = (p & 15) * 2;
-        const int64_t sc0 = col0 + scol2 < m ? col0 + scol2 : m - 1, sc1 = col0 + scol2 + 1 < m ? col0 + scol2 + 1 : m - 1;
-        const int64_t dcol = col0 + lane < m ? col0 + lane : m - 1;
+        const int64_t sc0 = act_row(scol2), sc1 = act_row(scol2 + 1);
+        const int64_t dcol = act_row(lane);
         constexpr int NQ = TYPE == B200_TYPE_Q8_0 ? 16 : TYPE == B200_TYPE_Q6_K ? 13 : 8;   // 16-byte pieces of the row's group
         for (int b = 0; b < nb; b++) {
             const int s = b % T::STAGES;
@@ -402,7 +442,8 @@ gemm_i8_tcgen05_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *d
 }
 
 template <int TYPE>
-int launch_i8(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s) {
+int launch_i8(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s,
+              GroupMap gm = GroupMap{nullptr, nullptr, nullptr, 0}, int64_t work_items = 0) {
     static bool attr_done[64] = {false};
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
@@ -415,13 +456,98 @@ int launch_i8(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView act
     int rc = device_error_word(&err);
     if (rc != B200_STATUS_SUCCESS) return rc;
     const int nb = (int)(k / GROUP_K);
-    const int64_t gx = (m + TI_COLS - 1) / TI_COLS, gy = (n + TI_ROWS - 1) / TI_ROWS;
+    const int64_t gx = gm.work_expert ? work_items : (m + TI_COLS - 1) / TI_COLS, gy = (n + TI_ROWS - 1) / TI_ROWS;
     B200_REQUIRE(gx < 0x7fffffffLL && gy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);
     return launch_pdl(gemm_i8_tcgen05_kernel<TYPE>, dim3((unsigned)gx, (unsigned)gy), dim3(TI_THREADS), (size_t)TiSizes<TYPE>::SMEM_BYTES, s, tiles, acts,
-                      dst, lddst, n, nb, m, err);
+                      dst, lddst, n, nb, m, err, gm);
+}
+
+// ---- MUL_MAT_ID: (token, slot) pairs grouped by expert ---------------------------------------------------------
+// counts[e] = pairs routed to expert e (the ids outside [0, n_expert) are skipped, as the per-pair kernels skip them)
+__global__ void mmid_count_kernel(const int32_t *ids, int n_pairs, int n_expert, int *counts) {
+    pdl_trigger();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_pairs) return;
+    const int e = ids[i];
+    if (e >= 0 && e < n_expert) atomicAdd(&counts[e], 1);
+}
+// one CTA: work items per expert (32 pairs each) laid out expert after expert; first_item[e] = the expert's first item
+__global__ void mmid_plan_kernel(const int *counts, int n_expert, int max_items, int *first_item, int *cursor, int *work_expert, int *col_act,
+                                 int *col_out) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ int total;
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < n_expert; e++) {
+            first_item[e] = at;
+            cursor[e] = 0;
+            const int items = (counts[e] + TI_COLS - 1) / TI_COLS;
+            for (int i = 0; i < items && at + i < max_items; i++) work_expert[at + i] = e;
+            at += items;
+        }
+        total = at < max_items ? at : max_items;
+        for (int w = total; w < max_items; w++) work_expert[w] = -1;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < max_items * TI_COLS; i += blockDim.x) {
+        col_act[i] = -1;
+        col_out[i] = -1;
+    }
+}
+// pair i takes the next free column of its expert's items (the order inside an expert does not matter: every output
+// element depends on its own pair only)
+__global__ void mmid_scatter_kernel(const int32_t *ids, int n_pairs, int n_ids, int ne11, int n_expert, const int *first_item, int *cursor,
+                                    int *col_act, int *col_out) {
+    pdl_trigger();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_pairs) return;
+    const int e = ids[i];
+    if (e < 0 || e >= n_expert) return;
+    const int at = atomicAdd(&cursor[e], 1);
+    const int tok = i / n_ids, slot = i % n_ids;
+    const int64_t col = (int64_t)first_item[e] * TI_COLS + at;
+    col_act[col] = tok * ne11 + slot % ne11;   // crates/ggml/src/compute.rs:2124: the activation row of a slot
+    col_out[col] = i;
 }
 
 }  // namespace
+
+// MUL_MAT_ID over MXFP4 / Q4_0 experts whose row count takes the 8x8 route (the chain of the per-pair gemv,
+// crates/ggml/src/compute.rs:2131-2151, repack.rs:1048-1068, is the per-block fma of this kernel): the pairs are counted
+// and grouped by expert on the device, and every expert's weights meet all the rows routed to it in tensor-core tiles
+// of 32 pairs.  lists: scratch of mmid_grouped_scratch_bytes(n_expert, pairs) bytes.
+size_t mmid_grouped_scratch_bytes(int64_t n_expert, int64_t n_pairs) {
+    const int64_t max_items = n_pairs / TI_COLS + n_expert;
+    return (size_t)(3 * n_expert + max_items + 2 * max_items * TI_COLS) * sizeof(int) + 256;
+}
+int launch_mul_mat_id_grouped(int type, int64_t n, int64_t k, int64_t n_expert, int64_t ne11, int64_t n_tok, int64_t n_ids, const uint8_t *tiles,
+                              ActView acts, const int32_t *ids, float *dst, void *lists, cudaStream_t s) {
+    B200_REQUIRE(type == B200_TYPE_MXFP4 || type == B200_TYPE_Q4_0, "mul_mat_id grouped: type %d is not a 32-element-block type on the 8x8 route", type);
+    const int64_t n_pairs = n_tok * n_ids;
+    B200_REQUIRE(n_pairs < 0x7fffffffLL / TI_COLS && n_expert < (1 << 20), "mul_mat_id grouped: too many pairs or experts");
+    const int64_t max_items = n_pairs / TI_COLS + n_expert;
+    int *counts = (int *)lists, *first_item = counts + n_expert, *cursor = first_item + n_expert, *work_expert = cursor + n_expert;
+    int *col_act = work_expert + max_items, *col_out = col_act + max_items * TI_COLS;
+    B200_CUDA(cudaMemsetAsync(counts, 0, sizeof(int) * (size_t)n_expert, s));
+    int rc = launch_pdl(mmid_count_kernel, dim3((unsigned)((n_pairs + 255) / 256)), dim3(256), 0, s, ids, (int)n_pairs, (int)n_expert, counts);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    rc = launch_pdl(mmid_plan_kernel, dim3(1), dim3(256), 0, s, (const int *)counts, (int)n_expert, (int)max_items, first_item, cursor, work_expert,
+                    col_act, col_out);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    rc = launch_pdl(mmid_scatter_kernel, dim3((unsigned)((n_pairs + 255) / 256)), dim3(256), 0, s, ids, (int)n_pairs, (int)n_ids, (int)ne11, (int)n_expert,
+                    (const int *)first_item, cursor, col_act, col_out);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    GroupMap gm;
+    gm.work_expert = work_expert;
+    gm.col_act = col_act;
+    gm.col_out = col_out;
+    gm.expert_bytes = (int64_t)((n + TILE_ROWS - 1) / TILE_ROWS) * (k / GROUP_K) * chunk_bytes(type);
+    if (type == B200_TYPE_MXFP4) return launch_i8<B200_TYPE_MXFP4>(n, k, TI_COLS, tiles, acts, dst, n, s, gm, max_items);
+    return launch_i8<B200_TYPE_Q4_0>(n, k, TI_COLS, tiles, acts, dst, n, s, gm, max_items);
+}
 
 // Q8_0 (fast numerics), Q4_0, MXFP4 (8x8 gemm chain) and Q6_K (tiled chain) prompt mat-muls, 32 activation rows and up
 int launch_gemm_tcgen05_i8(int type, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,

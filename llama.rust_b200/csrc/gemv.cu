@@ -938,6 +938,16 @@ int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint
     B200_REQUIRE(false, "mul_mat: no kernel yet for weight type %d with route %d (m = %lld)", type, route, (long long)m);
 }
 
+// B200_MMID_GROUPED=0 keeps MUL_MAT_ID on one CTA set per (token, slot) pair (for side-by-side measurements)
+static bool mmid_grouped_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_MMID_GROUPED");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
 // rows routed to each expert (for the tiled / row-dot split of K-quant experts)
 __global__ void count_expert_rows_kernel(const int32_t *ids, int64_t n_pairs, int n_expert, int *counts) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -965,6 +975,10 @@ int launch_mul_mat_id(int type, int64_t n, int64_t k, int64_t n_expert, int64_t 
     pm.min_count = 0;
     pm.max_count = 0x7fffffff;
     const bool repack = n % 8 == 0;
+    // enough pairs to fill tensor-core tiles: grouped by expert, every expert's weights read once (same per-block chain,
+    // same bits as the per-pair kernels below)
+    if ((type == B200_TYPE_MXFP4 || type == B200_TYPE_Q4_0) && repack && pairs >= 64 && mmid_grouped_enabled() && gemm_tcgen05_enabled())
+        return launch_mul_mat_id_grouped(type, n, k, n_expert, ne11, n_tok, n_ids, tiles, acts, ids, dst, counts, s);
     if (type == B200_TYPE_MXFP4 && repack) return launch_generic<TraitsB32<true>, 1>(n, nb, tiles, acts, dst, n, s, pm, pairs);
     if (type == B200_TYPE_Q4_0 && repack) return launch_generic<TraitsB32<false>, 1>(n, nb, tiles, acts, dst, n, s, pm, pairs);
     if (type == B200_TYPE_Q4_K && repack)

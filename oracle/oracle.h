@@ -116,6 +116,11 @@ int orc_flash_attn_ext(const OrcFlashArgs *a);
 int orc_mul_mat_repacked(int type, int64_t N, int64_t K, int64_t M, const void *Wrep, const float *X,
                          float *out, int n_threads);
 int orc_num_threads();
+// Vector forms of the Q4_K 8x8 tile core and the Q6_K row dot (oracle_simd.cpp): the same exact integers, so every
+// result stays bit-identical.  orc_set_simd caps the level (0 scalar, 1 AVX2, 2 AVX-512 VNNI; default 2);
+// orc_simd_level is what runs on this host under the cap.
+void orc_set_simd(int max_level);
+int orc_simd_level(void);
 int orc_pick_route(int type, int64_t N, int64_t M);   // the route orc_mul_mat takes with ORC_ROUTE_AUTO
 
 }  // extern "C"

@@ -5,6 +5,10 @@
 // crates/ggml/src/vec_dot.rs, repack.rs, tiled.rs and compute.rs.
 #include "oracle.h"
 
+// vector forms of the two integer cores (oracle_simd.cpp): 1 = filled the outputs, 0 = not available / switched off
+extern "C" int orc_q4kx8_ints_simd(const uint8_t *tile, const int8_t *q8, const int16_t *bs, int iacc[4][8], int imin[4][8]);
+extern "C" int orc_q6k_lane_sums_simd(const uint8_t *ql, const uint8_t *qh, const int8_t *sc, const int8_t *q8, const int16_t *bsums, int sumi[8]);
+
 #include <omp.h>
 
 #include <algorithm>
@@ -128,6 +132,10 @@ static float vec_dot_q6_K_q8_K(int64_t n, const block_q6_K *x, const block_q8_K 
         const uint8_t *ql = x[i].ql, *qh = x[i].qh;
         const int8_t *sc = x[i].scales;
         int sumi[8] = {0};
+        if (orc_q6k_lane_sums_simd(ql, qh, sc, y[i].qs, y[i].bsums, sumi)) {   // the same exact lane sums, bias already taken off
+            for (int l = 0; l < 8; l++) acc[l] = fmaf(d, (float)sumi[l], acc[l]);
+            continue;
+        }
         for (int j = 0; j < QK_K / 128; j++)
             for (int k = 0; k < 4; k++)
                 for (int ii = 0; ii < 32; ii++) {
@@ -201,6 +209,8 @@ static inline void q4kx8_scales(const uint8_t *tile, int sb, uint8_t *s, uint8_t
 // pair g for the 8 columns.  q8 = 256 plain-order quants, bs = 16 bsums.
 static inline void q4kx8_ints(const uint8_t *tile, const int8_t *q8, const int16_t *bs,
                               int iacc[4][8], int imin[4][8]) {
+    // the same exact integers from the vector form when the host has one (oracle_simd.cpp; orc_set_simd(0) turns it off)
+    if (orc_q4kx8_ints_simd(tile, q8, bs, iacc, imin)) return;
     for (int g = 0; g < 4; g++) {
         uint8_t s_lo[8], m_lo[8], s_hi[8], m_hi[8];
         q4kx8_scales(tile, 2 * g, s_lo, m_lo);

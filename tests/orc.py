@@ -55,8 +55,20 @@ def lib():
     L.orc_mul_mat_repacked.argtypes = [i32, i64, i64, i64, vp, vp, vp, i32]
     L.orc_mul_mat_id.argtypes = [i32, i64, i64, i64, i64, i64, i64, vp, vp, vp, vp, i32, i32]
     L.orc_flash_attn_ext.argtypes = [vp]
+    L.orc_set_simd.restype = None
+    L.orc_set_simd.argtypes = [i32]
+    L.orc_simd_level.restype = i32
     _lib = L
     return L
+
+
+def set_simd(max_level):
+    """Caps the oracle's vector level: 0 scalar, 1 AVX2, 2 AVX-512 VNNI."""
+    lib().orc_set_simd(max_level)
+
+
+def simd_level():
+    return lib().orc_simd_level()
 
 
 def _p(a):

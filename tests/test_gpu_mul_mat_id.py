@@ -66,3 +66,26 @@ def test_empty_batch(dev):
     w = dev.ExpertWeights(orc.MXFP4, W, 32, 256)
     out = dev.mul_mat_id(w, np.zeros((0, 1, 256), np.float32), np.zeros((0, 2), np.int32))
     assert out.shape == (0, 2, 32)
+
+
+@pytest.mark.parametrize("ty", [orc.MXFP4, orc.Q4_0], ids=lambda t: orc.TYPE_NAMES[t])
+def test_grouped_by_expert_with_ragged_counts(dev, ty):
+    """enough pairs for the expert-grouped tensor-core path: one expert gets far more than 32 pairs (several work
+    items, the last one short), one gets none, the pair count is not a multiple of 32"""
+    E, n, k, n_tok, top = 7, 96, 512, 71, 3
+    W = synth.weights(ty, E * n, k, seed=81).reshape(E, n, -1)
+    B = synth.activations(n_tok * top, k, seed=82).reshape(n_tok, top, k)
+    rng = np.random.default_rng(83)
+    ids = np.empty((n_tok, top), dtype=np.int32)
+    for t in range(n_tok):
+        # expert 0 in most tokens, expert 5 never; ids of a token are distinct
+        pool = [e for e in range(E) if e != 5]
+        chosen = [0] if t % 5 else []
+        rest = [e for e in pool if e not in chosen]
+        chosen += list(rng.permutation(rest)[:top - len(chosen)])
+        ids[t] = chosen
+    want, route = orc.mul_mat_id(ty, W, B, ids)
+    assert route == orc.ROUTE_REPACK
+    got = dev.mul_mat_id(dev.ExpertWeights(ty, W, n, k), B, ids)
+    assert dev.kernel_error() == 0
+    assert bits_equal(got, want)
