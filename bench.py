@@ -34,7 +34,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 Q4_K = 12
 SHAPES = [(4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096)]  # (n rows, k)
 METRIC = "q4_K_decode_mat_mul_hbm_gbs"
-CPU_KIND = "port"   # the CPU arm is the oracle's C++ restatement of the reference's routes (no Rust toolchain here)
+# the CPU arm is the oracle's C++ restatement of the reference's routes (no Rust toolchain here) with AVX2 / AVX-512 VNNI
+# bodies for the Q4_K 8x8 core and the Q6_K row dot, as the reference's CPU path has (bit-identical to the scalar loops)
+CPU_KIND = "port-simd"
+SIMD_NAMES = {0: "scalar", 1: "AVX2", 2: "AVX-512 VNNI"}
 # measured DRAM bytes / algorithmic bytes of one launch of the decode kernel in use (gemv_q4_K_row_kernel on
 # 14336 x 4096: dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture summarized in
 # profiles/gemv_q4_K_row_kernel_decode.md); weights are read once whatever the shape
@@ -207,12 +210,13 @@ def cpu_gemv_baseline(orc, seconds=10.0):
     reps_w, xs, outs = cpu_gemv_prepare(orc)
     cpu_gemv_step(orc, reps_w, xs, outs, threads)
     n_rep, t0 = 0, time.perf_counter()
-    while n_rep < 3 or (time.perf_counter() - t0 < seconds and n_rep < 50):
+    while n_rep < 3 or (time.perf_counter() - t0 < seconds and n_rep < 5000):
         cpu_gemv_step(orc, reps_w, xs, outs, threads)
         n_rep += 1
     dt = time.perf_counter() - t0
-    return {"value": total * n_rep / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
-            "sample": f"the full step x {n_rep} repetitions ({dt:.1f} s)"}
+    level = orc.simd_level()
+    return {"value": total * n_rep / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": CPU_KIND if level else "port",
+            "simd": SIMD_NAMES[level], "sample": f"the full step x {n_rep} repetitions ({dt:.1f} s)"}
 
 
 def run_gemv(b, args, rank, world, barrier, reduce_max, local):

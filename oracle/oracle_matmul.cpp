@@ -267,35 +267,42 @@ static void gemv_q4_K_8x8_q8_K(int64_t n, float *s, const uint8_t *vx, const uin
 static void gemm_q4_K_8x8_q8_K(int64_t n, float *s, int64_t bs, const uint8_t *vx, const uint8_t *vy,
                                int64_t nr, int64_t nc) {
     const int64_t nb = n / QK_K;
+    // the 4 rows of an activation tile in plain order, once per tile: element el of row r is at
+    // qs[(el/8)*32 + r*8 + el%8], its 16-element sums at 16*(el/64) + 4r + (el/16)%4
+    std::vector<int8_t> q8(nb * 4 * 256);
+    std::vector<int16_t> bsr(nb * 4 * 16);
     for (int64_t y = 0; y < nr / 4; y++) {
         const uint8_t *ablk = vy + y * nb * 1168;
+        for (int64_t b = 0; b < nb; b++) {
+            const int8_t *aq = (const int8_t *)(ablk + b * 1168 + 16);
+            const int16_t *abs_ = (const int16_t *)(ablk + b * 1168 + 1040);
+            for (int r = 0; r < 4; r++) {
+                int8_t *q = q8.data() + (b * 4 + r) * 256;
+                for (int p = 0; p < 32; p++) std::memcpy(q + 8 * p, aq + p * 32 + r * 8, 8);
+                for (int j = 0; j < 16; j++) bsr[(b * 4 + r) * 16 + j] = abs_[16 * (j / 4) + 4 * r + j % 4];
+            }
+        }
         for (int64_t x = 0; x < nc / 8; x++) {
             const uint8_t *bmat = vx + x * nb * 1152;
             float acc[4][8] = {{0}}, accmin[4][8] = {{0}};
             for (int64_t b = 0; b < nb; b++) {
                 const uint8_t *tile = bmat + b * 1152;
-                const uint8_t *a = ablk + b * 1168;
-                const float *ad = (const float *)a;
-                const int8_t *aq = (const int8_t *)(a + 16);
-                const int16_t *abs_ = (const int16_t *)(a + 1040);
-                // de-interleave the 4 rows once: element el of row r is at
-                // qs[(el/8)*32 + r*8 + el%8], bsums at 16*(el/64) + 4r + (el/16)%4
-                int8_t q8[4][256];
-                int16_t bsr[4][16];
-                for (int r = 0; r < 4; r++) {
-                    for (int el = 0; el < 256; el++) q8[r][el] = aq[(el / 8) * 32 + r * 8 + el % 8];
-                    for (int j = 0; j < 16; j++) bsr[r][j] = abs_[16 * (j / 4) + 4 * r + j % 4];
+                const float *ad = (const float *)(ablk + b * 1168);
+                float dcol[8], mcol[8];
+                for (int c = 0; c < 8; c++) {
+                    uint16_t dh, mh;
+                    std::memcpy(&dh, tile + 2 * c, 2);
+                    std::memcpy(&mh, tile + 16 + 2 * c, 2);
+                    dcol[c] = f32_of(dh);
+                    mcol[c] = f32_of(mh);
                 }
                 for (int r = 0; r < 4; r++) {
                     int ia[4][8], im[4][8];
-                    q4kx8_ints(tile, q8[r], bsr[r], ia, im);
+                    q4kx8_ints(tile, q8.data() + (b * 4 + r) * 256, bsr.data() + (b * 4 + r) * 16, ia, im);
                     for (int g = 0; g < 4; g++)
                         for (int c = 0; c < 8; c++) {
-                            uint16_t dh, mh;
-                            std::memcpy(&dh, tile + 2 * c, 2);
-                            std::memcpy(&mh, tile + 16 + 2 * c, 2);
-                            acc[r][c] = fmaf((float)ia[g][c], f32_of(dh) * ad[r], acc[r][c]);
-                            accmin[r][c] = fmaf((float)im[g][c], f32_of(mh) * ad[r], accmin[r][c]);
+                            acc[r][c] = fmaf((float)ia[g][c], dcol[c] * ad[r], acc[r][c]);
+                            accmin[r][c] = fmaf((float)im[g][c], mcol[c] * ad[r], accmin[r][c]);
                         }
                 }
             }
@@ -418,6 +425,13 @@ static float tiled_dot_q6_K(int64_t n, const block_q6_K *x, const block_q8_K *y)
     for (int64_t i = 0; i < n / QK_K; i++) {
         const uint8_t *ql = x[i].ql, *qh = x[i].qh;
         int s1 = 0;
+        int lanes[8];
+        // the vector row-dot core yields the same exact total, split over eight lanes
+        if (orc_q6k_lane_sums_simd(ql, qh, x[i].scales, y[i].qs, y[i].bsums, lanes)) {
+            for (int l = 0; l < 8; l++) s1 += lanes[l];
+            out = fmaf(f32_of(x[i].d) * (float)s1, y[i].d, out);
+            continue;
+        }
         for (int sb = 0; sb < 16; sb++) {
             int raw = 0;
             for (int t = 0; t < 16; t++) {
