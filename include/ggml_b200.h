@@ -84,9 +84,19 @@ int b200_kernel_error(int *code);
  * mat-muls of few row tiles take the bulk-copy streaming kernel (selectable otherwise with B200_GEMV_STREAM=1),
  * its waits poll at most spin_limit times, and its producer leaves ring unit skip_unit unfilled (-1 = none), so
  * that a test can watch a bounded wait run out: the kernel returns, its output rows stay unwritten and
- * b200_kernel_error reports code 1 (producer) or 2 (consumer).  spin_limit 0 disarms the hook. */
+ * b200_kernel_error reports code 1 (producer) or 2 (consumer).  spin_limit 0 disarms the hook.
+ * b200_debug_decode_step_launches: how many one-token steps the backend has run as its single persistent kernel so far
+ * in this process (a test that compares it with the node-by-node path first checks that it was taken at all).
+ * b200_debug_decode_step_wait: while spin_limit > 0 every wait of that kernel polls at most spin_limit times and CTA
+ * skip_cta never arrives at its grid barrier number skip_barrier (-1 = none): the others' wait runs out, the kernel
+ * returns with its outputs unfinished and b200_kernel_error reports code 5.  spin_limit 0 disarms the hook. */
 unsigned long long b200_debug_alloc_count(void);
 void b200_debug_stream_wait(int spin_limit, int skip_unit);
+unsigned long long b200_debug_decode_step_launches(void);
+/* profiling aid: the device clock (ns) at which CTA 0 of the last persistent step started and passed each of its grid
+ * barriers; call after synchronizing; returns how many stamps were copied (0 where there is nothing to read) */
+int b200_debug_decode_step_times(unsigned long long *out, int n);
+void b200_debug_decode_step_wait(int spin_limit, int skip_cta, int skip_barrier);
 /* Which kernel a Q4_K prompt mat-mul (8x8 gemm route, n weight rows, m >= 32 activation rows) takes on a GPU with
  * sm_count SMs: 0 = integer tcgen05 kernel, 3 / 4 = the two-pass f16-image kernels with 64 / 128 activation rows
  * per CTA.  Pure host arithmetic (CTA waves times measured time per wave, plus the expansion); no CUDA call.

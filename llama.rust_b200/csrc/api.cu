@@ -189,6 +189,9 @@ int b200_get_numerics(void) { return numerics_mode(); }
 unsigned long long b200_debug_alloc_count(void) { return library_alloc_count(); }
 
 void b200_debug_stream_wait(int spin_limit, int skip_unit) { gemv_stream_debug_wait(spin_limit, skip_unit); }
+unsigned long long b200_debug_decode_step_launches(void) { return decode_persistent_launches(); }
+int b200_debug_decode_step_times(unsigned long long *out, int n) { return decode_persistent_times(out, n); }
+void b200_debug_decode_step_wait(int spin_limit, int skip_cta, int skip_barrier) { decode_persistent_debug(spin_limit, skip_cta, skip_barrier); }
 
 int b200_prompt_kernel_choice(int64_t n, int64_t m, int sm_count) { return gemm_chain_pick_for(n, m, sm_count); }
 

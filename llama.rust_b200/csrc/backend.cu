@@ -17,6 +17,7 @@
 #include "common.cuh"
 #include "ggml_b200_backend.h"
 #include "tp.h"
+#include "decode_persistent.h"
 
 namespace b200 {
 namespace {
@@ -123,6 +124,21 @@ struct BackendCtx {
     bool fuse_siblings = true;      // one launch for one-row Q4_K mat-muls over the same activations (B200_FUSE_SIBLINGS=0 / fuse_siblings=0: off)
     bool fuse_prologue = true;      // the norm / silu / quantization in front of a one-row Q4_K mat-mul inside its kernel (B200_FUSE_PROLOGUE=0 / fuse_prologue=0: off)
     bool capturable = true;       // cleared by a node that had to talk to the device while being issued
+    // One-token steps recognized as a whole (see match_decode_step): the phase list of the persistent kernel, on the device
+    struct StepPlan {
+        uint64_t key = 0;
+        bool usable = false;        // false: the list was looked at and is not a step the kernel takes
+        int first = 0, last = 0;    // nodes [first, last) are the kernel's
+        int n_phases = 0;
+        DpPhase *dev_phases = nullptr;
+        DpSync *dev_sync = nullptr;
+        float *dev_partial = nullptr;
+        uint64_t generation = 0;
+        uint64_t used = 0;
+    };
+    std::vector<StepPlan> plans;
+    bool persistent_decode = false; // B200_DECODE_PERSISTENT=1 / decode_persistent=1: on
+    uint64_t current_key = 0;       // node_list_key of the list being computed (0: not known)
     TpGroup *tp = nullptr;        // the tensor-parallel group whose collectives the TP_* nodes run (owned by the driver)
 };
 constexpr size_t SHADOW_MAX_BYTES = 1 << 20;
@@ -1054,6 +1070,277 @@ static int compute_mul_mat_row_fused(BackendCtx *bc, const ggml_cgraph *g, int i
     return rc;
 }
 
+// ---- a one-token step as one persistent kernel ------------------------------------------------------------
+// The node list of a single-token llama step (crates/llama/src/graph_arch.rs:106-248 with the flash-attention branch
+// of attn_kv_cached, :1173-1240, and build_ffn_silu_par, :1128-1158) is, per layer and with the aliasing nodes
+// (RESHAPE / VIEW / PERMUTE) left out, the 20 operations of LAYER_OPS below; after the last layer come the output
+// norm, GET_ROWS of the wanted row and the output mat-mul.  When a list has exactly that form, every weight is
+// Q4_K or Q6_K in tile layout with whole row tiles, the numerics policy is the tolerant one (attention runs in its
+// fast form) and no tensor-parallel group is attached, the nodes from the first layer's norm to the logits run as
+// decode_persistent_kernel.  Anything else keeps the node-by-node path.
+static const int LAYER_OPS[20] = {GGML_OP_RMS_NORM, GGML_OP_MUL, GGML_OP_MUL_MAT, GGML_OP_ROPE, GGML_OP_SET_ROWS, GGML_OP_MUL_MAT, GGML_OP_SET_ROWS,
+                                  GGML_OP_MUL_MAT, GGML_OP_ROPE, GGML_OP_FLASH_ATTN_EXT, GGML_OP_MUL_MAT, GGML_OP_ADD, GGML_OP_RMS_NORM, GGML_OP_MUL,
+                                  GGML_OP_MUL_MAT, GGML_OP_UNARY, GGML_OP_MUL_MAT, GGML_OP_MUL, GGML_OP_MUL_MAT, GGML_OP_ADD};
+
+static bool step_weight_ok(const ggml_tensor *mm, const ggml_tensor *acts) {
+    const ggml_tensor *w = mm->src[0];
+    return supports_mul_mat(mm, nullptr) && mm->src[1] && mm->src[1]->data == acts->data && (w->type == B200_TYPE_Q4_K || w->type == B200_TYPE_Q6_K) &&
+           is_tiled_tensor(w) && w->ne[2] == 1 && w->ne[1] % TILE_ROWS == 0 && mm->ne[1] == 1 && mm->ne[2] == 1 && mm->ne[3] == 1 &&
+           ((uintptr_t)mm->data & 15) == 0 && ((uintptr_t)acts->data & 15) == 0;
+}
+static void step_mat(DpMat *m, const ggml_tensor *mm, int epi) {
+    memset(m, 0, sizeof(*m));
+    m->tiles = (const uint8_t *)mm->src[0]->data;
+    m->dst = (float *)mm->data;
+    m->type = mm->src[0]->type;
+    m->n_tiles = (int)(mm->src[0]->ne[1] / TILE_ROWS);
+    m->epi = epi;
+}
+static const ggml_tensor *other_src(const ggml_tensor *op, const ggml_tensor *one) { return op->src[0] == one ? op->src[1] : op->src[0]; }
+static bool norm_pair_ok(const ggml_tensor *norm, const ggml_tensor *mul) {
+    return norm->ne[1] == 1 && norm->ne[2] == 1 && norm->ne[3] == 1 && norm->ne[0] % GROUP_K == 0 && fuses_norm_mul(norm, mul) &&
+           dense_f32(norm->src[0]) && dense_f32(mul) && ((uintptr_t)norm->src[0]->data & 15) == 0 && ((uintptr_t)mul->src[1]->data & 15) == 0 &&
+           ((uintptr_t)norm->data & 15) == 0 && ((uintptr_t)mul->data & 15) == 0;
+}
+
+// fills `phases` for the nodes [*first, *last) of g; false: not a step the kernel takes
+static bool match_decode_step(BackendCtx *bc, const ggml_cgraph *g, std::vector<DpPhase> *phases, int *first, int *last, int *fa_splits,
+                              int *fa_heads) {
+    if (!bc->persistent_decode || numerics_mode() != 1 || bc->tp != nullptr) return false;
+    std::vector<int> ops;   // the nodes that compute something
+    for (int i = 0; i < g->n_nodes; i++)
+        if (g->nodes[i] && !is_alias_op(g->nodes[i])) ops.push_back(i);
+    auto T = [&](size_t c) { return g->nodes[ops[c]]; };
+    size_t c0 = 0;
+    while (c0 < ops.size() && T(c0)->op != GGML_OP_RMS_NORM) c0++;
+    size_t c = c0;
+    int n_layer = 0;
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, bc->device) != cudaSuccess || sms <= 0) return false;
+    int rot = 0;
+    auto gemv_phase = [&](int prologue, const ggml_tensor *x_in, const ggml_tensor *norm, const ggml_tensor *mul, int k) {
+        DpPhase P;
+        memset(&P, 0, sizeof(P));
+        P.kind = DP_GEMV;
+        P.prologue = prologue;
+        P.k = k;
+        P.nb = k / GROUP_K;
+        P.x = (const float *)x_in->data;
+        if (prologue == DP_PRO_NORM) {
+            P.norm_w = (const float *)mul->src[1]->data;
+            P.eps = param_f32(norm, 0);
+            P.y = (float *)norm->data;
+            P.y_mul = (float *)mul->data;
+        }
+        return P;
+    };
+    auto close_phase = [&](DpPhase &P) {
+        P.jobs = 0;
+        if (P.pair) P.jobs = P.mat[0].n_tiles;
+        else for (int m = 0; m < P.n_mat; m++) P.jobs += P.mat[m].n_tiles;
+        P.rot = rot % sms;
+        rot = (rot + P.jobs) % sms;
+        phases->push_back(P);
+    };
+    while (c + 20 <= ops.size()) {
+        bool is_layer = true;
+        for (int j = 0; j < 20 && is_layer; j++) is_layer = T(c + j)->op == LAYER_OPS[j];
+        if (!is_layer) break;
+        const ggml_tensor *norm1 = T(c), *mul1 = T(c + 1), *mmk = T(c + 2), *ropek = T(c + 3), *setk = T(c + 4), *mmv = T(c + 5), *setv = T(c + 6);
+        const ggml_tensor *mmq = T(c + 7), *ropeq = T(c + 8), *fa = T(c + 9), *mmo = T(c + 10), *add1 = T(c + 11), *norm2 = T(c + 12), *mul2 = T(c + 13);
+        const ggml_tensor *mmg = T(c + 14), *silu = T(c + 15), *mmu = T(c + 16), *gmul = T(c + 17), *mmd = T(c + 18), *add2 = T(c + 19);
+        if (!norm_pair_ok(norm1, mul1) || !norm_pair_ok(norm2, mul2)) return false;
+        if (!step_weight_ok(mmk, mul1) || !step_weight_ok(mmv, mul1) || !step_weight_ok(mmq, mul1)) return false;
+        const int64_t E = norm1->ne[0];
+        if (mmk->src[0]->ne[0] != E || mmg->src[0]->ne[0] != E) return false;
+        // rotation of K and Q: adjacent channel pairs, a by-position table, positions on the device
+        const ggml_tensor *ropes[2] = {ropek, ropeq};
+        const ggml_tensor *srcs[2] = {mmk, mmq};
+        const float *table = nullptr;
+        int64_t table_rows = 0;
+        for (int r = 0; r < 2; r++) {
+            const ggml_tensor *ro = ropes[r];
+            if (!supports_glue(ro, nullptr) || ro->src[2] || ro->op_params[2] != 0 || ro->src[0]->data != srcs[r]->data) return false;
+            if (ro->src[0]->ne[2] != 1 || ro->ne[0] != 128 || ro->op_params[1] > 128 || ro->op_params[1] % 2) return false;
+            if ((int64_t)ro->src[0]->nb[1] != ro->ne[0] * 4 || (int64_t)ro->nb[1] != ro->ne[0] * 4 || !ro->src[1] || ro->src[1]->type != B200_TYPE_I32) return false;
+            const std::vector<int32_t> key = rope_param_key(ro, std::vector<float>());
+            const float *t = nullptr;
+            for (auto &cand : bc->rope_by_pos)
+                if (cand.key == key && cand.dev) { t = cand.dev; table_rows = cand.rows; }
+            if (!t || (table && t != table)) return false;
+            table = t;
+        }
+        if (ropek->src[1]->data != ropeq->src[1]->data) return false;
+        // cache writes: F16 rows of the layer's cache, one cell index for both
+        if (setk->src[0]->data != ropek->data || setv->src[0]->data != mmv->data || setk->type != B200_TYPE_F16 || setv->type != B200_TYPE_F16) return false;
+        if (!supports_glue(setk, nullptr) || !supports_glue(setv, nullptr) || setk->src[1]->data != setv->src[1]->data || setk->src[1]->type != B200_TYPE_I64) return false;
+        if (setk->ne[0] != mmk->ne[0] || setv->ne[0] != mmv->ne[0] || setk->nb[1] != setk->ne[0] * 2 || setv->nb[1] != setv->ne[0] * 2) return false;
+        // attention: one token, head size 128, the rotated Q, the caches just written
+        if (!supports_flash(fa, nullptr) || fa->src[0]->data != ropeq->data || fa->src[4] || fa->src[0]->ne[0] != 128 || fa->src[2]->ne[0] != 128) return false;
+        if (fa->src[0]->ne[1] != 1 || !fa->src[3] || !is_contiguous(fa) || ((uintptr_t)fa->data & 15)) return false;
+        if (fa->src[1]->data != setk->data || fa->src[2]->data != setv->data) return false;
+        if (param_f32(fa, 1) != 0.0f || param_f32(fa, 2) != 0.0f) return false;
+        if (!step_weight_ok(mmo, fa) || !fuses_mul_mat_add(mmo, add1)) return false;
+        if (!step_weight_ok(mmg, mul2) || !step_weight_ok(mmu, mul2) || norm2->src[0]->data != add1->data) return false;
+        if (silu->src[0] != mmg || !supports_glue(silu, nullptr) || !fuses_silu_mul(silu, gmul) || other_src(gmul, silu) != mmu) return false;
+        if (mmg->src[0]->ne[1] != mmu->src[0]->ne[1] || !step_weight_ok(mmd, gmul) || !fuses_mul_mat_add(mmd, add2)) return false;
+        if (other_src(add2, mmd)->data != add1->data || other_src(add1, mmo)->data != norm1->src[0]->data) return false;
+        if (!dense_f32(add1) || !dense_f32(add2) || !dense_f32(gmul)) return false;
+
+        // phase 1: norm | K, V, Q | rope, cache rows
+        DpPhase P1 = gemv_phase(DP_PRO_NORM, norm1->src[0], norm1, mul1, (int)E);
+        P1.n_mat = 3;
+        step_mat(&P1.mat[0], mmq, DP_EPI_ROPE);
+        P1.mat[0].dst_raw = (float *)mmq->data;
+        P1.mat[0].dst = (float *)ropeq->data;
+        step_mat(&P1.mat[1], mmk, DP_EPI_ROPE_CACHE);
+        P1.mat[1].dst_raw = (float *)mmk->data;
+        P1.mat[1].dst = (float *)ropek->data;
+        P1.mat[1].cache = (__half *)setk->data;
+        step_mat(&P1.mat[2], mmv, DP_EPI_CACHE);
+        P1.mat[2].cache = (__half *)setv->data;
+        P1.head_dim = 128;
+        P1.n_dims = ropek->op_params[1];
+        P1.rope_table = table;
+        P1.rope_rows = table_rows;
+        P1.pos = (const int32_t *)ropek->src[1]->data;
+        P1.cell = (const int64_t *)setk->src[1]->data;
+        P1.cache_stride = setk->ne[0];
+        P1.cache_rows = setk->ne[1];
+        close_phase(P1);
+        // phase 2: attention
+        DpPhase P2;
+        memset(&P2, 0, sizeof(P2));
+        P2.kind = DP_ATTN;
+        {
+            const ggml_tensor *q = fa->src[0], *k = fa->src[1], *v = fa->src[2], *m = fa->src[3];
+            b200_flash_attn_args &a = P2.fa;
+            a.dk = q->ne[0]; a.dv = v->ne[0]; a.n_tok = q->ne[1]; a.n_head = q->ne[2]; a.n_head_kv = k->ne[2]; a.n_kv = k->ne[1];
+            a.q = (const float *)q->data; a.q_nb1 = (int64_t)q->nb[1]; a.q_nb2 = (int64_t)q->nb[2];
+            a.k = k->data; a.k_nb1 = (int64_t)k->nb[1]; a.k_nb2 = (int64_t)k->nb[2];
+            a.v = v->data; a.v_nb1 = (int64_t)v->nb[1]; a.v_nb2 = (int64_t)v->nb[2];
+            a.mask = m->data; a.mask_nb1 = (int64_t)m->nb[1];
+            memcpy(&a.scale, &fa->op_params[0], 4);
+            a.dst = (float *)fa->data;
+            a.n_chunks = bc->cpu_threads;
+            a.mode = 1;
+            if (a.n_head % a.n_head_kv || a.n_head / a.n_head_kv > 4 || a.n_head_kv > DP_MAX_KV_HEADS || a.n_kv <= 0 || a.q_nb1 % 4 || a.q_nb2 % 4) return false;
+            if (!flash_attn_fast_dims(&a, sms, 4, &P2.fd)) return false;
+            P2.scale_log2 = a.scale * 1.4426950408889634f;
+            if (*fa_splits && (*fa_splits != P2.fd.n_splits || *fa_heads != (int)a.n_head_kv)) return false;
+            *fa_splits = P2.fd.n_splits;
+            *fa_heads = (int)a.n_head_kv;
+        }
+        phases->push_back(P2);
+        // phase 3: attn_output + residual
+        DpPhase P3 = gemv_phase(DP_PRO_PLAIN, fa, nullptr, nullptr, (int)mmo->src[0]->ne[0]);
+        P3.n_mat = 1;
+        step_mat(&P3.mat[0], mmo, DP_EPI_ADD);
+        P3.addend = (const float *)other_src(add1, mmo)->data;
+        P3.sum = (float *)add1->data;
+        close_phase(P3);
+        // phase 4: norm | gate, up | silu(gate) * up
+        DpPhase P4 = gemv_phase(DP_PRO_NORM, norm2->src[0], norm2, mul2, (int)E);
+        P4.n_mat = 2;
+        P4.pair = 1;
+        step_mat(&P4.mat[0], mmg, DP_EPI_STORE);
+        step_mat(&P4.mat[1], mmu, DP_EPI_STORE);
+        P4.raw0 = (float *)mmg->data;
+        P4.raw1 = (float *)mmu->data;
+        P4.silu_out = (float *)silu->data;
+        P4.h_out = (float *)gmul->data;
+        P4.wide_end = bc->silu_wide ? (int)(mmg->ne[0] & ~(int64_t)15) : 0;
+        close_phase(P4);
+        // phase 5: ffn_down + residual
+        DpPhase P5 = gemv_phase(DP_PRO_PLAIN, gmul, nullptr, nullptr, (int)mmd->src[0]->ne[0]);
+        P5.n_mat = 1;
+        step_mat(&P5.mat[0], mmd, DP_EPI_ADD);
+        P5.addend = (const float *)add1->data;
+        P5.sum = (float *)add2->data;
+        close_phase(P5);
+        if (n_layer == 0) *first = ops[c];
+        n_layer++;
+        c += 20;
+    }
+    if (n_layer == 0 || c + 4 > ops.size()) return false;
+    // output norm, the wanted row, the output mat-mul
+    const ggml_tensor *normf = T(c), *mulf = T(c + 1), *rows = T(c + 2), *mmout = T(c + 3);
+    if (normf->op != GGML_OP_RMS_NORM || mulf->op != GGML_OP_MUL || rows->op != GGML_OP_GET_ROWS || mmout->op != GGML_OP_MUL_MAT) return false;
+    if (!norm_pair_ok(normf, mulf) || rows->src[0] != mulf || rows->ne[1] != 1 || mmout->src[1] != rows) return false;
+    {
+        // the row GET_ROWS would copy is row 0 of a one-row tensor: the mat-mul reads the weighted norm where it is
+        // (the copy, a node nothing else reads, is not made)
+        const ggml_tensor *w = mmout->src[0];
+        if (!supports_mul_mat(mmout, nullptr) || (w->type != B200_TYPE_Q4_K && w->type != B200_TYPE_Q6_K) || !is_tiled_tensor(w) || w->ne[2] != 1 ||
+            w->ne[1] % TILE_ROWS || mmout->ne[1] != 1 || ((uintptr_t)mmout->data & 15) || ((uintptr_t)rows->data & 15) || w->ne[0] != normf->ne[0])
+            return false;
+        DpPhase PF = gemv_phase(DP_PRO_NORM, normf->src[0], normf, mulf, (int)normf->ne[0]);
+        PF.n_mat = 1;
+        step_mat(&PF.mat[0], mmout, DP_EPI_STORE);
+        close_phase(PF);
+    }
+    for (const DpPhase &P : *phases) {
+        if (P.kind != DP_GEMV) continue;
+        if (decode_persistent_work_bytes(P.k) > decode_persistent_work_limit()) return false;
+        if (P.prologue == DP_PRO_NORM && P.k > decode_persistent_norm_max_k()) return false;
+    }
+    *last = ops[c + 3] + 1;
+    return true;
+}
+
+// the plan of the list being computed (built on first sight, rebuilt when an address it holds has been re-allocated)
+static int step_plan_for(BackendCtx *bc, const ggml_cgraph *g, uint64_t key, BackendCtx::StepPlan **out) {
+    *out = nullptr;
+    if (!bc->persistent_decode || numerics_mode() != 1 || bc->tp != nullptr || key == 0) return B200_STATUS_SUCCESS;
+    BackendCtx::StepPlan *p = nullptr;
+    for (auto &cand : bc->plans)
+        if (cand.key == key) p = &cand;
+    static uint64_t clock = 0;
+    if (p && p->generation == bc->generation) {
+        p->used = ++clock;
+        if (p->usable) *out = p;
+        return B200_STATUS_SUCCESS;
+    }
+    if (!p) {
+        if (bc->plans.size() >= 16) {
+            auto lru = std::min_element(bc->plans.begin(), bc->plans.end(),
+                                        [](const BackendCtx::StepPlan &a, const BackendCtx::StepPlan &b) { return a.used < b.used; });
+            B200_CUDA(cudaStreamSynchronize(bc->stream));
+            if (lru->dev_phases) cudaFree(lru->dev_phases);
+            if (lru->dev_sync) cudaFree(lru->dev_sync);
+            if (lru->dev_partial) cudaFree(lru->dev_partial);
+            bc->plans.erase(lru);
+        }
+        bc->plans.emplace_back();
+        p = &bc->plans.back();
+        p->key = key;
+    }
+    p->used = ++clock;
+    p->generation = bc->generation;
+    p->usable = false;
+    std::vector<DpPhase> phases;
+    int fa_splits = 0, fa_heads = 0;
+    if (!match_decode_step(bc, g, &phases, &p->first, &p->last, &fa_splits, &fa_heads)) return B200_STATUS_SUCCESS;
+    B200_CUDA(cudaStreamSynchronize(bc->stream));   // a launch in flight may still read the previous phase list
+    if (p->dev_phases) cudaFree(p->dev_phases);
+    if (p->dev_partial) cudaFree(p->dev_partial);
+    p->dev_phases = nullptr;
+    p->dev_partial = nullptr;
+    if (!p->dev_sync) B200_CUDA(cudaMalloc((void **)&p->dev_sync, sizeof(DpSync)));
+    B200_CUDA(cudaMalloc((void **)&p->dev_partial, decode_persistent_attn_partial_bytes(fa_heads, fa_splits, 128)));
+    for (DpPhase &P : phases)
+        if (P.kind == DP_ATTN) {
+            P.partial = p->dev_partial;
+            P.counters = p->dev_sync->fa_counters;
+        }
+    B200_CUDA(cudaMalloc((void **)&p->dev_phases, phases.size() * sizeof(DpPhase)));
+    B200_CUDA(cudaMemcpy(p->dev_phases, phases.data(), phases.size() * sizeof(DpPhase), cudaMemcpyHostToDevice));
+    p->n_phases = (int)phases.size();
+    p->usable = true;
+    *out = p;
+    return B200_STATUS_SUCCESS;
+}
+
 // Issues the launches of every node, in order, on the backend's stream.
 static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
     bc->act_src = nullptr;   // tensors may have been rewritten between graphs
@@ -1066,10 +1353,22 @@ static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
     std::vector<int> silu_of(g->n_nodes, -1);   // silu_of[j] = i: MUL node j also computes SILU node i
     std::vector<char> done(g->n_nodes, 0);      // mat-mul nodes that ran early, with a sibling
     PendingPrologue pending;                    // a norm / silu that rides with the mat-mul that follows it
+    BackendCtx::StepPlan *plan = nullptr;
+    {
+        int rc = step_plan_for(bc, g, bc->current_key, &plan);
+        if (rc != B200_STATUS_SUCCESS) return rc;
+    }
     for (int i = 0; i < g->n_nodes; i++) {
         const ggml_tensor *op = g->nodes[i];
         B200_REQUIRE(op != nullptr, "graph_compute: node %d is null", i);
         if (done[i]) continue;
+        if (plan && i == plan->first) {   // the layers and the output mat-mul of a one-token step: one kernel
+            bc->act_src = nullptr;
+            int rc = launch_decode_persistent(plan->dev_phases, plan->n_phases, plan->dev_sync, bc->stream);
+            if (rc != B200_STATUS_SUCCESS) return rc;
+            i = plan->last - 1;
+            continue;
+        }
         std::string why;
         if (!op_supported(op, &why)) {
             set_error("graph_compute: node %d '%s' (op %d) is not supported: %s", i, op->name, op->op, why.c_str());
@@ -1268,6 +1567,7 @@ static uint64_t node_list_key(const BackendCtx *bc, const ggml_cgraph *g) {
     h = fnv(h, &bc->fuse_prologue, sizeof(bool));
     const int numerics = numerics_mode();
     h = fnv(h, &numerics, sizeof(int));
+    h = fnv(h, &bc->persistent_decode, sizeof(bool));
     h = fnv(h, &g->n_nodes, sizeof(int));
     for (int i = 0; i < g->n_nodes; i++) {
         const ggml_tensor *t = g->nodes[i];
@@ -1308,9 +1608,19 @@ static int backend_graph_compute(ggml_backend_t be, ggml_cgraph *g) {
             if (bc->tp->hook) bc->capturable = false;   // the exchange happens on the host
         }
     }
-    if (!bc->graphs_enabled || !bc->capturable || g->n_nodes < 6) return run_nodes(bc, g);
-
+    bc->current_key = 0;
+    if (g->n_nodes < 6) return run_nodes(bc, g);
     const uint64_t key = node_list_key(bc, g);
+    bc->current_key = key;
+    {
+        // a step the persistent kernel takes is a handful of launches: nothing to capture
+        BackendCtx::StepPlan *plan = nullptr;
+        int rc = step_plan_for(bc, g, key, &plan);
+        if (rc != B200_STATUS_SUCCESS) return rc;
+        if (plan) return run_nodes(bc, g);
+    }
+    if (!bc->graphs_enabled || !bc->capturable) return run_nodes(bc, g);
+
     const unsigned long long sgen = scratch_generation();
     BackendCtx::CapturedGraph *c = nullptr;
     for (auto &cand : bc->captured)
@@ -1368,6 +1678,11 @@ static void backend_free(ggml_backend_t be) {
     cudaSetDevice(bc->device);
     cudaStreamSynchronize(bc->stream);
     drop_captured(bc);
+    for (auto &pl : bc->plans) {
+        if (pl.dev_phases) cudaFree(pl.dev_phases);
+        if (pl.dev_sync) cudaFree(pl.dev_sync);
+        if (pl.dev_partial) cudaFree(pl.dev_partial);
+    }
     if (bc->act) cudaFree(bc->act);
     if (bc->rope_dev) cudaFree(bc->rope_dev);
     for (auto &t : bc->rope_by_pos)
@@ -1451,6 +1766,8 @@ static ggml_backend_t dev_init_backend(ggml_backend_dev_t d, const char *params)
         if (fg && fg[0] == '0') bc->fuse_glue = false;
         const char *fp = getenv("B200_FUSE_PROLOGUE");
         if (fp && fp[0] == '0') bc->fuse_prologue = false;
+        const char *dp = getenv("B200_DECODE_PERSISTENT");
+        if (dp) bc->persistent_decode = dp[0] == '1';
     }
     if (cudaStreamCreateWithFlags(&bc->stream, cudaStreamNonBlocking) != cudaSuccess) {
         cudaGetLastError();
@@ -1474,6 +1791,8 @@ static ggml_backend_t dev_init_backend(ggml_backend_dev_t d, const char *params)
         if (p) bc->fuse_glue = atoi(p + 10) != 0;
         p = strstr(params, "fuse_prologue=");
         if (p) bc->fuse_prologue = atoi(p + 14) != 0;
+        p = strstr(params, "decode_persistent=");
+        if (p) bc->persistent_decode = atoi(p + 18) != 0;
     }
     ggml_backend *be = new ggml_backend();
     memset(&be->iface, 0, sizeof(be->iface));

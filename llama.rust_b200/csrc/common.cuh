@@ -240,6 +240,10 @@ bool no_scratch_mode();
 // device allocations the library itself has made so far (scratch blocks); exported as b200_debug_alloc_count
 unsigned long long library_alloc_count();
 void gemv_stream_debug_wait(int spin_limit, int skip_unit);
+// decode_persistent.cu: test hooks (see b200_debug_decode_step_*)
+void decode_persistent_debug(int spin_limit, int skip_cta, int skip_barrier);
+unsigned long long decode_persistent_launches();
+int decode_persistent_times(unsigned long long *out, int n);
 
 // route the reference takes for (type, n, m), and the activation quantizer that route reads
 int pick_route(int type, int64_t n, int64_t m);

@@ -26,6 +26,7 @@ lib.b200_llama_kv_clear.argtypes = [vp]
 lib.b200_llama_kv_used.argtypes = [vp]
 lib.b200_llama_kv_used.restype = i32
 lib.b200_llama_replay.argtypes = [vp, i32, C.POINTER(C.c_float)]
+lib.b200_llama_read_node.argtypes = [vp, C.c_char_p, vp, sz]
 lib.b200_llama_new_tp.argtypes = [C.POINTER(HParams), i32, i32, i32, i32, i32, i32, vp, C.POINTER(vp)]
 TP_HOOK = C.CFUNCTYPE(C.c_int, vp, C.c_int, C.c_int, C.c_int, vp, i64, vp, i64, i64)
 lib.b200_llama_new_tp_hook.argtypes = [C.POINTER(HParams), i32, i32, i32, i32, i32, i32, TP_HOOK, vp, C.POINTER(vp)]
@@ -123,6 +124,12 @@ class Llama:
 
     def kv_used(self):
         return lib.b200_llama_kv_used(self.ptr)
+
+    def read_node(self, name, count, dtype=np.float32):
+        """the last decode call's tensor of that name (b200_llama_read_node), `count` elements"""
+        out = np.empty(count, dtype=dtype)
+        check(lib.b200_llama_read_node(self.ptr, name.encode(), out.ctypes.data, out.nbytes), f"read_node {name}")
+        return out
 
     def replay(self, reps):
         ms = C.c_float(0)
