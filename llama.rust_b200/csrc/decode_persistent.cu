@@ -105,6 +105,16 @@ __device__ __forceinline__ int ld_relaxed_i32(const int *p) {
     return v;
 }
 
+// profiling aid: one thread of one CTA notes where its time goes
+__device__ __forceinline__ void trace_event(DpSync *sync, bool on, unsigned code) {
+    if (!on) return;
+    const unsigned n = sync->trace_n;
+    if (n < DP_TRACE_MAX) {
+        sync->trace[n] = ((unsigned long long)code << 56) | ((unsigned long long)clock64() & 0x00ffffffffffffffull);
+        sync->trace_n = n + 1;
+    }
+}
+
 // barrier ids: 0 = the whole CTA, 1 = the 16 consumer warps, 2 / 3 = consumer sets, 4 / 5 = attention groups
 __device__ __forceinline__ void consumer_sync() { named_sync(1, DP_CONSUMER_WARPS * 32); }
 struct SetSync {
@@ -568,6 +578,7 @@ decode_persistent_kernel(const DpPhase *__restrict__ phases, int n_phases, DpSyn
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
             sync->t_phase[0] = t;
         }
+        const bool tr = profile > 1 && cta == profile - 2 && tid == 0;   // B200_DECODE_PROFILE = 2 + c: trace CTA c
         unsigned count = 0;        // units this set has consumed
         unsigned barrier_no = 0;   // grid barriers passed
         bool alive = true;
@@ -577,7 +588,9 @@ decode_persistent_kernel(const DpPhase *__restrict__ phases, int n_phases, DpSyn
                 const GemvWork W = carve_gemv(work, P.k);
                 const int j0 = first_job(P, 0, cta, grid);   // set 0's first job: the CTA has work in this phase iff it exists
                 if (j0 < P.jobs) {
+                    trace_event(sync, tr, 1);
                     dp_prologue(P, W, ctl, warp, lane, j0 == 0);
+                    trace_event(sync, tr, 2);
                     uint32_t *xch = W.xch + (size_t)set * 2 * DP_XCH_WORDS;
                     float *fin = W.fin + (size_t)set * 8 * 32;
                     bool set_alive = true;
@@ -597,6 +610,7 @@ decode_persistent_kernel(const DpPhase *__restrict__ phases, int n_phases, DpSyn
                                 int ok = 1;
                                 if (lane == 0) ok = mbar_wait(&ctl->full[set][slot], (count / DP_SLOTS) & 1u, spin_limit, stop_p) ? 1 : 0;
                                 ok = __shfl_sync(0xffffffffu, ok, 0);
+                                trace_event(sync, tr, 3);
                                 const int g0 = u * gpu;
                                 const int ng = P.nb - g0 < gpu ? P.nb - g0 : gpu;
                                 uint32_t *xb = xch + (size_t)(count & 1u) * DP_XCH_WORDS;
@@ -621,7 +635,9 @@ decode_persistent_kernel(const DpPhase *__restrict__ phases, int n_phases, DpSyn
                                         }
                                     }
                                 }
+                                trace_event(sync, tr, 4);
                                 set_sync();
+                                trace_event(sync, tr, 5);
                                 if (*(volatile int *)&ctl->abort_set[set]) {
                                     set_alive = false;
                                     break;
@@ -649,6 +665,7 @@ decode_persistent_kernel(const DpPhase *__restrict__ phases, int n_phases, DpSyn
                                 }
                             }
                             if (!set_alive) break;
+                            trace_event(sync, tr, 6);
                             float v = 0.0f;
                             if (q4) {
                                 v = __fsub_rn(acc0, acc1);
@@ -681,6 +698,7 @@ decode_persistent_kernel(const DpPhase *__restrict__ phases, int n_phases, DpSyn
                                     dp_epilogue(P, M, tile, lane, v, err);
                                 }
                             }
+                            trace_event(sync, tr, 7);
                         }
                     }
                 }
@@ -700,6 +718,7 @@ decode_persistent_kernel(const DpPhase *__restrict__ phases, int n_phases, DpSyn
                     }
                 }
             }
+            trace_event(sync, tr, 8);
             if (ph + 1 == n_phases) break;
             // ---- phase boundary: grid barrier.  Thread 0 decides between two barriers of the consumers whether the CTA goes on.
             consumer_sync();
@@ -739,6 +758,7 @@ decode_persistent_kernel(const DpPhase *__restrict__ phases, int n_phases, DpSyn
                 }
             }
             consumer_sync();
+            trace_event(sync, tr, 9);
             if (*(volatile int *)&ctl->decision == 0) alive = false;
             barrier_no++;
         }
@@ -783,7 +803,7 @@ unsigned long long decode_persistent_launches() { return g_launches; }
 // nanosecond stamps of the last launch's phase boundaries (CTA 0), after the stream has drained; returns how many were copied
 int decode_persistent_times(unsigned long long *out, int n) {
     if (!g_last_sync || n <= 0) return 0;
-    if (n > 3 * DP_MAX_TIMED) n = 3 * DP_MAX_TIMED;   // t_phase, then t_first, then t_last
+    if (n > 3 * DP_MAX_TIMED + DP_TRACE_MAX + 1) n = 3 * DP_MAX_TIMED + DP_TRACE_MAX + 1;   // t_phase, t_first, t_last, trace, trace_n
     if (cudaMemcpy(out, g_last_sync->t_phase, (size_t)n * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess) {
         cudaGetLastError();
         return 0;
@@ -826,12 +846,13 @@ int launch_decode_persistent(const DpPhase *dev_phases, int n_phases, DpSync *de
     static int profile = -1;
     if (profile < 0) {
         const char *e = getenv("B200_DECODE_PROFILE");
-        profile = (e && e[0] == '1') ? 1 : 0;
+        profile = e ? atoi(e) : 0;
     }
     B200_CUDA(cudaMemsetAsync(dev_sync, 0, offsetof(DpSync, t_first), s));
     if (profile) {
         B200_CUDA(cudaMemsetAsync(dev_sync->t_first, 0xff, sizeof(dev_sync->t_first), s));
         B200_CUDA(cudaMemsetAsync(dev_sync->t_last, 0, sizeof(dev_sync->t_last), s));
+        B200_CUDA(cudaMemsetAsync(&dev_sync->trace_n, 0, sizeof(unsigned), s));
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)sm_count[dev]);

@@ -67,6 +67,7 @@ struct DpPhase {
 // device words the kernel synchronizes on: zeroed (stream-ordered) before every launch
 constexpr int DP_MAX_KV_HEADS = 254;
 constexpr int DP_MAX_TIMED = 512;
+constexpr int DP_TRACE_MAX = 4096;
 struct DpSync {
     unsigned arrived;       // grid barrier arrivals, monotonic over the launch
     int abort;              // a CTA gave up a wait: everybody leaves
@@ -74,6 +75,8 @@ struct DpSync {
     unsigned long long t_phase[DP_MAX_TIMED];   // %globaltimer of CTA 0 at the start and after every grid barrier (profiling aid)
     unsigned long long t_first[DP_MAX_TIMED];   // earliest and latest arrival of a CTA at each grid barrier (only while profiling is on)
     unsigned long long t_last[DP_MAX_TIMED];
+    unsigned long long trace[DP_TRACE_MAX];     // (event code << 56) | SM clock of one CTA's warp 0 (only while profiling is on)
+    unsigned trace_n;
 };
 
 size_t decode_persistent_attn_partial_bytes(int n_head_kv, int n_splits, int head_dim);

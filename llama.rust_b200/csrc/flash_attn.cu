@@ -589,6 +589,7 @@ int flash_attn_faithful_tiled(const b200_flash_attn_args *a, cudaStream_t s);   
 bool flash_attn_decode_head(const b200_flash_attn_args *a, int n_chunks, int64_t chunk, cudaStream_t s, int *rc);   // flash_attn_head.cu
 bool flash_attn_rows_visible(const b200_flash_attn_args *a, cudaStream_t s, int *rc);                               // flash_attn_vis.cu
 bool flash_attn_fast_rows(const b200_flash_attn_args *a, cudaStream_t s, int *rc);                                  // flash_attn_fast.cu
+bool flash_attn_fast_prefill(const b200_flash_attn_args *a, cudaStream_t s, int *rc);                               // flash_attn_prefill.cu
 
 // B200_FA_DECODE_FUSED=0 keeps single-row attention on the three-kernel path (for side-by-side measurements)
 static bool fa_decode_one_kernel_enabled() {
@@ -659,5 +660,9 @@ extern "C" int b200_flash_attn_ext(const struct b200_flash_attn_args *args, void
         if (flash_attn_fast_rows(args, (cudaStream_t)stream, &rc)) return rc;
     }
     if (args->n_tok < 64) return flash_attn_faithful_rows(args, (cudaStream_t)stream);
+    // prompt batches: the tensor-core kernel under mode 1 or the fast numerics policy, the bit-exact tiled kernel otherwise
+    if (args->mode == 1 || (args->mode == 0 && numerics_mode() == 1)) {
+        if (flash_attn_fast_prefill(args, (cudaStream_t)stream, &rc)) return rc;
+    }
     return flash_attn_faithful_tiled(args, (cudaStream_t)stream);
 }

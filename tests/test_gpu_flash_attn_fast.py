@@ -122,3 +122,73 @@ def test_unsupported_variants_fall_back_to_the_exact_kernels(dev):
     want, _ = orc.flash_attn(q, k, v, mask, 0.125, sinks=sinks, n_chunks=8)
     got = run_fast(dev, q, k, v, mask, 0.125, sinks=sinks, n_chunks=8)
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+# ---- prompt batches: the tensor-core kernel (csrc/flash_attn_prefill.cu) ---------------------------------------------
+PREFILL = [
+    # (H, Hkv, D, T, n_kv, causal)
+    (8, 2, 128, 64, 64, True),        # one tile, one row block per KV head
+    (8, 2, 128, 100, 1000, True),     # ragged rows, ragged last tile
+    (32, 8, 128, 512, 512, True),     # the prompt shape of the 8B model: half of every tile row is the causal future
+    (32, 8, 128, 128, 4096, True),    # a long cache in front of the batch
+    (6, 2, 64, 70, 333, True),        # three heads per KV head (a row block starts in the middle of a token), head size 64
+    (4, 4, 64, 65, 129, True),        # one head per KV head: 64 mask rows per row block
+    (8, 2, 128, 96, 777, False),      # no mask at all
+]
+
+
+@pytest.mark.parametrize("shape", PREFILL, ids=str)
+def test_prompt_batches(dev, shape):
+    H, Hkv, D, T, n_kv, causal = shape
+    q, k, v, mask = synth_case(H, Hkv, D, T, n_kv, seed=sum(shape[:5]), causal=causal)
+    scale = 1.0 / np.sqrt(float(D))
+    want = ref64(q, k, v, mask, scale)
+    got = run_fast(dev, q, k, v, mask, scale)
+    d_g64 = row_rel(got, want)
+    # the same function with q rounded to f16 first, as the CPU path (and this kernel) rounds it: flash_attn.rs:433
+    d_g64q = row_rel(got, ref64(q.astype(np.float16).astype(np.float32), k, v, mask, scale))
+    line = f"prompt {shape}: GPU-f64 {d_g64:.2e}  GPU-f64(q16) {d_g64q:.2e}"
+    if T * n_kv * H <= 8 * 100 * 1000:   # the CPU restatement is a scalar loop: small cases only
+        cpu, _ = orc.flash_attn(q, k, v, mask, scale)
+        d_gc, d_c64 = row_rel(got, cpu), row_rel(cpu, want)
+        line += f"  GPU-CPU {d_gc:.2e}  CPU-f64 {d_c64:.2e}"
+        assert d_gc <= 1.05 * (d_c64 + d_g64) + 1e-6
+    print(line)
+    assert d_g64 <= TOL
+
+
+def test_prompt_batch_with_holes_and_blind_rows(dev):
+    """a mask that is not causal: windows per token, a token that sees nothing, whole tiles nobody sees"""
+    H, Hkv, D, T, n_kv = 8, 2, 128, 130, 1500
+    q, k, v, _ = synth_case(H, Hkv, D, T, n_kv, seed=77, causal=False)
+    rng = np.random.default_rng(5)
+    m = np.full((T, n_kv), -np.inf, dtype=np.float16)
+    for t in range(T):
+        lo = int(rng.integers(0, 700))
+        m[t, lo:lo + 1 + int(rng.integers(0, 200))] = 0.0
+        m[t, 1400 + t % 7] = 0.0            # positions 900..1399 stay hidden from everyone: skipped tiles
+    m[17, :] = -np.inf
+    mask = m.view(np.uint16)
+    scale = 1.0 / np.sqrt(float(D))
+    got = run_fast(dev, q, k, v, mask, scale)
+    assert not got[17].any()
+    live = [t for t in range(T) if t != 17]
+    with np.errstate(invalid="ignore"):
+        want = ref64(q, k, v, mask, scale)
+    assert row_rel(got[live], want[live]) <= TOL
+
+
+def test_prompt_batches_follow_the_numerics_policy(dev):
+    """mode 0: the exact tiled kernel (the CPU's bits) under the exact policy, the tensor-core kernel under the fast one"""
+    q, k, v, mask = synth_case(8, 2, 128, 64, 256, seed=31)
+    scale = 1.0 / np.sqrt(128.0)
+    cpu, _ = orc.flash_attn(q, k, v, mask, scale)
+    kv = dev.KvCacheView(k, v)
+    assert np.array_equal(dev.flash_attn(q, kv, mask, scale).view(np.uint32), cpu.view(np.uint32))
+    dev.set_numerics(dev.FAST)
+    try:
+        got = dev.flash_attn(q, kv, mask, scale)
+    finally:
+        dev.set_numerics(dev.EXACT)
+    assert not np.array_equal(got.view(np.uint32), cpu.view(np.uint32))
+    assert row_rel(got, ref64(q, k, v, mask, scale)) <= TOL
