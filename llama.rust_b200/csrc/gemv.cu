@@ -915,13 +915,18 @@ int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint
         }
         return B200_STATUS_SUCCESS;
     }
-    // 32 activation rows and up: tcgen05 int8 kernels.  Q6_K (tiled chain), Q4_0 and MXFP4 (8x8 gemm chain) keep the CPU
+    // 32 activation rows and up: tcgen05 int8 kernels.  Q6_K (tiled chain, on request), Q4_0 and MXFP4 (8x8 gemm chain) keep the CPU
     // routes' bits; Q8_0's tensor-core form adds whole 32-element dots where the CPU adds eight 4-element lanes, so it
     // serves the fast numerics mode only.  The 32-element-block types take it from 8 rows on (their only alternative
     // re-reads the weights once per two activation rows).
     if (gemm_tcgen05_enabled() && gemm_mma_enabled()) {
-        if (type == B200_TYPE_Q6_K && route == B200_ROUTE_TILED && m >= GEMM_TCGEN05_MIN_COLS)
-            return launch_gemm_tcgen05_i8(type, n, k, m, tiles, acts, dst, lddst, s);
+        // Q6_K: the two-plane tcgen05 kernel gives the same bits as the mma.sync kernel below but measured slower
+        // (107-114 against 156-170 TOP/s on 14336 x 4096 with 512 / 2048 rows: its operand split is the bottleneck),
+        // so it runs only when asked for: B200_Q6K_TCGEN05=1, read per call
+        if (type == B200_TYPE_Q6_K && route == B200_ROUTE_TILED && m >= GEMM_TCGEN05_MIN_COLS) {
+            const char *e = getenv("B200_Q6K_TCGEN05");
+            if (e && e[0] == '1') return launch_gemm_tcgen05_i8(type, n, k, m, tiles, acts, dst, lddst, s);
+        }
         if ((type == B200_TYPE_Q4_0 || type == B200_TYPE_MXFP4) && route == B200_ROUTE_REPACK && m >= GEMM_MMA_MIN_COLS)
             return launch_gemm_tcgen05_i8(type, n, k, m, tiles, acts, dst, lddst, s);
         if (type == B200_TYPE_Q8_0 && route == B200_ROUTE_ROWDOT && m >= GEMM_MMA_MIN_COLS && numerics_mode() == 1)

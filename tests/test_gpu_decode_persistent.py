@@ -112,3 +112,38 @@ def test_persistent_step_crossing_a_256_cell_boundary(ll, fast):
 
 def test_persistent_step_wider_model(ll, fast):
     compare_runs(ll, fast, WIDE, seed=24, prompt_len=40, n_gen=4)
+
+
+def test_grid_barrier_wait_expiry_returns_with_a_code(ll, fast):
+    """One CTA of the persistent step never arrives at a grid barrier (test hook): every other CTA's bounded wait runs
+    out, the kernel returns, b200_kernel_error reports code 5, and after a cache reset the same driver gives the same
+    bits as the node-by-node path again."""
+    tensors = make_tensors(ll, MODEL, 31)
+    a = instance(ll, MODEL, tensors, 512, True)
+    b = instance(ll, MODEL, tensors, 512, False)
+    prompt = np.arange(1, 6, dtype=np.int32)
+    pos = np.arange(5, dtype=np.int32)
+    tok = a.decode(prompt, pos, logits=False, argmax=True)
+    fast.lib.b200_debug_decode_step_wait(4000, 3, 7)   # CTA 3 skips its 8th barrier: the second layer's attention
+    try:
+        # the decode call reads the device's error word after the step and fails with it: 5 = a grid-barrier wait ran
+        # out, 6 = a producer found its ring full for too long (its consumers were stuck at that barrier), 7 = a consumer
+        # gave up waiting for a copy; which of the waits that ran out wrote last is a race
+        with pytest.raises(b200.load().B200Error, match=r"error code [567]"):
+            a.decode([tok], [5])
+    finally:
+        fast.lib.b200_debug_decode_step_wait(0, -1, -1)
+    assert fast.kernel_error() == 0   # the failed call consumed the code
+    for gpu in (a, b):
+        gpu.kv_clear()
+    la, ta = a.decode(prompt, pos, logits=True, argmax=True)
+    lb, tb = b.decode(prompt, pos, logits=True, argmax=True)
+    assert bits_equal(la, lb) and ta == tb
+    before = fast.lib.b200_debug_decode_step_launches()
+    la = a.decode([ta], [5])
+    lb = b.decode([tb], [5])
+    assert fast.lib.b200_debug_decode_step_launches() == before + 1
+    assert fast.kernel_error() == 0
+    assert bits_equal(la, lb)
+    a.close()
+    b.close()

@@ -28,13 +28,15 @@ def dev():
 
 @pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
 @pytest.mark.parametrize("ty", [orc.Q6_K, orc.Q4_0, orc.MXFP4], ids=lambda t: orc.TYPE_NAMES[t])
-def test_bit_exact_types(dev, ty, shape):
+def test_bit_exact_types(dev, ty, shape, monkeypatch):
     n, k, m = shape
     if ty != orc.Q6_K and n % 8:
         pytest.skip("the 8x8 route needs rows % 8 == 0")
     W = synth.weights(ty, n, k, seed=400 + ty, period=512)
     x = synth.activations(m, k, seed=401 + m)
     want, _ = orc.mul_mat(ty, W, x)
+    # Q6_K takes its tcgen05 kernel only on request (the mma.sync kernel is the quicker one): ask for it here
+    monkeypatch.setenv("B200_Q6K_TCGEN05", "1")
     got = dev.mul_mat(dev.Weight(ty, W, k), x)
     assert dev.kernel_error() == 0
     assert bits_equal(got, want), f"max |d| = {np.abs(got - want).max()}"
