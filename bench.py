@@ -464,7 +464,47 @@ def run_llama(b, args, rank, world, barrier, reduce_max):
             traces[name] = gpu_greedy_trace(gpu, hp)
     b.set_numerics(b.FAST)
     gpu.close()
+    if world == 1 and not args.no_persistent:
+        try:
+            out["persistent_step_kernel"] = run_llama_persistent(b, args, out.get("greedy_tokens_head"))
+        except Exception as exc:   # an optional leg: say why it is missing
+            out["persistent_step_kernel"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
     return out, traces
+
+
+def run_llama_persistent(b, args, node_path_tokens):
+    """The same single-token steps with the whole step as ONE persistent kernel (opt-in: B200_DECODE_PERSISTENT=1): tokens/s,
+    the greedy tokens against the node-by-node run, and the mean time CTA 0 spends in each phase of a layer"""
+    import ctypes
+    old = os.environ.get("B200_DECODE_PERSISTENT")
+    os.environ["B200_DECODE_PERSISTENT"] = "1"   # read when the backend is created
+    try:
+        ll, hp, gpu, _ = build_llama(args.layers, n_ctx=2 * (PROMPT + GEN), device=int(os.environ.get("LOCAL_RANK", "0")))
+    finally:
+        if old is None:
+            del os.environ["B200_DECODE_PERSISTENT"]
+        else:
+            os.environ["B200_DECODE_PERSISTENT"] = old
+    b.set_numerics(b.FAST)
+    before = b.lib.b200_debug_decode_step_launches()
+    ident = lambda x: x
+    pp_e2e, pp_dev, tg_e2e, tg_dev, toks = time_llama_passes(gpu, hp, 1, lambda: None, ident, warm=1, reps=2)
+    steps = b.lib.b200_debug_decode_step_launches() - before
+    n = hp["n_layer"] * 5 + 1
+    buf = (ctypes.c_ulonglong * n)()
+    b.lib.b200_debug_decode_step_times.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    got = b.lib.b200_debug_decode_step_times(buf, n)
+    phases = {}
+    if got == n:
+        d = np.diff(np.array(buf[:got], dtype=np.float64)) / 1e3
+        for i, nm in enumerate(("qkv", "attention", "attn_output", "gate_up", "ffn_down")):
+            phases[nm] = float(np.mean(d[i::5][:hp["n_layer"]]))
+        phases["output"] = None   # the last phase ends with the kernel, not at a barrier
+    gpu.close()
+    return {"tg128_tok_s": 1.0 / tg_dev, "tg128_e2e_tok_s": 1.0 / tg_e2e, "tg128_ms_per_token": tg_dev * 1e3, "steps_run_as_one_kernel": int(steps),
+            "greedy_tokens_head": [int(t) for t in toks[:8]], "same_tokens_as_node_path": node_path_tokens == [int(t) for t in toks[:8]] if node_path_tokens else None,
+            "us_per_layer_phase_cta0": phases,
+            "note": "opt-in: slower than the node-by-node step of the same run; the phase times (grid barrier to grid barrier) show where"}
 
 
 def run_llama_70b_one_gpu(b, args):
@@ -938,6 +978,7 @@ def main():
     ap.add_argument("--cpu-layers", type=int, default=32, help="layers of the model the CPU baseline times")
     ap.add_argument("--no-llama", action="store_true", help="skip the Llama half of the metric")
     ap.add_argument("--no-70b", action="store_true", help="skip the 70B shape on one GPU (N = 1)")
+    ap.add_argument("--no-persistent", action="store_true", help="skip the persistent step-kernel leg of the Llama entry")
     ap.add_argument("--no-sweep", action="store_true", help="skip the mat-mul sweep / MUL_MAT_ID / FLASH_ATTN_EXT entries (N = 1)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)

@@ -707,13 +707,13 @@ decode_persistent_kernel(const DpPhase *__restrict__ phases, int n_phases, DpSyn
                 if (warp < DP_FA_GROUPS * FF_WARPS) {
                     const int fg = warp / FF_WARPS;
                     const FaGroupSync fsync{4 + fg};
-                    unsigned char *fsm = work + (size_t)fg * fa_fast_smem_bytes<128, DP_FA_ROWS>();
+                    unsigned char *fsm = work + (size_t)fg * fa_fast_smem_bytes<128, DP_FA_ROWS, 2>();
                     if ((tid & (FF_WARPS * 32 - 1)) == 0) ctl->fa_misc[fg].vis_list = nullptr;
                     const int units = P.fd.H_kv * P.fd.n_splits;
                     for (int u = fg * grid + cta; u < units; u += DP_FA_GROUPS * grid) {
                         const int hk = u / P.fd.n_splits, split = u - hk * P.fd.n_splits;
                         fsync();   // the group's shared memory is free again
-                        fa_fast_unit<128, DP_FA_ROWS>(P.fa, P.fd, P.scale_log2, P.partial, P.counters, split, hk, 0, 1, tid & (FF_WARPS * 32 - 1), fsm,
+                        fa_fast_unit<128, DP_FA_ROWS, 2>(P.fa, P.fd, P.scale_log2, P.partial, P.counters, split, hk, 0, 1, tid & (FF_WARPS * 32 - 1), fsm,
                                                       &ctl->fa_misc[fg], fsync);
                     }
                 }
@@ -815,7 +815,7 @@ size_t decode_persistent_work_limit() { return DP_WORK_BYTES; }
 int decode_persistent_norm_max_k() { return (int)dp_norm_max_blocks() * 256; }
 
 int launch_decode_persistent(const DpPhase *dev_phases, int n_phases, DpSync *dev_sync, cudaStream_t s) {
-    static_assert(DP_FA_GROUPS * fa_fast_smem_bytes<128, DP_FA_ROWS>() <= DP_WORK_BYTES, "attention tiles do not fit the work region");
+    static_assert(DP_FA_GROUPS * fa_fast_smem_bytes<128, DP_FA_ROWS, 2>() <= DP_WORK_BYTES, "attention tiles do not fit the work region");
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
     B200_REQUIRE(dev >= 0 && dev < 64, "decode step: device index %d out of range", dev);

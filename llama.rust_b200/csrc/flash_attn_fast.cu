@@ -29,17 +29,17 @@ struct CtaSync {
 };
 
 // partial[(((hk * row_blocks + rb) * n_splits + split) * FF_ROWS + r) * (D + 4)] = {acc[D], m, l, -, -}
-template <int D>
+template <int D, int NST, int ROWS>
 __global__ void __launch_bounds__(FF_WARPS * 32)
 fa_fast_rows_kernel(b200_flash_attn_args a, FastDims d, float scale_log2, float *__restrict__ partial, int *__restrict__ counters) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ FaFastMisc misc;
-    __shared__ unsigned short vis_list[FF_MAX_LIST];
-    if (threadIdx.x == 0) misc.vis_list = vis_list;
+    __shared__ unsigned short vis_list[ROWS > 4 ? FF_MAX_LIST : 1];   // only several tokens per step list their visible tiles
+    if (threadIdx.x == 0) misc.vis_list = ROWS > 4 ? vis_list : nullptr;
     __syncthreads();
     pdl_trigger();
     pdl_wait();   // q, the cache rows of this step and the mask come from earlier kernels / copies
-    fa_fast_unit<D, FF_ROWS>(a, d, scale_log2, partial, counters, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, (int)gridDim.z, (int)threadIdx.x, smem,
+    fa_fast_unit<D, ROWS, NST>(a, d, scale_log2, partial, counters, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, (int)gridDim.z, (int)threadIdx.x, smem,
                     &misc, CtaSync());
 }
 
@@ -52,6 +52,8 @@ __device__ int g_fast_counters_dev[4096];
 // SM, at least two tiles per unit once the context is long, at most FF_MAX_SPLITS per (KV head, row block).
 // false: a shape the fast path does not take.
 bool flash_attn_fast_dims(const b200_flash_attn_args *a, int sms, int rows, FastDims *out) {
+    // one token's rows (a unit of 4 rows is small: four of them share an SM) or a batch's (units of 16 rows, two per SM)
+    const int per_sm = rows <= 4 ? 4 : 2;
     FastDims d;
     d.T = (int)a->n_tok; d.H = (int)a->n_head; d.H_kv = (int)a->n_head_kv; d.group = d.H / d.H_kv;
     d.n_kv = a->n_kv;
@@ -59,7 +61,7 @@ bool flash_attn_fast_dims(const b200_flash_attn_args *a, int sms, int rows, Fast
     const int row_blocks = (rows_total + rows - 1) / rows;
     if (d.H_kv > 65535 || row_blocks > 65535 || d.H_kv * row_blocks > 4096) return false;
     const int64_t n_tiles = (d.n_kv + FF_TILE - 1) / FF_TILE;
-    int64_t want = (2 * (int64_t)sms + (int64_t)d.H_kv * row_blocks - 1) / ((int64_t)d.H_kv * row_blocks);
+    int64_t want = (per_sm * (int64_t)sms + (int64_t)d.H_kv * row_blocks - 1) / ((int64_t)d.H_kv * row_blocks);
     if (want > FF_MAX_SPLITS) want = FF_MAX_SPLITS;
     if (want > n_tiles) want = n_tiles;
     if (want < 1) want = 1;
@@ -82,11 +84,13 @@ bool flash_attn_fast_rows(const b200_flash_attn_args *a, cudaStream_t s, int *rc
         *rc = cuda_fail(cudaGetLastError(), "flash_attn fast: device query", __FILE__, __LINE__);
         return true;
     }
+    // the rows of one token on one KV head (single-token decode) travel as units of 4 rows: a quarter of the shared memory
+    const bool small = a->n_tok * (a->n_head / a->n_head_kv) <= 4;
+    const int rows = small ? 4 : FF_ROWS;
     FastDims d;
-    if (!flash_attn_fast_dims(a, sms, FF_ROWS, &d)) return false;
-    const int row_blocks = (d.T * d.group + FF_ROWS - 1) / FF_ROWS;
-    const int64_t n_tiles = (d.n_kv + FF_TILE - 1) / FF_TILE;
-    (void)n_tiles;
+    if (!flash_attn_fast_dims(a, sms, rows, &d)) return false;
+    if (small && d.T > 1) return false;
+    const int row_blocks = (d.T * d.group + rows - 1) / rows;
     if (!g_fast_counters[dev]) {   // a module variable: no allocation, zero-initialized on every device
         void *p = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&p, g_fast_counters_dev);
@@ -94,22 +98,44 @@ bool flash_attn_fast_rows(const b200_flash_attn_args *a, cudaStream_t s, int *rc
         g_fast_counters[dev] = (int *)p;
     }
     const int D = (int)a->dk;
-    const size_t part_b = (size_t)d.H_kv * row_blocks * d.n_splits * FF_ROWS * (D + 4) * 4;
+    const size_t part_b = (size_t)d.H_kv * row_blocks * d.n_splits * rows * (D + 4) * 4;
     void *scratch = nullptr;
     *rc = scratch_get(part_b, &scratch);
     if (*rc != B200_STATUS_SUCCESS) return true;
-    const size_t smem = (size_t)4 * FF_TILE * (D * 2 + 16) + (size_t)FF_ROWS * D * 4 + (size_t)FF_ROWS * FF_MAX_SPLITS * 4;
+    // a unit that walks several tiles keeps more of them in flight (long contexts: the cache comes from HBM); one or two
+    // tiles per unit need no more than double buffering
+    const bool deep = d.tiles_per_split >= 3;
     const dim3 grid((unsigned)d.n_splits, (unsigned)d.H_kv, (unsigned)row_blocks);
     const float scale_log2 = a->scale * LOG2E;
-    static bool attr_done[64][2] = {};
-    if (!attr_done[dev][D == 128]) {
-        cudaError_t e = D == 128 ? cudaFuncSetAttribute(fa_fast_rows_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                                 : cudaFuncSetAttribute(fa_fast_rows_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { *rc = cuda_fail(e, "cudaFuncSetAttribute", __FILE__, __LINE__); return true; }
-        attr_done[dev][D == 128] = true;
+    float *part = (float *)scratch;
+    int *cnt = g_fast_counters[dev];
+    static bool attr_done[64] = {};
+#define FA_FAST_CASE(DD, NN, RR)                                                                                                        \
+    do {                                                                                                                                \
+        const size_t smem = fa_fast_smem_bytes<DD, RR, NN>();                                                                           \
+        if (!attr_done[dev]) {                                                                                                          \
+            cudaError_t e = cudaSuccess;                                                                                                \
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_fast_rows_kernel<128, 2, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fa_fast_smem_bytes<128, 16, 2>()); \
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_fast_rows_kernel<128, 4, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fa_fast_smem_bytes<128, 16, 4>()); \
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_fast_rows_kernel<64, 2, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fa_fast_smem_bytes<64, 16, 2>());   \
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_fast_rows_kernel<64, 4, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fa_fast_smem_bytes<64, 16, 4>());   \
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_fast_rows_kernel<128, 2, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fa_fast_smem_bytes<128, 4, 2>());   \
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_fast_rows_kernel<128, 3, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fa_fast_smem_bytes<128, 4, 3>());   \
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_fast_rows_kernel<64, 2, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fa_fast_smem_bytes<64, 4, 2>());     \
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_fast_rows_kernel<64, 3, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fa_fast_smem_bytes<64, 4, 3>());     \
+            if (e != cudaSuccess) { *rc = cuda_fail(e, "cudaFuncSetAttribute", __FILE__, __LINE__); return true; }                      \
+            attr_done[dev] = true;                                                                                                      \
+        }                                                                                                                               \
+        *rc = launch_pdl(fa_fast_rows_kernel<DD, NN, RR>, grid, dim3(FF_WARPS * 32), smem, s, *a, d, scale_log2, part, cnt);               \
+    } while (0)
+    if (small) {
+        if (D == 128) { if (deep) FA_FAST_CASE(128, 3, 4); else FA_FAST_CASE(128, 2, 4); }
+        else { if (deep) FA_FAST_CASE(64, 3, 4); else FA_FAST_CASE(64, 2, 4); }
+    } else {
+        if (D == 128) { if (deep) FA_FAST_CASE(128, 4, 16); else FA_FAST_CASE(128, 2, 16); }
+        else { if (deep) FA_FAST_CASE(64, 4, 16); else FA_FAST_CASE(64, 2, 16); }
     }
-    if (D == 128) *rc = launch_pdl(fa_fast_rows_kernel<128>, grid, dim3(FF_WARPS * 32), smem, s, *a, d, scale_log2, (float *)scratch, g_fast_counters[dev]);
-    else *rc = launch_pdl(fa_fast_rows_kernel<64>, grid, dim3(FF_WARPS * 32), smem, s, *a, d, scale_log2, (float *)scratch, g_fast_counters[dev]);
+#undef FA_FAST_CASE
     return true;
 }
 

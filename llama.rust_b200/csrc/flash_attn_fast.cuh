@@ -40,21 +40,22 @@ struct FaFastMisc {
     float lsum[FF_ROWS];
     unsigned short *vis_list;   // [FF_MAX_LIST], only walked when several tokens share the step (null otherwise)
 };
-template <int D, int ROWS>
+template <int D, int ROWS, int NST>
 __host__ __device__ constexpr size_t fa_fast_smem_bytes() {
-    return (size_t)4 * FF_TILE * (D * 2 + 16) + (size_t)ROWS * D * 4 + (size_t)ROWS * FF_MAX_SPLITS * 4;
+    return (size_t)2 * NST * FF_TILE * (D * 2 + 16) + (size_t)ROWS * D * 4 + (size_t)ROWS * FF_MAX_SPLITS * 4;
 }
 // ROWS: the most query rows a unit carries (a multiple of FF_WARPS); it sizes the group's shared memory and the
-// partials' layout, not the arithmetic of a row.
-template <int D, int ROWS, class Sync>
+// partials' layout, not the arithmetic of a row.  NST: K / V tiles in flight or in use at a time (2 = double buffering;
+// a unit that walks many tiles of a long context keeps HBM busier with more); it does not touch the arithmetic either.
+template <int D, int ROWS, int NST, class Sync>
 __device__ __forceinline__ void fa_fast_unit(const b200_flash_attn_args &a, const FastDims &d, float scale_log2, float *__restrict__ partial,
                                              int *__restrict__ counters, int split, int hk, int rb, int row_blocks, int tid,
                                              unsigned char *smem, FaFastMisc *misc, Sync sync) {
     constexpr int KSTRIDE = D * 2 + 16;                      // bytes per staged row: 16 bytes of padding keep lanes on different banks
     constexpr int VEC = D / 32;                              // value elements per lane
-    unsigned char *ks = smem;                                // [2][FF_TILE][KSTRIDE]
-    unsigned char *vs = ks + 2 * FF_TILE * KSTRIDE;          // [2][FF_TILE][KSTRIDE]
-    float *qs = (float *)(vs + 2 * FF_TILE * KSTRIDE);       // [ROWS][D]
+    unsigned char *ks = smem;                                // [NST][FF_TILE][KSTRIDE]
+    unsigned char *vs = ks + NST * FF_TILE * KSTRIDE;        // [NST][FF_TILE][KSTRIDE]
+    float *qs = (float *)(vs + NST * FF_TILE * KSTRIDE);     // [ROWS][D]
     float *ps = qs + ROWS * D;                            // [ROWS][FF_TILE]; the merge reuses it as [ROWS][FF_MAX_SPLITS]
     const int lane = tid & 31, warp = tid >> 5;
     const int rows_total = d.T * d.group;                    // rows that read this KV head: row = t * group + g
@@ -131,10 +132,16 @@ __device__ __forceinline__ void fa_fast_unit(const b200_flash_attn_args &a, cons
     }
     auto tile_at = [&](int i) -> int64_t { return tile0 + (listed ? (int64_t)vis_list[i] : (int64_t)i); };
 
-    if (n_walk > 0) stage(tile_at(0), 0);
+    // NST - 1 tiles ahead of the one in use; a copy group is committed per step whether or not a tile was left to
+    // stage, so that "all but the last NST - 2 groups have landed" always means "tile `it` has landed"
+#pragma unroll
+    for (int i = 0; i < NST - 1; i++) {
+        if (i < n_walk) stage(tile_at(i), i);
+        else cp_async_commit();
+    }
     for (int it = 0; it < n_walk; it++) {
         const int64_t tile = tile_at(it);
-        const int buf = it & 1;
+        const int buf = it % NST;
         const int64_t pos = tile * FF_TILE + lane;
         // this tile's mask values travel while the K / V copies do: one round trip instead of two in a row
         float mvals[RPW];
@@ -147,12 +154,10 @@ __device__ __forceinline__ void fa_fast_unit(const b200_flash_attn_args &a, cons
                 mvals[i] = __half2float(((const __half *)((const unsigned char *)a.mask + (int64_t)t * a.mask_nb1))[pos]);
             }
         }
-        if (it + 1 < n_walk) {
-            stage(tile_at(it + 1), buf ^ 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        // the buffer of tile it + NST - 1 is the one tile it - 1 used: free since the barrier that ended that step
+        if (it + NST - 1 < n_walk) stage(tile_at(it + NST - 1), (it + NST - 1) % NST);
+        else cp_async_commit();
+        cp_async_wait<NST - 1>();
         sync();
         const unsigned char *krow = ks + ((size_t)buf * FF_TILE + lane) * KSTRIDE;
 #pragma unroll
@@ -166,16 +171,18 @@ __device__ __forceinline__ void fa_fast_unit(const b200_flash_attn_args &a, cons
             float s = -INFINITY;
             if (visible) {
                 const float *q = qs + rl * D;
-                float dot = 0.0f;
+                // four partial sums: one chain of D dependent multiply-adds would leave the warp waiting on its own results
+                float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
 #pragma unroll
                 for (int c = 0; c < D / 8; c++) {
                     const uint4 kv = *(const uint4 *)(krow + c * 16);
                     const float4 q0 = *(const float4 *)(q + c * 8), q1 = *(const float4 *)(q + c * 8 + 4);
                     const float2 k0 = __half22float2(*(const __half2 *)&kv.x), k1 = __half22float2(*(const __half2 *)&kv.y);
                     const float2 k2 = __half22float2(*(const __half2 *)&kv.z), k3 = __half22float2(*(const __half2 *)&kv.w);
-                    dot = fmaf(q0.x, k0.x, dot); dot = fmaf(q0.y, k0.y, dot); dot = fmaf(q0.z, k1.x, dot); dot = fmaf(q0.w, k1.y, dot);
-                    dot = fmaf(q1.x, k2.x, dot); dot = fmaf(q1.y, k2.y, dot); dot = fmaf(q1.z, k3.x, dot); dot = fmaf(q1.w, k3.y, dot);
+                    d0 = fmaf(q0.x, k0.x, d0); d1 = fmaf(q0.y, k0.y, d1); d2 = fmaf(q0.z, k1.x, d2); d3 = fmaf(q0.w, k1.y, d3);
+                    d0 = fmaf(q1.x, k2.x, d0); d1 = fmaf(q1.y, k2.y, d1); d2 = fmaf(q1.z, k3.x, d2); d3 = fmaf(q1.w, k3.y, d3);
                 }
+                const float dot = (d0 + d1) + (d2 + d3);
                 s = fmaf(dot, scale_log2, mval * LOG2E);   // log2 units: exp(x) = exp2(x * log2 e)
             }
             float tmax = s;
