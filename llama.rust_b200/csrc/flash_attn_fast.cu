@@ -52,8 +52,10 @@ __device__ int g_fast_counters_dev[4096];
 // SM, at least two tiles per unit once the context is long, at most FF_MAX_SPLITS per (KV head, row block).
 // false: a shape the fast path does not take.
 bool flash_attn_fast_dims(const b200_flash_attn_args *a, int sms, int rows, FastDims *out) {
-    // one token's rows (a unit of 4 rows is small: four of them share an SM) or a batch's (units of 16 rows, two per SM)
-    const int per_sm = rows <= 4 ? 4 : 2;
+    // units per SM the cut aims at: two; four for one token's rows over a long cache (a unit of 4 rows is small and there
+    // are tiles enough to feed them: measured 68 -> 60 us at 32768 positions, while below 8192 the extra splits only
+    // lengthen the merge)
+    const int per_sm = rows <= 4 && a->n_kv > 8192 ? 4 : 2;
     FastDims d;
     d.T = (int)a->n_tok; d.H = (int)a->n_head; d.H_kv = (int)a->n_head_kv; d.group = d.H / d.H_kv;
     d.n_kv = a->n_kv;
