@@ -244,6 +244,7 @@ void gemv_stream_debug_wait(int spin_limit, int skip_unit);
 void decode_persistent_debug(int spin_limit, int skip_cta, int skip_barrier);
 unsigned long long decode_persistent_launches();
 int decode_persistent_times(unsigned long long *out, int n);
+int flash_attn_prefill_profile(unsigned long long *out, int n);   // flash_attn_prefill_tc.cu
 
 // route the reference takes for (type, n, m), and the activation quantizer that route reads
 int pick_route(int type, int64_t n, int64_t m);

@@ -590,6 +590,17 @@ bool flash_attn_decode_head(const b200_flash_attn_args *a, int n_chunks, int64_t
 bool flash_attn_rows_visible(const b200_flash_attn_args *a, cudaStream_t s, int *rc);                               // flash_attn_vis.cu
 bool flash_attn_fast_rows(const b200_flash_attn_args *a, cudaStream_t s, int *rc);                                  // flash_attn_fast.cu
 bool flash_attn_fast_prefill(const b200_flash_attn_args *a, cudaStream_t s, int *rc);                               // flash_attn_prefill.cu
+bool flash_attn_fast_prefill_tc(const b200_flash_attn_args *a, cudaStream_t s, int *rc);                            // flash_attn_prefill_tc.cu
+
+// B200_FA_PREFILL_TC=1 sends fast-mode prompt attention with head size 128 to the tcgen05 kernel (read per call).  It gives
+// the same values as the mma.sync kernel and, measured on 512 query rows over 32768 cached positions, the same speed
+// (1.33 against 1.31 ms): with unswizzled core-matrix operands an M 128 x N 64 x K 16 MMA takes about 127 cycles and the
+// 16-byte cp.async copies that build those operands cost their warps about 90 cycles each, so the mma.sync kernel stays
+// the default until the operands come in through tensor-map copies in the 128-byte swizzle.
+static bool fa_prefill_tc_enabled() {
+    const char *e = getenv("B200_FA_PREFILL_TC");
+    return e && e[0] == '1';
+}
 
 // B200_FA_DECODE_FUSED=0 keeps single-row attention on the three-kernel path (for side-by-side measurements)
 static bool fa_decode_one_kernel_enabled() {
@@ -662,6 +673,7 @@ extern "C" int b200_flash_attn_ext(const struct b200_flash_attn_args *args, void
     if (args->n_tok < 64) return flash_attn_faithful_rows(args, (cudaStream_t)stream);
     // prompt batches: the tensor-core kernel under mode 1 or the fast numerics policy, the bit-exact tiled kernel otherwise
     if (args->mode == 1 || (args->mode == 0 && numerics_mode() == 1)) {
+        if (fa_prefill_tc_enabled() && flash_attn_fast_prefill_tc(args, (cudaStream_t)stream, &rc)) return rc;   // head size 128, tcgen05
         if (flash_attn_fast_prefill(args, (cudaStream_t)stream, &rc)) return rc;
     }
     return flash_attn_faithful_tiled(args, (cudaStream_t)stream);

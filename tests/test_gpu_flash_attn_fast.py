@@ -137,9 +137,16 @@ PREFILL = [
 ]
 
 
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma.sync"])
 @pytest.mark.parametrize("shape", PREFILL, ids=str)
-def test_prompt_batches(dev, shape):
+def test_prompt_batches(dev, shape, kernel, monkeypatch):
+    """the mma.sync kernel is the default; head size 128 with two or more heads per KV head also has a tcgen05 kernel,
+    taken when B200_FA_PREFILL_TC=1 (read per call)"""
     H, Hkv, D, T, n_kv, causal = shape
+    if kernel == "tcgen05":
+        if D != 128 or H == Hkv:
+            pytest.skip("no tcgen05 form for this shape")
+        monkeypatch.setenv("B200_FA_PREFILL_TC", "1")
     q, k, v, mask = synth_case(H, Hkv, D, T, n_kv, seed=sum(shape[:5]), causal=causal)
     scale = 1.0 / np.sqrt(float(D))
     want = ref64(q, k, v, mask, scale)
@@ -147,7 +154,7 @@ def test_prompt_batches(dev, shape):
     d_g64 = row_rel(got, want)
     # the same function with q rounded to f16 first, as the CPU path (and this kernel) rounds it: flash_attn.rs:433
     d_g64q = row_rel(got, ref64(q.astype(np.float16).astype(np.float32), k, v, mask, scale))
-    line = f"prompt {shape}: GPU-f64 {d_g64:.2e}  GPU-f64(q16) {d_g64q:.2e}"
+    line = f"prompt {shape} {kernel}: GPU-f64 {d_g64:.2e}  GPU-f64(q16) {d_g64q:.2e}"
     if T * n_kv * H <= 8 * 100 * 1000:   # the CPU restatement is a scalar loop: small cases only
         cpu, _ = orc.flash_attn(q, k, v, mask, scale)
         d_gc, d_c64 = row_rel(got, cpu), row_rel(cpu, want)
