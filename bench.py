@@ -41,7 +41,7 @@ SIMD_NAMES = {0: "scalar", 1: "AVX2", 2: "AVX-512 VNNI"}
 # measured DRAM bytes / algorithmic bytes of one launch of the decode kernel in use (gemv_q4_K_row_kernel on
 # 14336 x 4096: dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture summarized in
 # profiles/gemv_q4_K_row_kernel_decode.md); weights are read once whatever the shape
-NCU_TRAFFIC_RATIO = 33.11 / 33.03
+NCU_TRAFFIC_RATIO = 33.052416 / 33.103872
 PROMPT, GEN = 512, 128
 
 
@@ -400,6 +400,7 @@ def time_llama_passes(gpu, hp, world, barrier, reduce_max, warm=2, reps=3):
 
 
 PARITY_PROMPT, PARITY_STEPS = 16, 4
+CPU_TG_STEPS = 64   # single-token steps the CPU leg times (the first PARITY_STEPS of them are the parity comparison)
 
 
 def gpu_greedy_trace(gpu, hp):
@@ -580,7 +581,7 @@ def run_llama_tp(b, args, rank, world, local, barrier, reduce_max, shape):
             "pp512_ms": pp_dev * 1e3, "tg128_ms_per_token": tg_dev * 1e3}
 
 
-def cpu_llama_baseline(orc, orc_glue, n_layer, prompt_tokens=PARITY_PROMPT, gen_tokens=PARITY_STEPS):
+def cpu_llama_baseline(orc, orc_glue, n_layer, prompt_tokens=PARITY_PROMPT, gen_tokens=CPU_TG_STEPS):
     """The CPU restatement's Llama forward on the same shape: a prompt batch and a few greedy single-token steps.
     Weights are interleaved once, outside the timed region, as the reference does at load.  Also returns the logits
     and tokens of the run (the greedy-stream parity check of the GPU arm compares with them)."""
@@ -925,6 +926,32 @@ def case_gemm(args):
                       "tops": 2.0 * n * k * m / us / 1e6, "kernel_error": b.kernel_error()}), flush=True)
 
 
+def case_fa(args):
+    """`--case fa --tokens T --n-kv N --fa-mode M --launches R`: R FLASH_ATTN_EXT calls of the benchmark's head geometry (32 query
+    heads on 8 KV heads of 128, causal mask, F16 cache) with T query rows over N cached positions; mode 1 = the fast kernels,
+    2 = the bit-exact ones; prints the event-timed mean."""
+    import ctypes
+    b = load_pkg()
+    b.set_device(0)
+    H, HK, D, T, n_kv = 32, 8, 128, args.tokens, args.n_kv
+    rng = np.random.default_rng(80 + n_kv)
+    kv = b.KvCacheView(rng.standard_normal((HK, n_kv, D)).astype(np.float16).view(np.uint16), rng.standard_normal((HK, n_kv, D)).astype(np.float16).view(np.uint16))
+    q = rng.standard_normal((H, T, D)).astype(np.float32)
+    mask = np.where(np.arange(n_kv)[None, :] <= np.arange(T)[:, None] + (n_kv - T), 0.0, -np.inf).astype(np.float16).view(np.uint16)
+    dq, dm, dst = b.device_array(q), b.device_array(mask), b.DeviceBuffer(4 * T * H * D)
+    a = b.FlashAttnArgs()
+    a.dk, a.dv, a.n_tok, a.n_head, a.n_head_kv, a.n_kv = D, D, T, H, HK, n_kv
+    a.q, a.q_nb1, a.q_nb2 = dq.ptr, D * 4, T * D * 4
+    a.k, a.k_nb1, a.k_nb2 = kv.k.ptr, kv.k_nb1, kv.k_nb2
+    a.v, a.v_nb1, a.v_nb2 = kv.v.ptr, kv.v_nb1, kv.v_nb2
+    a.mask, a.mask_nb1, a.sinks = dm.ptr, n_kv * 2, None
+    a.scale, a.max_bias, a.logit_softcap, a.dst, a.n_chunks, a.mode = 1.0 / np.sqrt(D), 0.0, 0.0, dst.ptr, 8, args.fa_mode
+    ms = event_time(b, lambda: b.check(b.lib.b200_flash_attn_ext(ctypes.byref(a), None), "flash_attn_ext"), args.launches)
+    visible = sum(min(n_kv, t + n_kv - T + 1) for t in range(T))
+    print(json.dumps({"case": f"fa T {T} n_kv {n_kv} mode {args.fa_mode}", "launches": args.launches, "us_per_call": ms * 1e3,
+                      "tflops": 4.0 * D * H * visible / ms / 1e9, "cache_gbs": 2 * n_kv * HK * D * 2 / ms / 1e6, "kernel_error": b.kernel_error()}), flush=True)
+
+
 def case_llama(args):
     """`--case llama_tg|llama_pp|llama_b16 --layers L [--launches R]`: an L-layer model of the 8B shape; one prompt
     batch (llama_pp), R single-token steps after a 16-token prompt (llama_tg) or R steps of 16 sequences after
@@ -969,9 +996,12 @@ def case_llama(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "llama_tg", "llama_pp", "llama_b16"], help="one small case for a profiler")
+    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "fa", "llama_tg", "llama_pp", "llama_b16"], help="one small case for a profiler")
     ap.add_argument("--only", default="4096x4096", help="--case gemv / gemm: the shape NxK")
     ap.add_argument("--cols", type=int, default=512, help="--case gemm: activation rows")
+    ap.add_argument("--tokens", type=int, default=512, help="--case fa: query rows")
+    ap.add_argument("--n-kv", type=int, default=4096, help="--case fa: cached positions")
+    ap.add_argument("--fa-mode", type=int, default=1, help="--case fa: 1 fast kernels, 2 bit-exact kernels")
     ap.add_argument("--prompt", type=int, default=16, help="--case llama_tg: prompt tokens before the timed steps")
     ap.add_argument("--launches", type=int, default=64)
     ap.add_argument("--layers", type=int, default=32, help="layers of the 8B-shaped model (32 = the full model)")
@@ -987,6 +1017,8 @@ def main():
     args = ap.parse_args()
     if args.case == "gemv":
         return case_gemv(args)
+    if args.case == "fa":
+        return case_fa(args)
     if args.case == "gemm":
         return case_gemm(args)
     if args.case:
