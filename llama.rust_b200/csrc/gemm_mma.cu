@@ -290,7 +290,7 @@ gemm_q6_K_mma_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *dst
 // the result is the one the kernel above and the CPU produce.
 constexpr int SMALL_WIN = 8;
 struct SmallStage {
-    int ig[4][16][33];      // scaled pair dots [pair][column][row], rows padded to 33 words: the chain's lanes (rows) hit 32 banks
+    int ig[4][16][36];      // scaled pair dots [pair][column][row]; 36 words per column: the 32 lanes of a store (4 column pairs x 8 rows) and of the chain's loads (32 rows) each hit 32 different banks
     uint4 hdr[32];          // the rows' (d | dmin, 12 scale / min bytes)
     int bp[16][8];          // the columns' sub-block sums
     float da[16];           // the columns' super-block scales
@@ -334,10 +334,34 @@ gemm_q4_K_small_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *d
                 const short2 s2 = *(const short2 *)(acts.bsums + c * (K / 16) + (int64_t)b * 16 + 2 * sub);
                 s.bp[col][sub] = (int)s2.x + (int)s2.y;
             }
+            // every load of the super-block first (weight fragments of both row halves, activation fragments of both
+            // column patches): 64 registers of independent loads in flight per lane, then the arithmetic
+            uint2 wa[2][4], wb[2][4], ya[4][2][2];
+            uint4 hh[2][2];
 #pragma unroll
             for (int mt = 0; mt < 2; mt++) {
                 const int ra = 16 * mt + g8, rb = ra + 8;
-                const uint4 ha = *(const uint4 *)(chunk + ra * 16), hb = *(const uint4 *)(chunk + rb * 16);
+                hh[mt][0] = *(const uint4 *)(chunk + ra * 16);
+                hh[mt][1] = *(const uint4 *)(chunk + rb * 16);
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    const uint8_t *wq = chunk + 512 + (2 * g + (t >> 1)) * 512 + 8 * (t & 1);
+                    wa[mt][g] = ldg8(wq + ra * 16);
+                    wb[mt][g] = ldg8(wq + rb * 16);
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < 4; g++)
+#pragma unroll
+                for (int nt = 0; nt < 2; nt++) {
+                    const int8_t *aq = acts.qs + colb[nt] * K + (int64_t)b * 256 + 64 * g + 8 * t;
+                    ya[g][nt][0] = ldg8(aq);
+                    ya[g][nt][1] = ldg8(aq + 32);
+                }
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++) {
+                const int ra = 16 * mt + g8, rb = ra + 8;
+                const uint4 ha = hh[mt][0], hb = hh[mt][1];
                 uint32_t sc[2][2];   // [row a/b][sub-blocks 0..3 / 4..7], 6-bit scales one per byte (crates/ggml/src/quants.rs:421-429)
                 sc[0][0] = ha.y & 0x3f3f3f3fu;
                 sc[0][1] = (ha.w & 0x0f0f0f0fu) | (((ha.y >> 6) & 0x03030303u) << 4);
@@ -345,17 +369,15 @@ gemm_q4_K_small_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *d
                 sc[1][1] = (hb.w & 0x0f0f0f0fu) | (((hb.y >> 6) & 0x03030303u) << 4);
 #pragma unroll
                 for (int g = 0; g < 4; g++) {
-                    const uint8_t *wq = chunk + 512 + (2 * g + (t >> 1)) * 512 + 8 * (t & 1);
-                    const uint2 wa = ldg8(wq + ra * 16), wb = ldg8(wq + rb * 16);
+                    const uint2 va = wa[mt][g], vb = wb[mt][g];
                     const int sh = 16 * (g & 1);
 #pragma unroll
                     for (int nt = 0; nt < 2; nt++) {
-                        const int8_t *aq = acts.qs + colb[nt] * K + (int64_t)b * 256 + 64 * g + 8 * t;
-                        const uint2 y0 = ldg8(aq), y1 = ldg8(aq + 32);
+                        const uint2 y0 = ya[g][nt][0], y1 = ya[g][nt][1];
                         int d0[4], d1[4];
-                        mma_s8_k32(d0, wa.x & 0x0f0f0f0fu, wb.x & 0x0f0f0f0fu, wa.y & 0x0f0f0f0fu, wb.y & 0x0f0f0f0fu, y0.x, y0.y);
-                        mma_s8_k32(d1, (wa.x >> 4) & 0x0f0f0f0fu, (wb.x >> 4) & 0x0f0f0f0fu, (wa.y >> 4) & 0x0f0f0f0fu,
-                                   (wb.y >> 4) & 0x0f0f0f0fu, y1.x, y1.y);
+                        mma_s8_k32(d0, va.x & 0x0f0f0f0fu, vb.x & 0x0f0f0f0fu, va.y & 0x0f0f0f0fu, vb.y & 0x0f0f0f0fu, y0.x, y0.y);
+                        mma_s8_k32(d1, (va.x >> 4) & 0x0f0f0f0fu, (vb.x >> 4) & 0x0f0f0f0fu, (va.y >> 4) & 0x0f0f0f0fu,
+                                   (vb.y >> 4) & 0x0f0f0f0fu, y1.x, y1.y);
 #pragma unroll
                         for (int e = 0; e < 4; e++) {
                             const int r = e >> 1;   // c0, c1: row a; c2, c3: row b
