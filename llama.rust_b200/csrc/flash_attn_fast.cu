@@ -34,8 +34,8 @@ __global__ void __launch_bounds__(FF_WARPS * 32)
 fa_fast_rows_kernel(b200_flash_attn_args a, FastDims d, float scale_log2, float *__restrict__ partial, int *__restrict__ counters) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ FaFastMisc misc;
-    __shared__ unsigned short vis_list[ROWS > 4 ? FF_MAX_LIST : 1];   // only several tokens per step list their visible tiles
-    if (threadIdx.x == 0) misc.vis_list = ROWS > 4 ? vis_list : nullptr;
+    __shared__ unsigned short vis_list[FF_MAX_LIST];   // several tokens per step: the tiles this unit's rows see anything in
+    if (threadIdx.x == 0) misc.vis_list = vis_list;
     __syncthreads();
     pdl_trigger();
     pdl_wait();   // q, the cache rows of this step and the mask come from earlier kernels / copies
@@ -86,12 +86,14 @@ bool flash_attn_fast_rows(const b200_flash_attn_args *a, cudaStream_t s, int *rc
         *rc = cuda_fail(cudaGetLastError(), "flash_attn fast: device query", __FILE__, __LINE__);
         return true;
     }
-    // the rows of one token on one KV head (single-token decode) travel as units of 4 rows: a quarter of the shared memory
-    const bool small = a->n_tok * (a->n_head / a->n_head_kv) <= 4;
+    // Up to four query heads per KV head: a unit carries the rows of ONE token (4 rows, a quarter of the shared memory of a
+    // 16-row unit).  With several tokens per step over a shared cache every token sees its own part of it, and a unit
+    // that carries one token walks (and stages) only the tiles that token sees; 16-row units would stage every tile any
+    // of four tokens sees and leave three quarters of their rows idle on it.
+    const bool small = a->n_head / a->n_head_kv <= 4 && (a->n_tok == 1 || a->n_head / a->n_head_kv == 4);
     const int rows = small ? 4 : FF_ROWS;
     FastDims d;
     if (!flash_attn_fast_dims(a, sms, rows, &d)) return false;
-    if (small && d.T > 1) return false;
     const int row_blocks = (d.T * d.group + rows - 1) / rows;
     if (!g_fast_counters[dev]) {   // a module variable: no allocation, zero-initialized on every device
         void *p = nullptr;
