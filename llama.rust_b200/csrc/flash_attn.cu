@@ -591,6 +591,15 @@ bool flash_attn_rows_visible(const b200_flash_attn_args *a, cudaStream_t s, int 
 bool flash_attn_fast_rows(const b200_flash_attn_args *a, cudaStream_t s, int *rc);                                  // flash_attn_fast.cu
 bool flash_attn_fast_prefill(const b200_flash_attn_args *a, cudaStream_t s, int *rc);                               // flash_attn_prefill.cu
 bool flash_attn_fast_prefill_tc(const b200_flash_attn_args *a, cudaStream_t s, int *rc);                            // flash_attn_prefill_tc.cu
+bool flash_attn_decode_mma(const b200_flash_attn_args *a, cudaStream_t s, int *rc);                                 // flash_attn_decode_mma.cu
+
+// B200_FA_DECODE_MMA=0 keeps fast-mode attention of fewer than 64 query rows off the tensor-core flash-decoding kernel: single
+// rows then take the CUDA-core kernel (the one the persistent decode step carries), several rows the exact kernels
+// (read per call)
+static bool fa_decode_mma_enabled() {
+    const char *e = getenv("B200_FA_DECODE_MMA");
+    return !(e && e[0] == '0');
+}
 
 // B200_FA_PREFILL_TC=1 sends fast-mode prompt attention with head size 128 to the tcgen05 kernel (read per call).  It gives
 // the same values as the mma.sync kernel and, measured on 512 query rows over 32768 cached positions, the same speed
@@ -663,12 +672,14 @@ extern "C" int b200_flash_attn_ext(const struct b200_flash_attn_args *args, void
     using namespace b200;
     int rc = check_args(args);
     if (rc != B200_STATUS_SUCCESS) return rc;
-    // mode 1 asks for the fast kernel wherever it applies; under the fast numerics policy (mode 0) it takes single
-    // query rows only: for several rows over a shared cache, each seeing a small part of it, the exact kernels that
-    // walk per-row lists of visible positions are the quicker ones (measured on 16 sequences over 10240 cells)
-    const bool fast = args->mode == 1 || (args->mode == 0 && numerics_mode() == 1 && args->n_tok == 1);
-    if (fast && args->n_tok < 64) {
-        if (flash_attn_fast_rows(args, (cudaStream_t)stream, &rc)) return rc;
+    // mode 1 asks for the fast kernels wherever they apply; so does the fast numerics policy (mode 0) for the tensor-core
+    // decode kernel.  The CUDA-core kernel takes single query rows only under the policy: for several rows over a shared
+    // cache, each seeing a small part of it, the exact kernels that walk per-row lists of visible positions are quicker
+    // than it (measured on 16 sequences over 10240 cells).
+    const bool policy = args->mode == 0 && numerics_mode() == 1;
+    if ((args->mode == 1 || policy) && args->n_tok < 64) {
+        if (fa_decode_mma_enabled() && flash_attn_decode_mma(args, (cudaStream_t)stream, &rc)) return rc;
+        if ((args->mode == 1 || args->n_tok == 1) && flash_attn_fast_rows(args, (cudaStream_t)stream, &rc)) return rc;
     }
     if (args->n_tok < 64) return flash_attn_faithful_rows(args, (cudaStream_t)stream);
     // prompt batches: the tensor-core kernel under mode 1 or the fast numerics policy, the bit-exact tiled kernel otherwise

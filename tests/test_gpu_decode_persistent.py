@@ -28,10 +28,13 @@ def ll():
 
 
 @pytest.fixture
-def fast():
+def fast(monkeypatch):
+    """fast numerics, with the node-by-node path's attention on the CUDA-core kernel: the unit of work the persistent
+    kernel carries (the tensor-core decode kernel, the node path's default, rounds q and p to f16 and differs in bits)"""
     m = b200.load()
     before = m.get_numerics()
     m.set_numerics(m.FAST)
+    monkeypatch.setenv("B200_FA_DECODE_MMA", "0")
     yield m
     m.set_numerics(before)
 

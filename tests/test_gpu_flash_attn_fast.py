@@ -54,27 +54,36 @@ def run_fast(dev, q, k, v, mask, scale, **kw):
     return dev.flash_attn(q, dev.KvCacheView(k, v), mask, scale, mode=1, **kw)
 
 
-def test_fast_policy_takes_single_rows(dev):
-    """under the fast numerics policy a single query row takes the f32 kernel (not the CPU's bits), several rows
-    keep the exact kernels"""
+def test_fast_policy_takes_rows_below_a_prompt_batch(dev, monkeypatch):
+    """under the fast numerics policy fewer than 64 query rows take the tensor-core decode kernel (not the CPU's bits,
+    within the tolerance of f64); with that kernel switched off a single row takes the f32 CUDA-core kernel and several
+    rows keep the exact kernels"""
     scale = 1.0 / np.sqrt(128.0)
     dev.set_numerics(dev.FAST)
     try:
-        q, k, v, mask = synth_case(8, 2, 128, 1, 768, seed=9)
-        cpu, _ = orc.flash_attn(q, k, v, mask, scale, n_chunks=8)
-        got = dev.flash_attn(q, dev.KvCacheView(k, v), mask, scale, n_chunks=8)
-        assert not np.array_equal(got.view(np.uint32), cpu.view(np.uint32)) and row_rel(got, ref64(q, k, v, mask, scale)) <= 1e-5
-        q, k, v, mask = synth_case(8, 2, 128, 3, 300, seed=10)
-        cpu, _ = orc.flash_attn(q, k, v, mask, scale)
-        got = dev.flash_attn(q, dev.KvCacheView(k, v), mask, scale)
-        assert np.array_equal(got.view(np.uint32), cpu.view(np.uint32))
+        q1, k1, v1, mask1 = synth_case(8, 2, 128, 1, 768, seed=9)
+        cpu1, _ = orc.flash_attn(q1, k1, v1, mask1, scale, n_chunks=8)
+        q3, k3, v3, mask3 = synth_case(8, 2, 128, 3, 300, seed=10)
+        cpu3, _ = orc.flash_attn(q3, k3, v3, mask3, scale)
+        got = dev.flash_attn(q1, dev.KvCacheView(k1, v1), mask1, scale, n_chunks=8)
+        assert not np.array_equal(got.view(np.uint32), cpu1.view(np.uint32)) and row_rel(got, ref64(q1, k1, v1, mask1, scale)) <= TOL
+        got = dev.flash_attn(q3, dev.KvCacheView(k3, v3), mask3, scale)
+        assert not np.array_equal(got.view(np.uint32), cpu3.view(np.uint32)) and row_rel(got, ref64(q3, k3, v3, mask3, scale)) <= TOL
+        monkeypatch.setenv("B200_FA_DECODE_MMA", "0")
+        got = dev.flash_attn(q1, dev.KvCacheView(k1, v1), mask1, scale, n_chunks=8)
+        assert not np.array_equal(got.view(np.uint32), cpu1.view(np.uint32)) and row_rel(got, ref64(q1, k1, v1, mask1, scale)) <= 1e-5
+        got = dev.flash_attn(q3, dev.KvCacheView(k3, v3), mask3, scale)
+        assert np.array_equal(got.view(np.uint32), cpu3.view(np.uint32))
     finally:
         dev.set_numerics(dev.EXACT)
 
 
+@pytest.mark.parametrize("kernel", ["mma", "cuda-core"])
 @pytest.mark.parametrize("n_kv", [512, 768, 4096, 32768])
-def test_decode_one_row_gqa_128(dev, n_kv):
-    """the benchmark's decode shape: 32 query heads on 8 KV heads of 128, one query row, causal mask"""
+def test_decode_one_row_gqa_128(dev, n_kv, kernel, monkeypatch):
+    """the benchmark's decode shape: 32 query heads on 8 KV heads of 128, one query row, causal mask; the tensor-core
+    decode kernel (csrc/flash_attn_decode_mma.cu) and the CUDA-core one (csrc/flash_attn_fast.cu)"""
+    monkeypatch.setenv("B200_FA_DECODE_MMA", "1" if kernel == "mma" else "0")
     scale = 1.0 / np.sqrt(128.0)
     q, k, v, mask = synth_case(32, 8, 128, 1, n_kv, seed=n_kv + 1)
     cpu, _ = orc.flash_attn(q, k, v, mask, scale, n_chunks=8)
@@ -87,10 +96,12 @@ def test_decode_one_row_gqa_128(dev, n_kv):
     assert d_gc <= 1.05 * (d_c64 + d_g64) + 1e-6
 
 
-@pytest.mark.parametrize("shape", [(16, 3072, 128), (5, 300, 64), (2, 700, 128), (63, 200, 128)], ids=str)
-def test_few_rows_with_ragged_masks(dev, shape):
+@pytest.mark.parametrize("kernel", ["mma", "cuda-core"])
+@pytest.mark.parametrize("shape", [(16, 3072, 128), (5, 300, 64), (2, 700, 128), (63, 200, 128), (33, 9000, 128)], ids=str)
+def test_few_rows_with_ragged_masks(dev, shape, kernel, monkeypatch):
     """several rows, each with its own visible cells (batched decode over a shared cache), a row that sees nothing,
     a context that is not a multiple of the tile"""
+    monkeypatch.setenv("B200_FA_DECODE_MMA", "0" if kernel == "cuda-core" else "1")
     T, n_kv, D = shape
     q, k, v, _ = synth_case(8, 2, D, T, n_kv, seed=T * 7 + n_kv, causal=False)
     rng = np.random.default_rng(T)
@@ -112,6 +123,25 @@ def test_few_rows_with_ragged_masks(dev, shape):
         want = ref64(q, k, v, mask, scale)
     d_gc, d_g64, d_c64 = row_rel(got[live], cpu[live]), row_rel(got[live], want[live]), row_rel(cpu[live], want[live])
     print(f"rows {shape}: GPU-CPU {d_gc:.2e}  GPU-f64 {d_g64:.2e}  CPU-f64 {d_c64:.2e}")
+    assert d_g64 <= TOL and d_g64 <= max(d_c64, 1e-5)
+
+
+@pytest.mark.parametrize("heads", [(4, 4), (8, 4), (16, 2), (16, 1), (12, 4), (32, 8)], ids=str)
+@pytest.mark.parametrize("shape", [(1, 1000, 128, True), (7, 650, 64, True), (1, 333, 128, False), (4, 64, 64, False)], ids=str)
+def test_decode_kernel_head_groupings(dev, heads, shape):
+    """1, 2, 4, 8 and 16 query heads per KV head (row blocks of whole tokens; three heads per KV head do not tile a block
+    of 16 rows and take the CUDA-core kernel), head sizes 128 and 64, with a causal mask and with none, a cache
+    shorter than two tiles"""
+    H, Hkv = heads
+    T, n_kv, D, causal = shape
+    q, k, v, mask = synth_case(H, Hkv, D, T, n_kv, seed=H * 100 + T, causal=causal)
+    scale = 1.0 / np.sqrt(float(D))
+    cpu, _ = orc.flash_attn(q, k, v, mask, scale)
+    want = ref64(q, k, v, mask, scale)
+    got = run_fast(dev, q, k, v, mask, scale)
+    d_g64, d_c64 = row_rel(got, want), row_rel(cpu, want)
+    print(f"heads {heads} {shape}: GPU-f64 {d_g64:.2e}  CPU-f64 {d_c64:.2e}")
+    assert dev.kernel_error() == 0
     assert d_g64 <= TOL and d_g64 <= max(d_c64, 1e-5)
 
 
