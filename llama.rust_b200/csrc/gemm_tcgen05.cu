@@ -702,6 +702,12 @@ int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t
     B200_REQUIRE(mode == 1 || mode == 2, "gemm: unknown mode %d", mode);
     if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
     int choice = gemm_tcgen05_f16_choice();
+    // fast numerics: one tensor-memory drain per super-block instead of the CPU chain's per-pair fused multiply-adds
+    // (within 1e-5 of sum |w x|, both routes); B200_GEMM_FAST=0 keeps the exact kernels (read per call)
+    if (choice < 0 && numerics_mode() == 1 && m >= GEMM_FAST_MIN_COLS && !no_scratch_mode()) {
+        const char *e = getenv("B200_GEMM_FAST");
+        if (!(e && e[0] == '0')) return launch_gemm_q4_K_fast(n, k, m, tiles, acts, dst, lddst, s);
+    }
     if (mode == 1 && choice < 0) choice = gemm_chain_pick(n, m);
     if (no_scratch_mode() && (choice == 3 || choice == 4)) choice = 0;   // the two-pass kernels need the image block
     if (mode == 1 && choice == 2) return launch_gemm_tcgen05_f16x64(n, k, m, tiles, acts, dst, lddst, s);

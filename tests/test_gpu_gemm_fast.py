@@ -1,0 +1,64 @@
+"""Q4_K prompt mat-muls in the library's fast numerics mode (csrc/gemm_tcgen05_fast.cu) against the CPU oracle (-m gpu).
+
+The kernel accumulates a whole super-block on the tensor cores and applies the block scales once per super-block, where
+the CPU routes (8x8 gemm chain: crates/ggml/src/repack.rs:1692-1768; tiled chain: tiled.rs) run fused multiply-adds
+per sub-block pair.  It is held to the mat-mul tolerance, defined as the reference defines it
+(crates/ggml/src/compute.rs:7467-7577): |got - ref| <= 1e-5 * sum_k |w_k x_k| per output element; in exact mode
+the same call gives the CPU's bits."""
+import numpy as np
+import pytest
+
+import b200
+import orc
+import synth
+from conftest import bits_equal
+
+pytestmark = pytest.mark.gpu
+
+# (weight rows, row length, activation rows): ragged row blocks and column blocks, one and many super-blocks,
+# row counts that take the tiled route (n % 8 != 0) and the 8x8 route, the benchmark's square shape
+SHAPES = [(128, 256, 64), (256, 1024, 67), (296, 2048, 100), (300, 512, 129), (1024, 4096, 200), (4096, 4096, 512), (520, 14336, 256)]
+
+
+@pytest.fixture(scope="module")
+def dev():
+    mod = b200.load()
+    assert mod.device_count() > 0
+    mod.set_device(0)
+    return mod
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_q4_K_fast_mode_within_the_mat_mul_tolerance(dev, shape):
+    n, k, m = shape
+    W = synth.weights(orc.Q4_K, n, k, seed=420, period=512)
+    x = synth.activations(m, k, seed=421 + m)
+    want, _ = orc.mul_mat(orc.Q4_K, W, x)
+    dev.set_numerics(dev.FAST)
+    try:
+        got = dev.mul_mat(dev.Weight(orc.Q4_K, W, k), x)
+    finally:
+        dev.set_numerics(dev.EXACT)
+    assert dev.kernel_error() == 0
+    bound = 1e-5 * (np.abs(x).astype(np.float64) @ np.abs(orc.dequantize(orc.Q4_K, W, k)).astype(np.float64).T)
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    print(f"Q4_K {shape}: max |got - ref| / sum|w x| = {(err / (bound * 1e5)).max():.2e}")
+    assert (err <= bound).all(), f"worst ratio to the bound: {(err / bound).max():.3g}"
+    assert not bits_equal(got, want) or n * m < 1 << 14, "the fast kernel was not taken"
+    # and in exact mode the same call reproduces the CPU's chain
+    assert bits_equal(dev.mul_mat(dev.Weight(orc.Q4_K, W, k), x), want)
+
+
+def test_q4_K_fast_mode_switch(dev, monkeypatch):
+    """B200_GEMM_FAST=0 keeps the exact kernels under the fast policy too"""
+    n, k, m = 256, 1024, 64
+    W = synth.weights(orc.Q4_K, n, k, seed=430, period=512)
+    x = synth.activations(m, k, seed=431)
+    want, _ = orc.mul_mat(orc.Q4_K, W, x)
+    monkeypatch.setenv("B200_GEMM_FAST", "0")
+    dev.set_numerics(dev.FAST)
+    try:
+        got = dev.mul_mat(dev.Weight(orc.Q4_K, W, k), x)
+    finally:
+        dev.set_numerics(dev.EXACT)
+    assert bits_equal(got, want)
