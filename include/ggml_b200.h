@@ -99,6 +99,9 @@ int b200_debug_decode_step_times(unsigned long long *out, int n);
 /* profiling aid: with B200_FA_PREFILL_PROFILE=1 in the environment the tcgen05 prompt-attention kernel sums, for one thread
  * of each role of its first CTA, the SM clocks spent at each barrier and at work (24 counters); this reads them back */
 int b200_debug_fa_prefill_profile(unsigned long long *out, int n);
+/* profiling aid: with B200_GEMM_FAST_PROFILE=1 the fast-numerics Q4_K prompt mat-mul sums, for one thread of each role of its
+ * first CTA, the SM clocks spent at each barrier and at work (10 counters); this reads them back and clears them */
+int b200_debug_gemm_fast_profile(unsigned long long *out, int n);
 void b200_debug_decode_step_wait(int spin_limit, int skip_cta, int skip_barrier);
 /* Which kernel a Q4_K prompt mat-mul (8x8 gemm route, n weight rows, m >= 32 activation rows) takes on a GPU with
  * sm_count SMs: 0 = integer tcgen05 kernel, 3 / 4 = the two-pass f16-image kernels with 64 / 128 activation rows

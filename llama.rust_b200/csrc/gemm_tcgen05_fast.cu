@@ -35,7 +35,9 @@ namespace {
 
 constexpr int FQ_ROWS = 128, FQ_COLS = 128;
 constexpr int FQ_EPI_WARPS = 8, FQ_MMA_WARP = 8, FQ_LOAD_WARP = 9;
-constexpr int FQ_THREADS = 12 * 32;          // 168 registers each: no register hand-over between roles needed
+constexpr int FQ_PROD_WARP0 = 12, FQ_PROD_WARPS = 8;   // FUSED: the warps that unpack the CTA's weights (a row's half step per thread)
+constexpr int FQ_THREADS = 20 * 32;          // five warp groups: two of epilogue warps, the two single-thread roles, two of producers
+constexpr int FQ_REGS_EPI = 144, FQ_REGS_CTL = 40, FQ_REGS_PROD = 64;   // 2 x 144 + 40 + 2 x 64 = 456 <= 5 x 96
 constexpr int FQ_EXPAND_THREADS = 512;
 constexpr int FQ_PAIR_BYTES = FQ_ROWS * 128; // one pair column: 16384
 constexpr int FQ_A_BYTES = 4 * FQ_PAIR_BYTES, FQ_M_BYTES = FQ_ROWS * 32, FQ_DA_BYTES = FQ_COLS * 4;
@@ -87,14 +89,16 @@ __device__ __forceinline__ bool q_mbar_wait(uint32_t bar, uint32_t parity, volat
     *abort_flag = 1;
     return false;
 }
-__device__ __forceinline__ void q_tmem_ld8f(float (&v)[8], uint32_t taddr) {
-    uint32_t r[8];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr)
-                 : "memory");
-#pragma unroll
-    for (int i = 0; i < 8; i++) v[i] = __uint_as_float(r[i]);
+// 32 columns of this thread's tensor-memory lane
+__device__ __forceinline__ void q_tmem_ld32(uint32_t (&r)[32], uint32_t taddr) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+          "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+          "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
 }
 __device__ __forceinline__ void q_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, int accumulate) {
     asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(d_tmem), "l"(adesc), "l"(bdesc),
@@ -118,6 +122,20 @@ __device__ __forceinline__ uint32_t q_signed(uint32_t u, int shift) {
     return q_h2_bits(__hsub2(q_bits_h2(((u >> shift) & 0x00ff00ffu) | 0x64006400u), __float2half2_rn(1152.0f)));
 }
 __device__ __forceinline__ void q_stg128(uint8_t *p, uint32_t x, uint32_t y, uint32_t z, uint32_t w) { *reinterpret_cast<uint4 *>(p) = make_uint4(x, y, z, w); }
+
+// profiling aid (B200_GEMM_FAST_PROFILE=1): SM clocks one thread of each role of CTA (0, 0) spends waiting at each of its
+// barriers and working, summed over the steps: [0] epilogue warp 0 waiting for the accumulator, [1] draining it; [2] MMA
+// thread waiting for a stage, [3] for a tensor-memory stage, [4] issuing; [5] loader waiting for a free stage, [6] issuing;
+// [7] producer warp 12 waiting for a free stage, [8] converting; [9] the CTA's whole run
+__device__ unsigned long long g_fq_prof[16];
+#define FQ_MARK(k)                                            \
+    do {                                                      \
+        if (prof) {                                           \
+            const long long t_now = clock64();                \
+            pacc[k] += (unsigned long long)(t_now - t_prev);  \
+            t_prev = t_now;                                   \
+        }                                                     \
+    } while (0)
 
 struct alignas(16) FqBars {
     uint64_t full[FQ_STAGES], empty[FQ_STAGES], tfull[FQ_TSTAGES], tempty[FQ_TSTAGES];
@@ -225,9 +243,12 @@ __global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q8_K_acts_fast_kerne
     }
 }
 
+// FUSED: no weight images; warps 12..19 unpack the 128 rows' nibbles of every step straight into the stage (and the mins
+// into their slot), so the weights cross the L2 as 0.5625 bytes each instead of 2
+template <bool FUSED>
 __global__ void __launch_bounds__(FQ_THREADS, 1)
 gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *__restrict__ aimg, const uint8_t *__restrict__ bimg, float *dst,
-                              int64_t lddst, int64_t n, int nb, int64_t m, int *err) {
+                              int64_t lddst, int64_t n, int nb, int64_t m, int *err, int profile) {
     extern __shared__ uint8_t fq_raw[];
     __shared__ FqBars bars;
     pdl_trigger();
@@ -239,10 +260,14 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
     const int64_t col0 = cb * FQ_COLS;
     const int np = 2 * nb;   // pipeline steps: half super-blocks
     volatile int *abort_flag = &bars.abort_flag;
+    const bool prof = profile && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0;
+    long long t_prev = clock64();
+    const long long t_start = t_prev;
+    unsigned long long pacc[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};   // kept in registers, written once at the end
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < FQ_STAGES; i++) {
-            q_mbar_init(q_smem_u32(&bars.full[i]), 1);    // the loader's arrive + the bytes it announced
+            q_mbar_init(q_smem_u32(&bars.full[i]), FUSED ? 1 + FQ_PROD_WARPS : 1);   // the loader's arrive + the bytes it announced (+ the producer warps)
             q_mbar_init(q_smem_u32(&bars.empty[i]), 1);   // the MMA thread's commit
         }
         for (int i = 0; i < FQ_TSTAGES; i++) {
@@ -261,9 +286,10 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = bars.tmem_base;
-    pdl_wait();   // the images are the two previous kernels' output
 
     if (warp < FQ_EPI_WARPS) {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FQ_REGS_EPI));
+        pdl_wait();   // the images are the previous kernels' output, and the previous mat-mul may still be reading dst's producers
         const int q = warp & 3, h = warp >> 2;
         const bool row_ok = tile0 + q < tiles_n;
         const bool any_col = col0 + 64 * h < m;
@@ -278,36 +304,34 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
             const int t = b % FQ_TSTAGES;
             const float dw = f16_bits_to_f32((uint16_t)(dd_next & 0xffffu)), dmw = -f16_bits_to_f32((uint16_t)(dd_next >> 16));
             if (b + 1 < nb && row_ok) dd_next = *(const uint32_t *)(hdr + (int64_t)(b + 1) * 4608);
+            if (warp == 0) FQ_MARK(1);
             if (!__all_sync(0xffffffffu, q_mbar_wait(q_smem_u32(&bars.tfull[t]), (uint32_t)(b / FQ_TSTAGES) & 1u, abort_flag))) break;
+            if (warp == 0) FQ_MARK(0);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float4 *das = reinterpret_cast<const float4 *>(bars.da[b % FQ_DA_SLOTS] + 64 * h);
             const uint32_t trow = trow0 + (uint32_t)(t * 256);
-            // eight rounds of eight columns, the next round's loads in flight while this one's multiply-adds run
-            float ig[2][8], mg[2][8];
-            q_tmem_ld8f(ig[0], trow);
-            q_tmem_ld8f(mg[0], trow + 128);
+            // two rounds of 32 columns: one tensor-memory round trip each for ig and mg, then per column
+            //   acc += d_x (d ig - dmin mg)
+            uint32_t ig[32], mg[32];
 #pragma unroll
-            for (int r = 0; r < 8; r++) {
-                const int c0 = 8 * r;
+            for (int r = 0; r < 2; r++) {
+                q_tmem_ld32(ig, trow + (uint32_t)(32 * r));
+                q_tmem_ld32(mg, trow + (uint32_t)(128 + 32 * r));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (r < 7) {
-                    q_tmem_ld8f(ig[(r + 1) & 1], trow + (uint32_t)(c0 + 8));
-                    q_tmem_ld8f(mg[(r + 1) & 1], trow + (uint32_t)(128 + c0 + 8));
-                } else {
+                if (r == 1) {
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) q_mbar_arrive(q_smem_u32(&bars.tempty[t]));
                 }
                 if (any_col) {
 #pragma unroll
-                    for (int h2 = 0; h2 < 2; h2++) {
-                        const float4 dq = das[c0 / 4 + h2];
+                    for (int c4 = 0; c4 < 8; c4++) {
+                        const float4 dq = das[8 * r + c4];
                         const float dxs[4] = {dq.x, dq.y, dq.z, dq.w};
 #pragma unroll
-                        for (int c4 = 0; c4 < 4; c4++) {
-                            const int c = 4 * h2 + c4;
-                            acc[c0 + c] = fmaf(ig[r & 1][c], dw * dxs[c4], acc[c0 + c]);
-                            acc[c0 + c] = fmaf(mg[r & 1][c], dmw * dxs[c4], acc[c0 + c]);
+                        for (int c = 0; c < 4; c++) {
+                            const float tsum = fmaf(__uint_as_float(mg[4 * c4 + c]), dmw, __uint_as_float(ig[4 * c4 + c]) * dw);
+                            acc[32 * r + 4 * c4 + c] = fmaf(tsum, dxs[c], acc[32 * r + 4 * c4 + c]);
                         }
                     }
                 }
@@ -321,12 +345,90 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
                 if (col < m) dst[col * lddst + row] = acc[c];
             }
         }
-    } else if (warp == FQ_MMA_WARP) {
+    } else if (warp >= FQ_PROD_WARP0) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FQ_REGS_PROD));
+        if constexpr (FUSED) {
+            // thread = (row (tile tt, lane), pair column hh of the step): per step the two 16-byte pieces 4 hs + 2 hh, + 1 of the
+            // row's 128 nibble bytes, loaded one step ahead (the weights do not depend on the previous kernel)
+            const int pw = warp - FQ_PROD_WARP0, tt = pw & 3, hh = pw >> 2, prow = tt * 32 + lane, sw = prow & 7;
+            const bool tile_ok = tile0 + tt < tiles_n;
+            const uint8_t *src = tiles + (tile_ok ? tile0 + tt : 0) * (int64_t)nb * 4608 + lane * 16;
+            uint8_t *stage0 = fq_raw + (smem - q_smem_u32(fq_raw)) + hh * FQ_PAIR_BYTES + prow * 128;
+            uint8_t *am0 = fq_raw + (mslots - q_smem_u32(fq_raw)) + (prow >> 3) * 256 + (prow & 7) * 16;
+            uint4 hd = make_uint4(0, 0, 0, 0), hd_next = hd, w[2], wn[2];
+            wn[0] = wn[1] = hd;
+            if (tile_ok) {
+                hd_next = *(const uint4 *)src;
+#pragma unroll
+                for (int i = 0; i < 2; i++) wn[i] = ld_stream16(src + 512 + (2 * hh + i) * 512);
+            }
+            for (int p = 0; p < np; p++) {
+                const int s = p % FQ_STAGES, b = p >> 1, hs = p & 1;
+                w[0] = wn[0];
+                w[1] = wn[1];
+                if (hs == 0) hd = hd_next;
+                if (p + 1 < np && tile_ok) {
+                    const uint8_t *nx = src + (int64_t)((p + 1) >> 1) * 4608;
+                    if (hs == 1) hd_next = *(const uint4 *)nx;
+#pragma unroll
+                    for (int i = 0; i < 2; i++) wn[i] = ld_stream16(nx + 512 + (4 * (hs ^ 1) + 2 * hh + i) * 512);
+                }
+                if (warp == FQ_PROD_WARP0) FQ_MARK(8);
+                if (!__all_sync(0xffffffffu, q_mbar_wait(q_smem_u32(&bars.empty[s]), ((uint32_t)(p / FQ_STAGES) & 1u) ^ 1u, abort_flag))) break;
+                if (warp == FQ_PROD_WARP0) FQ_MARK(7);
+                if (profile == 2) {
+                    __syncwarp();
+                    if (lane == 0) q_mbar_arrive(q_smem_u32(&bars.full[s]));
+                    continue;
+                }
+                if (hs == 0 && hh == 0) {
+                    // the mins slot of super-block b - 2 is free: see the loader
+                    const uint32_t mn0 = hd.z & 0x3f3f3f3fu, mn1 = ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4);
+                    uint32_t mins[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) mins[j] = q_h2_bits(q_small2(((j < 4 ? mn0 : mn1) >> (8 * (j & 3))) & 0xffu));
+                    uint8_t *am = am0 + (b % FQ_MSLOTS) * 2 * FQ_M_BYTES;
+                    q_stg128(am, mins[0], mins[1], mins[2], mins[3]);
+                    q_stg128(am + 128, mins[4], mins[5], mins[6], mins[7]);
+                }
+                {
+                    // pair g = 2 hs + hh (sub-blocks 2 g, 2 g + 1): the step's pair column hh
+                    const int g = 2 * hs + hh;
+                    const uint32_t scw = g < 2 ? (hd.y & 0x3f3f3f3fu) : ((hd.w & 0x0f0f0f0fu) | (((hd.y >> 6) & 0x03030303u) << 4));
+                    const uint32_t s_lo = (scw >> (16 * (g & 1))) & 0xffu, s_hi = (scw >> (16 * (g & 1) + 8)) & 0xffu;
+                    const __half2 sl = q_small2(s_lo), sh = q_small2(s_hi);
+                    const __half2 cl = __hmul2(sl, __float2half2_rn(-1024.0f)), ch = __hmul2(sh, __float2half2_rn(-64.0f));
+                    const __half2 sh16 = __hmul2(sh, __float2half2_rn(0.0625f));
+                    uint8_t *dstp = stage0 + s * FQ_STAGE_BYTES;
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        const uint4 v = w[i];
+                        const uint32_t x8 = v.x >> 8, y8 = v.y >> 8, z8 = v.z >> 8, w8 = v.w >> 8;   // bytes 1 and 3
+                        const int c0 = 4 * i;
+                        q_stg128(dstp + (((c0 + 0) ^ sw) << 4), q_scaled_lo(v.x, sl, cl), q_scaled_lo(x8, sl, cl), q_scaled_lo(v.y, sl, cl), q_scaled_lo(y8, sl, cl));
+                        q_stg128(dstp + (((c0 + 1) ^ sw) << 4), q_scaled_lo(v.z, sl, cl), q_scaled_lo(z8, sl, cl), q_scaled_lo(v.w, sl, cl), q_scaled_lo(w8, sl, cl));
+                        q_stg128(dstp + (((c0 + 2) ^ sw) << 4), q_scaled_hi(v.x, sh16, ch), q_scaled_hi(x8, sh16, ch), q_scaled_hi(v.y, sh16, ch), q_scaled_hi(y8, sh16, ch));
+                        q_stg128(dstp + (((c0 + 3) ^ sw) << 4), q_scaled_hi(v.z, sh16, ch), q_scaled_hi(z8, sh16, ch), q_scaled_hi(v.w, sh16, ch), q_scaled_hi(w8, sh16, ch));
+                    }
+                }
+                // the stores (generic proxy) before the tensor core's reads (async proxy), then the warp's arrival
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) q_mbar_arrive(q_smem_u32(&bars.full[s]));
+            }
+        }
+    } else {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FQ_REGS_CTL));
+        pdl_wait();
+    if (warp == FQ_MMA_WARP) {
         if (lane == 0) {
             for (int p = 0; p < np; p++) {
                 const int s = p % FQ_STAGES, b = p >> 1, hs = p & 1, t = b % FQ_TSTAGES;
+                FQ_MARK(4);
                 if (!q_mbar_wait(q_smem_u32(&bars.full[s]), (uint32_t)(p / FQ_STAGES) & 1u, abort_flag)) break;
+                FQ_MARK(2);
                 if (hs == 0 && !q_mbar_wait(q_smem_u32(&bars.tempty[t]), ((uint32_t)(b / FQ_TSTAGES) & 1u) ^ 1u, abort_flag)) break;
+                FQ_MARK(3);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t a_base = smem + (uint32_t)(s * FQ_STAGE_BYTES), b_base = a_base + FQ_HALF;
                 const uint32_t d_ig = tmem + (uint32_t)(t * 256);
@@ -351,17 +453,23 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
         int issued = -1;
         for (int p = 0; p < np; p++) {
             const int s = p % FQ_STAGES, b = p >> 1, hs = p & 1;
+            FQ_MARK(6);
             if (!q_mbar_wait(q_smem_u32(&bars.empty[s]), ((uint32_t)(p / FQ_STAGES) & 1u) ^ 1u, abort_flag)) break;
+            FQ_MARK(5);
             const uint32_t bar = q_smem_u32(&bars.full[s]), stage = smem + (uint32_t)(s * FQ_STAGE_BYTES);
-            const uint8_t *ab = asrc + (int64_t)b * FQ_AIMG, *bb = bsrc + (int64_t)b * FQ_BIMG;
-            q_mbar_expect(bar, (uint32_t)(FQ_STAGE_BYTES + (hs == 0 ? 2 * FQ_M_BYTES + FQ_DA_BYTES : 0)));
-            q_bulk_load(stage, ab + hs * FQ_HALF, FQ_HALF, bar);
+            const uint8_t *ab = FUSED ? nullptr : asrc + (int64_t)b * FQ_AIMG, *bb = bsrc + (int64_t)b * FQ_BIMG;
+            if (profile == 2) {   // measurement only: no operand traffic at all (the outputs are garbage)
+                q_mbar_arrive(bar);
+                continue;
+            }
+            q_mbar_expect(bar, (uint32_t)((FUSED ? FQ_HALF : FQ_STAGE_BYTES) + (hs == 0 ? (FUSED ? 1 : 2) * FQ_M_BYTES + FQ_DA_BYTES : 0)));
+            if (!FUSED) q_bulk_load(stage, ab + hs * FQ_HALF, FQ_HALF, bar);
             q_bulk_load(stage + FQ_HALF, bb + hs * FQ_HALF, FQ_HALF, bar);
             if (hs == 0) {
                 // the mins slot of super-block b - 2 and the scale slot of b - 4 are free: the stage this step reuses was
                 // released by MMAs issued after the drain of super-block b - 2 had ended
                 const uint32_t ms = mslots + (uint32_t)((b % FQ_MSLOTS) * 2 * FQ_M_BYTES);
-                q_bulk_load(ms, ab + FQ_A_BYTES, FQ_M_BYTES, bar);
+                if (!FUSED) q_bulk_load(ms, ab + FQ_A_BYTES, FQ_M_BYTES, bar);
                 q_bulk_load(ms + FQ_M_BYTES, bb + FQ_A_BYTES, FQ_M_BYTES, bar);
                 q_bulk_load(q_smem_u32(bars.da[b % FQ_DA_SLOTS]), bb + FQ_A_BYTES + FQ_M_BYTES, FQ_DA_BYTES, bar);
             }
@@ -370,6 +478,7 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
         // a CTA that gives up still waits (bounded) for the copies it has in flight
         if (*abort_flag && issued >= 0) q_mbar_wait(q_smem_u32(&bars.full[issued % FQ_STAGES]), (uint32_t)(issued / FQ_STAGES) & 1u, abort_flag);
     }
+    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == FQ_MMA_WARP) {
@@ -377,6 +486,21 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
     }
     if (threadIdx.x == 0 && bars.abort_flag) atomicExch(err, FQ_ERR_WAIT);
+    if (prof) {
+#pragma unroll
+        for (int i = 0; i < 9; i++)
+            if (pacc[i]) atomicAdd(&g_fq_prof[i], pacc[i]);
+        if (threadIdx.x == 0) atomicAdd(&g_fq_prof[9], (unsigned long long)(clock64() - t_start));
+    }
+}
+
+// the clocks of the profiled launches so far (see g_fq_prof); reading clears them
+int gemm_fast_profile(unsigned long long *out, int n) {
+    if (n > 16) n = 16;
+    B200_CUDA(cudaMemcpyFromSymbol(out, g_fq_prof, (size_t)n * sizeof(unsigned long long)));
+    static const unsigned long long zeros[16] = {0};
+    B200_CUDA(cudaMemcpyToSymbol(g_fq_prof, zeros, sizeof(zeros)));
+    return B200_STATUS_SUCCESS;
 }
 
 int launch_gemm_q4_K_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s) {
@@ -387,28 +511,40 @@ int launch_gemm_q4_K_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles,
     B200_CUDA(cudaGetDevice(&dev));
     B200_REQUIRE(dev >= 0 && dev < 64, "gemm: device index %d out of range", dev);
     if (!attr_done[dev]) {
-        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FQ_SMEM_BYTES));
+        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_fast_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, FQ_SMEM_BYTES));
+        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_fast_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, FQ_SMEM_BYTES));
         attr_done[dev] = true;
     }
     int *err = nullptr;
     int rc = device_error_word(&err);
     if (rc != B200_STATUS_SUCCESS) return rc;
+    // B200_GEMM_FAST_FUSED=0: the weights through an image of their own (expanded by a kernel before the mat-mul) instead of
+    // the mat-mul's producer warps (read per call)
+    const char *ev = getenv("B200_GEMM_FAST_FUSED");
+    const bool fused = !(ev && ev[0] == '0');
+    const char *pv = getenv("B200_GEMM_FAST_PROFILE");
+    const int profile = pv && pv[0] >= '1' && pv[0] <= '2' ? pv[0] - '0' : 0;   // 2: no operand traffic, garbage out (measurement of the MMA / drain rate alone)
     const int nb = (int)(k / GROUP_K);
     const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
     const int64_t gx = (m + FQ_COLS - 1) / FQ_COLS, gy = (n + FQ_ROWS - 1) / FQ_ROWS;
     B200_REQUIRE(gx <= 65535 && gy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);
-    const size_t a_bytes = (size_t)gy * nb * FQ_AIMG, b_bytes = (size_t)gx * nb * FQ_BIMG;
+    const size_t a_bytes = fused ? 0 : (size_t)gy * nb * FQ_AIMG, b_bytes = (size_t)gx * nb * FQ_BIMG;
     void *block = nullptr;
     rc = scratch_get_images(a_bytes + b_bytes, &block);
     if (rc != B200_STATUS_SUCCESS) return rc;
     uint8_t *aimg = (uint8_t *)block, *bimg = aimg + a_bytes;
     const dim3 ga((unsigned)nb, (unsigned)gy), gb((unsigned)nb, (unsigned)gx), gg((unsigned)gx, (unsigned)gy);
-    rc = launch_pdl(expand_q4_K_weights_fast_kernel, ga, dim3(FQ_EXPAND_THREADS), (size_t)0, s, tiles, aimg, tiles_n, nb);
-    if (rc != B200_STATUS_SUCCESS) return rc;
+    if (!fused) {
+        rc = launch_pdl(expand_q4_K_weights_fast_kernel, ga, dim3(FQ_EXPAND_THREADS), (size_t)0, s, tiles, aimg, tiles_n, nb);
+        if (rc != B200_STATUS_SUCCESS) return rc;
+    }
     rc = launch_pdl(expand_q8_K_acts_fast_kernel, gb, dim3(FQ_EXPAND_THREADS), (size_t)0, s, acts, bimg, m, nb);
     if (rc != B200_STATUS_SUCCESS) return rc;
-    return launch_pdl(gemm_q4_K_tcgen05_fast_kernel, gg, dim3(FQ_THREADS), (size_t)FQ_SMEM_BYTES, s, tiles, (const uint8_t *)aimg, (const uint8_t *)bimg, dst,
-                      lddst, n, nb, m, err);
+    if (fused)
+        return launch_pdl(gemm_q4_K_tcgen05_fast_kernel<true>, gg, dim3(FQ_THREADS), (size_t)FQ_SMEM_BYTES, s, tiles, (const uint8_t *)aimg,
+                          (const uint8_t *)bimg, dst, lddst, n, nb, m, err, profile);
+    return launch_pdl(gemm_q4_K_tcgen05_fast_kernel<false>, gg, dim3(FQ_THREADS), (size_t)FQ_SMEM_BYTES, s, tiles, (const uint8_t *)aimg, (const uint8_t *)bimg,
+                      dst, lddst, n, nb, m, err, profile);
 }
 
 }  // namespace b200

@@ -44,7 +44,9 @@ def test_q4_K_fast_mode_within_the_mat_mul_tolerance(dev, shape):
     err = np.abs(got.astype(np.float64) - want.astype(np.float64))
     print(f"Q4_K {shape}: max |got - ref| / sum|w x| = {(err / (bound * 1e5)).max():.2e}")
     assert (err <= bound).all(), f"worst ratio to the bound: {(err / bound).max():.3g}"
-    assert not bits_equal(got, want) or n * m < 1 << 14, "the fast kernel was not taken"
+    # (rows % 8 != 0 takes the tiled route on the CPU, whose chain is this kernel's own per super-block expression: equal bits
+    # there say nothing; the 8x8 route's chain rounds per sub-block pair)
+    assert n % 8 or n * m < 1 << 14 or not bits_equal(got, want), "the fast kernel was not taken"
     # and in exact mode the same call reproduces the CPU's chain
     assert bits_equal(dev.mul_mat(dev.Weight(orc.Q4_K, W, k), x), want)
 
