@@ -923,12 +923,13 @@ def case_gemm(args):
     e1.synchronize()
     us = e0.elapsed_ms(e1) * 1e3 / args.launches
     out = {"case": f"gemm {args.only} x {m}", "launches": args.launches, "us_per_call": us, "tops": 2.0 * n * k * m / us / 1e6, "kernel_error": b.kernel_error()}
-    if os.environ.get("B200_GEMM_FAST_PROFILE") in ("1", "2"):
+    if os.environ.get("B200_GEMM_FAST_PROFILE") in ("1", "2", "3", "4"):
         # SM clocks per launch of one thread per role of the fast kernel's first CTA (csrc/gemm_tcgen05_fast.cu)
         import ctypes
         buf = (ctypes.c_ulonglong * 16)()
         b.check(b.lib.b200_debug_gemm_fast_profile(buf, 16), "gemm_fast_profile")
-        names = ["epi_wait_acc", "epi_drain", "mma_wait_stage", "mma_wait_tmem", "mma_issue", "load_wait_free", "load_issue", "prod_wait_free", "prod_convert", "cta_total"]
+        names = ["epi_wait_acc", "epi_drain", "mma_wait_stage", "mma_wait_tmem", "mma_issue", "load_wait_free", "load_issue", "prod_wait_free", "prod_fetch_ahead",
+                 "prod_convert_store", "prod_fence_arrive", "-", "cta_total"]
         out["clocks_per_launch"] = {nm: int(buf[i]) // (args.launches + 3) for i, nm in enumerate(names)}
     print(json.dumps(out), flush=True)
 

@@ -1,30 +1,37 @@
 // Q4_K prompt mat-mul in the fast numerics mode (within 1e-5 of sum |w x| per output, not the CPU's bits): tcgen05 f16 MMAs
-// that accumulate a whole 256-element super-block in tensor memory, one drain per super-block.
+// that accumulate a whole 256-element super-block, mins included, in ONE tensor-memory accumulator, drained once per
+// super-block.
 //
-// The bit-exact two-pass kernels (gemm_tcgen05_img.cu) drain the accumulator once per sub-block pair, because the CPU's
-// chain rounds there, and read their operands as unswizzled core matrices; both bound them far below the tensor cores'
-// rate.  Here, per super-block b of an output (row n, activation row m),
-//     ig = sum_j s_j sum_i w_ji x_ji      (s_j w <= 945, x: exact f16 operands; 256 products summed in f32 by the MMA)
-//     mg = sum_j m_j (bsum_2j + bsum_2j+1) (mins and 16-element activation sums <= 2032: exact; sum < 2^24)
-//     out += (d d_x) ig - (dmin d_x) mg
-// which is the function the CPU computes (crates/ggml/src/repack.rs:1692-1768, tiled.rs) with the f32 additions in
-// another order: ig itself may round once it passes 2^24, and the per-pair fused multiply-adds become one per super-block.
+// The bit-exact two-pass kernels (gemm_tcgen05_img.cu) drain two accumulators once per sub-block pair, because the CPU's chain
+// rounds there, and read their operands as unswizzled core matrices; both bound them far below the tensor cores' rate.
+// Measured here: an M = 128, K = 16 MMA takes 128 cycles whatever N <= 256 is, so only N = 256 runs the tensor core at its
+// rate, and 512 tensor-memory columns hold two stages of N = 256 only if a super-block needs one accumulator.  So, per
+// super-block b of an output (row n, activation row m), with d, dmin the row's block scales and rho = dmin / d,
+//     acc = sum_j s_j sum_i w_ji x_ji  -  sum_j (rho m_j) (bsum_2j + bsum_2j+1)
+//     out += d_x (d acc)
+// s_j w (<= 945), x and the 16-element activation sums (<= 2032) are exact f16 operands; rho m_j is an f32 carried as two
+// f16 operands (high part + remainder, 22 bits) against the sums repeated; the MMA adds the 256 + 32 products in f32.  This
+// is the function the CPU computes (crates/ggml/src/repack.rs:1692-1768, tiled.rs) with the f32 operations in another order.
+// A row whose d is zero, or whose rho m_j could leave the f16 range (rho > 952), gets zero mins operands for that
+// super-block and the drain subtracts d_x dmin sum_j m_j bsum_j for it on the CUDA cores instead (read back from the
+// activations' own sums; seen on no real tensor, kept exact all the same).
 //
-// Two passes, like the exact kernels: two small kernels expand the operands to f16 in exactly the shared-memory images the
-// tensor core reads, the mat-mul kernel moves those images with bulk copies.  Images, per 128-row (or 128-column) block
-// and super-block:
-//   A  four pair columns [128 rows][64 f16], rows 128 bytes apart, 16-byte chunks XOR-swizzled with row % 8 (the 128-byte
-//      swizzle of the matrix descriptor); within pair g the chunks are 4 p + 2 hi + half: 16-byte piece p of the pair's 32
-//      nibble bytes, low | high nibbles, bytes (0,2,1,3,4,6,5,7 | 8 ..)                                    65536 B
-//   Am [128 rows][16 f16], unswizzled core matrices: slots 2 j, 2 j + 1 = the min of sub-block j                 4096 B
-//   B  the activation bytes in the same layout and K order                                                     65536 B
-//   Bm [128 rows][16 f16]: the sixteen 16-element sums                                                          4096 B
-//   da 128 f32 activation scales                                                                                 512 B
-// Mat-mul kernel: 128 x 128 outputs per CTA; a pipeline step is half a super-block (two pair columns of A and of B,
-// 64 KB, three stages); warp 9 (one thread) copies, warp 8 (one thread) issues 8 (+ 1 for the mins) MMAs per step into one
-// of two tensor-memory stages (ig 128 columns, mg 128 columns), warps 0..7 drain: warp w owns rows 32 (w % 4) .. + 31 (its
-// tensor-memory lanes) and columns 64 (w / 4) .. + 63.  Every wait is bounded; a wait that runs out raises the CTA's abort
-// flag and the device error word.
+// Operands.  The activations are expanded once per mat-mul by a small kernel to the shared-memory images the tensor core
+// reads, per block of NC (128 or 256) activation rows and super-block:
+//   B   four pair columns [NC rows][64 f16], rows 128 bytes apart, 16-byte chunks XOR-swizzled with row % 8 (the 128-byte
+//       swizzle of the matrix descriptor); within pair g the chunks are 4 p + 2 hi + half: 16-byte piece p of the pair's 32
+//       nibble bytes, low | high nibbles, bytes (0,2,1,3,4,6,5,7 | 8 ..)
+//   Bm  [NC rows][32 f16], unswizzled core matrices: the sixteen 16-element sums, twice
+//   da  NC f32 activation scales
+// and move with bulk copies.  The weights take no image: four producer warps (a row per thread) unpack the 128 rows' nibbles
+// of every step straight into the stage in the same layout (A), and at the first step of a super-block the mins operand Am
+// [128 rows][32 f16] (slots 2 j, 2 j + 1 = high part of -rho m_j, slots 16 + 2 j, + 1 = the remainder), so the weights cross
+// the L2 as 0.5625 bytes each.
+// Mat-mul kernel: 128 x NC outputs per CTA; a pipeline step is one pair column (K = 64: 16 KB of A, NC x 128 bytes of B);
+// warp 9 (one thread) copies, warp 8 (one thread) issues 4 (+ 2 for the mins) MMAs per step into one of two tensor-memory
+// stages of NC columns, warps 0..7 drain: warp w owns rows 32 (w % 4) .. + 31 (its tensor-memory lanes) and columns
+// NC / 2 (w / 4) .. + NC / 2 - 1.  Every wait is bounded; a wait that runs out raises the CTA's abort flag and the device
+// error word.
 #include <cuda_fp16.h>
 
 #include "common.cuh"
@@ -33,24 +40,30 @@ namespace b200 {
 
 namespace {
 
-constexpr int FQ_ROWS = 128, FQ_COLS = 128;
+constexpr int FQ_ROWS = 128;
 constexpr int FQ_EPI_WARPS = 8, FQ_MMA_WARP = 8, FQ_LOAD_WARP = 9;
-constexpr int FQ_PROD_WARP0 = 12, FQ_PROD_WARPS = 8;   // FUSED: the warps that unpack the CTA's weights (a row's half step per thread)
-constexpr int FQ_THREADS = 20 * 32;          // five warp groups: two of epilogue warps, the two single-thread roles, two of producers
-constexpr int FQ_REGS_EPI = 144, FQ_REGS_CTL = 40, FQ_REGS_PROD = 64;   // 2 x 144 + 40 + 2 x 64 = 456 <= 5 x 96
+constexpr int FQ_PROD_WARP0 = 12, FQ_PROD_WARPS = 4;
+constexpr int FQ_THREADS = 16 * 32;          // four warp groups: two of epilogue warps, the two single-thread roles, the producers
+constexpr int FQ_REGS_EPI = 200, FQ_REGS_CTL = 40, FQ_REGS_PROD = 72;   // 2 x 200 + 40 + 72 = 512 = 4 x 128
 constexpr int FQ_EXPAND_THREADS = 512;
-constexpr int FQ_PAIR_BYTES = FQ_ROWS * 128; // one pair column: 16384
-constexpr int FQ_A_BYTES = 4 * FQ_PAIR_BYTES, FQ_M_BYTES = FQ_ROWS * 32, FQ_DA_BYTES = FQ_COLS * 4;
-constexpr int FQ_AIMG = FQ_A_BYTES + FQ_M_BYTES;                 // 69632
-constexpr int FQ_BIMG = FQ_A_BYTES + FQ_M_BYTES + FQ_DA_BYTES;   // 70144
-constexpr int FQ_STAGES = 3, FQ_TSTAGES = 2, FQ_MSLOTS = 2, FQ_DA_SLOTS = 4;
-constexpr int FQ_HALF = 2 * FQ_PAIR_BYTES;                       // 32768: half a super-block of one operand
-constexpr int FQ_STAGE_BYTES = 2 * FQ_HALF;                      // 65536
-constexpr int FQ_SMEM_BYTES = FQ_STAGES * FQ_STAGE_BYTES + FQ_MSLOTS * 2 * FQ_M_BYTES + 1024;   // 214016
+constexpr int FQ_A_STEP = FQ_ROWS * 128;     // one pair column of the weights: 16384
+constexpr int FQ_AM_BYTES = FQ_ROWS * 64;    // 8192
+constexpr int FQ_TSTAGES = 2, FQ_DA_SLOTS = 4;
 constexpr uint32_t FQ_WAIT_LIMIT = 1u << 22;
 constexpr int FQ_ERR_WAIT = 4;
-// kind::f16 instruction descriptor: f32 accumulator, f16 x f16, both operands K-major, N = 128, M = 128
-constexpr uint32_t FQ_IDESC = (1u << 4) | ((uint32_t)(FQ_COLS >> 3) << 17) | ((uint32_t)(FQ_ROWS >> 4) << 24);
+constexpr float FQ_RHO_MAX = 952.0f;         // 63 rho stays below 60000 < 65504
+
+template <int NC>
+struct FqCfg {
+    static constexpr int B_STEP = NC * 128;                       // one pair column of the activations
+    static constexpr int BM_BYTES = NC * 64, DA_BYTES = NC * 4;
+    static constexpr int BIMG = 4 * B_STEP + BM_BYTES + DA_BYTES; // per (column block, super-block)
+    static constexpr int STAGE = FQ_A_STEP + B_STEP;
+    static constexpr int STAGES = 4;                              // <= 4: one mins slot is enough (see the loader)
+    static constexpr int SMEM = STAGES * STAGE + FQ_AM_BYTES + BM_BYTES + 1024;   // 128: 148480, 256: 222208
+    // kind::f16 instruction descriptor: f32 accumulator, f16 x f16, both operands K-major, N = NC, M = 128
+    static constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(NC >> 3) << 17) | ((uint32_t)(FQ_ROWS >> 4) << 24);
+};
 
 __device__ __forceinline__ uint32_t q_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 // shared-memory matrix descriptors (version 1 in bit 46).  Unswizzled: K-adjacent core matrices lbo bytes apart, 8-row
@@ -100,9 +113,16 @@ __device__ __forceinline__ void q_tmem_ld32(uint32_t (&r)[32], uint32_t taddr) {
         : "r"(taddr)
         : "memory");
 }
-__device__ __forceinline__ void q_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, int accumulate) {
+// two f32 fused multiply-adds in one instruction
+__device__ __forceinline__ float2 q_fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(*reinterpret_cast<unsigned long long *>(&d)) : "l"(*reinterpret_cast<unsigned long long *>(&a)),
+        "l"(*reinterpret_cast<unsigned long long *>(&b)), "l"(*reinterpret_cast<unsigned long long *>(&c)));
+    return d;
+}
+__device__ __forceinline__ void q_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, int accumulate) {
     asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(d_tmem), "l"(adesc), "l"(bdesc),
-                 "r"(FQ_IDESC), "r"(accumulate)
+                 "r"(idesc), "r"(accumulate)
                  : "memory");
 }
 __device__ __forceinline__ uint32_t q_h2_bits(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
@@ -126,7 +146,8 @@ __device__ __forceinline__ void q_stg128(uint8_t *p, uint32_t x, uint32_t y, uin
 // profiling aid (B200_GEMM_FAST_PROFILE=1): SM clocks one thread of each role of CTA (0, 0) spends waiting at each of its
 // barriers and working, summed over the steps: [0] epilogue warp 0 waiting for the accumulator, [1] draining it; [2] MMA
 // thread waiting for a stage, [3] for a tensor-memory stage, [4] issuing; [5] loader waiting for a free stage, [6] issuing;
-// [7] producer warp 12 waiting for a free stage, [8] converting; [9] the CTA's whole run
+// [7] producer warp 12 waiting for a free stage, [8] fetching ahead, [9] converting and storing, [10] proxy fence and arrival;
+// [12] the CTA's whole run
 __device__ unsigned long long g_fq_prof[16];
 #define FQ_MARK(k)                                            \
     do {                                                      \
@@ -137,138 +158,96 @@ __device__ unsigned long long g_fq_prof[16];
         }                                                     \
     } while (0)
 
+template <int NC>
 struct alignas(16) FqBars {
-    uint64_t full[FQ_STAGES], empty[FQ_STAGES], tfull[FQ_TSTAGES], tempty[FQ_TSTAGES];
-    float da[FQ_DA_SLOTS][FQ_COLS];
+    uint64_t full[FqCfg<NC>::STAGES], empty[FqCfg<NC>::STAGES], tfull[FQ_TSTAGES], tempty[FQ_TSTAGES];
+    float da[FQ_DA_SLOTS][NC];
     uint32_t tmem_base;
     int abort_flag;
 };
 
+// a row's super-block takes the CUDA-core path for its mins: d == 0, or rho m_j could leave the f16 range
+__device__ __forceinline__ bool q_mins_apart(float d, float dmin) { return !(fabsf(dmin) <= FQ_RHO_MAX * d); }
+
 }  // namespace
 
-// Weights of one 128-row block and one super-block -> its A and Am images.  Warp (tt, aj): row (tile tt, lane), 16-byte
-// pieces aj and 4 + aj of the row's 128 nibble bytes.
-__global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q4_K_weights_fast_kernel(const uint8_t *__restrict__ tiles, uint8_t *aimg, int64_t tiles_n, int nb) {
-    pdl_trigger();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int tt = warp & 3, aj = warp >> 2;
-    const int b = blockIdx.x;
-    const int64_t rb = blockIdx.y, tile = rb * 4 + tt;
-    const bool tile_ok = tile < tiles_n;
-    const uint8_t *src = tiles + ((tile_ok ? tile : 0) * (int64_t)nb + b) * 4608 + lane * 16;
-    uint4 hd = make_uint4(0, 0, 0, 0), wq[2] = {hd, hd};
-    if (tile_ok) {
-        // the weights do not depend on the previous kernel
-        hd = *(const uint4 *)(src);
-        wq[0] = ld_stream16(src + 512 + aj * 512);
-        wq[1] = ld_stream16(src + 512 + (4 + aj) * 512);
-    }
-    pdl_wait();   // the previous mat-mul may still be reading the images
-    const int prow = tt * 32 + lane;
-    uint8_t *img = aimg + (rb * nb + b) * (int64_t)FQ_AIMG;
-    if (aj == 0) {
-        const uint32_t mn0 = hd.z & 0x3f3f3f3fu, mn1 = ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4);
-        uint32_t mins[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++) mins[j] = q_h2_bits(q_small2(((j < 4 ? mn0 : mn1) >> (8 * (j & 3))) & 0xffu));
-        uint8_t *am = img + FQ_A_BYTES + (prow >> 3) * 256 + (prow & 7) * 16;
-        q_stg128(am, mins[0], mins[1], mins[2], mins[3]);
-        q_stg128(am + 128, mins[4], mins[5], mins[6], mins[7]);
-    }
-    // piece within the pair pp = aj % 2: chunks 4 pp + {0, 1 low | 2, 3 high}, each at (chunk ^ row % 8)
-    const int sw = prow & 7;
-    uint8_t *rowp = img + prow * 128;
-#pragma unroll
-    for (int hs = 0; hs < 2; hs++) {
-        // piece c = 4 hs + aj of the row: pair g = c / 2 (sub-blocks 2 g, 2 g + 1)
-        const int g = 2 * hs + (aj >> 1);
-        const uint4 w = wq[hs];
-        const uint32_t scw = g < 2 ? (hd.y & 0x3f3f3f3fu) : ((hd.w & 0x0f0f0f0fu) | (((hd.y >> 6) & 0x03030303u) << 4));
-        const uint32_t s_lo = (scw >> (16 * (g & 1))) & 0xffu, s_hi = (scw >> (16 * (g & 1) + 8)) & 0xffu;
-        const __half2 sl = q_small2(s_lo), sh = q_small2(s_hi);
-        // -1024 s <= 64512 in magnitude: a multiple of 1024 below 65504, exact in f16
-        const __half2 cl = __hmul2(sl, __float2half2_rn(-1024.0f)), ch = __hmul2(sh, __float2half2_rn(-64.0f));
-        const __half2 sh16 = __hmul2(sh, __float2half2_rn(0.0625f));
-        const uint32_t x8 = w.x >> 8, y8 = w.y >> 8, z8 = w.z >> 8, w8 = w.w >> 8;   // bytes 1 and 3
-        uint8_t *dstp = rowp + g * FQ_PAIR_BYTES;
-        const int c0 = 4 * (aj & 1);
-        q_stg128(dstp + (((c0 + 0) ^ sw) << 4), q_scaled_lo(w.x, sl, cl), q_scaled_lo(x8, sl, cl), q_scaled_lo(w.y, sl, cl), q_scaled_lo(y8, sl, cl));
-        q_stg128(dstp + (((c0 + 1) ^ sw) << 4), q_scaled_lo(w.z, sl, cl), q_scaled_lo(z8, sl, cl), q_scaled_lo(w.w, sl, cl), q_scaled_lo(w8, sl, cl));
-        q_stg128(dstp + (((c0 + 2) ^ sw) << 4), q_scaled_hi(w.x, sh16, ch), q_scaled_hi(x8, sh16, ch), q_scaled_hi(w.y, sh16, ch), q_scaled_hi(y8, sh16, ch));
-        q_stg128(dstp + (((c0 + 3) ^ sw) << 4), q_scaled_hi(w.z, sh16, ch), q_scaled_hi(z8, sh16, ch), q_scaled_hi(w.w, sh16, ch), q_scaled_hi(w8, sh16, ch));
-    }
-}
-
-// Q8_K activations of one 128-row block and one super-block -> its B and Bm images and the scales.
+// Q8_K activations of one block of NC rows and one super-block -> its B and Bm images and the scales.
+template <int NC>
 __global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q8_K_acts_fast_kernel(ActView acts, uint8_t *bimg, int64_t m, int nb) {
+    using C = FqCfg<NC>;
     pdl_trigger();
-    pdl_wait();   // the activations come from the previous kernel
+    pdl_wait();   // the activations come from the previous kernel, and the previous mat-mul may still be reading the images
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
     const int b = blockIdx.x;
     const int64_t cb = blockIdx.y, K = acts.k;
-    uint8_t *img = bimg + (cb * nb + b) * (int64_t)FQ_BIMG;
-    // a warp reads 64 contiguous bytes (one pair) of 8 activation rows
-    const int bc = warp * 8 + (lane & 7), r = lane >> 3;
-    const int64_t col = cb * FQ_COLS + bc;
-    // piece r of the pair: (low p0, low p1, high p0, high p1) -> chunks 4 p + 2 hi + {0, 1}
-    const int c0 = 4 * (r & 1) + 2 * (r >> 1), sw = bc & 7;
-    uint8_t *rowp = img + bc * 128;
+    uint8_t *img = bimg + (cb * nb + b) * (int64_t)C::BIMG;
+    // a warp reads 64 contiguous bytes (one pair) of 8 activation rows; piece r of the pair: (low p0, low p1, high p0,
+    // high p1) -> chunks 4 p + 2 hi + {0, 1}
+    const int r = lane >> 3, c0 = 4 * (r & 1) + 2 * (r >> 1);
 #pragma unroll
-    for (int g = 0; g < 4; g++) {
-        uint4 y = make_uint4(0, 0, 0, 0);
-        if (col < m) y = *(const uint4 *)(acts.qs + col * K + (int64_t)b * 256 + g * 64 + r * 16);
-        // a row past the end holds zeros: 0x80 after the flip, 128 - 128 = 0
-        const uint32_t u0 = y.x ^ 0x80808080u, u1 = y.y ^ 0x80808080u, u2 = y.z ^ 0x80808080u, u3 = y.w ^ 0x80808080u;
-        uint8_t *dstp = rowp + g * FQ_PAIR_BYTES;
-        q_stg128(dstp + (((c0 + 0) ^ sw) << 4), q_signed(u0, 0), q_signed(u0, 8), q_signed(u1, 0), q_signed(u1, 8));
-        q_stg128(dstp + (((c0 + 1) ^ sw) << 4), q_signed(u2, 0), q_signed(u2, 8), q_signed(u3, 0), q_signed(u3, 8));
+    for (int rr = 0; rr < NC / 128; rr++) {
+        const int bc = rr * 128 + warp * 8 + (lane & 7), sw = bc & 7;
+        const int64_t col = cb * NC + bc;
+        uint8_t *rowp = img + bc * 128;
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            uint4 y = make_uint4(0, 0, 0, 0);
+            if (col < m) y = *(const uint4 *)(acts.qs + col * K + (int64_t)b * 256 + g * 64 + r * 16);
+            // a row past the end holds zeros: 0x80 after the flip, 128 - 128 = 0
+            const uint32_t u0 = y.x ^ 0x80808080u, u1 = y.y ^ 0x80808080u, u2 = y.z ^ 0x80808080u, u3 = y.w ^ 0x80808080u;
+            uint8_t *dstp = rowp + g * C::B_STEP;
+            q_stg128(dstp + (((c0 + 0) ^ sw) << 4), q_signed(u0, 0), q_signed(u0, 8), q_signed(u1, 0), q_signed(u1, 8));
+            q_stg128(dstp + (((c0 + 1) ^ sw) << 4), q_signed(u2, 0), q_signed(u2, 8), q_signed(u3, 0), q_signed(u3, 8));
+        }
     }
-    if (tid < 2 * FQ_COLS) {
-        // sums: thread (row tid / 2, half tid % 2): eight 16-element sums -> one core-matrix row
-        const int scol_i = tid >> 1, kc = tid & 1;
-        const int64_t scol = cb * FQ_COLS + scol_i;
+    for (int i = tid; i < 2 * NC; i += FQ_EXPAND_THREADS) {
+        // sums: (row i / 2, half i % 2): eight 16-element sums -> one core-matrix row, written twice (K slots 0..15, 16..31)
+        const int scol_i = i >> 1, kc = i & 1;
+        const int64_t scol = cb * NC + scol_i;
         short4 b0 = make_short4(0, 0, 0, 0), b1 = b0;
         if (scol < m) {
             const short4 *bp = (const short4 *)(acts.bsums + scol * (K / 16) + (int64_t)b * 16 + 8 * kc);
             b0 = bp[0];
             b1 = bp[1];
         }
-        uint8_t *bm = img + FQ_A_BYTES + (scol_i >> 3) * 256 + (scol_i & 7) * 16 + kc * 128;
-        q_stg128(bm, q_h2_bits(__halves2half2(__short2half_rn(b0.x), __short2half_rn(b0.y))), q_h2_bits(__halves2half2(__short2half_rn(b0.z), __short2half_rn(b0.w))),
-                 q_h2_bits(__halves2half2(__short2half_rn(b1.x), __short2half_rn(b1.y))), q_h2_bits(__halves2half2(__short2half_rn(b1.z), __short2half_rn(b1.w))));
-    } else if (tid < 3 * FQ_COLS) {
-        const int dcol_i = tid - 2 * FQ_COLS;
-        const int64_t dcol = cb * FQ_COLS + dcol_i;
-        reinterpret_cast<float *>(img + FQ_A_BYTES + FQ_M_BYTES)[dcol_i] = dcol < m ? acts.d[dcol * nb + b] : 0.0f;
+        uint8_t *bm = img + 4 * C::B_STEP + (scol_i >> 3) * 512 + (scol_i & 7) * 16 + kc * 128;
+        const uint32_t v0 = q_h2_bits(__halves2half2(__short2half_rn(b0.x), __short2half_rn(b0.y))), v1 = q_h2_bits(__halves2half2(__short2half_rn(b0.z), __short2half_rn(b0.w)));
+        const uint32_t v2 = q_h2_bits(__halves2half2(__short2half_rn(b1.x), __short2half_rn(b1.y))), v3 = q_h2_bits(__halves2half2(__short2half_rn(b1.z), __short2half_rn(b1.w)));
+        q_stg128(bm, v0, v1, v2, v3);
+        q_stg128(bm + 256, v0, v1, v2, v3);
+    }
+    for (int i = tid; i < NC; i += FQ_EXPAND_THREADS) {
+        const int64_t dcol = cb * NC + i;
+        reinterpret_cast<float *>(img + 4 * C::B_STEP + C::BM_BYTES)[i] = dcol < m ? acts.d[dcol * nb + b] : 0.0f;
     }
 }
 
-// FUSED: no weight images; warps 12..19 unpack the 128 rows' nibbles of every step straight into the stage (and the mins
-// into their slot), so the weights cross the L2 as 0.5625 bytes each instead of 2
-template <bool FUSED>
+template <int NC>
 __global__ void __launch_bounds__(FQ_THREADS, 1)
-gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *__restrict__ aimg, const uint8_t *__restrict__ bimg, float *dst,
-                              int64_t lddst, int64_t n, int nb, int64_t m, int *err, int profile) {
+gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *__restrict__ bimg, ActView acts, float *dst, int64_t lddst, int64_t n, int nb,
+                              int64_t m, int *err, int profile) {
+    using C = FqCfg<NC>;
+    constexpr int S = C::STAGES, CPT = NC / 2;   // columns per epilogue thread
     extern __shared__ uint8_t fq_raw[];
-    __shared__ FqBars bars;
+    __shared__ FqBars<NC> bars;
     pdl_trigger();
     const uint32_t smem = (q_smem_u32(fq_raw) + 1023u) & ~1023u;
-    const uint32_t mslots = smem + (uint32_t)(FQ_STAGES * FQ_STAGE_BYTES);
+    const uint32_t mslot = smem + (uint32_t)(S * C::STAGE);   // Am | Bm of the super-block whose MMAs run
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t rb = blockIdx.y, cb = blockIdx.x;
     const int64_t tile0 = rb * (FQ_ROWS / TILE_ROWS), tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
-    const int64_t col0 = cb * FQ_COLS;
-    const int np = 2 * nb;   // pipeline steps: half super-blocks
+    const int64_t col0 = cb * NC;
+    const int np = 4 * nb;   // pipeline steps: sub-block pairs
     volatile int *abort_flag = &bars.abort_flag;
     const bool prof = profile && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0;
     long long t_prev = clock64();
     const long long t_start = t_prev;
-    unsigned long long pacc[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};   // kept in registers, written once at the end
+    unsigned long long pacc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};   // kept in registers, written once at the end
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < FQ_STAGES; i++) {
-            q_mbar_init(q_smem_u32(&bars.full[i]), FUSED ? 1 + FQ_PROD_WARPS : 1);   // the loader's arrive + the bytes it announced (+ the producer warps)
-            q_mbar_init(q_smem_u32(&bars.empty[i]), 1);   // the MMA thread's commit
+        for (int i = 0; i < S; i++) {
+            q_mbar_init(q_smem_u32(&bars.full[i]), 1 + FQ_PROD_WARPS);   // the loader's arrive + the bytes it announced + the producer warps
+            q_mbar_init(q_smem_u32(&bars.empty[i]), 1);                  // the MMA thread's commit
         }
         for (int i = 0; i < FQ_TSTAGES; i++) {
             q_mbar_init(q_smem_u32(&bars.tfull[i]), 1);
@@ -278,8 +257,8 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == FQ_MMA_WARP) {
-        // all 512 columns: the CTA's shared memory already keeps a second CTA off this SM
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(q_smem_u32(&bars.tmem_base)), "r"(512) : "memory");
+        // both tensor-memory stages; the CTA's shared memory (or, with 128 columns, its registers) keeps a second CTA off this SM
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(q_smem_u32(&bars.tmem_base)), "r"(FQ_TSTAGES * NC) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -289,36 +268,37 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
 
     if (warp < FQ_EPI_WARPS) {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FQ_REGS_EPI));
-        pdl_wait();   // the images are the previous kernels' output, and the previous mat-mul may still be reading dst's producers
+        pdl_wait();   // the previous kernels in the stream may still read dst
         const int q = warp & 3, h = warp >> 2;
         const bool row_ok = tile0 + q < tiles_n;
-        const bool any_col = col0 + 64 * h < m;
+        const bool any_col = col0 + CPT * h < m;
         // (d, dmin) of this thread's row, one word per super-block, fetched one super-block ahead
         const uint8_t *hdr = tiles + (row_ok ? tile0 + q : 0) * (int64_t)nb * 4608 + lane * 16;
         uint32_t dd_next = row_ok ? *(const uint32_t *)(hdr) : 0u;
-        float acc[64];
+        float2 acc[CPT / 2];
 #pragma unroll
-        for (int c = 0; c < 64; c++) acc[c] = 0.0f;
-        const uint32_t trow0 = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(64 * h);
+        for (int c = 0; c < CPT / 2; c++) acc[c] = make_float2(0.0f, 0.0f);
+        bool any_apart = false;
+        const uint32_t trow0 = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(CPT * h);
         for (int b = 0; b < nb; b++) {
             const int t = b % FQ_TSTAGES;
-            const float dw = f16_bits_to_f32((uint16_t)(dd_next & 0xffffu)), dmw = -f16_bits_to_f32((uint16_t)(dd_next >> 16));
+            const float dw = f16_bits_to_f32((uint16_t)(dd_next & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(dd_next >> 16));
+            any_apart |= row_ok && dmw != 0.0f && q_mins_apart(dw, dmw);
             if (b + 1 < nb && row_ok) dd_next = *(const uint32_t *)(hdr + (int64_t)(b + 1) * 4608);
             if (warp == 0) FQ_MARK(1);
             if (!__all_sync(0xffffffffu, q_mbar_wait(q_smem_u32(&bars.tfull[t]), (uint32_t)(b / FQ_TSTAGES) & 1u, abort_flag))) break;
             if (warp == 0) FQ_MARK(0);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float4 *das = reinterpret_cast<const float4 *>(bars.da[b % FQ_DA_SLOTS] + 64 * h);
-            const uint32_t trow = trow0 + (uint32_t)(t * 256);
-            // two rounds of 32 columns: one tensor-memory round trip each for ig and mg, then per column
-            //   acc += d_x (d ig - dmin mg)
-            uint32_t ig[32], mg[32];
+            const float4 *das = reinterpret_cast<const float4 *>(bars.da[b % FQ_DA_SLOTS] + CPT * h);
+            const uint32_t trow = trow0 + (uint32_t)(t * NC);
+            const float2 dw2 = make_float2(dw, dw), zero2 = make_float2(0.0f, 0.0f);
+            // rounds of 32 columns, one tensor-memory round trip each: acc += (d_x d) v, two columns per instruction
+            uint32_t v[32];
 #pragma unroll
-            for (int r = 0; r < 2; r++) {
-                q_tmem_ld32(ig, trow + (uint32_t)(32 * r));
-                q_tmem_ld32(mg, trow + (uint32_t)(128 + 32 * r));
+            for (int r = 0; r < CPT / 32; r++) {
+                q_tmem_ld32(v, trow + (uint32_t)(32 * r));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (r == 1) {
+                if (r == CPT / 32 - 1) {
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) q_mbar_arrive(q_smem_u32(&bars.tempty[t]));
@@ -327,12 +307,9 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
 #pragma unroll
                     for (int c4 = 0; c4 < 8; c4++) {
                         const float4 dq = das[8 * r + c4];
-                        const float dxs[4] = {dq.x, dq.y, dq.z, dq.w};
-#pragma unroll
-                        for (int c = 0; c < 4; c++) {
-                            const float tsum = fmaf(__uint_as_float(mg[4 * c4 + c]), dmw, __uint_as_float(ig[4 * c4 + c]) * dw);
-                            acc[32 * r + 4 * c4 + c] = fmaf(tsum, dxs[c], acc[32 * r + 4 * c4 + c]);
-                        }
+                        const float2 s0 = q_fma2(make_float2(dq.x, dq.y), dw2, zero2), s1 = q_fma2(make_float2(dq.z, dq.w), dw2, zero2);
+                        acc[16 * r + 2 * c4] = q_fma2(make_float2(__uint_as_float(v[4 * c4]), __uint_as_float(v[4 * c4 + 1])), s0, acc[16 * r + 2 * c4]);
+                        acc[16 * r + 2 * c4 + 1] = q_fma2(make_float2(__uint_as_float(v[4 * c4 + 2]), __uint_as_float(v[4 * c4 + 3])), s1, acc[16 * r + 2 * c4 + 1]);
                     }
                 }
             }
@@ -340,157 +317,183 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
         const int64_t row = (tile0 + q) * TILE_ROWS + lane;
         if (row_ok && row < n && !*abort_flag) {
 #pragma unroll
-            for (int c = 0; c < 64; c++) {
-                const int64_t col = col0 + 64 * h + c;
-                if (col < m) dst[col * lddst + row] = acc[c];
+            for (int c = 0; c < CPT; c++) {
+                const int64_t col = col0 + CPT * h + c;
+                if (col < m) dst[col * lddst + row] = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
+            }
+            if (any_apart) {
+                // the super-blocks whose mins the tensor core did not take: out -= d_x dmin sum_j m_j (bsum_2j + bsum_2j+1)
+                for (int b = 0; b < nb; b++) {
+                    const uint4 hd = *(const uint4 *)(hdr + (int64_t)b * 4608);
+                    const float dw = f16_bits_to_f32((uint16_t)(hd.x & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(hd.x >> 16));
+                    if (dmw == 0.0f || !q_mins_apart(dw, dmw)) continue;
+                    const uint32_t mn0 = hd.z & 0x3f3f3f3fu, mn1 = ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4);
+                    for (int c = 0; c < CPT; c++) {
+                        const int64_t col = col0 + CPT * h + c;
+                        if (col >= m) break;
+                        const int16_t *bs = acts.bsums + col * (acts.k / 16) + (int64_t)b * 16;
+                        int mg = 0;
+                        for (int j = 0; j < 8; j++) mg += (int)(((j < 4 ? mn0 : mn1) >> (8 * (j & 3))) & 0xffu) * ((int)bs[2 * j] + (int)bs[2 * j + 1]);
+                        dst[col * lddst + row] -= acts.d[col * nb + b] * dmw * (float)mg;
+                    }
+                }
             }
         }
     } else if (warp >= FQ_PROD_WARP0) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FQ_REGS_PROD));
-        if constexpr (FUSED) {
-            // thread = (row (tile tt, lane), pair column hh of the step): per step the two 16-byte pieces 4 hs + 2 hh, + 1 of the
-            // row's 128 nibble bytes, loaded one step ahead (the weights do not depend on the previous kernel)
-            const int pw = warp - FQ_PROD_WARP0, tt = pw & 3, hh = pw >> 2, prow = tt * 32 + lane, sw = prow & 7;
-            const bool tile_ok = tile0 + tt < tiles_n;
-            const uint8_t *src = tiles + (tile_ok ? tile0 + tt : 0) * (int64_t)nb * 4608 + lane * 16;
-            uint8_t *stage0 = fq_raw + (smem - q_smem_u32(fq_raw)) + hh * FQ_PAIR_BYTES + prow * 128;
-            uint8_t *am0 = fq_raw + (mslots - q_smem_u32(fq_raw)) + (prow >> 3) * 256 + (prow & 7) * 16;
-            uint4 hd = make_uint4(0, 0, 0, 0), hd_next = hd, w[2], wn[2];
-            wn[0] = wn[1] = hd;
-            if (tile_ok) {
-                hd_next = *(const uint4 *)src;
+        // thread = row (tile tt, lane): per step the two 16-byte pieces 2 g, 2 g + 1 of its 128 nibble bytes, loaded three steps
+        // ahead into register set (step + 3) % 4 (the weights do not depend on the previous kernel)
+        const int tt = warp - FQ_PROD_WARP0, prow = tt * 32 + lane, sw = prow & 7;
+        const bool tile_ok = tile0 + tt < tiles_n;
+        const uint8_t *src = tiles + (tile_ok ? tile0 + tt : 0) * (int64_t)nb * 4608 + lane * 16;
+        uint8_t *stage0 = fq_raw + (smem - q_smem_u32(fq_raw)) + prow * 128;
+        uint8_t *am = fq_raw + (mslot - q_smem_u32(fq_raw)) + (prow >> 3) * 512 + (prow & 7) * 16;
+        const uint4 zero4 = make_uint4(0, 0, 0, 0);
+        uint4 hd = zero4, hd_next = zero4, w[4][2];
 #pragma unroll
-                for (int i = 0; i < 2; i++) wn[i] = ld_stream16(src + 512 + (2 * hh + i) * 512);
+        for (int i = 0; i < 4; i++) w[i][0] = w[i][1] = zero4;
+        if (tile_ok) {
+            hd_next = *(const uint4 *)src;
+#pragma unroll
+            for (int i = 0; i < 3; i++) {
+                if (i < np) {
+                    w[i][0] = ld_stream16(src + 512 + (2 * i) * 512);
+                    w[i][1] = ld_stream16(src + 512 + (2 * i + 1) * 512);
+                }
             }
-            for (int p = 0; p < np; p++) {
-                const int s = p % FQ_STAGES, b = p >> 1, hs = p & 1;
-                w[0] = wn[0];
-                w[1] = wn[1];
-                if (hs == 0) hd = hd_next;
-                if (p + 1 < np && tile_ok) {
-                    const uint8_t *nx = src + (int64_t)((p + 1) >> 1) * 4608;
-                    if (hs == 1) hd_next = *(const uint4 *)nx;
+        }
+        bool ok = true;
+        for (int b = 0; b < nb && ok; b++) {
+            hd = hd_next;
+            if (b + 1 < nb && tile_ok) hd_next = *(const uint4 *)(src + (int64_t)(b + 1) * 4608);
 #pragma unroll
-                    for (int i = 0; i < 2; i++) wn[i] = ld_stream16(nx + 512 + (4 * (hs ^ 1) + 2 * hh + i) * 512);
+            for (int g = 0; g < 4; g++) {
+                const int p = 4 * b + g, s = p % S;
+                if (p + 3 < np && tile_ok) {   // set (g + 3) % 4 was consumed in the previous step
+                    const uint8_t *nx = src + (int64_t)((p + 3) >> 2) * 4608 + 512 + (2 * ((g + 3) & 3)) * 512;
+                    w[(g + 3) & 3][0] = ld_stream16(nx);
+                    w[(g + 3) & 3][1] = ld_stream16(nx + 512);
                 }
                 if (warp == FQ_PROD_WARP0) FQ_MARK(8);
-                if (!__all_sync(0xffffffffu, q_mbar_wait(q_smem_u32(&bars.empty[s]), ((uint32_t)(p / FQ_STAGES) & 1u) ^ 1u, abort_flag))) break;
-                if (warp == FQ_PROD_WARP0) FQ_MARK(7);
-                if (profile == 2) {
-                    __syncwarp();
-                    if (lane == 0) q_mbar_arrive(q_smem_u32(&bars.full[s]));
-                    continue;
+                if (!__all_sync(0xffffffffu, q_mbar_wait(q_smem_u32(&bars.empty[s]), ((uint32_t)(p / S) & 1u) ^ 1u, abort_flag))) {
+                    ok = false;
+                    break;
                 }
-                if (hs == 0 && hh == 0) {
-                    // the mins slot of super-block b - 2 is free: see the loader
+                if (warp == FQ_PROD_WARP0) FQ_MARK(7);
+                if (g == 0) {
+                    // the mins slot is free: the stage this step reuses was released by MMAs issued after those of the previous
+                    // super-block's first step.  -rho m_j as high part + remainder; all zero where the drain takes the mins
+                    const float dw = f16_bits_to_f32((uint16_t)(hd.x & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(hd.x >> 16));
+                    const float nrho = (dmw == 0.0f || q_mins_apart(dw, dmw)) ? 0.0f : -(dmw / dw);
                     const uint32_t mn0 = hd.z & 0x3f3f3f3fu, mn1 = ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4);
-                    uint32_t mins[8];
+                    uint32_t hi[8], lo[8];
 #pragma unroll
-                    for (int j = 0; j < 8; j++) mins[j] = q_h2_bits(q_small2(((j < 4 ? mn0 : mn1) >> (8 * (j & 3))) & 0xffu));
-                    uint8_t *am = am0 + (b % FQ_MSLOTS) * 2 * FQ_M_BYTES;
-                    q_stg128(am, mins[0], mins[1], mins[2], mins[3]);
-                    q_stg128(am + 128, mins[4], mins[5], mins[6], mins[7]);
+                    for (int j = 0; j < 8; j++) {
+                        const float v = nrho * (float)(((j < 4 ? mn0 : mn1) >> (8 * (j & 3))) & 0xffu);
+                        const __half vh = __float2half_rn(v);
+                        const __half vl = __float2half_rn(v - __half2float(vh));
+                        hi[j] = q_h2_bits(__halves2half2(vh, vh));
+                        lo[j] = q_h2_bits(__halves2half2(vl, vl));
+                    }
+                    q_stg128(am, hi[0], hi[1], hi[2], hi[3]);
+                    q_stg128(am + 128, hi[4], hi[5], hi[6], hi[7]);
+                    q_stg128(am + 256, lo[0], lo[1], lo[2], lo[3]);
+                    q_stg128(am + 384, lo[4], lo[5], lo[6], lo[7]);
                 }
                 {
-                    // pair g = 2 hs + hh (sub-blocks 2 g, 2 g + 1): the step's pair column hh
-                    const int g = 2 * hs + hh;
+                    // pair g: sub-blocks 2 g, 2 g + 1
                     const uint32_t scw = g < 2 ? (hd.y & 0x3f3f3f3fu) : ((hd.w & 0x0f0f0f0fu) | (((hd.y >> 6) & 0x03030303u) << 4));
                     const uint32_t s_lo = (scw >> (16 * (g & 1))) & 0xffu, s_hi = (scw >> (16 * (g & 1) + 8)) & 0xffu;
                     const __half2 sl = q_small2(s_lo), sh = q_small2(s_hi);
+                    // -1024 s <= 64512 in magnitude: a multiple of 1024 below 65504, exact in f16
                     const __half2 cl = __hmul2(sl, __float2half2_rn(-1024.0f)), ch = __hmul2(sh, __float2half2_rn(-64.0f));
                     const __half2 sh16 = __hmul2(sh, __float2half2_rn(0.0625f));
-                    uint8_t *dstp = stage0 + s * FQ_STAGE_BYTES;
+                    uint8_t *dstp = stage0 + s * C::STAGE;
 #pragma unroll
                     for (int i = 0; i < 2; i++) {
-                        const uint4 v = w[i];
-                        const uint32_t x8 = v.x >> 8, y8 = v.y >> 8, z8 = v.z >> 8, w8 = v.w >> 8;   // bytes 1 and 3
+                        const uint4 x = w[g][i];
+                        const uint32_t x8 = x.x >> 8, y8 = x.y >> 8, z8 = x.z >> 8, w8 = x.w >> 8;   // bytes 1 and 3
                         const int c0 = 4 * i;
-                        q_stg128(dstp + (((c0 + 0) ^ sw) << 4), q_scaled_lo(v.x, sl, cl), q_scaled_lo(x8, sl, cl), q_scaled_lo(v.y, sl, cl), q_scaled_lo(y8, sl, cl));
-                        q_stg128(dstp + (((c0 + 1) ^ sw) << 4), q_scaled_lo(v.z, sl, cl), q_scaled_lo(z8, sl, cl), q_scaled_lo(v.w, sl, cl), q_scaled_lo(w8, sl, cl));
-                        q_stg128(dstp + (((c0 + 2) ^ sw) << 4), q_scaled_hi(v.x, sh16, ch), q_scaled_hi(x8, sh16, ch), q_scaled_hi(v.y, sh16, ch), q_scaled_hi(y8, sh16, ch));
-                        q_stg128(dstp + (((c0 + 3) ^ sw) << 4), q_scaled_hi(v.z, sh16, ch), q_scaled_hi(z8, sh16, ch), q_scaled_hi(v.w, sh16, ch), q_scaled_hi(w8, sh16, ch));
+                        q_stg128(dstp + (((c0 + 0) ^ sw) << 4), q_scaled_lo(x.x, sl, cl), q_scaled_lo(x8, sl, cl), q_scaled_lo(x.y, sl, cl), q_scaled_lo(y8, sl, cl));
+                        q_stg128(dstp + (((c0 + 1) ^ sw) << 4), q_scaled_lo(x.z, sl, cl), q_scaled_lo(z8, sl, cl), q_scaled_lo(x.w, sl, cl), q_scaled_lo(w8, sl, cl));
+                        q_stg128(dstp + (((c0 + 2) ^ sw) << 4), q_scaled_hi(x.x, sh16, ch), q_scaled_hi(x8, sh16, ch), q_scaled_hi(x.y, sh16, ch), q_scaled_hi(y8, sh16, ch));
+                        q_stg128(dstp + (((c0 + 3) ^ sw) << 4), q_scaled_hi(x.z, sh16, ch), q_scaled_hi(z8, sh16, ch), q_scaled_hi(x.w, sh16, ch), q_scaled_hi(w8, sh16, ch));
                     }
                 }
+                if (warp == FQ_PROD_WARP0) FQ_MARK(9);
                 // the stores (generic proxy) before the tensor core's reads (async proxy), then the warp's arrival
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) q_mbar_arrive(q_smem_u32(&bars.full[s]));
+                if (warp == FQ_PROD_WARP0) FQ_MARK(10);
             }
         }
     } else {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FQ_REGS_CTL));
-        pdl_wait();
-    if (warp == FQ_MMA_WARP) {
-        if (lane == 0) {
-            for (int p = 0; p < np; p++) {
-                const int s = p % FQ_STAGES, b = p >> 1, hs = p & 1, t = b % FQ_TSTAGES;
-                FQ_MARK(4);
-                if (!q_mbar_wait(q_smem_u32(&bars.full[s]), (uint32_t)(p / FQ_STAGES) & 1u, abort_flag)) break;
-                FQ_MARK(2);
-                if (hs == 0 && !q_mbar_wait(q_smem_u32(&bars.tempty[t]), ((uint32_t)(b / FQ_TSTAGES) & 1u) ^ 1u, abort_flag)) break;
-                FQ_MARK(3);
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_base = smem + (uint32_t)(s * FQ_STAGE_BYTES), b_base = a_base + FQ_HALF;
-                const uint32_t d_ig = tmem + (uint32_t)(t * 256);
-                if (hs == 0) {
-                    const uint32_t am = mslots + (uint32_t)((b % FQ_MSLOTS) * 2 * FQ_M_BYTES);
-                    q_mma(d_ig + 128, q_desc_plain(am, 128, 256), q_desc_plain(am + FQ_M_BYTES, 128, 256), 0);
-                }
-                const uint64_t ad = q_desc_sw128(a_base), bd = q_desc_sw128(b_base);
+        pdl_wait();   // the images are the previous kernel's output
+        if (warp == FQ_MMA_WARP) {
+            if (lane == 0) {
+                for (int p = 0; p < np; p++) {
+                    const int s = p % S, b = p >> 2, g = p & 3, t = b % FQ_TSTAGES;
+                    FQ_MARK(4);
+                    if (!q_mbar_wait(q_smem_u32(&bars.full[s]), (uint32_t)(p / S) & 1u, abort_flag)) break;
+                    FQ_MARK(2);
+                    if (g == 0 && !q_mbar_wait(q_smem_u32(&bars.tempty[t]), ((uint32_t)(b / FQ_TSTAGES) & 1u) ^ 1u, abort_flag)) break;
+                    FQ_MARK(3);
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_base = smem + (uint32_t)(s * C::STAGE), b_base = a_base + FQ_A_STEP;
+                    const uint32_t d_acc = tmem + (uint32_t)(t * NC);
+                    if (g == 0) {
+                        // the mins first (they clear the accumulator): K = 32 as two MMAs, core-matrix columns 0, 1 and 2, 3
+                        const uint64_t amd = q_desc_plain(mslot, 128, 512), bmd = q_desc_plain(mslot + FQ_AM_BYTES, 128, 512);
+                        q_mma(d_acc, amd, bmd, C::IDESC, 0);
+                        q_mma(d_acc, amd + (256 >> 4), bmd + (256 >> 4), C::IDESC, 1);
+                    }
+                    const uint64_t ad = q_desc_sw128(a_base), bd = q_desc_sw128(b_base);
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    // pair column i / 4 (16384 bytes on), K = 16 step i % 4 (32 bytes on); descriptor addresses count 16 bytes
-                    const uint64_t off = (uint64_t)((i >> 2) * (FQ_PAIR_BYTES >> 4) + (i & 3) * 2);
-                    q_mma(d_ig, ad + off, bd + off, (hs | i) != 0);
+                    for (int i = 0; i < 4; i++) q_mma(d_acc, ad + 2 * i, bd + 2 * i, C::IDESC, 1);   // K = 16 step i: 32 bytes on
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(q_smem_u32(&bars.empty[s])) : "memory");
+                    if (g == 3)
+                        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(q_smem_u32(&bars.tfull[t])) : "memory");
                 }
-                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(q_smem_u32(&bars.empty[s])) : "memory");
-                if (hs == 1)
-                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(q_smem_u32(&bars.tfull[t])) : "memory");
             }
+        } else if (warp == FQ_LOAD_WARP && lane == 0) {
+            const uint8_t *bsrc = bimg + cb * nb * (int64_t)C::BIMG;
+            int issued = -1;
+            for (int p = 0; p < np; p++) {
+                const int s = p % S, b = p >> 2, g = p & 3;
+                FQ_MARK(6);
+                if (!q_mbar_wait(q_smem_u32(&bars.empty[s]), ((uint32_t)(p / S) & 1u) ^ 1u, abort_flag)) break;
+                FQ_MARK(5);
+                const uint32_t bar = q_smem_u32(&bars.full[s]), stage = smem + (uint32_t)(s * C::STAGE);
+                const uint8_t *bb = bsrc + (int64_t)b * C::BIMG;
+                q_mbar_expect(bar, (uint32_t)(C::B_STEP + (g == 0 ? C::BM_BYTES + C::DA_BYTES : 0)));
+                q_bulk_load(stage + FQ_A_STEP, bb + g * C::B_STEP, C::B_STEP, bar);
+                if (g == 0) {
+                    // the mins slot: with at most four stages the stage this step reuses belonged to a step of the previous
+                    // super-block no earlier than its first, so that super-block's mins MMAs are done; the scale slot of
+                    // super-block b - 4: its drain ended before the MMAs of b - 2 began
+                    q_bulk_load(mslot + FQ_AM_BYTES, bb + 4 * C::B_STEP, C::BM_BYTES, bar);
+                    q_bulk_load(q_smem_u32(bars.da[b % FQ_DA_SLOTS]), bb + 4 * C::B_STEP + C::BM_BYTES, C::DA_BYTES, bar);
+                }
+                issued = p;
+            }
+            // a CTA that gives up still waits (bounded) for the copies it has in flight
+            if (*abort_flag && issued >= 0) q_mbar_wait(q_smem_u32(&bars.full[issued % S]), (uint32_t)(issued / S) & 1u, abort_flag);
         }
-    } else if (warp == FQ_LOAD_WARP && lane == 0) {
-        const uint8_t *asrc = aimg + rb * nb * (int64_t)FQ_AIMG, *bsrc = bimg + cb * nb * (int64_t)FQ_BIMG;
-        int issued = -1;
-        for (int p = 0; p < np; p++) {
-            const int s = p % FQ_STAGES, b = p >> 1, hs = p & 1;
-            FQ_MARK(6);
-            if (!q_mbar_wait(q_smem_u32(&bars.empty[s]), ((uint32_t)(p / FQ_STAGES) & 1u) ^ 1u, abort_flag)) break;
-            FQ_MARK(5);
-            const uint32_t bar = q_smem_u32(&bars.full[s]), stage = smem + (uint32_t)(s * FQ_STAGE_BYTES);
-            const uint8_t *ab = FUSED ? nullptr : asrc + (int64_t)b * FQ_AIMG, *bb = bsrc + (int64_t)b * FQ_BIMG;
-            if (profile == 2) {   // measurement only: no operand traffic at all (the outputs are garbage)
-                q_mbar_arrive(bar);
-                continue;
-            }
-            q_mbar_expect(bar, (uint32_t)((FUSED ? FQ_HALF : FQ_STAGE_BYTES) + (hs == 0 ? (FUSED ? 1 : 2) * FQ_M_BYTES + FQ_DA_BYTES : 0)));
-            if (!FUSED) q_bulk_load(stage, ab + hs * FQ_HALF, FQ_HALF, bar);
-            q_bulk_load(stage + FQ_HALF, bb + hs * FQ_HALF, FQ_HALF, bar);
-            if (hs == 0) {
-                // the mins slot of super-block b - 2 and the scale slot of b - 4 are free: the stage this step reuses was
-                // released by MMAs issued after the drain of super-block b - 2 had ended
-                const uint32_t ms = mslots + (uint32_t)((b % FQ_MSLOTS) * 2 * FQ_M_BYTES);
-                if (!FUSED) q_bulk_load(ms, ab + FQ_A_BYTES, FQ_M_BYTES, bar);
-                q_bulk_load(ms + FQ_M_BYTES, bb + FQ_A_BYTES, FQ_M_BYTES, bar);
-                q_bulk_load(q_smem_u32(bars.da[b % FQ_DA_SLOTS]), bb + FQ_A_BYTES + FQ_M_BYTES, FQ_DA_BYTES, bar);
-            }
-            issued = p;
-        }
-        // a CTA that gives up still waits (bounded) for the copies it has in flight
-        if (*abort_flag && issued >= 0) q_mbar_wait(q_smem_u32(&bars.full[issued % FQ_STAGES]), (uint32_t)(issued / FQ_STAGES) & 1u, abort_flag);
-    }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == FQ_MMA_WARP) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(FQ_TSTAGES * NC) : "memory");
     }
     if (threadIdx.x == 0 && bars.abort_flag) atomicExch(err, FQ_ERR_WAIT);
     if (prof) {
 #pragma unroll
-        for (int i = 0; i < 9; i++)
+        for (int i = 0; i < 12; i++)
             if (pacc[i]) atomicAdd(&g_fq_prof[i], pacc[i]);
-        if (threadIdx.x == 0) atomicAdd(&g_fq_prof[9], (unsigned long long)(clock64() - t_start));
+        if (threadIdx.x == 0) atomicAdd(&g_fq_prof[12], (unsigned long long)(clock64() - t_start));
     }
 }
 
@@ -503,48 +506,46 @@ int gemm_fast_profile(unsigned long long *out, int n) {
     return B200_STATUS_SUCCESS;
 }
 
-int launch_gemm_q4_K_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s) {
-    B200_REQUIRE(k % GROUP_K == 0, "gemm: k = %lld must be a multiple of 256", (long long)k);
-    if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
+template <int NC>
+static int launch_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, int *err, int profile, cudaStream_t s) {
+    using C = FqCfg<NC>;
     static bool attr_done[64] = {false};
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
     B200_REQUIRE(dev >= 0 && dev < 64, "gemm: device index %d out of range", dev);
     if (!attr_done[dev]) {
-        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_fast_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, FQ_SMEM_BYTES));
-        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_fast_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, FQ_SMEM_BYTES));
+        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_fast_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         attr_done[dev] = true;
     }
+    const int nb = (int)(k / GROUP_K);
+    const int64_t gx = (m + NC - 1) / NC, gy = (n + FQ_ROWS - 1) / FQ_ROWS;
+    B200_REQUIRE(gx <= 65535 && gy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);
+    void *block = nullptr;
+    int rc = scratch_get_images((size_t)gx * nb * C::BIMG, &block);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    uint8_t *bimg = (uint8_t *)block;
+    rc = launch_pdl(expand_q8_K_acts_fast_kernel<NC>, dim3((unsigned)nb, (unsigned)gx), dim3(FQ_EXPAND_THREADS), (size_t)0, s, acts, bimg, m, nb);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    return launch_pdl(gemm_q4_K_tcgen05_fast_kernel<NC>, dim3((unsigned)gx, (unsigned)gy), dim3(FQ_THREADS), (size_t)C::SMEM, s, tiles, (const uint8_t *)bimg, acts, dst,
+                      lddst, n, nb, m, err, profile);
+}
+
+int launch_gemm_q4_K_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s) {
+    B200_REQUIRE(k % GROUP_K == 0, "gemm: k = %lld must be a multiple of 256", (long long)k);
+    if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
     int *err = nullptr;
     int rc = device_error_word(&err);
     if (rc != B200_STATUS_SUCCESS) return rc;
-    // B200_GEMM_FAST_FUSED=0: the weights through an image of their own (expanded by a kernel before the mat-mul) instead of
-    // the mat-mul's producer warps (read per call)
-    const char *ev = getenv("B200_GEMM_FAST_FUSED");
-    const bool fused = !(ev && ev[0] == '0');
     const char *pv = getenv("B200_GEMM_FAST_PROFILE");
-    const int profile = pv && pv[0] >= '1' && pv[0] <= '2' ? pv[0] - '0' : 0;   // 2: no operand traffic, garbage out (measurement of the MMA / drain rate alone)
-    const int nb = (int)(k / GROUP_K);
-    const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
-    const int64_t gx = (m + FQ_COLS - 1) / FQ_COLS, gy = (n + FQ_ROWS - 1) / FQ_ROWS;
-    B200_REQUIRE(gx <= 65535 && gy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);
-    const size_t a_bytes = fused ? 0 : (size_t)gy * nb * FQ_AIMG, b_bytes = (size_t)gx * nb * FQ_BIMG;
-    void *block = nullptr;
-    rc = scratch_get_images(a_bytes + b_bytes, &block);
-    if (rc != B200_STATUS_SUCCESS) return rc;
-    uint8_t *aimg = (uint8_t *)block, *bimg = aimg + a_bytes;
-    const dim3 ga((unsigned)nb, (unsigned)gy), gb((unsigned)nb, (unsigned)gx), gg((unsigned)gx, (unsigned)gy);
-    if (!fused) {
-        rc = launch_pdl(expand_q4_K_weights_fast_kernel, ga, dim3(FQ_EXPAND_THREADS), (size_t)0, s, tiles, aimg, tiles_n, nb);
-        if (rc != B200_STATUS_SUCCESS) return rc;
-    }
-    rc = launch_pdl(expand_q8_K_acts_fast_kernel, gb, dim3(FQ_EXPAND_THREADS), (size_t)0, s, acts, bimg, m, nb);
-    if (rc != B200_STATUS_SUCCESS) return rc;
-    if (fused)
-        return launch_pdl(gemm_q4_K_tcgen05_fast_kernel<true>, gg, dim3(FQ_THREADS), (size_t)FQ_SMEM_BYTES, s, tiles, (const uint8_t *)aimg,
-                          (const uint8_t *)bimg, dst, lddst, n, nb, m, err, profile);
-    return launch_pdl(gemm_q4_K_tcgen05_fast_kernel<false>, gg, dim3(FQ_THREADS), (size_t)FQ_SMEM_BYTES, s, tiles, (const uint8_t *)aimg, (const uint8_t *)bimg,
-                      dst, lddst, n, nb, m, err, profile);
+    const int profile = pv && pv[0] == '1';
+    // 256 activation rows per CTA run the tensor core at its rate (128 at half of it) but halve the CTA count: taken when
+    // the 256-wide grid still covers most of the SMs; B200_GEMM_FAST_COLS=128 / 256 overrides (read per call)
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    const int64_t gy = (n + FQ_ROWS - 1) / FQ_ROWS;
+    bool wide = m > 128 && gy * ((m + 255) / 256) * 4 >= 3 * (int64_t)sms;
+    if (const char *cv = getenv("B200_GEMM_FAST_COLS")) wide = cv[0] == '2' ? true : cv[0] == '1' ? false : wide;
+    return wide ? launch_fast<256>(n, k, m, tiles, acts, dst, lddst, err, profile, s) : launch_fast<128>(n, k, m, tiles, acts, dst, lddst, err, profile, s);
 }
 
 }  // namespace b200

@@ -28,9 +28,11 @@ def dev():
     return mod
 
 
+@pytest.mark.parametrize("cols", ["128", "256"])
 @pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
-def test_q4_K_fast_mode_within_the_mat_mul_tolerance(dev, shape):
+def test_q4_K_fast_mode_within_the_mat_mul_tolerance(dev, shape, cols, monkeypatch):
     n, k, m = shape
+    monkeypatch.setenv("B200_GEMM_FAST_COLS", cols)
     W = synth.weights(orc.Q4_K, n, k, seed=420, period=512)
     x = synth.activations(m, k, seed=421 + m)
     want, _ = orc.mul_mat(orc.Q4_K, W, x)
@@ -44,11 +46,39 @@ def test_q4_K_fast_mode_within_the_mat_mul_tolerance(dev, shape):
     err = np.abs(got.astype(np.float64) - want.astype(np.float64))
     print(f"Q4_K {shape}: max |got - ref| / sum|w x| = {(err / (bound * 1e5)).max():.2e}")
     assert (err <= bound).all(), f"worst ratio to the bound: {(err / bound).max():.3g}"
-    # (rows % 8 != 0 takes the tiled route on the CPU, whose chain is this kernel's own per super-block expression: equal bits
-    # there say nothing; the 8x8 route's chain rounds per sub-block pair)
-    assert n % 8 or n * m < 1 << 14 or not bits_equal(got, want), "the fast kernel was not taken"
+    assert n * m < 1 << 14 or not bits_equal(got, want), "the fast kernel was not taken"
     # and in exact mode the same call reproduces the CPU's chain
     assert bits_equal(dev.mul_mat(dev.Weight(orc.Q4_K, W, k), x), want)
+
+
+@pytest.mark.parametrize("cols", ["128", "256"])
+def test_q4_K_fast_mode_blocks_with_odd_scales(dev, cols, monkeypatch):
+    """super-blocks whose d is zero, tiny against dmin (the ratio would leave the f16 range), or negative: the kernel takes
+    their mins on the CUDA cores; both column widths of the kernel"""
+    n, k, m = 264, 1536, 200
+    W = synth.weights(orc.Q4_K, n, k, seed=440, period=512).copy()
+    blocks = W.reshape(n, k // 256, 144)
+    d = blocks[:, :, 0:2].view(np.float16)
+    dmin = blocks[:, :, 2:4].view(np.float16)
+    d[3, 1] = 0.0
+    d[3, 4] = 0.0
+    dmin[3, 4] = 0.0
+    d[40, 0] = np.float16(6e-8)         # the smallest subnormal against an ordinary dmin
+    d[129, 5] = -d[129, 5]
+    dmin[200, 2] = -dmin[200, 2]
+    d[263, :] = 0.0
+    x = synth.activations(m, k, seed=441)
+    want, _ = orc.mul_mat(orc.Q4_K, W, x)
+    monkeypatch.setenv("B200_GEMM_FAST_COLS", cols)
+    dev.set_numerics(dev.FAST)
+    try:
+        got = dev.mul_mat(dev.Weight(orc.Q4_K, W, k), x)
+    finally:
+        dev.set_numerics(dev.EXACT)
+    assert dev.kernel_error() == 0
+    bound = 1e-5 * (np.abs(x).astype(np.float64) @ np.abs(orc.dequantize(orc.Q4_K, W, k)).astype(np.float64).T)
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert (err <= bound + 1e-30).all(), f"worst ratio to the bound: {(err / np.maximum(bound, 1e-30)).max():.3g}"
 
 
 def test_q4_K_fast_mode_switch(dev, monkeypatch):
