@@ -173,7 +173,8 @@ __device__ __forceinline__ bool q_mins_apart(float d, float dmin) { return !(fab
 
 // Q8_K activations of one block of NC rows and one super-block -> its B and Bm images and the scales.
 template <int NC>
-__global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q8_K_acts_fast_kernel(ActView acts, uint8_t *bimg, int64_t m, int nb) {
+__global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q8_K_acts_fast_kernel(ActView acts, uint8_t *bimg, int64_t m, int nb, float *zero_dst, int64_t lddst,
+                                                                                  int64_t n) {
     using C = FqCfg<NC>;
     pdl_trigger();
     pdl_wait();   // the activations come from the previous kernel, and the previous mat-mul may still be reading the images
@@ -220,6 +221,14 @@ __global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q8_K_acts_fast_kerne
         const int64_t dcol = cb * NC + i;
         reinterpret_cast<float *>(img + 4 * C::B_STEP + C::BM_BYTES)[i] = dcol < m ? acts.d[dcol * nb + b] : 0.0f;
     }
+    if (zero_dst) {
+        // the mat-mul adds two halves onto its output: this block clears slice b of the rows of its NC output columns
+        const int64_t r0 = n * b / nb, r1 = n * (b + 1) / nb, len = r1 - r0;
+        for (int64_t i = tid; i < len * NC; i += FQ_EXPAND_THREADS) {
+            const int64_t col = cb * NC + i / len;
+            if (col < m) zero_dst[col * lddst + r0 + i % len] = 0.0f;
+        }
+    }
 }
 
 template <int NC>
@@ -237,7 +246,11 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
     const int64_t rb = blockIdx.y, cb = blockIdx.x;
     const int64_t tile0 = rb * (FQ_ROWS / TILE_ROWS), tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
     const int64_t col0 = cb * NC;
-    const int np = 4 * nb;   // pipeline steps: sub-block pairs
+    // gridDim.z = 2: this CTA takes half of the super-blocks and adds its outputs onto a zeroed dst (two addends onto zero:
+    // the same sum in either order)
+    const int nbl = nb / (int)gridDim.z, b_off = (int)blockIdx.z * nbl;
+    const bool split = gridDim.z > 1;
+    const int np = 4 * nbl;   // pipeline steps: sub-block pairs
     volatile int *abort_flag = &bars.abort_flag;
     const bool prof = profile && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0;
     long long t_prev = clock64();
@@ -273,18 +286,18 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
         const bool row_ok = tile0 + q < tiles_n;
         const bool any_col = col0 + CPT * h < m;
         // (d, dmin) of this thread's row, one word per super-block, fetched one super-block ahead
-        const uint8_t *hdr = tiles + (row_ok ? tile0 + q : 0) * (int64_t)nb * 4608 + lane * 16;
+        const uint8_t *hdr = tiles + ((row_ok ? tile0 + q : 0) * (int64_t)nb + b_off) * 4608 + lane * 16;
         uint32_t dd_next = row_ok ? *(const uint32_t *)(hdr) : 0u;
         float2 acc[CPT / 2];
 #pragma unroll
         for (int c = 0; c < CPT / 2; c++) acc[c] = make_float2(0.0f, 0.0f);
         bool any_apart = false;
         const uint32_t trow0 = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(CPT * h);
-        for (int b = 0; b < nb; b++) {
+        for (int b = 0; b < nbl; b++) {
             const int t = b % FQ_TSTAGES;
             const float dw = f16_bits_to_f32((uint16_t)(dd_next & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(dd_next >> 16));
             any_apart |= row_ok && dmw != 0.0f && q_mins_apart(dw, dmw);
-            if (b + 1 < nb && row_ok) dd_next = *(const uint32_t *)(hdr + (int64_t)(b + 1) * 4608);
+            if (b + 1 < nbl && row_ok) dd_next = *(const uint32_t *)(hdr + (int64_t)(b + 1) * 4608);
             if (warp == 0) FQ_MARK(1);
             if (!__all_sync(0xffffffffu, q_mbar_wait(q_smem_u32(&bars.tfull[t]), (uint32_t)(b / FQ_TSTAGES) & 1u, abort_flag))) break;
             if (warp == 0) FQ_MARK(0);
@@ -319,11 +332,15 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
 #pragma unroll
             for (int c = 0; c < CPT; c++) {
                 const int64_t col = col0 + CPT * h + c;
-                if (col < m) dst[col * lddst + row] = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
+                const float v = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
+                if (col < m) {
+                    if (split) atomicAdd(dst + col * lddst + row, v);
+                    else dst[col * lddst + row] = v;
+                }
             }
             if (any_apart) {
                 // the super-blocks whose mins the tensor core did not take: out -= d_x dmin sum_j m_j (bsum_2j + bsum_2j+1)
-                for (int b = 0; b < nb; b++) {
+                for (int b = 0; b < nbl; b++) {
                     const uint4 hd = *(const uint4 *)(hdr + (int64_t)b * 4608);
                     const float dw = f16_bits_to_f32((uint16_t)(hd.x & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(hd.x >> 16));
                     if (dmw == 0.0f || !q_mins_apart(dw, dmw)) continue;
@@ -331,10 +348,12 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
                     for (int c = 0; c < CPT; c++) {
                         const int64_t col = col0 + CPT * h + c;
                         if (col >= m) break;
-                        const int16_t *bs = acts.bsums + col * (acts.k / 16) + (int64_t)b * 16;
+                        const int16_t *bs = acts.bsums + col * (acts.k / 16) + (int64_t)(b_off + b) * 16;
                         int mg = 0;
                         for (int j = 0; j < 8; j++) mg += (int)(((j < 4 ? mn0 : mn1) >> (8 * (j & 3))) & 0xffu) * ((int)bs[2 * j] + (int)bs[2 * j + 1]);
-                        dst[col * lddst + row] -= acts.d[col * nb + b] * dmw * (float)mg;
+                        const float sub = acts.d[col * nb + b_off + b] * dmw * (float)mg;
+                        if (split) atomicAdd(dst + col * lddst + row, -sub);
+                        else dst[col * lddst + row] -= sub;
                     }
                 }
             }
@@ -345,7 +364,7 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
         // ahead into register set (step + 3) % 4 (the weights do not depend on the previous kernel)
         const int tt = warp - FQ_PROD_WARP0, prow = tt * 32 + lane, sw = prow & 7;
         const bool tile_ok = tile0 + tt < tiles_n;
-        const uint8_t *src = tiles + (tile_ok ? tile0 + tt : 0) * (int64_t)nb * 4608 + lane * 16;
+        const uint8_t *src = tiles + ((tile_ok ? tile0 + tt : 0) * (int64_t)nb + b_off) * 4608 + lane * 16;
         uint8_t *stage0 = fq_raw + (smem - q_smem_u32(fq_raw)) + prow * 128;
         uint8_t *am = fq_raw + (mslot - q_smem_u32(fq_raw)) + (prow >> 3) * 512 + (prow & 7) * 16;
         const uint4 zero4 = make_uint4(0, 0, 0, 0);
@@ -363,9 +382,9 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
             }
         }
         bool ok = true;
-        for (int b = 0; b < nb && ok; b++) {
+        for (int b = 0; b < nbl && ok; b++) {
             hd = hd_next;
-            if (b + 1 < nb && tile_ok) hd_next = *(const uint4 *)(src + (int64_t)(b + 1) * 4608);
+            if (b + 1 < nbl && tile_ok) hd_next = *(const uint4 *)(src + (int64_t)(b + 1) * 4608);
 #pragma unroll
             for (int g = 0; g < 4; g++) {
                 const int p = 4 * b + g, s = p % S;
@@ -458,7 +477,7 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
                 }
             }
         } else if (warp == FQ_LOAD_WARP && lane == 0) {
-            const uint8_t *bsrc = bimg + cb * nb * (int64_t)C::BIMG;
+            const uint8_t *bsrc = bimg + (cb * nb + b_off) * (int64_t)C::BIMG;
             int issued = -1;
             for (int p = 0; p < np; p++) {
                 const int s = p % S, b = p >> 2, g = p & 3;
@@ -507,7 +526,8 @@ int gemm_fast_profile(unsigned long long *out, int n) {
 }
 
 template <int NC>
-static int launch_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, int *err, int profile, cudaStream_t s) {
+static int launch_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, int *err, int profile, int ksplit,
+                       cudaStream_t s) {
     using C = FqCfg<NC>;
     static bool attr_done[64] = {false};
     int dev = 0;
@@ -524,9 +544,10 @@ static int launch_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, Ac
     int rc = scratch_get_images((size_t)gx * nb * C::BIMG, &block);
     if (rc != B200_STATUS_SUCCESS) return rc;
     uint8_t *bimg = (uint8_t *)block;
-    rc = launch_pdl(expand_q8_K_acts_fast_kernel<NC>, dim3((unsigned)nb, (unsigned)gx), dim3(FQ_EXPAND_THREADS), (size_t)0, s, acts, bimg, m, nb);
+    rc = launch_pdl(expand_q8_K_acts_fast_kernel<NC>, dim3((unsigned)nb, (unsigned)gx), dim3(FQ_EXPAND_THREADS), (size_t)0, s, acts, bimg, m, nb,
+                    ksplit > 1 ? dst : (float *)nullptr, lddst, n);
     if (rc != B200_STATUS_SUCCESS) return rc;
-    return launch_pdl(gemm_q4_K_tcgen05_fast_kernel<NC>, dim3((unsigned)gx, (unsigned)gy), dim3(FQ_THREADS), (size_t)C::SMEM, s, tiles, (const uint8_t *)bimg, acts, dst,
+    return launch_pdl(gemm_q4_K_tcgen05_fast_kernel<NC>, dim3((unsigned)gx, (unsigned)gy, (unsigned)ksplit), dim3(FQ_THREADS), (size_t)C::SMEM, s, tiles, (const uint8_t *)bimg, acts, dst,
                       lddst, n, nb, m, err, profile);
 }
 
@@ -543,9 +564,25 @@ int launch_gemm_q4_K_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles,
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     const int64_t gy = (n + FQ_ROWS - 1) / FQ_ROWS;
-    bool wide = m > 128 && gy * ((m + 255) / 256) * 4 >= 3 * (int64_t)sms;
-    if (const char *cv = getenv("B200_GEMM_FAST_COLS")) wide = cv[0] == '2' ? true : cv[0] == '1' ? false : wide;
-    return wide ? launch_fast<256>(n, k, m, tiles, acts, dst, lddst, err, profile, s) : launch_fast<128>(n, k, m, tiles, acts, dst, lddst, err, profile, s);
+    const int64_t ctas256 = gy * ((m + 255) / 256);
+    bool wide = m > 128 && ctas256 * 4 >= 3 * (int64_t)sms;
+    // too few 256-wide CTAs and long rows: each half of the super-blocks in a CTA of its own (measured: 4096 x 14336 x 512
+    // 155 -> 121 us; at 4096 x 4096 the cleared output and the atomic adds cost more than the wider MMAs save: 49 -> 80 us).
+    // B200_GEMM_FAST_KSPLIT=0 / 1 overrides
+    int ksplit = 1;
+    if (m > 128 && !wide && (k / GROUP_K) % 2 == 0 && k / GROUP_K >= 32 && ctas256 * 8 >= 3 * (int64_t)sms) {
+        wide = true;
+        ksplit = 2;
+    }
+    if (const char *cv = getenv("B200_GEMM_FAST_COLS")) {
+        if (cv[0] == '2') wide = true;
+        if (cv[0] == '1') wide = false, ksplit = 1;
+    }
+    if (const char *kv = getenv("B200_GEMM_FAST_KSPLIT")) {
+        if (kv[0] == '0') ksplit = 1;
+        if (kv[0] == '1' && wide && (k / GROUP_K) % 2 == 0) ksplit = 2;
+    }
+    return wide ? launch_fast<256>(n, k, m, tiles, acts, dst, lddst, err, profile, ksplit, s) : launch_fast<128>(n, k, m, tiles, acts, dst, lddst, err, profile, 1, s);
 }
 
 }  // namespace b200

@@ -28,11 +28,20 @@ def dev():
     return mod
 
 
-@pytest.mark.parametrize("cols", ["128", "256"])
+def pick_kernel(monkeypatch, form):
+    """128 or 256 activation rows per CTA; "256k": 256 with the super-blocks split over two CTAs"""
+    monkeypatch.setenv("B200_GEMM_FAST_COLS", form[:3])
+    monkeypatch.setenv("B200_GEMM_FAST_KSPLIT", "1" if form.endswith("k") else "0")
+
+
+FORMS = ["128", "256", "256k"]
+
+
+@pytest.mark.parametrize("form", FORMS)
 @pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
-def test_q4_K_fast_mode_within_the_mat_mul_tolerance(dev, shape, cols, monkeypatch):
+def test_q4_K_fast_mode_within_the_mat_mul_tolerance(dev, shape, form, monkeypatch):
     n, k, m = shape
-    monkeypatch.setenv("B200_GEMM_FAST_COLS", cols)
+    pick_kernel(monkeypatch, form)
     W = synth.weights(orc.Q4_K, n, k, seed=420, period=512)
     x = synth.activations(m, k, seed=421 + m)
     want, _ = orc.mul_mat(orc.Q4_K, W, x)
@@ -51,8 +60,8 @@ def test_q4_K_fast_mode_within_the_mat_mul_tolerance(dev, shape, cols, monkeypat
     assert bits_equal(dev.mul_mat(dev.Weight(orc.Q4_K, W, k), x), want)
 
 
-@pytest.mark.parametrize("cols", ["128", "256"])
-def test_q4_K_fast_mode_blocks_with_odd_scales(dev, cols, monkeypatch):
+@pytest.mark.parametrize("form", FORMS)
+def test_q4_K_fast_mode_blocks_with_odd_scales(dev, form, monkeypatch):
     """super-blocks whose d is zero, tiny against dmin (the ratio would leave the f16 range), or negative: the kernel takes
     their mins on the CUDA cores; both column widths of the kernel"""
     n, k, m = 264, 1536, 200
@@ -69,7 +78,7 @@ def test_q4_K_fast_mode_blocks_with_odd_scales(dev, cols, monkeypatch):
     d[263, :] = 0.0
     x = synth.activations(m, k, seed=441)
     want, _ = orc.mul_mat(orc.Q4_K, W, x)
-    monkeypatch.setenv("B200_GEMM_FAST_COLS", cols)
+    pick_kernel(monkeypatch, form)
     dev.set_numerics(dev.FAST)
     try:
         got = dev.mul_mat(dev.Weight(orc.Q4_K, W, k), x)
