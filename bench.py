@@ -909,7 +909,8 @@ def case_gemm(args):
     b.set_device(0)
     n, k = (int(v) for v in args.only.lower().split("x"))
     m = args.cols
-    w = b.Weight(Q4_K, synth_weights(n, k, seed=7), k)
+    ty = SWEEP_TYPES[args.wtype][0]
+    w = b.Weight(ty, synth_weights(n, k, seed=7, ty=ty), k)
     x = np.random.default_rng(8).standard_normal((m, k)).astype(np.float32)
     dx, do = b.device_array(x), b.DeviceBuffer(4 * n * m)
     for _ in range(3):
@@ -922,7 +923,7 @@ def case_gemm(args):
     e1.record()
     e1.synchronize()
     us = e0.elapsed_ms(e1) * 1e3 / args.launches
-    out = {"case": f"gemm {args.only} x {m}", "launches": args.launches, "us_per_call": us, "tops": 2.0 * n * k * m / us / 1e6, "kernel_error": b.kernel_error()}
+    out = {"case": f"gemm {args.wtype} {args.only} x {m}", "launches": args.launches, "us_per_call": us, "tops": 2.0 * n * k * m / us / 1e6, "kernel_error": b.kernel_error()}
     if os.environ.get("B200_GEMM_FAST_PROFILE") in ("1", "2", "3", "4"):
         # SM clocks per launch of one thread per role of the fast kernel's first CTA (csrc/gemm_tcgen05_fast.cu)
         import ctypes
@@ -1007,6 +1008,7 @@ def main():
     ap.add_argument("--case", default=None, choices=["gemv", "gemm", "fa", "llama_tg", "llama_pp", "llama_b16"], help="one small case for a profiler")
     ap.add_argument("--only", default="4096x4096", help="--case gemv / gemm: the shape NxK")
     ap.add_argument("--cols", type=int, default=512, help="--case gemm: activation rows")
+    ap.add_argument("--wtype", default="Q4_K", choices=["Q4_K", "Q6_K"], help="--case gemm: weight type")
     ap.add_argument("--tokens", type=int, default=512, help="--case fa: query rows")
     ap.add_argument("--n-kv", type=int, default=4096, help="--case fa: cached positions")
     ap.add_argument("--fa-mode", type=int, default=1, help="--case fa: 1 fast kernels, 2 bit-exact kernels")

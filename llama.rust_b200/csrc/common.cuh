@@ -162,6 +162,7 @@ int gemm_chain_pick_for(int64_t n, int64_t m, int sm_count);
 int launch_gemm_tcgen05_f16x64(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s);
 // the same chain in two passes: operands expanded to f16 images once, then a mat-mul that only copies, multiplies and drains (gemm_tcgen05_img.cu)
 constexpr int GEMM_FAST_MIN_COLS = 64;   // activation rows from which the fast-numerics Q4_K prompt kernel takes the mat-mul
+int launch_gemm_kq_fast(int type, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s);   // Q4_K / Q6_K
 int launch_gemm_q4_K_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s);   // gemm_tcgen05_fast.cu
 int launch_gemm_tcgen05_img(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s);
 int launch_gemm_tcgen05_img128(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s);   // 128 activation rows per CTA

@@ -53,14 +53,22 @@ constexpr uint32_t FQ_WAIT_LIMIT = 1u << 22;
 constexpr int FQ_ERR_WAIT = 4;
 constexpr float FQ_RHO_MAX = 952.0f;         // 63 rho stays below 60000 < 65504
 
-template <int NC>
+// Q6_K (the same kernel, Q6 = true): no mins; a weight is s (q - 32) with an int8 scale per 16 elements, up to 4096 in
+// magnitude and so not always an f16 integer.  It goes in as two exact operands, s (8 (q >> 3) - 32) (a multiple of 8 up to
+// 4096) and s (q & 7) (up to 896), multiplied against the same activation image: twice the MMAs, one accumulator.  A step is
+// the 64 elements one (128-element half n, 16-byte piece l16) of the block's ql / qh bytes yields: the four 16-element runs
+// 128 n + 32 r + 16 l16 .. + 15, r = 0 .. 3, each under its own scale; chunk c of a step's image row holds elements
+// 8 (c % 2) .. + 7 of run c / 2 (bytes (0,2,1,3,4,6,5,7)).
+template <int NC, bool Q6>
 struct FqCfg {
-    static constexpr int B_STEP = NC * 128;                       // one pair column of the activations
-    static constexpr int BM_BYTES = NC * 64, DA_BYTES = NC * 4;
+    static constexpr int A_STEP = (Q6 ? 2 : 1) * FQ_A_STEP;       // Q6_K: the high-part tile, then the low-part tile
+    static constexpr int B_STEP = NC * 128;                       // one step of the activations
+    static constexpr int BM_BYTES = Q6 ? 0 : NC * 64, DA_BYTES = NC * 4;
+    static constexpr int AM_BYTES = Q6 ? 0 : FQ_AM_BYTES;
     static constexpr int BIMG = 4 * B_STEP + BM_BYTES + DA_BYTES; // per (column block, super-block)
-    static constexpr int STAGE = FQ_A_STEP + B_STEP;
-    static constexpr int STAGES = 4;                              // <= 4: one mins slot is enough (see the loader)
-    static constexpr int SMEM = STAGES * STAGE + FQ_AM_BYTES + BM_BYTES + 1024;   // 128: 148480, 256: 222208
+    static constexpr int STAGE = A_STEP + B_STEP;
+    static constexpr int STAGES = (Q6 && NC == 256) ? 3 : 4;      // <= 4: one mins slot is enough (see the loader)
+    static constexpr int SMEM = STAGES * STAGE + AM_BYTES + BM_BYTES + 1024;   // Q4_K: 148480 / 222208; Q6_K: 197632 / 197632
     // kind::f16 instruction descriptor: f32 accumulator, f16 x f16, both operands K-major, N = NC, M = 128
     static constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(NC >> 3) << 17) | ((uint32_t)(FQ_ROWS >> 4) << 24);
 };
@@ -158,9 +166,9 @@ __device__ unsigned long long g_fq_prof[16];
         }                                                     \
     } while (0)
 
-template <int NC>
+template <int NC, bool Q6>
 struct alignas(16) FqBars {
-    uint64_t full[FqCfg<NC>::STAGES], empty[FqCfg<NC>::STAGES], tfull[FQ_TSTAGES], tempty[FQ_TSTAGES];
+    uint64_t full[FqCfg<NC, Q6>::STAGES], empty[FqCfg<NC, Q6>::STAGES], tfull[FQ_TSTAGES], tempty[FQ_TSTAGES];
     float da[FQ_DA_SLOTS][NC];
     uint32_t tmem_base;
     int abort_flag;
@@ -172,10 +180,10 @@ __device__ __forceinline__ bool q_mins_apart(float d, float dmin) { return !(fab
 }  // namespace
 
 // Q8_K activations of one block of NC rows and one super-block -> its B and Bm images and the scales.
-template <int NC>
+template <int NC, bool Q6>
 __global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q8_K_acts_fast_kernel(ActView acts, uint8_t *bimg, int64_t m, int nb, float *zero_dst, int64_t lddst,
                                                                                   int64_t n) {
-    using C = FqCfg<NC>;
+    using C = FqCfg<NC, Q6>;
     pdl_trigger();
     pdl_wait();   // the activations come from the previous kernel, and the previous mat-mul may still be reading the images
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
@@ -184,7 +192,7 @@ __global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q8_K_acts_fast_kerne
     uint8_t *img = bimg + (cb * nb + b) * (int64_t)C::BIMG;
     // a warp reads 64 contiguous bytes (one pair) of 8 activation rows; piece r of the pair: (low p0, low p1, high p0,
     // high p1) -> chunks 4 p + 2 hi + {0, 1}
-    const int r = lane >> 3, c0 = 4 * (r & 1) + 2 * (r >> 1);
+    const int r = lane >> 3, c0 = Q6 ? 2 * r : 4 * (r & 1) + 2 * (r >> 1);
 #pragma unroll
     for (int rr = 0; rr < NC / 128; rr++) {
         const int bc = rr * 128 + warp * 8 + (lane & 7), sw = bc & 7;
@@ -193,7 +201,9 @@ __global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q8_K_acts_fast_kerne
 #pragma unroll
         for (int g = 0; g < 4; g++) {
             uint4 y = make_uint4(0, 0, 0, 0);
-            if (col < m) y = *(const uint4 *)(acts.qs + col * K + (int64_t)b * 256 + g * 64 + r * 16);
+            // Q4_K: step g = pair g, piece r of its 64 bytes.  Q6_K: step g = (n, l16) = (g / 2, g % 2), piece r = run r
+            const int src_off = Q6 ? 128 * (g >> 1) + 32 * r + 16 * (g & 1) : g * 64 + r * 16;
+            if (col < m) y = *(const uint4 *)(acts.qs + col * K + (int64_t)b * 256 + src_off);
             // a row past the end holds zeros: 0x80 after the flip, 128 - 128 = 0
             const uint32_t u0 = y.x ^ 0x80808080u, u1 = y.y ^ 0x80808080u, u2 = y.z ^ 0x80808080u, u3 = y.w ^ 0x80808080u;
             uint8_t *dstp = rowp + g * C::B_STEP;
@@ -201,7 +211,7 @@ __global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q8_K_acts_fast_kerne
             q_stg128(dstp + (((c0 + 1) ^ sw) << 4), q_signed(u2, 0), q_signed(u2, 8), q_signed(u3, 0), q_signed(u3, 8));
         }
     }
-    for (int i = tid; i < 2 * NC; i += FQ_EXPAND_THREADS) {
+    for (int i = tid; i < (Q6 ? 0 : 2 * NC); i += FQ_EXPAND_THREADS) {
         // sums: (row i / 2, half i % 2): eight 16-element sums -> one core-matrix row, written twice (K slots 0..15, 16..31)
         const int scol_i = i >> 1, kc = i & 1;
         const int64_t scol = cb * NC + scol_i;
@@ -231,14 +241,15 @@ __global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q8_K_acts_fast_kerne
     }
 }
 
-template <int NC>
+template <int NC, bool Q6>
 __global__ void __launch_bounds__(FQ_THREADS, 1)
-gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *__restrict__ bimg, ActView acts, float *dst, int64_t lddst, int64_t n, int nb,
+gemm_kq_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *__restrict__ bimg, ActView acts, float *dst, int64_t lddst, int64_t n, int nb,
                               int64_t m, int *err, int profile) {
-    using C = FqCfg<NC>;
+    using C = FqCfg<NC, Q6>;
     constexpr int S = C::STAGES, CPT = NC / 2;   // columns per epilogue thread
+    constexpr int CHUNK = Q6 ? 6720 : 4608;      // bytes of a 32-row tile's super-block
     extern __shared__ uint8_t fq_raw[];
-    __shared__ FqBars<NC> bars;
+    __shared__ FqBars<NC, Q6> bars;
     pdl_trigger();
     const uint32_t smem = (q_smem_u32(fq_raw) + 1023u) & ~1023u;
     const uint32_t mslot = smem + (uint32_t)(S * C::STAGE);   // Am | Bm of the super-block whose MMAs run
@@ -285,9 +296,10 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
         const int q = warp & 3, h = warp >> 2;
         const bool row_ok = tile0 + q < tiles_n;
         const bool any_col = col0 + CPT * h < m;
-        // (d, dmin) of this thread's row, one word per super-block, fetched one super-block ahead
-        const uint8_t *hdr = tiles + ((row_ok ? tile0 + q : 0) * (int64_t)nb + b_off) * 4608 + lane * 16;
-        uint32_t dd_next = row_ok ? *(const uint32_t *)(hdr) : 0u;
+        // (d, dmin) of this thread's row (Q6_K: d), one word per super-block, fetched one super-block ahead
+        const uint8_t *hdr = tiles + ((row_ok ? tile0 + q : 0) * (int64_t)nb + b_off) * CHUNK + (Q6 ? 6656 + lane * 2 : lane * 16);
+        const auto load_dd = [&](int b) -> uint32_t { return Q6 ? (uint32_t) * (const uint16_t *)(hdr + (int64_t)b * CHUNK) : *(const uint32_t *)(hdr + (int64_t)b * CHUNK); };
+        uint32_t dd_next = row_ok ? load_dd(0) : 0u;
         float2 acc[CPT / 2];
 #pragma unroll
         for (int c = 0; c < CPT / 2; c++) acc[c] = make_float2(0.0f, 0.0f);
@@ -296,8 +308,8 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
         for (int b = 0; b < nbl; b++) {
             const int t = b % FQ_TSTAGES;
             const float dw = f16_bits_to_f32((uint16_t)(dd_next & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(dd_next >> 16));
-            any_apart |= row_ok && dmw != 0.0f && q_mins_apart(dw, dmw);
-            if (b + 1 < nbl && row_ok) dd_next = *(const uint32_t *)(hdr + (int64_t)(b + 1) * 4608);
+            any_apart |= !Q6 && row_ok && dmw != 0.0f && q_mins_apart(dw, dmw);
+            if (b + 1 < nbl && row_ok) dd_next = load_dd(b + 1);
             if (warp == 0) FQ_MARK(1);
             if (!__all_sync(0xffffffffu, q_mbar_wait(q_smem_u32(&bars.tfull[t]), (uint32_t)(b / FQ_TSTAGES) & 1u, abort_flag))) break;
             if (warp == 0) FQ_MARK(0);
@@ -338,7 +350,7 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
                     else dst[col * lddst + row] = v;
                 }
             }
-            if (any_apart) {
+            if (!Q6 && any_apart) {
                 // the super-blocks whose mins the tensor core did not take: out -= d_x dmin sum_j m_j (bsum_2j + bsum_2j+1)
                 for (int b = 0; b < nbl; b++) {
                     const uint4 hd = *(const uint4 *)(hdr + (int64_t)b * 4608);
@@ -360,6 +372,82 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
         }
     } else if (warp >= FQ_PROD_WARP0) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FQ_REGS_PROD));
+        if constexpr (Q6) {
+            // thread = row (tile tt, lane): per step (n, l16) = (g / 2, g % 2) the 16-byte pieces ql[4 n + l16], ql[4 n + 2 + l16] and
+            // qh[2 n + l16] of its super-block, loaded two steps ahead (the weights do not depend on the previous kernel)
+            const int tt = warp - FQ_PROD_WARP0, prow = tt * 32 + lane, sw = prow & 7;
+            const bool tile_ok = tile0 + tt < tiles_n;
+            const uint8_t *src = tiles + ((tile_ok ? tile0 + tt : 0) * (int64_t)nb + b_off) * CHUNK + lane * 16;
+            uint8_t *stage0 = fq_raw + (smem - q_smem_u32(fq_raw)) + prow * 128;
+            const uint4 zero4 = make_uint4(0, 0, 0, 0);
+            uint4 sc = zero4, sc_next = zero4, w[4][3];
+#pragma unroll
+            for (int i = 0; i < 4; i++) w[i][0] = w[i][1] = w[i][2] = zero4;
+            const auto fetch = [&](int p, uint4(&dst3)[3]) {
+                const int g = p & 3, n = g >> 1, l16 = g & 1;
+                const uint8_t *c = src + (int64_t)(p >> 2) * CHUNK;
+                dst3[0] = ld_stream16(c + (4 * n + l16) * 512);
+                dst3[1] = ld_stream16(c + (4 * n + 2 + l16) * 512);
+                dst3[2] = ld_stream16(c + 4096 + (2 * n + l16) * 512);
+            };
+            if (tile_ok) {
+                sc_next = *(const uint4 *)(src + 6144);
+                if (0 < np) fetch(0, w[0]);
+                if (1 < np) fetch(1, w[1]);
+            }
+            bool ok = true;
+            for (int b = 0; b < nbl && ok; b++) {
+                sc = sc_next;
+                if (b + 1 < nbl && tile_ok) sc_next = *(const uint4 *)(src + (int64_t)(b + 1) * CHUNK + 6144);
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    const int p = 4 * b + g, s = p % S;
+                    if (p + 2 < np && tile_ok) fetch(p + 2, w[(g + 2) & 3]);   // set (g + 2) % 4 was consumed two steps ago
+                    if (warp == FQ_PROD_WARP0) FQ_MARK(8);
+                    if (!__all_sync(0xffffffffu, q_mbar_wait(q_smem_u32(&bars.empty[s]), ((uint32_t)(p / S) & 1u) ^ 1u, abort_flag))) {
+                        ok = false;
+                        break;
+                    }
+                    if (warp == FQ_PROD_WARP0) FQ_MARK(7);
+                    uint8_t *hip = stage0 + s * C::STAGE, *lop = hip + FQ_A_STEP;
+                    const uint4 A = w[g][0], B = w[g][1], H = w[g][2];
+#pragma unroll
+                    for (int r = 0; r < 4; r++) {
+                        // run r: elements 128 n + 32 r + 16 l16 .. + 15, scale 8 n + 2 r + l16
+                        const int si = 8 * (g >> 1) + 2 * r + (g & 1);
+                        const uint32_t sword = si < 4 ? sc.x : si < 8 ? sc.y : si < 12 ? sc.z : sc.w;
+                        const __half sh = __int2half_rn((int)(int8_t)(sword >> (8 * (si & 3))));
+                        const __half2 s2 = __halves2half2(sh, sh);
+                        const __half2 chi = __hmul2(s2, __float2half2_rn(-96.0f)), clo = __hmul2(s2, __float2half2_rn(-64.0f));
+                        uint32_t hi[8], lo[8];
+#pragma unroll
+                        for (int wd = 0; wd < 4; wd++) {
+                            const uint32_t aw = wd == 0 ? A.x : wd == 1 ? A.y : wd == 2 ? A.z : A.w, bw = wd == 0 ? B.x : wd == 1 ? B.y : wd == 2 ? B.z : B.w;
+                            const uint32_t hw = wd == 0 ? H.x : wd == 1 ? H.y : wd == 2 ? H.z : H.w;
+                            const uint32_t v = r == 0   ? (aw & 0x0f0f0f0fu) | ((hw << 4) & 0x30303030u)
+                                               : r == 1 ? (bw & 0x0f0f0f0fu) | ((hw << 2) & 0x30303030u)
+                                               : r == 2 ? ((aw >> 4) & 0x0f0f0f0fu) | (hw & 0x30303030u)
+                                                        : ((bw >> 4) & 0x0f0f0f0fu) | ((hw >> 2) & 0x30303030u);
+                            const uint32_t v8 = v >> 8;
+                            // (64 + 8 (q >> 3)) s - 96 s = s (8 (q >> 3) - 32);  (64 + (q & 7)) s - 64 s = s (q & 7): one rounding each, exact
+                            hi[2 * wd] = q_h2_bits(__hfma2(q_bits_h2(((v & 0x00380038u) << 4) | 0x54005400u), s2, chi));
+                            hi[2 * wd + 1] = q_h2_bits(__hfma2(q_bits_h2(((v8 & 0x00380038u) << 4) | 0x54005400u), s2, chi));
+                            lo[2 * wd] = q_h2_bits(__hfma2(q_bits_h2(((v & 0x00070007u) << 4) | 0x54005400u), s2, clo));
+                            lo[2 * wd + 1] = q_h2_bits(__hfma2(q_bits_h2(((v8 & 0x00070007u) << 4) | 0x54005400u), s2, clo));
+                        }
+                        q_stg128(hip + (((2 * r + 0) ^ sw) << 4), hi[0], hi[1], hi[2], hi[3]);
+                        q_stg128(hip + (((2 * r + 1) ^ sw) << 4), hi[4], hi[5], hi[6], hi[7]);
+                        q_stg128(lop + (((2 * r + 0) ^ sw) << 4), lo[0], lo[1], lo[2], lo[3]);
+                        q_stg128(lop + (((2 * r + 1) ^ sw) << 4), lo[4], lo[5], lo[6], lo[7]);
+                    }
+                    if (warp == FQ_PROD_WARP0) FQ_MARK(9);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) q_mbar_arrive(q_smem_u32(&bars.full[s]));
+                    if (warp == FQ_PROD_WARP0) FQ_MARK(10);
+                }
+            }
+        } else {
         // thread = row (tile tt, lane): per step the two 16-byte pieces 2 g, 2 g + 1 of its 128 nibble bytes, loaded three steps
         // ahead into register set (step + 3) % 4 (the weights do not depend on the previous kernel)
         const int tt = warp - FQ_PROD_WARP0, prow = tt * 32 + lane, sw = prow & 7;
@@ -447,6 +535,7 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
                 if (warp == FQ_PROD_WARP0) FQ_MARK(10);
             }
         }
+        }
     } else {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FQ_REGS_CTL));
         pdl_wait();   // the images are the previous kernel's output
@@ -460,17 +549,26 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
                     if (g == 0 && !q_mbar_wait(q_smem_u32(&bars.tempty[t]), ((uint32_t)(b / FQ_TSTAGES) & 1u) ^ 1u, abort_flag)) break;
                     FQ_MARK(3);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_base = smem + (uint32_t)(s * C::STAGE), b_base = a_base + FQ_A_STEP;
+                    const uint32_t a_base = smem + (uint32_t)(s * C::STAGE), b_base = a_base + C::A_STEP;
                     const uint32_t d_acc = tmem + (uint32_t)(t * NC);
-                    if (g == 0) {
-                        // the mins first (they clear the accumulator): K = 32 as two MMAs, core-matrix columns 0, 1 and 2, 3
-                        const uint64_t amd = q_desc_plain(mslot, 128, 512), bmd = q_desc_plain(mslot + FQ_AM_BYTES, 128, 512);
-                        q_mma(d_acc, amd, bmd, C::IDESC, 0);
-                        q_mma(d_acc, amd + (256 >> 4), bmd + (256 >> 4), C::IDESC, 1);
-                    }
                     const uint64_t ad = q_desc_sw128(a_base), bd = q_desc_sw128(b_base);
+                    if constexpr (Q6) {
+                        const uint64_t ad_lo = q_desc_sw128(a_base + FQ_A_STEP);
 #pragma unroll
-                    for (int i = 0; i < 4; i++) q_mma(d_acc, ad + 2 * i, bd + 2 * i, C::IDESC, 1);   // K = 16 step i: 32 bytes on
+                        for (int i = 0; i < 4; i++) {   // K = 16 step i: 32 bytes on; the high parts, then the low parts, of the same 16 elements
+                            q_mma(d_acc, ad + 2 * i, bd + 2 * i, C::IDESC, (g | i) != 0);
+                            q_mma(d_acc, ad_lo + 2 * i, bd + 2 * i, C::IDESC, 1);
+                        }
+                    } else {
+                        if (g == 0) {
+                            // the mins first (they clear the accumulator): K = 32 as two MMAs, core-matrix columns 0, 1 and 2, 3
+                            const uint64_t amd = q_desc_plain(mslot, 128, 512), bmd = q_desc_plain(mslot + FQ_AM_BYTES, 128, 512);
+                            q_mma(d_acc, amd, bmd, C::IDESC, 0);
+                            q_mma(d_acc, amd + (256 >> 4), bmd + (256 >> 4), C::IDESC, 1);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; i++) q_mma(d_acc, ad + 2 * i, bd + 2 * i, C::IDESC, 1);   // K = 16 step i: 32 bytes on
+                    }
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(q_smem_u32(&bars.empty[s])) : "memory");
                     if (g == 3)
                         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(q_smem_u32(&bars.tfull[t])) : "memory");
@@ -487,12 +585,12 @@ gemm_q4_K_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *
                 const uint32_t bar = q_smem_u32(&bars.full[s]), stage = smem + (uint32_t)(s * C::STAGE);
                 const uint8_t *bb = bsrc + (int64_t)b * C::BIMG;
                 q_mbar_expect(bar, (uint32_t)(C::B_STEP + (g == 0 ? C::BM_BYTES + C::DA_BYTES : 0)));
-                q_bulk_load(stage + FQ_A_STEP, bb + g * C::B_STEP, C::B_STEP, bar);
+                q_bulk_load(stage + C::A_STEP, bb + g * C::B_STEP, C::B_STEP, bar);
                 if (g == 0) {
                     // the mins slot: with at most four stages the stage this step reuses belonged to a step of the previous
                     // super-block no earlier than its first, so that super-block's mins MMAs are done; the scale slot of
                     // super-block b - 4: its drain ended before the MMAs of b - 2 began
-                    q_bulk_load(mslot + FQ_AM_BYTES, bb + 4 * C::B_STEP, C::BM_BYTES, bar);
+                    if constexpr (!Q6) q_bulk_load(mslot + FQ_AM_BYTES, bb + 4 * C::B_STEP, C::BM_BYTES, bar);
                     q_bulk_load(q_smem_u32(bars.da[b % FQ_DA_SLOTS]), bb + 4 * C::B_STEP + C::BM_BYTES, C::DA_BYTES, bar);
                 }
                 issued = p;
@@ -525,16 +623,16 @@ int gemm_fast_profile(unsigned long long *out, int n) {
     return B200_STATUS_SUCCESS;
 }
 
-template <int NC>
+template <int NC, bool Q6>
 static int launch_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, int *err, int profile, int ksplit,
                        cudaStream_t s) {
-    using C = FqCfg<NC>;
+    using C = FqCfg<NC, Q6>;
     static bool attr_done[64] = {false};
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
     B200_REQUIRE(dev >= 0 && dev < 64, "gemm: device index %d out of range", dev);
     if (!attr_done[dev]) {
-        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_tcgen05_fast_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        B200_CUDA(cudaFuncSetAttribute(gemm_kq_tcgen05_fast_kernel<NC, Q6>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         attr_done[dev] = true;
     }
     const int nb = (int)(k / GROUP_K);
@@ -544,15 +642,17 @@ static int launch_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, Ac
     int rc = scratch_get_images((size_t)gx * nb * C::BIMG, &block);
     if (rc != B200_STATUS_SUCCESS) return rc;
     uint8_t *bimg = (uint8_t *)block;
-    rc = launch_pdl(expand_q8_K_acts_fast_kernel<NC>, dim3((unsigned)nb, (unsigned)gx), dim3(FQ_EXPAND_THREADS), (size_t)0, s, acts, bimg, m, nb,
+    rc = launch_pdl(expand_q8_K_acts_fast_kernel<NC, Q6>, dim3((unsigned)nb, (unsigned)gx), dim3(FQ_EXPAND_THREADS), (size_t)0, s, acts, bimg, m, nb,
                     ksplit > 1 ? dst : (float *)nullptr, lddst, n);
     if (rc != B200_STATUS_SUCCESS) return rc;
-    return launch_pdl(gemm_q4_K_tcgen05_fast_kernel<NC>, dim3((unsigned)gx, (unsigned)gy, (unsigned)ksplit), dim3(FQ_THREADS), (size_t)C::SMEM, s, tiles, (const uint8_t *)bimg, acts, dst,
+    return launch_pdl(gemm_kq_tcgen05_fast_kernel<NC, Q6>, dim3((unsigned)gx, (unsigned)gy, (unsigned)ksplit), dim3(FQ_THREADS), (size_t)C::SMEM, s, tiles, (const uint8_t *)bimg, acts, dst,
                       lddst, n, nb, m, err, profile);
 }
 
-int launch_gemm_q4_K_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s) {
+// type: B200_TYPE_Q4_K or B200_TYPE_Q6_K
+int launch_gemm_kq_fast(int type, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s) {
     B200_REQUIRE(k % GROUP_K == 0, "gemm: k = %lld must be a multiple of 256", (long long)k);
+    B200_REQUIRE(type == B200_TYPE_Q4_K || type == B200_TYPE_Q6_K, "gemm: the fast kernel takes Q4_K and Q6_K, not type %d", type);
     if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
     int *err = nullptr;
     int rc = device_error_word(&err);
@@ -582,7 +682,15 @@ int launch_gemm_q4_K_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles,
         if (kv[0] == '0') ksplit = 1;
         if (kv[0] == '1' && wide && (k / GROUP_K) % 2 == 0) ksplit = 2;
     }
-    return wide ? launch_fast<256>(n, k, m, tiles, acts, dst, lddst, err, profile, ksplit, s) : launch_fast<128>(n, k, m, tiles, acts, dst, lddst, err, profile, 1, s);
+    if (type == B200_TYPE_Q6_K)
+        return wide ? launch_fast<256, true>(n, k, m, tiles, acts, dst, lddst, err, profile, ksplit, s)
+                    : launch_fast<128, true>(n, k, m, tiles, acts, dst, lddst, err, profile, 1, s);
+    return wide ? launch_fast<256, false>(n, k, m, tiles, acts, dst, lddst, err, profile, ksplit, s)
+                : launch_fast<128, false>(n, k, m, tiles, acts, dst, lddst, err, profile, 1, s);
+}
+
+int launch_gemm_q4_K_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s) {
+    return launch_gemm_kq_fast(B200_TYPE_Q4_K, n, k, m, tiles, acts, dst, lddst, s);
 }
 
 }  // namespace b200

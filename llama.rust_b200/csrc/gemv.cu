@@ -920,6 +920,15 @@ int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint
     // serves the fast numerics mode only.  The 32-element-block types take it from 8 rows on (their only alternative
     // re-reads the weights once per two activation rows).
     if (gemm_tcgen05_enabled() && gemm_mma_enabled()) {
+        // fast numerics: Q6_K prompt batches on the f16 tensor-core kernel with one accumulator per super-block (within 1e-5
+        // of sum |w x|), from 2048 weight rows (measured with 512 activation rows: 4096 x 14336 424 -> 218 us, 14336 x 4096
+        // 382 -> 204 us, but 1024 x 4096 48 -> 90 us: eight row blocks leave its producer warps nothing to hide behind);
+        // B200_GEMM_FAST=0 keeps the exact kernels, =2 lifts the row limit (read per call)
+        const char *fe = getenv("B200_GEMM_FAST");
+        if (type == B200_TYPE_Q6_K && route == B200_ROUTE_TILED && m >= GEMM_FAST_MIN_COLS && numerics_mode() == 1 && !no_scratch_mode() &&
+            (n >= 2048 || (fe && fe[0] == '2'))) {
+            if (!(fe && fe[0] == '0')) return launch_gemm_kq_fast(type, n, k, m, tiles, acts, dst, lddst, s);
+        }
         // Q6_K: the two-plane tcgen05 kernel gives the same bits as the mma.sync kernel below but measured slower
         // (107-114 against 156-170 TOP/s on 14336 x 4096 with 512 / 2048 rows: its operand split is the bottleneck),
         // so it runs only when asked for: B200_Q6K_TCGEN05=1, read per call

@@ -61,6 +61,53 @@ def test_q4_K_fast_mode_within_the_mat_mul_tolerance(dev, shape, form, monkeypat
 
 
 @pytest.mark.parametrize("form", FORMS)
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_q6_K_fast_mode_within_the_mat_mul_tolerance(dev, shape, form, monkeypatch):
+    """Q6_K on the same kernel: a weight s (q - 32) goes in as two exact f16 operands, s (8 (q >> 3) - 32) and s (q & 7)
+    (tiled chain on the CPU: crates/ggml/src/tiled.rs:723-839)"""
+    n, k, m = shape
+    pick_kernel(monkeypatch, form)
+    monkeypatch.setenv("B200_GEMM_FAST", "2")   # the fast kernel whatever the row count
+    W = synth.weights(orc.Q6_K, n, k, seed=450, period=512)
+    x = synth.activations(m, k, seed=451 + m)
+    want, _ = orc.mul_mat(orc.Q6_K, W, x)
+    dev.set_numerics(dev.FAST)
+    try:
+        got = dev.mul_mat(dev.Weight(orc.Q6_K, W, k), x)
+    finally:
+        dev.set_numerics(dev.EXACT)
+    assert dev.kernel_error() == 0
+    bound = 1e-5 * (np.abs(x).astype(np.float64) @ np.abs(orc.dequantize(orc.Q6_K, W, k)).astype(np.float64).T)
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    print(f"Q6_K {shape}: max |got - ref| / sum|w x| = {(err / (bound * 1e5)).max():.2e}")
+    assert (err <= bound).all(), f"worst ratio to the bound: {(err / bound).max():.3g}"
+    assert bits_equal(dev.mul_mat(dev.Weight(orc.Q6_K, W, k), x), want)
+
+
+def test_q6_K_fast_mode_extreme_scales(dev, monkeypatch):
+    """scales of -128 and 127 against quants of 0 and 63: the largest products the two operand parts have to carry"""
+    monkeypatch.setenv("B200_GEMM_FAST", "2")
+    n, k, m = 128, 512, 64
+    W = synth.weights(orc.Q6_K, n, k, seed=460).copy()
+    blocks = W.reshape(n, k // 256, 210)      # ql[128] qh[64] scales[16] d
+    blocks[0, 0, 192:208] = np.array([-128, 127] * 8, dtype=np.int8).view(np.uint8)
+    blocks[0, 0, 0:128] = 0xFF                # low nibbles 15 ...
+    blocks[0, 0, 128:192] = 0xFF              # ... high bits 3: q = 63
+    blocks[1, 1, 192:208] = np.array([127, -128] * 8, dtype=np.int8).view(np.uint8)
+    blocks[1, 1, 0:192] = 0                   # q = 0
+    x = synth.activations(m, k, seed=461)
+    want, _ = orc.mul_mat(orc.Q6_K, W, x)
+    dev.set_numerics(dev.FAST)
+    try:
+        got = dev.mul_mat(dev.Weight(orc.Q6_K, W, k), x)
+    finally:
+        dev.set_numerics(dev.EXACT)
+    bound = 1e-5 * (np.abs(x).astype(np.float64) @ np.abs(orc.dequantize(orc.Q6_K, W, k)).astype(np.float64).T)
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert (err <= bound).all(), f"worst ratio to the bound: {(err / bound).max():.3g}"
+
+
+@pytest.mark.parametrize("form", FORMS)
 def test_q4_K_fast_mode_blocks_with_odd_scales(dev, form, monkeypatch):
     """super-blocks whose d is zero, tiny against dmin (the ratio would leave the f16 range), or negative: the kernel takes
     their mins on the CUDA cores; both column widths of the kernel"""
