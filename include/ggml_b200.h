@@ -182,6 +182,13 @@ int b200_bench_mul_mat_q8(int type, int64_t n, int64_t k, int64_t m, const void 
  * them is a few microseconds of launch latency.  Every n[i] must take the 8x8 gemv route (a multiple of 8). */
 int b200_mul_mat_q8_multi(int type, int64_t k, int count, const int64_t *n, const void *const *dev_w, const void *dev_act,
                           int act_kind, float *const *dev_dst, void *stream);
+/* The same for m activation rows (prompt batches): count (1 .. 3) matrices of one type and row length against the same
+ * quantized activations, dev_dst[i] [m][lddst[i]].  All matrices must take the same CPU route for m rows (the route b200_mul_mat_q8 picks under B200_ROUTE_AUTO).
+ * Gives exactly what count calls of b200_mul_mat_q8 give; where the fast-numerics prompt kernel applies the matrices
+ * share one launch and one expansion of the activations (the q / k / v and gate / up projections of a layer,
+ * crates/llama/src/graph_arch.rs:171-190,1137-1151). */
+int b200_mul_mat_q8_rows_multi(int type, int64_t k, int64_t m, int count, const int64_t *n, const void *const *dev_w, const void *dev_act, int act_kind,
+                               float *const *dev_dst, const int64_t *lddst, void *stream);
 /* One-row Q4_K mat-mul(s) with the f32 op in front of them and the Q8_K quantization of its result run inside the
  * mat-mul kernel (at one token each of those ops is a launch of a few microseconds for a few KB of work):
  *   B200_ACT_PRO_PLAIN  act = q8_K(x)                          — a mat-mul whose activations are not quantized yet

@@ -485,6 +485,24 @@ int b200_mul_mat_q8_multi(int type, int64_t k, int count, const int64_t *n, cons
     return launch_gemv_q4_K_multi(count, n, (const uint8_t *const *)dev_w, dev_dst, k, a, (cudaStream_t)stream);
 }
 
+int b200_mul_mat_q8_rows_multi(int type, int64_t k, int64_t m, int count, const int64_t *n, const void *const *dev_w, const void *dev_act, int act_kind,
+                               float *const *dev_dst, const int64_t *lddst, void *stream) {
+    B200_REQUIRE(count >= 1 && count <= 3 && n && dev_w && dev_dst && lddst && dev_act, "mul_mat_q8_rows_multi: bad arguments");
+    if (m == 0) return B200_STATUS_SUCCESS;
+    int route = -1;
+    for (int i = 0; i < count; i++) {
+        int rc = check_mul_mat_args(type, n[i], k, m);
+        if (rc != B200_STATUS_SUCCESS) return rc;
+        B200_REQUIRE(dev_w[i] && dev_dst[i] && lddst[i] >= n[i], "mul_mat_q8_rows_multi: matrix %d: null pointer or dst row stride smaller than n", i);
+        const int r = pick_route(type, n[i], m);
+        B200_REQUIRE(route < 0 || r == route, "mul_mat_q8_rows_multi: matrix %d (%lld rows) takes another route than matrix 0", i, (long long)n[i]);
+        route = r;
+    }
+    B200_REQUIRE(act_kind == act_kind_for(type, route, m), "mul_mat_q8_rows_multi: activation kind %d does not fit type %d", act_kind, type);
+    ActBuf a = act_carve(const_cast<void *>(dev_act), m, k);
+    return launch_gemv_rows_multi(type, route, count, n, k, m, (const uint8_t *const *)dev_w, a.view(), dev_dst, lddst, (cudaStream_t)stream);
+}
+
 int b200_mul_mat_row_fused(int type, int64_t k, int count, const int64_t *n, const void *const *dev_w, float *const *dev_dst,
                            const struct b200_act_prologue *pro, const float *dev_addend, float *dev_sum, void *stream) {
     B200_REQUIRE(type == B200_TYPE_Q4_K, "mul_mat_row_fused: weight type %d is not supported (Q4_K only)", type);

@@ -491,9 +491,16 @@ static bool multi_candidate(const ggml_tensor *mm) {
     return mm->op == GGML_OP_MUL_MAT && w && x && w->type == B200_TYPE_Q4_K && w->ne[2] == 1 && w->ne[3] == 1 && w->ne[1] % 8 == 0 &&
            x->ne[1] == 1 && x->ne[2] == 1 && x->ne[3] == 1 && mm->data && supports_mul_mat(mm, nullptr);
 }
-static int find_sibling_mat_muls(const ggml_cgraph *g, int i, int *sib) {
+// the same for a prompt batch: Q4_K matrices on the 8x8 route over 64 or more activation rows, a multiple of 4 (no tail rows)
+static bool multi_candidate_rows(const ggml_tensor *mm) {
+    const ggml_tensor *w = mm->src[0], *x = mm->src[1];
+    return mm->op == GGML_OP_MUL_MAT && w && x && w->type == B200_TYPE_Q4_K && w->ne[2] == 1 && w->ne[3] == 1 && w->ne[1] % 8 == 0 &&
+           x->ne[1] >= 64 && x->ne[1] % 4 == 0 && x->ne[2] == 1 && x->ne[3] == 1 && mm->data && supports_mul_mat(mm, nullptr);
+}
+static int find_sibling_mat_muls(const ggml_cgraph *g, int i, int *sib, bool rows = false) {
     const ggml_tensor *first = g->nodes[i];
-    if (!multi_candidate(first)) return 0;
+    const auto cand = [rows](const ggml_tensor *t) { return rows ? multi_candidate_rows(t) : multi_candidate(t); };
+    if (!cand(first)) return 0;
     const ggml_tensor *x = first->src[1];
     int found = 0;
     for (int j = i + 1; j < g->n_nodes && j <= i + 12 && found < 2; j++) {
@@ -502,7 +509,7 @@ static int find_sibling_mat_muls(const ggml_cgraph *g, int i, int *sib) {
         const bool alias = t->op == GGML_OP_NONE || t->op == GGML_OP_RESHAPE || t->op == GGML_OP_VIEW || t->op == GGML_OP_PERMUTE ||
                            t->op == GGML_OP_TRANSPOSE;
         if (!alias && t->data && ranges_overlap(t->data, ggml_nbytes(t), x->data, ggml_nbytes(x))) break;   // the activations change here
-        if (alias || !multi_candidate(t) || t->src[1] != x) continue;
+        if (alias || !cand(t) || t->src[1] != x) continue;
         const ggml_tensor *after = j + 1 < g->n_nodes ? g->nodes[j + 1] : nullptr;
         if (after && fuses_mul_mat_add(t, after)) continue;
         if (ranges_overlap(t->data, ggml_nbytes(t), first->data, ggml_nbytes(first))) continue;
@@ -538,6 +545,27 @@ static int compute_mul_mat_multi(BackendCtx *bc, const ggml_cgraph *g, int i, co
     int rc = quantized_acts(bc, (const float *)x->data, (int64_t)(x->nb[1] / 4), 1, k, kind);
     if (rc != B200_STATUS_SUCCESS) return rc;
     return b200_mul_mat_q8_multi(B200_TYPE_Q4_K, k, n_sib + 1, n, w, bc->act, kind, dst, bc->stream);
+}
+
+// the same for a prompt batch: one quantization of the activation rows, one call for the sibling matrices
+static int compute_mul_mat_multi_rows(BackendCtx *bc, const ggml_cgraph *g, int i, const int *sib, int n_sib) {
+    const ggml_tensor *x = g->nodes[i]->src[1];
+    const int64_t k = x->ne[0], m = x->ne[1];
+    const int kind = act_kind_for(B200_TYPE_Q4_K, B200_ROUTE_REPACK, m);
+    int64_t n[3], ld[3];
+    const void *w[3];
+    float *dst[3];
+    for (int e = 0; e <= n_sib; e++) {
+        const ggml_tensor *mm = g->nodes[e == 0 ? i : sib[e - 1]];
+        n[e] = mm->src[0]->ne[1];
+        w[e] = mm->src[0]->data;
+        dst[e] = (float *)mm->data;
+        ld[e] = (int64_t)(mm->nb[1] / 4);
+        if (bc->act_src && ranges_overlap(mm->data, ggml_nbytes(mm), bc->act_src, (size_t)bc->act_ld * bc->act_m * 4)) bc->act_src = nullptr;
+    }
+    int rc = quantized_acts(bc, (const float *)x->data, (int64_t)(x->nb[1] / 4), m, k, kind);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    return b200_mul_mat_q8_rows_multi(B200_TYPE_Q4_K, k, m, n_sib + 1, n, w, bc->act, kind, dst, ld, bc->stream);
 }
 
 // fused: a one-row mat-mul whose result the next node adds to a tensor of the same shape (the residual)
@@ -1435,9 +1463,10 @@ static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
                     i++;
                 } else {
                     int sib[2];
-                    const int n_sib = bc->fuse_siblings ? find_sibling_mat_muls(g, i, sib) : 0;
+                    const bool rows = op->src[1]->ne[1] > 1;
+                    const int n_sib = bc->fuse_siblings ? find_sibling_mat_muls(g, i, sib, rows) : 0;
                     if (n_sib > 0) {
-                        rc = compute_mul_mat_multi(bc, g, i, sib, n_sib);
+                        rc = rows ? compute_mul_mat_multi_rows(bc, g, i, sib, n_sib) : compute_mul_mat_multi(bc, g, i, sib, n_sib);
                         for (int e = 0; e < n_sib; e++) done[sib[e]] = 1;
                     } else {
                         rc = compute_mul_mat(bc, op);

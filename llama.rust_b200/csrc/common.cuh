@@ -162,6 +162,11 @@ int gemm_chain_pick_for(int64_t n, int64_t m, int sm_count);
 int launch_gemm_tcgen05_f16x64(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s);
 // the same chain in two passes: operands expanded to f16 images once, then a mat-mul that only copies, multiplies and drains (gemm_tcgen05_img.cu)
 constexpr int GEMM_FAST_MIN_COLS = 64;   // activation rows from which the fast-numerics Q4_K prompt kernel takes the mat-mul
+int gemm_tcgen05_f16_choice();   // gemm_tcgen05.cu: B200_GEMM_TCGEN05_F16 (-1 = unset: the library picks)
+int launch_gemv_rows_multi(int type, int route, int count, const int64_t *n, int64_t k, int64_t m, const uint8_t *const *tiles, ActView acts, float *const *dst,
+                           const int64_t *lddst, cudaStream_t s);   // gemv.cu
+int launch_gemm_kq_fast_multi(int type, int count, const int64_t *n, int64_t k, int64_t m, const uint8_t *const *tiles, ActView acts, float *const *dst,
+                              const int64_t *lddst, cudaStream_t s);   // up to three matrices over the same activations
 int launch_gemm_kq_fast(int type, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s);   // Q4_K / Q6_K
 int launch_gemm_q4_K_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s);   // gemm_tcgen05_fast.cu
 int launch_gemm_tcgen05_img(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s);

@@ -665,7 +665,7 @@ gemm_q4_K_tcgen05_f16_kernel(const uint8_t *__restrict__ tiles, ActView acts, fl
 // B200_GEMM_TCGEN05_F16 picks the kernel of the gemm chain: 0 = the integer kernel of this file, 1 = its 32-column
 // f16-operand kernel, 2 = the 64-column one (gemm_tcgen05_f16.cu), 3 = the two-pass one (gemm_tcgen05_img.cu);
 // 4 = the two-pass one with 128 activation rows per CTA; unset = by estimated time among 0, 3 and 4 (gemm_chain_pick below).
-static int gemm_tcgen05_f16_choice() {
+int gemm_tcgen05_f16_choice() {
     static int v = -2;
     if (v == -2) {
         const char *e = getenv("B200_GEMM_TCGEN05_F16");

@@ -174,6 +174,17 @@ struct alignas(16) FqBars {
     int abort_flag;
 };
 
+// up to three weight matrices of one type and row length against the same activations in one launch (the q / k / v
+// projections of an attention block, the gate / up projections of an FFN): row block rb belongs to the last matrix e with
+// rb_start[e] <= rb
+struct FqMats {
+    const uint8_t *tiles[3];
+    float *dst[3];
+    int64_t n[3], lddst[3];
+    int rb_start[3];
+    int count;
+};
+
 // a row's super-block takes the CUDA-core path for its mins: d == 0, or rho m_j could leave the f16 range
 __device__ __forceinline__ bool q_mins_apart(float d, float dmin) { return !(fabsf(dmin) <= FQ_RHO_MAX * d); }
 
@@ -243,8 +254,7 @@ __global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q8_K_acts_fast_kerne
 
 template <int NC, bool Q6>
 __global__ void __launch_bounds__(FQ_THREADS, 1)
-gemm_kq_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *__restrict__ bimg, ActView acts, float *dst, int64_t lddst, int64_t n, int nb,
-                              int64_t m, int *err, int profile) {
+gemm_kq_tcgen05_fast_kernel(const __grid_constant__ FqMats mats, const uint8_t *__restrict__ bimg, ActView acts, int nb, int64_t m, int *err, int profile) {
     using C = FqCfg<NC, Q6>;
     constexpr int S = C::STAGES, CPT = NC / 2;   // columns per epilogue thread
     constexpr int CHUNK = Q6 ? 6720 : 4608;      // bytes of a 32-row tile's super-block
@@ -254,7 +264,11 @@ gemm_kq_tcgen05_fast_kernel(const uint8_t *__restrict__ tiles, const uint8_t *__
     const uint32_t smem = (q_smem_u32(fq_raw) + 1023u) & ~1023u;
     const uint32_t mslot = smem + (uint32_t)(S * C::STAGE);   // Am | Bm of the super-block whose MMAs run
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int64_t rb = blockIdx.y, cb = blockIdx.x;
+    const int mat = (mats.count > 2 && (int)blockIdx.y >= mats.rb_start[2]) ? 2 : (mats.count > 1 && (int)blockIdx.y >= mats.rb_start[1]) ? 1 : 0;
+    const uint8_t *__restrict__ tiles = mats.tiles[mat];
+    float *dst = mats.dst[mat];
+    const int64_t n = mats.n[mat], lddst = mats.lddst[mat];
+    const int64_t rb = (int)blockIdx.y - mats.rb_start[mat], cb = blockIdx.x;
     const int64_t tile0 = rb * (FQ_ROWS / TILE_ROWS), tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
     const int64_t col0 = cb * NC;
     // gridDim.z = 2: this CTA takes half of the super-blocks and adds its outputs onto a zeroed dst (two addends onto zero:
@@ -624,8 +638,7 @@ int gemm_fast_profile(unsigned long long *out, int n) {
 }
 
 template <int NC, bool Q6>
-static int launch_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, int *err, int profile, int ksplit,
-                       cudaStream_t s) {
+static int launch_fast(const FqMats &mats, int64_t gy, int64_t k, int64_t m, ActView acts, int *err, int profile, int ksplit, cudaStream_t s) {
     using C = FqCfg<NC, Q6>;
     static bool attr_done[64] = {false};
     int dev = 0;
@@ -636,24 +649,40 @@ static int launch_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, Ac
         attr_done[dev] = true;
     }
     const int nb = (int)(k / GROUP_K);
-    const int64_t gx = (m + NC - 1) / NC, gy = (n + FQ_ROWS - 1) / FQ_ROWS;
-    B200_REQUIRE(gx <= 65535 && gy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);
+    const int64_t gx = (m + NC - 1) / NC;
+    B200_REQUIRE(gx <= 65535 && gy <= 65535, "gemm: %lld row blocks x %lld column blocks are too many for one launch", (long long)gy, (long long)gx);
     void *block = nullptr;
     int rc = scratch_get_images((size_t)gx * nb * C::BIMG, &block);
     if (rc != B200_STATUS_SUCCESS) return rc;
     uint8_t *bimg = (uint8_t *)block;
     rc = launch_pdl(expand_q8_K_acts_fast_kernel<NC, Q6>, dim3((unsigned)nb, (unsigned)gx), dim3(FQ_EXPAND_THREADS), (size_t)0, s, acts, bimg, m, nb,
-                    ksplit > 1 ? dst : (float *)nullptr, lddst, n);
+                    ksplit > 1 ? mats.dst[0] : (float *)nullptr, mats.lddst[0], mats.n[0]);
     if (rc != B200_STATUS_SUCCESS) return rc;
-    return launch_pdl(gemm_kq_tcgen05_fast_kernel<NC, Q6>, dim3((unsigned)gx, (unsigned)gy, (unsigned)ksplit), dim3(FQ_THREADS), (size_t)C::SMEM, s, tiles, (const uint8_t *)bimg, acts, dst,
-                      lddst, n, nb, m, err, profile);
+    return launch_pdl(gemm_kq_tcgen05_fast_kernel<NC, Q6>, dim3((unsigned)gx, (unsigned)gy, (unsigned)ksplit), dim3(FQ_THREADS), (size_t)C::SMEM, s, mats,
+                      (const uint8_t *)bimg, acts, nb, m, err, profile);
 }
 
-// type: B200_TYPE_Q4_K or B200_TYPE_Q6_K
-int launch_gemm_kq_fast(int type, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s) {
+// type: B200_TYPE_Q4_K or B200_TYPE_Q6_K; count matrices (1 .. 3) of that type and row length k over the same m activation rows
+int launch_gemm_kq_fast_multi(int type, int count, const int64_t *n, int64_t k, int64_t m, const uint8_t *const *tiles, ActView acts, float *const *dst,
+                              const int64_t *lddst, cudaStream_t s) {
     B200_REQUIRE(k % GROUP_K == 0, "gemm: k = %lld must be a multiple of 256", (long long)k);
     B200_REQUIRE(type == B200_TYPE_Q4_K || type == B200_TYPE_Q6_K, "gemm: the fast kernel takes Q4_K and Q6_K, not type %d", type);
-    if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
+    B200_REQUIRE(count >= 1 && count <= 3, "gemm: %d matrices in one launch (1 .. 3)", count);
+    if (m == 0) return B200_STATUS_SUCCESS;
+    FqMats mats;
+    memset(&mats, 0, sizeof(mats));
+    int64_t gy = 0;
+    for (int e = 0; e < count; e++) {
+        if (n[e] == 0) continue;
+        const int c = mats.count++;
+        mats.tiles[c] = tiles[e];
+        mats.dst[c] = dst[e];
+        mats.n[c] = n[e];
+        mats.lddst[c] = lddst[e];
+        mats.rb_start[c] = (int)gy;
+        gy += (n[e] + FQ_ROWS - 1) / FQ_ROWS;
+    }
+    if (mats.count == 0) return B200_STATUS_SUCCESS;
     int *err = nullptr;
     int rc = device_error_word(&err);
     if (rc != B200_STATUS_SUCCESS) return rc;
@@ -663,14 +692,14 @@ int launch_gemm_kq_fast(int type, int64_t n, int64_t k, int64_t m, const uint8_t
     // the 256-wide grid still covers most of the SMs; B200_GEMM_FAST_COLS=128 / 256 overrides (read per call)
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    const int64_t gy = (n + FQ_ROWS - 1) / FQ_ROWS;
     const int64_t ctas256 = gy * ((m + 255) / 256);
     bool wide = m > 128 && ctas256 * 4 >= 3 * (int64_t)sms;
     // too few 256-wide CTAs and long rows: each half of the super-blocks in a CTA of its own (measured: 4096 x 14336 x 512
     // 155 -> 121 us; at 4096 x 4096 the cleared output and the atomic adds cost more than the wider MMAs save: 49 -> 80 us).
-    // B200_GEMM_FAST_KSPLIT=0 / 1 overrides
+    // One matrix only.  B200_GEMM_FAST_KSPLIT=0 / 1 overrides
     int ksplit = 1;
-    if (m > 128 && !wide && (k / GROUP_K) % 2 == 0 && k / GROUP_K >= 32 && ctas256 * 8 >= 3 * (int64_t)sms) {
+    const bool may_split = mats.count == 1 && (k / GROUP_K) % 2 == 0;
+    if (m > 128 && !wide && may_split && k / GROUP_K >= 32 && ctas256 * 8 >= 3 * (int64_t)sms) {
         wide = true;
         ksplit = 2;
     }
@@ -680,13 +709,15 @@ int launch_gemm_kq_fast(int type, int64_t n, int64_t k, int64_t m, const uint8_t
     }
     if (const char *kv = getenv("B200_GEMM_FAST_KSPLIT")) {
         if (kv[0] == '0') ksplit = 1;
-        if (kv[0] == '1' && wide && (k / GROUP_K) % 2 == 0) ksplit = 2;
+        if (kv[0] == '1' && wide && may_split) ksplit = 2;
     }
     if (type == B200_TYPE_Q6_K)
-        return wide ? launch_fast<256, true>(n, k, m, tiles, acts, dst, lddst, err, profile, ksplit, s)
-                    : launch_fast<128, true>(n, k, m, tiles, acts, dst, lddst, err, profile, 1, s);
-    return wide ? launch_fast<256, false>(n, k, m, tiles, acts, dst, lddst, err, profile, ksplit, s)
-                : launch_fast<128, false>(n, k, m, tiles, acts, dst, lddst, err, profile, 1, s);
+        return wide ? launch_fast<256, true>(mats, gy, k, m, acts, err, profile, ksplit, s) : launch_fast<128, true>(mats, gy, k, m, acts, err, profile, 1, s);
+    return wide ? launch_fast<256, false>(mats, gy, k, m, acts, err, profile, ksplit, s) : launch_fast<128, false>(mats, gy, k, m, acts, err, profile, 1, s);
+}
+
+int launch_gemm_kq_fast(int type, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s) {
+    return launch_gemm_kq_fast_multi(type, 1, &n, k, m, &tiles, acts, &dst, &lddst, s);
 }
 
 int launch_gemm_q4_K_fast(int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s) {

@@ -856,6 +856,23 @@ static int64_t gemv_stream_max_tiles() {
     return (int64_t)sms[dev] * gemv_stream_tiles_mult();
 }
 
+// Several Q4_K matrices of one row length against the same activation rows: one launch of the fast-numerics prompt kernel
+// where each of them would take it by itself (the same kernel, so the same bits as separate calls), separate launches
+// otherwise.
+int launch_gemv_rows_multi(int type, int route, int count, const int64_t *n, int64_t k, int64_t m, const uint8_t *const *tiles, ActView acts, float *const *dst,
+                           const int64_t *lddst, cudaStream_t s) {
+    const char *fe = getenv("B200_GEMM_FAST");
+    const bool whole = route == B200_ROUTE_TILED || (route == B200_ROUTE_REPACK && m % 4 == 0);   // no tail rows on another chain
+    if (count > 1 && type == B200_TYPE_Q4_K && whole && m >= GEMM_FAST_MIN_COLS && m >= GEMM_TCGEN05_MIN_COLS && gemm_mma_enabled() && gemm_tcgen05_enabled() &&
+        gemm_tcgen05_f16_choice() < 0 && numerics_mode() == 1 && !no_scratch_mode() && !(fe && fe[0] == '0'))
+        return launch_gemm_kq_fast_multi(type, count, n, k, m, tiles, acts, dst, lddst, s);
+    for (int e = 0; e < count; e++) {
+        int rc = launch_gemv(type, route, n[e], k, m, tiles[e], acts, dst[e], lddst[e], s);
+        if (rc != B200_STATUS_SUCCESS) return rc;
+    }
+    return B200_STATUS_SUCCESS;
+}
+
 int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst,
                 int64_t lddst, cudaStream_t s) {
     B200_REQUIRE(k % GROUP_K == 0, "gemv: k = %lld must be a multiple of 256", (long long)k);

@@ -53,3 +53,36 @@ def test_refusals(dev):
     assert rc != 0 and b"8x8 gemv route" in dev.lib.b200_last_error()
     rc = dev.lib.b200_mul_mat_q8_multi(orc.Q6_K, C.c_int64(512), 1, n_arr, nul, C.c_void_p(1), dev.ACT_Q8_K, nul, None)
     assert rc != 0 and b"Q4_K only" in dev.lib.b200_last_error()
+
+
+@pytest.mark.parametrize("mode", ["fast", "exact"])
+@pytest.mark.parametrize("case", [((1024, 1024, 4096), 4096, 256), ((14336, 14336), 4096, 512), ((4096, 264), 1024, 68), ((520,), 2048, 100)], ids=str)
+def test_rows_multi_equals_single_calls(dev, case, mode):
+    """b200_mul_mat_q8_rows_multi: several Q4_K matrices against the same prompt batch give, bit for bit, what one
+    b200_mul_mat_q8 call per matrix gives: in the fast numerics mode through one launch of the tensor-core kernel, in the
+    exact mode through the CPU chain's kernels"""
+    rows, k, m = case
+    x = synth.activations(m, k, seed=6)
+    Ws = [synth.weights(orc.Q4_K, n, k, seed=20 + i, period=64) for i, n in enumerate(rows)]
+    ws = [dev.Weight(orc.Q4_K, W, k) for W in Ws]
+    dx = dev.device_array(x)
+    kind = dev.act_kind_for(orc.Q4_K, rows[0], m)
+    act = dev.DeviceBuffer(dev.lib.b200_act_scratch_nbytes(m, k))
+    dev.check(dev.lib.b200_quantize_activations_device(kind, m, k, dx.ptr, k, act.ptr, None), "quantize")
+    outs = [dev.DeviceBuffer(4 * n * m) for n in rows]
+    count = len(rows)
+    n_arr = (C.c_int64 * count)(*rows)
+    ld_arr = (C.c_int64 * count)(*rows)
+    w_arr = (C.c_void_p * count)(*[w.ptr for w in ws])
+    d_arr = (C.c_void_p * count)(*[o.ptr for o in outs])
+    dev.set_numerics(dev.FAST if mode == "fast" else dev.EXACT)
+    try:
+        dev.check(dev.lib.b200_mul_mat_q8_rows_multi(orc.Q4_K, C.c_int64(k), C.c_int64(m), count, n_arr, w_arr, C.c_void_p(act.ptr), kind, d_arr, ld_arr, None),
+                  "rows_multi")
+        dev.synchronize()
+        assert dev.kernel_error() == 0
+        for w, o, n in zip(ws, outs, rows):
+            got = o.download(np.float32, n * m).reshape(m, n)
+            assert bits_equal(got, dev.mul_mat(w, x))
+    finally:
+        dev.set_numerics(dev.EXACT)
