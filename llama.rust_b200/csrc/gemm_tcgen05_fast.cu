@@ -688,21 +688,21 @@ int launch_gemm_kq_fast_multi(int type, int count, const int64_t *n, int64_t k, 
     if (rc != B200_STATUS_SUCCESS) return rc;
     const char *pv = getenv("B200_GEMM_FAST_PROFILE");
     const int profile = pv && pv[0] == '1';
-    // 256 activation rows per CTA run the tensor core at its rate (128 at half of it) but halve the CTA count: taken when
-    // the 256-wide grid still covers most of the SMs; B200_GEMM_FAST_COLS=128 / 256 overrides (read per call)
+    // 256 activation rows per CTA run the tensor core at its rate (128 at half of it) but halve the CTA count.  Picked by
+    // rounds of CTAs over the SMs times the measured time of a round (14336 x 4096 x 512: 42 us per round of 128-column
+    // CTAs, 55 us per round of 256-column ones).  Long rows of one matrix may also split their super-blocks over two CTAs
+    // that add onto a cleared output (measured: 4096 x 14336 x 512 155 -> 121 us; at 4096 x 4096 the cleared output and
+    // the atomic adds cost more than the wider MMAs save: 49 -> 80 us).  B200_GEMM_FAST_COLS=128 / 256 and
+    // B200_GEMM_FAST_KSPLIT=0 / 1 override (read per call)
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    const int64_t ctas256 = gy * ((m + 255) / 256);
-    bool wide = m > 128 && ctas256 * 4 >= 3 * (int64_t)sms;
-    // too few 256-wide CTAs and long rows: each half of the super-blocks in a CTA of its own (measured: 4096 x 14336 x 512
-    // 155 -> 121 us; at 4096 x 4096 the cleared output and the atomic adds cost more than the wider MMAs save: 49 -> 80 us).
-    // One matrix only.  B200_GEMM_FAST_KSPLIT=0 / 1 overrides
-    int ksplit = 1;
+    const auto rounds = [sms](int64_t ctas) { return (double)((ctas + sms - 1) / sms); };
+    const int64_t ctas128 = gy * ((m + 127) / 128), ctas256 = gy * ((m + 255) / 256);
     const bool may_split = mats.count == 1 && (k / GROUP_K) % 2 == 0;
-    if (m > 128 && !wide && may_split && k / GROUP_K >= 32 && ctas256 * 8 >= 3 * (int64_t)sms) {
-        wide = true;
-        ksplit = 2;
-    }
+    const double t128 = rounds(ctas128), t256 = m > 128 ? 1.31 * rounds(ctas256) : 1e30;
+    const double t256k = m > 128 && may_split && k / GROUP_K >= 32 ? 0.75 * rounds(2 * ctas256) : 1e30;
+    bool wide = t256 < t128 || t256k < t128;
+    int ksplit = t256k < t128 && t256k < t256 ? 2 : 1;
     if (const char *cv = getenv("B200_GEMM_FAST_COLS")) {
         if (cv[0] == '2') wide = true;
         if (cv[0] == '1') wide = false, ksplit = 1;
