@@ -184,8 +184,9 @@ int b200_mul_mat_q8_multi(int type, int64_t k, int count, const int64_t *n, cons
                           int act_kind, float *const *dev_dst, void *stream);
 /* The same for m activation rows (prompt batches): count (1 .. 3) matrices of one type and row length against the same
  * quantized activations, dev_dst[i] [m][lddst[i]].  All matrices must take the same CPU route for m rows (the route b200_mul_mat_q8 picks under B200_ROUTE_AUTO).
- * Gives exactly what count calls of b200_mul_mat_q8 give; where the fast-numerics prompt kernel applies the matrices
- * share one launch and one expansion of the activations (the q / k / v and gate / up projections of a layer,
+ * In the exact numerics mode it gives exactly what count calls of b200_mul_mat_q8 give; where the fast-numerics prompt
+ * kernel applies the matrices share one launch and one expansion of the activations, and the outputs agree with separate
+ * calls within that mode's tolerance (the kernel's CTAs cut the tiles' f32 sums in other places) (the q / k / v and gate / up projections of a layer,
  * crates/llama/src/graph_arch.rs:171-190,1137-1151). */
 int b200_mul_mat_q8_rows_multi(int type, int64_t k, int64_t m, int count, const int64_t *n, const void *const *dev_w, const void *dev_act, int act_kind,
                                float *const *dev_dst, const int64_t *lddst, void *stream);

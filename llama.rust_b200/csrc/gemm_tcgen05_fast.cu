@@ -172,6 +172,7 @@ struct alignas(16) FqBars {
     float da[FQ_DA_SLOTS][NC];
     uint32_t tmem_base;
     int abort_flag;
+    int seen;   // the epilogue's verdict on a partial tile's flag, for all its warps
 };
 
 // up to three weight matrices of one type and row length against the same activations in one launch (the q / k / v
@@ -192,8 +193,7 @@ __device__ __forceinline__ bool q_mins_apart(float d, float dmin) { return !(fab
 
 // Q8_K activations of one block of NC rows and one super-block -> its B and Bm images and the scales.
 template <int NC, bool Q6>
-__global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q8_K_acts_fast_kernel(ActView acts, uint8_t *bimg, int64_t m, int nb, float *zero_dst, int64_t lddst,
-                                                                                  int64_t n) {
+__global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q8_K_acts_fast_kernel(ActView acts, uint8_t *bimg, int64_t m, int nb) {
     using C = FqCfg<NC, Q6>;
     pdl_trigger();
     pdl_wait();   // the activations come from the previous kernel, and the previous mat-mul may still be reading the images
@@ -242,19 +242,28 @@ __global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q8_K_acts_fast_kerne
         const int64_t dcol = cb * NC + i;
         reinterpret_cast<float *>(img + 4 * C::B_STEP + C::BM_BYTES)[i] = dcol < m ? acts.d[dcol * nb + b] : 0.0f;
     }
-    if (zero_dst) {
-        // the mat-mul adds two halves onto its output: this block clears slice b of the rows of its NC output columns
-        const int64_t r0 = n * b / nb, r1 = n * (b + 1) / nb, len = r1 - r0;
-        for (int64_t i = tid; i < len * NC; i += FQ_EXPAND_THREADS) {
-            const int64_t col = cb * NC + i / len;
-            if (col < m) zero_dst[col * lddst + r0 + i % len] = 0.0f;
-        }
-    }
 }
+
+// Work split.  The mat-mul's work is the list of (output tile, super-block) units, tiles in (row block, column block) order
+// with the column blocks of a row block adjacent; CTA p of P (at most one per SM) takes units U p / P .. U (p + 1) / P - 1, a
+// contiguous run that may begin and end inside a tile.  A run's segment that covers a whole tile stores it.  A segment that
+// begins inside a tile (it can only be the run's first, so it is done early) leaves its partial tile in the CTA's slot of
+// a workspace and raises the CTA's flag; the segment that holds a tile's first super-block but not its last (it can only
+// be the run's last) waits, bounded, for the flags of the CTAs after it that hold the tile's other parts, adds their
+// partial tiles in ascending CTA order and stores: every output is summed in one fixed order whatever the timing.  The
+// flags are lowered again by their reader.  Nobody waits for a CTA that waits, and every CTA is resident (the grid is at
+// most one CTA per SM and a CTA takes an SM's whole shared memory or register file).
+struct FqSplit {
+    float *ws;          // [P][NC columns][128 rows] partial tiles
+    unsigned *flags;    // [P]
+    int gx;             // column blocks
+    int total_tiles;
+};
 
 template <int NC, bool Q6>
 __global__ void __launch_bounds__(FQ_THREADS, 1)
-gemm_kq_tcgen05_fast_kernel(const __grid_constant__ FqMats mats, const uint8_t *__restrict__ bimg, ActView acts, int nb, int64_t m, int *err, int profile) {
+gemm_kq_tcgen05_fast_kernel(const __grid_constant__ FqMats mats, const uint8_t *__restrict__ bimg, ActView acts, int nb, int64_t m, FqSplit sp, int *err,
+                            int profile) {
     using C = FqCfg<NC, Q6>;
     constexpr int S = C::STAGES, CPT = NC / 2;   // columns per epilogue thread
     constexpr int CHUNK = Q6 ? 6720 : 4608;      // bytes of a 32-row tile's super-block
@@ -264,23 +273,31 @@ gemm_kq_tcgen05_fast_kernel(const __grid_constant__ FqMats mats, const uint8_t *
     const uint32_t smem = (q_smem_u32(fq_raw) + 1023u) & ~1023u;
     const uint32_t mslot = smem + (uint32_t)(S * C::STAGE);   // Am | Bm of the super-block whose MMAs run
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int mat = (mats.count > 2 && (int)blockIdx.y >= mats.rb_start[2]) ? 2 : (mats.count > 1 && (int)blockIdx.y >= mats.rb_start[1]) ? 1 : 0;
-    const uint8_t *__restrict__ tiles = mats.tiles[mat];
-    float *dst = mats.dst[mat];
-    const int64_t n = mats.n[mat], lddst = mats.lddst[mat];
-    const int64_t rb = (int)blockIdx.y - mats.rb_start[mat], cb = blockIdx.x;
-    const int64_t tile0 = rb * (FQ_ROWS / TILE_ROWS), tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
-    const int64_t col0 = cb * NC;
-    // gridDim.z = 2: this CTA takes half of the super-blocks and adds its outputs onto a zeroed dst (two addends onto zero:
-    // the same sum in either order)
-    const int nbl = nb / (int)gridDim.z, b_off = (int)blockIdx.z * nbl;
-    const bool split = gridDim.z > 1;
-    const int np = 4 * nbl;   // pipeline steps: sub-block pairs
+    const int P = (int)gridDim.x, pcta = (int)blockIdx.x;
+    const int64_t U = (int64_t)sp.total_tiles * nb;
+    const int64_t u0 = U * pcta / P, u1 = U * (pcta + 1) / P;
+    const int n_sb = (int)(u1 - u0);   // super-blocks of this CTA's run
+    const int np = 4 * n_sb;           // pipeline steps: sub-block pairs
     volatile int *abort_flag = &bars.abort_flag;
-    const bool prof = profile && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0;
+    const bool prof = profile && blockIdx.x == 0 && lane == 0;
     long long t_prev = clock64();
     const long long t_start = t_prev;
     unsigned long long pacc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};   // kept in registers, written once at the end
+    // unit u -> its tile's matrix, row block within it and column block, and the super-block
+    struct Unit {
+        int mat, b;
+        int64_t tile, rb, cb;
+    };
+    const auto unit_of = [&](int64_t u) {
+        Unit x;
+        x.tile = u / nb;
+        x.b = (int)(u - x.tile * nb);
+        const int64_t rbg = x.tile / sp.gx;
+        x.cb = x.tile - rbg * sp.gx;
+        x.mat = (mats.count > 2 && rbg >= mats.rb_start[2]) ? 2 : (mats.count > 1 && rbg >= mats.rb_start[1]) ? 1 : 0;
+        x.rb = rbg - mats.rb_start[x.mat];
+        return x;
+    };
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < S; i++) {
@@ -308,115 +325,186 @@ gemm_kq_tcgen05_fast_kernel(const __grid_constant__ FqMats mats, const uint8_t *
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FQ_REGS_EPI));
         pdl_wait();   // the previous kernels in the stream may still read dst
         const int q = warp & 3, h = warp >> 2;
-        const bool row_ok = tile0 + q < tiles_n;
-        const bool any_col = col0 + CPT * h < m;
-        // (d, dmin) of this thread's row (Q6_K: d), one word per super-block, fetched one super-block ahead
-        const uint8_t *hdr = tiles + ((row_ok ? tile0 + q : 0) * (int64_t)nb + b_off) * CHUNK + (Q6 ? 6656 + lane * 2 : lane * 16);
-        const auto load_dd = [&](int b) -> uint32_t { return Q6 ? (uint32_t) * (const uint16_t *)(hdr + (int64_t)b * CHUNK) : *(const uint32_t *)(hdr + (int64_t)b * CHUNK); };
-        uint32_t dd_next = row_ok ? load_dd(0) : 0u;
-        float2 acc[CPT / 2];
-#pragma unroll
-        for (int c = 0; c < CPT / 2; c++) acc[c] = make_float2(0.0f, 0.0f);
-        bool any_apart = false;
         const uint32_t trow0 = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(CPT * h);
-        for (int b = 0; b < nbl; b++) {
-            const int t = b % FQ_TSTAGES;
-            const float dw = f16_bits_to_f32((uint16_t)(dd_next & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(dd_next >> 16));
-            any_apart |= !Q6 && row_ok && dmw != 0.0f && q_mins_apart(dw, dmw);
-            if (b + 1 < nbl && row_ok) dd_next = load_dd(b + 1);
-            if (warp == 0) FQ_MARK(1);
-            if (!__all_sync(0xffffffffu, q_mbar_wait(q_smem_u32(&bars.tfull[t]), (uint32_t)(b / FQ_TSTAGES) & 1u, abort_flag))) break;
-            if (warp == 0) FQ_MARK(0);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float4 *das = reinterpret_cast<const float4 *>(bars.da[b % FQ_DA_SLOTS] + CPT * h);
-            const uint32_t trow = trow0 + (uint32_t)(t * NC);
-            const float2 dw2 = make_float2(dw, dw), zero2 = make_float2(0.0f, 0.0f);
-            // rounds of 32 columns, one tensor-memory round trip each: acc += (d_x d) v, two columns per instruction
-            uint32_t v[32];
+        float *my_ws = sp.ws + ((size_t)pcta * NC + CPT * h) * FQ_ROWS + 32 * q + lane;   // + column * 128
+        float2 acc[CPT / 2];
+        bool ok = true;
+        int jb = 0;   // super-blocks of the run done so far: tensor-memory stage and scale slot
+        while (jb < n_sb && ok) {
+            // ---- one segment: super-blocks b_first .. b_last of one tile
+            const Unit un = unit_of(u0 + jb);
+            const int b_first = un.b, seg = (nb - b_first) < (n_sb - jb) ? (nb - b_first) : (n_sb - jb), b_last = b_first + seg - 1;
+            const uint8_t *tiles = mats.tiles[un.mat];
+            float *dst = mats.dst[un.mat];
+            const int64_t n = mats.n[un.mat], lddst = mats.lddst[un.mat];
+            const int64_t tile0 = un.rb * (FQ_ROWS / TILE_ROWS), tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS, col0 = un.cb * NC;
+            const bool row_ok = tile0 + q < tiles_n;
+            const bool any_col = col0 + CPT * h < m;
+            // (d, dmin) of this thread's row (Q6_K: d), one word per super-block, fetched one super-block ahead
+            const uint8_t *hdr = tiles + (row_ok ? tile0 + q : 0) * (int64_t)nb * CHUNK + (Q6 ? 6656 + lane * 2 : lane * 16);
+            const auto load_dd = [&](int b) -> uint32_t { return Q6 ? (uint32_t) * (const uint16_t *)(hdr + (int64_t)b * CHUNK) : *(const uint32_t *)(hdr + (int64_t)b * CHUNK); };
+            uint32_t dd_next = row_ok ? load_dd(b_first) : 0u;
 #pragma unroll
-            for (int r = 0; r < CPT / 32; r++) {
-                q_tmem_ld32(v, trow + (uint32_t)(32 * r));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (r == CPT / 32 - 1) {
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) q_mbar_arrive(q_smem_u32(&bars.tempty[t]));
+            for (int c = 0; c < CPT / 2; c++) acc[c] = make_float2(0.0f, 0.0f);
+            bool any_apart = false;
+            for (int b = b_first; b <= b_last; b++, jb++) {
+                const int t = jb % FQ_TSTAGES;
+                const float dw = f16_bits_to_f32((uint16_t)(dd_next & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(dd_next >> 16));
+                any_apart |= !Q6 && row_ok && dmw != 0.0f && q_mins_apart(dw, dmw);
+                if (b < b_last && row_ok) dd_next = load_dd(b + 1);
+                if (warp == 0) FQ_MARK(1);
+                if (!__all_sync(0xffffffffu, q_mbar_wait(q_smem_u32(&bars.tfull[t]), (uint32_t)(jb / FQ_TSTAGES) & 1u, abort_flag))) {
+                    ok = false;
+                    break;
                 }
-                if (any_col) {
+                if (warp == 0) FQ_MARK(0);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const float4 *das = reinterpret_cast<const float4 *>(bars.da[jb % FQ_DA_SLOTS] + CPT * h);
+                const uint32_t trow = trow0 + (uint32_t)(t * NC);
+                const float2 dw2 = make_float2(dw, dw), zero2 = make_float2(0.0f, 0.0f);
+                // rounds of 32 columns, one tensor-memory round trip each: acc += (d_x d) v, two columns per instruction
+                uint32_t v[32];
 #pragma unroll
-                    for (int c4 = 0; c4 < 8; c4++) {
-                        const float4 dq = das[8 * r + c4];
-                        const float2 s0 = q_fma2(make_float2(dq.x, dq.y), dw2, zero2), s1 = q_fma2(make_float2(dq.z, dq.w), dw2, zero2);
-                        acc[16 * r + 2 * c4] = q_fma2(make_float2(__uint_as_float(v[4 * c4]), __uint_as_float(v[4 * c4 + 1])), s0, acc[16 * r + 2 * c4]);
-                        acc[16 * r + 2 * c4 + 1] = q_fma2(make_float2(__uint_as_float(v[4 * c4 + 2]), __uint_as_float(v[4 * c4 + 3])), s1, acc[16 * r + 2 * c4 + 1]);
+                for (int r = 0; r < CPT / 32; r++) {
+                    q_tmem_ld32(v, trow + (uint32_t)(32 * r));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (r == CPT / 32 - 1) {
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) q_mbar_arrive(q_smem_u32(&bars.tempty[t]));
+                    }
+                    if (any_col) {
+#pragma unroll
+                        for (int c4 = 0; c4 < 8; c4++) {
+                            const float4 dq = das[8 * r + c4];
+                            const float2 s0 = q_fma2(make_float2(dq.x, dq.y), dw2, zero2), s1 = q_fma2(make_float2(dq.z, dq.w), dw2, zero2);
+                            acc[16 * r + 2 * c4] = q_fma2(make_float2(__uint_as_float(v[4 * c4]), __uint_as_float(v[4 * c4 + 1])), s0, acc[16 * r + 2 * c4]);
+                            acc[16 * r + 2 * c4 + 1] = q_fma2(make_float2(__uint_as_float(v[4 * c4 + 2]), __uint_as_float(v[4 * c4 + 3])), s1, acc[16 * r + 2 * c4 + 1]);
+                        }
                     }
                 }
             }
-        }
-        const int64_t row = (tile0 + q) * TILE_ROWS + lane;
-        if (row_ok && row < n && !*abort_flag) {
-#pragma unroll
-            for (int c = 0; c < CPT; c++) {
-                const int64_t col = col0 + CPT * h + c;
-                const float v = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
-                if (col < m) {
-                    if (split) atomicAdd(dst + col * lddst + row, v);
-                    else dst[col * lddst + row] = v;
-                }
-            }
-            if (!Q6 && any_apart) {
-                // the super-blocks whose mins the tensor core did not take: out -= d_x dmin sum_j m_j (bsum_2j + bsum_2j+1)
-                for (int b = 0; b < nbl; b++) {
-                    const uint4 hd = *(const uint4 *)(hdr + (int64_t)b * 4608);
-                    const float dw = f16_bits_to_f32((uint16_t)(hd.x & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(hd.x >> 16));
-                    if (dmw == 0.0f || !q_mins_apart(dw, dmw)) continue;
-                    const uint32_t mn0 = hd.z & 0x3f3f3f3fu, mn1 = ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4);
-                    for (int c = 0; c < CPT; c++) {
-                        const int64_t col = col0 + CPT * h + c;
-                        if (col >= m) break;
-                        const int16_t *bs = acts.bsums + col * (acts.k / 16) + (int64_t)(b_off + b) * 16;
-                        int mg = 0;
-                        for (int j = 0; j < 8; j++) mg += (int)(((j < 4 ? mn0 : mn1) >> (8 * (j & 3))) & 0xffu) * ((int)bs[2 * j] + (int)bs[2 * j + 1]);
-                        const float sub = acts.d[col * nb + b_off + b] * dmw * (float)mg;
-                        if (split) atomicAdd(dst + col * lddst + row, -sub);
-                        else dst[col * lddst + row] -= sub;
+            if (!ok) break;
+            // ---- the segment's outputs
+            const int64_t row = (tile0 + q) * TILE_ROWS + lane;
+            const bool partial = b_first > 0;   // begun by an earlier CTA: this one's part goes to the workspace
+            // the super-blocks whose mins the tensor core did not take: -= d_x dmin sum_j m_j (bsum_2j + bsum_2j+1), applied to
+            // what this thread has just stored (its row of the tile, or of the partial tile)
+            const auto mins_apart = [&]() {
+                if constexpr (!Q6) {
+                    if (!(any_apart && row_ok && row < n)) return;
+                    for (int b = b_first; b <= b_last; b++) {
+                        const uint4 hd = *(const uint4 *)(tiles + ((tile0 + q) * (int64_t)nb + b) * CHUNK + lane * 16);
+                        const float dw = f16_bits_to_f32((uint16_t)(hd.x & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(hd.x >> 16));
+                        if (dmw == 0.0f || !q_mins_apart(dw, dmw)) continue;
+                        const uint32_t mn0 = hd.z & 0x3f3f3f3fu, mn1 = ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4);
+                        for (int c = 0; c < CPT; c++) {
+                            const int64_t col = col0 + CPT * h + c;
+                            if (col >= m) break;
+                            const int16_t *bs = acts.bsums + col * (acts.k / 16) + (int64_t)b * 16;
+                            int mg = 0;
+                            for (int j = 0; j < 8; j++) mg += (int)(((j < 4 ? mn0 : mn1) >> (8 * (j & 3))) & 0xffu) * ((int)bs[2 * j] + (int)bs[2 * j + 1]);
+                            const float sub = acts.d[col * nb + b] * dmw * (float)mg;
+                            if (partial) my_ws[(size_t)c * FQ_ROWS] -= sub;
+                            else dst[col * lddst + row] -= sub;
+                        }
                     }
                 }
+            };
+            if (partial) {
+#pragma unroll
+                for (int c = 0; c < CPT; c++) my_ws[(size_t)c * FQ_ROWS] = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
+                mins_apart();
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"n"(FQ_EPI_WARPS * 32) : "memory");
+                if (threadIdx.x == 0) atomicExch(sp.flags + pcta, 1u);
+                continue;
             }
+            if (b_last < nb - 1) {
+                // the tile's first super-blocks, the rest is with the CTAs after this one: their partial tiles, in ascending order
+                int qhi = pcta + 1;
+                while (qhi < P - 1 && U * (qhi + 1) / P < (un.tile + 1) * nb) qhi++;   // the CTA whose run holds the tile's last super-block
+                for (int qq = pcta + 1; qq <= qhi; qq++) {
+                    if (threadIdx.x == 0) {
+                        bool seen = false;
+                        for (uint32_t itw = 0; itw < FQ_WAIT_LIMIT && !seen; itw++) {
+                            seen = *(volatile unsigned *)(sp.flags + qq) != 0u;
+                            if (!seen && (itw & 255) == 255 && *abort_flag) break;
+                        }
+                        if (!seen) *abort_flag = 1;
+                        bars.seen = seen ? 1 : 0;
+                    }
+                    asm volatile("bar.sync 1, %0;" ::"n"(FQ_EPI_WARPS * 32) : "memory");
+                    if (!*(volatile int *)&bars.seen) {
+                        ok = false;
+                        break;
+                    }
+                    __threadfence();
+                    const float *ows = sp.ws + ((size_t)qq * NC + CPT * h) * FQ_ROWS + 32 * q + lane;
+#pragma unroll
+                    for (int c = 0; c < CPT; c += 2) {
+                        acc[c >> 1].x = __fadd_rn(acc[c >> 1].x, __ldcg(ows + (size_t)c * FQ_ROWS));
+                        acc[c >> 1].y = __fadd_rn(acc[c >> 1].y, __ldcg(ows + (size_t)(c + 1) * FQ_ROWS));
+                    }
+                    // every epilogue warp has read the slot: its flag goes down for the next launch
+                    asm volatile("bar.sync 1, %0;" ::"n"(FQ_EPI_WARPS * 32) : "memory");
+                    if (threadIdx.x == 0) atomicExch(sp.flags + qq, 0u);
+                }
+                if (!ok) break;
+            }
+            if (row_ok && row < n) {
+#pragma unroll
+                for (int c = 0; c < CPT; c++) {
+                    const int64_t col = col0 + CPT * h + c;
+                    if (col < m) dst[col * lddst + row] = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
+                }
+            }
+            mins_apart();
         }
     } else if (warp >= FQ_PROD_WARP0) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FQ_REGS_PROD));
+        const int tt = warp - FQ_PROD_WARP0, prow = tt * 32 + lane, sw = prow & 7;
+        uint8_t *stage0 = fq_raw + (smem - q_smem_u32(fq_raw)) + prow * 128;
+        const uint4 zero4 = make_uint4(0, 0, 0, 0);
+        // the row's bytes of super-block unit u0 + js (nullptr past the matrix's last row tile or the run's end)
+        const auto chunk_of = [&](int js) -> const uint8_t * {
+            if (js >= n_sb) return nullptr;
+            const Unit un = unit_of(u0 + js);
+            const int64_t tile = un.rb * (FQ_ROWS / TILE_ROWS) + tt;
+            if (tile >= (mats.n[un.mat] + TILE_ROWS - 1) / TILE_ROWS) return nullptr;
+            return mats.tiles[un.mat] + (tile * (int64_t)nb + un.b) * CHUNK + lane * 16;
+        };
         if constexpr (Q6) {
             // thread = row (tile tt, lane): per step (n, l16) = (g / 2, g % 2) the 16-byte pieces ql[4 n + l16], ql[4 n + 2 + l16] and
             // qh[2 n + l16] of its super-block, loaded two steps ahead (the weights do not depend on the previous kernel)
-            const int tt = warp - FQ_PROD_WARP0, prow = tt * 32 + lane, sw = prow & 7;
-            const bool tile_ok = tile0 + tt < tiles_n;
-            const uint8_t *src = tiles + ((tile_ok ? tile0 + tt : 0) * (int64_t)nb + b_off) * CHUNK + lane * 16;
-            uint8_t *stage0 = fq_raw + (smem - q_smem_u32(fq_raw)) + prow * 128;
-            const uint4 zero4 = make_uint4(0, 0, 0, 0);
             uint4 sc = zero4, sc_next = zero4, w[4][3];
 #pragma unroll
             for (int i = 0; i < 4; i++) w[i][0] = w[i][1] = w[i][2] = zero4;
-            const auto fetch = [&](int p, uint4(&dst3)[3]) {
-                const int g = p & 3, n = g >> 1, l16 = g & 1;
-                const uint8_t *c = src + (int64_t)(p >> 2) * CHUNK;
-                dst3[0] = ld_stream16(c + (4 * n + l16) * 512);
-                dst3[1] = ld_stream16(c + (4 * n + 2 + l16) * 512);
-                dst3[2] = ld_stream16(c + 4096 + (2 * n + l16) * 512);
+            const auto fetch = [&](const uint8_t *c, int g, uint4(&dst3)[3]) {
+                const int n = g >> 1, l16 = g & 1;
+                if (c) {
+                    dst3[0] = ld_stream16(c + (4 * n + l16) * 512);
+                    dst3[1] = ld_stream16(c + (4 * n + 2 + l16) * 512);
+                    dst3[2] = ld_stream16(c + 4096 + (2 * n + l16) * 512);
+                } else {
+                    dst3[0] = dst3[1] = dst3[2] = zero4;
+                }
             };
-            if (tile_ok) {
-                sc_next = *(const uint4 *)(src + 6144);
-                if (0 < np) fetch(0, w[0]);
-                if (1 < np) fetch(1, w[1]);
+            const uint8_t *cur = chunk_of(0), *nxt = chunk_of(1);
+            if (cur) sc_next = *(const uint4 *)(cur + 6144);
+            if (n_sb > 0) {
+                fetch(cur, 0, w[0]);
+                fetch(cur, 1, w[1]);
             }
             bool ok = true;
-            for (int b = 0; b < nbl && ok; b++) {
+            for (int js = 0; js < n_sb && ok; js++) {
                 sc = sc_next;
-                if (b + 1 < nbl && tile_ok) sc_next = *(const uint4 *)(src + (int64_t)(b + 1) * CHUNK + 6144);
+                sc_next = nxt ? *(const uint4 *)(nxt + 6144) : zero4;
 #pragma unroll
                 for (int g = 0; g < 4; g++) {
-                    const int p = 4 * b + g, s = p % S;
-                    if (p + 2 < np && tile_ok) fetch(p + 2, w[(g + 2) & 3]);   // set (g + 2) % 4 was consumed two steps ago
+                    const int p = 4 * js + g, s = p % S;
+                    if (g < 2) fetch(cur, g + 2, w[g + 2]);   // set (g + 2) % 4 was consumed two steps ago
+                    else fetch(nxt, g - 2, w[g - 2]);
                     if (warp == FQ_PROD_WARP0) FQ_MARK(8);
                     if (!__all_sync(0xffffffffu, q_mbar_wait(q_smem_u32(&bars.empty[s]), ((uint32_t)(p / S) & 1u) ^ 1u, abort_flag))) {
                         ok = false;
@@ -460,95 +548,96 @@ gemm_kq_tcgen05_fast_kernel(const __grid_constant__ FqMats mats, const uint8_t *
                     if (lane == 0) q_mbar_arrive(q_smem_u32(&bars.full[s]));
                     if (warp == FQ_PROD_WARP0) FQ_MARK(10);
                 }
+                cur = nxt;
+                nxt = chunk_of(js + 2);
             }
         } else {
-        // thread = row (tile tt, lane): per step the two 16-byte pieces 2 g, 2 g + 1 of its 128 nibble bytes, loaded three steps
-        // ahead into register set (step + 3) % 4 (the weights do not depend on the previous kernel)
-        const int tt = warp - FQ_PROD_WARP0, prow = tt * 32 + lane, sw = prow & 7;
-        const bool tile_ok = tile0 + tt < tiles_n;
-        const uint8_t *src = tiles + ((tile_ok ? tile0 + tt : 0) * (int64_t)nb + b_off) * 4608 + lane * 16;
-        uint8_t *stage0 = fq_raw + (smem - q_smem_u32(fq_raw)) + prow * 128;
-        uint8_t *am = fq_raw + (mslot - q_smem_u32(fq_raw)) + (prow >> 3) * 512 + (prow & 7) * 16;
-        const uint4 zero4 = make_uint4(0, 0, 0, 0);
-        uint4 hd = zero4, hd_next = zero4, w[4][2];
+            // thread = row (tile tt, lane): per step the two 16-byte pieces 2 g, 2 g + 1 of its 128 nibble bytes, loaded three steps
+            // ahead into register set (step + 3) % 4 (the weights do not depend on the previous kernel)
+            uint8_t *am = fq_raw + (mslot - q_smem_u32(fq_raw)) + (prow >> 3) * 512 + (prow & 7) * 16;
+            uint4 hd = zero4, hd_next = zero4, w[4][2];
 #pragma unroll
-        for (int i = 0; i < 4; i++) w[i][0] = w[i][1] = zero4;
-        if (tile_ok) {
-            hd_next = *(const uint4 *)src;
-#pragma unroll
-            for (int i = 0; i < 3; i++) {
-                if (i < np) {
-                    w[i][0] = ld_stream16(src + 512 + (2 * i) * 512);
-                    w[i][1] = ld_stream16(src + 512 + (2 * i + 1) * 512);
+            for (int i = 0; i < 4; i++) w[i][0] = w[i][1] = zero4;
+            const auto fetch = [&](const uint8_t *c, int g, uint4(&dst2)[2]) {
+                if (c) {
+                    dst2[0] = ld_stream16(c + 512 + (2 * g) * 512);
+                    dst2[1] = ld_stream16(c + 512 + (2 * g + 1) * 512);
+                } else {
+                    dst2[0] = dst2[1] = zero4;
                 }
+            };
+            const uint8_t *cur = chunk_of(0), *nxt = chunk_of(1);
+            if (cur) hd_next = *(const uint4 *)cur;
+            if (n_sb > 0) {
+                fetch(cur, 0, w[0]);
+                fetch(cur, 1, w[1]);
+                fetch(cur, 2, w[2]);
             }
-        }
-        bool ok = true;
-        for (int b = 0; b < nbl && ok; b++) {
-            hd = hd_next;
-            if (b + 1 < nbl && tile_ok) hd_next = *(const uint4 *)(src + (int64_t)(b + 1) * 4608);
+            bool ok = true;
+            for (int js = 0; js < n_sb && ok; js++) {
+                hd = hd_next;
+                hd_next = nxt ? *(const uint4 *)nxt : zero4;
 #pragma unroll
-            for (int g = 0; g < 4; g++) {
-                const int p = 4 * b + g, s = p % S;
-                if (p + 3 < np && tile_ok) {   // set (g + 3) % 4 was consumed in the previous step
-                    const uint8_t *nx = src + (int64_t)((p + 3) >> 2) * 4608 + 512 + (2 * ((g + 3) & 3)) * 512;
-                    w[(g + 3) & 3][0] = ld_stream16(nx);
-                    w[(g + 3) & 3][1] = ld_stream16(nx + 512);
-                }
-                if (warp == FQ_PROD_WARP0) FQ_MARK(8);
-                if (!__all_sync(0xffffffffu, q_mbar_wait(q_smem_u32(&bars.empty[s]), ((uint32_t)(p / S) & 1u) ^ 1u, abort_flag))) {
-                    ok = false;
-                    break;
-                }
-                if (warp == FQ_PROD_WARP0) FQ_MARK(7);
-                if (g == 0) {
-                    // the mins slot is free: the stage this step reuses was released by MMAs issued after those of the previous
-                    // super-block's first step.  -rho m_j as high part + remainder; all zero where the drain takes the mins
-                    const float dw = f16_bits_to_f32((uint16_t)(hd.x & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(hd.x >> 16));
-                    const float nrho = (dmw == 0.0f || q_mins_apart(dw, dmw)) ? 0.0f : -(dmw / dw);
-                    const uint32_t mn0 = hd.z & 0x3f3f3f3fu, mn1 = ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4);
-                    uint32_t hi[8], lo[8];
-#pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const float v = nrho * (float)(((j < 4 ? mn0 : mn1) >> (8 * (j & 3))) & 0xffu);
-                        const __half vh = __float2half_rn(v);
-                        const __half vl = __float2half_rn(v - __half2float(vh));
-                        hi[j] = q_h2_bits(__halves2half2(vh, vh));
-                        lo[j] = q_h2_bits(__halves2half2(vl, vl));
+                for (int g = 0; g < 4; g++) {
+                    const int p = 4 * js + g, s = p % S;
+                    if (g == 0) fetch(cur, 3, w[3]);   // set (g + 3) % 4 was consumed in the previous step
+                    else fetch(nxt, g - 1, w[g - 1]);
+                    if (warp == FQ_PROD_WARP0) FQ_MARK(8);
+                    if (!__all_sync(0xffffffffu, q_mbar_wait(q_smem_u32(&bars.empty[s]), ((uint32_t)(p / S) & 1u) ^ 1u, abort_flag))) {
+                        ok = false;
+                        break;
                     }
-                    q_stg128(am, hi[0], hi[1], hi[2], hi[3]);
-                    q_stg128(am + 128, hi[4], hi[5], hi[6], hi[7]);
-                    q_stg128(am + 256, lo[0], lo[1], lo[2], lo[3]);
-                    q_stg128(am + 384, lo[4], lo[5], lo[6], lo[7]);
-                }
-                {
-                    // pair g: sub-blocks 2 g, 2 g + 1
-                    const uint32_t scw = g < 2 ? (hd.y & 0x3f3f3f3fu) : ((hd.w & 0x0f0f0f0fu) | (((hd.y >> 6) & 0x03030303u) << 4));
-                    const uint32_t s_lo = (scw >> (16 * (g & 1))) & 0xffu, s_hi = (scw >> (16 * (g & 1) + 8)) & 0xffu;
-                    const __half2 sl = q_small2(s_lo), sh = q_small2(s_hi);
-                    // -1024 s <= 64512 in magnitude: a multiple of 1024 below 65504, exact in f16
-                    const __half2 cl = __hmul2(sl, __float2half2_rn(-1024.0f)), ch = __hmul2(sh, __float2half2_rn(-64.0f));
-                    const __half2 sh16 = __hmul2(sh, __float2half2_rn(0.0625f));
-                    uint8_t *dstp = stage0 + s * C::STAGE;
+                    if (warp == FQ_PROD_WARP0) FQ_MARK(7);
+                    if (g == 0) {
+                        // the mins slot is free: the stage this step reuses was released by MMAs issued after those of the previous
+                        // super-block's first step.  -rho m_j as high part + remainder; all zero where the drain takes the mins
+                        const float dw = f16_bits_to_f32((uint16_t)(hd.x & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(hd.x >> 16));
+                        const float nrho = (dmw == 0.0f || q_mins_apart(dw, dmw)) ? 0.0f : -(dmw / dw);
+                        const uint32_t mn0 = hd.z & 0x3f3f3f3fu, mn1 = ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4);
+                        uint32_t hi[8], lo[8];
 #pragma unroll
-                    for (int i = 0; i < 2; i++) {
-                        const uint4 x = w[g][i];
-                        const uint32_t x8 = x.x >> 8, y8 = x.y >> 8, z8 = x.z >> 8, w8 = x.w >> 8;   // bytes 1 and 3
-                        const int c0 = 4 * i;
-                        q_stg128(dstp + (((c0 + 0) ^ sw) << 4), q_scaled_lo(x.x, sl, cl), q_scaled_lo(x8, sl, cl), q_scaled_lo(x.y, sl, cl), q_scaled_lo(y8, sl, cl));
-                        q_stg128(dstp + (((c0 + 1) ^ sw) << 4), q_scaled_lo(x.z, sl, cl), q_scaled_lo(z8, sl, cl), q_scaled_lo(x.w, sl, cl), q_scaled_lo(w8, sl, cl));
-                        q_stg128(dstp + (((c0 + 2) ^ sw) << 4), q_scaled_hi(x.x, sh16, ch), q_scaled_hi(x8, sh16, ch), q_scaled_hi(x.y, sh16, ch), q_scaled_hi(y8, sh16, ch));
-                        q_stg128(dstp + (((c0 + 3) ^ sw) << 4), q_scaled_hi(x.z, sh16, ch), q_scaled_hi(z8, sh16, ch), q_scaled_hi(x.w, sh16, ch), q_scaled_hi(w8, sh16, ch));
+                        for (int j = 0; j < 8; j++) {
+                            const float v = nrho * (float)(((j < 4 ? mn0 : mn1) >> (8 * (j & 3))) & 0xffu);
+                            const __half vh = __float2half_rn(v);
+                            const __half vl = __float2half_rn(v - __half2float(vh));
+                            hi[j] = q_h2_bits(__halves2half2(vh, vh));
+                            lo[j] = q_h2_bits(__halves2half2(vl, vl));
+                        }
+                        q_stg128(am, hi[0], hi[1], hi[2], hi[3]);
+                        q_stg128(am + 128, hi[4], hi[5], hi[6], hi[7]);
+                        q_stg128(am + 256, lo[0], lo[1], lo[2], lo[3]);
+                        q_stg128(am + 384, lo[4], lo[5], lo[6], lo[7]);
                     }
+                    {
+                        // pair g: sub-blocks 2 g, 2 g + 1
+                        const uint32_t scw = g < 2 ? (hd.y & 0x3f3f3f3fu) : ((hd.w & 0x0f0f0f0fu) | (((hd.y >> 6) & 0x03030303u) << 4));
+                        const uint32_t s_lo = (scw >> (16 * (g & 1))) & 0xffu, s_hi = (scw >> (16 * (g & 1) + 8)) & 0xffu;
+                        const __half2 sl = q_small2(s_lo), sh = q_small2(s_hi);
+                        // -1024 s <= 64512 in magnitude: a multiple of 1024 below 65504, exact in f16
+                        const __half2 cl = __hmul2(sl, __float2half2_rn(-1024.0f)), ch = __hmul2(sh, __float2half2_rn(-64.0f));
+                        const __half2 sh16 = __hmul2(sh, __float2half2_rn(0.0625f));
+                        uint8_t *dstp = stage0 + s * C::STAGE;
+#pragma unroll
+                        for (int i = 0; i < 2; i++) {
+                            const uint4 x = w[g][i];
+                            const uint32_t x8 = x.x >> 8, y8 = x.y >> 8, z8 = x.z >> 8, w8 = x.w >> 8;   // bytes 1 and 3
+                            const int c0 = 4 * i;
+                            q_stg128(dstp + (((c0 + 0) ^ sw) << 4), q_scaled_lo(x.x, sl, cl), q_scaled_lo(x8, sl, cl), q_scaled_lo(x.y, sl, cl), q_scaled_lo(y8, sl, cl));
+                            q_stg128(dstp + (((c0 + 1) ^ sw) << 4), q_scaled_lo(x.z, sl, cl), q_scaled_lo(z8, sl, cl), q_scaled_lo(x.w, sl, cl), q_scaled_lo(w8, sl, cl));
+                            q_stg128(dstp + (((c0 + 2) ^ sw) << 4), q_scaled_hi(x.x, sh16, ch), q_scaled_hi(x8, sh16, ch), q_scaled_hi(x.y, sh16, ch), q_scaled_hi(y8, sh16, ch));
+                            q_stg128(dstp + (((c0 + 3) ^ sw) << 4), q_scaled_hi(x.z, sh16, ch), q_scaled_hi(z8, sh16, ch), q_scaled_hi(x.w, sh16, ch), q_scaled_hi(w8, sh16, ch));
+                        }
+                    }
+                    if (warp == FQ_PROD_WARP0) FQ_MARK(9);
+                    // the stores (generic proxy) before the tensor core's reads (async proxy), then the warp's arrival
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) q_mbar_arrive(q_smem_u32(&bars.full[s]));
+                    if (warp == FQ_PROD_WARP0) FQ_MARK(10);
                 }
-                if (warp == FQ_PROD_WARP0) FQ_MARK(9);
-                // the stores (generic proxy) before the tensor core's reads (async proxy), then the warp's arrival
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) q_mbar_arrive(q_smem_u32(&bars.full[s]));
-                if (warp == FQ_PROD_WARP0) FQ_MARK(10);
+                cur = nxt;
+                nxt = chunk_of(js + 2);
             }
-        }
         }
     } else {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FQ_REGS_CTL));
@@ -556,11 +645,11 @@ gemm_kq_tcgen05_fast_kernel(const __grid_constant__ FqMats mats, const uint8_t *
         if (warp == FQ_MMA_WARP) {
             if (lane == 0) {
                 for (int p = 0; p < np; p++) {
-                    const int s = p % S, b = p >> 2, g = p & 3, t = b % FQ_TSTAGES;
+                    const int s = p % S, jb = p >> 2, g = p & 3, t = jb % FQ_TSTAGES;
                     FQ_MARK(4);
                     if (!q_mbar_wait(q_smem_u32(&bars.full[s]), (uint32_t)(p / S) & 1u, abort_flag)) break;
                     FQ_MARK(2);
-                    if (g == 0 && !q_mbar_wait(q_smem_u32(&bars.tempty[t]), ((uint32_t)(b / FQ_TSTAGES) & 1u) ^ 1u, abort_flag)) break;
+                    if (g == 0 && !q_mbar_wait(q_smem_u32(&bars.tempty[t]), ((uint32_t)(jb / FQ_TSTAGES) & 1u) ^ 1u, abort_flag)) break;
                     FQ_MARK(3);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t a_base = smem + (uint32_t)(s * C::STAGE), b_base = a_base + C::A_STEP;
@@ -589,23 +678,26 @@ gemm_kq_tcgen05_fast_kernel(const __grid_constant__ FqMats mats, const uint8_t *
                 }
             }
         } else if (warp == FQ_LOAD_WARP && lane == 0) {
-            const uint8_t *bsrc = bimg + (cb * nb + b_off) * (int64_t)C::BIMG;
             int issued = -1;
+            const uint8_t *bb = nullptr;
             for (int p = 0; p < np; p++) {
-                const int s = p % S, b = p >> 2, g = p & 3;
+                const int s = p % S, jb = p >> 2, g = p & 3;
+                if (g == 0) {
+                    const Unit un = unit_of(u0 + jb);
+                    bb = bimg + (un.cb * nb + un.b) * (int64_t)C::BIMG;
+                }
                 FQ_MARK(6);
                 if (!q_mbar_wait(q_smem_u32(&bars.empty[s]), ((uint32_t)(p / S) & 1u) ^ 1u, abort_flag)) break;
                 FQ_MARK(5);
                 const uint32_t bar = q_smem_u32(&bars.full[s]), stage = smem + (uint32_t)(s * C::STAGE);
-                const uint8_t *bb = bsrc + (int64_t)b * C::BIMG;
                 q_mbar_expect(bar, (uint32_t)(C::B_STEP + (g == 0 ? C::BM_BYTES + C::DA_BYTES : 0)));
                 q_bulk_load(stage + C::A_STEP, bb + g * C::B_STEP, C::B_STEP, bar);
                 if (g == 0) {
                     // the mins slot: with at most four stages the stage this step reuses belonged to a step of the previous
                     // super-block no earlier than its first, so that super-block's mins MMAs are done; the scale slot of
-                    // super-block b - 4: its drain ended before the MMAs of b - 2 began
+                    // super-block jb - 4: its drain ended before the MMAs of jb - 2 began
                     if constexpr (!Q6) q_bulk_load(mslot + FQ_AM_BYTES, bb + 4 * C::B_STEP, C::BM_BYTES, bar);
-                    q_bulk_load(q_smem_u32(bars.da[b % FQ_DA_SLOTS]), bb + 4 * C::B_STEP + C::BM_BYTES, C::DA_BYTES, bar);
+                    q_bulk_load(q_smem_u32(bars.da[jb % FQ_DA_SLOTS]), bb + 4 * C::B_STEP + C::BM_BYTES, C::DA_BYTES, bar);
                 }
                 issued = p;
             }
@@ -637,29 +729,50 @@ int gemm_fast_profile(unsigned long long *out, int n) {
     return B200_STATUS_SUCCESS;
 }
 
+// flags of the partial tiles: one word per CTA of the grid, all zero between launches (a module variable: no allocation)
+__device__ unsigned g_fq_flags[1024];
+
 template <int NC, bool Q6>
-static int launch_fast(const FqMats &mats, int64_t gy, int64_t k, int64_t m, ActView acts, int *err, int profile, int ksplit, cudaStream_t s) {
+static int launch_fast(const FqMats &mats, int64_t gy, int64_t k, int64_t m, ActView acts, int *err, int profile, int sms, cudaStream_t s) {
     using C = FqCfg<NC, Q6>;
     static bool attr_done[64] = {false};
+    static unsigned *flags[64] = {nullptr};
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
     B200_REQUIRE(dev >= 0 && dev < 64, "gemm: device index %d out of range", dev);
     if (!attr_done[dev]) {
         B200_CUDA(cudaFuncSetAttribute(gemm_kq_tcgen05_fast_kernel<NC, Q6>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        void *fp = nullptr;
+        B200_CUDA(cudaGetSymbolAddress(&fp, g_fq_flags));
+        flags[dev] = (unsigned *)fp;
         attr_done[dev] = true;
     }
     const int nb = (int)(k / GROUP_K);
     const int64_t gx = (m + NC - 1) / NC;
-    B200_REQUIRE(gx <= 65535 && gy <= 65535, "gemm: %lld row blocks x %lld column blocks are too many for one launch", (long long)gy, (long long)gx);
+    B200_REQUIRE(gx <= 65535 && gy * gx < (1ll << 31) / nb, "gemm: %lld row blocks x %lld column blocks are too many for one launch", (long long)gy, (long long)gx);
+    // one CTA per SM, each a contiguous run of (tile, super-block) units; B200_GEMM_FAST_CTAS=<n> sets another count (read per
+    // call; the tests use it to cut tiles in odd places)
+    const int64_t units = gy * gx * nb;
+    int64_t ctas = units < sms ? units : sms;
+    if (const char *cv = getenv("B200_GEMM_FAST_CTAS")) {
+        const long v = atol(cv);
+        if (v >= 1 && v <= sms && v <= units) ctas = v;
+    }
+    B200_REQUIRE(ctas <= 1024, "gemm: %lld CTAs exceed the partial-tile flags", (long long)ctas);
+    const size_t img_bytes = (size_t)gx * nb * C::BIMG, ws_bytes = (size_t)ctas * NC * FQ_ROWS * 4;
     void *block = nullptr;
-    int rc = scratch_get_images((size_t)gx * nb * C::BIMG, &block);
+    int rc = scratch_get_images(img_bytes + ws_bytes, &block);
     if (rc != B200_STATUS_SUCCESS) return rc;
     uint8_t *bimg = (uint8_t *)block;
-    rc = launch_pdl(expand_q8_K_acts_fast_kernel<NC, Q6>, dim3((unsigned)nb, (unsigned)gx), dim3(FQ_EXPAND_THREADS), (size_t)0, s, acts, bimg, m, nb,
-                    ksplit > 1 ? mats.dst[0] : (float *)nullptr, mats.lddst[0], mats.n[0]);
+    FqSplit sp;
+    sp.ws = (float *)(bimg + img_bytes);
+    sp.flags = flags[dev];
+    sp.gx = (int)gx;
+    sp.total_tiles = (int)(gy * gx);
+    rc = launch_pdl(expand_q8_K_acts_fast_kernel<NC, Q6>, dim3((unsigned)nb, (unsigned)gx), dim3(FQ_EXPAND_THREADS), (size_t)0, s, acts, bimg, m, nb);
     if (rc != B200_STATUS_SUCCESS) return rc;
-    return launch_pdl(gemm_kq_tcgen05_fast_kernel<NC, Q6>, dim3((unsigned)gx, (unsigned)gy, (unsigned)ksplit), dim3(FQ_THREADS), (size_t)C::SMEM, s, mats,
-                      (const uint8_t *)bimg, acts, nb, m, err, profile);
+    return launch_pdl(gemm_kq_tcgen05_fast_kernel<NC, Q6>, dim3((unsigned)ctas), dim3(FQ_THREADS), (size_t)C::SMEM, s, mats, (const uint8_t *)bimg, acts, nb, m, sp,
+                      err, profile);
 }
 
 // type: B200_TYPE_Q4_K or B200_TYPE_Q6_K; count matrices (1 .. 3) of that type and row length k over the same m activation rows
@@ -688,32 +801,15 @@ int launch_gemm_kq_fast_multi(int type, int count, const int64_t *n, int64_t k, 
     if (rc != B200_STATUS_SUCCESS) return rc;
     const char *pv = getenv("B200_GEMM_FAST_PROFILE");
     const int profile = pv && pv[0] == '1';
-    // 256 activation rows per CTA run the tensor core at its rate (128 at half of it) but halve the CTA count.  Picked by
-    // rounds of CTAs over the SMs times the measured time of a round (14336 x 4096 x 512: 42 us per round of 128-column
-    // CTAs, 55 us per round of 256-column ones).  Long rows of one matrix may also split their super-blocks over two CTAs
-    // that add onto a cleared output (measured: 4096 x 14336 x 512 155 -> 121 us; at 4096 x 4096 the cleared output and
-    // the atomic adds cost more than the wider MMAs save: 49 -> 80 us).  B200_GEMM_FAST_COLS=128 / 256 and
-    // B200_GEMM_FAST_KSPLIT=0 / 1 override (read per call)
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    const auto rounds = [sms](int64_t ctas) { return (double)((ctas + sms - 1) / sms); };
-    const int64_t ctas128 = gy * ((m + 127) / 128), ctas256 = gy * ((m + 255) / 256);
-    const bool may_split = mats.count == 1 && (k / GROUP_K) % 2 == 0;
-    const double t128 = rounds(ctas128), t256 = m > 128 ? 1.31 * rounds(ctas256) : 1e30;
-    const double t256k = m > 128 && may_split && k / GROUP_K >= 32 ? 0.75 * rounds(2 * ctas256) : 1e30;
-    bool wide = t256 < t128 || t256k < t128;
-    int ksplit = t256k < t128 && t256k < t256 ? 2 : 1;
-    if (const char *cv = getenv("B200_GEMM_FAST_COLS")) {
-        if (cv[0] == '2') wide = true;
-        if (cv[0] == '1') wide = false, ksplit = 1;
-    }
-    if (const char *kv = getenv("B200_GEMM_FAST_KSPLIT")) {
-        if (kv[0] == '0') ksplit = 1;
-        if (kv[0] == '1' && wide && may_split) ksplit = 2;
-    }
+    // 256 activation rows per CTA run the tensor core at its rate (an M 128 x K 16 MMA takes 128 cycles whatever N <= 256 is):
+    // taken whenever there are more than 128 rows.  B200_GEMM_FAST_COLS=128 / 256 overrides (read per call)
+    bool wide = m > 128;
+    if (const char *cv = getenv("B200_GEMM_FAST_COLS")) wide = cv[0] == '2' ? true : cv[0] == '1' ? false : wide;
     if (type == B200_TYPE_Q6_K)
-        return wide ? launch_fast<256, true>(mats, gy, k, m, acts, err, profile, ksplit, s) : launch_fast<128, true>(mats, gy, k, m, acts, err, profile, 1, s);
-    return wide ? launch_fast<256, false>(mats, gy, k, m, acts, err, profile, ksplit, s) : launch_fast<128, false>(mats, gy, k, m, acts, err, profile, 1, s);
+        return wide ? launch_fast<256, true>(mats, gy, k, m, acts, err, profile, sms, s) : launch_fast<128, true>(mats, gy, k, m, acts, err, profile, sms, s);
+    return wide ? launch_fast<256, false>(mats, gy, k, m, acts, err, profile, sms, s) : launch_fast<128, false>(mats, gy, k, m, acts, err, profile, sms, s);
 }
 
 int launch_gemm_kq_fast(int type, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst, cudaStream_t s) {

@@ -857,8 +857,8 @@ static int64_t gemv_stream_max_tiles() {
 }
 
 // Several Q4_K matrices of one row length against the same activation rows: one launch of the fast-numerics prompt kernel
-// where each of them would take it by itself (the same kernel, so the same bits as separate calls), separate launches
-// otherwise.
+// where each of them would take it by itself (the same kernel and tolerance; its CTAs cut the tiles' f32 sums in other
+// places than separate launches would), separate launches otherwise.
 int launch_gemv_rows_multi(int type, int route, int count, const int64_t *n, int64_t k, int64_t m, const uint8_t *const *tiles, ActView acts, float *const *dst,
                            const int64_t *lddst, cudaStream_t s) {
     const char *fe = getenv("B200_GEMM_FAST");

@@ -29,12 +29,15 @@ def dev():
 
 
 def pick_kernel(monkeypatch, form):
-    """128 or 256 activation rows per CTA; "256k": 256 with the super-blocks split over two CTAs"""
-    monkeypatch.setenv("B200_GEMM_FAST_COLS", form[:3])
-    monkeypatch.setenv("B200_GEMM_FAST_KSPLIT", "1" if form.endswith("k") else "0")
+    """128 or 256 activation rows per CTA; "/n": n CTAs instead of one per SM, so that the runs of (tile, super-block) units
+    cut the tiles in other places (partial tiles through the workspace, several CTAs per tile, several tiles per CTA)"""
+    cols, _, ctas = form.partition("/")
+    monkeypatch.setenv("B200_GEMM_FAST_COLS", cols)
+    if ctas:
+        monkeypatch.setenv("B200_GEMM_FAST_CTAS", ctas)
 
 
-FORMS = ["128", "256", "256k"]
+FORMS = ["128", "256", "256/7", "128/37", "256/3"]
 
 
 @pytest.mark.parametrize("form", FORMS)

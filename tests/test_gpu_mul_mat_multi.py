@@ -58,9 +58,10 @@ def test_refusals(dev):
 @pytest.mark.parametrize("mode", ["fast", "exact"])
 @pytest.mark.parametrize("case", [((1024, 1024, 4096), 4096, 256), ((14336, 14336), 4096, 512), ((4096, 264), 1024, 68), ((520,), 2048, 100)], ids=str)
 def test_rows_multi_equals_single_calls(dev, case, mode):
-    """b200_mul_mat_q8_rows_multi: several Q4_K matrices against the same prompt batch give, bit for bit, what one
-    b200_mul_mat_q8 call per matrix gives: in the fast numerics mode through one launch of the tensor-core kernel, in the
-    exact mode through the CPU chain's kernels"""
+    """b200_mul_mat_q8_rows_multi: several Q4_K matrices against the same prompt batch give what one b200_mul_mat_q8 call
+    per matrix gives: bit for bit in the exact numerics mode (the CPU chain's kernels); in the fast mode one launch of the
+    tensor-core kernel, whose CTAs cut the tiles' super-block sums in other places than a launch per matrix does, so the
+    f32 sums associate differently: held to a tenth of the mode's tolerance of 1e-5 sum |w x|"""
     rows, k, m = case
     x = synth.activations(m, k, seed=6)
     Ws = [synth.weights(orc.Q4_K, n, k, seed=20 + i, period=64) for i, n in enumerate(rows)]
@@ -81,8 +82,13 @@ def test_rows_multi_equals_single_calls(dev, case, mode):
                   "rows_multi")
         dev.synchronize()
         assert dev.kernel_error() == 0
-        for w, o, n in zip(ws, outs, rows):
+        for W, w, o, n in zip(Ws, ws, outs, rows):
             got = o.download(np.float32, n * m).reshape(m, n)
-            assert bits_equal(got, dev.mul_mat(w, x))
+            single = dev.mul_mat(w, x)
+            if mode == "exact":
+                assert bits_equal(got, single)
+            else:
+                bound = 1e-6 * (np.abs(x).astype(np.float64) @ np.abs(orc.dequantize(orc.Q4_K, W, k)).astype(np.float64).T)
+                assert (np.abs(got.astype(np.float64) - single.astype(np.float64)) <= bound).all()
     finally:
         dev.set_numerics(dev.EXACT)
