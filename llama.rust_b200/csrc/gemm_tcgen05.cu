@@ -703,10 +703,12 @@ int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t
     if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
     int choice = gemm_tcgen05_f16_choice();
     // fast numerics: one tensor-memory drain per super-block instead of the CPU chain's per-pair fused multiply-adds
-    // (within 1e-5 of sum |w x|, both routes); B200_GEMM_FAST=0 keeps the exact kernels (read per call)
+    // (within 1e-5 of sum |w x|, both routes), from 2048 weight rows (1024 x 4096 x 512: 38.9 us on the exact kernels, 55.9 on
+    // the fast one, whose fixed costs a matrix of sixteen tiles does not repay); B200_GEMM_FAST=0 keeps the exact kernels,
+    // =2 lifts the row limit (read per call)
     if (choice < 0 && numerics_mode() == 1 && m >= GEMM_FAST_MIN_COLS && !no_scratch_mode()) {
         const char *e = getenv("B200_GEMM_FAST");
-        if (!(e && e[0] == '0')) return launch_gemm_q4_K_fast(n, k, m, tiles, acts, dst, lddst, s);
+        if (!(e && e[0] == '0') && (n >= 2048 || (e && e[0] == '2'))) return launch_gemm_q4_K_fast(n, k, m, tiles, acts, dst, lddst, s);
     }
     if (mode == 1 && choice < 0) choice = gemm_chain_pick(n, m);
     if (no_scratch_mode() && (choice == 3 || choice == 4)) choice = 0;   // the two-pass kernels need the image block

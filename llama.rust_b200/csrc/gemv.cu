@@ -863,7 +863,9 @@ int launch_gemv_rows_multi(int type, int route, int count, const int64_t *n, int
                            const int64_t *lddst, cudaStream_t s) {
     const char *fe = getenv("B200_GEMM_FAST");
     const bool whole = route == B200_ROUTE_TILED || (route == B200_ROUTE_REPACK && m % 4 == 0);   // no tail rows on another chain
-    if (count > 1 && type == B200_TYPE_Q4_K && whole && m >= GEMM_FAST_MIN_COLS && m >= GEMM_TCGEN05_MIN_COLS && gemm_mma_enabled() && gemm_tcgen05_enabled() &&
+    int64_t rows = 0;
+    for (int e = 0; e < count; e++) rows += n[e];
+    if (count > 1 && type == B200_TYPE_Q4_K && whole && (rows >= 2048 || (fe && fe[0] == '2')) && m >= GEMM_FAST_MIN_COLS && m >= GEMM_TCGEN05_MIN_COLS && gemm_mma_enabled() && gemm_tcgen05_enabled() &&
         gemm_tcgen05_f16_choice() < 0 && numerics_mode() == 1 && !no_scratch_mode() && !(fe && fe[0] == '0'))
         return launch_gemm_kq_fast_multi(type, count, n, k, m, tiles, acts, dst, lddst, s);
     for (int e = 0; e < count; e++) {

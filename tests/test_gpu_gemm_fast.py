@@ -45,6 +45,7 @@ FORMS = ["128", "256", "256/7", "128/37", "256/3"]
 def test_q4_K_fast_mode_within_the_mat_mul_tolerance(dev, shape, form, monkeypatch):
     n, k, m = shape
     pick_kernel(monkeypatch, form)
+    monkeypatch.setenv("B200_GEMM_FAST", "2")   # the fast kernel whatever the row count
     W = synth.weights(orc.Q4_K, n, k, seed=420, period=512)
     x = synth.activations(m, k, seed=421 + m)
     want, _ = orc.mul_mat(orc.Q4_K, W, x)
@@ -129,6 +130,7 @@ def test_q4_K_fast_mode_blocks_with_odd_scales(dev, form, monkeypatch):
     x = synth.activations(m, k, seed=441)
     want, _ = orc.mul_mat(orc.Q4_K, W, x)
     pick_kernel(monkeypatch, form)
+    monkeypatch.setenv("B200_GEMM_FAST", "2")
     dev.set_numerics(dev.FAST)
     try:
         got = dev.mul_mat(dev.Weight(orc.Q4_K, W, k), x)
