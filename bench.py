@@ -684,8 +684,23 @@ def run_sweep(b):
             dx, do = b.device_array(x), b.DeviceBuffer(4 * n * m)
             ms = event_time(b, lambda: b.mul_mat_device(w, dx, m, do), 5 if name in ("Q8_0", "MXFP4") and m == 2048 else 10)
             tops = 2.0 * n * k * m / ms / 1e9
-            entry[f"m{m}"] = {"shape": f"{n}x{k}", "us": ms * 1e3, "tops": tops, "frac_int8_peak": tops / (2 * tc),
-                              "includes": "activation quantization + mat-mul, device-resident f32 in and out"}
+            entry[f"m{m}"] = {"shape": f"{n}x{k}", "us": ms * 1e3, "tops": tops, "frac_int8_peak": tops / (2 * tc), "frac_bf16_peak": tops / tc,
+                              "includes": "activation quantization + mat-mul, device-resident f32 in and out",
+                              "note": "Q4_K / Q6_K under the fast numerics policy run f16 MMAs (compare with the bf16 peak), the others int8 MMAs"}
+            if m == 512 and name in ("Q4_K", "Q6_K", "Q8_0"):
+                # the fast numerics mode's distance from the exact mode (= the CPU route's bits), as the reference defines
+                # the mat-mul tolerance: |fast - exact| / sum_k |w_k x_k| per output, over the first 256 weight rows
+                before = b.get_numerics()
+                fast = do.download(np.float32, n * m).reshape(m, n)[:, :256].astype(np.float64)
+                b.set_numerics(b.EXACT)
+                t0 = event_time(b, lambda: b.mul_mat_device(w, dx, m, do), 3)
+                exact = do.download(np.float32, n * m).reshape(m, n)[:, :256].astype(np.float64)
+                b.set_numerics(before)
+                wd = b.Weight(ty, w.download()[:256], k).dequantize().astype(np.float64)
+                denom = np.abs(x).astype(np.float64) @ np.abs(wd).T
+                entry[f"m{m}"].update({"exact_numerics_us": t0 * 1e3,
+                                       "max_fast_minus_exact_over_sum_abs_wx": float((np.abs(fast - exact) / np.maximum(denom, 1e-30)).max()),
+                                       "tolerance": 1e-5})
         del w
         mm[name] = entry
     out["mul_mat"] = mm
