@@ -39,8 +39,8 @@ METRIC = "q4_K_decode_mat_mul_hbm_gbs"
 CPU_KIND = "port-simd"
 SIMD_NAMES = {0: "scalar", 1: "AVX2", 2: "AVX-512 VNNI"}
 # measured DRAM bytes / algorithmic bytes of one launch of the decode kernel in use (gemv_q4_K_row_kernel on
-# 14336 x 4096: dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture summarized in
-# profiles/gemv_q4_K_row_kernel_decode.md); weights are read once whatever the shape
+# 14336 x 4096: dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture whose summary is kept with the other
+# profile summaries); weights are read once whatever the shape
 NCU_TRAFFIC_RATIO = 33.052416 / 33.103872
 PROMPT, GEN = 512, 128
 
