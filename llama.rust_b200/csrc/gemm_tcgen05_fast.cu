@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q8_K_acts_fast_kerne
     pdl_trigger();
     pdl_wait();   // the activations come from the previous kernel, and the previous mat-mul may still be reading the images
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
-    const int b = blockIdx.x;
+    const int b = blockIdx.x >> 2, g = blockIdx.x & 3;   // a CTA per (super-block, step): the launch is latency, not bytes
     const int64_t cb = blockIdx.y, K = acts.k;
     uint8_t *img = bimg + (cb * nb + b) * (int64_t)C::BIMG;
     // a warp reads 64 contiguous bytes (one pair) of 8 activation rows; piece r of the pair: (low p0, low p1, high p0,
@@ -209,8 +209,7 @@ __global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q8_K_acts_fast_kerne
         const int bc = rr * 128 + warp * 8 + (lane & 7), sw = bc & 7;
         const int64_t col = cb * NC + bc;
         uint8_t *rowp = img + bc * 128;
-#pragma unroll
-        for (int g = 0; g < 4; g++) {
+        {
             uint4 y = make_uint4(0, 0, 0, 0);
             // Q4_K: step g = pair g, piece r of its 64 bytes.  Q6_K: step g = (n, l16) = (g / 2, g % 2), piece r = run r
             const int src_off = Q6 ? 128 * (g >> 1) + 32 * r + 16 * (g & 1) : g * 64 + r * 16;
@@ -222,6 +221,7 @@ __global__ void __launch_bounds__(FQ_EXPAND_THREADS) expand_q8_K_acts_fast_kerne
             q_stg128(dstp + (((c0 + 1) ^ sw) << 4), q_signed(u2, 0), q_signed(u2, 8), q_signed(u3, 0), q_signed(u3, 8));
         }
     }
+    if (g != 0) return;   // the step-0 CTA also writes the super-block's sums and scales
     for (int i = tid; i < (Q6 ? 0 : 2 * NC); i += FQ_EXPAND_THREADS) {
         // sums: (row i / 2, half i % 2): eight 16-element sums -> one core-matrix row, written twice (K slots 0..15, 16..31)
         const int scol_i = i >> 1, kc = i & 1;
@@ -769,7 +769,7 @@ static int launch_fast(const FqMats &mats, int64_t gy, int64_t k, int64_t m, Act
     sp.flags = flags[dev];
     sp.gx = (int)gx;
     sp.total_tiles = (int)(gy * gx);
-    rc = launch_pdl(expand_q8_K_acts_fast_kernel<NC, Q6>, dim3((unsigned)nb, (unsigned)gx), dim3(FQ_EXPAND_THREADS), (size_t)0, s, acts, bimg, m, nb);
+    rc = launch_pdl(expand_q8_K_acts_fast_kernel<NC, Q6>, dim3((unsigned)(4 * nb), (unsigned)gx), dim3(FQ_EXPAND_THREADS), (size_t)0, s, acts, bimg, m, nb);
     if (rc != B200_STATUS_SUCCESS) return rc;
     return launch_pdl(gemm_kq_tcgen05_fast_kernel<NC, Q6>, dim3((unsigned)ctas), dim3(FQ_THREADS), (size_t)C::SMEM, s, mats, (const uint8_t *)bimg, acts, nb, m, sp,
                       err, profile);
