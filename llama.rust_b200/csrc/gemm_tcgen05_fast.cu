@@ -34,6 +34,8 @@
 // error word.
 #include <cuda_fp16.h>
 
+#include <cmath>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -750,10 +752,28 @@ static int launch_fast(const FqMats &mats, int64_t gy, int64_t k, int64_t m, Act
     const int nb = (int)(k / GROUP_K);
     const int64_t gx = (m + NC - 1) / NC;
     B200_REQUIRE(gx <= 65535 && gy * gx < (1ll << 31) / nb, "gemm: %lld row blocks x %lld column blocks are too many for one launch", (long long)gy, (long long)gx);
-    // one CTA per SM, each a contiguous run of (tile, super-block) units; B200_GEMM_FAST_CTAS=<n> sets another count (read per
-    // call; the tests use it to cut tiles in odd places)
+    // At most one CTA per SM, each a contiguous run of (tile, super-block) units.  How many: a run costs its super-blocks, plus,
+    // where runs cut tiles, the partial tiles the tile's owner has to add one after the other (measured: about 0.85 of a
+    // super-block's time each) and the write of its own (0.4).  1024 x 4096 x 512: 148 CTAs 56 us, 64 CTAs 38 us; 4096 x 4096 x
+    // 512: 148 CTAs 46 us, 128 CTAs (every tile in two halves) 43 us.  B200_GEMM_FAST_CTAS=<n> sets the count (read per call;
+    // the tests use it to cut tiles in odd places)
     const int64_t units = gy * gx * nb;
-    int64_t ctas = units < sms ? units : sms;
+    int64_t ctas = 1;
+    {
+        double best = 1e300;
+        const int64_t hi = units < sms ? units : sms;
+        for (int64_t pc = hi; pc >= 1 && pc >= hi / 4; pc--) {
+            const double run = (double)units / (double)pc;
+            const int64_t run_up = (units + pc - 1) / pc;
+            const bool whole = units % pc == 0 && (run_up % nb == 0 || nb % run_up == 0);   // every run ends where a tile or an even part of one ends
+            const double pieces = run >= nb ? (whole && run_up % nb == 0 ? 1.0 : 2.0) : std::ceil((double)nb / run) + (whole ? 0.0 : 1.0);
+            const double cost = (double)run_up + 0.85 * (pieces - 1.0) + (pieces > 1.0 ? 0.4 : 0.0);
+            if (cost < best) {
+                best = cost;
+                ctas = pc;
+            }
+        }
+    }
     if (const char *cv = getenv("B200_GEMM_FAST_CTAS")) {
         const long v = atol(cv);
         if (v >= 1 && v <= sms && v <= units) ctas = v;
