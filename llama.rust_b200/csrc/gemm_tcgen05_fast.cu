@@ -1,6 +1,6 @@
-// Q4_K prompt mat-mul in the fast numerics mode (within 1e-5 of sum |w x| per output, not the CPU's bits): tcgen05 f16 MMAs
-// that accumulate a whole 256-element super-block, mins included, in ONE tensor-memory accumulator, drained once per
-// super-block.
+// Q4_K (and Q6_K, below) prompt mat-mul in the fast numerics mode (within 1e-5 of sum |w x| per output, not the CPU's bits):
+// tcgen05 f16 MMAs that accumulate a whole 256-element super-block, mins included, in ONE tensor-memory accumulator, drained
+// once per super-block.
 //
 // The bit-exact two-pass kernels (gemm_tcgen05_img.cu) drain two accumulators once per sub-block pair, because the CPU's chain
 // rounds there, and read their operands as unswizzled core matrices; both bound them far below the tensor cores' rate.
@@ -27,11 +27,12 @@
 // of every step straight into the stage in the same layout (A), and at the first step of a super-block the mins operand Am
 // [128 rows][32 f16] (slots 2 j, 2 j + 1 = high part of -rho m_j, slots 16 + 2 j, + 1 = the remainder), so the weights cross
 // the L2 as 0.5625 bytes each.
-// Mat-mul kernel: 128 x NC outputs per CTA; a pipeline step is one pair column (K = 64: 16 KB of A, NC x 128 bytes of B);
+// Mat-mul kernel: tiles of 128 x NC outputs; a pipeline step is one pair column (K = 64: 16 KB of A, NC x 128 bytes of B);
 // warp 9 (one thread) copies, warp 8 (one thread) issues 4 (+ 2 for the mins) MMAs per step into one of two tensor-memory
 // stages of NC columns, warps 0..7 drain: warp w owns rows 32 (w % 4) .. + 31 (its tensor-memory lanes) and columns
-// NC / 2 (w / 4) .. + NC / 2 - 1.  Every wait is bounded; a wait that runs out raises the CTA's abort flag and the device
-// error word.
+// NC / 2 (w / 4) .. + NC / 2 - 1, warps 12..15 produce A.  A CTA walks a contiguous run of (tile, super-block) units (see
+// FqSplit); up to three matrices over the same activations share a launch (FqMats).  Every wait is bounded; a wait that
+// runs out raises the CTA's abort flag and the device error word.
 #include <cuda_fp16.h>
 
 #include <cmath>
