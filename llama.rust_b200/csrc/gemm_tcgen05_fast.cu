@@ -735,6 +735,14 @@ int gemm_fast_profile(unsigned long long *out, int n) {
 // flags of the partial tiles: one word per CTA of the grid, all zero between launches (a module variable: no allocation)
 __device__ unsigned g_fq_flags[1024];
 
+// after a launch that gave up (a bounded wait ran out) flags may be left raised: lower them all, after the device has drained
+int gemm_fast_reset_flags() {
+    B200_CUDA(cudaDeviceSynchronize());
+    static const unsigned zeros[1024] = {0};
+    B200_CUDA(cudaMemcpyToSymbol(g_fq_flags, zeros, sizeof(zeros)));
+    return B200_STATUS_SUCCESS;
+}
+
 template <int NC, bool Q6>
 static int launch_fast(const FqMats &mats, int64_t gy, int64_t k, int64_t m, ActView acts, int *err, int profile, int sms, cudaStream_t s) {
     using C = FqCfg<NC, Q6>;

@@ -415,7 +415,10 @@ int gemv_stream_error(int *code) {
     *code = 0;
     if (dev < 0 || dev >= 64 || !g_err_flag[dev]) return B200_STATUS_SUCCESS;
     B200_CUDA(cudaMemcpy(code, g_err_flag[dev], sizeof(int), cudaMemcpyDeviceToHost));
-    if (*code) B200_CUDA(cudaMemset(g_err_flag[dev], 0, sizeof(int)));
+    if (*code) {
+        B200_CUDA(cudaMemset(g_err_flag[dev], 0, sizeof(int)));
+        return gemm_fast_reset_flags();   // a kernel that gave up may have left partial-tile flags of the fast prompt mat-mul raised
+    }
     return B200_STATUS_SUCCESS;
 }
 
