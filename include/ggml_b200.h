@@ -102,6 +102,11 @@ int b200_debug_fa_prefill_profile(unsigned long long *out, int n);
 /* profiling aid: with B200_GEMM_FAST_PROFILE=1 the fast-numerics Q4_K prompt mat-mul sums, for one thread of each role of its
  * first CTA, the SM clocks spent at each barrier and at work (10 counters); this reads them back and clears them */
 int b200_debug_gemm_fast_profile(unsigned long long *out, int n);
+/* test hook: the fast-numerics prompt mat-mul cuts its work into one run per CTA, and a tile cut between CTAs is finished by
+ * the CTA holding its first part, which waits (bounded) for the others' partial tiles.  While spin_limit > 0 that wait polls
+ * at most spin_limit times and CTA mute_cta never announces its partial tile: the wait runs out, the kernel returns with that
+ * tile unwritten and b200_kernel_error reports code 4.  spin_limit 0 disarms the hook. */
+void b200_debug_gemm_fast_wait(int spin_limit, int mute_cta);
 void b200_debug_decode_step_wait(int spin_limit, int skip_cta, int skip_barrier);
 /* Which kernel a Q4_K prompt mat-mul (8x8 gemm route, n weight rows, m >= 32 activation rows) takes on a GPU with
  * sm_count SMs: 0 = integer tcgen05 kernel, 3 / 4 = the two-pass f16-image kernels with 64 / 128 activation rows

@@ -192,6 +192,7 @@ void b200_debug_stream_wait(int spin_limit, int skip_unit) { gemv_stream_debug_w
 unsigned long long b200_debug_decode_step_launches(void) { return decode_persistent_launches(); }
 int b200_debug_fa_prefill_profile(unsigned long long *out, int n) { return flash_attn_prefill_profile(out, n); }
 int b200_debug_gemm_fast_profile(unsigned long long *out, int n) { return gemm_fast_profile(out, n); }
+void b200_debug_gemm_fast_wait(int spin_limit, int mute_cta) { gemm_fast_debug_wait(spin_limit, mute_cta); }
 int b200_debug_decode_step_times(unsigned long long *out, int n) { return decode_persistent_times(out, n); }
 void b200_debug_decode_step_wait(int spin_limit, int skip_cta, int skip_barrier) { decode_persistent_debug(spin_limit, skip_cta, skip_barrier); }
 

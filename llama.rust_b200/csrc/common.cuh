@@ -253,6 +253,7 @@ void decode_persistent_debug(int spin_limit, int skip_cta, int skip_barrier);
 unsigned long long decode_persistent_launches();
 int decode_persistent_times(unsigned long long *out, int n);
 int gemm_fast_profile(unsigned long long *out, int n);            // gemm_tcgen05_fast.cu
+void gemm_fast_debug_wait(int spin_limit, int mute_cta);          // gemm_tcgen05_fast.cu: test hook
 int gemm_fast_reset_flags();                                      // gemm_tcgen05_fast.cu: the partial-tile flags of the current device, all down
 int flash_attn_prefill_profile(unsigned long long *out, int n);   // flash_attn_prefill_tc.cu
 

@@ -261,6 +261,8 @@ struct FqSplit {
     unsigned *flags;    // [P]
     int gx;             // column blocks
     int total_tiles;
+    unsigned wait_limit;   // polls of a partial tile's flag before the CTA gives up
+    int mute_cta;          // test hook: this CTA leaves its flag down (-1: none)
 };
 
 template <int NC, bool Q6>
@@ -420,7 +422,7 @@ gemm_kq_tcgen05_fast_kernel(const __grid_constant__ FqMats mats, const uint8_t *
                 mins_apart();
                 __threadfence();
                 asm volatile("bar.sync 1, %0;" ::"n"(FQ_EPI_WARPS * 32) : "memory");
-                if (threadIdx.x == 0) atomicExch(sp.flags + pcta, 1u);
+                if (threadIdx.x == 0 && pcta != sp.mute_cta) atomicExch(sp.flags + pcta, 1u);
                 continue;
             }
             if (b_last < nb - 1) {
@@ -430,7 +432,7 @@ gemm_kq_tcgen05_fast_kernel(const __grid_constant__ FqMats mats, const uint8_t *
                 for (int qq = pcta + 1; qq <= qhi; qq++) {
                     if (threadIdx.x == 0) {
                         bool seen = false;
-                        for (uint32_t itw = 0; itw < FQ_WAIT_LIMIT && !seen; itw++) {
+                        for (uint32_t itw = 0; itw < sp.wait_limit && !seen; itw++) {
                             seen = *(volatile unsigned *)(sp.flags + qq) != 0u;
                             if (!seen && (itw & 255) == 255 && *abort_flag) break;
                         }
@@ -735,6 +737,14 @@ int gemm_fast_profile(unsigned long long *out, int n) {
 // flags of the partial tiles: one word per CTA of the grid, all zero between launches (a module variable: no allocation)
 __device__ unsigned g_fq_flags[1024];
 
+// test hook: while spin_limit > 0 the wait for a partial tile's flag polls at most spin_limit times and CTA mute_cta never
+// raises its flag, so that a test can watch that wait run out (the kernel returns, error code 4)
+static int g_fq_wait_limit_override = 0, g_fq_mute_cta = -1;
+void gemm_fast_debug_wait(int spin_limit, int mute_cta) {
+    g_fq_wait_limit_override = spin_limit > 0 ? spin_limit : 0;
+    g_fq_mute_cta = mute_cta;
+}
+
 // after a launch that gave up (a bounded wait ran out) flags may be left raised: lower them all, after the device has drained
 int gemm_fast_reset_flags() {
     B200_CUDA(cudaDeviceSynchronize());
@@ -798,6 +808,8 @@ static int launch_fast(const FqMats &mats, int64_t gy, int64_t k, int64_t m, Act
     sp.flags = flags[dev];
     sp.gx = (int)gx;
     sp.total_tiles = (int)(gy * gx);
+    sp.wait_limit = g_fq_wait_limit_override > 0 ? (unsigned)g_fq_wait_limit_override : FQ_WAIT_LIMIT;
+    sp.mute_cta = g_fq_wait_limit_override > 0 ? g_fq_mute_cta : -1;
     rc = launch_pdl(expand_q8_K_acts_fast_kernel<NC, Q6>, dim3((unsigned)(4 * nb), (unsigned)gx), dim3(FQ_EXPAND_THREADS), (size_t)0, s, acts, bimg, m, nb);
     if (rc != B200_STATUS_SUCCESS) return rc;
     return launch_pdl(gemm_kq_tcgen05_fast_kernel<NC, Q6>, dim3((unsigned)ctas), dim3(FQ_THREADS), (size_t)C::SMEM, s, mats, (const uint8_t *)bimg, acts, nb, m, sp,

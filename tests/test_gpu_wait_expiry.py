@@ -79,3 +79,48 @@ def test_second_device_in_the_same_process():
             assert dev.kernel_error() == 0
     finally:
         dev.set_device(0)
+
+
+def test_fast_prompt_mat_mul_partial_tile_wait_expiry(monkeypatch):
+    """The fast-numerics prompt mat-mul cuts its work into one run per CTA; a tile cut between two CTAs is finished by the
+    one holding its first half, which waits (bounded) for the other's partial tile.  Here CTA 1 never announces its half:
+    the wait of CTA 0 runs out after 2000 polls, the kernel returns, b200_kernel_error reports code 4, tile 0 is left
+    unwritten, every other tile is what an undisturbed launch gives, and the next launch is undisturbed."""
+    dev = b200.load()
+    dev.set_device(0)
+    n, k, m = 4096, 4096, 512
+    monkeypatch.setenv("B200_GEMM_FAST_CTAS", "128")   # 64 tiles of 128 x 256, sixteen super-blocks each: every tile in two halves
+    W = synth.weights(orc.Q4_K, n, k, seed=81, period=512)
+    w = dev.Weight(orc.Q4_K, W, k)
+    x = synth.activations(m, k, seed=82)
+    dx = dev.device_array(x)
+    out = dev.DeviceBuffer(4 * n * m)
+    dev.set_numerics(dev.FAST)
+    try:
+        dev.mul_mat_device(w, dx, m, out)
+        dev.synchronize()
+        assert dev.kernel_error() == 0
+        good = out.download(np.float32, n * m).reshape(m, n).copy()
+
+        dev.check(dev.lib.b200_memset(out.ptr, 0xFF, 4 * n * m, None), "memset")
+        dev.synchronize()
+        dev.lib.b200_debug_gemm_fast_wait(2000, 1)
+        try:
+            dev.mul_mat_device(w, dx, m, out)
+            dev.synchronize()           # returns: the wait gave up
+        finally:
+            dev.lib.b200_debug_gemm_fast_wait(0, -1)
+        assert dev.kernel_error() == 4
+        assert dev.kernel_error() == 0   # the read cleared it (and lowered the flags)
+        got = out.download(np.uint32, n * m).reshape(m, n)
+        assert (got[:256, :128] == 0xFFFFFFFF).all(), "the unfinished tile must not be stored"
+        rest = np.ones((m, n), dtype=bool)
+        rest[:256, :128] = False
+        assert (got[rest] == good.view(np.uint32)[rest]).all()
+
+        dev.mul_mat_device(w, dx, m, out)
+        dev.synchronize()
+        assert dev.kernel_error() == 0
+        assert bits_equal(out.download(np.float32, n * m).reshape(m, n), good)
+    finally:
+        dev.set_numerics(dev.EXACT)
