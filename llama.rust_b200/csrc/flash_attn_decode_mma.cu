@@ -36,6 +36,7 @@ struct DmDims {
     int T, H, H_kv, group, row_blocks;
     int64_t n_kv;
     int n_splits, tiles_per_split;
+    int strided;   // listed walk: split s takes tiles s, s + n_splits, .. instead of the range [s, s + 1) * tiles_per_split
 };
 
 __device__ __forceinline__ uint32_t d_smem(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -154,6 +155,8 @@ fa_decode_mma_kernel(b200_flash_attn_args a, DmDims d, float scale_log2, float *
     // otherwise its first two tiles and the first tile's mask words are on their way while q is read
     const bool listed = a.mask != nullptr && d.T > 1;
     int n_walk = (int)(tile1 - tile0);
+    const int64_t l_base = d.strided ? split : tile0, l_step = d.strided ? d.n_splits : 1;   // the listed walk's tiles: l_base + l_step i
+    const int64_t n_local = !d.strided ? tile1 - tile0 : split < n_tiles_all ? (n_tiles_all - split + d.n_splits - 1) / d.n_splits : 0;
     uint32_t mk[2][2] = {{0u, 0u}, {0u, 0u}}, mk_next[2][2] = {{0u, 0u}, {0u, 0u}};
     if (!listed) {
         if (n_walk > 0) stage(tile0, 0); else d_commit();
@@ -183,8 +186,10 @@ fa_decode_mma_kernel(b200_flash_attn_args a, DmDims d, float scale_log2, float *
 
     if (listed) {
         unsigned char *flags = smem;   // the staging area is not in use yet
-        for (int64_t tl = warp; tl < tile1 - tile0; tl += DM_WARPS) {   // one warp per tile: lanes take two positions each
-            const int64_t p = (tile0 + tl) * DM_BN + 2 * lane;
+        // with several tokens per step a split takes every n_splits-th tile, not a contiguous range: the tiles a row block sees
+        // come in runs (a sequence's cells lie together), and contiguous ranges would leave some CTAs all of a run and others none
+        for (int64_t tl = warp; tl < n_local; tl += DM_WARPS) {   // one warp per tile: lanes take two positions each
+            const int64_t p = (l_base + tl * l_step) * DM_BN + 2 * lane;
             bool any = false;
             for (int t = 0; t < n_tok_blk && !any; t++)
                 if (p < d.n_kv) {
@@ -198,8 +203,8 @@ fa_decode_mma_kernel(b200_flash_attn_args a, DmDims d, float scale_log2, float *
         __syncthreads();
         if (warp == 0) {   // ordered compaction, 32 tiles at a time
             int count = 0;
-            for (int64_t base = 0; base < tile1 - tile0; base += 32) {
-                const bool f = base + lane < tile1 - tile0 && flags[base + lane];
+            for (int64_t base = 0; base < n_local; base += 32) {
+                const bool f = base + lane < n_local && flags[base + lane];
                 const unsigned bal = __ballot_sync(0xffffffffu, f);
                 if (f) vis_list[count + __popc(bal & ((1u << lane) - 1u))] = (unsigned short)(base + lane);
                 count += __popc(bal);
@@ -208,11 +213,11 @@ fa_decode_mma_kernel(b200_flash_attn_args a, DmDims d, float scale_log2, float *
         }
         __syncthreads();
         n_walk = n_vis_s;
-        if (n_walk > 0) stage(tile0 + vis_list[0], 0); else d_commit();
-        if (n_walk > 1) stage(tile0 + vis_list[1], 1); else d_commit();
-        if (n_walk > 0) mask_words(tile0 + vis_list[0], mk);
+        if (n_walk > 0) stage(l_base + vis_list[0] * l_step, 0); else d_commit();
+        if (n_walk > 1) stage(l_base + vis_list[1] * l_step, 1); else d_commit();
+        if (n_walk > 0) mask_words(l_base + vis_list[0] * l_step, mk);
     }
-    auto tile_at = [&](int i) -> int64_t { return tile0 + (listed ? (int64_t)vis_list[i] : (int64_t)i); };
+    auto tile_at = [&](int i) -> int64_t { return listed ? l_base + vis_list[i] * l_step : tile0 + (int64_t)i; };
 
     // ldmatrix addressing (see flash_attn_prefill.cu): K non-transposed, V transposed
     const int k_row = (lane & 7) + ((lane >> 4) << 3), k_col = ((lane >> 3) & 1) * 16;
@@ -405,6 +410,10 @@ bool flash_attn_decode_mma(const b200_flash_attn_args *a, cudaStream_t s, int *r
     d.tiles_per_split = (int)((n_tiles + want - 1) / want);
     d.n_splits = (int)((n_tiles + d.tiles_per_split - 1) / d.tiles_per_split);
     if (d.T > 1 && d.tiles_per_split > DM_MAX_LIST) return false;
+    {
+        const char *e = getenv("B200_FA_DECODE_STRIDED");
+        d.strided = !(e && e[0] == '0');   // on unless switched off
+    }
     if (!g_dm_counters[dev]) {   // a module variable: no allocation, zero-initialized on every device
         void *p = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&p, g_dm_counters_dev);
