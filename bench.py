@@ -939,6 +939,16 @@ def case_gemm(args):
     e1.synchronize()
     us = e0.elapsed_ms(e1) * 1e3 / args.launches
     out = {"case": f"gemm {args.wtype} {args.only} x {m}", "launches": args.launches, "us_per_call": us, "tops": 2.0 * n * k * m / us / 1e6, "kernel_error": b.kernel_error()}
+    if m < 32:
+        # a batched decode step's mat-mul: activations quantized beforehand, weight copies rotated to stay out of L2, launches replayed as one graph
+        wbytes = n * k * SWEEP_TYPES[args.wtype][1] // SWEEP_TYPES[args.wtype][2]
+        copies = max(2, min(32, (300 << 20) // max(wbytes, 1) + 1))
+        weights = [w] + [b.Weight(ty, synth_weights(n, k, seed=7, ty=ty), k) for _ in range(copies - 1)]
+        act = b.DeviceBuffer(b.lib.b200_act_scratch_nbytes(m, k))
+        kind = b.act_kind_for(ty, n, m)
+        b.check(b.lib.b200_quantize_activations_device(kind, m, k, dx.ptr, k, act.ptr, None), "quantize")
+        out["us_per_launch_graph"] = b.bench_mul_mat_q8(weights, act, kind, do, m, args.launches)
+        out["copies"] = copies
     if os.environ.get("B200_GEMM_FAST_PROFILE") in ("1", "2", "3", "4"):
         # SM clocks per launch of one thread per role of the fast kernel's first CTA (csrc/gemm_tcgen05_fast.cu)
         import ctypes

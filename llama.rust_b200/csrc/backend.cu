@@ -491,11 +491,12 @@ static bool multi_candidate(const ggml_tensor *mm) {
     return mm->op == GGML_OP_MUL_MAT && w && x && w->type == B200_TYPE_Q4_K && w->ne[2] == 1 && w->ne[3] == 1 && w->ne[1] % 8 == 0 &&
            x->ne[1] == 1 && x->ne[2] == 1 && x->ne[3] == 1 && mm->data && supports_mul_mat(mm, nullptr);
 }
-// the same for a prompt batch: Q4_K matrices on the 8x8 route over 64 or more activation rows, a multiple of 4 (no tail rows)
+// the same for a prompt batch or a batched decode step: Q4_K matrices on the 8x8 route over 64 or more activation rows, or 8 to 31
+// of them, a multiple of 4 (no tail rows)
 static bool multi_candidate_rows(const ggml_tensor *mm) {
     const ggml_tensor *w = mm->src[0], *x = mm->src[1];
     return mm->op == GGML_OP_MUL_MAT && w && x && w->type == B200_TYPE_Q4_K && w->ne[2] == 1 && w->ne[3] == 1 && w->ne[1] % 8 == 0 &&
-           x->ne[1] >= 64 && x->ne[1] % 4 == 0 && x->ne[2] == 1 && x->ne[3] == 1 && mm->data && supports_mul_mat(mm, nullptr);
+           (x->ne[1] >= 64 || (x->ne[1] >= 8 && x->ne[1] < 32)) && x->ne[1] % 4 == 0 && x->ne[2] == 1 && x->ne[3] == 1 && mm->data && supports_mul_mat(mm, nullptr);
 }
 static int find_sibling_mat_muls(const ggml_cgraph *g, int i, int *sib, bool rows = false) {
     const ggml_tensor *first = g->nodes[i];

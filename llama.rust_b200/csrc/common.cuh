@@ -147,6 +147,9 @@ int launch_gemv(int type, int route, int64_t n, int64_t k, int64_t m, const uint
 
 int launch_gemm_mma(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
                     cudaStream_t s);
+int launch_gemm_small_multi(int count, const int64_t *n, int64_t k, int64_t m, const uint8_t *const *tiles, ActView acts, float *const *dst,
+                            const int64_t *lddst, cudaStream_t s);
+bool gemm_small_multi_enabled();
 int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
                         cudaStream_t s);
 // Q8_0 / Q4_0 / MXFP4 / Q6_K prompt mat-muls on tcgen05 kind::i8 (gemm_tcgen05_i8.cu)

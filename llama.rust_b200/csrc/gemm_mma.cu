@@ -283,26 +283,51 @@ gemm_q6_K_mma_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *dst
 
 // ---- a handful of activation rows (batched decode: 8 to 31) ----------------------------------------------
 // With 16 columns the kernel above has one warp per 32-row tile walk all of K: 128 warps on the whole GPU for a
-// 4096-row matrix.  Here a CTA owns one row tile x 16 columns and its 8 warps split K: in every window of 8
-// super-blocks warp w computes super-block w's sub-block dots with mma.sync, scales them (integers) and leaves
-// ig[pair][row][col] in shared memory with the rows' headers, the columns' activation sums and scales; after
-// a barrier 256 chain threads (two (row, col) each) run the 8x8 gemm chain over the window in K order, so
-// the result is the one the kernel above and the CPU produce.
-constexpr int SMALL_WIN = 8;
+// 4096-row matrix.  Here a CTA owns one row tile x 16 columns and its SMALL_WIN (8 or 16) warps split K: in every
+// window of SMALL_WIN super-blocks warp w computes super-block w's sub-block dots with mma.sync, scales them
+// (integers) and leaves ig[col][row][pair] in shared memory with the rows' headers, the columns' activation sums
+// and scales; after a barrier the CTA's threads (one (row, col) each with 16 warps, two with 8) run the 8x8 gemm
+// chain over the window in K order, so the result is the one the kernel above and the CPU produce.  A warp's
+// window is one round trip to memory followed by its arithmetic, and the warps of a CTA take it in step, so the
+// time is windows x (latency + issue): 16 warps halve the windows of a long row (K of 4096 is one window).
 struct SmallStage {
-    int ig[4][16][36];      // scaled pair dots [pair][column][row]; 36 words per column: the 32 lanes of a store (4 column pairs x 8 rows) and of the chain's loads (32 rows) each hit 32 different banks
+    int4 ig[16][33];        // scaled pair dots [column][row] = {pair 0..3}; 33 entries per column: a store's quarter warp (rows g8, g8 + 1 of four column pairs) and a chain load's (eight rows of one column) each cover 32 different banks
     uint4 hdr[32];          // the rows' (d | dmin, 12 scale / min bytes)
-    int bp[16][8];          // the columns' sub-block sums
+    uint4 bp[16];           // the columns' sub-block sums, two 16-bit sums per word = one sub-block pair
     float da[16];           // the columns' super-block scales
 };
-__global__ void __launch_bounds__(SMALL_WIN * 32, 2)
-gemm_q4_K_small_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *dst, int64_t lddst, int64_t n, int nb, int64_t m) {
+// c + (low half of a) * (byte 0 of b) + (high half of a) * (byte 1 of b), halves signed, bytes unsigned; _hi: bytes 2 and 3
+__device__ __forceinline__ int dp2a_lo_su(uint32_t a, uint32_t b) {
+    int d;
+    asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(0));
+    return d;
+}
+__device__ __forceinline__ int dp2a_hi_su(uint32_t a, uint32_t b) {
+    int d;
+    asm("dp2a.hi.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(0));
+    return d;
+}
+// up to three matrices of one row length against the same activation rows in one launch: matrix e owns the CTAs
+// tile_start[e] .. tile_start[e + 1] of the grid's x range
+struct SmallMats {
+    const uint8_t *tiles[3];
+    float *dst[3];
+    int64_t n[3], lddst[3];
+    int tile_start[4];
+};
+template <int SMALL_WIN>
+__global__ void __launch_bounds__(SMALL_WIN * 32, 16 / SMALL_WIN)
+gemm_q4_K_small_kernel(const SmallMats mats, ActView acts, int nb, int64_t m) {
     extern __shared__ __align__(16) unsigned char small_sm[];
     SmallStage *st = (SmallStage *)small_sm;   // [SMALL_WIN]
     pdl_trigger();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g8 = lane >> 2, t = lane & 3;
-    const int64_t tile = blockIdx.x;
+    const int me = (int)blockIdx.x >= mats.tile_start[2] ? 2 : (int)blockIdx.x >= mats.tile_start[1] ? 1 : 0;
+    const uint8_t *tiles = mats.tiles[me];
+    float *dst = mats.dst[me];
+    const int64_t n = mats.n[me], lddst = mats.lddst[me];
+    const int64_t tile = (int)blockIdx.x - mats.tile_start[me];
     const int64_t col0 = (int64_t)blockIdx.y * 16;
     const int64_t K = acts.k;
     // activation rows this lane loads fragments from (patch nt, column g8 of it), clamped to the last valid one
@@ -313,26 +338,34 @@ gemm_q4_K_small_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *d
         colb[nt] = c < m ? c : m - 1;
     }
     const uint8_t *base = tiles + tile * (int64_t)nb * 4608;
-    // chain threads: row cr, columns cc and cc + 8
+    // chain threads: row cr, columns cc (and cc + 8 with 8 warps)
+    constexpr int NJ = 16 / SMALL_WIN;
     const int cr = threadIdx.x & 31, cc = threadIdx.x >> 5;
-    float sumf[2] = {0.0f, 0.0f}, summin[2] = {0.0f, 0.0f};
+    float sumf[NJ], summin[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; j++) sumf[j] = summin[j] = 0.0f;
     pdl_wait();
     for (int w0 = 0; w0 < nb; w0 += SMALL_WIN) {
         const int b = w0 + warp;
         if (b < nb) {
             SmallStage &s = st[warp];
             const uint8_t *chunk = base + (int64_t)b * 4608;
+            if (b + SMALL_WIN < nb) {   // the warp's super-block of the next window on its way to L2 (36 lines)
+                const uint8_t *nx = chunk + SMALL_WIN * 4608;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + lane * 128));
+                if (lane < 4) asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + 4096 + lane * 128));
+            }
             s.hdr[lane] = *(const uint4 *)(chunk + lane * 16);
             if (lane < 16) {
                 const int64_t c = col0 + lane < m ? col0 + lane : m - 1;
                 s.da[lane] = acts.d[c * nb + b];
             }
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int i = lane + 32 * j, col = i >> 3, sub = i & 7;   // 16 columns x 8 sub-blocks
+            for (int j = 0; j < 2; j++) {
+                const int i = lane + 32 * j, col = i >> 2, g = i & 3;   // 16 columns x 4 sub-block pairs
                 const int64_t c = col0 + col < m ? col0 + col : m - 1;
-                const short2 s2 = *(const short2 *)(acts.bsums + c * (K / 16) + (int64_t)b * 16 + 2 * sub);
-                s.bp[col][sub] = (int)s2.x + (int)s2.y;
+                const short4 s4 = *(const short4 *)(acts.bsums + c * (K / 16) + (int64_t)b * 16 + 4 * g);
+                ((uint32_t *)&s.bp[col])[g] = (uint32_t)((int)s4.x + (int)s4.y) & 0xffffu | (uint32_t)((int)s4.z + (int)s4.w) << 16;
             }
             // every load of the super-block first (weight fragments of both row halves, activation fragments of both
             // column patches): 64 registers of independent loads in flight per lane, then the arithmetic
@@ -367,10 +400,17 @@ gemm_q4_K_small_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *d
                 sc[0][1] = (ha.w & 0x0f0f0f0fu) | (((ha.y >> 6) & 0x03030303u) << 4);
                 sc[1][0] = hb.y & 0x3f3f3f3fu;
                 sc[1][1] = (hb.w & 0x0f0f0f0fu) | (((hb.y >> 6) & 0x03030303u) << 4);
+                int v[2][4][4];   // [column patch][accumulator][pair]
 #pragma unroll
                 for (int g = 0; g < 4; g++) {
                     const uint2 va = wa[mt][g], vb = wb[mt][g];
                     const int sh = 16 * (g & 1);
+                    int s_lo[2], s_hi[2];
+#pragma unroll
+                    for (int r = 0; r < 2; r++) {
+                        s_lo[r] = (sc[r][g >> 1] >> sh) & 0xff;
+                        s_hi[r] = (sc[r][g >> 1] >> (sh + 8)) & 0xff;
+                    }
 #pragma unroll
                     for (int nt = 0; nt < 2; nt++) {
                         const uint2 y0 = ya[g][nt][0], y1 = ya[g][nt][1];
@@ -379,13 +419,14 @@ gemm_q4_K_small_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *d
                         mma_s8_k32(d1, (va.x >> 4) & 0x0f0f0f0fu, (vb.x >> 4) & 0x0f0f0f0fu, (va.y >> 4) & 0x0f0f0f0fu,
                                    (vb.y >> 4) & 0x0f0f0f0fu, y1.x, y1.y);
 #pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            const int r = e >> 1;   // c0, c1: row a; c2, c3: row b
-                            const int s_lo = (sc[r][g >> 1] >> sh) & 0xff, s_hi = (sc[r][g >> 1] >> (sh + 8)) & 0xff;
-                            s.ig[g][8 * nt + 2 * t + (e & 1)][r ? rb : ra] = d0[e] * s_lo + d1[e] * s_hi;
-                        }
+                        for (int e = 0; e < 4; e++) v[nt][e][g] = d0[e] * s_lo[e >> 1] + d1[e] * s_hi[e >> 1];   // c0, c1: row a; c2, c3: row b
                     }
                 }
+#pragma unroll
+                for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++)
+                        s.ig[8 * nt + 2 * t + (e & 1)][(e >> 1) ? rb : ra] = make_int4(v[nt][e][0], v[nt][e][1], v[nt][e][2], v[nt][e][3]);
             }
         }
         __syncthreads();
@@ -396,26 +437,30 @@ gemm_q4_K_small_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *d
             const uint32_t mn_lo = hd.z & 0x3f3f3f3fu, mn_hi = ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4);
             const float dw = f16_bits_to_f32((uint16_t)(hd.x & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(hd.x >> 16));
 #pragma unroll
-            for (int j = 0; j < 2; j++) {
-                const int c = cc + 8 * j;
+            for (int j = 0; j < NJ; j++) {
+                const int c = cc + SMALL_WIN * j;
                 const float da = s.da[c];
                 const float sd = __fmul_rn(dw, da), sm = __fmul_rn(dmw, da);
-#pragma unroll
-                for (int g = 0; g < 4; g++) {
-                    const uint32_t mw = g < 2 ? mn_lo : mn_hi;
-                    const int m_lo = (mw >> (16 * (g & 1))) & 0xff, m_hi = (mw >> (16 * (g & 1) + 8)) & 0xff;
-                    const int mg = m_lo * s.bp[c][2 * g] + m_hi * s.bp[c][2 * g + 1];
-                    sumf[j] = __fmaf_rn((float)s.ig[g][c][cr], sd, sumf[j]);
-                    summin[j] = __fmaf_rn((float)mg, sm, summin[j]);
-                }
+                const int4 ig = s.ig[c][cr];
+                const uint4 bp = s.bp[c];
+                // pair g: mins 2g and 2g + 1 times the two sub-blocks' activation sums
+                const int mg0 = dp2a_lo_su(bp.x, mn_lo), mg1 = dp2a_hi_su(bp.y, mn_lo), mg2 = dp2a_lo_su(bp.z, mn_hi), mg3 = dp2a_hi_su(bp.w, mn_hi);
+                sumf[j] = __fmaf_rn((float)ig.x, sd, sumf[j]);
+                sumf[j] = __fmaf_rn((float)ig.y, sd, sumf[j]);
+                sumf[j] = __fmaf_rn((float)ig.z, sd, sumf[j]);
+                sumf[j] = __fmaf_rn((float)ig.w, sd, sumf[j]);
+                summin[j] = __fmaf_rn((float)mg0, sm, summin[j]);
+                summin[j] = __fmaf_rn((float)mg1, sm, summin[j]);
+                summin[j] = __fmaf_rn((float)mg2, sm, summin[j]);
+                summin[j] = __fmaf_rn((float)mg3, sm, summin[j]);
             }
         }
         __syncthreads();
     }
     const int64_t row = tile * TILE_ROWS + cr;
 #pragma unroll
-    for (int j = 0; j < 2; j++) {
-        const int64_t col = col0 + cc + 8 * j;
+    for (int j = 0; j < NJ; j++) {
+        const int64_t col = col0 + cc + SMALL_WIN * j;
         if (row < n && col < m) dst[col * lddst + row] = __fsub_rn(sumf[j], summin[j]);
     }
 }
@@ -426,7 +471,8 @@ struct SmallStageQ6 {
     float rr[16][33];       // [column][row]
     float da[16];
 };
-__global__ void __launch_bounds__(SMALL_WIN * 32, 2)
+template <int SMALL_WIN>
+__global__ void __launch_bounds__(SMALL_WIN * 32, 16 / SMALL_WIN)
 gemm_q6_K_small_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *dst, int64_t lddst, int64_t n, int nb, int64_t m) {
     __shared__ SmallStageQ6 st[SMALL_WIN];
     pdl_trigger();
@@ -442,14 +488,22 @@ gemm_q6_K_small_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *d
         colb[nt] = c < m ? c : m - 1;
     }
     const uint8_t *base = tiles + tile * (int64_t)nb * 6720;
+    constexpr int NJ = 16 / SMALL_WIN;
     const int cr = threadIdx.x & 31, cc = threadIdx.x >> 5;
-    float out[2] = {0.0f, 0.0f};
+    float out[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; j++) out[j] = 0.0f;
     pdl_wait();
     for (int w0 = 0; w0 < nb; w0 += SMALL_WIN) {
         const int b = w0 + warp;
         if (b < nb) {
             SmallStageQ6 &s = st[warp];
             const uint8_t *chunk = base + (int64_t)b * 6720;
+            if (b + SMALL_WIN < nb) {   // the warp's super-block of the next window on its way to L2 (53 lines)
+                const uint8_t *nx = chunk + SMALL_WIN * 6720;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + lane * 128));
+                if (lane < 21) asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + 4096 + lane * 128));
+            }
             if (lane < 16) {
                 const int64_t c = col0 + lane < m ? col0 + lane : m - 1;
                 s.da[lane] = acts.d[c * nb + b];
@@ -511,14 +565,14 @@ gemm_q6_K_small_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *d
         for (int w = 0; w < wn; w++) {
             const SmallStageQ6 &s = st[w];
 #pragma unroll
-            for (int j = 0; j < 2; j++) out[j] = __fmaf_rn(s.rr[cc + 8 * j][cr], s.da[cc + 8 * j], out[j]);
+            for (int j = 0; j < NJ; j++) out[j] = __fmaf_rn(s.rr[cc + SMALL_WIN * j][cr], s.da[cc + SMALL_WIN * j], out[j]);
         }
         __syncthreads();
     }
     const int64_t row = tile * TILE_ROWS + cr;
 #pragma unroll
-    for (int j = 0; j < 2; j++) {
-        const int64_t col = col0 + cc + 8 * j;
+    for (int j = 0; j < NJ; j++) {
+        const int64_t col = col0 + cc + SMALL_WIN * j;
         if (row < n && col < m) dst[col * lddst + row] = out[j];
     }
 }
@@ -533,6 +587,57 @@ static bool gemm_small_enabled() {
     return v == 1;
 }
 
+// sixteen warps per CTA (one window per 16 super-blocks, one CTA per SM) while the grid is at most one CTA per SM and the
+// rows have 16 super-blocks; eight warps and two CTAs per SM beyond that.  B200_GEMM_SMALL_WIN=8|16 forces one form.
+static bool small_wide(int nb, int64_t ctas) {
+    static int win_env = -1, sms[64] = {0};
+    if (win_env < 0) {
+        const char *e = getenv("B200_GEMM_SMALL_WIN");
+        win_env = (e && e[0] == '8') ? 8 : (e && e[0] == '1') ? 16 : 0;
+    }
+    if (win_env) return win_env == 16;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    if (!sms[dev] && cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return false;
+    return nb >= 16 && ctas <= sms[dev];
+}
+
+// count Q4_K matrices (8x8 gemm chain) of row length k against the same 8 to 31 activation rows, one launch
+int launch_gemm_small_multi(int count, const int64_t *n, int64_t k, int64_t m, const uint8_t *const *tiles, ActView acts, float *const *dst,
+                            const int64_t *lddst, cudaStream_t s) {
+    B200_REQUIRE(k % GROUP_K == 0, "gemm: k = %lld must be a multiple of 256", (long long)k);
+    B200_REQUIRE(count >= 1 && count <= 3 && m >= 1 && m < 32, "gemm: %d matrices x %lld activation rows do not fit the few-rows kernel", count, (long long)m);
+    const int nb = (int)(k / GROUP_K);
+    SmallMats mats;
+    int64_t total = 0;
+    for (int e = 0; e < 3; e++) {
+        const int src = e < count ? e : count - 1;
+        mats.tiles[e] = tiles[src];
+        mats.dst[e] = dst[src];
+        mats.n[e] = n[src];
+        mats.lddst[e] = lddst[src];
+        mats.tile_start[e] = e < count ? (int)total : 0x7fffffff;
+        if (e < count) total += (n[e] + TILE_ROWS - 1) / TILE_ROWS;
+    }
+    mats.tile_start[3] = (int)total;
+    if (total == 0) return B200_STATUS_SUCCESS;
+    const int64_t sy = (m + 15) / 16;
+    B200_REQUIRE(total < 0x7fffffffLL && sy <= 65535, "gemm: %lld row tiles x %lld is too large for one launch", (long long)total, (long long)m);
+    static bool attr_done[64] = {false};   // the attribute belongs to the (function, device) pair
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    B200_REQUIRE(dev >= 0 && dev < 64, "gemm: device index %d out of range", dev);
+    if (!attr_done[dev]) {
+        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_small_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(SmallStage) * 8)));
+        B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_small_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(SmallStage) * 16)));
+        attr_done[dev] = true;
+    }
+    const dim3 grid((unsigned)total, (unsigned)sy);
+    return small_wide(nb, total * sy) ? launch_pdl(gemm_q4_K_small_kernel<16>, grid, dim3(512), sizeof(SmallStage) * 16, s, mats, acts, nb, m)
+                                      : launch_pdl(gemm_q4_K_small_kernel<8>, grid, dim3(256), sizeof(SmallStage) * 8, s, mats, acts, nb, m);
+}
+bool gemm_small_multi_enabled() { return gemm_small_enabled(); }
+
 // mode: 1 = Q4_K gemm chain, 2 = Q4_K tiled chain, 6 = Q6_K tiled chain
 int launch_gemm_mma(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
                     cudaStream_t s) {
@@ -540,27 +645,16 @@ int launch_gemm_mma(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *ti
     if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
     const int nb = (int)(k / GROUP_K);
     const int64_t tiles_n = (n + TILE_ROWS - 1) / TILE_ROWS;
-    if (mode == 1 && m < 32 && gemm_small_enabled()) {
-        // a few activation rows: K split over the warps of a CTA
-        static bool attr_done[64] = {false};   // the attribute belongs to the (function, device) pair
-        const size_t smem = sizeof(SmallStage) * SMALL_WIN;
-        int dev = 0;
-        B200_CUDA(cudaGetDevice(&dev));
-        B200_REQUIRE(dev >= 0 && dev < 64, "gemm: device index %d out of range", dev);
-        if (!attr_done[dev]) {
-            B200_CUDA(cudaFuncSetAttribute(gemm_q4_K_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr_done[dev] = true;
-        }
+    if ((mode == 1 || mode == 6) && m < 32 && gemm_small_enabled()) {
+        // a few activation rows: K split over the warps of a CTA, sixteen of them when the row has as many super-blocks
         const int64_t sy = (m + 15) / 16;
         B200_REQUIRE(tiles_n < 0x7fffffffLL && sy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);
-        return launch_pdl(gemm_q4_K_small_kernel, dim3((unsigned)tiles_n, (unsigned)sy), dim3(SMALL_WIN * 32), smem, s, tiles, acts, dst, lddst,
-                          n, nb, m);
-    }
-    if (mode == 6 && m < 32 && gemm_small_enabled()) {
-        const int64_t sy = (m + 15) / 16;
-        B200_REQUIRE(tiles_n < 0x7fffffffLL && sy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);
-        return launch_pdl(gemm_q6_K_small_kernel, dim3((unsigned)tiles_n, (unsigned)sy), dim3(SMALL_WIN * 32), 0, s, tiles, acts, dst, lddst, n,
-                          nb, m);
+        const dim3 grid((unsigned)tiles_n, (unsigned)sy);
+        if (mode == 6)
+            return small_wide(nb, tiles_n * sy) ? launch_pdl(gemm_q6_K_small_kernel<16>, grid, dim3(512), 0, s, tiles, acts, dst, lddst, n, nb, m)
+                        : launch_pdl(gemm_q6_K_small_kernel<8>, grid, dim3(256), 0, s, tiles, acts, dst, lddst, n, nb, m);
+        const int64_t one = n;
+        return launch_gemm_small_multi(1, &one, k, m, &tiles, acts, &dst, &lddst, s);
     }
     const int64_t gx = (tiles_n + 3) / 4, gy = (m + 2 * MMA_COLS - 1) / (2 * MMA_COLS);
     B200_REQUIRE(gx < 0x7fffffffLL && gy <= 65535, "gemm: %lld x %lld is too large for one launch", (long long)n, (long long)m);

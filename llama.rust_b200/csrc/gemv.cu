@@ -886,6 +886,11 @@ int launch_gemv_rows_multi(int type, int route, int count, const int64_t *n, int
     if (count > 1 && type == B200_TYPE_Q4_K && whole && (rows >= 2048 || (fe && fe[0] == '2')) && m >= GEMM_FAST_MIN_COLS && m >= GEMM_TCGEN05_MIN_COLS && gemm_mma_enabled() && gemm_tcgen05_enabled() &&
         gemm_tcgen05_f16_choice() < 0 && numerics_mode() == 1 && !no_scratch_mode() && !(fe && fe[0] == '0'))
         return launch_gemm_kq_fast_multi(type, count, n, k, m, tiles, acts, dst, lddst, s);
+    // a batched decode step's rows (8 to 31, a multiple of 4): the few-rows kernel takes the matrices as one grid, the same
+    // CTAs and chains as separate launches (bit-identical)
+    if (count > 1 && count <= 3 && type == B200_TYPE_Q4_K && route == B200_ROUTE_REPACK && m % 4 == 0 && m >= GEMM_MMA_MIN_COLS && m < 32 && gemm_mma_enabled() &&
+        gemm_small_multi_enabled())
+        return launch_gemm_small_multi(count, n, k, m, tiles, acts, dst, lddst, s);
     for (int e = 0; e < count; e++) {
         int rc = launch_gemv(type, route, n[e], k, m, tiles[e], acts, dst[e], lddst[e], s);
         if (rc != B200_STATUS_SUCCESS) return rc;

@@ -56,12 +56,14 @@ def test_refusals(dev):
 
 
 @pytest.mark.parametrize("mode", ["fast", "exact"])
-@pytest.mark.parametrize("case", [((1024, 1024, 4096), 4096, 256), ((14336, 14336), 4096, 512), ((4096, 264), 1024, 68), ((520,), 2048, 100)], ids=str)
+@pytest.mark.parametrize("case", [((1024, 1024, 4096), 4096, 256), ((14336, 14336), 4096, 512), ((4096, 264), 1024, 68), ((520,), 2048, 100),
+                                  ((4096, 1024, 1024), 4096, 16), ((14336, 14336), 4096, 12), ((264, 520), 512, 28), ((1024, 1024), 14336, 8)], ids=str)
 def test_rows_multi_equals_single_calls(dev, case, mode):
     """b200_mul_mat_q8_rows_multi: several Q4_K matrices against the same prompt batch give what one b200_mul_mat_q8 call
     per matrix gives: bit for bit in the exact numerics mode (the CPU chain's kernels); in the fast mode one launch of the
     tensor-core kernel, whose CTAs cut the tiles' super-block sums in other places than a launch per matrix does, so the
-    f32 sums associate differently: held to a tenth of the mode's tolerance of 1e-5 sum |w x|"""
+    f32 sums associate differently: held to a tenth of the mode's tolerance of 1e-5 sum |w x|.  A batched decode step's 8 to
+    31 rows take the few-rows kernel with the matrices as one grid: the same CTAs and chains, bit-identical in both modes."""
     rows, k, m = case
     x = synth.activations(m, k, seed=6)
     Ws = [synth.weights(orc.Q4_K, n, k, seed=20 + i, period=64) for i, n in enumerate(rows)]
@@ -85,7 +87,7 @@ def test_rows_multi_equals_single_calls(dev, case, mode):
         for W, w, o, n in zip(Ws, ws, outs, rows):
             got = o.download(np.float32, n * m).reshape(m, n)
             single = dev.mul_mat(w, x)
-            if mode == "exact":
+            if mode == "exact" or m < 32:
                 assert bits_equal(got, single)
             else:
                 bound = 1e-6 * (np.abs(x).astype(np.float64) @ np.abs(orc.dequantize(orc.Q4_K, W, k)).astype(np.float64).T)
