@@ -175,6 +175,12 @@ int b200_mul_mat_q8(int type, int64_t n, int64_t k, int64_t m, const void *dev_w
  * (crates/llama/src/graph_arch.rs:209,226; crates/ggml/src/compute.rs:1174) without a second kernel. */
 int b200_mul_mat_q8_add(int type, int64_t n, int64_t k, const void *dev_w, const void *dev_act, int act_kind, float *dev_dst,
                         const float *dev_addend, float *dev_sum, int route, void *stream);
+/* The same for the 8 to 31 activation rows of a batched decode step (a multiple of 4 for Q4_K): every row c also gets
+ * dev_sum[c * ld_sum + i] = dst[c * lddst + i] + dev_addend[c * ld_addend + i].  Only the shapes the few-rows kernels take:
+ * b200_mul_mat_q8_rows_add_fusable says (1 / 0) whether (type, n weight rows, m activation rows) is one; the call refuses the others. */
+int b200_mul_mat_q8_rows_add_fusable(int type, int64_t n, int64_t m);
+int b200_mul_mat_q8_rows_add(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, const void *dev_act, int act_kind, float *dev_dst,
+                             int64_t lddst, const float *dev_addend, int64_t ld_addend, float *dev_sum, int64_t ld_sum, void *stream);
 /* Measurement helper (no counterpart in the reference): `reps` launches of b200_mul_mat_q8 over n_w rotating copies
  * of the weights (so that they come from HBM, not L2), captured into one CUDA graph and replayed, timed with events
  * on the launching stream.  This is what the kernel costs inside a decode step, where a replayed graph issues the

@@ -552,6 +552,29 @@ int b200_mul_mat_q8_add(int type, int64_t n, int64_t k, const void *dev_w, const
     return launch_gemv(type, route, n, k, 1, (const uint8_t *)dev_w, a, dev_dst, n, (cudaStream_t)stream);
 }
 
+int b200_mul_mat_q8_rows_add_fusable(int type, int64_t n, int64_t m) {
+    if (!is_quant_type(type) || n <= 0 || m <= 0) return 0;
+    return gemv_rows_add_fusable(type, pick_route(type, n, m), m) ? 1 : 0;
+}
+
+int b200_mul_mat_q8_rows_add(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, const void *dev_act, int act_kind, float *dev_dst, int64_t lddst,
+                             const float *dev_addend, int64_t ld_addend, float *dev_sum, int64_t ld_sum, void *stream) {
+    int rc = check_mul_mat_args(type, n, k, m);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    if (n == 0 || m == 0) return B200_STATUS_SUCCESS;
+    B200_REQUIRE(dev_w && dev_act && dev_dst && dev_addend && dev_sum, "mul_mat_q8_rows_add: null pointer");
+    B200_REQUIRE(lddst >= n && ld_addend >= n && ld_sum >= n, "mul_mat_q8_rows_add: row strides smaller than the rows");
+    const int route = pick_route(type, n, m);
+    B200_REQUIRE(gemv_rows_add_fusable(type, route, m), "mul_mat_q8_rows_add: type %d with %lld activation rows does not take a few-rows kernel", type, (long long)m);
+    B200_REQUIRE(act_kind == act_kind_for(type, route, m), "mul_mat_q8_rows_add: activation kind %d does not fit type %d", act_kind, type);
+    ActView a = act_carve(const_cast<void *>(dev_act), m, k).view();
+    a.addend = dev_addend;
+    a.sum = dev_sum;
+    a.ld_addend = ld_addend;
+    a.ld_sum = ld_sum;
+    return launch_gemv(type, route, n, k, m, (const uint8_t *)dev_w, a, dev_dst, lddst, (cudaStream_t)stream);
+}
+
 int b200_mul_mat(int type, int64_t n, int64_t k, int64_t m, const void *dev_w, const float *dev_x, int64_t ldx,
                  float *dev_dst, int64_t lddst, int route, void *stream) {
     B200_REQUIRE(is_quant_type(type), "mul_mat: weight type %d is not supported", type);

@@ -577,6 +577,30 @@ static bool fuses_mul_mat_add(const ggml_tensor *mm, const ggml_tensor *add) {
     // the sum must not land on the mat-mul's activations or weights
     return add->data != mm->src[1]->data && add->data != mm->data;
 }
+// the same for the 8 to 31 rows of a batched decode step, where the few-rows kernels add as they store
+static bool fuses_mul_mat_rows_add(const ggml_tensor *mm, const ggml_tensor *add) {
+    if (add->op != GGML_OP_ADD || !supports_glue(add, nullptr) || mm->ne[1] < 8 || mm->ne[1] >= 32 || mm->ne[2] != 1 || mm->ne[3] != 1) return false;
+    const ggml_tensor *w = mm->src[0], *x = mm->src[1];
+    if (!w || !x || w->ne[2] != 1 || w->ne[3] != 1 || x->ne[2] != 1 || x->ne[3] != 1 || !mm->data || !supports_mul_mat(mm, nullptr)) return false;
+    const ggml_tensor *other = add->src[0] == mm ? add->src[1] : add->src[1] == mm ? add->src[0] : nullptr;
+    if (!other || other == mm || !same_shape(other, mm) || !other->data || !add->data) return false;
+    if (mm->nb[0] != 4 || other->nb[0] != 4 || add->nb[0] != 4 || other->type != B200_TYPE_F32 || add->type != B200_TYPE_F32) return false;
+    if (!b200_mul_mat_q8_rows_add_fusable(w->type, w->ne[1], mm->ne[1])) return false;
+    // the sum must not land on the mat-mul's result, activations or weights
+    return !ranges_overlap(add->data, ggml_nbytes(add), mm->data, ggml_nbytes(mm)) && !ranges_overlap(add->data, ggml_nbytes(add), x->data, ggml_nbytes(x)) &&
+           !ranges_overlap(add->data, ggml_nbytes(add), w->data, ggml_nbytes(w));
+}
+static int compute_mul_mat_rows_add(BackendCtx *bc, const ggml_tensor *op, const ggml_tensor *add) {
+    const ggml_tensor *w = op->src[0], *x = op->src[1];
+    const ggml_tensor *other = add->src[0] == op ? add->src[1] : add->src[0];
+    const int64_t k = w->ne[0], n = w->ne[1], m = x->ne[1];
+    const int kind = act_kind_for(w->type, pick_route(w->type, n, m), m);
+    if (bc->act_src && ranges_overlap(op->data, ggml_nbytes(op), bc->act_src, (size_t)bc->act_ld * bc->act_m * 4)) bc->act_src = nullptr;
+    int rc = quantized_acts(bc, (const float *)x->data, (int64_t)(x->nb[1] / 4), m, k, kind);
+    if (rc != B200_STATUS_SUCCESS) return rc;
+    return b200_mul_mat_q8_rows_add(w->type, n, k, m, w->data, bc->act, kind, (float *)op->data, (int64_t)(op->nb[1] / 4), (const float *)other->data,
+                                    (int64_t)(other->nb[1] / 4), (float *)add->data, (int64_t)(add->nb[1] / 4), bc->stream);
+}
 static int compute_mul_mat_add(BackendCtx *bc, const ggml_tensor *op, const ggml_tensor *add) {
     const ggml_tensor *w = op->src[0], *x = op->src[1];
     const ggml_tensor *other = add->src[0] == op ? add->src[1] : add->src[0];
@@ -1461,6 +1485,11 @@ static int run_nodes(BackendCtx *bc, ggml_cgraph *g) {
                     if (bc->act_src && ranges_overlap(next->data, ggml_nbytes(next), bc->act_src, (size_t)bc->act_ld * bc->act_m * 4))
                         bc->act_src = nullptr;
                     rc = compute_mul_mat_add(bc, op, next);
+                    i++;
+                } else if (next && bc->fuse_siblings && fuses_mul_mat_rows_add(op, next)) {
+                    rc = compute_mul_mat_rows_add(bc, op, next);
+                    if (bc->act_src && ranges_overlap(next->data, ggml_nbytes(next), bc->act_src, (size_t)bc->act_ld * bc->act_m * 4))
+                        bc->act_src = nullptr;
                     i++;
                 } else {
                     int sib[2];

@@ -108,6 +108,8 @@ struct ActView {
     // attn_output and ffn_down in a decoder layer (crates/llama/src/graph_arch.rs:209,226), one rounded add
     const float *addend = nullptr;
     float *sum = nullptr;
+    // the few-rows kernels (8 to 31 activation rows) do the same for every row c: sum[c * ld_sum + i] = dst[c * lddst + i] + addend[c * ld_addend + i]
+    int64_t ld_addend = 0, ld_sum = 0;
 };
 struct ActBuf {
     int8_t *qs;
@@ -150,6 +152,7 @@ int launch_gemm_mma(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *ti
 int launch_gemm_small_multi(int count, const int64_t *n, int64_t k, int64_t m, const uint8_t *const *tiles, ActView acts, float *const *dst,
                             const int64_t *lddst, cudaStream_t s);
 bool gemm_small_multi_enabled();
+bool gemv_rows_add_fusable(int type, int route, int64_t m);
 int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
                         cudaStream_t s);
 // Q8_0 / Q4_0 / MXFP4 / Q6_K prompt mat-muls on tcgen05 kind::i8 (gemm_tcgen05_i8.cu)

@@ -188,15 +188,32 @@ fa_decode_mma_kernel(b200_flash_attn_args a, DmDims d, float scale_log2, float *
         unsigned char *flags = smem;   // the staging area is not in use yet
         // with several tokens per step a split takes every n_splits-th tile, not a contiguous range: the tiles a row block sees
         // come in runs (a sequence's cells lie together), and contiguous ranges would leave some CTAs all of a run and others none
-        for (int64_t tl = warp; tl < n_local; tl += DM_WARPS) {   // one warp per tile: lanes take two positions each
-            const int64_t p = (l_base + tl * l_step) * DM_BN + 2 * lane;
+        // one warp per tile.  Aligned mask rows: lane = (token lane / 8, 16-byte piece lane % 8 of the tile's 128 mask bytes), so
+        // four tokens' rows of a tile are one independent load per lane; otherwise lanes take two positions each, token by token
+        const bool pieces = (((uintptr_t)a.mask | (uintptr_t)a.mask_nb1) & 15) == 0;
+        for (int64_t tl = warp; tl < n_local; tl += DM_WARPS) {
+            const int64_t tile = l_base + tl * l_step;
             bool any = false;
-            for (int t = 0; t < n_tok_blk && !any; t++)
-                if (p < d.n_kv) {
-                    const uint32_t two = p + 1 < d.n_kv ? *(const uint32_t *)((const unsigned char *)a.mask + (int64_t)(tok0 + t) * a.mask_nb1 + p * 2)
-                                                        : (0xFC000000u | *(const uint16_t *)((const unsigned char *)a.mask + (int64_t)(tok0 + t) * a.mask_nb1 + p * 2));
-                    any = ((two & 0xffffu) != 0xFC00u) | ((two >> 16) != 0xFC00u);
+            if (pieces) {
+                const int64_t p = tile * DM_BN + 8 * (lane & 7);
+                for (int t = lane >> 3; t < n_tok_blk; t += 4) {
+                    const unsigned char *mp = (const unsigned char *)a.mask + (int64_t)(tok0 + t) * a.mask_nb1 + p * 2;
+                    if (p + 8 <= d.n_kv) {
+                        const uint4 w = *(const uint4 *)mp;
+                        any |= (w.x != 0xFC00FC00u) | (w.y != 0xFC00FC00u) | (w.z != 0xFC00FC00u) | (w.w != 0xFC00FC00u);
+                    } else {
+                        for (int e = 0; e < 8 && p + e < d.n_kv; e++) any |= *(const uint16_t *)(mp + 2 * e) != 0xFC00u;
+                    }
                 }
+            } else {
+                const int64_t p = tile * DM_BN + 2 * lane;
+                for (int t = 0; t < n_tok_blk && !any; t++)
+                    if (p < d.n_kv) {
+                        const uint32_t two = p + 1 < d.n_kv ? *(const uint32_t *)((const unsigned char *)a.mask + (int64_t)(tok0 + t) * a.mask_nb1 + p * 2)
+                                                            : (0xFC000000u | *(const uint16_t *)((const unsigned char *)a.mask + (int64_t)(tok0 + t) * a.mask_nb1 + p * 2));
+                        any = ((two & 0xffffu) != 0xFC00u) | ((two >> 16) != 0xFC00u);
+                    }
+            }
             const unsigned hit = __ballot_sync(0xffffffffu, any);
             if (lane == 0) flags[tl] = hit != 0u;
         }

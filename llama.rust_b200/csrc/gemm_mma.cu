@@ -292,7 +292,7 @@ gemm_q6_K_mma_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *dst
 // time is windows x (latency + issue): 16 warps halve the windows of a long row (K of 4096 is one window).
 struct SmallStage {
     int4 ig[16][33];        // scaled pair dots [column][row] = {pair 0..3}; 33 entries per column: a store's quarter warp (rows g8, g8 + 1 of four column pairs) and a chain load's (eight rows of one column) each cover 32 different banks
-    uint4 hdr[32];          // the rows' (d | dmin, 12 scale / min bytes)
+    uint4 hdr[32];          // the rows' (d, dmin as f32 bits, mins 0..3, mins 4..7 one per byte)
     uint4 bp[16];           // the columns' sub-block sums, two 16-bit sums per word = one sub-block pair
     float da[16];           // the columns' super-block scales
 };
@@ -355,7 +355,11 @@ gemm_q4_K_small_kernel(const SmallMats mats, ActView acts, int nb, int64_t m) {
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + lane * 128));
                 if (lane < 4) asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + 4096 + lane * 128));
             }
-            s.hdr[lane] = *(const uint4 *)(chunk + lane * 16);
+            {   // row `lane`: d, dmin as f32 and the eight 6-bit mins one per byte (crates/ggml/src/quants.rs:421-429), for the chain threads
+                const uint4 hd = *(const uint4 *)(chunk + lane * 16);
+                s.hdr[lane] = make_uint4(__float_as_uint(f16_bits_to_f32((uint16_t)(hd.x & 0xffffu))), __float_as_uint(f16_bits_to_f32((uint16_t)(hd.x >> 16))),
+                                         hd.z & 0x3f3f3f3fu, ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4));
+            }
             if (lane < 16) {
                 const int64_t c = col0 + lane < m ? col0 + lane : m - 1;
                 s.da[lane] = acts.d[c * nb + b];
@@ -434,8 +438,8 @@ gemm_q4_K_small_kernel(const SmallMats mats, ActView acts, int nb, int64_t m) {
         for (int w = 0; w < wn; w++) {
             const SmallStage &s = st[w];
             const uint4 hd = s.hdr[cr];
-            const uint32_t mn_lo = hd.z & 0x3f3f3f3fu, mn_hi = ((hd.w >> 4) & 0x0f0f0f0fu) | (((hd.z >> 6) & 0x03030303u) << 4);
-            const float dw = f16_bits_to_f32((uint16_t)(hd.x & 0xffffu)), dmw = f16_bits_to_f32((uint16_t)(hd.x >> 16));
+            const uint32_t mn_lo = hd.z, mn_hi = hd.w;
+            const float dw = __uint_as_float(hd.x), dmw = __uint_as_float(hd.y);
 #pragma unroll
             for (int j = 0; j < NJ; j++) {
                 const int c = cc + SMALL_WIN * j;
@@ -461,7 +465,11 @@ gemm_q4_K_small_kernel(const SmallMats mats, ActView acts, int nb, int64_t m) {
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
         const int64_t col = col0 + cc + SMALL_WIN * j;
-        if (row < n && col < m) dst[col * lddst + row] = __fsub_rn(sumf[j], summin[j]);
+        if (row < n && col < m) {
+            const float v = __fsub_rn(sumf[j], summin[j]);
+            dst[col * lddst + row] = v;
+            if (acts.sum) acts.sum[col * acts.ld_sum + row] = __fadd_rn(v, acts.addend[col * acts.ld_addend + row]);
+        }
     }
 }
 
@@ -573,7 +581,10 @@ gemm_q6_K_small_kernel(const uint8_t *__restrict__ tiles, ActView acts, float *d
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
         const int64_t col = col0 + cc + SMALL_WIN * j;
-        if (row < n && col < m) dst[col * lddst + row] = out[j];
+        if (row < n && col < m) {
+            dst[col * lddst + row] = out[j];
+            if (acts.sum) acts.sum[col * acts.ld_sum + row] = __fadd_rn(out[j], acts.addend[col * acts.ld_addend + row]);
+        }
     }
 }
 
@@ -607,6 +618,7 @@ int launch_gemm_small_multi(int count, const int64_t *n, int64_t k, int64_t m, c
                             const int64_t *lddst, cudaStream_t s) {
     B200_REQUIRE(k % GROUP_K == 0, "gemm: k = %lld must be a multiple of 256", (long long)k);
     B200_REQUIRE(count >= 1 && count <= 3 && m >= 1 && m < 32, "gemm: %d matrices x %lld activation rows do not fit the few-rows kernel", count, (long long)m);
+    B200_REQUIRE(count == 1 || !acts.sum, "gemm: the fused add goes with a single matrix");
     const int nb = (int)(k / GROUP_K);
     SmallMats mats;
     int64_t total = 0;

@@ -874,6 +874,12 @@ static int64_t gemv_stream_max_tiles() {
     return (int64_t)sms[dev] * gemv_stream_tiles_mult();
 }
 
+// whether launch_gemv takes (type, route, m activation rows) to a few-rows kernel, which can add a tensor to its result as it stores it
+bool gemv_rows_add_fusable(int type, int route, int64_t m) {
+    if (!(m >= GEMM_MMA_MIN_COLS && m < 32 && gemm_mma_enabled() && gemm_small_multi_enabled())) return false;
+    return (type == B200_TYPE_Q4_K && route == B200_ROUTE_REPACK && m % 4 == 0) || (type == B200_TYPE_Q6_K && route == B200_ROUTE_TILED);
+}
+
 // Several Q4_K matrices of one row length against the same activation rows: one launch of the fast-numerics prompt kernel
 // where each of them would take it by itself (the same kernel and tolerance; its CTAs cut the tiles' f32 sums in other
 // places than separate launches would), separate launches otherwise.

@@ -94,3 +94,49 @@ def test_rows_multi_equals_single_calls(dev, case, mode):
                 assert (np.abs(got.astype(np.float64) - single.astype(np.float64)) <= bound).all()
     finally:
         dev.set_numerics(dev.EXACT)
+
+
+@pytest.mark.parametrize("case", [(orc.Q4_K, 4096, 4096, 16), (orc.Q4_K, 1032, 512, 28), (orc.Q6_K, 4096, 14336, 16), (orc.Q6_K, 100, 512, 9),
+                                  (orc.Q4_K, 4096, 14336, 8)], ids=str)
+def test_rows_add_equals_mat_mul_then_add(dev, case):
+    """b200_mul_mat_q8_rows_add (the residual ADD of a batched decode step inside the few-rows kernels): dst is what
+    b200_mul_mat_q8 gives bit for bit, sum is dst + addend with one rounded f32 add per element, also with the sum written
+    over the addend (the residual updated in place) and with row strides larger than the rows."""
+    ty, n, k, m = case
+    assert dev.lib.b200_mul_mat_q8_rows_add_fusable(ty, C.c_int64(n), C.c_int64(m)) == 1
+    x = synth.activations(m, k, seed=11)
+    W = synth.weights(ty, n, k, seed=31, period=64)
+    w = dev.Weight(ty, W, k)
+    kind = dev.act_kind_for(ty, n, m)
+    act = dev.DeviceBuffer(dev.lib.b200_act_scratch_nbytes(m, k))
+    dx = dev.device_array(x)
+    dev.check(dev.lib.b200_quantize_activations_device(kind, m, k, dx.ptr, k, act.ptr, None), "quantize")
+    ld = n + 8
+    add = np.random.default_rng(5).standard_normal((m, ld)).astype(np.float32)
+    dadd = dev.device_array(add)
+    dst, dsum = dev.DeviceBuffer(4 * n * m), dev.DeviceBuffer(4 * ld * m)
+    dev.check(dev.lib.b200_mul_mat_q8_rows_add(ty, C.c_int64(n), C.c_int64(k), C.c_int64(m), C.c_void_p(w.ptr), C.c_void_p(act.ptr), kind, C.c_void_p(dst.ptr),
+                                               C.c_int64(n), C.c_void_p(dadd.ptr), C.c_int64(ld), C.c_void_p(dsum.ptr), C.c_int64(ld), None), "rows_add")
+    dev.synchronize()
+    assert dev.kernel_error() == 0
+    single = dev.mul_mat(w, x)
+    got = dst.download(np.float32, n * m).reshape(m, n)
+    assert bits_equal(got, single)
+    want_sum = single + add[:, :n]
+    assert bits_equal(dsum.download(np.float32, ld * m).reshape(m, ld)[:, :n], want_sum)
+    # in place: the sum lands on the addend
+    dev.check(dev.lib.b200_mul_mat_q8_rows_add(ty, C.c_int64(n), C.c_int64(k), C.c_int64(m), C.c_void_p(w.ptr), C.c_void_p(act.ptr), kind, C.c_void_p(dst.ptr),
+                                               C.c_int64(n), C.c_void_p(dadd.ptr), C.c_int64(ld), C.c_void_p(dadd.ptr), C.c_int64(ld), None), "rows_add in place")
+    dev.synchronize()
+    back = dadd.download(np.float32, ld * m).reshape(m, ld)
+    assert bits_equal(back[:, :n], want_sum) and bits_equal(back[:, n:], add[:, n:])
+
+
+def test_rows_add_refuses_other_shapes(dev):
+    assert dev.lib.b200_mul_mat_q8_rows_add_fusable(orc.Q4_K, C.c_int64(4096), C.c_int64(64)) == 0
+    assert dev.lib.b200_mul_mat_q8_rows_add_fusable(orc.Q4_K, C.c_int64(4096), C.c_int64(1)) == 0
+    assert dev.lib.b200_mul_mat_q8_rows_add_fusable(orc.Q8_0, C.c_int64(4096), C.c_int64(16)) == 0
+    one = C.c_void_p(256)
+    rc = dev.lib.b200_mul_mat_q8_rows_add(orc.Q4_K, C.c_int64(4096), C.c_int64(4096), C.c_int64(64), one, one, dev.ACT_Q8_K_MIXED, one, C.c_int64(4096), one,
+                                          C.c_int64(4096), one, C.c_int64(4096), None)
+    assert rc != 0 and b"few-rows kernel" in dev.lib.b200_last_error()
