@@ -375,20 +375,34 @@ fa_decode_mma_kernel(b200_flash_attn_args a, DmDims d, float scale_log2, float *
         if (lane == 0) lsum[r] = L;
     }
     __syncthreads();
-    for (int i = tid; i < nrows * (D / 4); i += DM_WARPS * 32) {
-        const int r = i / (D / 4), e = 4 * (i - r * (D / 4));
-        const float *pr = all + (int64_t)r * PSTRIDE + e;
-        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll 8
-        for (int sp = 0; sp < d.n_splits; sp++) {
-            const float4 v = __ldcg((const float4 *)(pr + (int64_t)sp * DM_BM * PSTRIDE));
-            const float w = mw[r * DM_MAX_SPLITS + sp];
-            acc.x = fmaf(v.x, w, acc.x); acc.y = fmaf(v.y, w, acc.y); acc.z = fmaf(v.z, w, acc.z); acc.w = fmaf(v.w, w, acc.w);
+    // a thread's (row, four columns) items side by side, so that their loads of a split's partials are in flight together
+    constexpr int ITEMS = DM_BM * (D / 4) / (DM_WARPS * 32);
+    float4 acc[ITEMS];
+#pragma unroll
+    for (int it = 0; it < ITEMS; it++) acc[it] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 4
+    for (int sp = 0; sp < d.n_splits; sp++) {
+#pragma unroll
+        for (int it = 0; it < ITEMS; it++) {
+            const int i = tid + it * DM_WARPS * 32;
+            if (i < nrows * (D / 4)) {
+                const int r = i / (D / 4), e = 4 * (i - r * (D / 4));
+                const float4 v = __ldcg((const float4 *)(all + ((int64_t)sp * DM_BM + r) * PSTRIDE + e));
+                const float w = mw[r * DM_MAX_SPLITS + sp];
+                acc[it].x = fmaf(v.x, w, acc[it].x); acc[it].y = fmaf(v.y, w, acc[it].y); acc[it].z = fmaf(v.z, w, acc[it].z); acc[it].w = fmaf(v.w, w, acc[it].w);
+            }
         }
-        const int row = row0 + r, t = row / d.group, h = hk * d.group + row % d.group;
-        const float L = lsum[r];
-        const float inv = L > 0.0f ? 1.0f / L : 0.0f;   // a row that sees nothing gives zeros, as on the CPU
-        *(float4 *)(a.dst + ((int64_t)t * d.H + h) * D + e) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+    }
+#pragma unroll
+    for (int it = 0; it < ITEMS; it++) {
+        const int i = tid + it * DM_WARPS * 32;
+        if (i < nrows * (D / 4)) {
+            const int r = i / (D / 4), e = 4 * (i - r * (D / 4));
+            const int row = row0 + r, t = row / d.group, h = hk * d.group + row % d.group;
+            const float L = lsum[r];
+            const float inv = L > 0.0f ? 1.0f / L : 0.0f;   // a row that sees nothing gives zeros, as on the CPU
+            *(float4 *)(a.dst + ((int64_t)t * d.H + h) * D + e) = make_float4(acc[it].x * inv, acc[it].y * inv, acc[it].z * inv, acc[it].w * inv);
+        }
     }
 }
 
@@ -420,7 +434,8 @@ bool flash_attn_decode_mma(const b200_flash_attn_args *a, cudaStream_t s, int *r
     }
     const int64_t n_tiles = (d.n_kv + DM_BN - 1) / DM_BN;
     // three CTAs per SM (what the shared memory allows), at most DM_MAX_SPLITS splits, at least one tile each
-    int64_t want = (3 * (int64_t)sms + (int64_t)d.H_kv * d.row_blocks - 1) / ((int64_t)d.H_kv * d.row_blocks);
+    // (rounded down: a grid of a few CTAs more than the SMs hold at once runs those few as a second wave and takes twice the time)
+    int64_t want = 3 * (int64_t)sms / ((int64_t)d.H_kv * d.row_blocks);
     if (want > DM_MAX_SPLITS) want = DM_MAX_SPLITS;
     if (want > n_tiles) want = n_tiles;
     if (want < 1) want = 1;
