@@ -107,6 +107,11 @@ int b200_debug_gemm_fast_profile(unsigned long long *out, int n);
  * at most spin_limit times and CTA mute_cta never announces its partial tile: the wait runs out, the kernel returns with that
  * tile unwritten and b200_kernel_error reports code 4.  spin_limit 0 disarms the hook. */
 void b200_debug_gemm_fast_wait(int spin_limit, int mute_cta);
+/* test hook: the persistent few-rows Q4_K mat-mul (8 to 31 activation rows) hands ring slots from a producer warp to multiply
+ * warps to chain warps through barriers.  While spin_limit > 0 its waits poll at most spin_limit times and the producer of the
+ * launch's first CTA leaves its unit skip_unit unfilled (-1 = none): a wait runs out, the kernel returns with that CTA's rows
+ * unwritten and b200_kernel_error reports code 4.  spin_limit 0 disarms the hook. */
+void b200_debug_rows_ring_wait(int spin_limit, int skip_unit);
 void b200_debug_decode_step_wait(int spin_limit, int skip_cta, int skip_barrier);
 /* Which kernel a Q4_K prompt mat-mul (8x8 gemm route, n weight rows, m >= 32 activation rows) takes on a GPU with
  * sm_count SMs: 0 = integer tcgen05 kernel, 3 / 4 = the two-pass f16-image kernels with 64 / 128 activation rows

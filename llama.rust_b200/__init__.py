@@ -77,6 +77,8 @@ def _load():
     L.b200_debug_stream_wait.restype = None
     L.b200_debug_gemm_fast_wait.argtypes = [i32, i32]
     L.b200_debug_gemm_fast_wait.restype = None
+    L.b200_debug_rows_ring_wait.argtypes = [i32, i32]
+    L.b200_debug_rows_ring_wait.restype = None
     L.b200_debug_decode_step_launches.restype = C.c_ulonglong
     L.b200_debug_decode_step_wait.argtypes = [i32, i32, i32]
     L.b200_debug_decode_step_wait.restype = None

@@ -193,6 +193,7 @@ unsigned long long b200_debug_decode_step_launches(void) { return decode_persist
 int b200_debug_fa_prefill_profile(unsigned long long *out, int n) { return flash_attn_prefill_profile(out, n); }
 int b200_debug_gemm_fast_profile(unsigned long long *out, int n) { return gemm_fast_profile(out, n); }
 void b200_debug_gemm_fast_wait(int spin_limit, int mute_cta) { gemm_fast_debug_wait(spin_limit, mute_cta); }
+void b200_debug_rows_ring_wait(int spin_limit, int skip_unit) { gemm_rows_ring_debug_wait(spin_limit, skip_unit); }
 int b200_debug_decode_step_times(unsigned long long *out, int n) { return decode_persistent_times(out, n); }
 void b200_debug_decode_step_wait(int spin_limit, int skip_cta, int skip_barrier) { decode_persistent_debug(spin_limit, skip_cta, skip_barrier); }
 

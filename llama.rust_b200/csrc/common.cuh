@@ -152,6 +152,9 @@ int launch_gemm_mma(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *ti
 int launch_gemm_small_multi(int count, const int64_t *n, int64_t k, int64_t m, const uint8_t *const *tiles, ActView acts, float *const *dst,
                             const int64_t *lddst, cudaStream_t s);
 bool gemm_small_multi_enabled();
+int launch_gemm_rows_ring(int count, const int64_t *n, int64_t k, int64_t m, const uint8_t *const *tiles, ActView acts, float *const *dst,
+                          const int64_t *lddst, cudaStream_t s);
+void gemm_rows_ring_debug_wait(int spin_limit, int skip_unit);
 bool gemv_rows_add_fusable(int type, int route, int64_t m);
 int launch_gemm_tcgen05(int mode, int64_t n, int64_t k, int64_t m, const uint8_t *tiles, ActView acts, float *dst, int64_t lddst,
                         cudaStream_t s);

@@ -619,6 +619,10 @@ int launch_gemm_small_multi(int count, const int64_t *n, int64_t k, int64_t m, c
     B200_REQUIRE(k % GROUP_K == 0, "gemm: k = %lld must be a multiple of 256", (long long)k);
     B200_REQUIRE(count >= 1 && count <= 3 && m >= 1 && m < 32, "gemm: %d matrices x %lld activation rows do not fit the few-rows kernel", count, (long long)m);
     B200_REQUIRE(count == 1 || !acts.sum, "gemm: the fused add goes with a single matrix");
+    {   // the persistent form first; -1: not a case for it
+        const int rc = launch_gemm_rows_ring(count, n, k, m, tiles, acts, dst, lddst, s);
+        if (rc != -1) return rc;
+    }
     const int nb = (int)(k / GROUP_K);
     SmallMats mats;
     int64_t total = 0;

@@ -124,3 +124,43 @@ def test_fast_prompt_mat_mul_partial_tile_wait_expiry(monkeypatch):
         assert bits_equal(out.download(np.float32, n * m).reshape(m, n), good)
     finally:
         dev.set_numerics(dev.EXACT)
+
+
+def test_few_rows_ring_mat_mul_wait_expiry():
+    """The persistent few-rows mat-mul (8 to 31 activation rows) passes ring slots from a producer warp to multiply warps to
+    chain warps.  Here the producer of the first CTA never fills its sixth unit: the multiply warp's wait runs out after
+    20000 polls, the CTA winds down without storing, the kernel returns, b200_kernel_error reports code 4, that CTA's row
+    tile is left unwritten, every other tile is what an undisturbed launch gives, and the next launch is undisturbed."""
+    dev = b200.load()
+    dev.set_device(0)
+    n, k, m = 4096, 4096, 16   # 128 row tiles: one per CTA
+    W = synth.weights(orc.Q4_K, n, k, seed=91, period=512)
+    w = dev.Weight(orc.Q4_K, W, k)
+    x = synth.activations(m, k, seed=92)
+    dx = dev.device_array(x)
+    out = dev.DeviceBuffer(4 * n * m)
+    dev.mul_mat_device(w, dx, m, out)
+    dev.synchronize()
+    assert dev.kernel_error() == 0
+    good = out.download(np.float32, n * m).reshape(m, n).copy()
+    want, _ = orc.mul_mat(orc.Q4_K, W, x)
+    assert bits_equal(good, want)
+
+    dev.check(dev.lib.b200_memset(out.ptr, 0xFF, 4 * n * m, None), "memset")
+    dev.synchronize()
+    dev.lib.b200_debug_rows_ring_wait(20000, 5)
+    try:
+        dev.mul_mat_device(w, dx, m, out)
+        dev.synchronize()           # returns: the wait gave up
+    finally:
+        dev.lib.b200_debug_rows_ring_wait(0, -1)
+    assert dev.kernel_error() == 4
+    assert dev.kernel_error() == 0
+    got = out.download(np.uint32, n * m).reshape(m, n)
+    assert (got[:, :32] == 0xFFFFFFFF).all(), "the unfinished tile must not be stored"
+    assert (got[:, 32:] == good.view(np.uint32)[:, 32:]).all()
+
+    dev.mul_mat_device(w, dx, m, out)
+    dev.synchronize()
+    assert dev.kernel_error() == 0
+    assert bits_equal(out.download(np.float32, n * m).reshape(m, n), good)
