@@ -4,7 +4,7 @@
 // dots of a window of super-blocks, then the f32 chain over the window), so a launch costs windows x waves of a
 // phase pair whatever the bytes.  Here one CTA per SM walks its share of the row tiles, and three kinds of warps
 // work on different super-blocks at the same time, handing slots of two rings to one another through mbarriers:
-//   * four producer lanes bring units = (row tile, super-block), 4608 weight bytes each, into the slots of the weight
+//   * sixteen producer lanes bring units = (row tile, super-block), 4608 weight bytes each, into the slots of the weight
 //     ring, one bulk copy per unit;
 //   * eight multiply warps take units round-robin: the unit's activation fragments, sub-block sums and scales straight
 //     from global memory (L2 hits, asked for before the wait for the slot), weight fragments from the slot into
@@ -155,12 +155,13 @@ gemm_q4_K_rows_ring_kernel(const RrMats mats, ActView acts, int nb, int64_t m, i
     if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
         {
-            // ---------------- producer warps (lane 0 of each; unit u goes to warp u % 4): the weights do not depend on the previous
-            // kernel in the stream.  One bulk copy per unit.  A bulk-copy instruction holds its lane for 500 to 900 cycles whatever
-            // its size, hence four issuing lanes; nine 16-byte cp.async copies per lane of a warp instead kept so many L1 misses
-            // outstanding that the multiply warps' activation loads (L2 hits) waited 960 cycles per unit to issue.
-            if (lane == 0) {
-                for (int u = warp; u < units; u += 4) {
+            // ---------------- producer lanes (four of each warp; unit u goes to issuer u % 16, which owns that ring slot): the
+            // weights do not depend on the previous kernel in the stream.  One bulk copy per unit.  A bulk-copy instruction holds
+            // its lane for 500 to 900 cycles whatever its size, hence many issuing lanes; nine 16-byte cp.async copies per lane of
+            // a warp instead kept so many L1 misses outstanding that the multiply warps' activation loads (L2 hits) waited 960
+            // cycles per unit to issue.
+            if (lane < 4) {   // issuer q = 4 warp + lane owns ring slot q: units q, q + 16, ..
+                for (int u = 4 * warp + lane; u < units; u += RR_SLOTS) {
                     const int st = u % RR_SLOTS;
                     const unsigned ph = (unsigned)((u / RR_SLOTS) & 1);
                     const int ti = u / nb;
@@ -368,7 +369,7 @@ gemm_q4_K_rows_ring_kernel(const RrMats mats, ActView acts, int nb, int64_t m, i
     // path the multiply warps have waited for each of them; after an abort the producer lanes wait (bounded) for the last
     // phase they started on each of their slots.
     __syncthreads();
-    if (*(volatile int *)&sh.abort_flag && warp < 4 && lane == 0) {
+    if (*(volatile int *)&sh.abort_flag && warp < 4 && lane < 4) {
         int never = 0;
         for (int i = 0; i < RR_SLOTS; i++)
             if (issued_mask & (1u << i)) rr_wait(&sh.full[i], (issued_parity >> i) & 1u, spin_limit < 4096u ? 4096u : spin_limit, &never);
