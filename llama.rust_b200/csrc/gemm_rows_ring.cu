@@ -16,7 +16,7 @@
 //     summin) for the four sub-block pairs, out = sumf - summin after the tile's last super-block.
 // Measured on the way (4096 x 14336 x 16, SM clocks per unit of one CTA): the activations as 32 more small bulk copies
 // per unit 2700; one producer lane for all units 860, of which 500 to 900 behind each bulk-copy instruction whatever its
-// size, hence four issuing lanes; nine 16-byte cp.async copies per lane of a producer warp instead: the multiply warps'
+// size, hence sixteen issuing lanes; nine 16-byte cp.async copies per lane of a producer warp instead: the multiply warps'
 // activation loads then took 960 cycles per unit to issue behind the outstanding misses.  As it stands a unit costs about
 // 700 cycles (a multiply warp 5000 per unit of its own, the chain 355), against 740 for the per-tile kernel.
 // The arithmetic, and so every bit of the result, is that of gemm_q4_K_small_kernel and of the CPU.
