@@ -32,7 +32,9 @@ namespace b200 {
 
 namespace {
 
-constexpr int RR_SLOTS = 16;
+constexpr int RR_WSLOTS = 32;                  // weight ring: a slot is in use from the copy's issue (a trip to HBM of 3 us under load) until a multiply warp has it in registers
+constexpr int RR_OSLOTS = 8;                   // ring of scaled dots: one slot per multiply warp
+constexpr int RR_ISSUERS = 16;
 constexpr int RR_MUL_WARPS = 8, RR_CHAIN_WARPS = 8;
 constexpr int RR_THREADS = 128 + RR_MUL_WARPS * 32 + RR_CHAIN_WARPS * 32;   // warp group 0: four producer warps
 constexpr unsigned RR_SPIN_LIMIT = 1u << 20;   // polls with a short sleep between them: about a second in all
@@ -58,9 +60,9 @@ struct RrMats {
 // two rings: the weights (producer -> multiply warps; a slot is free again as soon as its unit is in the multiply warp's
 // registers) and the scaled dots (multiply warps -> chain warps)
 struct RrShared {
-    uint8_t w[RR_SLOTS][4608];                 // a unit: 32 row headers, then 8 pieces of 32 rows x 16 bytes
-    RrSlot slot[RR_SLOTS];
-    uint64_t full[RR_SLOTS], wfree[RR_SLOTS], done[RR_SLOTS], empty[RR_SLOTS];
+    uint8_t w[RR_WSLOTS][4608];                // a unit: 32 row headers, then 8 pieces of 32 rows x 16 bytes
+    RrSlot slot[RR_OSLOTS];
+    uint64_t full[RR_WSLOTS], wfree[RR_WSLOTS], done[RR_OSLOTS], empty[RR_OSLOTS];
     int abort_flag;
 };
 
@@ -138,9 +140,11 @@ gemm_q4_K_rows_ring_kernel(const RrMats mats, ActView acts, int nb, int64_t m, i
     const int64_t K = acts.k;
 
     if (tid == 0) {
-        for (int i = 0; i < RR_SLOTS; i++) {
+        for (int i = 0; i < RR_WSLOTS; i++) {
             rr_init(&sh.full[i], 1);
             rr_init(&sh.wfree[i], 1);
+        }
+        for (int i = 0; i < RR_OSLOTS; i++) {
             rr_init(&sh.done[i], 1);
             rr_init(&sh.empty[i], RR_CHAIN_WARPS);
         }
@@ -160,13 +164,13 @@ gemm_q4_K_rows_ring_kernel(const RrMats mats, ActView acts, int nb, int64_t m, i
             // its lane for 500 to 900 cycles whatever its size, hence many issuing lanes; nine 16-byte cp.async copies per lane of
             // a warp instead kept so many L1 misses outstanding that the multiply warps' activation loads (L2 hits) waited 960
             // cycles per unit to issue.
-            if (lane < 4) {   // issuer q = 4 warp + lane owns ring slot q: units q, q + 16, ..
-                for (int u = 4 * warp + lane; u < units; u += RR_SLOTS) {
-                    const int st = u % RR_SLOTS;
-                    const unsigned ph = (unsigned)((u / RR_SLOTS) & 1);
+            if (lane < 4) {   // issuer q = 4 warp + lane: units q, q + 16, .., ring slots q and q + 16 in turn
+                for (int u = 4 * warp + lane; u < units; u += RR_ISSUERS) {
+                    const int st = u % RR_WSLOTS;
+                    const unsigned ph = (unsigned)((u / RR_WSLOTS) & 1);
                     const int ti = u / nb;
                     const int b = u - ti * nb;
-                    if (u >= RR_SLOTS && !rr_wait(&sh.wfree[st], ph ^ 1, spin_limit, &sh.abort_flag)) {
+                    if (u >= RR_WSLOTS && !rr_wait(&sh.wfree[st], ph ^ 1, spin_limit, &sh.abort_flag)) {
                         if (!*(volatile int *)&sh.abort_flag) {
                             atomicExch(err, RR_ERR_WAIT);
                             *(volatile int *)&sh.abort_flag = 1;
@@ -186,7 +190,7 @@ gemm_q4_K_rows_ring_kernel(const RrMats mats, ActView acts, int nb, int64_t m, i
         }
     } else if (warp < 4 + RR_MUL_WARPS) {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 144;");
-        // ---------------- multiply warps: unit u goes to warp u % 8, which also owns ring slots u % 16 of those units
+        // ---------------- multiply warps: unit u goes to warp u % 8, which so sees every phase of the weight slots it reads
         const int mw = warp - 4;
         const int g8 = lane >> 2, t = lane & 3;
         pdl_wait();   // the activations come from the previous kernel in the stream
@@ -204,8 +208,10 @@ gemm_q4_K_rows_ring_kernel(const RrMats mats, ActView acts, int nb, int64_t m, i
         }
         const float *dcol = acts.d + (col0 + (lane & 15) < m ? col0 + (lane & 15) : m - 1) * nb;
         for (int u = mw; u < units; u += RR_MUL_WARPS) {
-            const int st = u % RR_SLOTS;
-            const unsigned ph = (unsigned)((u / RR_SLOTS) & 1);
+            const int st = u % RR_WSLOTS;
+            const unsigned ph = (unsigned)((u / RR_WSLOTS) & 1);
+            const int os = u % RR_OSLOTS;                                // = mw: a multiply warp has one slot of scaled dots
+            const unsigned oph = (unsigned)((u / RR_OSLOTS) & 1);
             const int b = u % nb;
             // the unit's activation fragments, sums and scales: asked for before the wait for the slot
             uint2 ya[4][2][2];
@@ -245,14 +251,14 @@ gemm_q4_K_rows_ring_kernel(const RrMats mats, ActView acts, int nb, int64_t m, i
             __syncwarp();
             if (lane == 0) rr_arrive(&sh.wfree[st]);
             // the slot of the scaled dots: free once the chain warps are through with the unit that had it last
-            if (u >= RR_SLOTS && !rr_wait(&sh.empty[st], ph ^ 1, spin_limit, &sh.abort_flag)) {
+            if (u >= RR_OSLOTS && !rr_wait(&sh.empty[os], oph ^ 1, spin_limit, &sh.abort_flag)) {
                 if (!*(volatile int *)&sh.abort_flag) {
                     atomicExch(err, RR_ERR_WAIT);
                     *(volatile int *)&sh.abort_flag = 1;
                 }
                 break;
             }
-            RrSlot &s = sh.slot[st];
+            RrSlot &s = sh.slot[os];
             // row `lane`: d, dmin as f32 and the eight 6-bit mins one per byte for the chain threads, the eight 6-bit scales
             // one per byte for this warp's lanes (crates/ggml/src/quants.rs:421-429)
             s.hdr[lane] = make_uint4(__float_as_uint(f16_bits_to_f32((uint16_t)(hd.x & 0xffffu))), __float_as_uint(f16_bits_to_f32((uint16_t)(hd.x >> 16))),
@@ -298,7 +304,7 @@ gemm_q4_K_rows_ring_kernel(const RrMats mats, ActView acts, int nb, int64_t m, i
                         s.ig[8 * nt + 2 * t + (e & 1)][(e >> 1) ? rb : ra] = make_int4(v[nt][e][0], v[nt][e][1], v[nt][e][2], v[nt][e][3]);
             }
             __syncwarp();
-            if (lane == 0) rr_arrive(&sh.done[st]);
+            if (lane == 0) rr_arrive(&sh.done[os]);
         }
     } else {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
@@ -345,7 +351,7 @@ gemm_q4_K_rows_ring_kernel(const RrMats mats, ActView acts, int nb, int64_t m, i
             }
             __syncwarp();
             if (lane == 0) rr_arrive(&sh.empty[st]);
-            if (++st == RR_SLOTS) { st = 0; ph ^= 1; }
+            if (++st == RR_OSLOTS) { st = 0; ph ^= 1; }
             if (++b == nb) {
                 const int64_t row = cur.tile * TILE_ROWS + lane;
                 float *dst = mats.dst[cur.me];
@@ -371,7 +377,7 @@ gemm_q4_K_rows_ring_kernel(const RrMats mats, ActView acts, int nb, int64_t m, i
     __syncthreads();
     if (*(volatile int *)&sh.abort_flag && warp < 4 && lane < 4) {
         int never = 0;
-        for (int i = 0; i < RR_SLOTS; i++)
+        for (int i = 0; i < RR_WSLOTS; i++)
             if (issued_mask & (1u << i)) rr_wait(&sh.full[i], (issued_parity >> i) & 1u, spin_limit < 4096u ? 4096u : spin_limit, &never);
     }
 }
