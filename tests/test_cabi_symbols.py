@@ -62,3 +62,18 @@ def test_prompt_kernel_choice_follows_cta_waves():
     assert f(14336, 512, 148) == 4
     # a small GPU changes the wave counts, not the rule; sm_count <= 0 means 148
     assert f(4096, 64, 16) in (3, 4) and f(4096, 512, 0) == 4
+
+
+def test_rows_add_fusable_is_host_arithmetic():
+    """which (weight type, weight rows, activation rows) the few-rows kernels take with the residual add inside: 8 to 31 rows,
+    Q4_K on the 8x8 route with whole groups of four rows, or Q6_K on the tiled route; answered without a device"""
+    mod = b200.load()
+    f = mod.lib.b200_mul_mat_q8_rows_add_fusable
+    f.restype = ctypes.c_int
+    f.argtypes = [ctypes.c_int, ctypes.c_int64, ctypes.c_int64]
+    assert f(mod.Q4_K, 4096, 16) == 1 and f(mod.Q4_K, 4096, 8) == 1 and f(mod.Q4_K, 4096, 28) == 1
+    assert f(mod.Q4_K, 4096, 18) == 0          # two tail rows would go to another chain
+    assert f(mod.Q4_K, 4100, 16) == 0          # rows not a multiple of 8: not the 8x8 route
+    assert f(mod.Q6_K, 4096, 9) == 1 and f(mod.Q6_K, 100, 31) == 1
+    assert f(mod.Q6_K, 4096, 7) == 0 and f(mod.Q6_K, 4096, 32) == 0 and f(mod.Q4_K, 4096, 1) == 0
+    assert f(mod.Q8_0, 4096, 16) == 0 and f(mod.F32, 4096, 16) == 0 and f(mod.Q4_K, 0, 16) == 0
