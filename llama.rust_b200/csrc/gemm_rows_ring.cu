@@ -4,7 +4,7 @@
 // dots of a window of super-blocks, then the f32 chain over the window), so a launch costs windows x waves of a
 // phase pair whatever the bytes.  Here one CTA per SM walks its share of the row tiles, and three kinds of warps
 // work on different super-blocks at the same time, handing slots of two rings to one another through mbarriers:
-//   * sixteen producer lanes bring units = (row tile, super-block), 4608 weight bytes each, into the slots of the weight
+//   * eight producer lanes bring units = (row tile, super-block), 4608 weight bytes each, into the slots of the weight
 //     ring, one bulk copy per unit;
 //   * eight multiply warps take units round-robin: the unit's activation fragments, sub-block sums and scales straight
 //     from global memory (L2 hits, asked for before the wait for the slot), weight fragments from the slot into
@@ -32,9 +32,10 @@ namespace b200 {
 
 namespace {
 
-constexpr int RR_WSLOTS = 32;                  // weight ring: a slot is in use from the copy's issue (a trip to HBM of 3 us under load) until a multiply warp has it in registers
+constexpr int RR_WSLOTS = 24;                  // weight ring: a slot is in use from the copy's issue (a trip to HBM of 3 us under load) until a multiply warp has it in registers
 constexpr int RR_OSLOTS = 8;                   // ring of scaled dots: one slot per multiply warp
-constexpr int RR_ISSUERS = 16;
+constexpr int RR_ISSUERS = 8;                   // producer lanes; divides RR_WSLOTS, so a slot always has the same issuer
+constexpr int RR_XPITCH = 288;                 // a staged activation row: 256 bytes plus 32, so that the eight columns of a fragment load fall in different banks
 constexpr int RR_MUL_WARPS = 8, RR_CHAIN_WARPS = 8;
 constexpr int RR_THREADS = 128 + RR_MUL_WARPS * 32 + RR_CHAIN_WARPS * 32;   // warp group 0: four producer warps
 constexpr unsigned RR_SPIN_LIMIT = 1u << 20;   // polls with a short sleep between them: about a second in all
@@ -62,6 +63,7 @@ struct RrMats {
 struct RrShared {
     uint8_t w[RR_WSLOTS][4608];                // a unit: 32 row headers, then 8 pieces of 32 rows x 16 bytes
     RrSlot slot[RR_OSLOTS];
+    int8_t xs[RR_MUL_WARPS][16 * RR_XPITCH];   // a multiply warp's staging of its unit's activations: column c's 256 values at c * RR_XPITCH
     uint64_t full[RR_WSLOTS], wfree[RR_WSLOTS], done[RR_OSLOTS], empty[RR_OSLOTS];
     int abort_flag;
 };
@@ -164,8 +166,8 @@ gemm_q4_K_rows_ring_kernel(const RrMats mats, ActView acts, int nb, int64_t m, i
             // its lane for 500 to 900 cycles whatever its size, hence many issuing lanes; nine 16-byte cp.async copies per lane of
             // a warp instead kept so many L1 misses outstanding that the multiply warps' activation loads (L2 hits) waited 960
             // cycles per unit to issue.
-            if (lane < 4) {   // issuer q = 4 warp + lane: units q, q + 16, .., ring slots q and q + 16 in turn
-                for (int u = 4 * warp + lane; u < units; u += RR_ISSUERS) {
+            if (lane < 2) {   // issuer q = 2 warp + lane: units q, q + 8, .., ring slots q, q + 8 and q + 16 in turn
+                for (int u = 2 * warp + lane; u < units; u += RR_ISSUERS) {
                     const int st = u % RR_WSLOTS;
                     const unsigned ph = (unsigned)((u / RR_WSLOTS) & 1);
                     const int ti = u / nb;
@@ -194,14 +196,15 @@ gemm_q4_K_rows_ring_kernel(const RrMats mats, ActView acts, int nb, int64_t m, i
         const int mw = warp - 4;
         const int g8 = lane >> 2, t = lane & 3;
         pdl_wait();   // the activations come from the previous kernel in the stream
-        // activation rows this lane loads fragments from (patch nt, column g8 of it) and sums of (two items of 16 columns x 4
-        // sub-block pairs), clamped to the last valid row
-        const int8_t *xcol[2];
+        // the unit's activations come as whole 16-byte pieces (lane = piece lane % 16 of column 2 i + lane / 16: four full lines per
+        // load instruction; 8-byte fragment loads straight from global memory touched 128 lines per unit) into the warp's staging
+        // rows, and from there as fragments; sums: two items of 16 columns x 4 sub-block pairs.  Columns clamped to the last valid one.
+        const int8_t *xbase = acts.qs + 16 * (lane & 15);
+        const int64_t ccol = col0 + (lane >> 4), clast = m - 1;
+        int8_t *xst = sh.xs[mw];
         const int16_t *scol[2];
 #pragma unroll
         for (int j = 0; j < 2; j++) {
-            const int64_t c = col0 + 8 * j + g8 < m ? col0 + 8 * j + g8 : m - 1;
-            xcol[j] = acts.qs + c * K + 8 * t;
             const int i = lane + 32 * j;
             const int64_t cs = col0 + (i >> 2) < m ? col0 + (i >> 2) : m - 1;
             scol[j] = acts.bsums + cs * (K / 16) + 4 * (i & 3);
@@ -213,17 +216,11 @@ gemm_q4_K_rows_ring_kernel(const RrMats mats, ActView acts, int nb, int64_t m, i
             const int os = u % RR_OSLOTS;                                // = mw: a multiply warp has one slot of scaled dots
             const unsigned oph = (unsigned)((u / RR_OSLOTS) & 1);
             const int b = u % nb;
-            // the unit's activation fragments, sums and scales: asked for before the wait for the slot
-            uint2 ya[4][2][2];
+            // the unit's activations, sums and scales: asked for before the wait for the slot
+            uint4 xa[8];
             short4 s4[2];
 #pragma unroll
-            for (int g = 0; g < 4; g++)
-#pragma unroll
-                for (int nt = 0; nt < 2; nt++) {
-                    const int8_t *aq = xcol[nt] + (int64_t)b * 256 + 64 * g;
-                    ya[g][nt][0] = *(const uint2 *)aq;
-                    ya[g][nt][1] = *(const uint2 *)(aq + 32);
-                }
+            for (int i = 0; i < 8; i++) xa[i] = *(const uint4 *)(xbase + (ccol + 2 * i < clast ? ccol + 2 * i : clast) * K + (int64_t)b * 256);
 #pragma unroll
             for (int j = 0; j < 2; j++) s4[j] = *(const short4 *)(scol[j] + (int64_t)b * 16);
             const float da_u = dcol[b];
@@ -234,6 +231,20 @@ gemm_q4_K_rows_ring_kernel(const RrMats mats, ActView acts, int nb, int64_t m, i
                 }
                 break;
             }
+            // the activations through the staging rows into fragments
+            uint2 ya[4][2][2];
+#pragma unroll
+            for (int i = 0; i < 8; i++) *(uint4 *)(xst + (2 * i + (lane >> 4)) * RR_XPITCH + 16 * (lane & 15)) = xa[i];
+            __syncwarp();
+#pragma unroll
+            for (int g = 0; g < 4; g++)
+#pragma unroll
+                for (int nt = 0; nt < 2; nt++) {
+                    const int8_t *aq = xst + (8 * nt + g8) * RR_XPITCH + 64 * g + 8 * t;
+                    ya[g][nt][0] = *(const uint2 *)aq;
+                    ya[g][nt][1] = *(const uint2 *)(aq + 32);
+                }
+            __syncwarp();   // the staging rows are free for the next unit
             // the unit's weights into registers, and its ring slot back to the producers
             const uint8_t *wsm = sh.w[st];
             const uint4 hd = *(const uint4 *)(wsm + lane * 16);
@@ -375,7 +386,7 @@ gemm_q4_K_rows_ring_kernel(const RrMats mats, ActView acts, int nb, int64_t m, i
     // path the multiply warps have waited for each of them; after an abort the producer lanes wait (bounded) for the last
     // phase they started on each of their slots.
     __syncthreads();
-    if (*(volatile int *)&sh.abort_flag && warp < 4 && lane < 4) {
+    if (*(volatile int *)&sh.abort_flag && warp < 4 && lane < 2) {
         int never = 0;
         for (int i = 0; i < RR_WSLOTS; i++)
             if (issued_mask & (1u << i)) rr_wait(&sh.full[i], (issued_parity >> i) & 1u, spin_limit < 4096u ? 4096u : spin_limit, &never);
@@ -386,11 +397,12 @@ gemm_q4_K_rows_ring_kernel(const RrMats mats, ActView acts, int nb, int64_t m, i
 // unit skip_unit unfilled (-1 = none), so that a test can watch a wait run out (the kernel returns, error code 4)
 int g_rr_wait_limit_override = 0, g_rr_skip_unit = -1;
 
-// B200_GEMM_ROWS_RING=0 keeps the per-tile few-rows kernel, =1 takes this one for every shape, default: where it measured
-// faster (rows of 32 super-blocks and more, or more row tiles than two per SM) (read per call)
+// B200_GEMM_ROWS_RING=0 keeps the per-tile few-rows kernel, =2 takes this one only for rows of 32 super-blocks and more or more
+// row tiles than two per SM; default: every shape (a 16-sequence 8B step as a replayed graph: 5.05 ms without, 4.86 with the
+// rule, 4.76 with every shape) (read per call)
 int rows_ring_mode() {
     const char *e = getenv("B200_GEMM_ROWS_RING");
-    return e && e[0] == '0' ? 0 : e && e[0] == '1' ? 1 : 2;
+    return e && e[0] == '0' ? 0 : e && e[0] == '2' ? 2 : 1;
 }
 
 }  // namespace
