@@ -6,19 +6,22 @@
 // work on different super-blocks at the same time, handing slots of two rings to one another through mbarriers:
 //   * eight producer lanes bring units = (row tile, super-block), 4608 weight bytes each, into the slots of the weight
 //     ring, one bulk copy per unit;
-//   * eight multiply warps take units round-robin: the unit's activation fragments, sub-block sums and scales straight
-//     from global memory (L2 hits, asked for before the wait for the slot), weight fragments from the slot into
-//     registers (the slot goes back to the producers at once), one mma.sync (m16n8k32, s8 x s8 -> s32, accumulator
-//     cleared) per sub-block and 16 x 8 patch, the 6-bit scales applied as integers, and the scaled pair dots into a slot
-//     of the second ring together with the rows' unpacked headers and the columns' packed sums;
+//   * eight multiply warps take units round-robin: the unit's activations as whole 16-byte pieces from global memory (L2
+//     hits, asked for before the wait for the slot) through a staging area of the warp's own into fragments, weight
+//     fragments from the slot into registers (the slot goes back to the producers at once), one mma.sync (m16n8k32,
+//     s8 x s8 -> s32, accumulator cleared) per sub-block and 16 x 8 patch, the 6-bit scales applied as integers, and the
+//     scaled pair dots into the warp's slot of the second ring together with the rows' unpacked headers and the columns'
+//     packed sums;
 //   * eight chain warps (thread = one row x two columns) take the units in K order and run the 8x8 gemm chain of
 //     crates/ggml/src/repack.rs:1692-1768: sumf = fma(f32(ig[g]), d * d_x, sumf), summin = fma(f32(mg[g]), dmin * d_x,
 //     summin) for the four sub-block pairs, out = sumf - summin after the tile's last super-block.
 // Measured on the way (4096 x 14336 x 16, SM clocks per unit of one CTA): the activations as 32 more small bulk copies
 // per unit 2700; one producer lane for all units 860, of which 500 to 900 behind each bulk-copy instruction whatever its
-// size, hence sixteen issuing lanes; nine 16-byte cp.async copies per lane of a producer warp instead: the multiply warps'
-// activation loads then took 960 cycles per unit to issue behind the outstanding misses.  As it stands a unit costs about
-// 700 cycles (a multiply warp 5000 per unit of its own, the chain 355), against 740 for the per-tile kernel.
+// size, hence eight issuing lanes; nine 16-byte cp.async copies per lane of a producer warp instead: the multiply warps'
+// activation loads then took 960 cycles per unit to issue behind the outstanding misses; 8-byte activation fragment
+// loads straight from global memory touch 128 lines per unit, the 16-byte pieces 32.  As it stands a unit costs about
+// 700 cycles (a multiply warp 4700 per unit of its own, 2000 of them waiting; the chain 330), against 740 for the
+// per-tile kernel.
 // The arithmetic, and so every bit of the result, is that of gemm_q4_K_small_kernel and of the CPU.
 //
 // Every wait is bounded: a wait that runs out records error code 4 in the device's error word, raises the CTA's
