@@ -77,3 +77,27 @@ def test_rows_add_fusable_is_host_arithmetic():
     assert f(mod.Q6_K, 4096, 9) == 1 and f(mod.Q6_K, 100, 31) == 1
     assert f(mod.Q6_K, 4096, 7) == 0 and f(mod.Q6_K, 4096, 32) == 0 and f(mod.Q4_K, 4096, 1) == 0
     assert f(mod.Q8_0, 4096, 16) == 0 and f(mod.F32, 4096, 16) == 0 and f(mod.Q4_K, 0, 16) == 0
+
+
+def test_rows_add_refuses_bad_arguments_before_touching_a_device():
+    mod = b200.load()
+    f = mod.lib.b200_mul_mat_q8_rows_add
+    f.restype = ctypes.c_int
+    i64, vp = ctypes.c_int64, ctypes.c_void_p
+    f.argtypes = [ctypes.c_int, i64, i64, i64, vp, vp, ctypes.c_int, vp, i64, vp, i64, vp, i64, vp]
+    one = 256
+    # a weight type outside the path's five, a row length that is not a multiple of 256
+    assert f(mod.F32, 4096, 4096, 16, one, one, mod.ACT_Q8_K_MIXED, one, 4096, one, 4096, one, 4096, None) != 0
+    assert f(mod.Q4_K, 4096, 4000, 16, one, one, mod.ACT_Q8_K_MIXED, one, 4096, one, 4096, one, 4096, None) != 0
+    # null pointers, row strides smaller than the rows
+    assert f(mod.Q4_K, 4096, 4096, 16, one, one, mod.ACT_Q8_K_MIXED, one, 4096, None, 4096, one, 4096, None) != 0
+    assert b"null pointer" in mod.lib.b200_last_error()
+    assert f(mod.Q4_K, 4096, 4096, 16, one, one, mod.ACT_Q8_K_MIXED, one, 4096, one, 4000, one, 4096, None) != 0
+    assert b"row strides" in mod.lib.b200_last_error()
+    # a shape the few-rows kernels do not take, the wrong activation quantizer for the route
+    assert f(mod.Q4_K, 4096, 4096, 64, one, one, mod.ACT_Q8_K_MIXED, one, 4096, one, 4096, one, 4096, None) != 0
+    assert b"few-rows kernel" in mod.lib.b200_last_error()
+    assert f(mod.Q4_K, 4096, 4096, 16, one, one, mod.ACT_Q8_K, one, 4096, one, 4096, one, 4096, None) != 0
+    assert b"activation kind" in mod.lib.b200_last_error()
+    # nothing to do
+    assert f(mod.Q4_K, 0, 4096, 16, one, one, mod.ACT_Q8_K_MIXED, one, 4096, one, 4096, one, 4096, None) == 0
